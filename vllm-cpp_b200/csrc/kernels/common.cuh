@@ -1,0 +1,90 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions,
+// launch-error plumbing.  Every exported launcher returns 0 or a negative code and
+// leaves a message readable through vcb_last_error().
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define VCB_API extern "C" __attribute__((visibility("default")))
+
+// largest head size the attention-side kernels take (steps of 16 below it)
+#define VCB_MAX_HEAD_DIM 256
+
+// element type codes shared with the Python side
+enum VcbDtype : int { VCB_F32 = 0, VCB_BF16 = 1 };
+
+// bits of the device status word that kernels set instead of trapping
+enum VcbStatus : int {
+    VCB_STATUS_OK = 0,
+    VCB_STATUS_BAD_TOKEN = 1,      // token id outside the vocabulary
+    VCB_STATUS_BAD_PAGE = 2,       // page id outside the pool
+    VCB_STATUS_WAIT_TIMEOUT = 4,   // a bounded mbarrier wait gave up
+    VCB_STATUS_BAD_POSITION = 8,   // position outside the rotary table
+};
+
+void vcb_set_error(const char* fmt, ...);
+
+#define VCB_CHECK_ARG(cond, ...)                  \
+    do {                                          \
+        if (!(cond)) {                            \
+            vcb_set_error(__VA_ARGS__);           \
+            return -1;                            \
+        }                                         \
+    } while (0)
+
+#define VCB_CHECK_LAUNCH(name)                                                   \
+    do {                                                                         \
+        cudaError_t e_ = cudaGetLastError();                                     \
+        if (e_ != cudaSuccess) {                                                 \
+            vcb_set_error("%s: launch failed: %s", name, cudaGetErrorString(e_)); \
+            return -2;                                                           \
+        }                                                                        \
+    } while (0)
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// load element i of an array whose element type is only known at run time
+__device__ __forceinline__ float load_as_f32(const void* p, int dtype, size_t i) {
+    return dtype == VCB_F32 ? ((const float*)p)[i] : __bfloat162float(((const __nv_bfloat16*)p)[i]);
+}
+__device__ __forceinline__ void store_from_f32(void* p, int dtype, size_t i, float v) {
+    if (dtype == VCB_F32) ((float*)p)[i] = v;
+    else ((__nv_bfloat16*)p)[i] = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The order of
+// the additions depends only on the block size, so equal inputs give equal sums.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}

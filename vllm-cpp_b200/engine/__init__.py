@@ -1,0 +1,3 @@
+from .step import ModelRunner, StepContext, StepEntry
+
+__all__ = ["ModelRunner", "StepContext", "StepEntry"]

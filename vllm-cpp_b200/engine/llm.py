@@ -1,0 +1,164 @@
+"""The Python entry point: load a model folder, submit token lists, step, collect tokens.
+
+Names follow the reference's PagedEngine (src/paged_engine.h:24-47): ``submit_tokens``,
+``step`` returning request ids / new token ids / finished flags and the two token
+counts, ``get_request``, ``remove_request``, ``has_requests``; ``generate`` is the
+loop of its cpu_runner (src/cpu_runner.cpp:85-114) for a list of prompts.  There
+is no tokenizer: prompts are token ids, as with the runner's ``--tokens``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..config import EngineConfig
+from ..models import build_model, expected_tensors, load_config
+from ..runtime import runtime
+from ..sampling import Sampler, SamplingOptions
+from ..weights import RandomWeightStore, open_model_weights
+from .step import ModelRunner, StepEntry
+
+TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+# the reference's generation defaults (src/config.h:97-100)
+TEMPERATURE, TOP_P, REPEAT_PENALTY, MAX_NEW_TOKENS = 0.7, 0.8, 1.1, 2048
+
+
+@dataclass
+class EngineOutput:
+    request_ids: list = field(default_factory=list)
+    new_token_ids: list = field(default_factory=list)
+    finished: list = field(default_factory=list)
+    num_prompt_tokens: int = 0
+    num_generation_tokens: int = 0
+    preempted: list = field(default_factory=list)
+
+
+class LLM:
+    """One model on one GPU with its cache, scheduler and sampler."""
+
+    def __init__(self, model=None, *, config=None, random_seed: int | None = None, engine: EngineConfig | None = None,
+                 **engine_options):
+        """``model``: a folder with config.json and *.safetensors.  Or ``config`` (a typed
+        configuration) with ``random_seed``: random weights drawn on the device, no file."""
+        self.engine_config = engine or EngineConfig(**engine_options)
+        ec = self.engine_config
+        if not torch.cuda.is_available():
+            raise RuntimeError("vllm_cpp_b200 runs on a CUDA device (sm_100a); none is available")
+        self.device = torch.device(ec.device)
+        torch.cuda.set_device(self.device)
+        dtype = TORCH_DTYPES[ec.dtype]
+        if model is not None:
+            self.config = load_config(model)
+            store = open_model_weights(model, dtype, self.device)
+        else:
+            if config is None or random_seed is None:
+                raise ValueError("give a model folder, or a configuration and random_seed")
+            self.config = config
+            store = RandomWeightStore(expected_tensors(config), random_seed, dtype, self.device)
+        self.model = build_model(self.config, dtype, self.device)
+        self.model.load(store)
+        store.release()
+        self.max_model_len = min(ec.max_model_len or self.model.spec.max_positions, self.model.spec.max_positions)
+        self.runner = ModelRunner(self.model, ec.page_size, ec.num_pages, ec.max_num_seqs, dtype, self.device)
+        rt = runtime()
+        self.scheduler = rt.Scheduler(self.runner.layout.runtime_groups(rt, ec.page_size, ec.num_pages),
+                                      ec.max_num_seqs, ec.max_step_tokens, self.max_model_len)
+        self.sampler = Sampler(self.model.spec.vocab_size, ec.max_num_seqs, self.device)
+        self.default_stop_ids = list(self.model.spec.stop_ids)
+        self._options: dict[int, SamplingOptions] = {}
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    # ---- the reference's engine surface ----
+    def submit_tokens(self, prompt_tokens, max_new_tokens: int = MAX_NEW_TOKENS, temperature: float = TEMPERATURE,
+                      top_p: float = TOP_P, *, repeat_penalty: float = REPEAT_PENALTY, seed: int = 0,
+                      stop_ids=None, ignore_eos: bool = False) -> int:
+        rt = runtime()
+        prompt = [int(t) for t in prompt_tokens]
+        for t in prompt:
+            if not 0 <= t < self.model.spec.vocab_size:
+                raise ValueError(f"token id {t} is outside the vocabulary of {self.model.spec.vocab_size}")
+        stops = [] if ignore_eos else list(self.default_stop_ids if stop_ids is None else stop_ids)
+        opts = SamplingOptions(float(temperature), float(top_p), float(repeat_penalty), int(seed))
+        rid = self.scheduler.submit(prompt, int(max_new_tokens),
+                                    rt.SamplingParams(opts.temperature, opts.top_p, opts.repeat_penalty,
+                                                      opts.seed & 0xFFFFFFFFFFFFFFFF), stops)
+        self._options[rid] = opts
+        return rid
+
+    def has_requests(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    def get_request(self, request_id: int):
+        return self.scheduler.request(request_id) if self.scheduler.knows(request_id) else None
+
+    def remove_request(self, request_id: int) -> None:
+        if self.scheduler.knows(request_id):
+            self.scheduler.abort(request_id)
+            self.scheduler.forget(request_id)
+        self._options.pop(request_id, None)
+
+    def step(self) -> EngineOutput:
+        out = EngineOutput()
+        sched = self.scheduler.schedule()
+        out.preempted = list(sched.preempted)
+        out.num_prompt_tokens, out.num_generation_tokens = sched.num_prompt_tokens, sched.num_generation_tokens
+        if not sched.entries:
+            return out
+        cache = self.scheduler.cache()
+        n_groups = cache.num_groups()
+        entries, sampled_entries = [], []
+        for e in sched.entries:
+            tables = [cache.block_table(e.request, g) for g in range(n_groups)]
+            n = len(e.tokens)
+            entries.append(StepEntry(e.slot, e.start_pos, list(e.tokens), tables, [n - 1] if e.sample else []))
+            if e.sample:
+                sampled_entries.append(e)
+        penalised = {e.slot for e in sched.entries if self._options[e.request].repeat_penalty not in (0.0, 1.0)}
+        from .step import StepContext  # noqa: F401  (kept local: the runner builds the context)
+        logits = self.runner.step(entries, check=False)
+        self.h2d_bytes += self.runner.last_h2d_bytes
+        if penalised:
+            self.sampler.observe(self.runner.last_ctx, penalised)
+        tokens: list[int] = []
+        if sampled_entries:
+            toks = self.sampler.sample(logits, [self._options[e.request] for e in sampled_entries],
+                                       [e.gen_step for e in sampled_entries], [e.slot for e in sampled_entries])
+            host = torch.cat([toks, self.runner.status]).cpu()   # one copy back: the tokens and the status word
+            self.d2h_bytes += host.numel() * 4
+            if int(host[-1]):
+                from .. import ops
+                ops.check_status(self.runner.status)
+            tokens = host[:-1].tolist()
+        finished = set(self.scheduler.update(tokens))
+        for e, t in zip(sampled_entries, tokens):
+            out.request_ids.append(e.request)
+            out.new_token_ids.append(t)
+            out.finished.append(e.request in finished)
+        return out
+
+    # ---- convenience ----
+    def generate(self, prompts, max_new_tokens: int = MAX_NEW_TOKENS, temperature: float = TEMPERATURE,
+                 top_p: float = TOP_P, *, repeat_penalty: float = REPEAT_PENALTY, seed: int = 0, stop_ids=None,
+                 ignore_eos: bool = False, on_token=None) -> list[list[int]]:
+        """Generates for every prompt (a list of token ids each); request i samples with seed + i."""
+        rids = [self.submit_tokens(p, max_new_tokens, temperature, top_p, repeat_penalty=repeat_penalty,
+                                   seed=seed + i, stop_ids=stop_ids, ignore_eos=ignore_eos)
+                for i, p in enumerate(prompts)]
+        results = {r: [] for r in rids}
+        while self.has_requests():
+            o = self.step()
+            for rid, tok in zip(o.request_ids, o.new_token_ids):
+                if rid in results:
+                    results[rid].append(tok)
+                    if on_token:
+                        on_token(rid, tok)
+        for r in rids:
+            self.scheduler.forget(r)
+            self._options.pop(r, None)
+        return [results[r] for r in rids]
+
+    def stats(self):
+        return self.scheduler.stats()

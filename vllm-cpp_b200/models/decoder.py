@@ -1,0 +1,88 @@
+"""The generic decoder: embedding, a list of layers, the order they run in, final
+norm, LM head -- built from a :class:`ModelSpec` through the part registries.
+
+The forward pass follows the reference's layer loop (src/model.cpp:1176-1263)
+with two generalisations that are data in the spec: the execution order is a
+list of (layer, cache) runs, so a layer may run twice or read a cache another run
+filled; and each layer names its own parts, so mixers and feed-forwards may
+differ along the depth.  Final norm and LM head run only on the rows whose logits
+were asked for (the reference: last position only, src/model.cpp:1255-1263).
+"""
+from __future__ import annotations
+
+from ..parts.base import BuildContext, CacheSpec
+from ..parts.embedding import LMHead, TokenEmbedding
+from ..registry import ModelSpec, part_class
+from ..weights.loader import TensorSpec, WeightStore
+
+
+def _build_layer(lspec, build: BuildContext):
+    parts = {}
+    for role, (pspec, sub) in lspec.parts.items():
+        family = {"norm1": "norm", "norm2": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}.get(role, role)
+        parts[role] = part_class(family, pspec.kind)(pspec.params, lspec.prefix + sub, build)
+    return part_class("block", lspec.block.kind)(lspec.block.params, lspec.prefix, build, parts)
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, build: BuildContext):
+        self.spec = spec
+        self.build = build
+        self.embedding = TokenEmbedding(spec.embed_tensor, spec.vocab_size, spec.hidden_size)
+        self.layers = [_build_layer(l, build) for l in spec.layers]
+        self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm.params, spec.final_norm_prefix, build)
+        self.lm_head = LMHead(spec.lm_head_tensor, spec.vocab_size, spec.hidden_size, self.embedding)
+        self.order = list(spec.order)
+        for run in self.order:
+            if not 0 <= run.layer < len(self.layers):
+                raise ValueError(f"the execution order names layer {run.layer}, the model has {len(self.layers)}")
+
+    # ---- weights ----
+    def tensor_specs(self) -> list[TensorSpec]:
+        specs = list(self.embedding.tensor_specs())
+        for layer in self.layers:
+            specs += layer.tensor_specs()
+        specs += self.final_norm.tensor_specs() + self.lm_head.tensor_specs()
+        return specs
+
+    def load(self, store: WeightStore) -> None:
+        store.check(self.tensor_specs())
+        self.embedding.bind(store)
+        for layer in self.layers:
+            layer.bind(store)
+        self.final_norm.bind(store)
+        self.lm_head.bind(store)
+
+    # ---- caches ----
+    def cache_specs(self) -> dict[int, CacheSpec]:
+        """cache id -> what the writing run's mixer keeps there."""
+        specs: dict[int, CacheSpec] = {}
+        for run in self.order:
+            if run.cache is None or not run.writes:
+                continue
+            spec = self.layers[run.layer].mixer.cache_spec()
+            if spec is None:
+                raise ValueError(f"layer {run.layer} was given cache {run.cache} but its mixer keeps nothing")
+            if run.cache in specs:
+                raise ValueError(f"cache {run.cache} is written by more than one run")
+            specs[run.cache] = spec
+        for run in self.order:
+            if run.cache is not None and not run.writes:
+                if run.cache not in specs:
+                    raise ValueError(f"layer {run.layer} reads cache {run.cache}, which no run writes")
+                if self.layers[run.layer].mixer.cache_spec() != specs[run.cache]:
+                    raise ValueError(f"layer {run.layer} reads cache {run.cache} of another shape than it expects")
+        return specs
+
+    # ---- one step ----
+    def forward(self, ctx, caches):
+        """ctx: the step's tensors; caches: cache id -> view.  Returns 32-bit logits [rows, vocab]."""
+        resid = self.embedding.forward(ctx.token_ids, ctx.T, ctx.status)
+        pending = None
+        for run in self.order:
+            cache = caches[run.cache] if run.cache is not None else None
+            pending = self.layers[run.layer].forward(resid, pending, ctx, cache, run.writes)
+        if ctx.n_rows == 0:
+            return None
+        y = self.final_norm.forward(resid, pending, rows=ctx.logit_rows)
+        return self.lm_head.forward(y)

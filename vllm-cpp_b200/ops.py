@@ -1,0 +1,212 @@
+"""Python face of the CUDA kernels in ``csrc/kernels`` (loaded through ctypes).
+
+Each function takes torch CUDA tensors, checks shapes and dtypes, and launches
+on torch's current stream.  There is no CPU fallback and no library fallback:
+if the kernel library cannot be built or loaded, importing a kernel raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+STATUS_BITS = {1: "token id outside the vocabulary", 2: "page id outside the pool",
+               4: "a bounded wait inside a kernel gave up", 8: "position outside the rotary table"}
+ITEM_INTS = 6
+
+_lib = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported element type {t.dtype} (float32 or bfloat16)")
+
+
+def lib():
+    """The loaded kernel library; built on first use."""
+    global _lib
+    if _lib is None:
+        path = _build.build_kernels()
+        try:
+            L = ctypes.CDLL(str(path))
+        except OSError as e:
+            raise KernelError(f"cannot load the CUDA kernel library {path}: {e}") from e
+        L.vcb_last_error.restype = ctypes.c_char_p
+        _declare(L)
+        _lib = L
+    return _lib
+
+
+def _declare(L):
+    P, I, LL, F = c_void_p, c_int, c_longlong, c_float
+    sigs = {
+        "vcb_embed_gather": [P, I, P, P, I, I, I, P, P],
+        "vcb_add_rmsnorm": [P, P, I, I, LL, P, I, F, P, I, P, I, I, P],
+        "vcb_swiglu": [P, P, I, I, I, P],
+        "vcb_qknorm_rope_kvwrite": [P, I, P, P, I, I, F, P, I, P, P, P, P, LL, I, I, I, I, I, I, I, P, P],
+        "vcb_sgemm_tn": [P, P, P, I, I, I, LL, LL, LL, P],
+        "vcb_attn_paged": [P, P, I, P, LL, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, P],
+        "vcb_attn_merge": [P, P, P, P, I, I, I, I, I, P],
+        "vcb_sample": [P, LL, I, I, P, P, P, P],
+        "vcb_count_tokens": [P, P, P, I, I, P],
+    }
+    for name, args in sigs.items():
+        fn = getattr(L, name)
+        fn.argtypes = args
+        fn.restype = c_int
+
+
+def _call(name: str, *args):
+    L = lib()
+    rc = getattr(L, name)(*args)
+    if rc != 0:
+        raise KernelError(L.vcb_last_error().decode() or f"{name} failed with code {rc}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, contiguous=True):
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, found {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def check_status(status: torch.Tensor, where: str = "step") -> None:
+    """Reads the device status word (a synchronising copy) and raises on any set bit."""
+    v = int(status.item())
+    if v:
+        status.zero_()
+        what = [msg for bit, msg in STATUS_BITS.items() if v & bit]
+        raise KernelError(f"{where}: a kernel reported: " + "; ".join(what))
+
+
+# --------------------------------------------------------------------------
+
+
+def embed_gather(table, ids, out, status):
+    _need(table, "table"); _need(ids, "ids", torch.int32); _need(out, "out", torch.float32)
+    T, H = out.shape
+    V = table.shape[0]
+    assert table.shape[1] == H and ids.numel() >= T
+    _call("vcb_embed_gather", _p(table), _dt(table), _p(ids), _p(out), T, H, V, _p(status), _stream())
+
+
+def add_rmsnorm(resid, delta, weight, eps, out, rows=None):
+    """resid [T,H] f32 (updated in place with the deltas unless ``rows`` is given);
+    delta None, [T,H] or [S,T,H]; out [n,H] in the activation dtype."""
+    _need(resid, "resid", torch.float32); _need(weight, "weight"); _need(out, "out")
+    T, H = resid.shape
+    S, stride, dptr, ddt = 0, 0, None, F32
+    if delta is not None:
+        _need(delta, "delta")
+        if delta.dim() == 2:
+            delta = delta.unsqueeze(0)
+        S = delta.shape[0]
+        assert delta.shape[1] >= T and delta.shape[2] == H, (delta.shape, resid.shape)
+        stride, dptr, ddt = delta.stride(0), delta.data_ptr(), _dt(delta)
+    n = T if rows is None else rows.numel()
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    assert out.shape[0] >= n and out.shape[1] == H and weight.numel() == H
+    _call("vcb_add_rmsnorm", _p(resid), dptr, ddt, S, stride, _p(weight), _dt(weight), float(eps), _p(out), _dt(out),
+          _p(rows), n, H, _stream())
+
+
+def swiglu(gate_up, out):
+    _need(gate_up, "gate_up"); _need(out, "out", gate_up.dtype)
+    T, I2 = gate_up.shape
+    assert out.shape == (T, I2 // 2)
+    _call("vcb_swiglu", _p(gate_up), _p(out), _dt(out), T, I2 // 2, _stream())
+
+
+def qknorm_rope_kvwrite(qkv, q_weight, k_weight, eps, cos_sin, positions, slot_map, q_out, pages, nh, nkv, hd,
+                        status, has_kv=True, use_norm=True):
+    """pages: one layer's [num_pages, 2, nkv, page_size, hd]; slot_map int32 [T] = page * page_size + offset or -1."""
+    _need(qkv, "qkv"); _need(cos_sin, "cos_sin", torch.float32); _need(positions, "positions", torch.int32)
+    _need(q_out, "q_out", qkv.dtype)
+    T = qkv.shape[0]
+    width = (nh + (2 * nkv if has_kv else 0)) * hd
+    assert qkv.shape[1] == width, (qkv.shape, width)
+    assert cos_sin.shape[1] == hd
+    wdt = F32
+    if use_norm:
+        _need(q_weight, "q_norm weight"); wdt = _dt(q_weight)
+        if has_kv:
+            _need(k_weight, "k_norm weight", q_weight.dtype)
+    page_stride = page_size = num_pages = 0
+    if has_kv:
+        _need(pages, "pages", qkv.dtype); _need(slot_map, "slot_map", torch.int32)
+        num_pages, two, nkv_p, page_size, hd_p = pages.shape
+        assert two == 2 and nkv_p == nkv and hd_p == hd
+        page_stride = pages.stride(0)
+    _call("vcb_qknorm_rope_kvwrite", _p(qkv), _dt(qkv), _p(q_weight), _p(k_weight), wdt, int(use_norm), float(eps),
+          _p(cos_sin), cos_sin.shape[0], _p(positions), _p(slot_map), _p(q_out), _p(pages), page_stride,
+          max(page_size, 1), num_pages, nh, nkv, hd, T, int(has_kv), _p(status), _stream())
+
+
+def sgemm_tn(a, b, out):
+    """out[M,N] = a[M,K] . b[N,K]^T in true 32-bit."""
+    _need(a, "a", torch.float32, contiguous=False); _need(b, "b", torch.float32, contiguous=False)
+    _need(out, "out", torch.float32, contiguous=False)
+    M, K = a.shape
+    N = b.shape[0]
+    assert b.shape[1] == K and out.shape == (M, N)
+    assert a.stride(1) == 1 and b.stride(1) == 1 and out.stride(1) == 1
+    _call("vcb_sgemm_tn", _p(a), _p(b), _p(out), M, N, K, a.stride(0), b.stride(0), out.stride(0), _stream())
+
+
+def attn_paged(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, rows_max, part_o, part_ml,
+               nh, nkv, hd, window, status):
+    _need(q, "q"); _need(out, "out", q.dtype); _need(pages, "pages", q.dtype)
+    for name, t in (("block_table", block_table), ("q_start", q_start), ("q_len", q_len), ("ctx_len", ctx_len),
+                    ("items", items)):
+        _need(t, name, torch.int32)
+    num_pages, two, nkv_p, page_size, hd_p = pages.shape
+    assert two == 2 and nkv_p == nkv and hd_p == hd
+    _call("vcb_attn_paged", _p(q), _p(out), _dt(q), _p(pages), pages.stride(0), _p(block_table), block_table.shape[1],
+          _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, rows_max, _p(part_o), _p(part_ml), nh, nkv, hd,
+          page_size, num_pages, int(window or 0), 1.0 / math.sqrt(hd), _p(status), _stream())
+
+
+def attn_merge(part_o, part_ml, dec_rows, out, n_dec, nh, hd, nslices):
+    _need(part_o, "part_o", torch.float32); _need(part_ml, "part_ml", torch.float32)
+    _need(dec_rows, "dec_rows", torch.int32); _need(out, "out")
+    _call("vcb_attn_merge", _p(part_o), _p(part_ml), _p(dec_rows), _p(out), _dt(out), n_dec, nh, hd, nslices, _stream())
+
+
+def sample(logits, params, counts, out):
+    """logits [R,V] f32; params [R,8] int32 records (see sampling.cu); counts [slots,V] int32 or None."""
+    _need(logits, "logits", torch.float32, contiguous=False); _need(params, "params", torch.int32)
+    _need(out, "out", torch.int32)
+    R, V = logits.shape
+    assert logits.stride(1) == 1 and params.shape == (R, 8) and out.numel() >= R
+    if counts is not None:
+        _need(counts, "counts", torch.int32)
+        assert counts.shape[1] == V
+    _call("vcb_sample", _p(logits), logits.stride(0), R, V, _p(params), _p(counts), _p(out), _stream())
+
+
+def count_tokens(ids, slots, counts, n):
+    _need(ids, "ids", torch.int32); _need(slots, "slots", torch.int32); _need(counts, "counts", torch.int32)
+    _call("vcb_count_tokens", _p(ids), _p(slots), _p(counts), n, counts.shape[1], _stream())

@@ -1,0 +1,147 @@
+"""Grouped-query attention mixer over the paged cache.
+
+Per token: q, k, v projections (one stacked product), RMSNorm of every Q and K
+head over head_dim with one gain vector each (the formula of the reference's
+head_norm sketch, cuda/attention.cu:169-182; its forward never applies it), rotary
+rotation of Q and K, K and V stored in the request's pages, then softmax attention
+of each query over the keys of its own request up to its position (and, with
+``window`` W, not further back than W keys), query head h reading KV head
+h // (heads / kv_heads) with scores scaled by 1/sqrt(head_dim)
+(src/model.cpp:1000-1052), and the output projection.
+
+A run with ``writes=False`` reads a cache that another run filled: only the query
+side is computed, and the part must have been built with ``has_kv`` False.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..registry import PartSpec, part_class
+from ..weights.loader import TensorSpec
+from .base import CacheSpec, Mixer
+from .linear import matmul_tn
+
+DECODE_ROWS = 8     # rows a block of the decode variant of the attention kernel holds
+SPAN_ROWS = 32      # rows of the prompt-portion variant
+MAX_SLICES = 32
+TARGET_BLOCKS = 2 * 148
+
+
+class AttentionPlan:
+    """Work items of the attention kernel for one step and one head layout, on the device."""
+
+    def __init__(self, ctx, nh: int, nkv: int):
+        g = nh // nkv
+        dev = ctx.device
+        dec = [i for i, n in enumerate(ctx.host_q_len) if n == 1]
+        spans = [i for i, n in enumerate(ctx.host_q_len) if n > 1]
+        self.n_dec = len(dec)
+        self.nslices = 1
+        self.dec_items = self.dec_rows = self.span_items = None
+        self.n_span_items = 0
+        if dec:
+            hchunks = -(-g // min(g, DECODE_ROWS))
+            blocks = len(dec) * nkv * hchunks
+            max_ctx = max(ctx.host_ctx_len[i] for i in dec)
+            by_pages = max(1, max_ctx // 256)      # at least 256 keys a slice
+            self.nslices = int(max(1, min(MAX_SLICES, by_pages, -(-TARGET_BLOCKS // blocks))))
+            items = np.zeros((len(dec) * self.nslices, ops.ITEM_INTS), dtype=np.int32)
+            k = 0
+            for n, e in enumerate(dec):
+                for s in range(self.nslices):
+                    items[k] = (e, 0, 1, s, self.nslices, n)
+                    k += 1
+            self.dec_items = torch.from_numpy(items).to(dev)
+            self.dec_rows = torch.tensor([ctx.host_q_start[e] for e in dec], dtype=torch.int32).to(dev)
+        if spans:
+            nq_max = max(1, SPAN_ROWS // min(g, SPAN_ROWS))
+            rows = []
+            for e in spans:
+                n = ctx.host_q_len[e]
+                for q0 in range(0, n, nq_max):
+                    rows.append((e, q0, min(nq_max, n - q0), 0, 1, 0))
+            self.n_span_items = len(rows)
+            self.span_items = torch.tensor(rows, dtype=torch.int32).to(dev)
+
+
+class GQAAttention(Mixer):
+    """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``eps``
+    (of the per-head norms), ``qk_norm`` (bool), ``window`` (0: all keys), ``has_kv``
+    (bool, default True), ``position`` (a PartSpec of the position family).
+    Tensors under ``<prefix>``: q_proj.weight [nh*hd, H], k_proj.weight, v_proj.weight
+    [nkv*hd, H], o_proj.weight [H, nh*hd], q_norm.weight, k_norm.weight [hd]."""
+
+    def __init__(self, params, prefix, build):
+        super().__init__(params, prefix, build)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.nh, self.nkv, self.hd = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"])
+        self.eps = float(p.get("eps", 1e-6))
+        self.qk_norm = bool(p.get("qk_norm", True))
+        self.window = int(p.get("window") or 0)
+        self.has_kv = bool(p.get("has_kv", True))
+        if self.nh % self.nkv:
+            raise ValueError(f"{self.nh} query heads are not a multiple of {self.nkv} KV heads")
+        if self.hd % 16 or not 16 <= self.hd <= 256:
+            raise ValueError(f"head_dim {self.hd} is not supported: the kernels take multiples of 16 from 16 to 256")
+        pos: PartSpec = p["position"]
+        self.rope = part_class("position", pos.kind)(pos.params, prefix, build)
+        self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
+
+    def cache_spec(self):
+        return CacheSpec("kv", num_kv_heads=self.nkv, head_dim=self.hd, window=self.window)
+
+    def tensor_specs(self):
+        p, H, nh, nkv, hd = self.prefix, self.hidden, self.nh, self.nkv, self.hd
+        specs = [TensorSpec(p + "q_proj.weight", (nh * hd, H)), TensorSpec(p + "o_proj.weight", (H, nh * hd))]
+        if self.has_kv:
+            specs += [TensorSpec(p + "k_proj.weight", (nkv * hd, H)), TensorSpec(p + "v_proj.weight", (nkv * hd, H))]
+        if self.qk_norm:
+            specs.append(TensorSpec(p + "q_norm.weight", (hd,), "vector"))
+            if self.has_kv:
+                specs.append(TensorSpec(p + "k_norm.weight", (hd,), "vector"))
+        return specs
+
+    def bind(self, store):
+        p = self.prefix
+        names = [p + "q_proj.weight"] + ([p + "k_proj.weight", p + "v_proj.weight"] if self.has_kv else [])
+        self.w_qkv = store.matrices(names)
+        self.w_o = store.matrix(p + "o_proj.weight")
+        if self.qk_norm:
+            self.q_norm_w = store.vector(p + "q_norm.weight")
+            if self.has_kv:
+                self.k_norm_w = store.vector(p + "k_norm.weight")
+                if self.k_norm_w.dtype != self.q_norm_w.dtype:
+                    self.k_norm_w = self.k_norm_w.float()
+                    self.q_norm_w = self.q_norm_w.float()
+
+    def forward(self, x, ctx, cache, writes=True):
+        if writes != self.has_kv:
+            raise ValueError("an attention part built with has_kv must write its cache, one without must not")
+        T = x.shape[0]
+        nh, nkv, hd = self.nh, self.nkv, self.hd
+        group = ctx.groups[cache.group]
+        qkv = matmul_tn(x, self.w_qkv)
+        q = torch.empty((T, nh * hd), dtype=x.dtype, device=x.device)
+        ops.qknorm_rope_kvwrite(qkv, self.q_norm_w, self.k_norm_w, self.eps, self.rope.table, ctx.positions,
+                                group.slot_map, q, cache.pages, nh, nkv, hd, ctx.status,
+                                has_kv=self.has_kv, use_norm=self.qk_norm)
+        out = torch.empty_like(q)
+        plan = ctx.plan(("attention", nh, nkv), lambda: AttentionPlan(ctx, nh, nkv))
+        common = dict(nh=nh, nkv=nkv, hd=hd, window=self.window, status=ctx.status)
+        if plan.n_dec:
+            S = plan.nslices
+            part_o = part_ml = None
+            if S > 1:
+                part_o = torch.empty((plan.n_dec * nh * S, hd), dtype=torch.float32, device=x.device)
+                part_ml = torch.empty((plan.n_dec * nh * S, 2), dtype=torch.float32, device=x.device)
+            ops.attn_paged(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
+                           plan.dec_items, plan.n_dec * S, DECODE_ROWS, part_o, part_ml, **common)
+            if S > 1:
+                ops.attn_merge(part_o, part_ml, plan.dec_rows, out, plan.n_dec, nh, hd, S)
+        if plan.n_span_items:
+            ops.attn_paged(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
+                           plan.span_items, plan.n_span_items, SPAN_ROWS, None, None, **common)
+        return matmul_tn(out, self.w_o, out_dtype=torch.float32)

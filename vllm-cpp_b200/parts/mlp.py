@@ -1,0 +1,40 @@
+"""SwiGLU feed-forward: down(silu(gate(y)) * up(y)), silu(z) = z / (1 + exp(-z))
+(src/model.cpp:964-966, 1237-1244), with separate input and output buffers for the
+down projection.  gate and up are stacked into one [2I, H] matrix at load so one
+product yields both."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..weights.loader import TensorSpec
+from .base import FeedForward
+from .linear import matmul_tn
+
+
+class SwiGLUMLP(FeedForward):
+    """params: ``hidden_size``, ``intermediate_size``.
+    Tensors: ``<prefix>gate_proj.weight`` [I,H], ``up_proj.weight`` [I,H], ``down_proj.weight`` [H,I]."""
+
+    def __init__(self, params, prefix, build):
+        super().__init__(params, prefix, build)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.w_gate_up = None
+        self.w_down = None
+
+    def tensor_specs(self):
+        p, H, I = self.prefix, self.hidden, self.inter
+        return [TensorSpec(p + "gate_proj.weight", (I, H)), TensorSpec(p + "up_proj.weight", (I, H)),
+                TensorSpec(p + "down_proj.weight", (H, I))]
+
+    def bind(self, store):
+        p = self.prefix
+        self.w_gate_up = store.matrices([p + "gate_proj.weight", p + "up_proj.weight"])
+        self.w_down = store.matrix(p + "down_proj.weight")
+
+    def forward(self, x, ctx):
+        gate_up = matmul_tn(x, self.w_gate_up)
+        act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
+        ops.swiglu(gate_up, act)
+        return matmul_tn(act, self.w_down, out_dtype=torch.float32)

@@ -1,0 +1,38 @@
+"""Rotary position encoding: the table of cosines and sines.
+
+inv_freq_i = theta^(-2i/head_dim), angle = position * inv_freq_i
+(src/model.cpp:582-589, 979-982); ``theta`` is a parameter (the reference's CPU
+path uses the constant ROPE_BASE instead of config.json's rope_theta,
+src/config.h:43).  The table [max_positions, head_dim] holds head_dim/2 cosines
+then head_dim/2 sines per position, computed in 64-bit on the host and rounded
+once to 32-bit, so large positions lose nothing to a fast sincos on the device.
+The rotation itself pairs lanes (i, i + head_dim/2) (src/mlx_backend.cpp:411-412,
+cuda/attention_kernels.cuh:275-287) and is applied inside the fused
+norm-rotate-store kernel.
+"""
+from __future__ import annotations
+
+import torch
+
+from .base import PositionEncoding
+
+
+class RotaryEmbedding(PositionEncoding):
+    """params: ``head_dim``, ``theta``, ``max_positions``."""
+
+    def __init__(self, params, prefix, build):
+        super().__init__(params, prefix, build)
+        self.head_dim = int(params["head_dim"])
+        self.theta = float(params["theta"])
+        self.max_positions = int(params["max_positions"])
+        key = ("rope_table", self.head_dim, self.theta, self.max_positions)
+        if key not in build.shared:
+            build.shared[key] = self._make_table().to(build.device)
+        self.table = build.shared[key]
+
+    def _make_table(self) -> torch.Tensor:
+        half = self.head_dim // 2
+        i = torch.arange(half, dtype=torch.float64)
+        inv_freq = self.theta ** (-2.0 * i / self.head_dim)
+        ang = torch.arange(self.max_positions, dtype=torch.float64)[:, None] * inv_freq[None, :]
+        return torch.cat([torch.cos(ang), torch.sin(ang)], dim=1).to(torch.float32).contiguous()

@@ -1,0 +1,79 @@
+"""Choosing next tokens from logits, on the device.
+
+Options and their defaults are the reference's: temperature 0.7, top-p 0.8 and a
+repetition penalty of 1.1 over everything the request has seen so far
+(src/config.h:97-99; src/model.cpp:1291-1352; history = prompt + generated in the
+engine path, src/paged_engine.cpp:544-549).  temperature <= 0 is greedy
+(src/mlx_backend.cpp:516-524).  A request's draw at generated-token index ``step``
+depends only on (seed, step) and its logits, so a request that was preempted and
+recomputed continues with the same tokens.
+
+The occurrence counts behind the penalty are per-request state of fixed size:
+one row of ``[slots, vocab]`` int32 per state slot, cleared when a request's
+first tokens arrive, bumped for every token fed to the model.
+"""
+from __future__ import annotations
+
+import struct
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from .. import ops
+
+
+@dataclass(frozen=True)
+class SamplingOptions:
+    temperature: float = 0.7
+    top_p: float = 0.8
+    repeat_penalty: float = 1.1
+    seed: int = 0
+
+
+def _f2i(x: float) -> int:
+    return struct.unpack("<i", struct.pack("<f", float(x)))[0]
+
+
+class Sampler:
+    def __init__(self, vocab_size: int, num_slots: int, device):
+        self.vocab, self.num_slots, self.device = vocab_size, num_slots, torch.device(device)
+        self.counts = None   # allocated when the first request with a penalty shows up
+
+    def _need_counts(self):
+        if self.counts is None:
+            self.counts = torch.zeros((self.num_slots, self.vocab), dtype=torch.int32, device=self.device)
+
+    def observe(self, ctx, penalised_slots: set) -> None:
+        """Counts the step's tokens into their requests' rows (requests without a penalty are skipped)."""
+        if not penalised_slots:
+            return
+        self._need_counts()
+        fresh = [e.slot for e in ctx.entries if e.start_pos == 0 and e.slot in penalised_slots]
+        if fresh:
+            self.counts.index_fill_(0, torch.tensor(fresh, dtype=torch.long, device=self.device), 0)
+        slot_of_token = np.empty(ctx.T, dtype=np.int32)
+        for i, e in enumerate(ctx.entries):
+            s = ctx.host_q_start[i]
+            slot_of_token[s:s + len(e.tokens)] = e.slot if e.slot in penalised_slots else -1
+        slots = torch.from_numpy(slot_of_token).to(self.device)
+        ops.count_tokens(ctx.token_ids, slots, self.counts, ctx.T)
+
+    def sample(self, logits: torch.Tensor, options: list[SamplingOptions], steps: list[int], slots: list[int]) -> torch.Tensor:
+        """One token per row of ``logits``; returns int32 [rows] on the device."""
+        R = logits.shape[0]
+        rec = np.zeros((R, 8), dtype=np.int32)
+        use_counts = False
+        for i, (o, step, slot) in enumerate(zip(options, steps, slots)):
+            pen = o.repeat_penalty if o.repeat_penalty and o.repeat_penalty > 0 else 1.0
+            use_counts |= pen != 1.0
+            seed = int(o.seed) & 0xFFFFFFFFFFFFFFFF
+            rec[i] = (_f2i(o.temperature), _f2i(o.top_p), _f2i(pen), slot if pen != 1.0 else -1,
+                      np.uint32(seed & 0xFFFFFFFF).view(np.int32), np.uint32(seed >> 32).view(np.int32),
+                      np.uint32(step & 0xFFFFFFFF).view(np.int32), 0)
+        if use_counts:
+            self._need_counts()
+        params = torch.from_numpy(rec).to(self.device)
+        out = torch.empty(R, dtype=torch.int32, device=self.device)
+        ops.sample(logits, params, self.counts if use_counts else None, out)
+        return out
