@@ -1,0 +1,340 @@
+"""Each CUDA kernel alone against a plain PyTorch 32/64-bit restatement of the same op, at
+sizes other than the engine's tiny models (odd widths, head sizes in steps of 16, MQA/MHA/GQA)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("table_dtype", DTYPES)
+def test_embed_gather(table_dtype):
+    from vllm_cpp_b200 import ops
+    V, H, T = 301, 72, 19
+    table = torch.randn(V, H, device=dev()).to(table_dtype)
+    ids = torch.randint(0, V, (T,), device=dev(), dtype=torch.int32)
+    out = torch.empty(T, H, device=dev())
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    ops.embed_gather(table, ids, out, status)
+    assert torch.equal(out, table.float()[ids.long()])
+    assert status.item() == 0
+    ids[3] = V  # outside the vocabulary: reported, row zeroed, nothing read out of bounds
+    ops.embed_gather(table, ids, out, status)
+    assert status.item() == 1 and out[3].abs().max().item() == 0
+    status.zero_()
+
+
+@pytest.mark.parametrize("H", [72, 1000, 4096, 14000])
+@pytest.mark.parametrize("S", [0, 1, 3])
+@pytest.mark.parametrize("out_dtype,w_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                               (torch.bfloat16, torch.float32)])
+def test_add_rmsnorm(H, S, out_dtype, w_dtype):
+    from vllm_cpp_b200 import ops
+    T, eps = 7, 1e-5
+    resid = torch.randn(T, H, device=dev())
+    delta = torch.randn(S, T, H, device=dev()) if S else None
+    w = (1 + 0.1 * torch.randn(H, device=dev())).to(w_dtype)
+    out = torch.empty(T, H, device=dev(), dtype=out_dtype)
+    x = resid.double() + (delta.double().sum(0) if S else 0)
+    want = w.double() * x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+    r = resid.clone()
+    ops.add_rmsnorm(r, delta, w, eps, out)
+    torch.testing.assert_close(out.double(), want, **tol(out_dtype))
+    torch.testing.assert_close(r.double(), x, rtol=1e-6, atol=1e-6)
+    # gathered rows: stream untouched
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32, device=dev())
+    r2 = resid.clone()
+    out2 = torch.empty(3, H, device=dev(), dtype=out_dtype)
+    ops.add_rmsnorm(r2, delta, w, eps, out2, rows)
+    torch.testing.assert_close(out2.double(), want[rows.long()], **tol(out_dtype))
+    assert torch.equal(r2, resid)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    from vllm_cpp_b200 import ops
+    T, I = 5, 200
+    gu = (3 * torch.randn(T, 2 * I, device=dev())).to(dtype)
+    out = torch.empty(T, I, device=dev(), dtype=dtype)
+    ops.swiglu(gu, out)
+    g, u = gu[:, :I].double(), gu[:, I:].double()
+    torch.testing.assert_close(out.double(), g / (1 + torch.exp(-g)) * u, **tol(dtype))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (3, 200, 96), (17, 384, 200), (130, 67, 33), (64, 64, 1)])
+def test_sgemm_tn(M, N, K):
+    from vllm_cpp_b200 import ops
+    a, b = torch.randn(M, K, device=dev()), torch.randn(N, K, device=dev())
+    out = torch.empty(M, N, device=dev())
+    ops.sgemm_tn(a, b, out)
+    # 32-bit accumulation of K products of unit-scale numbers: error bound about K * 2^-24 * |a||b|
+    torch.testing.assert_close(out.double(), a.double() @ b.double().T, rtol=1e-5, atol=K * 2.0 ** -24 * 16)
+    # a row's result does not depend on what else is in the batch
+    out1 = torch.empty(1, N, device=dev())
+    ops.sgemm_tn(a[M - 1:M].contiguous(), b, out1)
+    assert torch.equal(out1[0], out[M - 1])
+
+
+def rope_table(hd, theta, n):
+    i = torch.arange(hd // 2, dtype=torch.float64)
+    ang = torch.arange(n, dtype=torch.float64)[:, None] * theta ** (-2 * i / hd)[None]
+    return torch.cat([ang.cos(), ang.sin()], 1).float().to(dev())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (6, 2, 32), (5, 5, 48), (8, 1, 128), (3, 1, 256)])
+def test_qknorm_rope_kvwrite(dtype, nh, nkv, hd):
+    from vllm_cpp_b200 import ops
+    T, ps, num_pages, eps, max_pos = 11, 4, 9, 1e-5, 64
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=dev()).to(dtype)
+    qw = (1 + 0.1 * torch.randn(hd, device=dev())).to(dtype)
+    kw = (1 + 0.1 * torch.randn(hd, device=dev())).to(dtype)
+    table = rope_table(hd, 1e4, max_pos)
+    pos = torch.randint(0, max_pos, (T,), device=dev(), dtype=torch.int32)
+    slots = torch.randperm(num_pages * ps, device=dev())[:T].to(torch.int32)
+    slots[4] = -1  # a padded token stores nothing
+    pages = torch.zeros(num_pages, 2, nkv, ps, hd, device=dev(), dtype=dtype)
+    q_out = torch.empty(T, nh * hd, device=dev(), dtype=dtype)
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    ops.qknorm_rope_kvwrite(qkv, qw, kw, eps, table, pos, slots, q_out, pages, nh, nkv, hd, status)
+    assert status.item() == 0
+    x = qkv.double().view(T, nh + 2 * nkv, hd)
+
+    def norm_rope(h, w):
+        h = w.double() * h / torch.sqrt((h * h).mean(-1, keepdim=True) + eps)
+        c, s = table[pos.long(), :hd // 2].double()[:, None], table[pos.long(), hd // 2:].double()[:, None]
+        a, b = h[..., :hd // 2], h[..., hd // 2:]
+        return torch.cat([a * c - b * s, b * c + a * s], -1)
+
+    q_want, k_want, v_want = norm_rope(x[:, :nh], qw), norm_rope(x[:, nh:nh + nkv], kw), x[:, nh + nkv:]
+    torch.testing.assert_close(q_out.double().view(T, nh, hd), q_want, **tol(dtype))
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        torch.testing.assert_close(pages[s // ps, 0, :, s % ps].double(), k_want[t], **tol(dtype))
+        torch.testing.assert_close(pages[s // ps, 1, :, s % ps].double(), v_want[t], **tol(dtype))
+    written = {int(s) for s in slots if s >= 0}
+    for s in range(num_pages * ps):
+        if s not in written:
+            assert pages[s // ps, :, :, s % ps].abs().max().item() == 0
+
+
+def build_paged(seqs_kv, nkv, hd, ps, dtype, num_pages, shuffle_seed=0):
+    """Scatters per-request K/V [len, nkv, hd] into shuffled pages; returns pages and block tables."""
+    g = torch.Generator().manual_seed(shuffle_seed)
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    pages = torch.full((num_pages, 2, nkv, ps, hd), float("nan"), device=dev(), dtype=dtype)
+    tables = []
+    for k, v in seqs_kv:
+        n = k.shape[0]
+        tab = [perm.pop() for _ in range(-(-n // ps))]
+        for p in range(n):
+            pages[tab[p // ps], 0, :, p % ps] = k[p].to(dtype)
+            pages[tab[p // ps], 1, :, p % ps] = v[p].to(dtype)
+        tables.append(tab)
+    return pages, tables
+
+
+def attention_reference(q, k, v, start, window):
+    """q [n, nh, hd] at positions start..start+n-1 over k, v [start+n, nkv, hd] (64-bit)."""
+    n, nh, hd = q.shape
+    nkv = k.shape[1]
+    out = torch.empty(n, nh, hd, dtype=torch.float64)
+    kpos = torch.arange(k.shape[0])
+    for i in range(n):
+        p = start + i
+        ok = kpos <= p
+        if window:
+            ok &= kpos > p - window
+        for h in range(nh):
+            s = (k[:, h // (nh // nkv)] @ q[i, h]) / math.sqrt(hd)
+            s = s.masked_fill(~ok, float("-inf"))
+            out[i, h] = torch.softmax(s, 0) @ v[:, h // (nh // nkv)]
+    return out
+
+
+def run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft=None):
+    """shapes: list of (cached tokens before the step, query tokens of the step)."""
+    from vllm_cpp_b200 import ops
+    from vllm_cpp_b200.parts.attention import AttentionPlan, DECODE_ROWS, SPAN_ROWS
+    torch.manual_seed(1)
+    seqs, qs = [], []
+    for start, n in shapes:
+        k = torch.randn(start + n, nkv, hd, dtype=torch.float64)
+        v = torch.randn(start + n, nkv, hd, dtype=torch.float64)
+        q = torch.randn(n, nh, hd, dtype=torch.float64)
+        if craft:
+            craft(q, k, v, start, n)
+        # what the kernel sees is rounded to its storage type
+        k, v, q = k.to(dtype).double(), v.to(dtype).double(), q.to(dtype).double()
+        seqs.append((k, v))
+        qs.append(q)
+    num_pages = sum(-(-(s + n) // ps) for s, n in shapes) + 3
+    pages, tables = build_paged(seqs, nkv, hd, ps, dtype, num_pages)
+
+    class Ctx:
+        pass
+    ctx = Ctx()
+    ctx.device = dev()
+    ctx.host_q_len = [n for _, n in shapes]
+    ctx.host_ctx_len = [s + n for s, n in shapes]
+    ctx.host_q_start = list(np.cumsum([0] + ctx.host_q_len[:-1]))
+    plan = AttentionPlan(ctx, nh, nkv)
+    E, T = len(shapes), sum(ctx.host_q_len)
+    mb = max(len(t) for t in tables)
+    bt = torch.full((E, mb), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        bt[i, :len(t)] = torch.tensor(t)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())
+    q_flat = torch.cat(qs).to(dtype).to(dev()).view(T, nh * hd)
+    out = torch.full_like(q_flat, float("nan"))
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    args = (pages, bt.to(dev()), i32(ctx.host_q_start), i32(ctx.host_q_len), i32(ctx.host_ctx_len))
+    if plan.n_dec:
+        S = plan.nslices
+        po = torch.empty(plan.n_dec * nh * S, hd, device=dev()) if S > 1 else None
+        pm = torch.empty(plan.n_dec * nh * S, 2, device=dev()) if S > 1 else None
+        ops.attn_paged(q_flat, out, *args, plan.dec_items, plan.n_dec * S, DECODE_ROWS, po, pm, nh, nkv, hd, window, status)
+        if S > 1:
+            ops.attn_merge(po, pm, plan.dec_rows, out, plan.n_dec, nh, hd, S)
+    if plan.n_span_items:
+        ops.attn_paged(q_flat, out, *args, plan.span_items, plan.n_span_items, SPAN_ROWS, None, None, nh, nkv, hd, window, status)
+    assert status.item() == 0
+    got = out.double().cpu().view(T, nh, hd)
+    t = 0
+    for (start, n), q, (k, v) in zip(shapes, qs, seqs):
+        want = attention_reference(q, k, v, start, window)
+        torch.testing.assert_close(got[t:t + n], want, **tol(dtype))
+        t += n
+    return plan
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(4, 2, 16, 4), (6, 2, 32, 8), (8, 8, 64, 16), (4, 1, 128, 16),
+                                          (12, 1, 48, 16), (2, 1, 256, 32), (40, 2, 16, 8)])
+def test_attention_mixed_batch(dtype, nh, nkv, hd, ps):
+    # prompt portions of several sizes beside single decoded tokens, page edges on both sides
+    run_attention(dtype, nh, nkv, hd, ps, 0, [(0, 7), (31, 1), (0, 1), (13, 34), (63, 2), (200, 1), (16, 16)])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 5, 24, 100])
+def test_attention_window(dtype, window):
+    run_attention(dtype, 6, 2, 32, 8, window, [(0, 40), (57, 1), (23, 3), (130, 1)])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_long_decode_is_sliced(dtype):
+    plan = run_attention(dtype, 8, 2, 64, 16, 0, [(3000, 1), (1025, 1)])
+    assert plan.nslices > 1
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("far", [0, 3, 511, 512, 1777])
+def test_attention_far_key_stands_out(dtype, far):
+    """One key among two thousand carries nearly all the weight: a kernel that skips or misplaces it shows."""
+    def craft(q, k, v, start, n):
+        q[:] = q / q.norm(dim=-1, keepdim=True) * 8
+        k[far] = q[0, 0] * 4
+        v[far] = 50.0
+    run_attention(dtype, 4, 4, 64, 16, 0, [(2047, 1)], craft)
+    run_attention(dtype, 4, 4, 64, 16, 0, [(2040, 8)], craft)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("offset", [0, 1])
+def test_attention_window_edge(dtype, offset):
+    """A dominant key exactly at the window's first position must count; one position earlier it must not."""
+    W, start = 24, 100
+    def craft(q, k, v, s, n):
+        q[:] = q / q.norm(dim=-1, keepdim=True) * 8
+        edge = (s + n - 1) - W + 1 - offset      # offset 0: last key inside; 1: first key outside
+        k[edge] = q[-1, 0] * 4
+        v[edge] = 50.0
+    run_attention(dtype, 2, 2, 32, 8, W, [(start, 1)], craft)
+    run_attention(dtype, 2, 2, 32, 8, W, [(start - 5, 6)], craft)
+
+
+def plain_sample(*a, **k):
+    import plain_qwen3
+    return plain_qwen3.sample(*a, **k)
+
+
+@pytest.mark.parametrize("V", [50, 1000, 20011])
+def test_sampling_matches_plain(V):
+    from vllm_cpp_b200.sampling import Sampler, SamplingOptions
+    rng = np.random.default_rng(V)
+    logits = torch.tensor(rng.normal(0, 2, size=(6, V)), dtype=torch.float32)
+    logits[1, 7] = logits[1].max() + 0.0   # a tie for greedy: lowest index wins
+    logits[1, 3] = logits[1, 7]
+    opts = [SamplingOptions(0.0, 1.0, 1.0, 0), SamplingOptions(0.0, 0.8, 1.0, 0), SamplingOptions(0.8, 1.0, 1.0, 4),
+            SamplingOptions(1.3, 0.8, 1.0, 5), SamplingOptions(0.7, 0.5, 1.2, 6), SamplingOptions(0.0, 1.0, 1.5, 7)]
+    steps = [0, 1, 2, 3, 4, 5]
+    slots = [0, 1, 2, 3, 4, 5]
+    s = Sampler(V, 6, dev())
+    history = {4: rng.integers(0, V, 30).tolist() + [int(logits[4].argmax())] * 3, 5: [int(logits[5].argmax())] * 4}
+    s._need_counts()
+    for slot, h in history.items():
+        for t in h:
+            s.counts[slot, t] += 1
+    got = s.sample(logits.to(dev()), opts, steps, slots).cpu().tolist()
+    for i, o in enumerate(opts):
+        want = plain_sample(logits[i].numpy(), temperature=o.temperature, top_p=o.top_p, repeat_penalty=o.repeat_penalty,
+                            history=history.get(i, ()), seed=o.seed, step=steps[i])
+        assert got[i] == want, (i, got[i], want)
+    assert got[1] == 3
+
+
+def test_sampling_distribution():
+    """Empirical frequencies of seeded draws follow softmax(logits / T) cut to the nucleus."""
+    from vllm_cpp_b200.sampling import Sampler, SamplingOptions
+    V, N = 12, 4000
+    logits = torch.tensor([2.0, 1.5, 1.0, 0.5, 0.0, -0.5, -1.0, -1.5, -2.0, -2.5, -3.0, -9.0])
+    rows = logits[None].repeat(N, 1).to(dev())
+    s = Sampler(V, 1, dev())
+    for top_p in (1.0, 0.7):
+        toks = s.sample(rows, [SamplingOptions(0.9, top_p, 1.0, 123)] * N, list(range(N)), [0] * N).cpu().numpy()
+        p = torch.softmax(logits.double() / 0.9, 0).numpy()
+        if top_p < 1:
+            order = np.argsort(-p)
+            keep = order[:int(np.searchsorted(np.cumsum(p[order]), top_p)) + 1]
+            mask = np.zeros(V, bool); mask[keep] = True
+            p = np.where(mask, p, 0); p /= p.sum()
+            assert set(np.unique(toks)) <= set(keep.tolist())
+        freq = np.bincount(toks, minlength=V) / N
+        assert np.abs(freq - p).max() < 0.03
+
+
+def test_count_tokens():
+    from vllm_cpp_b200 import ops
+    V = 37
+    ids = torch.tensor([1, 1, 5, 36, 1, 2], dtype=torch.int32, device=dev())
+    slots = torch.tensor([0, 0, 1, 1, -1, 0], dtype=torch.int32, device=dev())
+    counts = torch.zeros(2, V, dtype=torch.int32, device=dev())
+    ops.count_tokens(ids, slots, counts, 6)
+    assert counts[0, 1] == 2 and counts[0, 2] == 1 and counts[1, 5] == 1 and counts[1, 36] == 1 and counts.sum() == 5
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    from vllm_cpp_b200 import ops
+    with pytest.raises(ops.KernelError, match="CUDA tensor"):
+        ops.swiglu(torch.zeros(2, 4), torch.zeros(2, 2))
+    q = torch.zeros(1, 24, device=dev())
+    pages = torch.zeros(2, 2, 1, 4, 24, device=dev())
+    z = torch.zeros(1, dtype=torch.int32, device=dev())
+    items = torch.zeros(1, 6, dtype=torch.int32, device=dev())
+    with pytest.raises(ops.KernelError, match="multiple of 16"):
+        ops.attn_paged(q, q.clone(), pages, z.view(1, 1), z, z, z, items, 1, 8, None, None, 1, 1, 24, 0, z)

@@ -1,0 +1,67 @@
+"""bin/trace_run against the plain implementation: the same requests whole, with the last 32
+tokens one by one, in portions of changing size down to two tokens, and mixed (up to four live
+requests, pages used again) -- in 32-bit and in bfloat16, on both tiny configurations."""
+import numpy as np
+import pytest
+
+import replay_util as R
+from conftest import TINY, TINY_PAGE, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [40, 75, 128, 33, 90, 64, 17, 2], "B": [1, 7, 33, 64, 150, 256, 97, 130]}
+# largest |difference| allowed, as a fraction of the largest |logit| of the reference row set
+REL_TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+
+
+def make_requests(name):
+    vocab = TINY[name]["vocab_size"]
+    return {f"r{i}": random_tokens(vocab, n, 100 * i + len(name)) for i, n in enumerate(LENGTHS[name])}
+
+
+def compare(name, dtype, trace, out_dir, requests, plain_logits):
+    vocab = TINY[name]["vocab_size"]
+    worst = 0.0
+    for step, want in enumerate(trace.wanted):
+        got = R.read_step(out_dir, step, vocab)
+        if not want:
+            assert got is None
+            continue
+        assert got is not None and got.shape == (len(want), vocab), f"step {step}: {None if got is None else got.shape}"
+        ref = np.stack([plain_logits(name, requests[rid])[pos] for rid, pos in want])
+        scale = np.abs(ref).max()
+        err = np.abs(got - ref).max(axis=1) / scale
+        bad = np.nonzero(err > REL_TOL[dtype])[0]
+        assert len(bad) == 0, (f"{name} {dtype}: step {step}, first wrong row {want[bad[0]]} (request, position): "
+                               f"relative error {err[bad[0]]:.3e} > {REL_TOL[dtype]}")
+        worst = max(worst, err.max())
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+def test_replay(name, dtype, mode, model_dirs, plain_logits, tmp_path):
+    requests = make_requests(name)
+    trace = {"whole": R.whole, "tail": R.tail_one_by_one, "portions": R.portions, "mixed": R.mixed}[mode](requests)
+    out = R.run_trace(model_dirs[name], dtype, trace, tmp_path / "out", TINY_PAGE[name])
+    worst = compare(name, dtype, trace, out, requests, plain_logits)
+    print(f"{name} {dtype} {mode}: worst relative error {worst:.3e}, pool {trace.max_tokens} tokens, {len(trace.steps)} steps")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_modes_agree_with_each_other(dtype, model_dirs, tmp_path):
+    """Cutting and batching change the logits by rounding only (far below the distance to the reference)."""
+    name = "B"
+    requests = make_requests(name)
+    vocab = TINY[name]["vocab_size"]
+    rows = {}
+    for mode, build in (("whole", R.whole), ("mixed", R.mixed)):
+        trace = build(requests)
+        out = R.run_trace(model_dirs[name], dtype, trace, tmp_path / mode, TINY_PAGE[name])
+        for step, want in enumerate(trace.wanted):
+            got = R.read_step(out, step, vocab)
+            for i, key in enumerate(want):
+                rows.setdefault(key, {})[mode] = got[i]
+    worst = max(np.abs(v["whole"] - v["mixed"]).max() / np.abs(v["whole"]).max() for v in rows.values())
+    assert worst < (1e-5 if dtype == "float32" else 2e-2), worst
