@@ -1,0 +1,117 @@
+"""Generation through the Python entry point and the command line against the plain implementation:
+greedy and seeded sampling, portions under a token budget, preemption by recompute, long decoding."""
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from conftest import ROOT, TINY, TINY_PAGE, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+def make_llm(model_dir, name, dtype="float32", **kw):
+    from vllm_cpp_b200 import LLM, EngineConfig
+    opts = dict(dtype=dtype, page_size=TINY_PAGE[name], max_tokens=1024, max_num_seqs=4, max_step_tokens=16)
+    opts.update(kw)
+    return LLM(model_dir, engine=EngineConfig(**opts))
+
+
+def plain_generate(plain_models, name, prompt, n, **kw):
+    import plain_qwen3
+    cfg, w = plain_models[name]
+    return plain_qwen3.generate(cfg, w, prompt, n, **kw)
+
+
+def test_greedy_config_a(model_dirs, plain_models):
+    """3 requests with prompts of 5, 11 and 17 tokens, 8 greedy tokens each, pages of 4."""
+    prompts = [random_tokens(256, n, 1 + i) for i, n in enumerate((5, 11, 17))]
+    llm = make_llm(model_dirs["A"], "A")
+    got = llm.generate(prompts, 8, 0.0, 1.0, repeat_penalty=1.0)
+    assert got == [plain_generate(plain_models, "A", p, 8) for p in prompts]
+
+
+def test_sampled_config_b(model_dirs, plain_models):
+    """4 requests (1, 7, 33, 64 tokens), portions of 16 beside decoding, temperature 0.8 seed 4, 12 tokens."""
+    prompts = [random_tokens(384, n, 3 + i) for i, n in enumerate((1, 7, 33, 64))]
+    llm = make_llm(model_dirs["B"], "B")
+    got = llm.generate(prompts, 12, 0.8, 1.0, repeat_penalty=1.0, seed=4)
+    want = [plain_generate(plain_models, "B", p, 12, temperature=0.8, seed=4 + i) for i, p in enumerate(prompts)]
+    assert got == want
+
+
+def test_reference_defaults_top_p_and_penalty(model_dirs, plain_models):
+    """The reference's own defaults: temperature 0.7, top-p 0.8, repetition penalty 1.1 over prompt + output."""
+    prompts = [random_tokens(256, n, 20 + i) for i, n in enumerate((9, 30))]
+    llm = make_llm(model_dirs["A"], "A")
+    got = llm.generate(prompts, 10, seed=11)
+    want = [plain_generate(plain_models, "A", p, 10, temperature=0.7, top_p=0.8, repeat_penalty=1.1, seed=11 + i)
+            for i, p in enumerate(prompts)]
+    assert got == want
+
+
+def test_bfloat16_greedy_mostly_agrees(model_dirs, plain_models):
+    prompts = [random_tokens(384, n, 40 + i) for i, n in enumerate((12, 50, 100))]
+    llm = make_llm(model_dirs["B"], "B", dtype="bfloat16")
+    got = llm.generate(prompts, 16, 0.0, 1.0, repeat_penalty=1.0)
+    want = [plain_generate(plain_models, "B", p, 16) for p in prompts]
+    first = sum(g[0] == w[0] for g, w in zip(got, want))
+    agree = sum(a == b for g, w in zip(got, want) for a, b in zip(g, w))
+    assert first == 3 and agree >= 36, (got, want)
+
+
+def test_preemption_recomputes_to_the_same_tokens(model_dirs, plain_models):
+    """A pool too small for all requests at their full length: the youngest is preempted, recomputed
+    later, and every request still produces the tokens it produces alone."""
+    prompts = [random_tokens(256, n, 60 + i) for i, n in enumerate((30, 28, 26, 20))]
+    llm = make_llm(model_dirs["A"], "A", max_tokens=128, max_step_tokens=32)
+    got = llm.generate(prompts, 24, 0.9, 1.0, repeat_penalty=1.0, seed=3)
+    assert llm.stats().preemptions > 0
+    want = [plain_generate(plain_models, "A", p, 24, temperature=0.9, seed=3 + i) for i, p in enumerate(prompts)]
+    assert got == want
+    cache = llm.scheduler.cache()
+    cache.check_invariants()
+    assert cache.free_pages(0) == 128 // TINY_PAGE["A"] and cache.free_slots() == 4
+
+
+def test_long_decoding_and_stop(model_dirs, plain_models):
+    """One request decoding up to the model's last position; then one that stops on a stop id."""
+    prompt = random_tokens(384, 3, 77)
+    llm = make_llm(model_dirs["B"], "B")
+    got = llm.generate([prompt], 253, 0.0, 1.0, repeat_penalty=1.0)[0]
+    want = plain_generate(plain_models, "B", prompt, 253)
+    assert len(got) == 253 and got == want
+    stop = want[5]
+    first = want.index(stop)
+    got2 = llm.generate([prompt], 50, 0.0, 1.0, repeat_penalty=1.0, stop_ids=[stop])[0]
+    assert got2 == want[:first + 1]
+
+
+def test_engine_surface(model_dirs):
+    """submit_tokens / step / get_request / remove_request / has_requests, as the reference's engine has them."""
+    llm = make_llm(model_dirs["A"], "A")
+    rid = llm.submit_tokens([1, 2, 3], 4, 0.0, 1.0, repeat_penalty=1.0)
+    assert llm.has_requests()
+    out = llm.step()
+    assert out.request_ids == [rid] and len(out.new_token_ids) == 1 and out.num_prompt_tokens == 3
+    assert llm.get_request(rid).generated == out.new_token_ids
+    llm.remove_request(rid)
+    assert not llm.has_requests() and llm.get_request(rid) is None
+    with pytest.raises(ValueError):
+        llm.submit_tokens([], 4)
+    with pytest.raises(ValueError):
+        llm.submit_tokens([999], 4)
+    with pytest.raises(ValueError):
+        llm.submit_tokens([1] * 120, 20)   # beyond the model's 128 positions
+
+
+def test_command_line(model_dirs, plain_models):
+    prompt = random_tokens(256, 6, 5)
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "vllm_cpp_run"), str(model_dirs["A"]), "--tokens",
+                        ",".join(map(str, prompt)), "--max-new", "5", "--temp", "0", "--top-p", "1", "--repeat-penalty", "1",
+                        "--dtype", "float32", "--page-size", "4", "--max-tokens", "256", "--debug"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
+    got = [int(t) for t in r.stdout.strip().splitlines()[-1].split(",")]
+    assert got == plain_generate(plain_models, "A", prompt, 5)

@@ -68,8 +68,13 @@ def _declare(L):
         fn.restype = c_int
 
 
+launch_count = 0   # kernels of this library launched so far (every launcher starts exactly one)
+
+
 def _call(name: str, *args):
+    global launch_count
     L = lib()
+    launch_count += 1
     rc = getattr(L, name)(*args)
     if rc != 0:
         raise KernelError(L.vcb_last_error().decode() or f"{name} failed with code {rc}")
