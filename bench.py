@@ -89,6 +89,8 @@ def main():
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
+    ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profiling runs)")
+    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill"], help="what to run (profiling runs)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -112,13 +114,15 @@ def main():
     cfg = Qwen3Config(**cfgd)
     B_MAX = 64
     points = [args.batch] if args.skip_points else sorted({1, args.batch, B_MAX})
+    max_seqs = max(points)
     steps_total = args.steps + args.warmup + 8
     per_req = -(-(args.context + steps_total) // 64) * 64
     max_tokens = max(max(points) * per_req, 8192)
     t0 = time.time()
     llm = LLM(config=cfg, random_seed=0, engine=EngineConfig(dtype="bfloat16", page_size=PAGE, max_tokens=max_tokens,
                                                             max_num_seqs=max(points), max_step_tokens=PREFILL_TOKENS,
-                                                            max_model_len=args.context + steps_total + 8))
+                                                            max_model_len=args.context + steps_total + 8,
+                                                            cuda_graphs=not args.no_graphs))
     runner = llm.runner
     dev = runner.device
     load_s = time.time() - t0
@@ -137,7 +141,8 @@ def main():
     windows = []
 
     def fresh_cache():
-        return rt.CacheManager(runner.layout.runtime_groups(rt, PAGE, max_tokens // PAGE), max(points))
+        runner.reset_tables()
+        return rt.CacheManager(runner.layout.runtime_groups(rt, PAGE, max_tokens // PAGE), max_seqs)
 
     # the cache of requests that "hold" a context: random keys and values stand for a processed prompt
     for t in runner.cache.tensors:
@@ -182,11 +187,16 @@ def main():
     from vllm_cpp_b200.sampling import SamplingOptions
     GREEDY = SamplingOptions(0.0, 1.0, 1.0, 0)
 
+    if args.mode == "prefill":
+        points = []
     results = {}
     for B in points:
         st = args.steps if B == args.batch else max(8, args.steps // 4)
         results[B] = decode_point(B, st, args.warmup)
-    head = results[args.batch]
+    if args.mode == "decode":
+        print(json.dumps({"mode": "decode", "ms_per_step": {b: results[b]["ms"] for b in points}}))
+        return 0
+    head = results.get(args.batch)
 
     # prefill: one prompt of 2,048 tokens in one step, logits of the last token only
     def prefill_once():
@@ -209,6 +219,9 @@ def main():
     pf_ms = statistics.median(pf)
     T = PREFILL_TOKENS
     pf_flops = 2.0 * T * L * layer_params + 2.0 * V * H + L * 4.0 * nh * hd * (T * (T + 1) / 2)
+    if args.mode == "prefill":
+        print(json.dumps({"mode": "prefill", "ms": pf_ms, "tokens_per_s": T * 1000.0 / pf_ms}))
+        return 0
     prefill = {"value": T * 1000.0 / pf_ms, "tokens": T, "ms": pf_ms, "frac": pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
 
     # end to end through the Python entry point: host token lists in, host tokens out, every step

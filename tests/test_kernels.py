@@ -167,9 +167,21 @@ def attention_reference(q, k, v, start, window):
 
 
 def run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft=None):
+    """Runs the plain kernel, and the tensor-core kernel too where it takes the type and head size."""
+    from vllm_cpp_b200 import ops
+    plan = _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma=False)
+    if ops.attn_mma_supported(dtype, hd):
+        plan = _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma=True)
+    return plan
+
+
+def _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma):
     """shapes: list of (cached tokens before the step, query tokens of the step)."""
     from vllm_cpp_b200 import ops
-    from vllm_cpp_b200.parts.attention import AttentionPlan, DECODE_ROWS, SPAN_ROWS
+    from vllm_cpp_b200.parts import attention as A
+    DECODE_ROWS, SPAN_ROWS = (A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS) if mma else (A.DECODE_ROWS, A.SPAN_ROWS)
+    AttentionPlan = lambda c, h, k: A.AttentionPlan(c, h, k, DECODE_ROWS, SPAN_ROWS)
+    kernel = ops.attn_mma if mma else ops.attn_paged
     torch.manual_seed(1)
     seqs, qs = [], []
     for start, n in shapes:
@@ -207,11 +219,11 @@ def run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft=None):
         S = plan.nslices
         po = torch.empty(plan.n_dec * nh * S, hd, device=dev()) if S > 1 else None
         pm = torch.empty(plan.n_dec * nh * S, 2, device=dev()) if S > 1 else None
-        ops.attn_paged(q_flat, out, *args, plan.dec_items, plan.n_dec * S, DECODE_ROWS, po, pm, nh, nkv, hd, window, status)
+        kernel(q_flat, out, *args, plan.dec_items, plan.n_dec * S, DECODE_ROWS, po, pm, nh, nkv, hd, window, status)
         if S > 1:
             ops.attn_merge(po, pm, plan.dec_rows, out, plan.n_dec, nh, hd, S)
     if plan.n_span_items:
-        ops.attn_paged(q_flat, out, *args, plan.span_items, plan.n_span_items, SPAN_ROWS, None, None, nh, nkv, hd, window, status)
+        kernel(q_flat, out, *args, plan.span_items, plan.n_span_items, SPAN_ROWS, None, None, nh, nkv, hd, window, status)
     assert status.item() == 0
     got = out.double().cpu().view(T, nh, hd)
     t = 0
@@ -224,7 +236,8 @@ def run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft=None):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd,ps", [(4, 2, 16, 4), (6, 2, 32, 8), (8, 8, 64, 16), (4, 1, 128, 16),
-                                          (12, 1, 48, 16), (2, 1, 256, 32), (40, 2, 16, 8)])
+                                          (12, 1, 48, 16), (2, 1, 256, 32), (40, 2, 16, 8), (6, 2, 64, 8),
+                                          (32, 8, 128, 16), (40, 2, 128, 4), (5, 1, 64, 5)])
 def test_attention_mixed_batch(dtype, nh, nkv, hd, ps):
     # prompt portions of several sizes beside single decoded tokens, page edges on both sides
     run_attention(dtype, nh, nkv, hd, ps, 0, [(0, 7), (31, 1), (0, 1), (13, 34), (63, 2), (200, 1), (16, 16)])
@@ -232,8 +245,9 @@ def test_attention_mixed_batch(dtype, nh, nkv, hd, ps):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 5, 24, 100])
-def test_attention_window(dtype, window):
-    run_attention(dtype, 6, 2, 32, 8, window, [(0, 40), (57, 1), (23, 3), (130, 1)])
+@pytest.mark.parametrize("hd", [32, 64])
+def test_attention_window(dtype, window, hd):
+    run_attention(dtype, 6, 2, hd, 8, window, [(0, 40), (57, 1), (23, 3), (130, 1), (300, 70)])
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -256,7 +270,8 @@ def test_attention_far_key_stands_out(dtype, far):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("offset", [0, 1])
-def test_attention_window_edge(dtype, offset):
+@pytest.mark.parametrize("hd", [32, 128])
+def test_attention_window_edge(dtype, offset, hd):
     """A dominant key exactly at the window's first position must count; one position earlier it must not."""
     W, start = 24, 100
     def craft(q, k, v, s, n):
@@ -264,8 +279,8 @@ def test_attention_window_edge(dtype, offset):
         edge = (s + n - 1) - W + 1 - offset      # offset 0: last key inside; 1: first key outside
         k[edge] = q[-1, 0] * 4
         v[edge] = 50.0
-    run_attention(dtype, 2, 2, 32, 8, W, [(start, 1)], craft)
-    run_attention(dtype, 2, 2, 32, 8, W, [(start - 5, 6)], craft)
+    run_attention(dtype, 2, 2, hd, 8, W, [(start, 1)], craft)
+    run_attention(dtype, 2, 2, hd, 8, W, [(start - 5, 6)], craft)
 
 
 def plain_sample(*a, **k):

@@ -26,6 +26,7 @@ struct AttnArgs {
     const void* pages;
     long long page_stride;
     const int* block_table;
+    const int* table_row;  // entry -> row of block_table (a request's slot), or null: row = entry
     int max_blocks;
     const int* q_start;
     const int* q_len;
@@ -117,7 +118,7 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
     __syncthreads();
 
     const T* pages = reinterpret_cast<const T*>(a.pages);
-    const int* bt = a.block_table + (size_t)e * a.max_blocks;
+    const int* bt = a.block_table + (size_t)(a.table_row ? a.table_row[e] : e) * a.max_blocks;
 
     for (int t0 = k_begin; t0 < k_end; t0 += TK) {
         const int n_valid = min(TK, k_end - t0);
@@ -297,7 +298,7 @@ int launch_attn(const AttnArgs& a, int n_items, cudaStream_t stream) {
 
 // rows_max: 8 for items of single decoded tokens (key range may be sliced), 32 for prompt portions
 VCB_API int vcb_attn_paged(const void* q, void* out, int dtype, const void* pages, long long page_stride,
-                           const int* block_table, int max_blocks, const int* q_start, const int* q_len,
+                           const int* block_table, const int* table_row, int max_blocks, const int* q_start, const int* q_len,
                            const int* ctx_len, const int* items, int n_items, int rows_max, float* part_o,
                            float* part_ml, int nh, int nkv, int hd, int page_size, int num_pages, int window,
                            float scale, int* status, cudaStream_t stream) {
@@ -306,7 +307,7 @@ VCB_API int vcb_attn_paged(const void* q, void* out, int dtype, const void* page
     VCB_CHECK_ARG(hd >= 16 && hd % 16 == 0 && hd <= VCB_MAX_HEAD_DIM, "attn_paged: head_dim %d must be a multiple of 16 in [16, %d]", hd, VCB_MAX_HEAD_DIM);
     VCB_CHECK_ARG(rows_max == 8 || rows_max == 32, "attn_paged: rows_max must be 8 or 32");
     VCB_CHECK_ARG(page_size > 0 && window >= 0, "attn_paged: bad page_size %d or window %d", page_size, window);
-    AttnArgs a{q, out, pages, page_stride, block_table, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml,
+    AttnArgs a{q, out, pages, page_stride, block_table, table_row, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml,
                nh, nkv, hd, page_size, num_pages, window, scale, status};
     if (dtype == VCB_F32) return rows_max == 8 ? launch_attn<float, 8>(a, n_items, stream) : launch_attn<float, 32>(a, n_items, stream);
     return rows_max == 8 ? launch_attn<__nv_bfloat16, 8>(a, n_items, stream) : launch_attn<__nv_bfloat16, 32>(a, n_items, stream);

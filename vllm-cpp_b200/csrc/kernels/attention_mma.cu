@@ -1,0 +1,373 @@
+// bfloat16 attention over the paged cache on tensor cores (head_dim 64 or 128).
+//
+// Same contract and work items as attention.cu (one item = an entry, a run of
+// query tokens, one slice of the key range; rows = tokens x the query heads that
+// share a KV head), same math in 32-bit: scores (q.k)/sqrt(head_dim), keys in
+// (pos - window, pos], streaming softmax, sum_j w_j v_j
+// (src/model.cpp:1000-1052 of the reference).  What differs is how the work is
+// laid on the SM:
+//  * K and V tiles of 64 keys are gathered from their pages into shared memory
+//    with cp.async, 16 bytes a thread, double buffered, so HBM reads stay in
+//    flight while the previous tile is multiplied;
+//  * Q.K^T and P.V are mma.sync m16n8k16 products (bf16 in, f32 accumulate) fed by
+//    ldmatrix from a 16-byte XOR-swizzled layout;
+//  * the four warps either take four different row groups and all keys of a tile
+//    (prompt portions: 64 rows a block) or the same 16 rows and a quarter of the
+//    tile's keys each (single decoded tokens: few rows, long key ranges), their
+//    partial softmax states merged through shared memory at the end.
+// Rows beyond the item's real rows and keys beyond the slice are zero-filled and
+// masked, never read from memory that is not theirs.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+namespace {
+
+constexpr int BN = 64;        // keys per tile
+constexpr int NT = 128;       // threads per block
+constexpr int ITEM_INTS = 6;  // entry, q0, nq, slice, nslices, decode index
+
+struct AttnArgs {
+    const __nv_bfloat16* q;
+    __nv_bfloat16* out;
+    const __nv_bfloat16* pages;
+    long long page_stride;
+    const int* block_table;
+    const int* table_row;
+    int max_blocks;
+    const int* q_start;
+    const int* q_len;
+    const int* ctx_len;
+    const int* items;
+    float* part_o;
+    float* part_ml;
+    int nh, nkv, page_size, num_pages, window;
+    float scale;
+    int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// byte offset of 16-byte chunk `c` of row `r` in a tile whose rows are ROWB bytes
+template <int ROWB> __device__ __forceinline__ int swz(int r, int c) { return r * ROWB + ((c ^ (r & 7)) << 4); }
+
+// WR row groups x WK key groups = 4 warps
+template <int HD, int WR, int WK>
+__global__ __launch_bounds__(NT) void attn_mma_kernel(AttnArgs a) {
+    static_assert(WR * WK == 4 && HD % 64 == 0, "layout");
+    constexpr int RMAX = 16 * WR;   // rows a block holds
+    constexpr int CH = HD / 8;      // 16-byte chunks per row
+    constexpr int ROWB = HD * 2;
+    constexpr int KW = BN / WK;     // keys of a tile that one warp multiplies
+    constexpr int NS = KW / 8;      // score n-tiles per warp
+    constexpr int ND = HD / 8;      // output n-tiles
+    constexpr float LOG2E = 1.4426950408889634f;
+
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* q_s = smem;
+    uint8_t* k_s = q_s + RMAX * ROWB;        // 2 stages
+    uint8_t* v_s = k_s + 2 * BN * ROWB;      // 2 stages
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wr = warp / WK, wk = warp % WK;
+    const int* item = a.items + (size_t)blockIdx.x * ITEM_INTS;
+    const int e = item[0], q0 = item[1], nq = item[2], slice = item[3], nslices = item[4], dec_index = item[5];
+
+    const int g = a.nh / a.nkv;
+    const int gq_max = g < RMAX ? g : RMAX;
+    const int hchunks = (g + gq_max - 1) / gq_max;
+    const int kvh = blockIdx.y / hchunks, hc = blockIdx.y % hchunks;
+    const int head0 = kvh * g + hc * gq_max;
+    const int gq = min(gq_max, g - hc * gq_max);
+    const int R = nq * gq;
+
+    const int qlen = a.q_len[e], ctx = a.ctx_len[e];
+    if (qlen <= 0 || ctx <= 0) return;
+    const int row0 = a.q_start[e] + q0;
+    const int pos0 = ctx - qlen + q0;
+    const int pos_last = pos0 + nq - 1;
+    const int W = a.window;
+    const int ps = a.page_size;
+    const int lo = W > 0 ? max(0, pos0 - W + 1) : 0;
+    const int hi = pos_last + 1;
+    const int pb_lo = lo / ps, pb_hi = (hi + ps - 1) / ps;
+    const int pps = (pb_hi - pb_lo + nslices - 1) / nslices;
+    const int my_pb_lo = pb_lo + slice * pps, my_pb_hi = min(pb_hi, my_pb_lo + pps);
+    const int k_begin = max(lo, my_pb_lo * ps), k_end = min(hi, my_pb_hi * ps);
+    const int n_tiles = k_end > k_begin ? (k_end - k_begin + BN - 1) / BN : 0;
+
+    const int* bt = a.block_table + (size_t)(a.table_row ? a.table_row[e] : e) * a.max_blocks;
+
+    // ---- Q rows -> shared memory (rows beyond R are zero) ----
+    for (int idx = tid; idx < RMAX * CH; idx += NT) {
+        const int r = idx / CH, c = idx % CH;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < R) {
+            const int iq = r / gq, ih = r % gq;
+            v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(row0 + iq) * a.nh + head0 + ih) * HD + c * 8);
+        }
+        *reinterpret_cast<uint4*>(q_s + swz<ROWB>(r, c)) = v;
+    }
+
+    // ---- tile loader: 64 keys x HD of K and of V, gathered page by page ----
+    auto load_tile = [&](int stage, int t0) {
+        uint8_t* kd = k_s + stage * BN * ROWB;
+        uint8_t* vd = v_s + stage * BN * ROWB;
+#pragma unroll
+        for (int i = 0; i < BN * CH / NT; ++i) {
+            const int idx = tid + i * NT;
+            const int j = idx / CH, c = idx % CH;
+            const int kidx = t0 + j;
+            const __nv_bfloat16* src = a.pages;
+            int bytes = 0;
+            if (kidx < k_end) {
+                const int page = bt[kidx / ps];
+                if (page < 0 || page >= a.num_pages) {
+                    atomicOr(a.status, VCB_STATUS_BAD_PAGE);
+                } else {
+                    src = a.pages + (size_t)page * a.page_stride + ((size_t)kvh * ps + kidx % ps) * HD + c * 8;
+                    bytes = 16;
+                }
+            }
+            const int off = swz<ROWB>(j, c);
+            cp_async16(smem_u32(kd + off), src, bytes);
+            cp_async16(smem_u32(vd + off), bytes ? src + (size_t)a.nkv * ps * HD : src, bytes);
+        }
+    };
+
+    if (n_tiles > 0) load_tile(0, k_begin);
+    cp_async_commit();
+    __syncthreads();   // Q is in shared memory
+
+    // ---- Q fragments stay in registers ----
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+        ldmatrix_x4(qf[ks], smem_u32(q_s + swz<ROWB>(wr * 16 + (lane & 15), ks * 2 + (lane >> 4))));
+
+    float o[ND][4];
+#pragma unroll
+    for (int i = 0; i < ND; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F};   // rows lane/4 and lane/4 + 8 of this warp's group
+    float l_run[2] = {0.f, 0.f};                       // per-thread partial sums (reduced over the quad at the end)
+    const int r_a = wr * 16 + (lane >> 2), r_b = r_a + 8;
+    const int pos_a = pos0 + r_a / gq, pos_b = pos0 + r_b / gq;
+    const bool ok_a = r_a < R, ok_b = r_b < R;
+
+    for (int it = 0; it < n_tiles; ++it) {
+        if (it + 1 < n_tiles) {
+            load_tile((it + 1) & 1, k_begin + (it + 1) * BN);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint8_t* kt = k_s + (it & 1) * BN * ROWB;
+        const uint8_t* vt = v_s + (it & 1) * BN * ROWB;
+        const int key0 = k_begin + it * BN + wk * KW;   // first key this warp multiplies
+
+        // S = Q K^T
+        float s[NS][4];
+#pragma unroll
+        for (int i = 0; i < NS; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+            for (int np = 0; np < KW / 16; ++np) {
+                uint32_t b[4];
+                const int mi = lane >> 3;
+                const int krow = wk * KW + np * 16 + (mi >> 1) * 8 + (lane & 7);
+                ldmatrix_x4(b, smem_u32(kt + swz<ROWB>(krow, ks * 2 + (mi & 1))));
+                mma_16816(s[2 * np], qf[ks], b[0], b[1]);
+                mma_16816(s[2 * np + 1], qf[ks], b[2], b[3]);
+            }
+        }
+        // mask, running maximum
+        float mx_a = -CUDART_INF_F, mx_b = -CUDART_INF_F;
+#pragma unroll
+        for (int i = 0; i < NS; ++i) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int kidx = key0 + i * 8 + 2 * (lane & 3) + c;
+                const bool in = kidx < k_end;
+                const bool sa = ok_a && in && kidx <= pos_a && (W <= 0 || kidx > pos_a - W);
+                const bool sb = ok_b && in && kidx <= pos_b && (W <= 0 || kidx > pos_b - W);
+                s[i][c] = sa ? s[i][c] * a.scale : -CUDART_INF_F;
+                s[i][2 + c] = sb ? s[i][2 + c] * a.scale : -CUDART_INF_F;
+                mx_a = fmaxf(mx_a, s[i][c]);
+                mx_b = fmaxf(mx_b, s[i][2 + c]);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        const float mn_a = fmaxf(m_run[0], mx_a), mn_b = fmaxf(m_run[1], mx_b);
+        const float use_a = mn_a == -CUDART_INF_F ? 0.f : mn_a, use_b = mn_b == -CUDART_INF_F ? 0.f : mn_b;
+        const float al_a = exp2f((m_run[0] - use_a) * LOG2E), al_b = exp2f((m_run[1] - use_b) * LOG2E);
+        m_run[0] = mn_a;
+        m_run[1] = mn_b;
+        float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+        for (int i = 0; i < NS; ++i) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                s[i][c] = exp2f((s[i][c] - use_a) * LOG2E);
+                s[i][2 + c] = exp2f((s[i][2 + c] - use_b) * LOG2E);
+                sum_a += s[i][c];
+                sum_b += s[i][2 + c];
+            }
+        }
+        l_run[0] = l_run[0] * al_a + sum_a;
+        l_run[1] = l_run[1] * al_b + sum_b;
+#pragma unroll
+        for (int i = 0; i < ND; ++i) {
+            o[i][0] *= al_a; o[i][1] *= al_a; o[i][2] *= al_b; o[i][3] *= al_b;
+        }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < KW / 16; ++kk) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int dp = 0; dp < HD / 16; ++dp) {
+                uint32_t b[4];
+                const int mi = lane >> 3;
+                const int vrow = wk * KW + kk * 16 + (mi & 1) * 8 + (lane & 7);
+                ldmatrix_x4_trans(b, smem_u32(vt + swz<ROWB>(vrow, dp * 2 + (mi >> 1))));
+                mma_16816(o[2 * dp], pa, b[0], b[1]);
+                mma_16816(o[2 * dp + 1], pa, b[2], b[3]);
+            }
+        }
+        __syncthreads();   // the stage may be overwritten by the load issued two iterations on
+    }
+
+    // ---- partial states -> shared memory: o_s[wk][row][HD], ml_s[wk][row][2] ----
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
+    float* o_s = reinterpret_cast<float*>(k_s);             // 64 x HD floats = the four K/V stages' first half
+    float* ml_s = o_s + 64 * HD;                            // 64 x 2 floats
+    {
+        const int ra = wk * RMAX + r_a, rb = wk * RMAX + r_b;
+#pragma unroll
+        for (int i = 0; i < ND; ++i) {
+            const int d = i * 8 + 2 * (lane & 3);
+            *reinterpret_cast<float2*>(o_s + (size_t)ra * HD + d) = make_float2(o[i][0], o[i][1]);
+            *reinterpret_cast<float2*>(o_s + (size_t)rb * HD + d) = make_float2(o[i][2], o[i][3]);
+        }
+        if ((lane & 3) == 0) {
+            ml_s[ra * 2] = m_run[0]; ml_s[ra * 2 + 1] = l_run[0];
+            ml_s[rb * 2] = m_run[1]; ml_s[rb * 2 + 1] = l_run[1];
+        }
+    }
+    __syncthreads();
+
+    // ---- merge the key groups and write ----
+    for (int idx = tid; idx < R * (HD / 2); idx += NT) {
+        const int r = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
+        float m = -CUDART_INF_F;
+#pragma unroll
+        for (int w = 0; w < WK; ++w) m = fmaxf(m, ml_s[(w * RMAX + r) * 2]);
+        float l = 0.f, o0 = 0.f, o1 = 0.f;
+#pragma unroll
+        for (int w = 0; w < WK; ++w) {
+            const float mw = ml_s[(w * RMAX + r) * 2];
+            if (mw == -CUDART_INF_F) continue;
+            const float f = exp2f((mw - m) * LOG2E);
+            l += ml_s[(w * RMAX + r) * 2 + 1] * f;
+            const float2 ov = *reinterpret_cast<const float2*>(o_s + (size_t)(w * RMAX + r) * HD + d);
+            o0 += ov.x * f;
+            o1 += ov.y * f;
+        }
+        const int iq = r / gq, ih = r % gq;
+        if (nslices == 1) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            *reinterpret_cast<__nv_bfloat162*>(a.out + ((size_t)(row0 + iq) * a.nh + head0 + ih) * HD + d) =
+                __floats2bfloat162_rn(o0 * inv, o1 * inv);
+        } else {
+            const size_t prow = ((size_t)dec_index * a.nh + head0 + r) * nslices + slice;
+            *reinterpret_cast<float2*>(a.part_o + prow * HD + d) = make_float2(o0, o1);
+            if (d == 0) {
+                a.part_ml[prow * 2] = m;
+                a.part_ml[prow * 2 + 1] = l;
+            }
+        }
+    }
+}
+
+template <int HD, int WR, int WK>
+int launch(const AttnArgs& a, int n_items, cudaStream_t stream) {
+    constexpr int RMAX = 16 * WR;
+    const int g = a.nh / a.nkv;
+    const int gq_max = g < RMAX ? g : RMAX;
+    const int hchunks = (g + gq_max - 1) / gq_max;
+    const size_t stages = (size_t)RMAX * HD * 2 + 4 * (size_t)BN * HD * 2;
+    const size_t merge = (size_t)RMAX * HD * 2 + (64 * (size_t)HD + 128) * sizeof(float);
+    const size_t smem = stages > merge ? stages : merge;
+    auto kern = attn_mma_kernel<HD, WR, WK>;
+    static bool opted = false;
+    if (!opted) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            vcb_set_error("attn_mma: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+            return -2;
+        }
+        opted = true;
+    }
+    kern<<<dim3(n_items, a.nkv * hchunks), NT, smem, stream>>>(a);
+    VCB_CHECK_LAUNCH("attn_mma");
+    return 0;
+}
+
+}  // namespace
+
+// rows_max: 16 (single decoded tokens; the four warps split each tile's keys) or 64 (prompt portions).
+// Only bfloat16 and head_dim 64 or 128; the caller falls back to vcb_attn_paged otherwise.
+VCB_API int vcb_attn_mma_supported(int dtype, int hd) { return dtype == VCB_BF16 && (hd == 64 || hd == 128); }
+
+VCB_API int vcb_attn_mma(const void* q, void* out, const void* pages, long long page_stride, const int* block_table,
+                         const int* table_row, int max_blocks, const int* q_start, const int* q_len,
+                         const int* ctx_len, const int* items, int n_items, int rows_max, float* part_o,
+                         float* part_ml, int nh, int nkv, int hd, int page_size, int num_pages, int window,
+                         float scale, int* status, cudaStream_t stream) {
+    if (n_items == 0) return 0;
+    VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_mma: %d query heads are not a multiple of %d KV heads", nh, nkv);
+    VCB_CHECK_ARG(hd == 64 || hd == 128, "attn_mma: head_dim %d is not 64 or 128", hd);
+    VCB_CHECK_ARG(rows_max == 16 || rows_max == 64, "attn_mma: rows_max must be 16 or 64");
+    VCB_CHECK_ARG(page_size > 0 && window >= 0, "attn_mma: bad page_size %d or window %d", page_size, window);
+    AttnArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_stride, block_table,
+               table_row, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml, nh, nkv, page_size, num_pages,
+               window, scale, status};
+    if (hd == 64) return rows_max == 16 ? launch<64, 1, 4>(a, n_items, stream) : launch<64, 4, 1>(a, n_items, stream);
+    return rows_max == 16 ? launch<128, 1, 4>(a, n_items, stream) : launch<128, 4, 1>(a, n_items, stream);
+}

@@ -228,3 +228,22 @@ VCB_API int vcb_qknorm_rope_kvwrite(const void* qkv, int dtype, const void* qw, 
     VCB_CHECK_LAUNCH("qknorm_rope_kvwrite");
     return 0;
 }
+
+// ---------------------------------------------------------------------------
+// dst[idx[i]] = val[i]: how new block-table entries reach the device-resident tables
+// ---------------------------------------------------------------------------
+__global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict__ idx, const int* __restrict__ val,
+                                   const int* __restrict__ count, int capacity, long long dst_size) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int n = min(*count, capacity);
+    if (i < n && idx[i] >= 0 && idx[i] < dst_size) dst[idx[i]] = val[i];
+}
+
+// count lives on the device so that a captured launch can serve any number of updates up to capacity
+VCB_API int vcb_scatter_i32(int* dst, const int* idx, const int* val, const int* count, int capacity,
+                            long long dst_size, cudaStream_t stream) {
+    if (capacity == 0) return 0;
+    scatter_i32_kernel<<<(capacity + 255) / 256, 256, 0, stream>>>(dst, idx, val, count, capacity, dst_size);
+    VCB_CHECK_LAUNCH("scatter_i32");
+    return 0;
+}

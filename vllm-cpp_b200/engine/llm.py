@@ -61,7 +61,8 @@ class LLM:
         self.model.load(store)
         store.release()
         self.max_model_len = min(ec.max_model_len or self.model.spec.max_positions, self.model.spec.max_positions)
-        self.runner = ModelRunner(self.model, ec.page_size, ec.num_pages, ec.max_num_seqs, dtype, self.device)
+        self.runner = ModelRunner(self.model, ec.page_size, ec.num_pages, ec.max_num_seqs, dtype, self.device,
+                                  cuda_graphs=ec.cuda_graphs, max_model_len=self.max_model_len)
         rt = runtime()
         self.scheduler = rt.Scheduler(self.runner.layout.runtime_groups(rt, ec.page_size, ec.num_pages),
                                       ec.max_num_seqs, ec.max_step_tokens, self.max_model_len)
@@ -117,7 +118,6 @@ class LLM:
             if e.sample:
                 sampled_entries.append(e)
         penalised = {e.slot for e in sched.entries if self._options[e.request].repeat_penalty not in (0.0, 1.0)}
-        from .step import StepContext  # noqa: F401  (kept local: the runner builds the context)
         logits = self.runner.step(entries, check=False)
         self.h2d_bytes += self.runner.last_h2d_bytes
         if penalised:

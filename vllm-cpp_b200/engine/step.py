@@ -10,6 +10,15 @@ The reference's PagedEngine::step (src/paged_engine.cpp:245-300) schedules, runs
 each request on its own (whole prompt in run_prefill :318, one token in
 run_decode :451), samples and detokenises in one call; here those are separate
 layers and the batch is processed as one.
+
+What reaches the device each step is one packed int32 buffer (token ids,
+positions, per-entry starts and lengths, slots, wanted rows, each group's cache
+slot of every token, and the block-table entries that are new since the last
+step).  The block tables themselves stay on the device, one row per request slot,
+and only grow by those new entries.  A step made of single tokens only (decoding)
+has a fixed shape once its entry count is rounded up, so it is captured once per
+rounded count as a CUDA graph and replayed afterwards; the launch cost of a few
+hundred small kernels would otherwise exceed the time the GPU needs for them.
 """
 from __future__ import annotations
 
@@ -36,97 +45,59 @@ class StepEntry:
 class GroupContext:
     page_size: int
     window: int
-    block_table: torch.Tensor         # int32 [E, max_blocks]
-    slot_map: torch.Tensor            # int32 [T]: page * page_size + offset of each token's cache entry
+    block_table: torch.Tensor         # int32 [num_slots, max_blocks], device resident, row = request slot
+    slot_map: torch.Tensor            # int32 [T]: page * page_size + offset of each token's cache entry, -1: none
+    upd_count: torch.Tensor           # int32 [1]
+    upd_idx: torch.Tensor             # int32 [U]  flat indices into block_table
+    upd_val: torch.Tensor             # int32 [U]
+    upd_capacity: int
+
+
+class MetaLayout:
+    """Where each array sits in the packed int32 buffer of a step with T tokens, E entries, R wanted rows,
+    U block-table updates per group and G paged groups."""
+
+    def __init__(self, T, E, R, U, G):
+        self.T, self.E, self.R, self.U, self.G = T, E, R, U, G
+        names = [("token_ids", T), ("positions", T), ("q_start", E), ("q_len", E), ("ctx_len", E), ("slots", E),
+                 ("logit_rows", max(R, 1))]
+        for g in range(G):
+            names += [(f"slot_map{g}", T), (f"upd_count{g}", 1), (f"upd_idx{g}", max(U, 1)), (f"upd_val{g}", max(U, 1))]
+        self.offsets = {}
+        off = 0
+        for n, size in names:
+            self.offsets[n] = (off, off + size)
+            off += size
+        self.size = off
 
 
 class StepContext:
-    """Tensors and counts of one step, shared by all parts."""
+    """Tensors and counts of one step, shared by all parts.  ``T`` and ``E`` are the launch sizes (the real
+    counts, or the rounded-up counts of a captured step whose extra entries are empty)."""
 
-    def __init__(self, entries: list[StepEntry], layout: CacheLayout, page_size: int, device, status: torch.Tensor):
-        self.device = device
-        self.status = status
-        self.entries = entries
-        E = self.E = len(entries)
-        lens = [len(e.tokens) for e in entries]
-        T = self.T = int(sum(lens))
-        self.host_q_len = lens
-        self.host_q_start = [0] * E
-        self.host_ctx_len = [e.start_pos + n for e, n in zip(entries, lens)]
-        self.host_slots = [e.slot for e in entries]
-        token_ids = np.empty(T, dtype=np.int32)
-        positions = np.empty(T, dtype=np.int32)
-        entry_of = np.empty(T, dtype=np.int32)
-        rows = []
-        t = 0
-        for i, e in enumerate(entries):
-            n = lens[i]
-            self.host_q_start[i] = t
-            token_ids[t:t + n] = e.tokens
-            positions[t:t + n] = np.arange(e.start_pos, e.start_pos + n, dtype=np.int32)
-            entry_of[t:t + n] = i
-            for w in e.want:
-                if not 0 <= w < n:
-                    raise ValueError(f"wanted place {w} is outside the entry's {n} tokens")
-                rows.append(t + w)
-            t += n
-        self.n_rows = len(rows)
-        self.host_positions = positions
-
-        n_paged = len(layout.paged)
-        max_blocks = [1] * n_paged
-        for g in range(n_paged):
-            max_blocks[g] = max([1] + [len(e.tables[g]) for e in entries])
-        # one packed int32 buffer, one copy to the device
-        sizes = [T, T, T, E, E, E, E, max(self.n_rows, 1)]
-        for g in range(n_paged):
-            sizes += [E * max_blocks[g], T]
-        offs = np.concatenate([[0], np.cumsum(sizes)])
-        packed = np.zeros(int(offs[-1]), dtype=np.int32)
-        packed[offs[0]:offs[1]] = token_ids
-        packed[offs[1]:offs[2]] = positions
-        packed[offs[2]:offs[3]] = entry_of
-        packed[offs[3]:offs[4]] = self.host_q_start
-        packed[offs[4]:offs[5]] = lens
-        packed[offs[5]:offs[6]] = self.host_ctx_len
-        packed[offs[6]:offs[7]] = self.host_slots
-        packed[offs[7]:offs[7] + self.n_rows] = rows
-        for g in range(n_paged):
-            mb = max_blocks[g]
-            bt = np.full((E, mb), -1, dtype=np.int32)
-            sm = np.empty(T, dtype=np.int32)
-            for i, e in enumerate(entries):
-                tab = np.asarray(e.tables[g], dtype=np.int32)
-                bt[i, :len(tab)] = tab
-                pos = positions[self.host_q_start[i]:self.host_q_start[i] + lens[i]]
-                blk = pos // page_size
-                if len(tab) == 0 or blk.max(initial=0) >= len(tab):
-                    raise ValueError(f"entry {i}: the block table of group {g} does not reach position {int(pos.max())}")
-                pages = tab[blk]
-                if (pages < 0).any():
-                    raise ValueError(f"entry {i}: a token would be stored in a page that was given back")
-                sm[self.host_q_start[i]:self.host_q_start[i] + lens[i]] = pages * page_size + pos % page_size
-            packed[offs[8 + 2 * g]:offs[9 + 2 * g]] = bt.ravel()
-            packed[offs[9 + 2 * g]:offs[10 + 2 * g]] = sm
-        dev = torch.from_numpy(packed).pin_memory().to(device, non_blocking=True) if device.type == "cuda" \
-            else torch.from_numpy(packed)
-        self.h2d_bytes = packed.nbytes
-
-        def view(k):
-            return dev[int(offs[k]):int(offs[k + 1])]
-
-        self.token_ids, self.positions, self.entry_of_token = view(0), view(1), view(2)
-        self.q_start, self.q_len, self.ctx_len, self.slots = view(3), view(4), view(5), view(6)
-        self.logit_rows = view(7)[:self.n_rows]
-        self.groups: list[GroupContext] = []
-        for gi, g in enumerate(layout.groups):
+    def __init__(self, runner, layout: MetaLayout, dev_buffer: torch.Tensor, static: bool):
+        self.device = runner.device
+        self.status = runner.status
+        self.static = static
+        self.meta_layout = layout
+        self.T, self.E, self.n_rows = layout.T, layout.E, layout.R
+        self.buffer = dev_buffer
+        v = lambda n: dev_buffer[layout.offsets[n][0]:layout.offsets[n][1]]
+        self.token_ids, self.positions = v("token_ids"), v("positions")
+        self.q_start, self.q_len, self.ctx_len, self.slots = v("q_start"), v("q_len"), v("ctx_len"), v("slots")
+        self.logit_rows = v("logit_rows")[:layout.R]
+        self.groups = []
+        for g in runner.layout.groups:
             if g.paged:
                 k = g.runtime_index
-                self.groups.append(GroupContext(page_size, g.spec.window,
-                                                view(8 + 2 * k).view(E, max_blocks[k]), view(9 + 2 * k)))
+                self.groups.append(GroupContext(runner.page_size, g.spec.window, runner.tables[k], v(f"slot_map{k}"),
+                                                v(f"upd_count{k}"), v(f"upd_idx{k}"), v(f"upd_val{k}"), layout.U))
             else:
                 self.groups.append(None)
         self._plans: dict = {}
+        # host-side facts of the current step (refreshed by fill)
+        self.entries: list[StepEntry] = []
+        self.host_q_len, self.host_q_start, self.host_ctx_len, self.host_slots = [], [], [], []
 
     def plan(self, key, make):
         """Per-step data that several layers share (built by the first one that asks)."""
@@ -136,40 +107,209 @@ class StepContext:
 
 
 class ModelRunner:
-    """Owns the model, its device cache and the status word; runs steps."""
+    """Owns the model, its device cache, the device-resident block tables and the status word; runs steps."""
 
-    def __init__(self, model, page_size: int, num_pages: int, num_slots: int, dtype: torch.dtype, device):
+    GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+    def __init__(self, model, page_size: int, num_pages: int, num_slots: int, dtype: torch.dtype, device,
+                 cuda_graphs: bool = True, max_model_len: int | None = None):
         self.model = model
         self.device = torch.device(device)
         self.dtype = dtype
         self.page_size = page_size
+        self.num_slots = num_slots
         self.layout = CacheLayout(model.cache_specs())
         self.cache = DeviceCache(self.layout, page_size, num_pages, num_slots, dtype, self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.vocab_size = model.spec.vocab_size
-        self.launches = 0
+        self.max_positions = min(max_model_len or model.spec.max_positions, model.spec.max_positions)
+        self.max_blocks = -(-self.max_positions // page_size)
+        n_paged = len(self.layout.paged)
+        self.tables = [torch.full((num_slots, self.max_blocks), -1, dtype=torch.int32, device=self.device)
+                       for _ in range(n_paged)]
+        self._uploaded = [[0] * num_slots for _ in range(n_paged)]   # table entries of each slot already on the device
+        self.cuda_graphs = cuda_graphs and self.device.type == "cuda"
+        self._graphs: dict[int, tuple] = {}
+        self.last_ctx = None
+        self.last_h2d_bytes = 0
+        self.graph_replays = 0
+        self.launches_per_graph: dict[int, int] = {}
 
-    def step(self, entries: list[StepEntry], check: bool = True) -> torch.Tensor | None:
-        """Runs the entries' tokens as one batch.  Returns logits [wanted rows, vocab] (32-bit, on the
-        device) in the order of the entries and of their ``want`` lists, or None if nothing was wanted."""
-        if not entries:
-            return None
+    # ------------------------------------------------------------------ host side of a step
+    def _validate(self, entries):
         slots = [e.slot for e in entries]
         if len(set(slots)) != len(slots):
             raise ValueError("two entries of one step belong to the same request")
         for e in entries:
             if not e.tokens:
                 raise ValueError("an entry without tokens")
-            bad = [t for t in e.tokens if not 0 <= t < self.vocab_size]
-            if bad:
-                raise ValueError(f"token id {bad[0]} is outside the vocabulary of {self.vocab_size}")
-            if e.start_pos + len(e.tokens) > self.model.spec.max_positions:
-                raise ValueError(f"position {e.start_pos + len(e.tokens) - 1} is beyond the model's "
-                                 f"{self.model.spec.max_positions} positions")
+            if not 0 <= e.slot < self.num_slots:
+                raise ValueError(f"slot {e.slot} is outside the {self.num_slots} request slots")
+            if min(e.tokens) < 0 or max(e.tokens) >= self.vocab_size:
+                bad = [t for t in e.tokens if not 0 <= t < self.vocab_size][0]
+                raise ValueError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
+            if e.start_pos + len(e.tokens) > self.max_positions:
+                raise ValueError(f"position {e.start_pos + len(e.tokens) - 1} is beyond the {self.max_positions} "
+                                 f"positions this engine was set up for")
+            for w in e.want:
+                if not 0 <= w < len(e.tokens):
+                    raise ValueError(f"wanted place {w} is outside the entry's {len(e.tokens)} tokens")
+
+    def _table_updates(self, entries):
+        """Per paged group: (flat indices, values) of block-table entries the device does not have yet."""
+        ups = []
+        for g in range(len(self.tables)):
+            idx, val = [], []
+            for e in entries:
+                if e.start_pos == 0:
+                    self._uploaded[g][e.slot] = 0     # a request that starts (again) from nothing
+                tab = e.tables[g]
+                have = self._uploaded[g][e.slot]
+                need = -(-(e.start_pos + len(e.tokens)) // self.page_size)
+                if need > len(tab):
+                    raise ValueError(f"the block table of group {g} does not reach position "
+                                     f"{e.start_pos + len(e.tokens) - 1}")
+                for b in range(have, need):
+                    idx.append(e.slot * self.max_blocks + b)
+                    val.append(tab[b])
+                self._uploaded[g][e.slot] = max(have, need)
+            ups.append((idx, val))
+        return ups
+
+    def _fill(self, lay: MetaLayout, entries, updates):
+        """Packs the step into one host int32 array following the layout; also returns the host-side facts."""
+        packed = np.zeros(lay.size, dtype=np.int32)
+        o = lay.offsets
+        E = len(entries)
+        lens = [len(e.tokens) for e in entries]
+        starts = np.concatenate([[0], np.cumsum(lens)])[:-1].astype(np.int32) if E else np.zeros(0, np.int32)
+        T = int(sum(lens))
+        tok = packed[o["token_ids"][0]:o["token_ids"][1]]
+        pos = packed[o["positions"][0]:o["positions"][1]]
+        rows = []
+        for i, e in enumerate(entries):
+            s, n = int(starts[i]), lens[i]
+            tok[s:s + n] = e.tokens
+            pos[s:s + n] = np.arange(e.start_pos, e.start_pos + n, dtype=np.int32)
+            rows += [s + w for w in e.want]
+        packed[o["q_start"][0]:o["q_start"][0] + E] = starts
+        packed[o["q_start"][0] + E:o["q_start"][1]] = T          # empty padding entries start at the end
+        packed[o["q_len"][0]:o["q_len"][0] + E] = lens
+        packed[o["ctx_len"][0]:o["ctx_len"][0] + E] = [e.start_pos + n for e, n in zip(entries, lens)]
+        packed[o["slots"][0]:o["slots"][0] + E] = [e.slot for e in entries]
+        packed[o["logit_rows"][0]:o["logit_rows"][0] + len(rows)] = rows
+        ps = self.page_size
+        for g in range(len(self.tables)):
+            sm = packed[o[f"slot_map{g}"][0]:o[f"slot_map{g}"][1]]
+            sm[:] = -1
+            for i, e in enumerate(entries):
+                s, n = int(starts[i]), lens[i]
+                tab = np.asarray(e.tables[g], dtype=np.int64)
+                p = np.arange(e.start_pos, e.start_pos + n)
+                pages = tab[p // ps]
+                if (pages < 0).any():
+                    raise ValueError("a token would be stored in a page that was given back")
+                sm[s:s + n] = pages * ps + p % ps
+            idx, val = updates[g]
+            if len(idx) > lay.U:
+                raise RuntimeError("internal: more block-table updates than the step's buffer holds")
+            packed[o[f"upd_count{g}"][0]] = len(idx)
+            packed[o[f"upd_idx{g}"][0]:o[f"upd_idx{g}"][0] + len(idx)] = idx
+            packed[o[f"upd_val{g}"][0]:o[f"upd_val{g}"][0] + len(idx)] = val
+        facts = dict(entries=entries, host_q_len=lens, host_q_start=[int(s) for s in starts],
+                     host_ctx_len=[e.start_pos + n for e, n in zip(entries, lens)],
+                     host_slots=[e.slot for e in entries])
+        return packed, facts
+
+    def _apply_table_updates(self, ctx: StepContext):
+        for k, table in enumerate(self.tables):
+            g = next(gc for gc, grp in zip(ctx.groups, self.layout.groups) if grp.paged and grp.runtime_index == k)
+            if g.upd_capacity:
+                ops.scatter_i32(table, g.upd_idx, g.upd_val, g.upd_count, g.upd_capacity)
+
+    def reset_tables(self) -> None:
+        """Forgets which block-table entries the device holds.  A request normally (re)starts at position 0,
+        which does this for its slot; call this when slots are handed to requests that start further on."""
+        self._uploaded = [[0] * self.num_slots for _ in self.tables]
+
+    # ------------------------------------------------------------------ running
+    def step(self, entries: list[StepEntry], check: bool = True) -> torch.Tensor | None:
+        """Runs the entries' tokens as one batch.  Returns logits [wanted rows, vocab] (32-bit, on the
+        device) in the order of the entries and of their ``want`` lists, or None if nothing was wanted.
+        The returned tensor of a decoding step is reused by the next such step: copy what must outlive it."""
+        if not entries:
+            return None
+        self._validate(entries)
         self.cache.reset_state([e.slot for e in entries if e.start_pos == 0])
-        ctx = StepContext(entries, self.layout, self.page_size, self.device, self.status)
-        self.last_ctx, self.last_h2d_bytes = ctx, ctx.h2d_bytes
-        logits = self.model.forward(ctx, self.cache.views)
+        updates = self._table_updates(entries)
+        n_rows = sum(len(e.want) for e in entries)
+        decode_only = all(len(e.tokens) == 1 for e in entries)
+        bucket = next((b for b in self.GRAPH_BUCKETS if b >= len(entries)), None)
+        if (self.cuda_graphs and decode_only and bucket is not None and all(len(e.want) == 1 for e in entries)
+                and all(len(u[0]) <= bucket for u in updates)):
+            logits = self._step_graph(entries, updates, bucket)
+        else:
+            logits = self._step_eager(entries, updates, n_rows)
         if check:
             ops.check_status(self.status)
         return logits
+
+    def _step_eager(self, entries, updates, n_rows):
+        T = sum(len(e.tokens) for e in entries)
+        U = max([len(u[0]) for u in updates] + [0])
+        lay = MetaLayout(T, len(entries), n_rows, U, len(self.tables))
+        host, facts = self._fill(lay, entries, updates)
+        dev = torch.from_numpy(host).pin_memory().to(self.device, non_blocking=True)
+        ctx = StepContext(self, lay, dev, static=False)
+        ctx.__dict__.update(facts)
+        self.last_ctx, self.last_h2d_bytes = ctx, host.nbytes
+        self._apply_table_updates(ctx)
+        return self.model.forward(ctx, self.cache.views)
+
+    def _step_graph(self, entries, updates, bucket):
+        if bucket not in self._graphs:
+            self._capture(bucket)
+        graph, ctx, logits, pinned = self._graphs[bucket]
+        host, facts = self._fill(ctx.meta_layout, entries, updates)
+        ctx.__dict__.update(facts)
+        pinned.copy_(torch.from_numpy(host))
+        ctx.buffer.copy_(pinned, non_blocking=True)
+        self.last_ctx, self.last_h2d_bytes = ctx, host.nbytes
+        graph.replay()
+        self.graph_replays += 1
+        ops.launch_count += self.launches_per_graph[bucket]
+        return logits[:len(entries)]
+
+    def _capture(self, bucket: int):
+        """Captures the forward pass of ``bucket`` single-token entries.  The capture itself runs on empty
+        entries (length 0), which store nothing and attend to nothing."""
+        lay = MetaLayout(bucket, bucket, bucket, bucket, len(self.tables))
+        dev = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
+        pinned = torch.zeros(lay.size, dtype=torch.int32).pin_memory()
+        ctx = StepContext(self, lay, dev, static=True)
+        host = np.zeros(lay.size, dtype=np.int32)
+        o = lay.offsets
+        for g in range(len(self.tables)):
+            host[o[f"slot_map{g}"][0]:o[f"slot_map{g}"][1]] = -1
+        host[o["logit_rows"][0]:o["logit_rows"][1]] = np.arange(bucket)
+        dev.copy_(torch.from_numpy(host))
+        ctx.host_q_len, ctx.host_q_start = [1] * bucket, list(range(bucket))
+        ctx.host_ctx_len, ctx.host_slots = [0] * bucket, [0] * bucket
+
+        def run():
+            self._apply_table_updates(ctx)
+            return self.model.forward(ctx, self.cache.views)
+
+        # warm up on a side stream (library handles, lazy module loads), then capture
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            run()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        before = ops.launch_count
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = run()
+        self.launches_per_graph[bucket] = ops.launch_count - before
+        self._graphs[bucket] = (graph, ctx, logits, pinned)

@@ -57,7 +57,10 @@ def _declare(L):
         "vcb_swiglu": [P, P, I, I, I, P],
         "vcb_qknorm_rope_kvwrite": [P, I, P, P, I, I, F, P, I, P, P, P, P, LL, I, I, I, I, I, I, I, P, P],
         "vcb_sgemm_tn": [P, P, P, I, I, I, LL, LL, LL, P],
-        "vcb_attn_paged": [P, P, I, P, LL, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, P],
+        "vcb_attn_paged": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, P],
+        "vcb_scatter_i32": [P, P, P, P, I, LL, P],
+        "vcb_attn_mma": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, P],
+        "vcb_attn_mma_supported": [I, I],
         "vcb_attn_merge": [P, P, P, P, I, I, I, I, I, P],
         "vcb_sample": [P, LL, I, I, P, P, P, P],
         "vcb_count_tokens": [P, P, P, I, I, P],
@@ -182,14 +185,15 @@ def sgemm_tn(a, b, out):
 
 
 def attn_paged(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, rows_max, part_o, part_ml,
-               nh, nkv, hd, window, status):
+               nh, nkv, hd, window, status, table_row=None):
+    """block_table int32 [rows, max_blocks]; entry e reads row ``table_row[e]`` (row e when table_row is None)."""
     _need(q, "q"); _need(out, "out", q.dtype); _need(pages, "pages", q.dtype)
     for name, t in (("block_table", block_table), ("q_start", q_start), ("q_len", q_len), ("ctx_len", ctx_len),
                     ("items", items)):
         _need(t, name, torch.int32)
     num_pages, two, nkv_p, page_size, hd_p = pages.shape
     assert two == 2 and nkv_p == nkv and hd_p == hd
-    _call("vcb_attn_paged", _p(q), _p(out), _dt(q), _p(pages), pages.stride(0), _p(block_table), block_table.shape[1],
+    _call("vcb_attn_paged", _p(q), _p(out), _dt(q), _p(pages), pages.stride(0), _p(block_table), _p(table_row), block_table.shape[1],
           _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, rows_max, _p(part_o), _p(part_ml), nh, nkv, hd,
           page_size, num_pages, int(window or 0), 1.0 / math.sqrt(hd), _p(status), _stream())
 
@@ -215,3 +219,29 @@ def sample(logits, params, counts, out):
 def count_tokens(ids, slots, counts, n):
     _need(ids, "ids", torch.int32); _need(slots, "slots", torch.int32); _need(counts, "counts", torch.int32)
     _call("vcb_count_tokens", _p(ids), _p(slots), _p(counts), n, counts.shape[1], _stream())
+
+
+def scatter_i32(dst, idx, val, count, capacity):
+    """dst.flat[idx[i]] = val[i] for i < min(count[0], capacity); count is a device int32."""
+    _need(dst, "dst", torch.int32); _need(idx, "idx", torch.int32); _need(val, "val", torch.int32)
+    _need(count, "count", torch.int32)
+    _call("vcb_scatter_i32", _p(dst), _p(idx), _p(val), _p(count), capacity, dst.numel(), _stream())
+
+
+def attn_mma_supported(dtype: torch.dtype, hd: int) -> bool:
+    """Whether the tensor-core attention kernel takes this element type and head size."""
+    return bool(lib().vcb_attn_mma_supported(BF16 if dtype == torch.bfloat16 else F32, hd))
+
+
+def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, rows_max, part_o, part_ml,
+             nh, nkv, hd, window, status, table_row=None):
+    """Tensor-core variant of :func:`attn_paged` (bfloat16, head_dim 64 or 128; rows_max 16 or 64)."""
+    _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(pages, "pages", torch.bfloat16)
+    for name, t in (("block_table", block_table), ("q_start", q_start), ("q_len", q_len), ("ctx_len", ctx_len),
+                    ("items", items)):
+        _need(t, name, torch.int32)
+    num_pages, two, nkv_p, page_size, hd_p = pages.shape
+    assert two == 2 and nkv_p == nkv and hd_p == hd
+    _call("vcb_attn_mma", _p(q), _p(out), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
+          block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, rows_max, _p(part_o),
+          _p(part_ml), nh, nkv, hd, page_size, num_pages, int(window or 0), 1.0 / math.sqrt(hd), _p(status), _stream())

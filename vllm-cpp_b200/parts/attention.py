@@ -23,16 +23,18 @@ from ..weights.loader import TensorSpec
 from .base import CacheSpec, Mixer
 from .linear import matmul_tn
 
-DECODE_ROWS = 8     # rows a block of the decode variant of the attention kernel holds
-SPAN_ROWS = 32      # rows of the prompt-portion variant
-MAX_SLICES = 32
-TARGET_BLOCKS = 2 * 148
+DECODE_ROWS = 8     # rows a block of the decode variant of the plain attention kernel holds
+SPAN_ROWS = 32      # rows of its prompt-portion variant
+MMA_DECODE_ROWS = 16   # the same for the tensor-core kernel
+MMA_SPAN_ROWS = 64
+MAX_SLICES = 64
+TARGET_BLOCKS = 6 * 148
 
 
 class AttentionPlan:
     """Work items of the attention kernel for one step and one head layout, on the device."""
 
-    def __init__(self, ctx, nh: int, nkv: int):
+    def __init__(self, ctx, nh: int, nkv: int, decode_rows: int = DECODE_ROWS, span_rows: int = SPAN_ROWS):
         g = nh // nkv
         dev = ctx.device
         dec = [i for i, n in enumerate(ctx.host_q_len) if n == 1]
@@ -42,10 +44,12 @@ class AttentionPlan:
         self.dec_items = self.dec_rows = self.span_items = None
         self.n_span_items = 0
         if dec:
-            hchunks = -(-g // min(g, DECODE_ROWS))
+            hchunks = -(-g // min(g, decode_rows))
             blocks = len(dec) * nkv * hchunks
-            max_ctx = max(ctx.host_ctx_len[i] for i in dec)
-            by_pages = max(1, max_ctx // 256)      # at least 256 keys a slice
+            if getattr(ctx, "static", False):
+                by_pages = MAX_SLICES              # a captured step serves any context length
+            else:
+                by_pages = max(1, max(ctx.host_ctx_len[i] for i in dec) // 256)   # at least 256 keys a slice
             self.nslices = int(max(1, min(MAX_SLICES, by_pages, -(-TARGET_BLOCKS // blocks))))
             items = np.zeros((len(dec) * self.nslices, ops.ITEM_INTS), dtype=np.int32)
             k = 0
@@ -56,7 +60,7 @@ class AttentionPlan:
             self.dec_items = torch.from_numpy(items).to(dev)
             self.dec_rows = torch.tensor([ctx.host_q_start[e] for e in dec], dtype=torch.int32).to(dev)
         if spans:
-            nq_max = max(1, SPAN_ROWS // min(g, SPAN_ROWS))
+            nq_max = max(1, span_rows // min(g, span_rows))
             rows = []
             for e in spans:
                 n = ctx.host_q_len[e]
@@ -129,19 +133,22 @@ class GQAAttention(Mixer):
                                 group.slot_map, q, cache.pages, nh, nkv, hd, ctx.status,
                                 has_kv=self.has_kv, use_norm=self.qk_norm)
         out = torch.empty_like(q)
-        plan = ctx.plan(("attention", nh, nkv), lambda: AttentionPlan(ctx, nh, nkv))
-        common = dict(nh=nh, nkv=nkv, hd=hd, window=self.window, status=ctx.status)
+        mma = ops.attn_mma_supported(x.dtype, hd)
+        kernel = ops.attn_mma if mma else ops.attn_paged
+        dec_rows, span_rows = (MMA_DECODE_ROWS, MMA_SPAN_ROWS) if mma else (DECODE_ROWS, SPAN_ROWS)
+        plan = ctx.plan(("attention", nh, nkv, mma), lambda: AttentionPlan(ctx, nh, nkv, dec_rows, span_rows))
+        common = dict(nh=nh, nkv=nkv, hd=hd, window=self.window, status=ctx.status, table_row=ctx.slots)
         if plan.n_dec:
             S = plan.nslices
             part_o = part_ml = None
             if S > 1:
                 part_o = torch.empty((plan.n_dec * nh * S, hd), dtype=torch.float32, device=x.device)
                 part_ml = torch.empty((plan.n_dec * nh * S, 2), dtype=torch.float32, device=x.device)
-            ops.attn_paged(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
-                           plan.dec_items, plan.n_dec * S, DECODE_ROWS, part_o, part_ml, **common)
+            kernel(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
+                   plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml, **common)
             if S > 1:
                 ops.attn_merge(part_o, part_ml, plan.dec_rows, out, plan.n_dec, nh, hd, S)
         if plan.n_span_items:
-            ops.attn_paged(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
-                           plan.span_items, plan.n_span_items, SPAN_ROWS, None, None, **common)
+            kernel(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
+                   plan.span_items, plan.n_span_items, span_rows, None, None, **common)
         return matmul_tn(out, self.w_o, out_dtype=torch.float32)
