@@ -171,7 +171,8 @@ def run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft=None):
     from vllm_cpp_b200 import ops
     plan = _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma=False)
     if ops.attn_mma_supported(dtype, hd):
-        plan = _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma=True)
+        plan = _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma=True)           # TMA tile loads where the page size allows
+        plan = _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma="no_tma")      # cp.async tile loads
     return plan
 
 
@@ -181,7 +182,8 @@ def _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma):
     from vllm_cpp_b200.parts import attention as A
     DECODE_ROWS, SPAN_ROWS = (A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS) if mma else (A.DECODE_ROWS, A.SPAN_ROWS)
     AttentionPlan = lambda c, h, k: A.AttentionPlan(c, h, k, DECODE_ROWS, SPAN_ROWS)
-    kernel = ops.attn_mma if mma else ops.attn_paged
+    import functools
+    kernel = (functools.partial(ops.attn_mma, allow_tma=(mma is True)) if mma else ops.attn_paged)
     torch.manual_seed(1)
     seqs, qs = [], []
     for start, n in shapes:
@@ -353,3 +355,96 @@ def test_kernels_refuse_what_they_cannot_do():
     items = torch.zeros(1, 6, dtype=torch.int32, device=dev())
     with pytest.raises(ops.KernelError, match="multiple of 16"):
         ops.attn_paged(q, q.clone(), pages, z.view(1, 1), z, z, z, items, 1, 8, None, None, 1, 1, 24, 0, z)
+
+
+@pytest.mark.parametrize("M,T,K,splits", [
+    (128, 16, 64, 1), (128, 1, 64, 1), (64, 3, 96, 1), (200, 17, 200, 1), (384, 8, 4096, 4), (6144, 8, 4096, 3),
+    (4096, 64, 1024, 2), (1000, 33, 520, 2), (256, 100, 256, 1), (384, 256, 512, 1), (300, 700, 328, 1),
+    (4096, 2048, 512, 1), (128, 130, 8, 1)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_bf16_tn(M, T, K, splits, out_dtype):
+    """The tcgen05/TMA product against 64-bit: tile edges in every dimension, k tails, k-slices, 1 to 2048 tokens."""
+    from vllm_cpp_b200 import ops
+    if splits > 1 and out_dtype != torch.float32:
+        pytest.skip("k-slices write 32-bit partial sums")
+    torch.manual_seed(M + T + K)
+    w = torch.randn(M, K, device=dev()).to(torch.bfloat16)
+    x = torch.randn(T, K, device=dev()).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    S = ops.gemm_effective_splits(K, splits)
+    out = torch.full((S, T, M) if S > 1 else (T, M), float("nan"), dtype=out_dtype, device=dev())
+    ops.gemm_bf16_tn(w, x, out, splits, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    got = out.double().sum(0) if S > 1 else out.double()
+    want = x.double() @ w.double().T
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(got, want, rtol=1e-4, atol=K * 2.0 ** -24 * 64)
+    else:
+        torch.testing.assert_close(got, want, rtol=1e-2, atol=1e-2 * K ** 0.5)
+    # a token's result does not depend on what else is in the batch
+    if T > 1 and S == 1:
+        one = torch.empty((1, M), dtype=out_dtype, device=dev())
+        ops.gemm_bf16_tn(w, x[T - 1:T].contiguous(), one, 1, status)
+        assert torch.equal(one[0], out[T - 1])
+
+
+def test_gemm_bf16_tn_refuses_unaligned_rows():
+    from vllm_cpp_b200 import ops
+    w = torch.zeros(128, 100, device=dev(), dtype=torch.bfloat16)
+    x = torch.zeros(4, 100, device=dev(), dtype=torch.bfloat16)
+    out = torch.zeros(4, 128, device=dev())
+    with pytest.raises(ops.KernelError, match="multiples of 8"):
+        ops.gemm_bf16_tn(w, x, out, 1, torch.zeros(1, dtype=torch.int32, device=dev()))
+
+
+@pytest.mark.parametrize("out_dtype", DTYPES)
+def test_partial_sum_inputs(out_dtype):
+    """The kernels that read a product cut into k-slices add the slices themselves."""
+    from vllm_cpp_b200 import ops
+    T, I, S = 5, 72, 3
+    parts = torch.randn(S, T, 2 * I, device=dev())
+    out = torch.empty(T, I, device=dev(), dtype=out_dtype)
+    ops.swiglu(parts, out)
+    tot = parts.double().sum(0)
+    g, u = tot[:, :I], tot[:, I:]
+    torch.testing.assert_close(out.double(), g / (1 + torch.exp(-g)) * u, **tol(out_dtype))
+
+    nh, nkv, hd, ps, num_pages, eps = 4, 2, 32, 4, 6, 1e-6
+    qkv = torch.randn(S, T, (nh + 2 * nkv) * hd, device=dev())
+    one = qkv.sum(0)
+    w = torch.ones(hd, device=dev())
+    table = rope_table(hd, 1e4, 64)
+    pos = torch.arange(T, device=dev(), dtype=torch.int32)
+    slots = torch.arange(T, device=dev(), dtype=torch.int32)
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    res = []
+    for inp in (qkv, one):
+        pages = torch.zeros(num_pages, 2, nkv, ps, hd, device=dev(), dtype=out_dtype)
+        q = torch.empty(T, nh * hd, device=dev(), dtype=out_dtype)
+        ops.qknorm_rope_kvwrite(inp, w, w, eps, table, pos, slots, q, pages, nh, nkv, hd, status)
+        res.append((q.double(), pages.double()))
+    torch.testing.assert_close(res[0][0], res[1][0], **tol(out_dtype))
+    torch.testing.assert_close(res[0][1], res[1][1], **tol(out_dtype))
+
+
+def test_sampling_split_over_blocks_matches_plain():
+    """Rows without a nucleus cut are dealt to several blocks per row; the token is the same."""
+    from vllm_cpp_b200.sampling import Sampler, SamplingOptions
+    V = 50021
+    rng = np.random.default_rng(5)
+    logits = torch.tensor(rng.normal(0, 2, size=(5, V)), dtype=torch.float32)
+    logits[0, 40000] = logits[0, 17] = logits[0].max() + 1   # greedy tie across blocks: lowest index
+    opts = [SamplingOptions(0.0, 1.0, 1.0, 0), SamplingOptions(0.0, 0.5, 1.0, 0), SamplingOptions(0.8, 1.0, 1.0, 4),
+            SamplingOptions(1.3, 1.0, 1.0, 5), SamplingOptions(0.7, 1.0, 1.3, 6)]
+    s = Sampler(V, 5, dev())
+    s._need_counts()
+    hist = rng.integers(0, V, 40).tolist() + [int(logits[4].argmax())] * 2
+    for t in hist:
+        s.counts[4, t] += 1
+    got = s.sample(logits.to(dev()), opts, [3, 4, 5, 6, 7], [0, 1, 2, 3, 4]).cpu().tolist()
+    for i, o in enumerate(opts):
+        want = plain_sample(logits[i].numpy(), temperature=o.temperature, top_p=o.top_p, repeat_penalty=o.repeat_penalty,
+                            history=hist if i == 4 else (), seed=o.seed, step=3 + i)
+        assert got[i] == want, (i, got[i], want)
+    assert got[0] == 17

@@ -17,9 +17,19 @@
 //    partial softmax states merged through shared memory at the end.
 // Rows beyond the item's real rows and keys beyond the slice are zero-filled and
 // masked, never read from memory that is not theirs.
+//
+// Two loaders feed the same multiply code.  With pages of 8, 16, 32 or 64 tokens a fifth warp issues TMA
+// tile loads (cp.async.bulk.tensor with 128-byte swizzle, one box per page and 64 lanes of head_dim) into a
+// ring of three stages guarded by full/empty mbarriers, so the four multiplying warps spend no instructions
+// on addresses; every wait is bounded and reports through the status word.  Other page sizes use cp.async
+// from all threads with two stages.
 #include "common.cuh"
 
+#include <cuda.h>
 #include <math_constants.h>
+
+#include <mutex>
+#include <unordered_map>
 
 namespace {
 
@@ -72,12 +82,55 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// byte offset of 16-byte chunk `c` of row `r` in a tile whose rows are ROWB bytes
-template <int ROWB> __device__ __forceinline__ int swz(int r, int c) { return r * ROWB + ((c ^ (r & 7)) << 4); }
+// Byte offset of 16-byte chunk `c` of row `r` in a tile of ROWS rows: the tile is stored as head_dim/64 blocks of
+// [ROWS][128 bytes], each 128-byte row XOR-swizzled by its row index -- the layout a 128-byte-swizzled TMA box
+// of 64 lanes produces, and conflict-free for ldmatrix.
+template <int ROWS> __device__ __forceinline__ int swz(int r, int c) {
+    return (c >> 3) * (ROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+}
 
-// WR row groups x WK key groups = 4 warps
-template <int HD, int WR, int WK>
-__global__ __launch_bounds__(NT) void attn_mma_kernel(AttnArgs a) {
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+constexpr long long WAIT_CLOCKS = 2000000000ll;   // about a second
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_CLOCKS) {
+            *abort_flag = 1;
+            atomicOr(status, VCB_STATUS_WAIT_TIMEOUT);
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+// WR row groups x WK key groups = 4 multiplying warps; TMA adds a fifth warp that only issues tile loads.
+template <int HD, int WR, int WK, bool TMA>
+__global__ __launch_bounds__(TMA ? NT + 32 : NT) void attn_mma_kernel(const __grid_constant__ CUtensorMap kv_map,
+                                                                        AttnArgs a) {
     static_assert(WR * WK == 4 && HD % 64 == 0, "layout");
     constexpr int RMAX = 16 * WR;   // rows a block holds
     constexpr int CH = HD / 8;      // 16-byte chunks per row
@@ -85,15 +138,23 @@ __global__ __launch_bounds__(NT) void attn_mma_kernel(AttnArgs a) {
     constexpr int KW = BN / WK;     // keys of a tile that one warp multiplies
     constexpr int NS = KW / 8;      // score n-tiles per warp
     constexpr int ND = HD / 8;      // output n-tiles
+    constexpr int STAGES = (TMA && WK == 4) ? 3 : 2;   // decoding streams keys: a deeper ring; prompt portions multiply more
+    constexpr int TILE_BYTES = BN * ROWB;   // one K or V tile
     constexpr float LOG2E = 1.4426950408889634f;
 
-    extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t* q_s = smem;
-    uint8_t* k_s = q_s + RMAX * ROWB;        // 2 stages
-    uint8_t* v_s = k_s + 2 * BN * ROWB;      // 2 stages
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base_u32 = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzle atoms are 1024-byte aligned
+    uint8_t* smem = smem_raw + (base_u32 - smem_u32(smem_raw));
+    uint8_t* k_s = smem;                              // STAGES tiles
+    uint8_t* v_s = k_s + STAGES * TILE_BYTES;         // STAGES tiles
+    uint8_t* q_s = v_s + STAGES * TILE_BYTES;         // RMAX rows
+    uint8_t* bar_s = q_s + RMAX * ROWB;               // 2 * STAGES mbarriers, then the abort flag
+    auto full_bar = [&](int st) { return smem_u32(bar_s) + 8u * st; };
+    auto empty_bar = [&](int st) { return smem_u32(bar_s) + 8u * (STAGES + st); };
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_s + 16 * STAGES);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int wr = warp / WK, wk = warp % WK;
+    const int wr = (warp & 3) / WK, wk = (warp & 3) % WK;
     const int* item = a.items + (size_t)blockIdx.x * ITEM_INTS;
     const int e = item[0], q0 = item[1], nq = item[2], slice = item[3], nslices = item[4], dec_index = item[5];
 
@@ -118,25 +179,37 @@ __global__ __launch_bounds__(NT) void attn_mma_kernel(AttnArgs a) {
     const int pps = (pb_hi - pb_lo + nslices - 1) / nslices;
     const int my_pb_lo = pb_lo + slice * pps, my_pb_hi = min(pb_hi, my_pb_lo + pps);
     const int k_begin = max(lo, my_pb_lo * ps), k_end = min(hi, my_pb_hi * ps);
-    const int n_tiles = k_end > k_begin ? (k_end - k_begin + BN - 1) / BN : 0;
+    // tiles start on a page boundary when TMA loads whole pages
+    const int t_first = TMA ? my_pb_lo * ps : k_begin;
+    const int n_tiles = k_end > k_begin ? (k_end - t_first + BN - 1) / BN : 0;
 
     const int* bt = a.block_table + (size_t)(a.table_row ? a.table_row[e] : e) * a.max_blocks;
 
+    if (TMA && tid == 0) {
+        for (int st = 0; st < STAGES; ++st) {
+            mbar_init(full_bar(st), 1);
+            mbar_init(empty_bar(st), 4);   // one arrival per multiplying warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+
     // ---- Q rows -> shared memory (rows beyond R are zero) ----
-    for (int idx = tid; idx < RMAX * CH; idx += NT) {
+    for (int idx = tid; idx < RMAX * CH; idx += blockDim.x) {
         const int r = idx / CH, c = idx % CH;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (r < R) {
             const int iq = r / gq, ih = r % gq;
             v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(row0 + iq) * a.nh + head0 + ih) * HD + c * 8);
         }
-        *reinterpret_cast<uint4*>(q_s + swz<ROWB>(r, c)) = v;
+        *reinterpret_cast<uint4*>(q_s + swz<RMAX>(r, c)) = v;
     }
 
-    // ---- tile loader: 64 keys x HD of K and of V, gathered page by page ----
+    // ---- cp.async loader (all threads): 64 keys x HD of K and of V, gathered page by page ----
     auto load_tile = [&](int stage, int t0) {
-        uint8_t* kd = k_s + stage * BN * ROWB;
-        uint8_t* vd = v_s + stage * BN * ROWB;
+        uint8_t* kd = k_s + stage * TILE_BYTES;
+        uint8_t* vd = v_s + stage * TILE_BYTES;
 #pragma unroll
         for (int i = 0; i < BN * CH / NT; ++i) {
             const int idx = tid + i * NT;
@@ -153,21 +226,55 @@ __global__ __launch_bounds__(NT) void attn_mma_kernel(AttnArgs a) {
                     bytes = 16;
                 }
             }
-            const int off = swz<ROWB>(j, c);
+            const int off = swz<BN>(j, c);
             cp_async16(smem_u32(kd + off), src, bytes);
             cp_async16(smem_u32(vd + off), bytes ? src + (size_t)a.nkv * ps * HD : src, bytes);
         }
     };
 
-    if (n_tiles > 0) load_tile(0, k_begin);
-    cp_async_commit();
-    __syncthreads();   // Q is in shared memory
+    if (!TMA) {
+        if (n_tiles > 0) load_tile(0, t_first);
+        cp_async_commit();
+    }
+    __syncthreads();   // Q and the barriers are in shared memory
 
-    // ---- Q fragments stay in registers ----
-    uint32_t qf[HD / 16][4];
+    if (TMA && warp == 4) {
+        // ---- TMA producer: one box of [page_size keys x 64 lanes] per page, per half of head_dim, for K and V ----
+        if (lane == 0) {
+            const int pages_per_tile = BN / ps;
+            const int rows_kv = a.nkv * ps;          // rows of the flattened [pages * 2 * nkv * ps, HD] view per K or V
+            int armed = 0;
+            for (int it = 0; it < n_tiles; ++it) {
+                const int st = it % STAGES;
+                if (!mbar_wait(empty_bar(st), ((it / STAGES) & 1) ^ 1u, abort_flag, a.status)) break;
+                const int pb0 = my_pb_lo + it * pages_per_tile;
+                const int np = min(pages_per_tile, my_pb_hi - pb0);
+                mbar_expect_tx(full_bar(st), (uint32_t)(np * ps * ROWB * 2));
+                const uint32_t kd = smem_u32(k_s + st * TILE_BYTES), vd = smem_u32(v_s + st * TILE_BYTES);
+                for (int pg = 0; pg < np; ++pg) {
+                    int page = bt[pb0 + pg];
+                    if (page < 0 || page >= a.num_pages) {
+                        atomicOr(a.status, VCB_STATUS_BAD_PAGE);
+                        page = 0;   // keep the byte count whole; the status word reports the fault
+                    }
+                    const int krow = (page * 2 * a.nkv + kvh) * ps;
 #pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks)
-        ldmatrix_x4(qf[ks], smem_u32(q_s + swz<ROWB>(wr * 16 + (lane & 15), ks * 2 + (lane >> 4))));
+                    for (int h = 0; h < HD / 64; ++h) {
+                        const uint32_t off = h * (BN * 128) + pg * ps * 128;
+                        tma_load_2d(kd + off, &kv_map, full_bar(st), h * 64, krow);
+                        tma_load_2d(vd + off, &kv_map, full_bar(st), h * 64, krow + rows_kv);
+                    }
+                }
+                armed = it + 1;
+            }
+            if (*abort_flag) {   // let copies in flight land before the block goes away
+                for (int i = max(0, armed - STAGES); i < armed; ++i) {
+                    const long long t0 = clock64();
+                    while (!mbar_try(full_bar(i % STAGES), (i / STAGES) & 1) && clock64() - t0 < WAIT_CLOCKS) {}
+                }
+            }
+        }
+    }
 
     float o[ND][4];
 #pragma unroll
@@ -178,106 +285,154 @@ __global__ __launch_bounds__(NT) void attn_mma_kernel(AttnArgs a) {
     const int pos_a = pos0 + r_a / gq, pos_b = pos0 + r_b / gq;
     const bool ok_a = r_a < R, ok_b = r_b < R;
 
-    for (int it = 0; it < n_tiles; ++it) {
-        if (it + 1 < n_tiles) {
-            load_tile((it + 1) & 1, k_begin + (it + 1) * BN);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
-        const uint8_t* kt = k_s + (it & 1) * BN * ROWB;
-        const uint8_t* vt = v_s + (it & 1) * BN * ROWB;
-        const int key0 = k_begin + it * BN + wk * KW;   // first key this warp multiplies
+    if (warp < 4) {
+        // ---- Q fragments stay in registers ----
+        uint32_t qf[HD / 16][4];
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+            ldmatrix_x4(qf[ks], smem_u32(q_s + swz<RMAX>(wr * 16 + (lane & 15), ks * 2 + (lane >> 4))));
 
-        // S = Q K^T
-        float s[NS][4];
+        for (int it = 0; it < n_tiles; ++it) {
+            const int st = it % STAGES;
+            const int t0 = t_first + it * BN;
+            if (TMA) {
+                if (!mbar_wait(full_bar(st), (it / STAGES) & 1, abort_flag, a.status)) break;
+                if (t0 + BN > k_end) {
+                    // the last page may hold slots beyond the sequence (and rows of pages not loaded are stale):
+                    // their V must be finite, because a zero weight times NaN is NaN.  Each warp clears what it reads.
+                    for (int idx = lane; idx < KW * CH; idx += 32) {
+                        const int j = wk * KW + idx / CH, c = idx % CH;
+                        if (t0 + j >= k_end) *reinterpret_cast<uint4*>(v_s + st * TILE_BYTES + swz<BN>(j, c)) = make_uint4(0, 0, 0, 0);
+                    }
+                    __syncwarp();
+                }
+            } else {
+                if (it + 1 < n_tiles) {
+                    load_tile((it + 1) & 1, t0 + BN);
+                    cp_async_commit();
+                    cp_async_wait<1>();
+                } else {
+                    cp_async_wait<0>();
+                }
+                __syncthreads();
+            }
+            const uint8_t* kt = k_s + st * TILE_BYTES;
+            const uint8_t* vt = v_s + st * TILE_BYTES;
+            const int key0 = t0 + wk * KW;   // first key this warp multiplies
+
+            // S = Q K^T
+            float s[NS][4];
 #pragma unroll
-        for (int i = 0; i < NS; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+            for (int i = 0; i < NS; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
+            for (int ks = 0; ks < HD / 16; ++ks) {
 #pragma unroll
-            for (int np = 0; np < KW / 16; ++np) {
-                uint32_t b[4];
-                const int mi = lane >> 3;
-                const int krow = wk * KW + np * 16 + (mi >> 1) * 8 + (lane & 7);
-                ldmatrix_x4(b, smem_u32(kt + swz<ROWB>(krow, ks * 2 + (mi & 1))));
-                mma_16816(s[2 * np], qf[ks], b[0], b[1]);
-                mma_16816(s[2 * np + 1], qf[ks], b[2], b[3]);
+                for (int np = 0; np < KW / 16; ++np) {
+                    uint32_t b[4];
+                    const int mi = lane >> 3;
+                    const int krow = wk * KW + np * 16 + (mi >> 1) * 8 + (lane & 7);
+                    ldmatrix_x4(b, smem_u32(kt + swz<BN>(krow, ks * 2 + (mi & 1))));
+                    mma_16816(s[2 * np], qf[ks], b[0], b[1]);
+                    mma_16816(s[2 * np + 1], qf[ks], b[2], b[3]);
+                }
+            }
+            // mask (only where the tile touches an edge of some row's key range), running maximum
+            // rows beyond R hold zero queries and are never written, so they need no mask of their own
+            const bool inner = key0 >= k_begin && key0 + KW <= k_end && key0 + KW - 1 <= pos0 && (W <= 0 || key0 > pos_last - W);
+            float mx_a = -CUDART_INF_F, mx_b = -CUDART_INF_F;
+            if (__all_sync(0xffffffffu, inner)) {
+#pragma unroll
+                for (int i = 0; i < NS; ++i) {
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        s[i][c] *= a.scale;
+                        s[i][2 + c] *= a.scale;
+                        mx_a = fmaxf(mx_a, s[i][c]);
+                        mx_b = fmaxf(mx_b, s[i][2 + c]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < NS; ++i) {
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const int kidx = key0 + i * 8 + 2 * (lane & 3) + c;
+                        const bool in = kidx >= k_begin && kidx < k_end;
+                        const bool sa = ok_a && in && kidx <= pos_a && (W <= 0 || kidx > pos_a - W);
+                        const bool sb = ok_b && in && kidx <= pos_b && (W <= 0 || kidx > pos_b - W);
+                        s[i][c] = sa ? s[i][c] * a.scale : -CUDART_INF_F;
+                        s[i][2 + c] = sb ? s[i][2 + c] * a.scale : -CUDART_INF_F;
+                        mx_a = fmaxf(mx_a, s[i][c]);
+                        mx_b = fmaxf(mx_b, s[i][2 + c]);
+                    }
+                }
+            }
+            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+            const float mn_a = fmaxf(m_run[0], mx_a), mn_b = fmaxf(m_run[1], mx_b);
+            const float use_a = mn_a == -CUDART_INF_F ? 0.f : mn_a, use_b = mn_b == -CUDART_INF_F ? 0.f : mn_b;
+            const bool moved = mn_a != m_run[0] || mn_b != m_run[1];
+            const float al_a = exp2f((m_run[0] - use_a) * LOG2E), al_b = exp2f((m_run[1] - use_b) * LOG2E);
+            m_run[0] = mn_a;
+            m_run[1] = mn_b;
+            float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+            for (int i = 0; i < NS; ++i) {
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    s[i][c] = exp2f((s[i][c] - use_a) * LOG2E);
+                    s[i][2 + c] = exp2f((s[i][2 + c] - use_b) * LOG2E);
+                    sum_a += s[i][c];
+                    sum_b += s[i][2 + c];
+                }
+            }
+            l_run[0] = l_run[0] * al_a + sum_a;
+            l_run[1] = l_run[1] * al_b + sum_b;
+            if (__any_sync(0xffffffffu, moved)) {   // the running maximum seldom moves after the first tiles
+#pragma unroll
+                for (int i = 0; i < ND; ++i) {
+                    o[i][0] *= al_a; o[i][1] *= al_a; o[i][2] *= al_b; o[i][3] *= al_b;
+                }
+            }
+            // O += P V
+#pragma unroll
+            for (int kk = 0; kk < KW / 16; ++kk) {
+                uint32_t pa[4];
+                pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+                pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int dp = 0; dp < HD / 16; ++dp) {
+                    uint32_t b[4];
+                    const int mi = lane >> 3;
+                    const int vrow = wk * KW + kk * 16 + (mi & 1) * 8 + (lane & 7);
+                    ldmatrix_x4_trans(b, smem_u32(vt + swz<BN>(vrow, dp * 2 + (mi >> 1))));
+                    mma_16816(o[2 * dp], pa, b[0], b[1]);
+                    mma_16816(o[2 * dp + 1], pa, b[2], b[3]);
+                }
+            }
+            if (TMA) {
+                if (t0 + BN > k_end) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the clearing stores above
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_bar(st));   // this warp is done with the stage
+            } else {
+                __syncthreads();   // the stage may be overwritten by the load issued in the next iteration
             }
         }
-        // mask, running maximum
-        float mx_a = -CUDART_INF_F, mx_b = -CUDART_INF_F;
-#pragma unroll
-        for (int i = 0; i < NS; ++i) {
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                const int kidx = key0 + i * 8 + 2 * (lane & 3) + c;
-                const bool in = kidx < k_end;
-                const bool sa = ok_a && in && kidx <= pos_a && (W <= 0 || kidx > pos_a - W);
-                const bool sb = ok_b && in && kidx <= pos_b && (W <= 0 || kidx > pos_b - W);
-                s[i][c] = sa ? s[i][c] * a.scale : -CUDART_INF_F;
-                s[i][2 + c] = sb ? s[i][2 + c] * a.scale : -CUDART_INF_F;
-                mx_a = fmaxf(mx_a, s[i][c]);
-                mx_b = fmaxf(mx_b, s[i][2 + c]);
-            }
-        }
-        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
-        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
-        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
-        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-        const float mn_a = fmaxf(m_run[0], mx_a), mn_b = fmaxf(m_run[1], mx_b);
-        const float use_a = mn_a == -CUDART_INF_F ? 0.f : mn_a, use_b = mn_b == -CUDART_INF_F ? 0.f : mn_b;
-        const float al_a = exp2f((m_run[0] - use_a) * LOG2E), al_b = exp2f((m_run[1] - use_b) * LOG2E);
-        m_run[0] = mn_a;
-        m_run[1] = mn_b;
-        float sum_a = 0.f, sum_b = 0.f;
-#pragma unroll
-        for (int i = 0; i < NS; ++i) {
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                s[i][c] = exp2f((s[i][c] - use_a) * LOG2E);
-                s[i][2 + c] = exp2f((s[i][2 + c] - use_b) * LOG2E);
-                sum_a += s[i][c];
-                sum_b += s[i][2 + c];
-            }
-        }
-        l_run[0] = l_run[0] * al_a + sum_a;
-        l_run[1] = l_run[1] * al_b + sum_b;
-#pragma unroll
-        for (int i = 0; i < ND; ++i) {
-            o[i][0] *= al_a; o[i][1] *= al_a; o[i][2] *= al_b; o[i][3] *= al_b;
-        }
-        // O += P V
-#pragma unroll
-        for (int kk = 0; kk < KW / 16; ++kk) {
-            uint32_t pa[4];
-            pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-            pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-            pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-            pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-#pragma unroll
-            for (int dp = 0; dp < HD / 16; ++dp) {
-                uint32_t b[4];
-                const int mi = lane >> 3;
-                const int vrow = wk * KW + kk * 16 + (mi & 1) * 8 + (lane & 7);
-                ldmatrix_x4_trans(b, smem_u32(vt + swz<ROWB>(vrow, dp * 2 + (mi >> 1))));
-                mma_16816(o[2 * dp], pa, b[0], b[1]);
-                mma_16816(o[2 * dp + 1], pa, b[2], b[3]);
-            }
-        }
-        __syncthreads();   // the stage may be overwritten by the load issued two iterations on
     }
+    __syncthreads();   // every tile has been multiplied; the stages are free
 
     // ---- partial states -> shared memory: o_s[wk][row][HD], ml_s[wk][row][2] ----
-    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
-    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
-    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
-    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
-    float* o_s = reinterpret_cast<float*>(k_s);             // 64 x HD floats = the four K/V stages' first half
+    float* o_s = reinterpret_cast<float*>(k_s);             // 64 x HD floats, over the K stages (and into V's)
     float* ml_s = o_s + 64 * HD;                            // 64 x 2 floats
-    {
+    if (warp < 4) {
+        l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
+        l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
+        l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
+        l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
         const int ra = wk * RMAX + r_a, rb = wk * RMAX + r_b;
 #pragma unroll
         for (int i = 0; i < ND; ++i) {
@@ -293,7 +448,7 @@ __global__ __launch_bounds__(NT) void attn_mma_kernel(AttnArgs a) {
     __syncthreads();
 
     // ---- merge the key groups and write ----
-    for (int idx = tid; idx < R * (HD / 2); idx += NT) {
+    for (int idx = tid; idx < R * (HD / 2); idx += blockDim.x) {
         const int r = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
         float m = -CUDART_INF_F;
 #pragma unroll
@@ -325,16 +480,90 @@ __global__ __launch_bounds__(NT) void attn_mma_kernel(AttnArgs a) {
     }
 }
 
-template <int HD, int WR, int WK>
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// The pages of one layer seen as a matrix [num_pages * 2 * nkv * page_size, HD]; boxes of [page_size rows, 64 lanes].
+bool kv_tensor_map(const void* pages, long long rows, int hd, int page_size, CUtensorMap* out) {
+    struct Key {
+        const void* p; long long rows; int hd, ps;
+        bool operator==(const Key& o) const { return p == o.p && rows == o.rows && hd == o.hd && ps == o.ps; }
+    };
+    struct Hash {
+        size_t operator()(const Key& k) const {
+            return std::hash<const void*>()(k.p) ^ (std::hash<long long>()(k.rows) * 31) ^ (size_t)(k.hd * 131 + k.ps);
+        }
+    };
+    static std::mutex mu;
+    static std::unordered_map<Key, CUtensorMap, Hash> cache;
+    const Key key{pages, rows, hd, page_size};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return true;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        vcb_set_error("attn_mma: the driver does not offer cuTensorMapEncodeTiled");
+        return false;
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)page_size};
+    const cuuint32_t elem[2] = {1, 1};
+    CUtensorMap m;
+    const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        vcb_set_error("attn_mma: cuTensorMapEncodeTiled failed with %d (rows %lld, head_dim %d, page %d)", (int)r, rows, hd, page_size);
+        return false;
+    }
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, m);
+    *out = m;
+    return true;
+}
+
+template <int HD, int WR, int WK, bool TMA>
 int launch(const AttnArgs& a, int n_items, cudaStream_t stream) {
     constexpr int RMAX = 16 * WR;
+    constexpr int STAGES = (TMA && WK == 4) ? 3 : 2;
     const int g = a.nh / a.nkv;
     const int gq_max = g < RMAX ? g : RMAX;
     const int hchunks = (g + gq_max - 1) / gq_max;
-    const size_t stages = (size_t)RMAX * HD * 2 + 4 * (size_t)BN * HD * 2;
-    const size_t merge = (size_t)RMAX * HD * 2 + (64 * (size_t)HD + 128) * sizeof(float);
-    const size_t smem = stages > merge ? stages : merge;
-    auto kern = attn_mma_kernel<HD, WR, WK>;
+    const size_t stages = 2 * (size_t)STAGES * BN * HD * 2 + (size_t)RMAX * HD * 2 + 16 * STAGES + 16;
+    const size_t merge = (64 * (size_t)HD + 128) * sizeof(float);
+    const size_t smem = (stages > merge ? stages : merge) + 1024;   // + alignment slack
+    CUtensorMap map;
+    memset(&map, 0, sizeof(map));
+    if (TMA) {
+        const long long rows = (long long)a.num_pages * 2 * a.nkv * a.page_size;
+        if (a.page_stride != (long long)2 * a.nkv * a.page_size * HD) {
+            vcb_set_error("attn_mma: the pages of a layer must be contiguous for TMA loads");
+            return -1;
+        }
+        if (!kv_tensor_map(a.pages, rows, HD, a.page_size, &map)) return -3;
+    }
+    auto kern = attn_mma_kernel<HD, WR, WK, TMA>;
     static bool opted = false;
     if (!opted) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -344,9 +573,14 @@ int launch(const AttnArgs& a, int n_items, cudaStream_t stream) {
         }
         opted = true;
     }
-    kern<<<dim3(n_items, a.nkv * hchunks), NT, smem, stream>>>(a);
+    kern<<<dim3(n_items, a.nkv * hchunks), TMA ? NT + 32 : NT, smem, stream>>>(map, a);
     VCB_CHECK_LAUNCH("attn_mma");
     return 0;
+}
+
+template <int HD, bool TMA>
+int launch_rows(const AttnArgs& a, int n_items, int rows_max, cudaStream_t stream) {
+    return rows_max == 16 ? launch<HD, 1, 4, TMA>(a, n_items, stream) : launch<HD, 4, 1, TMA>(a, n_items, stream);
 }
 
 }  // namespace
@@ -359,7 +593,7 @@ VCB_API int vcb_attn_mma(const void* q, void* out, const void* pages, long long 
                          const int* table_row, int max_blocks, const int* q_start, const int* q_len,
                          const int* ctx_len, const int* items, int n_items, int rows_max, float* part_o,
                          float* part_ml, int nh, int nkv, int hd, int page_size, int num_pages, int window,
-                         float scale, int* status, cudaStream_t stream) {
+                         float scale, int* status, int allow_tma, cudaStream_t stream) {
     if (n_items == 0) return 0;
     VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_mma: %d query heads are not a multiple of %d KV heads", nh, nkv);
     VCB_CHECK_ARG(hd == 64 || hd == 128, "attn_mma: head_dim %d is not 64 or 128", hd);
@@ -368,6 +602,8 @@ VCB_API int vcb_attn_mma(const void* q, void* out, const void* pages, long long 
     AttnArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_stride, block_table,
                table_row, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml, nh, nkv, page_size, num_pages,
                window, scale, status};
-    if (hd == 64) return rows_max == 16 ? launch<64, 1, 4>(a, n_items, stream) : launch<64, 4, 1>(a, n_items, stream);
-    return rows_max == 16 ? launch<128, 1, 4>(a, n_items, stream) : launch<128, 4, 1>(a, n_items, stream);
+    const bool tma = allow_tma && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64) &&
+                     ((uintptr_t)pages % 16 == 0) && page_stride == (long long)2 * nkv * page_size * hd;
+    if (hd == 64) return tma ? launch_rows<64, true>(a, n_items, rows_max, stream) : launch_rows<64, false>(a, n_items, rows_max, stream);
+    return tma ? launch_rows<128, true>(a, n_items, rows_max, stream) : launch_rows<128, false>(a, n_items, rows_max, stream);
 }

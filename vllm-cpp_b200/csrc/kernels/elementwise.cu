@@ -76,6 +76,63 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const void* __rest
         store_from_f32(out, out_dtype, (size_t)i * H + h, load_as_f32(w, w_dtype, h) * xs[h] * inv);
 }
 
+// Same contract for the shapes serving uses (H a multiple of 4, 32-bit deltas, bfloat16 out): 16-byte loads, every
+// load of a row issued before any is used, the row kept in registers.  VPT = float4s per thread.
+template <int VPT>
+__global__ __launch_bounds__(1024) void add_rmsnorm_vec_kernel(float* __restrict__ resid, const float* __restrict__ delta,
+                                                               int S, size_t delta_stride, const void* __restrict__ w,
+                                                               int w_dtype, float eps, __nv_bfloat16* __restrict__ out,
+                                                               const int* __restrict__ rows, int H) {
+    __shared__ float scratch[33];
+    const int i = blockIdx.x;
+    const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+    const bool write_back = rows == nullptr && S > 0;
+    const int H4 = H >> 2;
+    float4 x[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int c = threadIdx.x + v * blockDim.x;
+        if (c < H4) x[v] = reinterpret_cast<const float4*>(resid + r * H)[c];
+    }
+    for (int s = 0; s < S; ++s) {
+        const float4* d4 = reinterpret_cast<const float4*>(delta + (size_t)s * delta_stride + r * H);
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            const int c = threadIdx.x + v * blockDim.x;
+            if (c < H4) {
+                const float4 d = d4[c];
+                x[v].x += d.x; x[v].y += d.y; x[v].z += d.z; x[v].w += d.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int c = threadIdx.x + v * blockDim.x;
+        if (c < H4) {
+            ss += x[v].x * x[v].x + x[v].y * x[v].y + x[v].z * x[v].z + x[v].w * x[v].w;
+            if (write_back) reinterpret_cast<float4*>(resid + r * H)[c] = x[v];
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int c = threadIdx.x + v * blockDim.x;
+        if (c < H4) {
+            const int h = c * 4;
+            const float w0 = load_as_f32(w, w_dtype, h), w1 = load_as_f32(w, w_dtype, h + 1);
+            const float w2 = load_as_f32(w, w_dtype, h + 2), w3 = load_as_f32(w, w_dtype, h + 3);
+            __nv_bfloat162 lo = __floats2bfloat162_rn(w0 * x[v].x * inv, w1 * x[v].y * inv);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(w2 * x[v].z * inv, w3 * x[v].w * inv);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            reinterpret_cast<uint2*>(out + (size_t)i * H)[c] = pk;
+        }
+    }
+}
+
 VCB_API int vcb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, int S, long long delta_stride,
                             const void* w, int w_dtype, float eps, void* out, int out_dtype, const int* rows,
                             int n_out, int H, cudaStream_t stream) {
@@ -88,6 +145,20 @@ VCB_API int vcb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, in
         cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         opted_in = true;
     }
+    const bool vec = H % 4 == 0 && out_dtype == VCB_BF16 && (S == 0 || delta_dtype == VCB_F32) && delta_stride % 4 == 0 &&
+                     ((uintptr_t)resid % 16 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)out % 8 == 0) && H <= 16384;
+    if (vec) {
+        const int H4 = H / 4;
+        const int threads = H4 >= 1024 ? 1024 : ((H4 + 31) / 32) * 32;
+        const int vpt = (H4 + threads - 1) / threads;
+        const float* d = (const float*)delta;
+        __nv_bfloat16* o = (__nv_bfloat16*)out;
+        if (vpt == 1) add_rmsnorm_vec_kernel<1><<<n_out, threads, 0, stream>>>(resid, d, S, (size_t)delta_stride, w, w_dtype, eps, o, rows, H);
+        else if (vpt == 2) add_rmsnorm_vec_kernel<2><<<n_out, threads, 0, stream>>>(resid, d, S, (size_t)delta_stride, w, w_dtype, eps, o, rows, H);
+        else add_rmsnorm_vec_kernel<4><<<n_out, threads, 0, stream>>>(resid, d, S, (size_t)delta_stride, w, w_dtype, eps, o, rows, H);
+        VCB_CHECK_LAUNCH("add_rmsnorm");
+        return 0;
+    }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     add_rmsnorm_kernel<<<n_out, threads, smem, stream>>>(resid, delta, delta_dtype, S, (size_t)delta_stride, w, w_dtype,
                                                          eps, out, out_dtype, rows, H);
@@ -98,23 +169,33 @@ VCB_API int vcb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, in
 // ---------------------------------------------------------------------------
 // SiLU-gate product: out[t,i] = silu(gu[t,i]) * gu[t,I+i]
 // ---------------------------------------------------------------------------
-template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+template <typename TIN, typename T>
+__global__ void swiglu_kernel(const TIN* __restrict__ gu, int S, size_t s_stride, T* __restrict__ out, int I, size_t total) {
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I, i = idx % I;
-        const float g = to_f32(gu[t * 2 * I + i]);
-        const float u = to_f32(gu[t * 2 * I + I + i]);
+        float g = 0.f, u = 0.f;
+        for (int s = 0; s < S; ++s) {   // k-slice partials of the product are added in slice order
+            g += to_f32(gu[s * s_stride + t * 2 * I + i]);
+            u += to_f32(gu[s * s_stride + t * 2 * I + I + i]);
+        }
         out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
     }
 }
 
-VCB_API int vcb_swiglu(const void* gate_up, void* out, int dtype, int T, int I, cudaStream_t stream) {
+// gate_up: [S, T, 2I] of in_dtype (S partial sums, s_stride elements apart); out: [T, I] of out_dtype
+VCB_API int vcb_swiglu(const void* gate_up, int in_dtype, int S, long long s_stride, void* out, int out_dtype, int T,
+                       int I, cudaStream_t stream) {
     if (T == 0) return 0;
-    VCB_CHECK_ARG(T > 0 && I > 0, "swiglu: bad sizes T=%d I=%d", T, I);
+    VCB_CHECK_ARG(T > 0 && I > 0 && S >= 1, "swiglu: bad sizes T=%d I=%d S=%d", T, I, S);
     const size_t total = (size_t)T * I;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    if (dtype == VCB_F32) swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, I, total);
-    else swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, total);
+    if (in_dtype == VCB_F32 && out_dtype == VCB_F32)
+        swiglu_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)gate_up, S, (size_t)s_stride, (float*)out, I, total);
+    else if (in_dtype == VCB_F32)
+        swiglu_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float*)gate_up, S, (size_t)s_stride, (__nv_bfloat16*)out, I, total);
+    else if (out_dtype == VCB_BF16)
+        swiglu_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, S, (size_t)s_stride, (__nv_bfloat16*)out, I, total);
+    else { vcb_set_error("swiglu: bfloat16 input with 32-bit output is not a combination the engine uses"); return -1; }
     VCB_CHECK_LAUNCH("swiglu");
     return 0;
 }
@@ -126,8 +207,8 @@ VCB_API int vcb_swiglu(const void* gate_up, void* out, int dtype, int T, int I, 
 //   cos_sin: [max_pos, hd]  (hd/2 cosines then hd/2 sines, 32-bit)
 //   pages:   [num_pages, 2, nkv, page_size, hd] of one layer
 // ---------------------------------------------------------------------------
-template <typename T>
-__global__ void qknorm_rope_kvwrite_kernel(const T* __restrict__ qkv, const void* __restrict__ qw,
+template <typename TIN, typename T>
+__global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, size_t s_stride, const void* __restrict__ qw,
                                            const void* __restrict__ kw, int w_dtype, int use_norm, float eps,
                                            const float* __restrict__ cos_sin, int max_pos,
                                            const int* __restrict__ positions, const int* __restrict__ slot_map,
@@ -139,7 +220,7 @@ __global__ void qknorm_rope_kvwrite_kernel(const T* __restrict__ qkv, const void
     const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (gw >= (long long)n_tokens * heads_total) return;
     const int t = (int)(gw / heads_total), h = (int)(gw % heads_total);
-    const T* src = qkv + (size_t)t * heads_total * hd + (size_t)h * hd;
+    const TIN* src = qkv + (size_t)t * heads_total * hd + (size_t)h * hd;
     const int half = hd >> 1;
 
     long long slot = -1;
@@ -155,7 +236,11 @@ __global__ void qknorm_rope_kvwrite_kernel(const T* __restrict__ qkv, const void
     if (h >= nh + nkv) {  // V head: stored as it is
         const int kvh = h - nh - nkv;
         T* dst = pages + (slot / page_size) * page_stride + ((size_t)(nkv + kvh) * page_size + slot % page_size) * hd;
-        for (int i = lane; i < hd; i += 32) dst[i] = src[i];
+        for (int i = lane; i < hd; i += 32) {
+            float v = 0.f;
+            for (int s = 0; s < S; ++s) v += to_f32(src[s * s_stride + i]);
+            dst[i] = from_f32<T>(v);
+        }
         return;
     }
 
@@ -171,8 +256,11 @@ __global__ void qknorm_rope_kvwrite_kernel(const T* __restrict__ qkv, const void
     for (int j = 0; j < MAXP; ++j) {
         const int p = lane + 32 * j;
         if (p < half) {
-            x1[j] = to_f32(src[p]);
-            x2[j] = to_f32(src[p + half]);
+            x1[j] = x2[j] = 0.f;
+            for (int s = 0; s < S; ++s) {   // k-slice partials of the projection are added in slice order
+                x1[j] += to_f32(src[s * s_stride + p]);
+                x2[j] += to_f32(src[s * s_stride + p + half]);
+            }
             ss += x1[j] * x1[j] + x2[j] * x2[j];
         }
     }
@@ -202,29 +290,30 @@ __global__ void qknorm_rope_kvwrite_kernel(const T* __restrict__ qkv, const void
     }
 }
 
-VCB_API int vcb_qknorm_rope_kvwrite(const void* qkv, int dtype, const void* qw, const void* kw, int w_dtype,
-                                    int use_norm, float eps, const float* cos_sin, int max_pos, const int* positions,
-                                    const int* slot_map, void* q_out, void* pages, long long page_stride,
-                                    int page_size, int num_pages, int nh, int nkv, int hd, int T, int has_kv,
-                                    int* status, cudaStream_t stream) {
+// qkv: [S, T, width] of in_dtype (S partial sums, s_stride elements apart); q_out and pages of out_dtype
+VCB_API int vcb_qknorm_rope_kvwrite(const void* qkv, int in_dtype, int S, long long s_stride, int out_dtype,
+                                    const void* qw, const void* kw, int w_dtype, int use_norm, float eps,
+                                    const float* cos_sin, int max_pos, const int* positions, const int* slot_map,
+                                    void* q_out, void* pages, long long page_stride, int page_size, int num_pages,
+                                    int nh, int nkv, int hd, int T, int has_kv, int* status, cudaStream_t stream) {
     if (T == 0) return 0;
     VCB_CHECK_ARG(hd > 0 && hd % 2 == 0 && hd <= VCB_MAX_HEAD_DIM,
                   "qknorm_rope_kvwrite: head_dim %d must be even and <= %d", hd, VCB_MAX_HEAD_DIM);
-    VCB_CHECK_ARG(nh > 0 && nkv > 0 && page_size > 0, "qknorm_rope_kvwrite: bad sizes nh=%d nkv=%d page=%d", nh, nkv,
-                  page_size);
+    VCB_CHECK_ARG(nh > 0 && nkv > 0 && page_size > 0 && S >= 1, "qknorm_rope_kvwrite: bad sizes nh=%d nkv=%d page=%d S=%d",
+                  nh, nkv, page_size, S);
     const long long warps = (long long)T * (nh + (has_kv ? 2 * nkv : 0));
     const int wpb = 4;
     const long long blocks = (warps + wpb - 1) / wpb;
     VCB_CHECK_ARG(blocks < (1ll << 31), "qknorm_rope_kvwrite: too many blocks");
-    if (dtype == VCB_F32)
-        qknorm_rope_kvwrite_kernel<float><<<(unsigned)blocks, wpb * 32, 0, stream>>>(
-            (const float*)qkv, qw, kw, w_dtype, use_norm, eps, cos_sin, max_pos, positions, slot_map, (float*)q_out,
-            (float*)pages, page_stride, page_size, num_pages, nh, nkv, hd, T, has_kv, status);
-    else
-        qknorm_rope_kvwrite_kernel<__nv_bfloat16><<<(unsigned)blocks, wpb * 32, 0, stream>>>(
-            (const __nv_bfloat16*)qkv, qw, kw, w_dtype, use_norm, eps, cos_sin, max_pos, positions, slot_map,
-            (__nv_bfloat16*)q_out, (__nv_bfloat16*)pages, page_stride, page_size, num_pages, nh, nkv, hd, T, has_kv,
-            status);
+#define VCB_QK_LAUNCH(TIN, TOUT)                                                                                      \
+    qknorm_rope_kvwrite_kernel<TIN, TOUT><<<(unsigned)blocks, wpb * 32, 0, stream>>>(                                  \
+        (const TIN*)qkv, S, (size_t)s_stride, qw, kw, w_dtype, use_norm, eps, cos_sin, max_pos, positions, slot_map,   \
+        (TOUT*)q_out, (TOUT*)pages, page_stride, page_size, num_pages, nh, nkv, hd, T, has_kv, status)
+    if (in_dtype == VCB_F32 && out_dtype == VCB_F32) VCB_QK_LAUNCH(float, float);
+    else if (in_dtype == VCB_F32) VCB_QK_LAUNCH(float, __nv_bfloat16);
+    else if (out_dtype == VCB_BF16) VCB_QK_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else { vcb_set_error("qknorm_rope_kvwrite: bfloat16 input with 32-bit output is not a combination the engine uses"); return -1; }
+#undef VCB_QK_LAUNCH
     VCB_CHECK_LAUNCH("qknorm_rope_kvwrite");
     return 0;
 }

@@ -1,0 +1,453 @@
+// bfloat16 projections on the fifth-generation tensor cores:
+//     out[z][t][m] = sum over the z-th slice of k of  W[m][k] * X[t][k]
+// i.e. y = x . W^T with W stored [out_features, in_features] as in the checkpoint
+// (src/model.cpp:932-944 of the reference; its CUDA sketch calls cublasGemmEx for
+// this, cuda/tp_model.cu:259-269).
+//
+// Orientation.  The weight matrix is the M operand of the MMA (tiles of 128 output
+// features = 128 TMEM lanes), the tokens are the N operand (16 to 256 per tile).
+// One orientation serves a 2,048-token prompt portion and a single decoded token:
+// with few tokens the kernel is a pipeline that streams weights from HBM at full
+// rate into MMAs of small N; with many it is a 128x256 tile kernel.  The
+// accumulator D[feature][token] lives in TMEM; each epilogue thread owns one
+// feature (lane) and walks the tokens, so a warp's store of one token covers 32
+// consecutive features of the row-major output: coalesced.
+//
+// Blocks are persistent (one per SM) and walk work units (feature tiles x token tiles x k-slices) round
+// robin.  Roles (192 threads): warp 0 issues TMA loads (cp.async.bulk.tensor, 128-byte
+// swizzle, zero fill beyond the matrix edges) into a ring of stages guarded by
+// full/empty mbarriers; warp 1 allocates TMEM and issues tcgen05.mma
+// (kind::f16, bf16 x bf16 -> f32) from shared-memory descriptors, releasing each
+// stage with tcgen05.commit; warps 2-5 read the accumulator with tcgen05.ld once
+// the last commit lands and store it.  Split-K: blockIdx.z takes a slice of K and
+// writes an f32 partial; the consumer (the next norm or element-wise kernel) adds
+// the partials in slice order, so results do not depend on timing.
+//
+// Every mbarrier wait is bounded by the clock; a wait that runs out sets a bit in
+// the status word, raises an abort flag that the other roles see, and the block
+// still frees its TMEM and returns.  No cluster multicast anywhere.
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int BM = 128;   // output features per tile (TMEM lanes)
+constexpr int BK = 64;    // k per stage: 64 bf16 = 128 bytes = one swizzle span
+constexpr int UMMA_K = 16;
+constexpr int NTHREADS = 192;
+constexpr long long WAIT_CLOCKS = 2000000000ll;   // about a second
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the barrier did not flip within WAIT_CLOCKS or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_CLOCKS) {
+            *abort_flag = 1;
+            atomicOr(status, VCB_STATUS_WAIT_TIMEOUT);
+            return false;
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled:
+// start address / 16 in bits 0-13, leading byte offset (unused for this layout, 1) in 16-29, stride
+// between 8-row groups (1024 bytes) / 16 in 32-45, descriptor version 1 in 46-47, layout 2 = SWIZZLE_128B in 61-63.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor of kind::f16: f32 accumulate (bits 4-5 = 1), A and B bfloat16 (bits 7-9, 10-12 = 1),
+// both K-major (bits 15, 16 = 0), N / 8 in bits 17-22, M / 16 in bits 24-28.
+__host__ __device__ constexpr uint32_t instr_desc(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+struct GemmArgs {
+    void* out;
+    int out_dtype;            // VCB_F32 or VCB_BF16
+    int M, N, K;              // features, tokens, inner size
+    long long ldc;            // elements between output rows (tokens)
+    long long split_stride;   // elements between the partials of consecutive k-slices
+    int kb_per_split;         // 64-wide k-blocks per slice
+    int splits;               // k-slices
+    int* status;
+};
+
+// MT = 128-feature tiles per work unit that share one token tile (2 halves the bytes that cross L2 per flop);
+// ACC = accumulator buffers in TMEM (2: the epilogue of one unit overlaps the MMAs of the next).
+template <int BN, int STAGES, int MT, int ACC>
+struct Smem {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = MT * A_BYTES + B_BYTES;
+    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int NUM_BARS = 2 * STAGES + 2 * ACC;
+    static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;   // + alignment slack
+};
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Persistent: each block walks the work units blockIdx.x, blockIdx.x + gridDim.x, ...; a unit is
+// (feature tile group, token tile, k-slice).  The stage ring and the accumulator ring run on across units, so
+// the loads of the next unit are in flight while the current one is multiplied and the one before is stored.
+template <int BN, int STAGES, int MT, int ACC>
+__global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                    const __grid_constant__ CUtensorMap map_x,
+                                                                    GemmArgs g) {
+    using L = Smem<BN, STAGES, MT, ACC>;
+    constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;            // columns of one 128-feature accumulator
+    constexpr uint32_t TMEM_COLS = ACC * MT * ACC_COLS;         // a power of two in [32, 512]
+    static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns");
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + L::BAR_OFFSET;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto acc_full_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+    auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * STAGES + ACC + a); };
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(gen + L::BAR_OFFSET + L::NUM_BARS * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::BAR_OFFSET + L::NUM_BARS * 8 + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_kb = (g.K + BK - 1) / BK;
+    const int m_tiles = (g.M + BM * MT - 1) / (BM * MT);
+    const int n_tiles = (g.N + BN - 1) / BN;
+    const int units = m_tiles * n_tiles * g.splits;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < ACC; ++a) {
+            mbar_init(acc_full_bar(a), 1);
+            mbar_init(acc_empty_bar(a), 4);   // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32((const void*)tmem_holder)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    // unit -> (first feature, first token, first k-block, k-blocks)
+    auto unit_at = [&](int u, int& m0, int& n0, int& kb0, int& nkb, int& z) {
+        z = u / (m_tiles * n_tiles);
+        const int rem = u % (m_tiles * n_tiles);
+        n0 = (rem / m_tiles) * BN;
+        m0 = (rem % m_tiles) * (BM * MT);
+        kb0 = z * g.kb_per_split;
+        nkb = min(total_kb, kb0 + g.kb_per_split) - kb0;
+    };
+
+    if (warp == 0) {
+        // ---- TMA producer ----
+        if (lane == 0) {
+            int it = 0, armed = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                int m0, n0, kb0, nkb, z;
+                unit_at(u, m0, n0, kb0, nkb, z);
+                for (int i = 0; i < nkb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, g.status)) { ok = false; break; }
+                    mbar_expect_tx(full_bar(s), L::STAGE_BYTES);
+                    const uint32_t a_dst = base + s * L::STAGE_BYTES;
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+                        tma_load_2d(a_dst + mt * L::A_BYTES, &map_w, full_bar(s), (kb0 + i) * BK, m0 + mt * BM);
+                    tma_load_2d(a_dst + MT * L::A_BYTES, &map_x, full_bar(s), (kb0 + i) * BK, n0);
+                    armed = it + 1;
+                }
+            }
+            if (*abort_flag) {
+                // let the copies already in flight land before the block goes away
+                for (int i = max(0, armed - STAGES); i < armed; ++i) {
+                    const long long t0 = clock64();
+                    while (!mbar_try(full_bar(i % STAGES), (i / STAGES) & 1) && clock64() - t0 < WAIT_CLOCKS) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ----
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BN);
+            int it = 0, j = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++j) {
+                int m0, n0, kb0, nkb, z;
+                unit_at(u, m0, n0, kb0, nkb, z);
+                const int a = j % ACC;
+                ok = mbar_wait(acc_empty_bar(a), ((j / ACC) & 1) ^ 1u, abort_flag, g.status);   // drained by the epilogue
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + a * (MT * ACC_COLS);
+                for (int i = 0; i < nkb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag, g.status);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = base + s * L::STAGE_BYTES;
+                    const uint64_t db = smem_desc(a_addr + MT * L::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // 16 k = 32 bytes further along the 128-byte rows: +2 in the descriptor's 16-byte units
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt)
+                            tc_mma(tmem_d + mt * ACC_COLS, smem_desc(a_addr + mt * L::A_BYTES) + 2 * k, db + 2 * k, idesc,
+                                   (i > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit(empty_bar(s));   // arrives when these MMAs have read the stage
+                }
+                if (ok) tc_commit(acc_full_bar(a));
+            }
+        }
+    } else {
+        // ---- epilogue: warps 2..5 own TMEM lane quarters 2, 3, 0, 1 ----
+        const int q = warp & 3;
+        int j = 0;
+        for (int u = blockIdx.x; u < units; u += gridDim.x, ++j) {
+            int m0, n0, kb0, nkb, z;
+            unit_at(u, m0, n0, kb0, nkb, z);
+            const int a = j % ACC;
+            if (!mbar_wait(acc_full_bar(a), (j / ACC) & 1, abort_flag, g.status)) break;
+            tc_fence_after();
+            const uint32_t tmem_d = tmem_base + a * (MT * ACC_COLS);
+            const size_t zoff = (size_t)z * g.split_stride;
+#pragma unroll 1
+            for (int cc = 0; cc < MT * BN; cc += 16) {
+                const int mt = cc / BN, c0 = cc % BN;
+                if (n0 + c0 >= g.N) continue;   // uniform over the warp
+                const int m = m0 + mt * BM + q * 32 + lane;
+                uint32_t v[16];
+                tc_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * ACC_COLS + c0), v);
+                tc_wait_ld();
+                if (m < g.M) {
+                    if (g.out_dtype == VCB_F32) {
+                        float* o = reinterpret_cast<float*>(g.out) + zoff;
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj)
+                            if (n0 + c0 + jj < g.N) o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __uint_as_float(v[jj]);
+                    } else {
+                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + zoff;
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj)
+                            if (n0 + c0 + jj < g.N) o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __float2bfloat16_rn(__uint_as_float(v[jj]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(a));   // this warp has read its quarter of the accumulator
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side: tensor maps (cached) and launch
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    long long rows, cols, ld;
+    int box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = std::hash<const void*>()(k.ptr);
+        for (long long v : {k.rows, k.cols, k.ld, (long long)k.box_rows}) h = h * 1000003u ^ std::hash<long long>()(v);
+        return h;
+    }
+};
+
+// A [rows, cols] bfloat16 matrix with `ld` elements between rows; boxes of box_rows x 64, 128-byte swizzle.
+bool tensor_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    const MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return true;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        vcb_set_error("gemm_bf16_tn: the driver does not offer cuTensorMapEncodeTiled");
+        return false;
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUtensorMap m;
+    const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        vcb_set_error("gemm_bf16_tn: cuTensorMapEncodeTiled failed with %d (rows %lld, cols %lld, ld %lld, box %d)",
+                      (int)r, rows, cols, ld, box_rows);
+        return false;
+    }
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, m);
+    *out = m;
+    return true;
+}
+
+int num_sms() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int BN, int STAGES, int MT, int ACC>
+int launch(const void* W, const void* X, const GemmArgs& g, long long ldw, long long ldx, int splits, cudaStream_t stream) {
+    using L = Smem<BN, STAGES, MT, ACC>;
+    CUtensorMap mw, mx;
+    if (!tensor_map(W, g.M, g.K, ldw, BM, &mw) || !tensor_map(X, g.N, g.K, ldx, BN, &mx)) return -3;
+    auto kern = gemm_bf16_tn_kernel<BN, STAGES, MT, ACC>;
+    static bool opted = false;
+    if (!opted) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) {
+            vcb_set_error("gemm_bf16_tn: %d bytes of shared memory refused: %s", L::TOTAL, cudaGetErrorString(e));
+            return -2;
+        }
+        opted = true;
+    }
+    const long long units = (long long)((g.M + BM * MT - 1) / (BM * MT)) * ((g.N + BN - 1) / BN) * splits;
+    const int grid = (int)(units < num_sms() ? units : num_sms());
+    kern<<<grid, NTHREADS, L::TOTAL, stream>>>(mw, mx, g);
+    VCB_CHECK_LAUNCH("gemm_bf16_tn");
+    return 0;
+}
+
+}  // namespace
+
+// out[z][t][m] (z < splits) = sum over k-slice z of W[m][k] X[t][k];  W [M,K], X [N,K] bfloat16, K contiguous.
+// out_dtype bfloat16 needs splits == 1.  The number of slices actually used is vcb_gemm_effective_splits(K, splits).
+VCB_API int vcb_gemm_effective_splits(int K, int splits) {
+    const int total_kb = (K + BK - 1) / BK;
+    if (splits < 1) splits = 1;
+    if (splits > total_kb) splits = total_kb;
+    const int kb_per_split = (total_kb + splits - 1) / splits;
+    return (total_kb + kb_per_split - 1) / kb_per_split;
+}
+
+VCB_API int vcb_gemm_bf16_tn(const void* W, const void* X, void* out, int out_dtype, int M, int N, int K,
+                             long long ldw, long long ldx, long long ldc, int splits, long long split_stride,
+                             int* status, cudaStream_t stream) {
+    VCB_CHECK_ARG(M > 0 && N > 0 && K > 0, "gemm_bf16_tn: bad sizes M=%d N=%d K=%d", M, N, K);
+    VCB_CHECK_ARG(K % 8 == 0 && ldw % 8 == 0 && ldx % 8 == 0,
+                  "gemm_bf16_tn: inner size %d and row strides %lld, %lld must be multiples of 8 (16-byte rows for TMA)", K, ldw, ldx);
+    VCB_CHECK_ARG(((uintptr_t)W % 16 == 0) && ((uintptr_t)X % 16 == 0), "gemm_bf16_tn: operands must be 16-byte aligned");
+    VCB_CHECK_ARG(splits >= 1 && (splits == 1 || out_dtype == VCB_F32), "gemm_bf16_tn: k-slices need 32-bit partial outputs");
+    const int total_kb = (K + BK - 1) / BK;
+    if (splits > total_kb) splits = total_kb;
+    const int kb_per_split = (total_kb + splits - 1) / splits;
+    splits = (total_kb + kb_per_split - 1) / kb_per_split;
+    GemmArgs g{out, out_dtype, M, N, K, ldc, split_stride, kb_per_split, splits, status};
+    int rc;
+    if (N <= 16) rc = launch<16, 8, 1, 2>(W, X, g, ldw, ldx, splits, stream);
+    else if (N <= 32) rc = launch<32, 8, 1, 2>(W, X, g, ldw, ldx, splits, stream);
+    else if (N <= 64) rc = launch<64, 8, 1, 2>(W, X, g, ldw, ldx, splits, stream);
+    else if (N <= 128) rc = launch<128, 6, 1, 2>(W, X, g, ldw, ldx, splits, stream);
+    else if (M <= 128) rc = launch<256, 4, 1, 2>(W, X, g, ldw, ldx, splits, stream);
+    else rc = launch<256, 3, 2, 1>(W, X, g, ldw, ldx, splits, stream);   // 256 features x 256 tokens a unit
+    return rc;
+}

@@ -158,6 +158,57 @@ __global__ __launch_bounds__(1024) void sample_kernel(const float* __restrict__ 
     if (threadIdx.x == 0) out[row] = zi;
 }
 
+// Two-stage variant for rows that need no nucleus cut (top_p >= 1 or greedy): the vocabulary is dealt to
+// `nb` blocks per row, each leaves its best (value, index), and the last stage picks among them with the same
+// lowest-index rule, so the token equals the single-block kernel's.
+__global__ __launch_bounds__(512) void sample_part_kernel(const float* __restrict__ logits, long long row_stride, int V,
+                                                          const RowParams* __restrict__ params,
+                                                          const int* __restrict__ counts_table, float* __restrict__ part_v,
+                                                          int* __restrict__ part_i) {
+    __shared__ float sv[33];
+    __shared__ int si[33];
+    const int row = blockIdx.x, nb = gridDim.y, b = blockIdx.y;
+    const RowParams p = params[row];
+    const float* lg = logits + (size_t)row * row_stride;
+    const int* counts = (counts_table && p.slot >= 0 && p.repeat_penalty != 1.0f) ? counts_table + (size_t)p.slot * V : nullptr;
+    const bool greedy = !(p.temperature > 0.f);
+    const float inv_t = greedy ? 1.f : 1.0f / p.temperature;
+    const unsigned long long key = mix64(((unsigned long long)p.seed_lo << 32) | (unsigned long long)p.step);
+    const int chunk = (V + nb - 1) / nb;
+    const int lo = b * chunk, hi = min(V, lo + chunk);
+    float best = -CUDART_INF_F;
+    int best_i = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        float s = score_at(lg, counts, p.repeat_penalty, inv_t, i);
+        if (!greedy) s -= logf(-logf(uniform01(key, (unsigned int)i)));
+        if (s > best || (s == best && i < best_i)) { best = s; best_i = i; }
+    }
+    block_argmax(best, best_i, sv, si);
+    if (threadIdx.x == 0) {
+        part_v[row * nb + b] = best;
+        part_i[row * nb + b] = best_i;
+    }
+}
+
+__global__ void sample_pick_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int nb,
+                                   int* __restrict__ out) {
+    const int row = blockIdx.x;
+    float best = -CUDART_INF_F;
+    int best_i = 0x7fffffff;
+    for (int b = threadIdx.x; b < nb; b += 32) {
+        const float v = part_v[row * nb + b];
+        const int i = part_i[row * nb + b];
+        if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if (threadIdx.x == 0) out[row] = best_i;
+}
+
 __global__ void count_tokens_kernel(const int* __restrict__ ids, const int* __restrict__ slots, int* __restrict__ counts,
                                     int n, int V) {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
@@ -184,5 +235,19 @@ VCB_API int vcb_count_tokens(const int* ids, const int* slots, int* counts, int 
     if (n == 0) return 0;
     count_tokens_kernel<<<(n + 255) / 256, 256, 0, stream>>>(ids, slots, counts, n, V);
     VCB_CHECK_LAUNCH("count_tokens");
+    return 0;
+}
+
+// For batches in which no row cuts a nucleus: `nb` blocks per row; part_v / part_i hold n_rows * nb entries.
+VCB_API int vcb_sample_split(const float* logits, long long row_stride, int n_rows, int V, const void* params,
+                             const int* counts_table, float* part_v, int* part_i, int nb, int* out,
+                             cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    VCB_CHECK_ARG(n_rows > 0 && V > 0 && row_stride >= V && nb >= 1 && nb <= 1024, "sample_split: bad sizes");
+    sample_part_kernel<<<dim3(n_rows, nb), 512, 0, stream>>>(logits, row_stride, V, (const RowParams*)params,
+                                                             counts_table, part_v, part_i);
+    VCB_CHECK_LAUNCH("sample_part");
+    sample_pick_kernel<<<n_rows, 32, 0, stream>>>(part_v, part_i, nb, out);
+    VCB_CHECK_LAUNCH("sample_pick");
     return 0;
 }

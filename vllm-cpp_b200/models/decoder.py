@@ -85,4 +85,4 @@ class DecoderModel:
         if ctx.n_rows == 0:
             return None
         y = self.final_norm.forward(resid, pending, rows=ctx.logit_rows)
-        return self.lm_head.forward(y)
+        return self.lm_head.forward(y, ctx.status)

@@ -54,15 +54,18 @@ def _declare(L):
     sigs = {
         "vcb_embed_gather": [P, I, P, P, I, I, I, P, P],
         "vcb_add_rmsnorm": [P, P, I, I, LL, P, I, F, P, I, P, I, I, P],
-        "vcb_swiglu": [P, P, I, I, I, P],
-        "vcb_qknorm_rope_kvwrite": [P, I, P, P, I, I, F, P, I, P, P, P, P, LL, I, I, I, I, I, I, I, P, P],
+        "vcb_swiglu": [P, I, I, LL, P, I, I, I, P],
+        "vcb_qknorm_rope_kvwrite": [P, I, I, LL, I, P, P, I, I, F, P, I, P, P, P, P, LL, I, I, I, I, I, I, I, P, P],
+        "vcb_gemm_bf16_tn": [P, P, P, I, I, I, I, LL, LL, LL, I, LL, P, P],
+        "vcb_gemm_effective_splits": [I, I],
         "vcb_sgemm_tn": [P, P, P, I, I, I, LL, LL, LL, P],
         "vcb_attn_paged": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, P],
         "vcb_scatter_i32": [P, P, P, P, I, LL, P],
-        "vcb_attn_mma": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, P],
+        "vcb_attn_mma": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, I, P],
         "vcb_attn_mma_supported": [I, I],
         "vcb_attn_merge": [P, P, P, P, I, I, I, I, I, P],
         "vcb_sample": [P, LL, I, I, P, P, P, P],
+        "vcb_sample_split": [P, LL, I, I, P, P, P, P, I, P, P],
         "vcb_count_tokens": [P, P, P, I, I, P],
     }
     for name, args in sigs.items():
@@ -141,21 +144,31 @@ def add_rmsnorm(resid, delta, weight, eps, out, rows=None):
           _p(rows), n, H, _stream())
 
 
+def _partials(t: torch.Tensor, name: str):
+    """[T, W] or [S, T, W] (S partial sums to be added) -> (S, stride between partials)."""
+    _need(t, name)
+    if t.dim() == 2:
+        return 1, 0
+    return t.shape[0], t.stride(0)
+
+
 def swiglu(gate_up, out):
-    _need(gate_up, "gate_up"); _need(out, "out", gate_up.dtype)
-    T, I2 = gate_up.shape
+    """gate_up [T, 2I] or [S, T, 2I] (32-bit partial sums); out [T, I]."""
+    S, stride = _partials(gate_up, "gate_up"); _need(out, "out")
+    T, I2 = gate_up.shape[-2:]
     assert out.shape == (T, I2 // 2)
-    _call("vcb_swiglu", _p(gate_up), _p(out), _dt(out), T, I2 // 2, _stream())
+    _call("vcb_swiglu", _p(gate_up), _dt(gate_up), S, stride, _p(out), _dt(out), T, I2 // 2, _stream())
 
 
 def qknorm_rope_kvwrite(qkv, q_weight, k_weight, eps, cos_sin, positions, slot_map, q_out, pages, nh, nkv, hd,
                         status, has_kv=True, use_norm=True):
-    """pages: one layer's [num_pages, 2, nkv, page_size, hd]; slot_map int32 [T] = page * page_size + offset or -1."""
-    _need(qkv, "qkv"); _need(cos_sin, "cos_sin", torch.float32); _need(positions, "positions", torch.int32)
-    _need(q_out, "q_out", qkv.dtype)
-    T = qkv.shape[0]
+    """qkv [T, W] or [S, T, W] (32-bit partial sums); pages: one layer's [num_pages, 2, nkv, page_size, hd];
+    slot_map int32 [T] = page * page_size + offset or -1."""
+    S, stride = _partials(qkv, "qkv")
+    _need(cos_sin, "cos_sin", torch.float32); _need(positions, "positions", torch.int32); _need(q_out, "q_out")
+    T = qkv.shape[-2]
     width = (nh + (2 * nkv if has_kv else 0)) * hd
-    assert qkv.shape[1] == width, (qkv.shape, width)
+    assert qkv.shape[-1] == width, (qkv.shape, width)
     assert cos_sin.shape[1] == hd
     wdt = F32
     if use_norm:
@@ -164,13 +177,35 @@ def qknorm_rope_kvwrite(qkv, q_weight, k_weight, eps, cos_sin, positions, slot_m
             _need(k_weight, "k_norm weight", q_weight.dtype)
     page_stride = page_size = num_pages = 0
     if has_kv:
-        _need(pages, "pages", qkv.dtype); _need(slot_map, "slot_map", torch.int32)
+        _need(pages, "pages", q_out.dtype); _need(slot_map, "slot_map", torch.int32)
         num_pages, two, nkv_p, page_size, hd_p = pages.shape
         assert two == 2 and nkv_p == nkv and hd_p == hd
         page_stride = pages.stride(0)
-    _call("vcb_qknorm_rope_kvwrite", _p(qkv), _dt(qkv), _p(q_weight), _p(k_weight), wdt, int(use_norm), float(eps),
-          _p(cos_sin), cos_sin.shape[0], _p(positions), _p(slot_map), _p(q_out), _p(pages), page_stride,
-          max(page_size, 1), num_pages, nh, nkv, hd, T, int(has_kv), _p(status), _stream())
+    _call("vcb_qknorm_rope_kvwrite", _p(qkv), _dt(qkv), S, stride, _dt(q_out), _p(q_weight), _p(k_weight), wdt,
+          int(use_norm), float(eps), _p(cos_sin), cos_sin.shape[0], _p(positions), _p(slot_map), _p(q_out), _p(pages),
+          page_stride, max(page_size, 1), num_pages, nh, nkv, hd, T, int(has_kv), _p(status), _stream())
+
+
+def gemm_effective_splits(K: int, splits: int) -> int:
+    return int(lib().vcb_gemm_effective_splits(K, splits))
+
+
+def gemm_bf16_tn(w, x, out, splits, status):
+    """out[z, t, m] = sum over k-slice z of w[m, k] x[t, k]   (tcgen05 + TMA; w [M,K], x [T,K] bfloat16).
+    out: [T, M] (bfloat16 or float32, one slice) or [S, T, M] float32 with S = gemm_effective_splits(K, splits)."""
+    _need(w, "w", torch.bfloat16, contiguous=False); _need(x, "x", torch.bfloat16, contiguous=False); _need(out, "out")
+    M, K = w.shape
+    T = x.shape[0]
+    assert x.shape[1] == K and w.stride(1) == 1 and x.stride(1) == 1
+    S = gemm_effective_splits(K, splits)
+    if out.dim() == 2:
+        assert S == 1 and out.shape == (T, M)
+        ldc, sstride = out.stride(0), 0
+    else:
+        assert out.shape == (S, T, M) and out.dtype == torch.float32
+        ldc, sstride = out.stride(1), out.stride(0)
+    _call("vcb_gemm_bf16_tn", _p(w), _p(x), _p(out), _dt(out), M, T, K, w.stride(0), x.stride(0), ldc, S, sstride,
+          _p(status), _stream())
 
 
 def sgemm_tn(a, b, out):
@@ -204,8 +239,9 @@ def attn_merge(part_o, part_ml, dec_rows, out, n_dec, nh, hd, nslices):
     _call("vcb_attn_merge", _p(part_o), _p(part_ml), _p(dec_rows), _p(out), _dt(out), n_dec, nh, hd, nslices, _stream())
 
 
-def sample(logits, params, counts, out):
-    """logits [R,V] f32; params [R,8] int32 records (see sampling.cu); counts [slots,V] int32 or None."""
+def sample(logits, params, counts, out, no_nucleus=False):
+    """logits [R,V] f32; params [R,8] int32 records (see sampling.cu); counts [slots,V] int32 or None.
+    ``no_nucleus``: no row has top_p < 1, so the vocabulary can be dealt to several blocks per row."""
     _need(logits, "logits", torch.float32, contiguous=False); _need(params, "params", torch.int32)
     _need(out, "out", torch.int32)
     R, V = logits.shape
@@ -213,6 +249,15 @@ def sample(logits, params, counts, out):
     if counts is not None:
         _need(counts, "counts", torch.int32)
         assert counts.shape[1] == V
+    nb = max(1, min(64, 2 * 148 // max(R, 1), V // 2048))
+    if no_nucleus and nb > 1:
+        global launch_count
+        part_v = torch.empty(R * nb, dtype=torch.float32, device=logits.device)
+        part_i = torch.empty(R * nb, dtype=torch.int32, device=logits.device)
+        _call("vcb_sample_split", _p(logits), logits.stride(0), R, V, _p(params), _p(counts), _p(part_v), _p(part_i),
+              nb, _p(out), _stream())
+        launch_count += 1   # two kernels
+        return
     _call("vcb_sample", _p(logits), logits.stride(0), R, V, _p(params), _p(counts), _p(out), _stream())
 
 
@@ -234,7 +279,7 @@ def attn_mma_supported(dtype: torch.dtype, hd: int) -> bool:
 
 
 def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, rows_max, part_o, part_ml,
-             nh, nkv, hd, window, status, table_row=None):
+             nh, nkv, hd, window, status, table_row=None, allow_tma=True):
     """Tensor-core variant of :func:`attn_paged` (bfloat16, head_dim 64 or 128; rows_max 16 or 64)."""
     _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(pages, "pages", torch.bfloat16)
     for name, t in (("block_table", block_table), ("q_start", q_start), ("q_len", q_len), ("ctx_len", ctx_len),
@@ -244,4 +289,5 @@ def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items
     assert two == 2 and nkv_p == nkv and hd_p == hd
     _call("vcb_attn_mma", _p(q), _p(out), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
           block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, rows_max, _p(part_o),
-          _p(part_ml), nh, nkv, hd, page_size, num_pages, int(window or 0), 1.0 / math.sqrt(hd), _p(status), _stream())
+          _p(part_ml), nh, nkv, hd, page_size, num_pages, int(window or 0), 1.0 / math.sqrt(hd), _p(status), int(allow_tma),
+          _stream())

@@ -28,7 +28,7 @@ SPAN_ROWS = 32      # rows of its prompt-portion variant
 MMA_DECODE_ROWS = 16   # the same for the tensor-core kernel
 MMA_SPAN_ROWS = 64
 MAX_SLICES = 64
-TARGET_BLOCKS = 6 * 148
+TARGET_BLOCKS = 2 * 148   # blocks of the decode kernel that are resident at once (two per SM)
 
 
 class AttentionPlan:
@@ -49,8 +49,9 @@ class AttentionPlan:
             if getattr(ctx, "static", False):
                 by_pages = MAX_SLICES              # a captured step serves any context length
             else:
-                by_pages = max(1, max(ctx.host_ctx_len[i] for i in dec) // 256)   # at least 256 keys a slice
-            self.nslices = int(max(1, min(MAX_SLICES, by_pages, -(-TARGET_BLOCKS // blocks))))
+                by_pages = max(1, max(ctx.host_ctx_len[i] for i in dec) // 128)   # at least 128 keys a slice
+            # as many slices as keep every block resident in one wave
+            self.nslices = int(max(1, min(MAX_SLICES, by_pages, TARGET_BLOCKS // blocks)))
             items = np.zeros((len(dec) * self.nslices, ops.ITEM_INTS), dtype=np.int32)
             k = 0
             for n, e in enumerate(dec):
@@ -127,7 +128,7 @@ class GQAAttention(Mixer):
         T = x.shape[0]
         nh, nkv, hd = self.nh, self.nkv, self.hd
         group = ctx.groups[cache.group]
-        qkv = matmul_tn(x, self.w_qkv)
+        qkv = matmul_tn(x, self.w_qkv, ctx.status, allow_partials=True)
         q = torch.empty((T, nh * hd), dtype=x.dtype, device=x.device)
         ops.qknorm_rope_kvwrite(qkv, self.q_norm_w, self.k_norm_w, self.eps, self.rope.table, ctx.positions,
                                 group.slot_map, q, cache.pages, nh, nkv, hd, ctx.status,
@@ -151,4 +152,4 @@ class GQAAttention(Mixer):
         if plan.n_span_items:
             kernel(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
                    plan.span_items, plan.n_span_items, span_rows, None, None, **common)
-        return matmul_tn(out, self.w_o, out_dtype=torch.float32)
+        return matmul_tn(out, self.w_o, ctx.status, out_dtype=torch.float32, allow_partials=True)

@@ -38,5 +38,5 @@ class LMHead:
     def bind(self, store):
         self.weight = self.embedding.table if self.name is None else store.matrix(self.name)
 
-    def forward(self, y):
-        return matmul_tn(y, self.weight, out_dtype=torch.float32)
+    def forward(self, y, status=None):
+        return matmul_tn(y, self.weight, status, out_dtype=torch.float32)

@@ -34,7 +34,7 @@ class SwiGLUMLP(FeedForward):
         self.w_down = store.matrix(p + "down_proj.weight")
 
     def forward(self, x, ctx):
-        gate_up = matmul_tn(x, self.w_gate_up)
+        gate_up = matmul_tn(x, self.w_gate_up, ctx.status, allow_partials=True)
         act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
         ops.swiglu(gate_up, act)
-        return matmul_tn(act, self.w_down, out_dtype=torch.float32)
+        return matmul_tn(act, self.w_down, ctx.status, out_dtype=torch.float32, allow_partials=True)

@@ -64,6 +64,7 @@ class Sampler:
         R = logits.shape[0]
         rec = np.zeros((R, 8), dtype=np.int32)
         use_counts = False
+        no_nucleus = all(not (o.temperature > 0) or o.top_p >= 1.0 for o in options)
         for i, (o, step, slot) in enumerate(zip(options, steps, slots)):
             pen = o.repeat_penalty if o.repeat_penalty and o.repeat_penalty > 0 else 1.0
             use_counts |= pen != 1.0
@@ -75,5 +76,5 @@ class Sampler:
             self._need_counts()
         params = torch.from_numpy(rec).to(self.device)
         out = torch.empty(R, dtype=torch.int32, device=self.device)
-        ops.sample(logits, params, self.counts if use_counts else None, out)
+        ops.sample(logits, params, self.counts if use_counts else None, out, no_nucleus)
         return out
