@@ -7,7 +7,8 @@ sources (laik/vllm-cpp; file:line given per function, paths relative to that
 project).  Where the reference's CPU forward departs from the intended Qwen3
 model (per-head q/k norm never applied, interleaved RoPE lanes, constant RoPE
 base), the intended model is the default and the reference's behaviour is
-kept behind switches (``qk_norm=False``, ``rope_interleaved=True``) so the
+kept behind switches (``qk_norm=False``, ``rope_interleaved_lanes=True``,
+``down_in_place=True``) so the
 oracle itself can be anchored against the compiled reference
 (tests/golden/make_golden.py).
 """
@@ -145,10 +146,23 @@ def silu(z):
     return z / (1.0 + torch.exp(-z))
 
 
-def swiglu_mlp(y, w_gate, w_up, w_down):
-    """down(silu(gate(y)) * up(y)) (src/model.cpp:1237-1244, without the in-place
-    aliasing of the down projection's input and output)."""
-    return linear(silu(linear(y, w_gate)) * linear(y, w_up), w_down)
+def swiglu_mlp(y, w_gate, w_up, w_down, down_in_place=False):
+    """down(silu(gate(y)) * up(y)) (src/model.cpp:1237-1244).  The reference computes the
+    down projection in place -- output j is stored over input j before output j+1 is
+    summed (:1243-1244) -- which the intended model does not do; ``down_in_place`` repeats
+    that only so this file can be anchored against the reference's output."""
+    a = silu(linear(y, w_gate)) * linear(y, w_up)
+    if not down_in_place:
+        return linear(a, w_down)
+    out = torch.empty(a.shape[0], w_down.shape[0], dtype=a.dtype)
+    for t in range(a.shape[0]):
+        buf = a[t].clone()
+        for j in range(w_down.shape[0]):
+            v = buf @ w_down[j]
+            out[t, j] = v
+            if j < buf.shape[0]:
+                buf[j] = v
+    return out
 
 
 # --------------------------------------------------------------------------
@@ -171,7 +185,7 @@ def layer_windows(cfg):
     return [None] * L
 
 
-def forward(cfg, weights, ids, *, qk_norm=True, rope_interleaved_lanes=False, return_hidden=False):
+def forward(cfg, weights, ids, *, qk_norm=True, rope_interleaved_lanes=False, down_in_place=False, return_hidden=False):
     """Logits [T, vocab] at every position of one whole sequence
     (the layer order of src/model.cpp:1176-1263)."""
     W = {k: v.double() for k, v in weights.items()}
@@ -200,7 +214,8 @@ def forward(cfg, weights, ids, *, qk_norm=True, rope_interleaved_lanes=False, re
         a = attention(q, k, v, windows[l]).reshape(T, nh * hd)
         x = x + linear(a, W[p + "self_attn.o_proj.weight"])
         y = rms_norm(x, W[p + "post_attention_layernorm.weight"], eps)
-        x = x + swiglu_mlp(y, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"], W[p + "mlp.down_proj.weight"])
+        x = x + swiglu_mlp(y, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"], W[p + "mlp.down_proj.weight"],
+                           down_in_place)
     if return_hidden:
         return x
     y = rms_norm(x, W["model.norm.weight"], eps)

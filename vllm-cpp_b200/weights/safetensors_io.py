@@ -13,6 +13,7 @@ from __future__ import annotations
 import json
 import mmap
 import struct
+import warnings
 from pathlib import Path
 
 import numpy as np
@@ -71,7 +72,9 @@ def read_safetensors(path) -> dict[str, torch.Tensor]:
         if end - begin != numel * esize or begin < 0 or base + end > size:
             raise SafetensorsError(f"{path}: tensor '{name}' spans bytes [{begin}, {end}) but shape {shape} of "
                                    f"{dtype_name} needs {numel * esize} (file holds {size - base} data bytes)")
-        raw = torch.from_numpy(buf[base + begin: base + end])
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)   # the map is read-only on purpose; nothing writes through it
+            raw = torch.from_numpy(buf[base + begin: base + end])
         out[name] = raw.view(tdtype).reshape(shape) if numel else torch.empty(shape, dtype=tdtype)
     return out
 
