@@ -1,0 +1,313 @@
+"""Each part of a layer alone against the plain implementation's function for it, and the generality of the
+assembly: a toy mixer with state of its own, a layer that runs twice, and a layer that reads another layer's
+cache -- all registered from here, without a change to the package's files."""
+import json
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def build_ctx(dtype):
+    from vllm_cpp_b200.parts import BuildContext
+    return BuildContext(dtype, torch.device(DEV))
+
+
+def store_of(tensors, dtype):
+    from vllm_cpp_b200.weights import WeightStore
+    return WeightStore(tensors, dtype, DEV)
+
+
+def tol(dtype):
+    return dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part(dtype):
+    from vllm_cpp_b200.parts import RMSNorm
+    H, T, eps = 96, 5, 1e-5
+    w = (1 + 0.1 * torch.randn(H)).to(torch.bfloat16)
+    part = RMSNorm({"size": H, "eps": eps}, "n.", build_ctx(dtype))
+    assert [s.name for s in part.tensor_specs()] == ["n.weight"]
+    part.bind(store_of({"n.weight": w}, dtype))
+    resid, delta = torch.randn(T, H, device=DEV), torch.randn(2, T, H, device=DEV)
+    want_x = resid.double().cpu() + delta.double().cpu().sum(0)
+    y = part.forward(resid, delta)
+    torch.testing.assert_close(y.double().cpu(), P.rms_norm(want_x, w.double(), eps), **tol(dtype))
+    torch.testing.assert_close(resid.double().cpu(), want_x, rtol=1e-6, atol=1e-6)     # the stream took the deltas
+
+
+def test_rotary_table():
+    from vllm_cpp_b200.parts import RotaryEmbedding
+    part = RotaryEmbedding({"head_dim": 32, "theta": 1e6, "max_positions": 300}, "", build_ctx(torch.float32))
+    cos, sin = P.rope_angles(32, 1e6, list(range(300)))
+    torch.testing.assert_close(part.table.cpu().double(), torch.cat([cos, sin], 1), rtol=0, atol=1e-7)
+    other = RotaryEmbedding({"head_dim": 32, "theta": 1e6, "max_positions": 300}, "x.", part.build)
+    assert other.table is part.table                                                  # equal parameters share one table
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T", [3, 150])
+def test_swiglu_part(dtype, T):
+    from vllm_cpp_b200.parts import SwiGLUMLP
+    H, I = 96, 200
+    w = {f"m.{n}_proj.weight": (0.1 * torch.randn(*s)).to(torch.bfloat16)
+         for n, s in (("gate", (I, H)), ("up", (I, H)), ("down", (H, I)))}
+    part = SwiGLUMLP({"hidden_size": H, "intermediate_size": I}, "m.", build_ctx(dtype))
+    part.bind(store_of(w, dtype))
+    x = torch.randn(T, H).to(torch.bfloat16)
+
+    class Ctx:
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    y = part.forward(x.to(DEV).to(dtype), Ctx())
+    y = y.double().cpu().sum(0) if y.dim() == 3 else y.double().cpu()
+    want = P.swiglu_mlp(x.double(), *(w[f"m.{n}_proj.weight"].double() for n in ("gate", "up", "down")))
+    torch.testing.assert_close(y, want, **tol(dtype))
+    assert Ctx.status.item() == 0
+
+
+class OnePartModel:
+    """Just enough of a model for ModelRunner: one mixer, one cache, returns the mixer's output rows."""
+
+    def __init__(self, mixer, hidden, x_by_token):
+        self.mixer, self.x = mixer, x_by_token
+
+        class Spec:
+            vocab_size, max_positions = x_by_token.shape[0], 4096
+        self.spec = Spec()
+
+    def cache_specs(self):
+        return {0: self.mixer.cache_spec()}
+
+    def forward(self, ctx, caches):
+        x = self.x[ctx.token_ids.long()]                # "embedding": token id t stands for row t of x
+        d = self.mixer.forward(x, ctx, caches[0], True)
+        return d.sum(0) if d.dim() == 3 else d
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, 0), (6, 2, 32, 9), (8, 2, 64, 0), (4, 4, 128, 40)])
+def test_attention_part_in_portions(dtype, nh, nkv, hd, window):
+    """The attention mixer alone, fed one sequence in portions (17, 1, 1, 30, 2, ...) through the paged cache."""
+    from vllm_cpp_b200.engine.step import ModelRunner, StepEntry
+    from vllm_cpp_b200.parts import GQAAttention
+    from vllm_cpp_b200.registry import PartSpec
+    from vllm_cpp_b200.runtime import runtime
+    H, T, eps, theta, ps = 72, 90, 1e-6, 1e4, 8
+    torch.manual_seed(nh * hd)
+    w = {"a.q_proj.weight": 0.15 * torch.randn(nh * hd, H), "a.k_proj.weight": 0.15 * torch.randn(nkv * hd, H),
+         "a.v_proj.weight": 0.15 * torch.randn(nkv * hd, H), "a.o_proj.weight": 0.15 * torch.randn(H, nh * hd),
+         "a.q_norm.weight": 1 + 0.1 * torch.randn(hd), "a.k_norm.weight": 1 + 0.1 * torch.randn(hd)}
+    w = {k: v.to(torch.bfloat16) for k, v in w.items()}
+    rope = PartSpec("rope", {"head_dim": hd, "theta": theta, "max_positions": 4096})
+    part = GQAAttention({"hidden_size": H, "num_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "eps": eps,
+                         "qk_norm": True, "window": window, "position": rope}, "a.", build_ctx(dtype))
+    part.bind(store_of(w, dtype))
+    x = torch.randn(T, H).to(torch.bfloat16)
+    runner = ModelRunner(OnePartModel(part, H, x.to(DEV).to(dtype)), ps, 32, 2, dtype, DEV, cuda_graphs=False)
+    rt = runtime()
+    cm = rt.CacheManager(runner.layout.runtime_groups(rt, ps, 32), 2)
+    cm.open(0)
+    got, p = [], 0
+    for n in [17, 1, 1, 30, 2, 1, 38]:
+        assert cm.reserve(0, p + n)
+        out = runner.step([StepEntry(cm.slot(0), p, list(range(p, p + n)), [cm.block_table(0, 0)], list(range(n)))])
+        cm.commit(0, p + n)
+        got.append(out.double().cpu())
+        p += n
+    got = torch.cat(got)
+    # the same in the plain implementation's functions
+    W = {k: v.double() for k, v in w.items()}
+    xd = x.double()
+    q = P.head_rms_norm(P.linear(xd, W["a.q_proj.weight"]).view(T, nh, hd), W["a.q_norm.weight"], eps)
+    k = P.head_rms_norm(P.linear(xd, W["a.k_proj.weight"]).view(T, nkv, hd), W["a.k_norm.weight"], eps)
+    v = P.linear(xd, W["a.v_proj.weight"]).view(T, nkv, hd)
+    cos, sin = P.rope_angles(hd, theta, list(range(T)))
+    a = P.attention(P.rope_half_split(q, cos, sin), P.rope_half_split(k, cos, sin), v, window or None)
+    want = P.linear(a.reshape(T, nh * hd), W["a.o_proj.weight"])
+    torch.testing.assert_close(got, want, **tol(dtype))
+    if window:
+        assert cm.block_table(0, 0)[0] == -1         # pages the window has passed were given back on the way
+
+
+# ----------------------------------------------------------------------------------------------------------
+# a toy architecture, defined here: a mixer with state of its own, a layer run twice, a layer reading another's cache
+# ----------------------------------------------------------------------------------------------------------
+
+@dataclass(frozen=True)
+class ToyConfig:
+    vocab_size: int = 97
+    hidden_size: int = 48
+    intermediate_size: int = 80
+    num_heads: int = 4
+    num_kv_heads: int = 2
+    head_dim: int = 16
+    eps: float = 1e-5
+    theta: float = 1e4
+    max_positions: int = 128
+    architecture: str = "ToyForCausalLM"
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(**{k: d[k] for k in cls.__dataclass_fields__ if k in d and k != "architecture"})
+
+    def to_dict(self):
+        d = {k: getattr(self, k) for k in self.__dataclass_fields__ if k != "architecture"}
+        d["architectures"] = [self.architecture]
+        return d
+
+
+def register_toy():
+    from vllm_cpp_b200.parts import CacheSpec, Mixer
+    from vllm_cpp_b200.registry import LayerRun, LayerSpec, ModelSpec, PartSpec, register_architecture, register_part
+    from vllm_cpp_b200.weights import TensorSpec
+
+    class RunningMeanMixer(Mixer):
+        """delta_t = W . mean(x_0..x_t): needs the running sum of a request's inputs, a state of fixed size."""
+        capturable = False
+
+        def cache_spec(self):
+            return CacheSpec("state", shape=(int(self.params["size"]),), dtype="float32")
+
+        def tensor_specs(self):
+            n = int(self.params["size"])
+            return [TensorSpec(self.prefix + "mix.weight", (n, n))]
+
+        def bind(self, store):
+            self.w = store.matrix(self.prefix + "mix.weight")
+
+        def forward(self, x, ctx, cache, writes=True):
+            out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+            for i, e in enumerate(ctx.entries):
+                s, n = ctx.host_q_start[i], len(e.tokens)
+                run = cache.state[e.slot] + torch.cumsum(x[s:s + n].float(), 0)
+                cache.state[e.slot] = run[-1]
+                count = torch.arange(e.start_pos + 1, e.start_pos + n + 1, device=x.device, dtype=torch.float32)
+                out[s:s + n] = run / count[:, None]
+            return out @ self.w.float().T
+
+    def describe(cfg: ToyConfig):
+        H = cfg.hidden_size
+        norm = PartSpec("rmsnorm", {"size": H, "eps": cfg.eps})
+        ffn = PartSpec("swiglu", {"hidden_size": H, "intermediate_size": cfg.intermediate_size})
+        rope = PartSpec("rope", {"head_dim": cfg.head_dim, "theta": cfg.theta, "max_positions": cfg.max_positions})
+        attn = dict(hidden_size=H, num_heads=cfg.num_heads, num_kv_heads=cfg.num_kv_heads, head_dim=cfg.head_dim,
+                    eps=cfg.eps, qk_norm=True, window=0, position=rope)
+
+        def layer(i, mixer):
+            return LayerSpec(prefix=f"toy.{i}.", block=PartSpec("prenorm"),
+                             parts={"norm1": (norm, "n1."), "mixer": (mixer, "mix."), "norm2": (norm, "n2."),
+                                    "feed_forward": (ffn, "ff.")})
+        layers = (layer(0, PartSpec("gqa_attention", dict(attn, has_kv=True))),
+                  layer(1, PartSpec("running_mean", {"size": H})),
+                  layer(2, PartSpec("gqa_attention", dict(attn, has_kv=False))))
+        order = (LayerRun(0, 0), LayerRun(1, 1), LayerRun(0, 2), LayerRun(2, 0, writes=False), LayerRun(1, 3))
+        return ModelSpec(hidden_size=H, vocab_size=cfg.vocab_size, max_positions=cfg.max_positions,
+                         embed_tensor="toy.embed.weight", layers=layers, order=order, final_norm=norm,
+                         final_norm_prefix="toy.norm.", lm_head_tensor=None)
+
+    register_part("mixer", "running_mean", RunningMeanMixer)
+    register_architecture("ToyForCausalLM", ToyConfig, describe)
+
+
+def plain_toy(cfg: ToyConfig, W, ids):
+    """The toy model on one whole sequence, from the plain implementation's functions."""
+    T, nh, nkv, hd = len(ids), cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+    cos, sin = P.rope_angles(hd, cfg.theta, list(range(T)))
+    x = P.embed(ids, W["toy.embed.weight"])
+    kept = {}
+
+    def attn_layer(i, x, own_kv, key):
+        p = f"toy.{i}."
+        y = P.rms_norm(x, W[p + "n1.weight"], cfg.eps)
+        q = P.rope_half_split(P.head_rms_norm(P.linear(y, W[p + "mix.q_proj.weight"]).view(T, nh, hd), W[p + "mix.q_norm.weight"], cfg.eps), cos, sin)
+        if own_kv:
+            k = P.rope_half_split(P.head_rms_norm(P.linear(y, W[p + "mix.k_proj.weight"]).view(T, nkv, hd), W[p + "mix.k_norm.weight"], cfg.eps), cos, sin)
+            kept[key] = (k, P.linear(y, W[p + "mix.v_proj.weight"]).view(T, nkv, hd))
+        k, v = kept[key]
+        x = x + P.linear(P.attention(q, k, v).reshape(T, nh * hd), W[p + "mix.o_proj.weight"])
+        y = P.rms_norm(x, W[p + "n2.weight"], cfg.eps)
+        return x + P.swiglu_mlp(y, W[p + "ff.gate_proj.weight"], W[p + "ff.up_proj.weight"], W[p + "ff.down_proj.weight"])
+
+    def mean_layer(x):
+        p = "toy.1."
+        y = P.rms_norm(x, W[p + "n1.weight"], cfg.eps)
+        mean = torch.cumsum(y, 0) / torch.arange(1, T + 1, dtype=torch.float64)[:, None]
+        x = x + P.linear(mean, W[p + "mix.mix.weight"])
+        y = P.rms_norm(x, W[p + "n2.weight"], cfg.eps)
+        return x + P.swiglu_mlp(y, W[p + "ff.gate_proj.weight"], W[p + "ff.up_proj.weight"], W[p + "ff.down_proj.weight"])
+
+    x = attn_layer(0, x, True, 0)
+    x = mean_layer(x)
+    x = attn_layer(0, x, True, 2)       # the same layer again, with a cache of its own
+    x = attn_layer(2, x, False, 0)      # queries of layer 2 over the keys the first run of layer 0 stored
+    x = mean_layer(x)                   # and the stateful layer again, with a second state
+    return P.linear(P.rms_norm(x, W["toy.norm.weight"], cfg.eps), W["toy.embed.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_registers_builds_and_steps(dtype, tmp_path):
+    from vllm_cpp_b200 import load_config, write_random_model, unregister_architecture, unregister_part
+    from vllm_cpp_b200.engine.llm import TORCH_DTYPES
+    from vllm_cpp_b200.engine.step import ModelRunner, StepEntry
+    from vllm_cpp_b200.models import build_model
+    from vllm_cpp_b200.runtime import runtime
+    from vllm_cpp_b200.weights import open_model_weights
+    register_toy()
+    try:
+        cfg = ToyConfig()
+        folder = write_random_model(cfg, 3, tmp_path / "toy")
+        assert load_config(folder) == cfg
+        _, W = P.read_model(folder)
+        W = {k: v.double() for k, v in W.items()}
+        assert "toy.2.mix.k_proj.weight" not in W and "toy.1.mix.mix.weight" in W     # the reader of a cache has no K/V weights
+        td = TORCH_DTYPES[dtype]
+        model = build_model(cfg, td, DEV)
+        store = open_model_weights(folder, td, DEV)
+        model.load(store)
+        assert not model.capturable
+        ps = 4
+        runner = ModelRunner(model, ps, 64, 3, td, DEV)
+        kinds = [(g.spec.kind, len(g.cache_ids)) for g in runner.layout.groups]
+        assert kinds == [("kv", 2), ("state", 2)]          # caches 0 and 2 share pages; 1 and 3 are two states per slot
+        rt = runtime()
+        cm = rt.CacheManager(runner.layout.runtime_groups(rt, ps, 64), 3)
+        rng = np.random.default_rng(0)
+        seqs = {r: rng.integers(0, cfg.vocab_size, n).tolist() for r, n in ((0, 50), (1, 23), (2, 9))}
+        want = {r: plain_toy(cfg, W, t) for r, t in seqs.items()}
+        pos = {r: 0 for r in seqs}
+        cuts = {0: [7, 1, 20, 2, 1, 19], 1: [1, 1, 21], 2: [9]}
+        for r in seqs:
+            cm.open(r)
+        worst = 0.0
+        for step in range(6):
+            entries, rows = [], []
+            for r in seqs:
+                if step < len(cuts[r]):
+                    n = cuts[r][step]
+                    assert cm.reserve(r, pos[r] + n)
+                    entries.append(StepEntry(cm.slot(r), pos[r], seqs[r][pos[r]:pos[r] + n], [cm.block_table(r, 0)], list(range(n))))
+                    rows += [(r, pos[r] + i) for i in range(n)]
+                    pos[r] += n
+            out = runner.step(entries).double().cpu()
+            for r in seqs:
+                cm.commit(r, pos[r])
+            ref = torch.stack([want[r][p] for r, p in rows])
+            worst = max(worst, ((out - ref).abs().max() / ref.abs().max()).item())
+        assert worst < (2e-5 if dtype == "float32" else 4e-2), worst
+        # a slot handed to another request starts from a clean state
+        cm.close(2)
+        cm.open(7)
+        assert cm.slot(7) == 2 and cm.reserve(7, 9)
+        out = runner.step([StepEntry(2, 0, seqs[2], [cm.block_table(7, 0)], [8])]).double().cpu()
+        assert ((out[0] - want[2][8]).abs().max() / want[2][8].abs().max()).item() < (2e-5 if dtype == "float32" else 4e-2)
+    finally:
+        unregister_architecture("ToyForCausalLM")
+        unregister_part("mixer", "running_mean")

@@ -128,7 +128,7 @@ class ModelRunner:
         self.tables = [torch.full((num_slots, self.max_blocks), -1, dtype=torch.int32, device=self.device)
                        for _ in range(n_paged)]
         self._uploaded = [[0] * num_slots for _ in range(n_paged)]   # table entries of each slot already on the device
-        self.cuda_graphs = cuda_graphs and self.device.type == "cuda"
+        self.cuda_graphs = cuda_graphs and self.device.type == "cuda" and getattr(model, "capturable", True)
         self._graphs: dict[int, tuple] = {}
         self.last_ctx = None
         self.last_h2d_bytes = 0

@@ -37,6 +37,11 @@ class DecoderModel:
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"the execution order names layer {run.layer}, the model has {len(self.layers)}")
 
+    @property
+    def capturable(self) -> bool:
+        """Whether a decoding step of this model can be captured as a CUDA graph."""
+        return all(getattr(p, "capturable", True) for layer in self.layers for p in layer.parts.values())
+
     # ---- weights ----
     def tensor_specs(self) -> list[TensorSpec]:
         specs = list(self.embedding.tensor_specs())

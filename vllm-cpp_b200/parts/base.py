@@ -54,6 +54,9 @@ class CacheSpec:
 
 class Part:
     family = ""
+    # False for a part whose forward reads host-side facts of the step (ctx.entries and the like): a model with
+    # such a part is run kernel by kernel instead of from a captured graph
+    capturable = True
 
     def __init__(self, params: dict, prefix: str, build: BuildContext):
         self.params = dict(params)
