@@ -324,3 +324,84 @@ VCB_API int vcb_attn_merge(const float* part_o, const float* part_ml, const int*
     VCB_CHECK_LAUNCH("attn_merge");
     return 0;
 }
+
+// ---------------------------------------------------------------------------
+// Sliced decode attention that allocates nothing (declared in no_alloc_api.h).
+//
+// Same kernels as vcb_attn_paged + vcb_attn_merge, but the (max, sum, output) partials of the key slices live in
+// a fixed array inside this library instead of buffers the caller allocates.  The array exists once per GPU that
+// loads the library, from load until exit, whether or not this entry point is ever called.
+// ---------------------------------------------------------------------------
+#include "no_alloc_api.h"
+
+#include <mutex>
+
+static __device__ __align__(256) float g_decode_partials[VCB_NO_ALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_partials_addr[MAX_DEVICES];   // device address of g_decode_partials on each device, once looked up
+bool g_partials_known[MAX_DEVICES];
+std::mutex g_partials_mutex;
+
+// In host code `g_decode_partials` is only a handle for the runtime; the address a kernel can use must be asked
+// for, per device, with that device current.
+int partials_address(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+        vcb_set_error("attn_decode_no_alloc: cannot tell the current device (%s)", cudaGetErrorString(e));
+        return -2;
+    }
+    std::lock_guard<std::mutex> lock(g_partials_mutex);
+    if (!g_partials_known[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_decode_partials);
+        if (e != cudaSuccess || p == nullptr) {
+            vcb_set_error("attn_decode_no_alloc: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+            return -2;
+        }
+        g_partials_addr[dev] = static_cast<float*>(p);
+        g_partials_known[dev] = true;
+    }
+    *out = g_partials_addr[dev];
+    return 0;
+}
+}  // namespace
+
+VCB_API int vcb_attn_decode_no_alloc(const void* q, void* out, int dtype, const void* pages, long long page_stride,
+                                     const int* block_table, const int* table_row, int max_blocks,
+                                     const int* q_start, const int* q_len, const int* ctx_len, const int* items,
+                                     const int* dec_rows, int n_dec, int nslices, int nh, int nkv, int hd,
+                                     int page_size, int num_pages, int window, float scale, int* status,
+                                     cudaStream_t stream) {
+    if (n_dec == 0) return 0;
+    VCB_CHECK_ARG(n_dec > 0 && nslices >= 2, "attn_decode_no_alloc: needs at least one token and two key slices (got %d, %d)", n_dec, nslices);
+    VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_decode_no_alloc: %d query heads are not a multiple of %d KV heads", nh, nkv);
+    VCB_CHECK_ARG(hd >= 16 && hd % 16 == 0 && hd <= VCB_MAX_HEAD_DIM, "attn_decode_no_alloc: head_dim %d must be a multiple of 16 in [16, %d]", hd, VCB_MAX_HEAD_DIM);
+    VCB_CHECK_ARG(page_size > 0 && window >= 0, "attn_decode_no_alloc: bad page_size %d or window %d", page_size, window);
+    const long long rows = (long long)n_dec * nh * nslices;
+    const long long need = rows * (hd + 2);
+    VCB_CHECK_ARG(need <= (long long)VCB_NO_ALLOC_SCRATCH_FLOATS,
+                  "attn_decode_no_alloc: %d tokens x %d heads x %d slices x (head_dim %d + 2) = %lld floats of partials exceed "
+                  "the built-in scratch of %lld floats; use fewer slices or the allocating entry points",
+                  n_dec, nh, nslices, hd, need, (long long)VCB_NO_ALLOC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    if (int rc = partials_address(&scratch)) return rc;
+    float* part_o = scratch;               // [rows, hd]
+    float* part_ml = scratch + rows * hd;  // [rows, 2]
+    // every slice of every live row writes its partial (an empty slice writes max = -inf, sum = 0), so nothing of
+    // an earlier call's contents is read and nothing has to be cleared
+    AttnArgs a{q, out, pages, page_stride, block_table, table_row, max_blocks, q_start, q_len, ctx_len, items, part_o,
+               part_ml, nh, nkv, hd, page_size, num_pages, window, scale, status};
+    const int rc = dtype == VCB_F32 ? launch_attn<float, 8>(a, n_dec * nslices, stream)
+                                    : launch_attn<__nv_bfloat16, 8>(a, n_dec * nslices, stream);
+    if (rc) return rc;
+    const int threads = hd <= 64 ? 64 : (hd <= 128 ? 128 : 256);
+    if (dtype == VCB_F32)
+        attn_merge_kernel<float><<<dim3(n_dec, nh), threads, 0, stream>>>(part_o, part_ml, dec_rows, (float*)out, nh, hd, nslices);
+    else
+        attn_merge_kernel<__nv_bfloat16><<<dim3(n_dec, nh), threads, 0, stream>>>(part_o, part_ml, dec_rows, (__nv_bfloat16*)out, nh, hd, nslices);
+    VCB_CHECK_LAUNCH("attn_decode_no_alloc merge");
+    return 0;
+}
