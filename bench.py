@@ -115,7 +115,8 @@ def main():
     B_MAX = 64
     points = [args.batch] if args.skip_points else sorted({1, args.batch, B_MAX})
     max_seqs = max(points)
-    steps_total = args.steps + args.warmup + 8
+    # room for the end-to-end run, whose requests start decoding up to two steps apart each
+    steps_total = args.steps + args.warmup + 2 * args.batch + 24
     per_req = -(-(args.context + steps_total) // 64) * 64
     max_tokens = max(max(points) * per_req, 8192)
     t0 = time.time()
@@ -169,8 +170,8 @@ def main():
             l0 = ops.launch_count
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            logits = runner.step(entries, check=False)
-            toks = llm.sampler.sample(logits, [GREEDY] * B, [0] * B, [e.slot for e in entries])
+            flat, use_counts, no_nucleus = Sampler.records([GREEDY] * B, [0] * B, [e.slot for e in entries])
+            toks = runner.step(entries, check=False, user=flat, post=sample_post, post_key=("sample", False, True))
             e1.record()
             e1.synchronize()
             if timed:
@@ -184,8 +185,11 @@ def main():
         return dict(ms=ms, tok_s=B * 1000.0 / ms, launches=launches,
                     bytes=weight_bytes + B * (args.context + warmup + steps / 2) * kv_bytes_per_token)
 
-    from vllm_cpp_b200.sampling import SamplingOptions
+    from vllm_cpp_b200.sampling import Sampler, SamplingOptions
     GREEDY = SamplingOptions(0.0, 1.0, 1.0, 0)
+
+    def sample_post(ctx, logits):   # what LLM.step runs after the model, captured with the step
+        return llm.sampler.sample_records(logits, ctx.user[:8 * logits.shape[0]].view(-1, 8), False, True)
 
     if args.mode == "prefill":
         points = []
@@ -228,7 +232,7 @@ def main():
     B = args.batch
     e2e_steps = args.steps
     for r in range(B):
-        llm.submit_tokens(rng.integers(0, V, args.context - args.warmup).tolist(), args.warmup + e2e_steps + 2, 0.0, 1.0,
+        llm.submit_tokens(rng.integers(0, V, args.context - args.warmup).tolist(), args.warmup + e2e_steps + 2 * B + 8, 0.0, 1.0,
                           repeat_penalty=1.0, ignore_eos=True)
     while True:   # feed the prompts; stop when every request is decoding
         o = llm.step()

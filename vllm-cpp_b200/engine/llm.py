@@ -71,6 +71,7 @@ class LLM:
         self._options: dict[int, SamplingOptions] = {}
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        self._pinned = None
 
     # ---- the reference's engine surface ----
     def submit_tokens(self, prompt_tokens, max_new_tokens: int = MAX_NEW_TOKENS, temperature: float = TEMPERATURE,
@@ -118,26 +119,48 @@ class LLM:
             if e.sample:
                 sampled_entries.append(e)
         penalised = {e.slot for e in sched.entries if self._options[e.request].repeat_penalty not in (0.0, 1.0)}
-        logits = self.runner.step(entries, check=False)
-        self.h2d_bytes += self.runner.last_h2d_bytes
-        if penalised:
-            self.sampler.observe(self.runner.last_ctx, penalised)
         tokens: list[int] = []
         if sampled_entries:
-            toks = self.sampler.sample(logits, [self._options[e.request] for e in sampled_entries],
-                                       [e.gen_step for e in sampled_entries], [e.slot for e in sampled_entries])
-            host = torch.cat([toks, self.runner.status]).cpu()   # one copy back: the tokens and the status word
-            self.d2h_bytes += host.numel() * 4
-            if int(host[-1]):
+            flat, use_counts, no_nucleus = Sampler.records([self._options[e.request] for e in sampled_entries],
+                                                           [e.gen_step for e in sampled_entries],
+                                                           [e.slot for e in sampled_entries])
+            n_rows = len(sampled_entries)
+
+            def post(ctx, logits):
+                if penalised:
+                    self.sampler.observe(ctx, penalised)
+                return self.sampler.sample_records(logits, ctx.user[:8 * logits.shape[0]].view(-1, 8), use_counts, no_nucleus)
+
+            # a step that counts token occurrences reads host-side facts, so it is not captured (key None keeps it eager)
+            toks = self.runner.step(entries, check=False, user=flat, post=post,
+                                    post_key=None if penalised else ("sample", use_counts, no_nucleus))
+            host = self._readback(toks[:n_rows])
+            if host[-1]:
                 from .. import ops
                 ops.check_status(self.runner.status)
-            tokens = host[:-1].tolist()
+            tokens = host[:-1]
+        else:
+            self.runner.step(entries, check=False)
+            if penalised:
+                self.sampler.observe(self.runner.last_ctx, penalised)
+        self.h2d_bytes += self.runner.last_h2d_bytes
         finished = set(self.scheduler.update(tokens))
         for e, t in zip(sampled_entries, tokens):
             out.request_ids.append(e.request)
             out.new_token_ids.append(t)
             out.finished.append(e.request in finished)
         return out
+
+    def _readback(self, toks: torch.Tensor) -> list[int]:
+        """The sampled tokens and the status word in one pinned buffer, one synchronisation."""
+        n = toks.numel()
+        if self._pinned is None or self._pinned.numel() < n + 1:
+            self._pinned = torch.empty(max(n + 1, 257), dtype=torch.int32).pin_memory()
+        self._pinned[:n].copy_(toks, non_blocking=True)
+        self._pinned[n:n + 1].copy_(self.runner.status, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes += (n + 1) * 4
+        return self._pinned[:n + 1].tolist()
 
     # ---- convenience ----
     def generate(self, prompts, max_new_tokens: int = MAX_NEW_TOKENS, temperature: float = TEMPERATURE,

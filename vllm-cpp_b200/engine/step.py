@@ -57,10 +57,10 @@ class MetaLayout:
     """Where each array sits in the packed int32 buffer of a step with T tokens, E entries, R wanted rows,
     U block-table updates per group and G paged groups."""
 
-    def __init__(self, T, E, R, U, G):
-        self.T, self.E, self.R, self.U, self.G = T, E, R, U, G
+    def __init__(self, T, E, R, U, G, X=0):
+        self.T, self.E, self.R, self.U, self.G, self.X = T, E, R, U, G, X
         names = [("token_ids", T), ("positions", T), ("q_start", E), ("q_len", E), ("ctx_len", E), ("slots", E),
-                 ("logit_rows", max(R, 1))]
+                 ("logit_rows", max(R, 1)), ("user", max(X, 1))]
         for g in range(G):
             names += [(f"slot_map{g}", T), (f"upd_count{g}", 1), (f"upd_idx{g}", max(U, 1)), (f"upd_val{g}", max(U, 1))]
         self.offsets = {}
@@ -86,6 +86,7 @@ class StepContext:
         self.token_ids, self.positions = v("token_ids"), v("positions")
         self.q_start, self.q_len, self.ctx_len, self.slots = v("q_start"), v("q_len"), v("ctx_len"), v("slots")
         self.logit_rows = v("logit_rows")[:layout.R]
+        self.user = v("user")[:layout.X]      # integers of the caller's own (the sampler's per-row records)
         self.groups = []
         for g in runner.layout.groups:
             if g.paged:
@@ -129,11 +130,11 @@ class ModelRunner:
                        for _ in range(n_paged)]
         self._uploaded = [[0] * num_slots for _ in range(n_paged)]   # table entries of each slot already on the device
         self.cuda_graphs = cuda_graphs and self.device.type == "cuda" and getattr(model, "capturable", True)
-        self._graphs: dict[int, tuple] = {}
+        self._graphs: dict[tuple, tuple] = {}
         self.last_ctx = None
         self.last_h2d_bytes = 0
         self.graph_replays = 0
-        self.launches_per_graph: dict[int, int] = {}
+        self.launches_per_graph: dict[tuple, int] = {}
 
     # ------------------------------------------------------------------ host side of a step
     def _validate(self, entries):
@@ -233,10 +234,15 @@ class ModelRunner:
         self._uploaded = [[0] * self.num_slots for _ in self.tables]
 
     # ------------------------------------------------------------------ running
-    def step(self, entries: list[StepEntry], check: bool = True) -> torch.Tensor | None:
+    def step(self, entries: list[StepEntry], check: bool = True, user=None, post=None, post_key=None):
         """Runs the entries' tokens as one batch.  Returns logits [wanted rows, vocab] (32-bit, on the
         device) in the order of the entries and of their ``want`` lists, or None if nothing was wanted.
-        The returned tensor of a decoding step is reused by the next such step: copy what must outlive it."""
+        The returned tensor of a decoding step is reused by the next such step: copy what must outlive it.
+
+        ``user``: int32 numbers of the caller's own, carried to the device with the step's buffer (``ctx.user``).
+        ``post(ctx, logits)``: work to run right after the model on the same stream (sampling); its result is
+        returned instead of the logits.  A captured step includes it, so ``post_key`` must name everything about
+        it that changes which kernels it launches."""
         if not entries:
             return None
         self._validate(entries)
@@ -246,44 +252,82 @@ class ModelRunner:
         decode_only = all(len(e.tokens) == 1 for e in entries)
         bucket = next((b for b in self.GRAPH_BUCKETS if b >= len(entries)), None)
         if (self.cuda_graphs and decode_only and bucket is not None and all(len(e.want) == 1 for e in entries)
-                and all(len(u[0]) <= bucket for u in updates)):
-            logits = self._step_graph(entries, updates, bucket)
+                and all(len(u[0]) <= bucket for u in updates) and (post is None or post_key is not None)):
+            logits = self._step_graph(entries, updates, bucket, user, post, post_key)
         else:
-            logits = self._step_eager(entries, updates, n_rows)
+            logits = self._step_eager(entries, updates, n_rows, user, post)
         if check:
             ops.check_status(self.status)
         return logits
 
-    def _step_eager(self, entries, updates, n_rows):
+    def _step_eager(self, entries, updates, n_rows, user=None, post=None):
         T = sum(len(e.tokens) for e in entries)
         U = max([len(u[0]) for u in updates] + [0])
-        lay = MetaLayout(T, len(entries), n_rows, U, len(self.tables))
+        lay = MetaLayout(T, len(entries), n_rows, U, len(self.tables), 0 if user is None else len(user))
         host, facts = self._fill(lay, entries, updates)
+        if user is not None:
+            host[lay.offsets["user"][0]:lay.offsets["user"][0] + len(user)] = user
         dev = torch.from_numpy(host).pin_memory().to(self.device, non_blocking=True)
         ctx = StepContext(self, lay, dev, static=False)
         ctx.__dict__.update(facts)
         self.last_ctx, self.last_h2d_bytes = ctx, host.nbytes
         self._apply_table_updates(ctx)
-        return self.model.forward(ctx, self.cache.views)
+        logits = self.model.forward(ctx, self.cache.views)
+        return post(ctx, logits) if post is not None else logits
 
-    def _step_graph(self, entries, updates, bucket):
-        if bucket not in self._graphs:
-            self._capture(bucket)
-        graph, ctx, logits, pinned = self._graphs[bucket]
-        host, facts = self._fill(ctx.meta_layout, entries, updates)
+    USER_INTS_PER_ENTRY = 8   # room in a captured step's buffer for the caller's numbers
+
+    def _fill_decode(self, lay: MetaLayout, entries, updates, user):
+        """_fill for single-token entries, without per-entry array work."""
+        E, B, ps = len(entries), lay.E, self.page_size
+        pad = B - E
+        toks = [e.tokens[0] for e in entries]
+        pos = [e.start_pos for e in entries]
+        parts = [toks, [0] * pad, pos, [0] * pad, list(range(E)), [E] * pad, [1] * E, [0] * pad,
+                 [p + 1 for p in pos], [0] * pad, [e.slot for e in entries], [0] * pad,
+                 list(range(E)), [0] * pad]
+        ux = [0] * max(lay.X, 1)
+        if user is not None:
+            ux[:len(user)] = [int(v) for v in user]
+        parts.append(ux)
+        for g in range(len(self.tables)):
+            sm = []
+            for e, p in zip(entries, pos):
+                page = e.tables[g][p // ps]
+                if page < 0:
+                    raise ValueError("a token would be stored in a page that was given back")
+                sm.append(page * ps + p % ps)
+            idx, val = updates[g]
+            n = len(idx)
+            parts += [sm, [-1] * pad, [n], idx, [0] * (lay.U - n), val, [0] * (lay.U - n)]
+        flat = [x for part in parts for x in part]
+        assert len(flat) == lay.size, (len(flat), lay.size)
+        facts = dict(entries=entries, host_q_len=[1] * E, host_q_start=list(range(E)),
+                     host_ctx_len=[p + 1 for p in pos], host_slots=[e.slot for e in entries])
+        return np.asarray(flat, dtype=np.int32), facts
+
+    def _step_graph(self, entries, updates, bucket, user=None, post=None, post_key=None):
+        key = (bucket, post_key if post is not None else None)
+        if key not in self._graphs:
+            self._capture(key, post)
+        graph, ctx, result, pinned = self._graphs[key]
+        if user is not None and len(user) > ctx.meta_layout.X:
+            raise ValueError(f"a captured step carries at most {ctx.meta_layout.X} user integers, {len(user)} given")
+        host, facts = self._fill_decode(ctx.meta_layout, entries, updates, user)
         ctx.__dict__.update(facts)
         pinned.copy_(torch.from_numpy(host))
         ctx.buffer.copy_(pinned, non_blocking=True)
         self.last_ctx, self.last_h2d_bytes = ctx, host.nbytes
         graph.replay()
         self.graph_replays += 1
-        ops.launch_count += self.launches_per_graph[bucket]
-        return logits[:len(entries)]
+        ops.launch_count += self.launches_per_graph[key]
+        return result[:len(entries)]
 
-    def _capture(self, bucket: int):
-        """Captures the forward pass of ``bucket`` single-token entries.  The capture itself runs on empty
-        entries (length 0), which store nothing and attend to nothing."""
-        lay = MetaLayout(bucket, bucket, bucket, bucket, len(self.tables))
+    def _capture(self, key, post=None):
+        """Captures the forward pass of ``bucket`` single-token entries (and what ``post`` adds).  The capture
+        itself runs on empty entries (length 0), which store nothing and attend to nothing."""
+        bucket = key[0]
+        lay = MetaLayout(bucket, bucket, bucket, bucket, len(self.tables), bucket * self.USER_INTS_PER_ENTRY)
         dev = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
         pinned = torch.zeros(lay.size, dtype=torch.int32).pin_memory()
         ctx = StepContext(self, lay, dev, static=True)
@@ -298,7 +342,8 @@ class ModelRunner:
 
         def run():
             self._apply_table_updates(ctx)
-            return self.model.forward(ctx, self.cache.views)
+            logits = self.model.forward(ctx, self.cache.views)
+            return post(ctx, logits) if post is not None else logits
 
         # warm up on a side stream (library handles, lazy module loads), then capture
         side = torch.cuda.Stream(device=self.device)
@@ -310,6 +355,6 @@ class ModelRunner:
         before = ops.launch_count
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            logits = run()
-        self.launches_per_graph[bucket] = ops.launch_count - before
-        self._graphs[bucket] = (graph, ctx, logits, pinned)
+            result = run()
+        self.launches_per_graph[key] = ops.launch_count - before
+        self._graphs[key] = (graph, ctx, result, pinned)

@@ -59,22 +59,32 @@ class Sampler:
         slots = torch.from_numpy(slot_of_token).to(self.device)
         ops.count_tokens(ctx.token_ids, slots, self.counts, ctx.T)
 
-    def sample(self, logits: torch.Tensor, options: list[SamplingOptions], steps: list[int], slots: list[int]) -> torch.Tensor:
-        """One token per row of ``logits``; returns int32 [rows] on the device."""
-        R = logits.shape[0]
-        rec = np.zeros((R, 8), dtype=np.int32)
-        use_counts = False
-        no_nucleus = all(not (o.temperature > 0) or o.top_p >= 1.0 for o in options)
-        for i, (o, step, slot) in enumerate(zip(options, steps, slots)):
+    @staticmethod
+    def records(options: list[SamplingOptions], steps: list[int], slots: list[int]):
+        """Per-row records for the kernel as a flat list of int32 (8 per row), and the two facts that decide which
+        kernels run: whether any row has a penalty (needs the count table), whether no row cuts a nucleus."""
+        flat, use_counts, no_nucleus = [], False, True
+        for o, step, slot in zip(options, steps, slots):
             pen = o.repeat_penalty if o.repeat_penalty and o.repeat_penalty > 0 else 1.0
             use_counts |= pen != 1.0
+            no_nucleus &= (not o.temperature > 0) or o.top_p >= 1.0
             seed = int(o.seed) & 0xFFFFFFFFFFFFFFFF
-            rec[i] = (_f2i(o.temperature), _f2i(o.top_p), _f2i(pen), slot if pen != 1.0 else -1,
-                      np.uint32(seed & 0xFFFFFFFF).view(np.int32), np.uint32(seed >> 32).view(np.int32),
-                      np.uint32(step & 0xFFFFFFFF).view(np.int32), 0)
+            lo, hi, st = seed & 0xFFFFFFFF, seed >> 32, step & 0xFFFFFFFF
+            flat += [_f2i(o.temperature), _f2i(o.top_p), _f2i(pen), slot if pen != 1.0 else -1,
+                     lo - (1 << 32) if lo >= (1 << 31) else lo, hi - (1 << 32) if hi >= (1 << 31) else hi,
+                     st - (1 << 32) if st >= (1 << 31) else st, 0]
+        return flat, use_counts, no_nucleus
+
+    def sample_records(self, logits: torch.Tensor, params: torch.Tensor, use_counts: bool, no_nucleus: bool) -> torch.Tensor:
+        """One token per row of ``logits`` from records already on the device (int32 [rows, 8])."""
         if use_counts:
             self._need_counts()
-        params = torch.from_numpy(rec).to(self.device)
-        out = torch.empty(R, dtype=torch.int32, device=self.device)
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
         ops.sample(logits, params, self.counts if use_counts else None, out, no_nucleus)
         return out
+
+    def sample(self, logits: torch.Tensor, options: list[SamplingOptions], steps: list[int], slots: list[int]) -> torch.Tensor:
+        """One token per row of ``logits``; returns int32 [rows] on the device."""
+        flat, use_counts, no_nucleus = self.records(options, steps, slots)
+        params = torch.tensor(flat, dtype=torch.int32).view(-1, 8).to(self.device)
+        return self.sample_records(logits, params, use_counts, no_nucleus)
