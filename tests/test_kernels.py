@@ -448,3 +448,43 @@ def test_sampling_split_over_blocks_matches_plain():
                             history=hist if i == 4 else (), seed=o.seed, step=3 + i)
         assert got[i] == want, (i, got[i], want)
     assert got[0] == 17
+
+
+@pytest.mark.parametrize("I,T,K", [(128, 256, 64), (200, 300, 96), (12288 // 8, 2048, 512), (72, 130, 264)])
+def test_gemm_bf16_swiglu(I, T, K):
+    """The product with the SiLU-gate in its epilogue against 64-bit."""
+    from vllm_cpp_b200 import ops
+    torch.manual_seed(I + T)
+    w = (torch.randn(2 * I, K, device=dev()) * 0.2).to(torch.bfloat16)
+    x = torch.randn(T, K, device=dev()).to(torch.bfloat16)
+    out = torch.full((T, I), float("nan"), dtype=torch.bfloat16, device=dev())
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    ops.gemm_bf16_swiglu(w, x, out, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    gu = x.double() @ w.double().T
+    g, u = gu[:, :I], gu[:, I:]
+    torch.testing.assert_close(out.double(), g / (1 + torch.exp(-g)) * u, rtol=2e-2, atol=2e-2)
+
+
+def test_qknorm_fast_path_matches_general_path():
+    """head_dim 128 in bfloat16 takes a vectorised kernel; the same inputs as 32-bit partial sums take the general one."""
+    from vllm_cpp_b200 import ops
+    T, nh, nkv, hd, ps, num_pages = 9, 6, 2, 128, 4, 5
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=dev()).to(torch.bfloat16)
+    qw = (1 + 0.1 * torch.randn(hd, device=dev())).to(torch.bfloat16)
+    kw = (1 + 0.1 * torch.randn(hd, device=dev())).to(torch.bfloat16)
+    table = rope_table(hd, 1e6, 64)
+    pos = torch.randint(0, 64, (T,), device=dev(), dtype=torch.int32)
+    slots = torch.randperm(num_pages * ps, device=dev())[:T].to(torch.int32)
+    slots[2] = -1
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    res = []
+    for inp in (qkv, qkv.float().unsqueeze(0)):
+        pages = torch.zeros(num_pages, 2, nkv, ps, hd, device=dev(), dtype=torch.bfloat16)
+        q = torch.zeros(T, nh * hd, device=dev(), dtype=torch.bfloat16)
+        ops.qknorm_rope_kvwrite(inp, qw, kw, 1e-6, table, pos, slots, q, pages, nh, nkv, hd, status)
+        res.append((q.float(), pages.float()))
+    assert status.item() == 0
+    torch.testing.assert_close(res[0][0], res[1][0], rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(res[0][1], res[1][1], rtol=1e-2, atol=1e-2)

@@ -182,12 +182,39 @@ __global__ void swiglu_kernel(const TIN* __restrict__ gu, int S, size_t s_stride
     }
 }
 
+// bfloat16 in and out, one slice, I a multiple of 8: 16-byte loads and stores
+__global__ void swiglu_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I8, size_t total8) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I8, i = idx % I8;
+        const uint4 g4 = reinterpret_cast<const uint4*>(gu + t * 16 * I8)[i];
+        const uint4 u4 = reinterpret_cast<const uint4*>(gu + t * 16 * I8 + 8 * (size_t)I8)[i];
+        const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float g0 = __uint_as_float(gw[k] << 16), g1 = __uint_as_float(gw[k] & 0xffff0000u);
+            const float u0 = __uint_as_float(uw[k] << 16), u1 = __uint_as_float(uw[k] & 0xffff0000u);
+            __nv_bfloat162 o = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+            ow[k] = *reinterpret_cast<uint32_t*>(&o);
+        }
+        reinterpret_cast<uint4*>(out + t * 8 * I8)[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
 // gate_up: [S, T, 2I] of in_dtype (S partial sums, s_stride elements apart); out: [T, I] of out_dtype
 VCB_API int vcb_swiglu(const void* gate_up, int in_dtype, int S, long long s_stride, void* out, int out_dtype, int T,
                        int I, cudaStream_t stream) {
     if (T == 0) return 0;
     VCB_CHECK_ARG(T > 0 && I > 0 && S >= 1, "swiglu: bad sizes T=%d I=%d S=%d", T, I, S);
     const size_t total = (size_t)T * I;
+    if (in_dtype == VCB_BF16 && out_dtype == VCB_BF16 && S == 1 && I % 8 == 0 && ((uintptr_t)gate_up % 16 == 0) &&
+        ((uintptr_t)out % 16 == 0)) {
+        const size_t total8 = total / 8;
+        const int nb = (int)((total8 + 255) / 256 < 148 * 32 ? (total8 + 255) / 256 : 148 * 32);
+        swiglu_bf16_vec_kernel<<<nb, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I / 8, total8);
+        VCB_CHECK_LAUNCH("swiglu");
+        return 0;
+    }
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     if (in_dtype == VCB_F32 && out_dtype == VCB_F32)
         swiglu_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)gate_up, S, (size_t)s_stride, (float*)out, I, total);
@@ -290,6 +317,68 @@ __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, s
     }
 }
 
+// Same contract for the serving shape of prompt portions (head_dim 128, bfloat16 in and out, no partial sums):
+// one block per token, its warps walk the heads; each lane owns lanes {2l, 2l+1} and their partners 64 further
+// on, loads them as two 4-byte words, and keeps the token's cosines and sines in registers for all heads.
+__global__ __launch_bounds__(256) void qknorm_rope_kvwrite_hd128_kernel(
+    const __nv_bfloat16* __restrict__ qkv, const void* __restrict__ qw, const void* __restrict__ kw, int w_dtype,
+    int use_norm, float eps, const float* __restrict__ cos_sin, int max_pos, const int* __restrict__ positions,
+    const int* __restrict__ slot_map, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ pages,
+    long long page_stride, int page_size, int num_pages, int nh, int nkv, int has_kv, int* status) {
+    constexpr int hd = 128, half = 64;
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int heads_total = nh + (has_kv ? 2 * nkv : 0);
+    int pos = positions[t];
+    if (pos < 0 || pos >= max_pos) {
+        if (threadIdx.x == 0) atomicOr(status, VCB_STATUS_BAD_POSITION);
+        pos = 0;
+    }
+    const float2 c = *reinterpret_cast<const float2*>(cos_sin + (size_t)pos * hd + 2 * lane);
+    const float2 sn = *reinterpret_cast<const float2*>(cos_sin + (size_t)pos * hd + half + 2 * lane);
+    int slot = has_kv ? slot_map[t] : -1;
+    if (slot >= 0 && slot / page_size >= num_pages) {
+        if (threadIdx.x == 0) atomicOr(status, VCB_STATUS_BAD_PAGE);
+        slot = -1;
+    }
+    float gq[4] = {1.f, 1.f, 1.f, 1.f}, gk[4] = {1.f, 1.f, 1.f, 1.f};   // gains of this lane's four elements
+    if (use_norm) {
+        gq[0] = load_as_f32(qw, w_dtype, 2 * lane); gq[1] = load_as_f32(qw, w_dtype, 2 * lane + 1);
+        gq[2] = load_as_f32(qw, w_dtype, half + 2 * lane); gq[3] = load_as_f32(qw, w_dtype, half + 2 * lane + 1);
+        if (has_kv) {
+            gk[0] = load_as_f32(kw, w_dtype, 2 * lane); gk[1] = load_as_f32(kw, w_dtype, 2 * lane + 1);
+            gk[2] = load_as_f32(kw, w_dtype, half + 2 * lane); gk[3] = load_as_f32(kw, w_dtype, half + 2 * lane + 1);
+        }
+    }
+    const __nv_bfloat16* row = qkv + (size_t)t * heads_total * hd;
+    for (int h = warp; h < heads_total; h += nwarps) {
+        const __nv_bfloat16* src = row + (size_t)h * hd;
+        __nv_bfloat16* dst;
+        if (h < nh) {
+            dst = q_out + ((size_t)t * nh + h) * hd;
+        } else {
+            if (slot < 0) continue;   // padded token: nothing to store
+            const int kv = h >= nh + nkv, kvh = kv ? h - nh - nkv : h - nh;
+            dst = pages + (size_t)(slot / page_size) * page_stride + ((size_t)(kv * nkv + kvh) * page_size + slot % page_size) * hd;
+        }
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(src + 2 * lane);
+        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(src + half + 2 * lane);
+        if (h >= nh + nkv) {   // V: stored as it is
+            *reinterpret_cast<__nv_bfloat162*>(dst + 2 * lane) = lo;
+            *reinterpret_cast<__nv_bfloat162*>(dst + half + 2 * lane) = hi;
+            continue;
+        }
+        float a0 = __low2float(lo), a1 = __high2float(lo), b0 = __low2float(hi), b1 = __high2float(hi);
+        if (use_norm) {
+            const float ss = warp_sum(a0 * a0 + a1 * a1 + b0 * b0 + b1 * b1);
+            const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+            const float* gw = h < nh ? gq : gk;
+            a0 = gw[0] * a0 * inv; a1 = gw[1] * a1 * inv; b0 = gw[2] * b0 * inv; b1 = gw[3] * b1 * inv;
+        }
+        *reinterpret_cast<__nv_bfloat162*>(dst + 2 * lane) = __floats2bfloat162_rn(a0 * c.x - b0 * sn.x, a1 * c.y - b1 * sn.y);
+        *reinterpret_cast<__nv_bfloat162*>(dst + half + 2 * lane) = __floats2bfloat162_rn(b0 * c.x + a0 * sn.x, b1 * c.y + a1 * sn.y);
+    }
+}
+
 // qkv: [S, T, width] of in_dtype (S partial sums, s_stride elements apart); q_out and pages of out_dtype
 VCB_API int vcb_qknorm_rope_kvwrite(const void* qkv, int in_dtype, int S, long long s_stride, int out_dtype,
                                     const void* qw, const void* kw, int w_dtype, int use_norm, float eps,
@@ -301,6 +390,14 @@ VCB_API int vcb_qknorm_rope_kvwrite(const void* qkv, int in_dtype, int S, long l
                   "qknorm_rope_kvwrite: head_dim %d must be even and <= %d", hd, VCB_MAX_HEAD_DIM);
     VCB_CHECK_ARG(nh > 0 && nkv > 0 && page_size > 0 && S >= 1, "qknorm_rope_kvwrite: bad sizes nh=%d nkv=%d page=%d S=%d",
                   nh, nkv, page_size, S);
+    if (hd == 128 && in_dtype == VCB_BF16 && out_dtype == VCB_BF16 && S == 1 && ((uintptr_t)qkv % 4 == 0) &&
+        ((uintptr_t)q_out % 4 == 0) && ((uintptr_t)pages % 4 == 0)) {
+        qknorm_rope_kvwrite_hd128_kernel<<<T, 256, 0, stream>>>(
+            (const __nv_bfloat16*)qkv, qw, kw, w_dtype, use_norm, eps, cos_sin, max_pos, positions, slot_map,
+            (__nv_bfloat16*)q_out, (__nv_bfloat16*)pages, page_stride, page_size, num_pages, nh, nkv, has_kv, status);
+        VCB_CHECK_LAUNCH("qknorm_rope_kvwrite");
+        return 0;
+    }
     const long long warps = (long long)T * (nh + (has_kv ? 2 * nkv : 0));
     const int wpb = 4;
     const long long blocks = (warps + wpb - 1) / wpb;

@@ -124,6 +124,7 @@ struct GemmArgs {
     long long split_stride;   // elements between the partials of consecutive k-slices
     int kb_per_split;         // 64-wide k-blocks per slice
     int splits;               // k-slices
+    int swiglu_rows;          // 0, or I: W is [gate (I rows); up (I rows)] and the output is silu(gate) * up, [tokens, I]
     int* status;
 };
 
@@ -167,7 +168,8 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_kb = (g.K + BK - 1) / BK;
-    const int m_tiles = (g.M + BM * MT - 1) / (BM * MT);
+    const int unit_rows = g.swiglu_rows ? BM : BM * MT;   // output features per unit
+    const int m_tiles = (g.M + unit_rows - 1) / unit_rows;
     const int n_tiles = (g.N + BN - 1) / BN;
     const int units = m_tiles * n_tiles * g.splits;
 
@@ -199,7 +201,7 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
         z = u / (m_tiles * n_tiles);
         const int rem = u % (m_tiles * n_tiles);
         n0 = (rem / m_tiles) * BN;
-        m0 = (rem % m_tiles) * (BM * MT);
+        m0 = (rem % m_tiles) * unit_rows;
         kb0 = z * g.kb_per_split;
         nkb = min(total_kb, kb0 + g.kb_per_split) - kb0;
     };
@@ -220,7 +222,8 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
                     const uint32_t a_dst = base + s * L::STAGE_BYTES;
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt)
-                        tma_load_2d(a_dst + mt * L::A_BYTES, &map_w, full_bar(s), (kb0 + i) * BK, m0 + mt * BM);
+                        tma_load_2d(a_dst + mt * L::A_BYTES, &map_w, full_bar(s), (kb0 + i) * BK,
+                                    m0 + mt * (g.swiglu_rows ? g.swiglu_rows : BM));
                     tma_load_2d(a_dst + MT * L::A_BYTES, &map_x, full_bar(s), (kb0 + i) * BK, n0);
                     armed = it + 1;
                 }
@@ -279,6 +282,28 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
             tc_fence_after();
             const uint32_t tmem_d = tmem_base + a * (MT * ACC_COLS);
             const size_t zoff = (size_t)z * g.split_stride;
+            if (MT == 2 && g.swiglu_rows) {
+                // accumulator 0 holds the gate rows, accumulator 1 the up rows of the same 128 features
+                const int m = m0 + q * 32 + lane;
+                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    if (n0 + c0 >= g.N) break;   // uniform over the warp
+                    uint32_t vg[16], vu[16];
+                    tc_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, vg);
+                    tc_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(ACC_COLS + c0), vu);
+                    tc_wait_ld();
+                    if (m < g.M) {
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj) {
+                            if (n0 + c0 + jj < g.N) {
+                                const float gv = __uint_as_float(vg[jj]), uv = __uint_as_float(vu[jj]);
+                                o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
+                            }
+                        }
+                    }
+                }
+            } else
 #pragma unroll 1
             for (int cc = 0; cc < MT * BN; cc += 16) {
                 const int mt = cc / BN, c0 = cc % BN;
@@ -396,10 +421,11 @@ int num_sms() {
 }
 
 template <int BN, int STAGES, int MT, int ACC>
-int launch(const void* W, const void* X, const GemmArgs& g, long long ldw, long long ldx, int splits, cudaStream_t stream) {
+int launch_maps(const void* W, long long w_rows, const void* X, const GemmArgs& g, long long ldw, long long ldx, int splits,
+                cudaStream_t stream) {
     using L = Smem<BN, STAGES, MT, ACC>;
     CUtensorMap mw, mx;
-    if (!tensor_map(W, g.M, g.K, ldw, BM, &mw) || !tensor_map(X, g.N, g.K, ldx, BN, &mx)) return -3;
+    if (!tensor_map(W, w_rows, g.K, ldw, BM, &mw) || !tensor_map(X, g.N, g.K, ldx, BN, &mx)) return -3;
     auto kern = gemm_bf16_tn_kernel<BN, STAGES, MT, ACC>;
     static bool opted = false;
     if (!opted) {
@@ -410,11 +436,17 @@ int launch(const void* W, const void* X, const GemmArgs& g, long long ldw, long 
         }
         opted = true;
     }
-    const long long units = (long long)((g.M + BM * MT - 1) / (BM * MT)) * ((g.N + BN - 1) / BN) * splits;
+    const int unit_rows = g.swiglu_rows ? BM : BM * MT;
+    const long long units = (long long)((g.M + unit_rows - 1) / unit_rows) * ((g.N + BN - 1) / BN) * splits;
     const int grid = (int)(units < num_sms() ? units : num_sms());
     kern<<<grid, NTHREADS, L::TOTAL, stream>>>(mw, mx, g);
     VCB_CHECK_LAUNCH("gemm_bf16_tn");
     return 0;
+}
+
+template <int BN, int STAGES, int MT, int ACC>
+int launch(const void* W, const void* X, const GemmArgs& g, long long ldw, long long ldx, int splits, cudaStream_t stream) {
+    return launch_maps<BN, STAGES, MT, ACC>(W, g.M, X, g, ldw, ldx, splits, stream);
 }
 
 }  // namespace
@@ -429,6 +461,20 @@ VCB_API int vcb_gemm_effective_splits(int K, int splits) {
     return (total_kb + kb_per_split - 1) / kb_per_split;
 }
 
+// Fused feed-forward front half: W = [gate (I rows); up (I rows)] x [K]; out[t][i] = silu(gate_i . x_t) * (up_i . x_t),
+// bfloat16 [N, I].  The gate tile and the up tile of the same 128 features are the two accumulators of one unit.
+VCB_API int vcb_gemm_bf16_swiglu(const void* W, const void* X, void* out, int I, int N, int K, long long ldw,
+                                 long long ldx, long long ldc, int* status, cudaStream_t stream) {
+    VCB_CHECK_ARG(I > 0 && N > 0 && K > 0, "gemm_bf16_swiglu: bad sizes I=%d N=%d K=%d", I, N, K);
+    VCB_CHECK_ARG(K % 8 == 0 && ldw % 8 == 0 && ldx % 8 == 0,
+                  "gemm_bf16_swiglu: inner size %d and row strides %lld, %lld must be multiples of 8 (16-byte rows for TMA)", K, ldw, ldx);
+    VCB_CHECK_ARG(((uintptr_t)W % 16 == 0) && ((uintptr_t)X % 16 == 0), "gemm_bf16_swiglu: operands must be 16-byte aligned");
+    const int total_kb = (K + BK - 1) / BK;
+    GemmArgs g{out, VCB_BF16, I, N, K, ldc, 0, total_kb, 1, I, status};
+    // the weight map spans both halves so that the up tile is addressed as row I + m
+    return launch_maps<256, 3, 2, 1>(W, 2LL * I, X, g, ldw, ldx, 1, stream);
+}
+
 VCB_API int vcb_gemm_bf16_tn(const void* W, const void* X, void* out, int out_dtype, int M, int N, int K,
                              long long ldw, long long ldx, long long ldc, int splits, long long split_stride,
                              int* status, cudaStream_t stream) {
@@ -441,7 +487,7 @@ VCB_API int vcb_gemm_bf16_tn(const void* W, const void* X, void* out, int out_dt
     if (splits > total_kb) splits = total_kb;
     const int kb_per_split = (total_kb + splits - 1) / splits;
     splits = (total_kb + kb_per_split - 1) / kb_per_split;
-    GemmArgs g{out, out_dtype, M, N, K, ldc, split_stride, kb_per_split, splits, status};
+    GemmArgs g{out, out_dtype, M, N, K, ldc, split_stride, kb_per_split, splits, 0, status};
     int rc;
     if (N <= 16) rc = launch<16, 8, 1, 2>(W, X, g, ldw, ldx, splits, stream);
     else if (N <= 32) rc = launch<32, 8, 1, 2>(W, X, g, ldw, ldx, splits, stream);

@@ -58,6 +58,7 @@ def _declare(L):
         "vcb_qknorm_rope_kvwrite": [P, I, I, LL, I, P, P, I, I, F, P, I, P, P, P, P, LL, I, I, I, I, I, I, I, P, P],
         "vcb_gemm_bf16_tn": [P, P, P, I, I, I, I, LL, LL, LL, I, LL, P, P],
         "vcb_gemm_effective_splits": [I, I],
+        "vcb_gemm_bf16_swiglu": [P, P, P, I, I, I, LL, LL, LL, P, P],
         "vcb_sgemm_tn": [P, P, P, I, I, I, LL, LL, LL, P],
         "vcb_attn_paged": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, P],
         "vcb_scatter_i32": [P, P, P, P, I, LL, P],
@@ -206,6 +207,18 @@ def gemm_bf16_tn(w, x, out, splits, status):
         ldc, sstride = out.stride(1), out.stride(0)
     _call("vcb_gemm_bf16_tn", _p(w), _p(x), _p(out), _dt(out), M, T, K, w.stride(0), x.stride(0), ldc, S, sstride,
           _p(status), _stream())
+
+
+def gemm_bf16_swiglu(w_gate_up, x, out, status):
+    """out[t, i] = silu(gate_i . x_t) * (up_i . x_t) with w_gate_up = [gate (I rows); up (I rows)]: the product and
+    the SiLU-gate in one kernel (the two 128-feature tiles are the two accumulators of one unit)."""
+    _need(w_gate_up, "w_gate_up", torch.bfloat16); _need(x, "x", torch.bfloat16, contiguous=False)
+    _need(out, "out", torch.bfloat16)
+    I2, K = w_gate_up.shape
+    T = x.shape[0]
+    assert I2 % 2 == 0 and x.shape[1] == K and x.stride(1) == 1 and out.shape == (T, I2 // 2)
+    _call("vcb_gemm_bf16_swiglu", _p(w_gate_up), _p(x), _p(out), I2 // 2, T, K, w_gate_up.stride(0), x.stride(0),
+          out.stride(0), _p(status), _stream())
 
 
 def sgemm_tn(a, b, out):

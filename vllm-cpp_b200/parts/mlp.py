@@ -9,7 +9,9 @@ import torch
 from .. import ops
 from ..weights.loader import TensorSpec
 from .base import FeedForward
-from .linear import matmul_tn
+from .linear import LIBRARY_GEMM, matmul_tn
+
+FUSE_ABOVE_TOKENS = 128   # below this the product is cut into k-slices, whose sums must exist before the SiLU
 
 
 class SwiGLUMLP(FeedForward):
@@ -34,7 +36,11 @@ class SwiGLUMLP(FeedForward):
         self.w_down = store.matrix(p + "down_proj.weight")
 
     def forward(self, x, ctx):
-        gate_up = matmul_tn(x, self.w_gate_up, ctx.status, allow_partials=True)
         act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        ops.swiglu(gate_up, act)
+        if x.dtype == torch.bfloat16 and x.shape[0] > FUSE_ABOVE_TOKENS and not LIBRARY_GEMM and self.hidden % 8 == 0:
+            # many tokens: no k-slices are needed, so the SiLU-gate runs in the product's epilogue
+            ops.gemm_bf16_swiglu(self.w_gate_up, x, act, ctx.status)
+        else:
+            gate_up = matmul_tn(x, self.w_gate_up, ctx.status, allow_partials=True)
+            ops.swiglu(gate_up, act)
         return matmul_tn(act, self.w_down, ctx.status, out_dtype=torch.float32, allow_partials=True)
