@@ -115,3 +115,22 @@ def test_command_line(model_dirs, plain_models):
     assert r.returncode == 0, r.stderr[-3000:]
     got = [int(t) for t in r.stdout.strip().splitlines()[-1].split(",")]
     assert got == plain_generate(plain_models, "A", prompt, 5)
+
+
+def test_sizes_that_fit_no_fast_path(tmp_path, plain_models):
+    """Hidden size 100 (rows no multiple of 16 bytes), head_dim 48, 5 heads over 1 KV head, odd vocabulary:
+    both precisions still run, through the plain kernels where the tensor-core ones cannot."""
+    import plain_qwen3
+    from vllm_cpp_b200 import LLM, EngineConfig, Qwen3Config, write_random_model
+    cfg = Qwen3Config(vocab_size=211, hidden_size=100, intermediate_size=108, num_hidden_layers=2, num_attention_heads=5,
+                      num_key_value_heads=1, head_dim=48, max_position_embeddings=96, rms_norm_eps=1e-5, rope_theta=5e4,
+                      tie_word_embeddings=False)
+    d = write_random_model(cfg, 9, tmp_path / "odd")
+    pc, pw = plain_qwen3.read_model(d)
+    prompts = [random_tokens(211, n, 90 + n) for n in (3, 20, 41)]
+    want = [plain_qwen3.generate(pc, pw, p, 10) for p in prompts]
+    llm = LLM(d, engine=EngineConfig(dtype="float32", page_size=8, max_tokens=512, max_num_seqs=4, max_step_tokens=16))
+    assert llm.generate(prompts, 10, 0.0, 1.0, repeat_penalty=1.0) == want
+    llm = LLM(d, engine=EngineConfig(dtype="bfloat16", page_size=8, max_tokens=512, max_num_seqs=4, max_step_tokens=16))
+    got = llm.generate(prompts, 10, 0.0, 1.0, repeat_penalty=1.0)
+    assert sum(a == b for g, w in zip(got, want) for a, b in zip(g, w)) >= 24

@@ -488,3 +488,15 @@ def test_qknorm_fast_path_matches_general_path():
     assert status.item() == 0
     torch.testing.assert_close(res[0][0], res[1][0], rtol=1e-2, atol=1e-2)
     torch.testing.assert_close(res[0][1], res[1][1], rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_bf16_product_of_unaligned_inner_size(out_dtype):
+    """An inner size that is no multiple of 8 cannot be addressed by TMA; the projection falls back to the plain kernel."""
+    from vllm_cpp_b200.parts.linear import matmul_tn
+    T, N, K = 5, 70, 100
+    x = torch.randn(T, K, device=dev()).to(torch.bfloat16)
+    w = torch.randn(N, K, device=dev()).to(torch.bfloat16)
+    y = matmul_tn(x, w, torch.zeros(1, dtype=torch.int32, device=dev()), out_dtype=out_dtype, allow_partials=True)
+    assert y.shape == (T, N) and y.dtype == out_dtype
+    torch.testing.assert_close(y.double(), x.double() @ w.double().T, rtol=1e-2, atol=1e-1)

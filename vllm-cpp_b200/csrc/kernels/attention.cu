@@ -256,6 +256,8 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
 template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   const int* __restrict__ dec_rows, T* __restrict__ out, int nh, int hd, int nslices) {
+    pdl_trigger();
+    pdl_wait();
     const int n = blockIdx.x, h = blockIdx.y;
     const size_t prow0 = ((size_t)n * nh + h) * nslices;
     float m = -CUDART_INF_F;
@@ -318,9 +320,9 @@ VCB_API int vcb_attn_merge(const float* part_o, const float* part_ml, const int*
     if (n_dec == 0) return 0;
     const int threads = hd <= 64 ? 64 : (hd <= 128 ? 128 : 256);
     if (dtype == VCB_F32)
-        attn_merge_kernel<float><<<dim3(n_dec, nh), threads, 0, stream>>>(part_o, part_ml, dec_rows, (float*)out, nh, hd, nslices);
+        launch_pdl(attn_merge_kernel<float>, dim3(n_dec, nh), dim3(threads), 0, stream, part_o, part_ml, dec_rows, (float*)out, nh, hd, nslices);
     else
-        attn_merge_kernel<__nv_bfloat16><<<dim3(n_dec, nh), threads, 0, stream>>>(part_o, part_ml, dec_rows, (__nv_bfloat16*)out, nh, hd, nslices);
+        launch_pdl(attn_merge_kernel<__nv_bfloat16>, dim3(n_dec, nh), dim3(threads), 0, stream, part_o, part_ml, dec_rows, (__nv_bfloat16*)out, nh, hd, nslices);
     VCB_CHECK_LAUNCH("attn_merge");
     return 0;
 }
@@ -399,9 +401,9 @@ VCB_API int vcb_attn_decode_no_alloc(const void* q, void* out, int dtype, const 
     if (rc) return rc;
     const int threads = hd <= 64 ? 64 : (hd <= 128 ? 128 : 256);
     if (dtype == VCB_F32)
-        attn_merge_kernel<float><<<dim3(n_dec, nh), threads, 0, stream>>>(part_o, part_ml, dec_rows, (float*)out, nh, hd, nslices);
+        launch_pdl(attn_merge_kernel<float>, dim3(n_dec, nh), dim3(threads), 0, stream, part_o, part_ml, dec_rows, (float*)out, nh, hd, nslices);
     else
-        attn_merge_kernel<__nv_bfloat16><<<dim3(n_dec, nh), threads, 0, stream>>>(part_o, part_ml, dec_rows, (__nv_bfloat16*)out, nh, hd, nslices);
+        launch_pdl(attn_merge_kernel<__nv_bfloat16>, dim3(n_dec, nh), dim3(threads), 0, stream, part_o, part_ml, dec_rows, (__nv_bfloat16*)out, nh, hd, nslices);
     VCB_CHECK_LAUNCH("attn_decode_no_alloc merge");
     return 0;
 }

@@ -153,6 +153,8 @@ __global__ __launch_bounds__(TMA ? NT + 32 : NT) void attn_mma_kernel(const __gr
     auto empty_bar = [&](int st) { return smem_u32(bar_s) + 8u * (STAGES + st); };
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_s + 16 * STAGES);
 
+    pdl_trigger();
+    pdl_wait();   // the queries and the newest keys come from the kernel before this one
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wr = (warp & 3) / WK, wk = (warp & 3) % WK;
     const int* item = a.items + (size_t)blockIdx.x * ITEM_INTS;
@@ -573,7 +575,7 @@ int launch(const AttnArgs& a, int n_items, cudaStream_t stream) {
         }
         opted = true;
     }
-    kern<<<dim3(n_items, a.nkv * hchunks), TMA ? NT + 32 : NT, smem, stream>>>(map, a);
+    launch_pdl(kern, dim3(n_items, a.nkv * hchunks), dim3(TMA ? NT + 32 : NT), smem, stream, map, a);
     VCB_CHECK_LAUNCH("attn_mma");
     return 0;
 }

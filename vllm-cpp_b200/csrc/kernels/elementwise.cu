@@ -10,6 +10,7 @@
 #include "common.cuh"
 
 #include <stdarg.h>
+#include <stdlib.h>
 
 // ---------------------------------------------------------------------------
 // error text shared by all launchers of the library
@@ -25,11 +26,23 @@ void vcb_set_error(const char* fmt, ...) {
 
 VCB_API const char* vcb_last_error() { return g_last_error; }
 
+// VLLM_CPP_B200_PDL=0 turns programmatic dependent launch off (every kernel then waits for the one before it)
+bool vcb_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("VLLM_CPP_B200_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
 // ---------------------------------------------------------------------------
 // embedding gather: out[t,:] = table[ids[t],:] widened to 32-bit
 // ---------------------------------------------------------------------------
 __global__ void embed_gather_kernel(const void* __restrict__ table, int table_dtype, const int* __restrict__ ids,
                                     float* __restrict__ out, int H, int V, int* status) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < V;
@@ -43,7 +56,7 @@ VCB_API int vcb_embed_gather(const void* table, int table_dtype, const int* ids,
                              int* status, cudaStream_t stream) {
     if (T == 0) return 0;
     VCB_CHECK_ARG(T > 0 && H > 0 && V > 0, "embed_gather: bad sizes T=%d H=%d V=%d", T, H, V);
-    embed_gather_kernel<<<T, 256, 0, stream>>>(table, table_dtype, ids, out, H, V, status);
+    launch_pdl(embed_gather_kernel, dim3(T), dim3(256), 0, stream, table, table_dtype, ids, out, H, V, status);
     VCB_CHECK_LAUNCH("embed_gather");
     return 0;
 }
@@ -84,6 +97,8 @@ __global__ __launch_bounds__(1024) void add_rmsnorm_vec_kernel(float* __restrict
                                                                int w_dtype, float eps, __nv_bfloat16* __restrict__ out,
                                                                const int* __restrict__ rows, int H) {
     __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x;
     const size_t r = rows ? (size_t)rows[i] : (size_t)i;
     const bool write_back = rows == nullptr && S > 0;
@@ -153,9 +168,9 @@ VCB_API int vcb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, in
         const int vpt = (H4 + threads - 1) / threads;
         const float* d = (const float*)delta;
         __nv_bfloat16* o = (__nv_bfloat16*)out;
-        if (vpt == 1) add_rmsnorm_vec_kernel<1><<<n_out, threads, 0, stream>>>(resid, d, S, (size_t)delta_stride, w, w_dtype, eps, o, rows, H);
-        else if (vpt == 2) add_rmsnorm_vec_kernel<2><<<n_out, threads, 0, stream>>>(resid, d, S, (size_t)delta_stride, w, w_dtype, eps, o, rows, H);
-        else add_rmsnorm_vec_kernel<4><<<n_out, threads, 0, stream>>>(resid, d, S, (size_t)delta_stride, w, w_dtype, eps, o, rows, H);
+        if (vpt == 1) launch_pdl(add_rmsnorm_vec_kernel<1>, dim3(n_out), dim3(threads), 0, stream, resid, d, S, (size_t)delta_stride, w, w_dtype, eps, o, rows, H);
+        else if (vpt == 2) launch_pdl(add_rmsnorm_vec_kernel<2>, dim3(n_out), dim3(threads), 0, stream, resid, d, S, (size_t)delta_stride, w, w_dtype, eps, o, rows, H);
+        else launch_pdl(add_rmsnorm_vec_kernel<4>, dim3(n_out), dim3(threads), 0, stream, resid, d, S, (size_t)delta_stride, w, w_dtype, eps, o, rows, H);
         VCB_CHECK_LAUNCH("add_rmsnorm");
         return 0;
     }
@@ -171,6 +186,8 @@ VCB_API int vcb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, in
 // ---------------------------------------------------------------------------
 template <typename TIN, typename T>
 __global__ void swiglu_kernel(const TIN* __restrict__ gu, int S, size_t s_stride, T* __restrict__ out, int I, size_t total) {
+    pdl_trigger();
+    pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I, i = idx % I;
         float g = 0.f, u = 0.f;
@@ -217,11 +234,11 @@ VCB_API int vcb_swiglu(const void* gate_up, int in_dtype, int S, long long s_str
     }
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     if (in_dtype == VCB_F32 && out_dtype == VCB_F32)
-        swiglu_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)gate_up, S, (size_t)s_stride, (float*)out, I, total);
+        launch_pdl(swiglu_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, S, (size_t)s_stride, (float*)out, I, total);
     else if (in_dtype == VCB_F32)
-        swiglu_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float*)gate_up, S, (size_t)s_stride, (__nv_bfloat16*)out, I, total);
+        launch_pdl(swiglu_kernel<float, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, S, (size_t)s_stride, (__nv_bfloat16*)out, I, total);
     else if (out_dtype == VCB_BF16)
-        swiglu_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, S, (size_t)s_stride, (__nv_bfloat16*)out, I, total);
+        launch_pdl(swiglu_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up, S, (size_t)s_stride, (__nv_bfloat16*)out, I, total);
     else { vcb_set_error("swiglu: bfloat16 input with 32-bit output is not a combination the engine uses"); return -1; }
     VCB_CHECK_LAUNCH("swiglu");
     return 0;
@@ -242,6 +259,8 @@ __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, s
                                            T* __restrict__ q_out, T* __restrict__ pages, long long page_stride,
                                            int page_size, int num_pages, int nh, int nkv, int hd, int n_tokens,
                                            int has_kv, int* status) {
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int heads_total = nh + (has_kv ? 2 * nkv : 0);
     const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -403,7 +422,7 @@ VCB_API int vcb_qknorm_rope_kvwrite(const void* qkv, int in_dtype, int S, long l
     const long long blocks = (warps + wpb - 1) / wpb;
     VCB_CHECK_ARG(blocks < (1ll << 31), "qknorm_rope_kvwrite: too many blocks");
 #define VCB_QK_LAUNCH(TIN, TOUT)                                                                                      \
-    qknorm_rope_kvwrite_kernel<TIN, TOUT><<<(unsigned)blocks, wpb * 32, 0, stream>>>(                                  \
+    launch_pdl(qknorm_rope_kvwrite_kernel<TIN, TOUT>, dim3((unsigned)blocks), dim3(wpb * 32), 0, stream,                 \
         (const TIN*)qkv, S, (size_t)s_stride, qw, kw, w_dtype, use_norm, eps, cos_sin, max_pos, positions, slot_map,   \
         (TOUT*)q_out, (TOUT*)pages, page_stride, page_size, num_pages, nh, nkv, hd, T, has_kv, status)
     if (in_dtype == VCB_F32 && out_dtype == VCB_F32) VCB_QK_LAUNCH(float, float);
@@ -420,6 +439,8 @@ VCB_API int vcb_qknorm_rope_kvwrite(const void* qkv, int in_dtype, int S, long l
 // ---------------------------------------------------------------------------
 __global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict__ idx, const int* __restrict__ val,
                                    const int* __restrict__ count, int capacity, long long dst_size) {
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const int n = min(*count, capacity);
     if (i < n && idx[i] >= 0 && idx[i] < dst_size) dst[idx[i]] = val[i];
@@ -429,7 +450,7 @@ __global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict_
 VCB_API int vcb_scatter_i32(int* dst, const int* idx, const int* val, const int* count, int capacity,
                             long long dst_size, cudaStream_t stream) {
     if (capacity == 0) return 0;
-    scatter_i32_kernel<<<(capacity + 255) / 256, 256, 0, stream>>>(dst, idx, val, count, capacity, dst_size);
+    launch_pdl(scatter_i32_kernel, dim3((capacity + 255) / 256), dim3(256), 0, stream, dst, idx, val, count, capacity, dst_size);
     VCB_CHECK_LAUNCH("scatter_i32");
     return 0;
 }

@@ -166,6 +166,7 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(gen + L::BAR_OFFSET + L::NUM_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::BAR_OFFSET + L::NUM_BARS * 8 + 8);
 
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_kb = (g.K + BK - 1) / BK;
     const int unit_rows = g.swiglu_rows ? BM : BM * MT;   // output features per unit
@@ -211,15 +212,40 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
         if (lane == 0) {
             int it = 0, armed = 0;
             bool ok = true;
+            // The weights are written by no kernel of the step, so the first ring of weight tiles is requested
+            // before waiting for the kernel that produces the activations: the weight stream is already in
+            // flight while that kernel drains.  The activation tiles of those stages follow after the wait.
+            int early = 0;
+            {
+                int m0, n0, kb0, nkb, z;
+                if ((int)blockIdx.x < units) {
+                    unit_at(blockIdx.x, m0, n0, kb0, nkb, z);
+                    early = min(nkb, STAGES);
+                    for (int i = 0; i < early; ++i) {
+                        mbar_expect_tx(full_bar(i), L::STAGE_BYTES);
+                        const uint32_t a_dst = base + i * L::STAGE_BYTES;
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt)
+                            tma_load_2d(a_dst + mt * L::A_BYTES, &map_w, full_bar(i), (kb0 + i) * BK,
+                                        m0 + mt * (g.swiglu_rows ? g.swiglu_rows : BM));
+                    }
+                    armed = early;
+                }
+            }
+            pdl_wait();
             for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
                 int m0, n0, kb0, nkb, z;
                 unit_at(u, m0, n0, kb0, nkb, z);
                 for (int i = 0; i < nkb; ++i, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
+                    const uint32_t a_dst = base + s * L::STAGE_BYTES;
+                    if (it < early) {   // its weight tiles are already on their way
+                        tma_load_2d(a_dst + MT * L::A_BYTES, &map_x, full_bar(s), (kb0 + i) * BK, n0);
+                        continue;
+                    }
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, g.status)) { ok = false; break; }
                     mbar_expect_tx(full_bar(s), L::STAGE_BYTES);
-                    const uint32_t a_dst = base + s * L::STAGE_BYTES;
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt)
                         tma_load_2d(a_dst + mt * L::A_BYTES, &map_w, full_bar(s), (kb0 + i) * BK,
@@ -439,7 +465,7 @@ int launch_maps(const void* W, long long w_rows, const void* X, const GemmArgs& 
     const int unit_rows = g.swiglu_rows ? BM : BM * MT;
     const long long units = (long long)((g.M + unit_rows - 1) / unit_rows) * ((g.N + BN - 1) / BN) * splits;
     const int grid = (int)(units < num_sms() ? units : num_sms());
-    kern<<<grid, NTHREADS, L::TOTAL, stream>>>(mw, mx, g);
+    launch_pdl(kern, dim3(grid), dim3(NTHREADS), L::TOTAL, stream, mw, mx, g);
     VCB_CHECK_LAUNCH("gemm_bf16_tn");
     return 0;
 }

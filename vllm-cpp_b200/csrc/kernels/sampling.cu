@@ -167,6 +167,8 @@ __global__ __launch_bounds__(512) void sample_part_kernel(const float* __restric
                                                           int* __restrict__ part_i) {
     __shared__ float sv[33];
     __shared__ int si[33];
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x, nb = gridDim.y, b = blockIdx.y;
     const RowParams p = params[row];
     const float* lg = logits + (size_t)row * row_stride;
@@ -192,6 +194,8 @@ __global__ __launch_bounds__(512) void sample_part_kernel(const float* __restric
 
 __global__ void sample_pick_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int nb,
                                    int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x;
     float best = -CUDART_INF_F;
     int best_i = 0x7fffffff;
@@ -244,10 +248,10 @@ VCB_API int vcb_sample_split(const float* logits, long long row_stride, int n_ro
                              cudaStream_t stream) {
     if (n_rows == 0) return 0;
     VCB_CHECK_ARG(n_rows > 0 && V > 0 && row_stride >= V && nb >= 1 && nb <= 1024, "sample_split: bad sizes");
-    sample_part_kernel<<<dim3(n_rows, nb), 512, 0, stream>>>(logits, row_stride, V, (const RowParams*)params,
-                                                             counts_table, part_v, part_i);
+    launch_pdl(sample_part_kernel, dim3(n_rows, nb), dim3(512), 0, stream, logits, row_stride, V, (const RowParams*)params,
+               counts_table, part_v, part_i);
     VCB_CHECK_LAUNCH("sample_part");
-    sample_pick_kernel<<<n_rows, 32, 0, stream>>>(part_v, part_i, nb, out);
+    launch_pdl(sample_pick_kernel, dim3(n_rows), dim3(32), 0, stream, part_v, part_i, nb, out);
     VCB_CHECK_LAUNCH("sample_pick");
     return 0;
 }

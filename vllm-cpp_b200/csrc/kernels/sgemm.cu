@@ -9,8 +9,9 @@
 namespace {
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
-__global__ __launch_bounds__(256) void sgemm_tn_kernel(const float* __restrict__ A, const float* __restrict__ B,
-                                                       float* __restrict__ C, int M, int N, int K, long long lda,
+template <typename TI, typename TO>
+__global__ __launch_bounds__(256) void sgemm_tn_kernel(const TI* __restrict__ A, const TI* __restrict__ B,
+                                                       TO* __restrict__ C, int M, int N, int K, long long lda,
                                                        long long ldb, long long ldc, int vec_ok) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Bs[BK][BN + 4];
@@ -28,23 +29,23 @@ __global__ __launch_bounds__(256) void sgemm_tn_kernel(const float* __restrict__
         float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
         const int k = k0 + lk;
         if (m0 + lr < M) {
-            const float* p = A + (long long)(m0 + lr) * lda + k;
-            if (vec_ok && k + 3 < K) {
+            const TI* p = A + (long long)(m0 + lr) * lda + k;
+            if (sizeof(TI) == 4 && vec_ok && k + 3 < K) {
                 const float4 v = *reinterpret_cast<const float4*>(p);
                 a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w;
             } else {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) if (k + i < K) a[i] = p[i];
+                for (int i = 0; i < 4; ++i) if (k + i < K) a[i] = to_f32(p[i]);
             }
         }
         if (n0 + lr < N) {
-            const float* p = B + (long long)(n0 + lr) * ldb + k;
-            if (vec_ok && k + 3 < K) {
+            const TI* p = B + (long long)(n0 + lr) * ldb + k;
+            if (sizeof(TI) == 4 && vec_ok && k + 3 < K) {
                 const float4 v = *reinterpret_cast<const float4*>(p);
                 b[0] = v.x; b[1] = v.y; b[2] = v.z; b[3] = v.w;
             } else {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) if (k + i < K) b[i] = p[i];
+                for (int i = 0; i < 4; ++i) if (k + i < K) b[i] = to_f32(p[i]);
             }
         }
 #pragma unroll
@@ -73,7 +74,7 @@ __global__ __launch_bounds__(256) void sgemm_tn_kernel(const float* __restrict__
 #pragma unroll
         for (int j = 0; j < TN; ++j) {
             const int n = n0 + tx * TN + j;
-            if (n < N) C[(long long)m * ldc + n] = acc[i][j];
+            if (n < N) C[(long long)m * ldc + n] = from_f32<TO>(acc[i][j]);
         }
     }
 }
@@ -87,7 +88,24 @@ VCB_API int vcb_sgemm_tn(const float* A, const float* B, float* C, int M, int N,
     const int gy = (M + BM - 1) / BM, gx = (N + BN - 1) / BN;
     VCB_CHECK_ARG(gy <= 65535, "sgemm_tn: M=%d exceeds %d rows per launch", M, 65535 * BM);
     const int vec_ok = (lda % 4 == 0) && (ldb % 4 == 0) && ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0);
-    sgemm_tn_kernel<<<dim3(gx, gy), 256, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc, vec_ok);
+    sgemm_tn_kernel<float, float><<<dim3(gx, gy), 256, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc, vec_ok);
     VCB_CHECK_LAUNCH("sgemm_tn");
+    return 0;
+}
+
+// The same loop for bfloat16 operands whose rows are not 16-byte multiples (which the TMA kernel cannot
+// address): bfloat16 in, 32-bit accumulation in k order, bfloat16 or 32-bit out.  Slow; exists so that no
+// configuration is refused.
+VCB_API int vcb_gemm_bf16_plain(const void* A, const void* B, void* C, int out_dtype, int M, int N, int K, long long lda,
+                                long long ldb, long long ldc, cudaStream_t stream) {
+    if (M == 0 || N == 0) return 0;
+    VCB_CHECK_ARG(M > 0 && N > 0 && K > 0, "gemm_bf16_plain: bad sizes M=%d N=%d K=%d", M, N, K);
+    const int gy = (M + BM - 1) / BM, gx = (N + BN - 1) / BN;
+    VCB_CHECK_ARG(gy <= 65535, "gemm_bf16_plain: M=%d exceeds %d rows per launch", M, 65535 * BM);
+    if (out_dtype == VCB_F32)
+        sgemm_tn_kernel<__nv_bfloat16, float><<<dim3(gx, gy), 256, 0, stream>>>((const __nv_bfloat16*)A, (const __nv_bfloat16*)B, (float*)C, M, N, K, lda, ldb, ldc, 0);
+    else
+        sgemm_tn_kernel<__nv_bfloat16, __nv_bfloat16><<<dim3(gx, gy), 256, 0, stream>>>((const __nv_bfloat16*)A, (const __nv_bfloat16*)B, (__nv_bfloat16*)C, M, N, K, lda, ldb, ldc, 0);
+    VCB_CHECK_LAUNCH("gemm_bf16_plain");
     return 0;
 }

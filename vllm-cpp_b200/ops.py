@@ -60,6 +60,7 @@ def _declare(L):
         "vcb_gemm_effective_splits": [I, I],
         "vcb_gemm_bf16_swiglu": [P, P, P, I, I, I, LL, LL, LL, P, P],
         "vcb_sgemm_tn": [P, P, P, I, I, I, LL, LL, LL, P],
+        "vcb_gemm_bf16_plain": [P, P, P, I, I, I, I, LL, LL, LL, P],
         "vcb_attn_paged": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, P],
         "vcb_scatter_i32": [P, P, P, P, I, LL, P],
         "vcb_attn_mma": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, I, P],
@@ -185,6 +186,22 @@ def qknorm_rope_kvwrite(qkv, q_weight, k_weight, eps, cos_sin, positions, slot_m
     _call("vcb_qknorm_rope_kvwrite", _p(qkv), _dt(qkv), S, stride, _dt(q_out), _p(q_weight), _p(k_weight), wdt,
           int(use_norm), float(eps), _p(cos_sin), cos_sin.shape[0], _p(positions), _p(slot_map), _p(q_out), _p(pages),
           page_stride, max(page_size, 1), num_pages, nh, nkv, hd, T, int(has_kv), _p(status), _stream())
+
+
+def gemm_bf16_plain(x, w, out):
+    """out[T,N] = x[T,K] . w[N,K]^T for bfloat16 operands of any inner size (no TMA alignment needed)."""
+    _need(x, "x", torch.bfloat16, contiguous=False); _need(w, "w", torch.bfloat16, contiguous=False); _need(out, "out")
+    T, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (T, N) and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _call("vcb_gemm_bf16_plain", _p(x), _p(w), _p(out), _dt(out), T, N, K, x.stride(0), w.stride(0), out.stride(0), _stream())
+
+
+def gemm_tma_ok(x, w) -> bool:
+    """Whether the tcgen05/TMA product can address these operands (16-byte rows and bases)."""
+    K = x.shape[1]
+    return (K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0)
 
 
 def gemm_effective_splits(K: int, splits: int) -> int:

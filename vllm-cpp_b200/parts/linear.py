@@ -68,6 +68,11 @@ def matmul_tn(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor | None = No
     if LIBRARY_GEMM:
         return torch.mm(x, w.t(), out_dtype=torch.float32) if out_dtype == torch.float32 else torch.mm(x, w.t())
     K = x.shape[1]
+    if not ops.gemm_tma_ok(x, w):
+        # rows that are not 16-byte multiples (an inner size like 100): the plain kernel takes them
+        out = torch.empty((T, N), dtype=out_dtype, device=x.device)
+        ops.gemm_bf16_plain(x, w, out)
+        return out
     splits = choose_splits(N, T, K) if allow_partials else 1
     splits = ops.gemm_effective_splits(K, splits)
     if splits > 1:

@@ -37,7 +37,7 @@ class SwiGLUMLP(FeedForward):
 
     def forward(self, x, ctx):
         act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        if x.dtype == torch.bfloat16 and x.shape[0] > FUSE_ABOVE_TOKENS and not LIBRARY_GEMM and self.hidden % 8 == 0:
+        if x.dtype == torch.bfloat16 and x.shape[0] > FUSE_ABOVE_TOKENS and not LIBRARY_GEMM and ops.gemm_tma_ok(x, self.w_gate_up):
             # many tokens: no k-slices are needed, so the SiLU-gate runs in the product's epilogue
             ops.gemm_bf16_swiglu(self.w_gate_up, x, act, ctx.status)
         else:
