@@ -12,7 +12,7 @@
 //  * Q.K^T and P.V are mma.sync m16n8k16 products (bf16 in, f32 accumulate) fed by
 //    ldmatrix from a 16-byte XOR-swizzled layout;
 //  * the four warps either take four different row groups and all keys of a tile
-//    (prompt portions: 64 rows a block) or the same 16 rows and a quarter of the
+//    (prompt portions: 128 rows a block, two 16-row tiles a warp) or the same 16 rows and a quarter of the
 //    tile's keys each (single decoded tokens: few rows, long key ranges), their
 //    partial softmax states merged through shared memory at the end.
 // Rows beyond the item's real rows and keys beyond the slice are zero-filled and
@@ -128,11 +128,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 }
 
 // WR row groups x WK key groups = 4 multiplying warps; TMA adds a fifth warp that only issues tile loads.
-template <int HD, int WR, int WK, bool TMA>
+template <int HD, int WR, int WK, int MR, bool TMA>
 __global__ __launch_bounds__(TMA ? NT + 32 : NT) void attn_mma_kernel(const __grid_constant__ CUtensorMap kv_map,
                                                                         AttnArgs a) {
     static_assert(WR * WK == 4 && HD % 64 == 0, "layout");
-    constexpr int RMAX = 16 * WR;   // rows a block holds
+    constexpr int RMAX = 16 * WR * MR;   // rows a block holds: WR warp groups x MR tiles of 16 rows each
     constexpr int CH = HD / 8;      // 16-byte chunks per row
     constexpr int ROWB = HD * 2;
     constexpr int KW = BN / WK;     // keys of a tile that one warp multiplies
@@ -278,21 +278,31 @@ __global__ __launch_bounds__(TMA ? NT + 32 : NT) void attn_mma_kernel(const __gr
         }
     }
 
-    float o[ND][4];
+    float o[MR][ND][4];
+    float m_run[MR][2], l_run[MR][2];   // rows lane/4 and lane/4 + 8 of each of this warp's 16-row tiles
+    int r_a[MR], pos_a[MR], pos_b[MR];
+    bool ok_a[MR], ok_b[MR];
 #pragma unroll
-    for (int i = 0; i < ND; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F};   // rows lane/4 and lane/4 + 8 of this warp's group
-    float l_run[2] = {0.f, 0.f};                       // per-thread partial sums (reduced over the quad at the end)
-    const int r_a = wr * 16 + (lane >> 2), r_b = r_a + 8;
-    const int pos_a = pos0 + r_a / gq, pos_b = pos0 + r_b / gq;
-    const bool ok_a = r_a < R, ok_b = r_b < R;
+    for (int mr = 0; mr < MR; ++mr) {
+#pragma unroll
+        for (int i = 0; i < ND; ++i) o[mr][i][0] = o[mr][i][1] = o[mr][i][2] = o[mr][i][3] = 0.f;
+        m_run[mr][0] = m_run[mr][1] = -CUDART_INF_F;
+        l_run[mr][0] = l_run[mr][1] = 0.f;   // per-thread partial sums (reduced over the quad at the end)
+        r_a[mr] = (wr * MR + mr) * 16 + (lane >> 2);
+        pos_a[mr] = pos0 + r_a[mr] / gq;
+        pos_b[mr] = pos0 + (r_a[mr] + 8) / gq;
+        ok_a[mr] = r_a[mr] < R;
+        ok_b[mr] = r_a[mr] + 8 < R;
+    }
 
     if (warp < 4) {
-        // ---- Q fragments stay in registers ----
-        uint32_t qf[HD / 16][4];
+        // ---- one 16-row tile per warp: its Q fragments stay in registers; two: they are re-read per key tile ----
+        uint32_t qf[MR == 1 ? HD / 16 : 1][4];
+        if (MR == 1) {
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks)
-            ldmatrix_x4(qf[ks], smem_u32(q_s + swz<RMAX>(wr * 16 + (lane & 15), ks * 2 + (lane >> 4))));
+            for (int ks = 0; ks < HD / 16; ++ks)
+                ldmatrix_x4(qf[MR == 1 ? ks : 0], smem_u32(q_s + swz<RMAX>(wr * 16 + (lane & 15), ks * 2 + (lane >> 4))));
+        }
 
         for (int it = 0; it < n_tiles; ++it) {
             const int st = it % STAGES;
@@ -323,97 +333,123 @@ __global__ __launch_bounds__(TMA ? NT + 32 : NT) void attn_mma_kernel(const __gr
             const int key0 = t0 + wk * KW;   // first key this warp multiplies
 
             // S = Q K^T
-            float s[NS][4];
+            float s[MR][NS][4];
 #pragma unroll
-            for (int i = 0; i < NS; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+            for (int mr = 0; mr < MR; ++mr)
+#pragma unroll
+                for (int i = 0; i < NS; ++i) s[mr][i][0] = s[mr][i][1] = s[mr][i][2] = s[mr][i][3] = 0.f;
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
+                uint32_t qk[MR][4];
+#pragma unroll
+                for (int mr = 0; mr < MR; ++mr) {
+                    if (MR == 1) {
+                        qk[mr][0] = qf[MR == 1 ? ks : 0][0]; qk[mr][1] = qf[MR == 1 ? ks : 0][1];
+                        qk[mr][2] = qf[MR == 1 ? ks : 0][2]; qk[mr][3] = qf[MR == 1 ? ks : 0][3];
+                    } else {
+                        ldmatrix_x4(qk[mr], smem_u32(q_s + swz<RMAX>((wr * MR + mr) * 16 + (lane & 15), ks * 2 + (lane >> 4))));
+                    }
+                }
 #pragma unroll
                 for (int np = 0; np < KW / 16; ++np) {
                     uint32_t b[4];
                     const int mi = lane >> 3;
                     const int krow = wk * KW + np * 16 + (mi >> 1) * 8 + (lane & 7);
                     ldmatrix_x4(b, smem_u32(kt + swz<BN>(krow, ks * 2 + (mi & 1))));
-                    mma_16816(s[2 * np], qf[ks], b[0], b[1]);
-                    mma_16816(s[2 * np + 1], qf[ks], b[2], b[3]);
+#pragma unroll
+                    for (int mr = 0; mr < MR; ++mr) {
+                        mma_16816(s[mr][2 * np], qk[mr], b[0], b[1]);
+                        mma_16816(s[mr][2 * np + 1], qk[mr], b[2], b[3]);
+                    }
                 }
             }
             // mask (only where the tile touches an edge of some row's key range), running maximum
             // rows beyond R hold zero queries and are never written, so they need no mask of their own
             const bool inner = key0 >= k_begin && key0 + KW <= k_end && key0 + KW - 1 <= pos0 && (W <= 0 || key0 > pos_last - W);
-            float mx_a = -CUDART_INF_F, mx_b = -CUDART_INF_F;
-            if (__all_sync(0xffffffffu, inner)) {
+            const bool all_inner = __all_sync(0xffffffffu, inner);
+            uint32_t pa[MR][KW / 16][4];
+#pragma unroll
+            for (int mr = 0; mr < MR; ++mr) {
+                float mx_a = -CUDART_INF_F, mx_b = -CUDART_INF_F;
+                if (all_inner) {
+#pragma unroll
+                    for (int i = 0; i < NS; ++i) {
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            s[mr][i][c] *= a.scale;
+                            s[mr][i][2 + c] *= a.scale;
+                            mx_a = fmaxf(mx_a, s[mr][i][c]);
+                            mx_b = fmaxf(mx_b, s[mr][i][2 + c]);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < NS; ++i) {
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            const int kidx = key0 + i * 8 + 2 * (lane & 3) + c;
+                            const bool in = kidx >= k_begin && kidx < k_end;
+                            const bool sa = ok_a[mr] && in && kidx <= pos_a[mr] && (W <= 0 || kidx > pos_a[mr] - W);
+                            const bool sb = ok_b[mr] && in && kidx <= pos_b[mr] && (W <= 0 || kidx > pos_b[mr] - W);
+                            s[mr][i][c] = sa ? s[mr][i][c] * a.scale : -CUDART_INF_F;
+                            s[mr][i][2 + c] = sb ? s[mr][i][2 + c] * a.scale : -CUDART_INF_F;
+                            mx_a = fmaxf(mx_a, s[mr][i][c]);
+                            mx_b = fmaxf(mx_b, s[mr][i][2 + c]);
+                        }
+                    }
+                }
+                mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+                mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+                mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+                mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+                const float mn_a = fmaxf(m_run[mr][0], mx_a), mn_b = fmaxf(m_run[mr][1], mx_b);
+                const float use_a = mn_a == -CUDART_INF_F ? 0.f : mn_a, use_b = mn_b == -CUDART_INF_F ? 0.f : mn_b;
+                const bool moved = mn_a != m_run[mr][0] || mn_b != m_run[mr][1];
+                const float al_a = exp2f((m_run[mr][0] - use_a) * LOG2E), al_b = exp2f((m_run[mr][1] - use_b) * LOG2E);
+                m_run[mr][0] = mn_a;
+                m_run[mr][1] = mn_b;
+                float sum_a = 0.f, sum_b = 0.f;
+                const float off_a = use_a * LOG2E, off_b = use_b * LOG2E;
 #pragma unroll
                 for (int i = 0; i < NS; ++i) {
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
-                        s[i][c] *= a.scale;
-                        s[i][2 + c] *= a.scale;
-                        mx_a = fmaxf(mx_a, s[i][c]);
-                        mx_b = fmaxf(mx_b, s[i][2 + c]);
+                        s[mr][i][c] = exp2f(fmaf(s[mr][i][c], LOG2E, -off_a));
+                        s[mr][i][2 + c] = exp2f(fmaf(s[mr][i][2 + c], LOG2E, -off_b));
+                        sum_a += s[mr][i][c];
+                        sum_b += s[mr][i][2 + c];
                     }
                 }
-            } else {
+                l_run[mr][0] = l_run[mr][0] * al_a + sum_a;
+                l_run[mr][1] = l_run[mr][1] * al_b + sum_b;
+                if (__any_sync(0xffffffffu, moved)) {   // the running maximum seldom moves after the first tiles
 #pragma unroll
-                for (int i = 0; i < NS; ++i) {
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        const int kidx = key0 + i * 8 + 2 * (lane & 3) + c;
-                        const bool in = kidx >= k_begin && kidx < k_end;
-                        const bool sa = ok_a && in && kidx <= pos_a && (W <= 0 || kidx > pos_a - W);
-                        const bool sb = ok_b && in && kidx <= pos_b && (W <= 0 || kidx > pos_b - W);
-                        s[i][c] = sa ? s[i][c] * a.scale : -CUDART_INF_F;
-                        s[i][2 + c] = sb ? s[i][2 + c] * a.scale : -CUDART_INF_F;
-                        mx_a = fmaxf(mx_a, s[i][c]);
-                        mx_b = fmaxf(mx_b, s[i][2 + c]);
+                    for (int i = 0; i < ND; ++i) {
+                        o[mr][i][0] *= al_a; o[mr][i][1] *= al_a; o[mr][i][2] *= al_b; o[mr][i][3] *= al_b;
                     }
                 }
-            }
-            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
-            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
-            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
-            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-            const float mn_a = fmaxf(m_run[0], mx_a), mn_b = fmaxf(m_run[1], mx_b);
-            const float use_a = mn_a == -CUDART_INF_F ? 0.f : mn_a, use_b = mn_b == -CUDART_INF_F ? 0.f : mn_b;
-            const bool moved = mn_a != m_run[0] || mn_b != m_run[1];
-            const float al_a = exp2f((m_run[0] - use_a) * LOG2E), al_b = exp2f((m_run[1] - use_b) * LOG2E);
-            m_run[0] = mn_a;
-            m_run[1] = mn_b;
-            float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
-            for (int i = 0; i < NS; ++i) {
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    s[i][c] = exp2f((s[i][c] - use_a) * LOG2E);
-                    s[i][2 + c] = exp2f((s[i][2 + c] - use_b) * LOG2E);
-                    sum_a += s[i][c];
-                    sum_b += s[i][2 + c];
-                }
-            }
-            l_run[0] = l_run[0] * al_a + sum_a;
-            l_run[1] = l_run[1] * al_b + sum_b;
-            if (__any_sync(0xffffffffu, moved)) {   // the running maximum seldom moves after the first tiles
-#pragma unroll
-                for (int i = 0; i < ND; ++i) {
-                    o[i][0] *= al_a; o[i][1] *= al_a; o[i][2] *= al_b; o[i][3] *= al_b;
+                for (int kk = 0; kk < KW / 16; ++kk) {
+                    pa[mr][kk][0] = pack_bf16(s[mr][2 * kk][0], s[mr][2 * kk][1]);
+                    pa[mr][kk][1] = pack_bf16(s[mr][2 * kk][2], s[mr][2 * kk][3]);
+                    pa[mr][kk][2] = pack_bf16(s[mr][2 * kk + 1][0], s[mr][2 * kk + 1][1]);
+                    pa[mr][kk][3] = pack_bf16(s[mr][2 * kk + 1][2], s[mr][2 * kk + 1][3]);
                 }
             }
             // O += P V
 #pragma unroll
             for (int kk = 0; kk < KW / 16; ++kk) {
-                uint32_t pa[4];
-                pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-                pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-                pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-                pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
                 for (int dp = 0; dp < HD / 16; ++dp) {
                     uint32_t b[4];
                     const int mi = lane >> 3;
                     const int vrow = wk * KW + kk * 16 + (mi & 1) * 8 + (lane & 7);
                     ldmatrix_x4_trans(b, smem_u32(vt + swz<BN>(vrow, dp * 2 + (mi >> 1))));
-                    mma_16816(o[2 * dp], pa, b[0], b[1]);
-                    mma_16816(o[2 * dp + 1], pa, b[2], b[3]);
+#pragma unroll
+                    for (int mr = 0; mr < MR; ++mr) {
+                        mma_16816(o[mr][2 * dp], pa[mr][kk], b[0], b[1]);
+                        mma_16816(o[mr][2 * dp + 1], pa[mr][kk], b[2], b[3]);
+                    }
                 }
             }
             if (TMA) {
@@ -425,26 +461,29 @@ __global__ __launch_bounds__(TMA ? NT + 32 : NT) void attn_mma_kernel(const __gr
             }
         }
     }
-    __syncthreads();   // every tile has been multiplied; the stages are free
+    __syncthreads();   // every tile has been multiplied; the stages and the Q rows are free
 
     // ---- partial states -> shared memory: o_s[wk][row][HD], ml_s[wk][row][2] ----
-    float* o_s = reinterpret_cast<float*>(k_s);             // 64 x HD floats, over the K stages (and into V's)
-    float* ml_s = o_s + 64 * HD;                            // 64 x 2 floats
+    float* o_s = reinterpret_cast<float*>(k_s);             // WK * RMAX x HD floats, over the K and V stages
+    float* ml_s = o_s + WK * RMAX * HD;                     // WK * RMAX x 2 floats
     if (warp < 4) {
-        l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
-        l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
-        l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
-        l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
-        const int ra = wk * RMAX + r_a, rb = wk * RMAX + r_b;
 #pragma unroll
-        for (int i = 0; i < ND; ++i) {
-            const int d = i * 8 + 2 * (lane & 3);
-            *reinterpret_cast<float2*>(o_s + (size_t)ra * HD + d) = make_float2(o[i][0], o[i][1]);
-            *reinterpret_cast<float2*>(o_s + (size_t)rb * HD + d) = make_float2(o[i][2], o[i][3]);
-        }
-        if ((lane & 3) == 0) {
-            ml_s[ra * 2] = m_run[0]; ml_s[ra * 2 + 1] = l_run[0];
-            ml_s[rb * 2] = m_run[1]; ml_s[rb * 2 + 1] = l_run[1];
+        for (int mr = 0; mr < MR; ++mr) {
+            l_run[mr][0] += __shfl_xor_sync(0xffffffffu, l_run[mr][0], 1);
+            l_run[mr][0] += __shfl_xor_sync(0xffffffffu, l_run[mr][0], 2);
+            l_run[mr][1] += __shfl_xor_sync(0xffffffffu, l_run[mr][1], 1);
+            l_run[mr][1] += __shfl_xor_sync(0xffffffffu, l_run[mr][1], 2);
+            const int ra = wk * RMAX + r_a[mr], rb = ra + 8;
+#pragma unroll
+            for (int i = 0; i < ND; ++i) {
+                const int d = i * 8 + 2 * (lane & 3);
+                *reinterpret_cast<float2*>(o_s + (size_t)ra * HD + d) = make_float2(o[mr][i][0], o[mr][i][1]);
+                *reinterpret_cast<float2*>(o_s + (size_t)rb * HD + d) = make_float2(o[mr][i][2], o[mr][i][3]);
+            }
+            if ((lane & 3) == 0) {
+                ml_s[ra * 2] = m_run[mr][0]; ml_s[ra * 2 + 1] = l_run[mr][0];
+                ml_s[rb * 2] = m_run[mr][1]; ml_s[rb * 2 + 1] = l_run[mr][1];
+            }
         }
     }
     __syncthreads();
@@ -545,15 +584,15 @@ bool kv_tensor_map(const void* pages, long long rows, int hd, int page_size, CUt
     return true;
 }
 
-template <int HD, int WR, int WK, bool TMA>
+template <int HD, int WR, int WK, int MR, bool TMA>
 int launch(const AttnArgs& a, int n_items, cudaStream_t stream) {
-    constexpr int RMAX = 16 * WR;
+    constexpr int RMAX = 16 * WR * MR;
     constexpr int STAGES = (TMA && WK == 4) ? 3 : 2;
     const int g = a.nh / a.nkv;
     const int gq_max = g < RMAX ? g : RMAX;
     const int hchunks = (g + gq_max - 1) / gq_max;
     const size_t stages = 2 * (size_t)STAGES * BN * HD * 2 + (size_t)RMAX * HD * 2 + 16 * STAGES + 16;
-    const size_t merge = (64 * (size_t)HD + 128) * sizeof(float);
+    const size_t merge = ((size_t)WK * RMAX * HD + (size_t)WK * RMAX * 2) * sizeof(float);
     const size_t smem = (stages > merge ? stages : merge) + 1024;   // + alignment slack
     CUtensorMap map;
     memset(&map, 0, sizeof(map));
@@ -565,7 +604,7 @@ int launch(const AttnArgs& a, int n_items, cudaStream_t stream) {
         }
         if (!kv_tensor_map(a.pages, rows, HD, a.page_size, &map)) return -3;
     }
-    auto kern = attn_mma_kernel<HD, WR, WK, TMA>;
+    auto kern = attn_mma_kernel<HD, WR, WK, MR, TMA>;
     static bool opted = false;
     if (!opted) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -582,12 +621,13 @@ int launch(const AttnArgs& a, int n_items, cudaStream_t stream) {
 
 template <int HD, bool TMA>
 int launch_rows(const AttnArgs& a, int n_items, int rows_max, cudaStream_t stream) {
-    return rows_max == 16 ? launch<HD, 1, 4, TMA>(a, n_items, stream) : launch<HD, 4, 1, TMA>(a, n_items, stream);
+    return rows_max == 16 ? launch<HD, 1, 4, 1, TMA>(a, n_items, stream) : launch<HD, 4, 1, 2, TMA>(a, n_items, stream);
 }
 
 }  // namespace
 
-// rows_max: 16 (single decoded tokens; the four warps split each tile's keys) or 64 (prompt portions).
+// rows_max: 16 (single decoded tokens; the four warps split each tile's keys) or 128 (prompt portions; each warp
+// holds two 16-row tiles, so every K and V fragment it reads feeds two MMAs).
 // Only bfloat16 and head_dim 64 or 128; the caller falls back to vcb_attn_paged otherwise.
 VCB_API int vcb_attn_mma_supported(int dtype, int hd) { return dtype == VCB_BF16 && (hd == 64 || hd == 128); }
 
@@ -599,7 +639,7 @@ VCB_API int vcb_attn_mma(const void* q, void* out, const void* pages, long long 
     if (n_items == 0) return 0;
     VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_mma: %d query heads are not a multiple of %d KV heads", nh, nkv);
     VCB_CHECK_ARG(hd == 64 || hd == 128, "attn_mma: head_dim %d is not 64 or 128", hd);
-    VCB_CHECK_ARG(rows_max == 16 || rows_max == 64, "attn_mma: rows_max must be 16 or 64");
+    VCB_CHECK_ARG(rows_max == 16 || rows_max == 128, "attn_mma: rows_max must be 16 or 128");
     VCB_CHECK_ARG(page_size > 0 && window >= 0, "attn_mma: bad page_size %d or window %d", page_size, window);
     AttnArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_stride, block_table,
                table_row, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml, nh, nkv, page_size, num_pages,

@@ -26,7 +26,7 @@ from .linear import matmul_tn
 DECODE_ROWS = 8     # rows a block of the decode variant of the plain attention kernel holds
 SPAN_ROWS = 32      # rows of its prompt-portion variant
 MMA_DECODE_ROWS = 16   # the same for the tensor-core kernel
-MMA_SPAN_ROWS = 64
+MMA_SPAN_ROWS = 128
 MAX_SLICES = 64
 TARGET_BLOCKS = 2 * 148   # blocks of the decode kernel that are resident at once (two per SM)
 
@@ -67,6 +67,8 @@ class AttentionPlan:
                 n = ctx.host_q_len[e]
                 for q0 in range(0, n, nq_max):
                     rows.append((e, q0, min(nq_max, n - q0), 0, 1, 0))
+            # longest key ranges first: the blocks that run longest start first, the short ones fill the tail
+            rows.sort(key=lambda r: -(ctx.host_ctx_len[r[0]] - ctx.host_q_len[r[0]] + r[1] + r[2]))
             self.n_span_items = len(rows)
             self.span_items = torch.tensor(rows, dtype=torch.int32).to(dev)
 
