@@ -1,0 +1,51 @@
+"""The serving kernels at the layer sizes of the benchmark model (Qwen3-8B shape: hidden 4096, 32/8 heads of 128,
+intermediate 12288, vocabulary 151936; two layers to keep it short) against the engine's own true-32-bit path,
+whose kernels the other tests tie to the plain implementation at small sizes.  Same random weights, a prompt fed
+in portions, then decoding through captured steps."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_bf16_engine_follows_the_32_bit_engine_at_8b_layer_sizes():
+    from vllm_cpp_b200 import LLM, EngineConfig, Qwen3Config
+    from vllm_cpp_b200.engine.step import StepEntry
+    from vllm_cpp_b200.runtime import runtime
+    cfg = Qwen3Config(vocab_size=151936, hidden_size=4096, intermediate_size=12288, num_hidden_layers=2,
+                      num_attention_heads=32, num_key_value_heads=8, head_dim=128, max_position_embeddings=4096,
+                      rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+    rng = np.random.default_rng(0)
+    tokens = {0: rng.integers(0, cfg.vocab_size, 700).tolist(), 1: rng.integers(0, cfg.vocab_size, 150).tolist()}
+    # portions: a long one (fused feed-forward path, 256-token tiles), short ones (k-sliced products), then single tokens
+    plan = [[(0, 300), (1, 17)], [(0, 300), (1, 100)], [(0, 90), (1, 25)]] + [[(0, 1), (1, 1)]] * 8 + [[(0, 2)]]
+    rows = {}
+    for dtype in ("float32", "bfloat16"):
+        llm = LLM(config=cfg, random_seed=1, engine=EngineConfig(dtype=dtype, page_size=16, max_tokens=2048, max_num_seqs=2,
+                                                                 max_step_tokens=512))
+        runner = llm.runner
+        rt = runtime()
+        cm = rt.CacheManager(runner.layout.runtime_groups(rt, 16, 128), 2)
+        pos = {0: 0, 1: 0}
+        for r in pos:
+            cm.open(r)
+        got = []
+        for step in plan:
+            entries = []
+            for r, n in step:
+                assert cm.reserve(r, pos[r] + n)
+                entries.append(StepEntry(cm.slot(r), pos[r], tokens[r][pos[r]:pos[r] + n], [cm.block_table(r, 0)], [n - 1]))
+                pos[r] += n
+            got.append(runner.step(entries).float().cpu().clone())
+            for r, _ in step:
+                cm.commit(r, pos[r])
+        rows[dtype] = torch.cat(got)
+        if dtype == "bfloat16":
+            assert runner.graph_replays >= 7          # the single-token steps ran from a captured graph
+        del llm, runner
+        torch.cuda.empty_cache()
+    ref, got = rows["float32"], rows["bfloat16"]
+    err = ((got - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)).max().item()
+    assert err < 3e-2, err
+    assert (got.argmax(dim=1) == ref.argmax(dim=1)).float().mean().item() >= 0.8
