@@ -221,8 +221,12 @@ def _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma):
         S = plan.nslices
         po = torch.empty(plan.n_dec * nh * S, hd, device=dev()) if S > 1 else None
         pm = torch.empty(plan.n_dec * nh * S, 2, device=dev()) if S > 1 else None
-        kernel(q_flat, out, *args, plan.dec_items, plan.n_dec * S, DECODE_ROWS, po, pm, nh, nkv, hd, window, status)
-        if S > 1:
+        fused = mma is True and S > 1      # the last-arriving block merges the key slices itself
+        extra = dict(slice_counters=plan.slice_counters, dec_rows=plan.dec_rows) if fused else {}
+        kernel(q_flat, out, *args, plan.dec_items, plan.n_dec * S, DECODE_ROWS, po, pm, nh, nkv, hd, window, status, **extra)
+        if fused:
+            assert int(plan.slice_counters.abs().sum()) == 0        # left ready for the next launch
+        elif S > 1:
             ops.attn_merge(po, pm, plan.dec_rows, out, plan.n_dec, nh, hd, S)
     if plan.n_span_items:
         kernel(q_flat, out, *args, plan.span_items, plan.n_span_items, SPAN_ROWS, None, None, nh, nkv, hd, window, status)

@@ -51,6 +51,8 @@ struct AttnArgs {
     const int* items;
     float* part_o;
     float* part_ml;
+    int* slice_counters;   // one per (decoded token, KV head group): slices finished; null: a separate kernel merges
+    const int* dec_rows;   // output row of each decoded token (for the merging block)
     int nh, nkv, page_size, num_pages, window;
     float scale;
     int* status;
@@ -519,6 +521,45 @@ __global__ __launch_bounds__(TMA ? NT + 32 : NT) void attn_mma_kernel(const __gr
             }
         }
     }
+
+    // ---- the block that finishes the last slice of a (token, head group) merges the slices ----
+    if (nslices > 1 && a.slice_counters != nullptr) {
+        __shared__ int is_last;
+        __threadfence();            // this block's partials are visible before its arrival is counted
+        __syncthreads();
+        int* counter = a.slice_counters + (size_t)dec_index * gridDim.y + blockIdx.y;
+        if (tid == 0) {
+            const int prev = atomicAdd(counter, 1);
+            is_last = prev == nslices - 1;
+            if (is_last) *counter = 0;   // ready for the next launch
+        }
+        __syncthreads();
+        if (is_last) {
+            __threadfence();        // the other slices' partials are visible to this block
+            const int out_row = a.dec_rows[dec_index];
+            if (out_row >= 0) {
+                for (int idx = tid; idx < gq * (HD / 2); idx += blockDim.x) {
+                    const int ih = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
+                    const size_t prow0 = ((size_t)dec_index * a.nh + head0 + ih) * nslices;
+                    float m = -CUDART_INF_F;
+                    for (int sl = 0; sl < nslices; ++sl) m = fmaxf(m, __ldcg(a.part_ml + (prow0 + sl) * 2));
+                    float l = 0.f, o0 = 0.f, o1 = 0.f;
+                    for (int sl = 0; sl < nslices; ++sl) {     // slice order, as the separate merge kernel does
+                        const float ms = __ldcg(a.part_ml + (prow0 + sl) * 2);
+                        if (ms == -CUDART_INF_F) continue;
+                        const float w = expf(ms - m);
+                        l += __ldcg(a.part_ml + (prow0 + sl) * 2 + 1) * w;
+                        const float2 ov = __ldcg(reinterpret_cast<const float2*>(a.part_o + (prow0 + sl) * HD + d));
+                        o0 += ov.x * w;
+                        o1 += ov.y * w;
+                    }
+                    const float inv = l > 0.f ? 1.f / l : 0.f;
+                    *reinterpret_cast<__nv_bfloat162*>(a.out + ((size_t)out_row * a.nh + head0 + ih) * HD + d) =
+                        __floats2bfloat162_rn(o0 * inv, o1 * inv);
+                }
+            }
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -634,16 +675,17 @@ VCB_API int vcb_attn_mma_supported(int dtype, int hd) { return dtype == VCB_BF16
 VCB_API int vcb_attn_mma(const void* q, void* out, const void* pages, long long page_stride, const int* block_table,
                          const int* table_row, int max_blocks, const int* q_start, const int* q_len,
                          const int* ctx_len, const int* items, int n_items, int rows_max, float* part_o,
-                         float* part_ml, int nh, int nkv, int hd, int page_size, int num_pages, int window,
-                         float scale, int* status, int allow_tma, cudaStream_t stream) {
+                         float* part_ml, int* slice_counters, const int* dec_rows, int nh, int nkv, int hd,
+                         int page_size, int num_pages, int window, float scale, int* status, int allow_tma,
+                         cudaStream_t stream) {
     if (n_items == 0) return 0;
     VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_mma: %d query heads are not a multiple of %d KV heads", nh, nkv);
     VCB_CHECK_ARG(hd == 64 || hd == 128, "attn_mma: head_dim %d is not 64 or 128", hd);
     VCB_CHECK_ARG(rows_max == 16 || rows_max == 128, "attn_mma: rows_max must be 16 or 128");
     VCB_CHECK_ARG(page_size > 0 && window >= 0, "attn_mma: bad page_size %d or window %d", page_size, window);
     AttnArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_stride, block_table,
-               table_row, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml, nh, nkv, page_size, num_pages,
-               window, scale, status};
+               table_row, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml, slice_counters, dec_rows, nh, nkv,
+               page_size, num_pages, window, scale, status};
     const bool tma = allow_tma && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64) &&
                      ((uintptr_t)pages % 16 == 0) && page_stride == (long long)2 * nkv * page_size * hd;
     if (hd == 64) return tma ? launch_rows<64, true>(a, n_items, rows_max, stream) : launch_rows<64, false>(a, n_items, rows_max, stream);

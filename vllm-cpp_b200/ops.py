@@ -63,7 +63,7 @@ def _declare(L):
         "vcb_gemm_bf16_plain": [P, P, P, I, I, I, I, LL, LL, LL, P],
         "vcb_attn_paged": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, P],
         "vcb_scatter_i32": [P, P, P, P, I, LL, P],
-        "vcb_attn_mma": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, I, P],
+        "vcb_attn_mma": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, F, P, I, P],
         "vcb_attn_mma_supported": [I, I],
         "vcb_attn_merge": [P, P, P, P, I, I, I, I, I, P],
         "vcb_sample": [P, LL, I, I, P, P, P, P],
@@ -309,8 +309,10 @@ def attn_mma_supported(dtype: torch.dtype, hd: int) -> bool:
 
 
 def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, rows_max, part_o, part_ml,
-             nh, nkv, hd, window, status, table_row=None, allow_tma=True):
-    """Tensor-core variant of :func:`attn_paged` (bfloat16, head_dim 64 or 128; rows_max 16 or 128)."""
+             nh, nkv, hd, window, status, table_row=None, allow_tma=True, slice_counters=None, dec_rows=None):
+    """Tensor-core variant of :func:`attn_paged` (bfloat16, head_dim 64 or 128; rows_max 16 or 128).
+    With ``slice_counters`` (int32 zeros, one per decoded token and KV head group, left at zero again) and
+    ``dec_rows``, the block that finishes a token's last key slice merges the slices itself."""
     _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(pages, "pages", torch.bfloat16)
     for name, t in (("block_table", block_table), ("q_start", q_start), ("q_len", q_len), ("ctx_len", ctx_len),
                     ("items", items)):
@@ -319,5 +321,5 @@ def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items
     assert two == 2 and nkv_p == nkv and hd_p == hd
     _call("vcb_attn_mma", _p(q), _p(out), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
           block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, rows_max, _p(part_o),
-          _p(part_ml), nh, nkv, hd, page_size, num_pages, int(window or 0), 1.0 / math.sqrt(hd), _p(status), int(allow_tma),
-          _stream())
+          _p(part_ml), _p(slice_counters), _p(dec_rows), nh, nkv, hd, page_size, num_pages, int(window or 0),
+          1.0 / math.sqrt(hd), _p(status), int(allow_tma), _stream())

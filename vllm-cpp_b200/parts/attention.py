@@ -60,6 +60,8 @@ class AttentionPlan:
                     k += 1
             self.dec_items = torch.from_numpy(items).to(dev)
             self.dec_rows = torch.tensor([ctx.host_q_start[e] for e in dec], dtype=torch.int32).to(dev)
+            # arrival counters of the key slices (the tensor-core kernel merges in its last-arriving block)
+            self.slice_counters = torch.zeros(len(dec) * nkv * hchunks, dtype=torch.int32, device=dev)
         if spans:
             nq_max = max(1, span_rows // min(g, span_rows))
             rows = []
@@ -147,10 +149,15 @@ class GQAAttention(Mixer):
             if S > 1:
                 part_o = torch.empty((plan.n_dec * nh * S, hd), dtype=torch.float32, device=x.device)
                 part_ml = torch.empty((plan.n_dec * nh * S, 2), dtype=torch.float32, device=x.device)
-            kernel(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
-                   plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml, **common)
-            if S > 1:
-                ops.attn_merge(part_o, part_ml, plan.dec_rows, out, plan.n_dec, nh, hd, S)
+            if mma:
+                ops.attn_mma(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
+                             plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml,
+                             slice_counters=plan.slice_counters if S > 1 else None, dec_rows=plan.dec_rows, **common)
+            else:
+                ops.attn_paged(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
+                               plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml, **common)
+                if S > 1:
+                    ops.attn_merge(part_o, part_ml, plan.dec_rows, out, plan.n_dec, nh, hd, S)
         if plan.n_span_items:
             kernel(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
                    plan.span_items, plan.n_span_items, span_rows, None, None, **common)
