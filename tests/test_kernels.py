@@ -364,7 +364,7 @@ def test_kernels_refuse_what_they_cannot_do():
 @pytest.mark.parametrize("M,T,K,splits", [
     (128, 16, 64, 1), (128, 1, 64, 1), (64, 3, 96, 1), (200, 17, 200, 1), (384, 8, 4096, 4), (6144, 8, 4096, 3),
     (4096, 64, 1024, 2), (1000, 33, 520, 2), (256, 100, 256, 1), (384, 256, 512, 1), (300, 700, 328, 1),
-    (4096, 2048, 512, 1), (128, 130, 8, 1)])
+    (4096, 2048, 512, 1), (128, 130, 8, 1), (6144, 2048, 256, 1), (6144, 700, 128, 1)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gemm_bf16_tn(M, T, K, splits, out_dtype):
     """The tcgen05/TMA product against 64-bit: tile edges in every dimension, k tails, k-slices, 1 to 2048 tokens."""

@@ -153,8 +153,9 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
                                                                     GemmArgs g) {
     using L = Smem<BN, STAGES, MT, ACC>;
     constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;            // columns of one 128-feature accumulator
-    constexpr uint32_t TMEM_COLS = ACC * MT * ACC_COLS;         // a power of two in [32, 512]
-    static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns");
+    constexpr uint32_t USED_COLS = ACC * MT * ACC_COLS;
+    constexpr uint32_t TMEM_COLS = USED_COLS <= 32 ? 32 : USED_COLS <= 64 ? 64 : USED_COLS <= 128 ? 128 : USED_COLS <= 256 ? 256 : 512;
+    static_assert(USED_COLS <= 512, "TMEM columns");   // allocations are powers of two in [32, 512]
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
@@ -520,6 +521,12 @@ VCB_API int vcb_gemm_bf16_tn(const void* W, const void* X, void* out, int out_dt
     else if (N <= 64) rc = launch<64, 8, 1, 2>(W, X, g, ldw, ldx, splits, stream);
     else if (N <= 128) rc = launch<128, 6, 1, 2>(W, X, g, ldw, ldx, splits, stream);
     else if (M <= 128) rc = launch<256, 4, 1, 2>(W, X, g, ldw, ldx, splits, stream);
-    else rc = launch<256, 3, 2, 1>(W, X, g, ldw, ldx, splits, stream);   // 256 features x 256 tokens a unit
+    else {
+        // 256 features x 256 or 192 tokens a unit: whichever leaves the last round over the SMs less empty
+        const long long mu = (M + 2 * BM - 1) / (2 * BM);
+        auto cost = [&](int bn) { const long long units = mu * ((N + bn - 1) / bn); return ((units + num_sms() - 1) / num_sms()) * bn; };
+        if (cost(192) < cost(256)) rc = launch<192, 3, 2, 1>(W, X, g, ldw, ldx, splits, stream);
+        else rc = launch<256, 3, 2, 1>(W, X, g, ldw, ldx, splits, stream);
+    }
     return rc;
 }
