@@ -1,7 +1,5 @@
 """Shared fixtures: tiny model folders with random weights (made in a temporary folder), the
 plain implementation's logits for them, and the ``gpu`` marker."""
-import json
-import os
 import sys
 from pathlib import Path
 

@@ -3,10 +3,9 @@ greedy and seeded sampling, portions under a token budget, preemption by recompu
 import subprocess
 import sys
 
-import numpy as np
 import pytest
 
-from conftest import ROOT, TINY, TINY_PAGE, random_tokens
+from conftest import ROOT, TINY_PAGE, random_tokens
 
 pytestmark = pytest.mark.gpu
 

@@ -1,8 +1,6 @@
 """Each part of a layer alone against the plain implementation's function for it, and the generality of the
 assembly: a toy mixer with state of its own, a layer that runs twice, and a layer that reads another layer's
 cache -- all registered from here, without a change to the package's files."""
-import json
-import math
 from dataclasses import dataclass
 
 import numpy as np

@@ -2,13 +2,12 @@
 import json
 import struct
 
-import numpy as np
 import pytest
 import torch
 
 from conftest import tiny_config
 from vllm_cpp_b200 import expected_tensors, load_config, write_random_model
-from vllm_cpp_b200.weights import (SafetensorsError, TensorSpec, WeightError, WeightStore, open_model_weights,
+from vllm_cpp_b200.weights import (SafetensorsError, WeightError, WeightStore, open_model_weights,
                                    read_safetensors, write_safetensors)
 
 

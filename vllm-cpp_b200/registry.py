@@ -44,7 +44,7 @@ class LayerSpec:
     """One layer: the arrangement (block) and the parts it arranges; ``prefix`` starts its tensor names."""
     prefix: str
     block: PartSpec
-    parts: dict  # role -> PartSpec, e.g. {"norm1":…, "mixer":…, "norm2":…, "feed_forward":…}
+    parts: dict  # role -> (PartSpec, sub-prefix), e.g. {"norm1": (…, "input_layernorm."), "mixer": (…, "self_attn."), …}
 
 
 @dataclass(frozen=True)
