@@ -30,6 +30,8 @@
 
 #include <cuda.h>
 
+#include <stdlib.h>
+
 #include <mutex>
 #include <unordered_map>
 
@@ -153,6 +155,7 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
                                                                     GemmArgs g) {
     using L = Smem<BN, STAGES, MT, ACC>;
     constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;            // columns of one 128-feature accumulator
+    constexpr int CHUNK = BN % 64 == 0 ? 64 : (BN % 32 == 0 ? 32 : 16);   // accumulator columns read per wait in the epilogue
     constexpr uint32_t USED_COLS = ACC * MT * ACC_COLS;
     constexpr uint32_t TMEM_COLS = USED_COLS <= 32 ? 32 : USED_COLS <= 64 ? 64 : USED_COLS <= 128 ? 128 : USED_COLS <= 256 ? 256 : 512;
     static_assert(USED_COLS <= 512, "TMEM columns");   // allocations are powers of two in [32, 512]
@@ -314,17 +317,20 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
                 const int m = m0 + q * 32 + lane;
                 __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out);
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
+                for (int c0 = 0; c0 < BN; c0 += 32) {
                     if (n0 + c0 >= g.N) break;   // uniform over the warp
-                    uint32_t vg[16], vu[16];
-                    tc_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, vg);
-                    tc_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(ACC_COLS + c0), vu);
+                    uint32_t vg[2][16], vu[2][16];
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        tc_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(c0 + 16 * b), vg[b]);
+                        tc_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(ACC_COLS + c0 + 16 * b), vu[b]);
+                    }
                     tc_wait_ld();
                     if (m < g.M) {
 #pragma unroll
-                        for (int jj = 0; jj < 16; ++jj) {
+                        for (int jj = 0; jj < 32; ++jj) {
                             if (n0 + c0 + jj < g.N) {
-                                const float gv = __uint_as_float(vg[jj]), uv = __uint_as_float(vu[jj]);
+                                const float gv = __uint_as_float(vg[jj / 16][jj % 16]), uv = __uint_as_float(vu[jj / 16][jj % 16]);
                                 o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
                             }
                         }
@@ -332,24 +338,28 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
                 }
             } else
 #pragma unroll 1
-            for (int cc = 0; cc < MT * BN; cc += 16) {
+            for (int cc = 0; cc < MT * BN; cc += CHUNK) {
                 const int mt = cc / BN, c0 = cc % BN;
                 if (n0 + c0 >= g.N) continue;   // uniform over the warp
                 const int m = m0 + mt * BM + q * 32 + lane;
-                uint32_t v[16];
-                tc_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * ACC_COLS + c0), v);
+                // several TMEM loads in flight before one wait: their latencies overlap
+                uint32_t v[CHUNK / 16][16];
+#pragma unroll
+                for (int b = 0; b < CHUNK / 16; ++b)
+                    tc_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * ACC_COLS + c0 + 16 * b), v[b]);
                 tc_wait_ld();
                 if (m < g.M) {
                     if (g.out_dtype == VCB_F32) {
                         float* o = reinterpret_cast<float*>(g.out) + zoff;
 #pragma unroll
-                        for (int jj = 0; jj < 16; ++jj)
-                            if (n0 + c0 + jj < g.N) o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __uint_as_float(v[jj]);
+                        for (int jj = 0; jj < CHUNK; ++jj)
+                            if (n0 + c0 + jj < g.N) o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __uint_as_float(v[jj / 16][jj % 16]);
                     } else {
                         __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + zoff;
 #pragma unroll
-                        for (int jj = 0; jj < 16; ++jj)
-                            if (n0 + c0 + jj < g.N) o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __float2bfloat16_rn(__uint_as_float(v[jj]));
+                        for (int jj = 0; jj < CHUNK; ++jj)
+                            if (n0 + c0 + jj < g.N)
+                                o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __float2bfloat16_rn(__uint_as_float(v[jj / 16][jj % 16]));
                     }
                 }
             }
@@ -363,6 +373,238 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Two blocks on two SMs working as a pair (cta_group::2) for prompt portions.
+//
+// One MMA of the pair covers 256 features (128 TMEM lanes in each block) x 256 tokens; each block loads only its own
+// 128-token half of the token tile, which the tensor cores of both read.  With two such accumulators per block a
+// pair's unit is 512 features x 256 tokens for 48 KB per block and k-step of 64 -- a quarter less traffic from L2
+// per flop than the single-block kernel's 64 KB, and these products are bound by that traffic.
+//
+// Block 0 of the pair issues every MMA.  Both blocks' TMA loads report to block 0's "full" barrier
+// (cp.async.bulk.tensor with .cta_group::2 lets a load signal the peer's barrier; no multicast load is used);
+// tcgen05.commit with a two-block arrival mask releases the stage, and hands over the accumulators, in both
+// blocks; the epilogue warps of both report the drained accumulators to block 0.
+// ---------------------------------------------------------------------------
+constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;   // a shared::cluster address with this bit cleared names block 0 of the pair
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_block0, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar_block0), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at this shared-memory offset in both blocks of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_block0(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & PEER_BIT_MASK) : "memory");
+}
+
+template <int STAGES>
+struct SmemPair {
+    static constexpr int BN = 256;
+    static constexpr int A_BYTES = BM * BK * 2;           // one 128-feature tile
+    static constexpr int B_BYTES = (BN / 2) * BK * 2;     // this block's half of the token tile
+    static constexpr int STAGE_BYTES = 2 * A_BYTES + B_BYTES;
+    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int NUM_BARS = 2 * STAGES + 2;
+    static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;
+};
+
+template <int STAGES>
+__global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                         const __grid_constant__ CUtensorMap map_x,
+                                                                         GemmArgs g) {
+    using L = SmemPair<STAGES>;
+    constexpr int BN = 256;
+    constexpr uint32_t TMEM_COLS = 512;   // two accumulators of 256 token columns
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + L::BAR_OFFSET;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    const uint32_t acc_full_bar = bars + 8u * (2 * STAGES);
+    const uint32_t acc_empty_bar = bars + 8u * (2 * STAGES + 1);
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(gen + L::BAR_OFFSET + L::NUM_BARS * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::BAR_OFFSET + L::NUM_BARS * 8 + 8);
+
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();          // 0 issues the MMAs
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int total_kb = (g.K + BK - 1) / BK;
+    const int unit_rows = g.swiglu_rows ? 2 * BM : 4 * BM;   // output features per pair unit
+    const int m_tiles = (g.M + unit_rows - 1) / unit_rows;
+    const int n_tiles = (g.N + BN - 1) / BN;
+    const int units = m_tiles * n_tiles;
+    // first row in W of this block's feature tile mt
+    auto w_row = [&](int m0, int mt) {
+        return g.swiglu_rows ? m0 + (int)rank * BM + mt * g.swiglu_rows : m0 + ((int)rank * 2 + mt) * BM;
+    };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(acc_full_bar, 1);
+        mbar_init(acc_empty_bar, 8);   // four epilogue warps in each block of the pair
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32((const void*)tmem_holder)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();   // the peer's barriers exist before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        // ---- TMA producer (in both blocks): its two feature tiles and its half of the token tile ----
+        if (lane == 0) {
+            pdl_wait();
+            int it = 0, armed = 0;
+            bool ok = true;
+            for (int u = pair; u < units && ok; u += pairs) {
+                const int m0 = (u % m_tiles) * unit_rows, n0 = (u / m_tiles) * BN;
+                for (int i = 0; i < total_kb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1u, abort_flag, g.status)) { ok = false; break; }
+                    if (rank == 0) mbar_expect_tx(full_bar(s), 2 * L::STAGE_BYTES);   // both blocks' bytes land on block 0's barrier
+                    const uint32_t dst = base + s * L::STAGE_BYTES;
+                    const uint32_t bar0 = full_bar(s) & PEER_BIT_MASK;
+                    tma_load_2d_pair(dst, &map_w, bar0, i * BK, w_row(m0, 0));
+                    tma_load_2d_pair(dst + L::A_BYTES, &map_w, bar0, i * BK, w_row(m0, 1));
+                    tma_load_2d_pair(dst + 2 * L::A_BYTES, &map_x, bar0, i * BK, n0 + (int)rank * (BN / 2));
+                    armed = it + 1;
+                }
+            }
+            if (*abort_flag && rank == 0) {
+                for (int i = max(0, armed - STAGES); i < armed; ++i) {
+                    const long long t0 = clock64();
+                    while (!mbar_try(full_bar(i % STAGES), (i / STAGES) & 1) && clock64() - t0 < WAIT_CLOCKS) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer: block 0 only ----
+        if (lane == 0 && rank == 0) {
+            // M = 256 (both blocks' lanes), N = 256
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+            int it = 0, j = 0;
+            bool ok = true;
+            for (int u = pair; u < units && ok; u += pairs, ++j) {
+                ok = mbar_wait(acc_empty_bar, (j & 1) ^ 1u, abort_flag, g.status);   // both epilogues drained the last unit
+                if (!ok) break;
+                tc_fence_after();
+                for (int i = 0; i < total_kb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag, g.status);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = base + s * L::STAGE_BYTES;
+                    const uint64_t db = smem_desc(a_addr + 2 * L::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+#pragma unroll
+                        for (int mt = 0; mt < 2; ++mt)
+                            tc_mma_pair(tmem_base + mt * BN, smem_desc(a_addr + mt * L::A_BYTES) + 2 * k, db + 2 * k, idesc,
+                                        (i > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit_pair(empty_bar(s));   // frees the stage in both blocks
+                }
+                if (ok) tc_commit_pair(acc_full_bar);
+            }
+        }
+    } else {
+        // ---- epilogue (both blocks): each owns its 128 lanes of both accumulators ----
+        const int q = warp & 3;
+        int j = 0;
+        for (int u = pair; u < units; u += pairs, ++j) {
+            const int m0 = (u % m_tiles) * unit_rows, n0 = (u / m_tiles) * BN;
+            if (!mbar_wait(acc_full_bar, j & 1, abort_flag, g.status)) break;
+            tc_fence_after();
+            if (g.swiglu_rows) {
+                const int m = m0 + (int)rank * BM + q * 32 + lane;
+                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    if (n0 + c0 >= g.N) break;   // uniform over the warp
+                    uint32_t vg[16], vu[16];
+                    tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, vg);
+                    tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + c0), vu);
+                    tc_wait_ld();
+                    if (m < g.M) {
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj) {
+                            if (n0 + c0 + jj < g.N) {
+                                const float gv = __uint_as_float(vg[jj]), uv = __uint_as_float(vu[jj]);
+                                o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
+                            }
+                        }
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int cc = 0; cc < 2 * BN; cc += 16) {
+                    const int mt = cc / BN, c0 = cc % BN;
+                    if (n0 + c0 >= g.N) continue;   // uniform over the warp
+                    const int m = m0 + ((int)rank * 2 + mt) * BM + q * 32 + lane;
+                    uint32_t v[16];
+                    tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * BN + c0), v);
+                    tc_wait_ld();
+                    if (m < g.M) {
+                        if (g.out_dtype == VCB_F32) {
+                            float* o = reinterpret_cast<float*>(g.out);
+#pragma unroll
+                            for (int jj = 0; jj < 16; ++jj)
+                                if (n0 + c0 + jj < g.N) o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __uint_as_float(v[jj]);
+                        } else {
+                            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out);
+#pragma unroll
+                            for (int jj = 0; jj < 16; ++jj)
+                                if (n0 + c0 + jj < g.N) o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __float2bfloat16_rn(__uint_as_float(v[jj]));
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_block0(acc_empty_bar);
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    cluster_sync();   // neither block leaves while the other may still signal its barriers or read its tiles
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -476,6 +718,60 @@ int launch(const void* W, const void* X, const GemmArgs& g, long long ldw, long 
     return launch_maps<BN, STAGES, MT, ACC>(W, g.M, X, g, ldw, ldx, splits, stream);
 }
 
+// VLLM_CPP_B200_GEMM_PAIRS=1 sends prompt-portion products to the two-block kernel.  Off by default: measured on
+// B200 it is no faster than the single-block kernel at the benchmark's shapes (qkv 118 vs 96 us, o 60 vs 60,
+// gate_up 432 vs 426, down 180 vs 174), so the bytes it saves are not what bounds these products.
+bool pairs_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("VLLM_CPP_B200_GEMM_PAIRS");
+        on = (e && e[0] == '1') ? 1 : 0;
+    }
+    return on == 1;
+}
+
+int launch_pair(const void* W, long long w_rows, const void* X, const GemmArgs& g, long long ldw, long long ldx,
+                cudaStream_t stream) {
+    constexpr int STAGES = 4;
+    using L = SmemPair<STAGES>;
+    CUtensorMap mw, mx;
+    if (!tensor_map(W, w_rows, g.K, ldw, BM, &mw) || !tensor_map(X, g.N, g.K, ldx, 128, &mx)) return -3;
+    auto kern = gemm_bf16_tn_pair_kernel<STAGES>;
+    static bool opted = false;
+    if (!opted) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) {
+            vcb_set_error("gemm_bf16_tn: %d bytes of shared memory refused: %s", L::TOTAL, cudaGetErrorString(e));
+            return -2;
+        }
+        opted = true;
+    }
+    const int unit_rows = g.swiglu_rows ? 2 * BM : 4 * BM;
+    const long long units = (long long)((g.M + unit_rows - 1) / unit_rows) * ((g.N + 255) / 256);
+    const long long max_pairs = num_sms() / 2;
+    const int pairs = (int)(units < max_pairs ? units : max_pairs);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = L::TOTAL;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = vcb_pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, mx, g);
+    if (e != cudaSuccess) {
+        vcb_set_error("gemm_bf16_tn (pairs): launch failed: %s", cudaGetErrorString(e));
+        return -2;
+    }
+    return 0;
+}
+
 }  // namespace
 
 // out[z][t][m] (z < splits) = sum over k-slice z of W[m][k] X[t][k];  W [M,K], X [N,K] bfloat16, K contiguous.
@@ -499,6 +795,7 @@ VCB_API int vcb_gemm_bf16_swiglu(const void* W, const void* X, void* out, int I,
     const int total_kb = (K + BK - 1) / BK;
     GemmArgs g{out, VCB_BF16, I, N, K, ldc, 0, total_kb, 1, I, status};
     // the weight map spans both halves so that the up tile is addressed as row I + m
+    if (pairs_enabled()) return launch_pair(W, 2LL * I, X, g, ldw, ldx, stream);
     return launch_maps<256, 3, 2, 1>(W, 2LL * I, X, g, ldw, ldx, 1, stream);
 }
 
@@ -521,6 +818,7 @@ VCB_API int vcb_gemm_bf16_tn(const void* W, const void* X, void* out, int out_dt
     else if (N <= 64) rc = launch<64, 8, 1, 2>(W, X, g, ldw, ldx, splits, stream);
     else if (N <= 128) rc = launch<128, 6, 1, 2>(W, X, g, ldw, ldx, splits, stream);
     else if (M <= 128) rc = launch<256, 4, 1, 2>(W, X, g, ldw, ldx, splits, stream);
+    else if (pairs_enabled() && M >= 512) rc = launch_pair(W, M, X, g, ldw, ldx, stream);
     else {
         // 256 features x 256 or 192 tokens a unit: whichever leaves the last round over the SMs less empty
         const long long mu = (M + 2 * BM - 1) / (2 * BM);
