@@ -214,10 +214,10 @@ __global__ void sample_pick_kernel(const float* __restrict__ part_v, const int* 
 }
 
 __global__ void count_tokens_kernel(const int* __restrict__ ids, const int* __restrict__ slots, int* __restrict__ counts,
-                                    int n, int V) {
+                                    int n, int V, int slot_bias) {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= n) return;
-    const int id = ids[t], slot = slots[t];
+    const int id = ids[t], slot = slots[t] - slot_bias;
     if (slot >= 0 && id >= 0 && id < V) atomicAdd(counts + (size_t)slot * V + id, 1);
 }
 
@@ -235,9 +235,10 @@ VCB_API int vcb_sample(const float* logits, long long row_stride, int n_rows, in
     return 0;
 }
 
-VCB_API int vcb_count_tokens(const int* ids, const int* slots, int* counts, int n, int V, cudaStream_t stream) {
+// counts[slots[t] - slot_bias][ids[t]] += 1 for every token whose slot entry, less the bias, is >= 0
+VCB_API int vcb_count_tokens(const int* ids, const int* slots, int* counts, int n, int V, int slot_bias, cudaStream_t stream) {
     if (n == 0) return 0;
-    count_tokens_kernel<<<(n + 255) / 256, 256, 0, stream>>>(ids, slots, counts, n, V);
+    count_tokens_kernel<<<(n + 255) / 256, 256, 0, stream>>>(ids, slots, counts, n, V, slot_bias);
     VCB_CHECK_LAUNCH("count_tokens");
     return 0;
 }

@@ -119,30 +119,38 @@ class LLM:
             if e.sample:
                 sampled_entries.append(e)
         penalised = {e.slot for e in sched.entries if self._options[e.request].repeat_penalty not in (0.0, 1.0)}
+        if penalised:
+            self.sampler._need_counts()
+            self.sampler.forget([e.slot for e in sched.entries if e.start_pos == 0 and e.slot in penalised])
+        # Beside the model's own numbers the step carries 8 per sampled row and then, where occurrences are
+        # counted, one per token (its request's slot + 1, 0 for none).  A captured step pads rows and tokens to
+        # its own size, so the per-token part starts after the padded rows.
+        flat, use_counts, no_nucleus = Sampler.records([self._options[e.request] for e in sampled_entries],
+                                                       [e.gen_step for e in sampled_entries],
+                                                       [e.slot for e in sampled_entries])
+        n_rows = len(sampled_entries)
+        rows_pad = self.runner.capture_size(entries) or n_rows
+        user = flat + [0] * (8 * (rows_pad - n_rows))
+        if penalised:
+            user += Sampler.token_slots(entries, penalised)
+        counting = bool(penalised)
+
+        def post(ctx, logits):
+            if counting:
+                self.sampler.observe(ctx.token_ids, ctx.user[8 * rows_pad:8 * rows_pad + ctx.T], ctx.T)
+            if logits is None:
+                return None
+            return self.sampler.sample_records(logits, ctx.user[:8 * logits.shape[0]].view(-1, 8), use_counts, no_nucleus)
+
+        toks = self.runner.step(entries, check=False, user=user, post=post,
+                                post_key=("sample", counting, use_counts, no_nucleus))
         tokens: list[int] = []
         if sampled_entries:
-            flat, use_counts, no_nucleus = Sampler.records([self._options[e.request] for e in sampled_entries],
-                                                           [e.gen_step for e in sampled_entries],
-                                                           [e.slot for e in sampled_entries])
-            n_rows = len(sampled_entries)
-
-            def post(ctx, logits):
-                if penalised:
-                    self.sampler.observe(ctx, penalised)
-                return self.sampler.sample_records(logits, ctx.user[:8 * logits.shape[0]].view(-1, 8), use_counts, no_nucleus)
-
-            # a step that counts token occurrences reads host-side facts, so it is not captured (key None keeps it eager)
-            toks = self.runner.step(entries, check=False, user=flat, post=post,
-                                    post_key=None if penalised else ("sample", use_counts, no_nucleus))
             host = self._readback(toks[:n_rows])
             if host[-1]:
                 from .. import ops
                 ops.check_status(self.runner.status)
             tokens = host[:-1]
-        else:
-            self.runner.step(entries, check=False)
-            if penalised:
-                self.sampler.observe(self.runner.last_ctx, penalised)
         self.h2d_bytes += self.runner.last_h2d_bytes
         finished = set(self.scheduler.update(tokens))
         for e, t in zip(sampled_entries, tokens):

@@ -233,6 +233,15 @@ class ModelRunner:
         which does this for its slot; call this when slots are handed to requests that start further on."""
         self._uploaded = [[0] * self.num_slots for _ in self.tables]
 
+    def capture_size(self, entries) -> int | None:
+        """The padded entry count of the captured step that would run these entries, or None if they run
+        kernel by kernel (prompt portions, rows wanted other than one per entry, graphs switched off)."""
+        if not self.cuda_graphs or not entries:
+            return None
+        if not all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries):
+            return None
+        return next((b for b in self.GRAPH_BUCKETS if b >= len(entries)), None)
+
     # ------------------------------------------------------------------ running
     def step(self, entries: list[StepEntry], check: bool = True, user=None, post=None, post_key=None):
         """Runs the entries' tokens as one batch.  Returns logits [wanted rows, vocab] (32-bit, on the
@@ -249,10 +258,8 @@ class ModelRunner:
         self.cache.reset_state([e.slot for e in entries if e.start_pos == 0])
         updates = self._table_updates(entries)
         n_rows = sum(len(e.want) for e in entries)
-        decode_only = all(len(e.tokens) == 1 for e in entries)
-        bucket = next((b for b in self.GRAPH_BUCKETS if b >= len(entries)), None)
-        if (self.cuda_graphs and decode_only and bucket is not None and all(len(e.want) == 1 for e in entries)
-                and all(len(u[0]) <= bucket for u in updates) and (post is None or post_key is not None)):
+        bucket = self.capture_size(entries)
+        if bucket and all(len(u[0]) <= bucket for u in updates) and (post is None or post_key is not None):
             logits = self._step_graph(entries, updates, bucket, user, post, post_key)
         else:
             logits = self._step_eager(entries, updates, n_rows, user, post)
@@ -275,7 +282,7 @@ class ModelRunner:
         logits = self.model.forward(ctx, self.cache.views)
         return post(ctx, logits) if post is not None else logits
 
-    USER_INTS_PER_ENTRY = 8   # room in a captured step's buffer for the caller's numbers
+    USER_INTS_PER_ENTRY = 12  # room in a captured step's buffer for the caller's numbers
 
     def _fill_decode(self, lay: MetaLayout, entries, updates, user):
         """_fill for single-token entries, without per-entry array work."""

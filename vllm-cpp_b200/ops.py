@@ -68,7 +68,7 @@ def _declare(L):
         "vcb_attn_merge": [P, P, P, P, I, I, I, I, I, P],
         "vcb_sample": [P, LL, I, I, P, P, P, P],
         "vcb_sample_split": [P, LL, I, I, P, P, P, P, I, P, P],
-        "vcb_count_tokens": [P, P, P, I, I, P],
+        "vcb_count_tokens": [P, P, P, I, I, I, P],
     }
     for name, args in sigs.items():
         fn = getattr(L, name)
@@ -291,9 +291,10 @@ def sample(logits, params, counts, out, no_nucleus=False):
     _call("vcb_sample", _p(logits), logits.stride(0), R, V, _p(params), _p(counts), _p(out), _stream())
 
 
-def count_tokens(ids, slots, counts, n):
+def count_tokens(ids, slots, counts, n, slot_bias=0):
+    """counts[slots[t] - slot_bias, ids[t]] += 1 for tokens whose slot entry less the bias is >= 0."""
     _need(ids, "ids", torch.int32); _need(slots, "slots", torch.int32); _need(counts, "counts", torch.int32)
-    _call("vcb_count_tokens", _p(ids), _p(slots), _p(counts), n, counts.shape[1], _stream())
+    _call("vcb_count_tokens", _p(ids), _p(slots), _p(counts), n, counts.shape[1], slot_bias, _stream())
 
 
 def scatter_i32(dst, idx, val, count, capacity):

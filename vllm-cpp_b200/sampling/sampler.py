@@ -44,20 +44,24 @@ class Sampler:
         if self.counts is None:
             self.counts = torch.zeros((self.num_slots, self.vocab), dtype=torch.int32, device=self.device)
 
-    def observe(self, ctx, penalised_slots: set) -> None:
-        """Counts the step's tokens into their requests' rows (requests without a penalty are skipped)."""
-        if not penalised_slots:
-            return
+    def forget(self, slots: list[int]) -> None:
+        """Clears the counts of slots whose requests start (again) from their first token."""
+        if slots and self.counts is not None:
+            self.counts.index_fill_(0, torch.tensor(slots, dtype=torch.long, device=self.device), 0)
+
+    @staticmethod
+    def token_slots(entries, penalised_slots: set) -> list[int]:
+        """For every token of the step: its request's slot + 1 if that request has a penalty, else 0."""
+        out = []
+        for e in entries:
+            out += [e.slot + 1 if e.slot in penalised_slots else 0] * len(e.tokens)
+        return out
+
+    def observe(self, token_ids: torch.Tensor, token_slots_plus1: torch.Tensor, n: int) -> None:
+        """Counts the step's tokens into their requests' rows; everything is on the device, so a captured step
+        can include it."""
         self._need_counts()
-        fresh = [e.slot for e in ctx.entries if e.start_pos == 0 and e.slot in penalised_slots]
-        if fresh:
-            self.counts.index_fill_(0, torch.tensor(fresh, dtype=torch.long, device=self.device), 0)
-        slot_of_token = np.empty(ctx.T, dtype=np.int32)
-        for i, e in enumerate(ctx.entries):
-            s = ctx.host_q_start[i]
-            slot_of_token[s:s + len(e.tokens)] = e.slot if e.slot in penalised_slots else -1
-        slots = torch.from_numpy(slot_of_token).to(self.device)
-        ops.count_tokens(ctx.token_ids, slots, self.counts, ctx.T)
+        ops.count_tokens(token_ids, token_slots_plus1, self.counts, n, slot_bias=1)
 
     @staticmethod
     def records(options: list[SamplingOptions], steps: list[int], slots: list[int]):
