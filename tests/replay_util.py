@@ -106,7 +106,7 @@ def mixed(requests, seed=0, max_live=4, decode_tail=12):
     return t
 
 
-def run_trace(model_dir, dtype, trace, out_dir, page_size, extra_env=None, timeout=900):
+def run_trace(model_dir, dtype, trace, out_dir, page_size, extra_env=None, timeout=900, extra_args=()):
     """Runs bin/trace_run on the trace; returns per-step arrays [wanted, vocab] (None where nothing was wanted)."""
     out_dir = Path(out_dir)
     out_dir.mkdir(parents=True, exist_ok=True)
@@ -114,7 +114,7 @@ def run_trace(model_dir, dtype, trace, out_dir, page_size, extra_env=None, timeo
     env = dict(os.environ)
     env.update(extra_env or {})
     cmd = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", dtype,
-           "--out", str(out_dir), "--max-tokens", str(trace.max_tokens), "--page-size", str(page_size)]
+           "--out", str(out_dir), "--max-tokens", str(trace.max_tokens), "--page-size", str(page_size), *extra_args]
     r = subprocess.run(cmd, input=text, capture_output=True, text=True, env=env, timeout=timeout)
     assert r.returncode == 0, f"trace_run failed ({r.returncode}):\n{r.stdout[-2000:]}\n{r.stderr[-4000:]}"
     done = [l for l in r.stdout.splitlines() if l.startswith("done ")]

@@ -65,3 +65,15 @@ def test_replay_modes_agree_with_each_other(dtype, model_dirs, tmp_path):
                 rows.setdefault(key, {})[mode] = got[i]
     worst = max(np.abs(v["whole"] - v["mixed"]).max() / np.abs(v["whole"]).max() for v in rows.values())
     assert worst < (1e-5 if dtype == "float32" else 2e-2), worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_replay_mixed_with_poisoned_pages(name, dtype, model_dirs, plain_logits, tmp_path):
+    """The mixed trace again with the cache NaN-filled at the start and every returned page NaN-filled again:
+    a key read from a page's unwritten tail, from a page a window has passed, or from a previous owner's
+    leftovers would turn the logits into NaN."""
+    requests = make_requests(name)
+    trace = R.mixed(requests, seed=1)
+    out = R.run_trace(model_dirs[name], dtype, trace, tmp_path / "out", TINY_PAGE[name], extra_args=["--poison"])
+    compare(name, dtype, trace, out, requests, plain_logits)

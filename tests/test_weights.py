@@ -104,3 +104,14 @@ def test_random_weights_mode(tmp_path):
     w = tc["model.layers.0.mlp.up_proj.weight"]
     assert abs(w.std().item() - 0.02) < 0.002 and abs(tc["model.norm.weight"].mean().item() - 1) < 0.05
     assert {s.name: s.shape for s in expected_tensors(tiny_config("B"))}["model.layers.2.self_attn.o_proj.weight"] == (96, 192)
+
+
+def test_shard_index_is_checked(tmp_path):
+    import json
+    cfg = tiny_config("A")
+    d = write_random_model(cfg, 1, tmp_path / "m")
+    (d / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"x": "model.safetensors", "y": "model-00002.safetensors"}}))
+    with pytest.raises(WeightError, match="model-00002.safetensors"):
+        open_model_weights(d, torch.float32, "cpu")
+    (d / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"x": "model.safetensors"}}))
+    assert "model.norm.weight" in open_model_weights(d, torch.float32, "cpu")

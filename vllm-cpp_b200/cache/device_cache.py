@@ -106,3 +106,12 @@ class DeviceCache:
         for g, t in zip(self.layout.groups, self.tensors):
             if g.paged:
                 t.fill_(value)
+
+    def poison_pages(self, runtime_group: int, pages: list[int], value: float = float("nan")) -> None:
+        """The same for the pages a request gives back: whoever gets them next must write before it reads."""
+        pages = [p for p in pages if p >= 0]
+        if not pages:
+            return
+        for g, t in zip(self.layout.groups, self.tensors):
+            if g.paged and g.runtime_index == runtime_group:
+                t[:, torch.tensor(pages, dtype=torch.long, device=t.device)] = value

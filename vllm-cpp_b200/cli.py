@@ -72,6 +72,7 @@ def main(argv=None) -> int:
     max_tokens = -(-args.max_tokens // args.page_size) * args.page_size
     llm = LLM(args.model_path, engine=EngineConfig(dtype=args.dtype, page_size=args.page_size, max_tokens=max_tokens,
                                                    max_num_seqs=args.max_batch, max_step_tokens=args.max_step_tokens))
+    llm.debug = args.debug
     print(f"Model loaded in {int((time.time() - t0) * 1000)} ms", file=sys.stderr)
     for i, p in enumerate(prompts):
         print(f"Input tokens (raw) [{i}]: {len(p)} tokens", file=sys.stderr)

@@ -72,6 +72,8 @@ class LLM:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self._pinned = None
+        self.debug = False   # one structured line per step on standard error
+        self._step_index = 0
 
     # ---- the reference's engine surface ----
     def submit_tokens(self, prompt_tokens, max_new_tokens: int = MAX_NEW_TOKENS, temperature: float = TEMPERATURE,
@@ -103,6 +105,21 @@ class LLM:
         self._options.pop(request_id, None)
 
     def step(self) -> EngineOutput:
+        import time
+        t0 = time.perf_counter()
+        out = self._step()
+        if self.debug:
+            import sys
+            c = self.scheduler.cache()
+            free = [c.free_pages(g) for g in range(c.num_groups())]
+            print(f"[step {self._step_index}] prompt_tokens={out.num_prompt_tokens} generation_tokens={out.num_generation_tokens} "
+                  f"sampled={len(out.new_token_ids)} finished={sum(out.finished)} preempted={len(out.preempted)} "
+                  f"waiting={self.scheduler.num_waiting()} running={self.scheduler.num_running()} free_pages={free} "
+                  f"ms={(time.perf_counter() - t0) * 1e3:.2f}", file=sys.stderr, flush=True)
+        self._step_index += 1
+        return out
+
+    def _step(self) -> EngineOutput:
         out = EngineOutput()
         sched = self.scheduler.schedule()
         out.preempted = list(sched.preempted)

@@ -128,6 +128,17 @@ def open_model_weights(model_dir, compute_dtype: torch.dtype, device) -> WeightS
     files = sorted(model_dir.glob("*.safetensors"))
     if not files:
         raise WeightError(f"{model_dir}: no .safetensors file in the model folder")
+    index = model_dir / "model.safetensors.index.json"
+    if index.is_file():
+        # a sharded checkpoint says which file holds which tensor: every file it names must be there
+        import json
+        try:
+            named = set(json.loads(index.read_text()).get("weight_map", {}).values())
+        except (json.JSONDecodeError, AttributeError):
+            raise WeightError(f"{index}: not a valid shard index") from None
+        gone = sorted(n for n in named if not (model_dir / n).is_file())
+        if gone:
+            raise WeightError(f"{model_dir}: the shard index names files that are missing: {gone}")
     tensors: dict[str, torch.Tensor] = {}
     for f in files:
         for name, t in read_safetensors(f).items():
