@@ -12,7 +12,7 @@
 //  * Q.K^T and P.V are mma.sync m16n8k16 products (bf16 in, f32 accumulate) fed by
 //    ldmatrix from a 16-byte XOR-swizzled layout;
 //  * the four warps either take four different row groups and all keys of a tile
-//    (prompt portions: 128 rows a block, two 16-row tiles a warp) or the same 16 rows and a quarter of the
+//    (prompt portions: 128 rows a block on eight warps) or the same 16 rows and a quarter of the
 //    tile's keys each (single decoded tokens: few rows, long key ranges), their
 //    partial softmax states merged through shared memory at the end.
 // Rows beyond the item's real rows and keys beyond the slice are zero-filled and
@@ -34,7 +34,6 @@
 namespace {
 
 constexpr int BN = 64;        // keys per tile
-constexpr int NT = 128;       // threads per block
 constexpr int ITEM_INTS = 6;  // entry, q0, nq, slice, nslices, decode index
 
 struct AttnArgs {
@@ -129,11 +128,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 
-// WR row groups x WK key groups = 4 multiplying warps; TMA adds a fifth warp that only issues tile loads.
+// WR row groups x WK key groups multiplying warps, MR tiles of 16 rows each; TMA adds one warp that only issues
+// tile loads.
 template <int HD, int WR, int WK, int MR, bool TMA>
-__global__ __launch_bounds__(TMA ? NT + 32 : NT) void attn_mma_kernel(const __grid_constant__ CUtensorMap kv_map,
+__global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel(const __grid_constant__ CUtensorMap kv_map,
                                                                         AttnArgs a) {
-    static_assert(WR * WK == 4 && HD % 64 == 0, "layout");
+    static_assert(HD % 64 == 0 && BN % (16 * WK) == 0, "layout");
+    constexpr int NW = WR * WK;     // multiplying warps
+    constexpr int NT = NW * 32;     // their threads
     constexpr int RMAX = 16 * WR * MR;   // rows a block holds: WR warp groups x MR tiles of 16 rows each
     constexpr int CH = HD / 8;      // 16-byte chunks per row
     constexpr int ROWB = HD * 2;
@@ -158,7 +160,7 @@ __global__ __launch_bounds__(TMA ? NT + 32 : NT) void attn_mma_kernel(const __gr
     pdl_trigger();
     pdl_wait();   // the queries and the newest keys come from the kernel before this one
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int wr = (warp & 3) / WK, wk = (warp & 3) % WK;
+    const int wr = (warp % NW) / WK, wk = (warp % NW) % WK;
     const int* item = a.items + (size_t)blockIdx.x * ITEM_INTS;
     const int e = item[0], q0 = item[1], nq = item[2], slice = item[3], nslices = item[4], dec_index = item[5];
 
@@ -192,7 +194,7 @@ __global__ __launch_bounds__(TMA ? NT + 32 : NT) void attn_mma_kernel(const __gr
     if (TMA && tid == 0) {
         for (int st = 0; st < STAGES; ++st) {
             mbar_init(full_bar(st), 1);
-            mbar_init(empty_bar(st), 4);   // one arrival per multiplying warp
+            mbar_init(empty_bar(st), NW);   // one arrival per multiplying warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -242,7 +244,7 @@ __global__ __launch_bounds__(TMA ? NT + 32 : NT) void attn_mma_kernel(const __gr
     }
     __syncthreads();   // Q and the barriers are in shared memory
 
-    if (TMA && warp == 4) {
+    if (TMA && warp == NW) {
         // ---- TMA producer: one box of [page_size keys x 64 lanes] per page, per half of head_dim, for K and V ----
         if (lane == 0) {
             const int pages_per_tile = BN / ps;
@@ -297,7 +299,7 @@ __global__ __launch_bounds__(TMA ? NT + 32 : NT) void attn_mma_kernel(const __gr
         ok_b[mr] = r_a[mr] + 8 < R;
     }
 
-    if (warp < 4) {
+    if (warp < NW) {
         // ---- one 16-row tile per warp: its Q fragments stay in registers; two: they are re-read per key tile ----
         uint32_t qf[MR == 1 ? HD / 16 : 1][4];
         if (MR == 1) {
@@ -468,7 +470,7 @@ __global__ __launch_bounds__(TMA ? NT + 32 : NT) void attn_mma_kernel(const __gr
     // ---- partial states -> shared memory: o_s[wk][row][HD], ml_s[wk][row][2] ----
     float* o_s = reinterpret_cast<float*>(k_s);             // WK * RMAX x HD floats, over the K and V stages
     float* ml_s = o_s + WK * RMAX * HD;                     // WK * RMAX x 2 floats
-    if (warp < 4) {
+    if (warp < NW) {
 #pragma unroll
         for (int mr = 0; mr < MR; ++mr) {
             l_run[mr][0] += __shfl_xor_sync(0xffffffffu, l_run[mr][0], 1);
@@ -655,20 +657,20 @@ int launch(const AttnArgs& a, int n_items, cudaStream_t stream) {
         }
         opted = true;
     }
-    launch_pdl(kern, dim3(n_items, a.nkv * hchunks), dim3(TMA ? NT + 32 : NT), smem, stream, map, a);
+    launch_pdl(kern, dim3(n_items, a.nkv * hchunks), dim3(WR * WK * 32 + (TMA ? 32 : 0)), smem, stream, map, a);
     VCB_CHECK_LAUNCH("attn_mma");
     return 0;
 }
 
 template <int HD, bool TMA>
 int launch_rows(const AttnArgs& a, int n_items, int rows_max, cudaStream_t stream) {
-    return rows_max == 16 ? launch<HD, 1, 4, 1, TMA>(a, n_items, stream) : launch<HD, 4, 1, 2, TMA>(a, n_items, stream);
+    return rows_max == 16 ? launch<HD, 1, 4, 1, TMA>(a, n_items, stream) : launch<HD, 8, 1, 1, TMA>(a, n_items, stream);
 }
 
 }  // namespace
 
-// rows_max: 16 (single decoded tokens; the four warps split each tile's keys) or 128 (prompt portions; each warp
-// holds two 16-row tiles, so every K and V fragment it reads feeds two MMAs).
+// rows_max: 16 (single decoded tokens; four warps split each tile's keys) or 128 (prompt portions; eight warps of
+// 16 rows each share the K and V tiles, enough independent MMA chains per SM to keep the tensor pipe fed).
 // Only bfloat16 and head_dim 64 or 128; the caller falls back to vcb_attn_paged otherwise.
 VCB_API int vcb_attn_mma_supported(int dtype, int hd) { return dtype == VCB_BF16 && (hd == 64 || hd == 128); }
 
