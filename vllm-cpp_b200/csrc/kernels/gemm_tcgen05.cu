@@ -820,10 +820,17 @@ VCB_API int vcb_gemm_bf16_tn(const void* W, const void* X, void* out, int out_dt
     else if (M <= 128) rc = launch<256, 4, 1, 2>(W, X, g, ldw, ldx, splits, stream);
     else if (pairs_enabled() && M >= 512) rc = launch_pair(W, M, X, g, ldw, ldx, stream);
     else {
-        // 256 features x 256 or 192 tokens a unit: whichever leaves the last round over the SMs less empty
-        const long long mu = (M + 2 * BM - 1) / (2 * BM);
-        auto cost = [&](int bn) { const long long units = mu * ((N + bn - 1) / bn); return ((units + num_sms() - 1) / num_sms()) * bn; };
-        if (cost(192) < cost(256)) rc = launch<192, 3, 2, 1>(W, X, g, ldw, ldx, splits, stream);
+        // Units of 128 x 256 (two accumulator buffers: the epilogue of one unit overlaps the MMAs of the next),
+        // 256 x 256 or 256 x 192 tokens: whichever needs the least time over the SMs, counting whole rounds.
+        // Measured at 2,048 tokens the 128 x 256 units are as fast per flop as the 256-feature ones (the ring of
+        // stages, not the traffic, bounds the main loop), so ties go to them.
+        auto cost = [&](int mt, int bn) {
+            const long long units = (long long)((M + mt * BM - 1) / (mt * BM)) * ((N + bn - 1) / bn);
+            return ((units + num_sms() - 1) / num_sms()) * (long long)(mt * bn);
+        };
+        const long long c1 = cost(1, 256), c2 = cost(2, 256), c3 = cost(2, 192);
+        if (c1 <= c2 && c1 <= c3) rc = launch<256, 4, 1, 2>(W, X, g, ldw, ldx, splits, stream);
+        else if (c3 < c2) rc = launch<192, 3, 2, 1>(W, X, g, ldw, ldx, splits, stream);
         else rc = launch<256, 3, 2, 1>(W, X, g, ldw, ldx, splits, stream);
     }
     return rc;
