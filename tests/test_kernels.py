@@ -364,7 +364,8 @@ def test_kernels_refuse_what_they_cannot_do():
 @pytest.mark.parametrize("M,T,K,splits", [
     (128, 16, 64, 1), (128, 1, 64, 1), (64, 3, 96, 1), (200, 17, 200, 1), (384, 8, 4096, 4), (6144, 8, 4096, 3),
     (4096, 64, 1024, 2), (1000, 33, 520, 2), (256, 100, 256, 1), (384, 256, 512, 1), (300, 700, 328, 1),
-    (4096, 2048, 512, 1), (128, 130, 8, 1), (6144, 2048, 256, 1), (6144, 700, 128, 1)])
+    (4096, 2048, 512, 1), (128, 130, 8, 1), (6144, 2048, 256, 1), (6144, 700, 128, 1),
+    (4096, 256, 1024, 4), (600, 513, 2048, 3), (1000, 160, 1536, 8)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gemm_bf16_tn(M, T, K, splits, out_dtype):
     """The tcgen05/TMA product against 64-bit: tile edges in every dimension, k tails, k-slices, 1 to 2048 tokens."""
@@ -391,6 +392,37 @@ def test_gemm_bf16_tn(M, T, K, splits, out_dtype):
         one = torch.empty((1, M), dtype=out_dtype, device=dev())
         ops.gemm_bf16_tn(w, x[T - 1:T].contiguous(), one, 1, status)
         assert torch.equal(one[0], out[T - 1])
+
+
+@pytest.mark.parametrize("shape", range(7))
+@pytest.mark.parametrize("M,T,K,splits", [(300, 5, 200, 1), (520, 300, 1096, 1), (520, 300, 1096, 3), (128, 700, 64, 1)])
+def test_gemm_bf16_tn_every_unit_shape(shape, M, T, K, splits):
+    """Each unit shape of the kernel, forced, at sizes that are not the ones it is chosen for: many token tiles
+    of a small shape, one ragged tile of a large one, k-slices."""
+    from vllm_cpp_b200 import ops
+    torch.manual_seed(shape + M + T)
+    w = torch.randn(M, K, device=dev()).to(torch.bfloat16)
+    x = torch.randn(T, K, device=dev()).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    S = ops.gemm_effective_splits(K, splits)
+    out = torch.full((S, T, M) if S > 1 else (T, M), float("nan"), dtype=torch.float32, device=dev())
+    ops.gemm_bf16_tn(w, x, out, splits, status, shape=shape)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    got = out.double().sum(0) if S > 1 else out.double()
+    torch.testing.assert_close(got, x.double() @ w.double().T, rtol=1e-4, atol=K * 2.0 ** -24 * 64)
+    with pytest.raises(ops.KernelError, match="no unit shape"):
+        ops.gemm_bf16_tn(w, x, out, splits, status, shape=7)
+
+
+def test_choose_splits_fills_the_sms():
+    from vllm_cpp_b200.parts.linear import choose_splits
+    assert choose_splits(6144, 256, 4096) == 3      # 48 units of 128 x 256 -> 144
+    assert choose_splits(4096, 256, 12288) == 4     # 32 units -> 128
+    assert choose_splits(4096, 512, 4096) == 2      # 64 units -> 128
+    assert choose_splits(4096, 1024, 4096) == 1     # 128 units already
+    assert choose_splits(24576, 2048, 4096) == 1
+    assert choose_splits(6144, 8, 4096) == 3
 
 
 def test_gemm_bf16_tn_refuses_unaligned_rows():
@@ -454,7 +486,8 @@ def test_sampling_split_over_blocks_matches_plain():
     assert got[0] == 17
 
 
-@pytest.mark.parametrize("I,T,K", [(128, 256, 64), (200, 300, 96), (12288 // 8, 2048, 512), (72, 130, 264)])
+@pytest.mark.parametrize("I,T,K", [(128, 256, 64), (200, 300, 96), (12288 // 8, 2048, 512), (72, 130, 264), (264, 160, 128),
+                                   (1024, 385, 64)])
 def test_gemm_bf16_swiglu(I, T, K):
     """The product with the SiLU-gate in its epilogue against 64-bit."""
     from vllm_cpp_b200 import ops

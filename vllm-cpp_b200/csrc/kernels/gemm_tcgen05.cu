@@ -796,12 +796,60 @@ VCB_API int vcb_gemm_bf16_swiglu(const void* W, const void* X, void* out, int I,
     GemmArgs g{out, VCB_BF16, I, N, K, ldc, 0, total_kb, 1, I, status};
     // the weight map spans both halves so that the up tile is addressed as row I + m
     if (pairs_enabled()) return launch_pair(W, 2LL * I, X, g, ldw, ldx, stream);
+    // 192 or 256 tokens a unit: whichever leaves fewer whole rounds of work over the SMs
+    auto cost = [&](int bn) {
+        const long long units = (long long)((I + BM - 1) / BM) * ((N + bn - 1) / bn);
+        return ((units + num_sms() - 1) / num_sms()) * (long long)bn;
+    };
+    if (cost(192) < cost(256)) return launch_maps<192, 3, 2, 1>(W, 2LL * I, X, g, ldw, ldx, 1, stream);
     return launch_maps<256, 3, 2, 1>(W, 2LL * I, X, g, ldw, ldx, 1, stream);
 }
 
-VCB_API int vcb_gemm_bf16_tn(const void* W, const void* X, void* out, int out_dtype, int M, int N, int K,
-                             long long ldw, long long ldx, long long ldc, int splits, long long split_stride,
-                             int* status, cudaStream_t stream) {
+// The unit shapes that are built: tokens per tile (BN), stages of the ring, 128-feature tiles per unit, accumulators.
+enum GemmShape { SHAPE_N16 = 0, SHAPE_N32, SHAPE_N64, SHAPE_N128, SHAPE_N256, SHAPE_M256_N192, SHAPE_M256_N256, SHAPE_COUNT };
+
+namespace {
+int launch_shape(int shape, const void* W, const void* X, const GemmArgs& g, long long ldw, long long ldx, int splits,
+                 cudaStream_t stream) {
+    switch (shape) {
+        case SHAPE_N16: return launch<16, 8, 1, 2>(W, X, g, ldw, ldx, splits, stream);
+        case SHAPE_N32: return launch<32, 8, 1, 2>(W, X, g, ldw, ldx, splits, stream);
+        case SHAPE_N64: return launch<64, 8, 1, 2>(W, X, g, ldw, ldx, splits, stream);
+        case SHAPE_N128: return launch<128, 6, 1, 2>(W, X, g, ldw, ldx, splits, stream);
+        case SHAPE_N256: return launch<256, 4, 1, 2>(W, X, g, ldw, ldx, splits, stream);
+        case SHAPE_M256_N192: return launch<192, 3, 2, 1>(W, X, g, ldw, ldx, splits, stream);
+        case SHAPE_M256_N256: return launch<256, 3, 2, 1>(W, X, g, ldw, ldx, splits, stream);
+    }
+    vcb_set_error("gemm_bf16_tn: no unit shape %d (0..%d)", shape, SHAPE_COUNT - 1);
+    return -1;
+}
+
+int pick_shape(int M, int N, int splits) {
+    if (N <= 16) return SHAPE_N16;
+    if (N <= 32) return SHAPE_N32;
+    if (N <= 64) return SHAPE_N64;
+    if (N <= 128) return SHAPE_N128;
+    // a sliced product has too few units for the SMs: the smallest units with 256 tokens measured fastest
+    // at every size from 160 to 1,024 tokens
+    if (M <= 128 || splits > 1) return SHAPE_N256;
+    // Units of 128 x 256 (two accumulator buffers: the epilogue of one unit overlaps the MMAs of the next),
+    // 256 x 256 or 256 x 192 tokens: whichever needs the least time over the SMs, counting whole rounds.
+    // Measured at 2,048 tokens the 128 x 256 units are as fast per flop as the 256-feature ones (the ring of
+    // stages, not the traffic, bounds the main loop), so ties go to them.
+    auto cost = [&](int mt, int bn) {
+        const long long units = (long long)((M + mt * BM - 1) / (mt * BM)) * ((N + bn - 1) / bn);
+        return ((units + num_sms() - 1) / num_sms()) * (long long)(mt * bn);
+    };
+    const long long c1 = cost(1, 256), c2 = cost(2, 256), c3 = cost(2, 192);
+    if (c1 <= c2 && c1 <= c3) return SHAPE_N256;
+    return c3 < c2 ? SHAPE_M256_N192 : SHAPE_M256_N256;
+}
+}  // namespace
+
+// shape < 0: chosen from the sizes; otherwise one of GemmShape, whatever the sizes (tests and measurements).
+VCB_API int vcb_gemm_bf16_tn_shape(const void* W, const void* X, void* out, int out_dtype, int M, int N, int K,
+                                   long long ldw, long long ldx, long long ldc, int splits, long long split_stride,
+                                   int shape, int* status, cudaStream_t stream) {
     VCB_CHECK_ARG(M > 0 && N > 0 && K > 0, "gemm_bf16_tn: bad sizes M=%d N=%d K=%d", M, N, K);
     VCB_CHECK_ARG(K % 8 == 0 && ldw % 8 == 0 && ldx % 8 == 0,
                   "gemm_bf16_tn: inner size %d and row strides %lld, %lld must be multiples of 8 (16-byte rows for TMA)", K, ldw, ldx);
@@ -812,26 +860,12 @@ VCB_API int vcb_gemm_bf16_tn(const void* W, const void* X, void* out, int out_dt
     const int kb_per_split = (total_kb + splits - 1) / splits;
     splits = (total_kb + kb_per_split - 1) / kb_per_split;
     GemmArgs g{out, out_dtype, M, N, K, ldc, split_stride, kb_per_split, splits, 0, status};
-    int rc;
-    if (N <= 16) rc = launch<16, 8, 1, 2>(W, X, g, ldw, ldx, splits, stream);
-    else if (N <= 32) rc = launch<32, 8, 1, 2>(W, X, g, ldw, ldx, splits, stream);
-    else if (N <= 64) rc = launch<64, 8, 1, 2>(W, X, g, ldw, ldx, splits, stream);
-    else if (N <= 128) rc = launch<128, 6, 1, 2>(W, X, g, ldw, ldx, splits, stream);
-    else if (M <= 128) rc = launch<256, 4, 1, 2>(W, X, g, ldw, ldx, splits, stream);
-    else if (pairs_enabled() && M >= 512) rc = launch_pair(W, M, X, g, ldw, ldx, stream);
-    else {
-        // Units of 128 x 256 (two accumulator buffers: the epilogue of one unit overlaps the MMAs of the next),
-        // 256 x 256 or 256 x 192 tokens: whichever needs the least time over the SMs, counting whole rounds.
-        // Measured at 2,048 tokens the 128 x 256 units are as fast per flop as the 256-feature ones (the ring of
-        // stages, not the traffic, bounds the main loop), so ties go to them.
-        auto cost = [&](int mt, int bn) {
-            const long long units = (long long)((M + mt * BM - 1) / (mt * BM)) * ((N + bn - 1) / bn);
-            return ((units + num_sms() - 1) / num_sms()) * (long long)(mt * bn);
-        };
-        const long long c1 = cost(1, 256), c2 = cost(2, 256), c3 = cost(2, 192);
-        if (c1 <= c2 && c1 <= c3) rc = launch<256, 4, 1, 2>(W, X, g, ldw, ldx, splits, stream);
-        else if (c3 < c2) rc = launch<192, 3, 2, 1>(W, X, g, ldw, ldx, splits, stream);
-        else rc = launch<256, 3, 2, 1>(W, X, g, ldw, ldx, splits, stream);
-    }
-    return rc;
+    if (shape < 0 && pairs_enabled() && N > 128 && M >= 512) return launch_pair(W, M, X, g, ldw, ldx, stream);
+    return launch_shape(shape < 0 ? pick_shape(M, N, splits) : shape, W, X, g, ldw, ldx, splits, stream);
+}
+
+VCB_API int vcb_gemm_bf16_tn(const void* W, const void* X, void* out, int out_dtype, int M, int N, int K,
+                             long long ldw, long long ldx, long long ldc, int splits, long long split_stride,
+                             int* status, cudaStream_t stream) {
+    return vcb_gemm_bf16_tn_shape(W, X, out, out_dtype, M, N, K, ldw, ldx, ldc, splits, split_stride, -1, status, stream);
 }

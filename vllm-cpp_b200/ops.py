@@ -57,6 +57,7 @@ def _declare(L):
         "vcb_swiglu": [P, I, I, LL, P, I, I, I, P],
         "vcb_qknorm_rope_kvwrite": [P, I, I, LL, I, P, P, I, I, F, P, I, P, P, P, P, LL, I, I, I, I, I, I, I, P, P],
         "vcb_gemm_bf16_tn": [P, P, P, I, I, I, I, LL, LL, LL, I, LL, P, P],
+        "vcb_gemm_bf16_tn_shape": [P, P, P, I, I, I, I, LL, LL, LL, I, LL, I, P, P],
         "vcb_gemm_effective_splits": [I, I],
         "vcb_gemm_bf16_swiglu": [P, P, P, I, I, I, LL, LL, LL, P, P],
         "vcb_sgemm_tn": [P, P, P, I, I, I, LL, LL, LL, P],
@@ -208,9 +209,13 @@ def gemm_effective_splits(K: int, splits: int) -> int:
     return int(lib().vcb_gemm_effective_splits(K, splits))
 
 
-def gemm_bf16_tn(w, x, out, splits, status):
+GEMM_SHAPES = ("n16", "n32", "n64", "n128", "n256", "m256_n192", "m256_n256")   # unit shapes of the kernel, by index
+
+
+def gemm_bf16_tn(w, x, out, splits, status, shape=-1):
     """out[z, t, m] = sum over k-slice z of w[m, k] x[t, k]   (tcgen05 + TMA; w [M,K], x [T,K] bfloat16).
-    out: [T, M] (bfloat16 or float32, one slice) or [S, T, M] float32 with S = gemm_effective_splits(K, splits)."""
+    out: [T, M] (bfloat16 or float32, one slice) or [S, T, M] float32 with S = gemm_effective_splits(K, splits).
+    ``shape`` forces one of GEMM_SHAPES (an index) whatever the sizes; -1 lets the kernel choose."""
     _need(w, "w", torch.bfloat16, contiguous=False); _need(x, "x", torch.bfloat16, contiguous=False); _need(out, "out")
     M, K = w.shape
     T = x.shape[0]
@@ -222,8 +227,8 @@ def gemm_bf16_tn(w, x, out, splits, status):
     else:
         assert out.shape == (S, T, M) and out.dtype == torch.float32
         ldc, sstride = out.stride(1), out.stride(0)
-    _call("vcb_gemm_bf16_tn", _p(w), _p(x), _p(out), _dt(out), M, T, K, w.stride(0), x.stride(0), ldc, S, sstride,
-          _p(status), _stream())
+    _call("vcb_gemm_bf16_tn_shape", _p(w), _p(x), _p(out), _dt(out), M, T, K, w.stride(0), x.stride(0), ldc, S, sstride,
+          int(shape), _p(status), _stream())
 
 
 def gemm_bf16_swiglu(w_gate_up, x, out, status):

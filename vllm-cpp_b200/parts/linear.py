@@ -19,6 +19,7 @@ import torch
 from .. import ops
 
 NUM_SMS = 148
+MAX_SPLIT_TOKENS = 1024     # above this many tokens a product is never cut into k-slices
 LIBRARY_GEMM = os.environ.get("VLLM_CPP_B200_LIBRARY_GEMM", "0") == "1"
 
 
@@ -30,13 +31,30 @@ def token_tile(T: int) -> int:
 
 
 def choose_splits(M: int, T: int, K: int, max_splits: int = 8) -> int:
-    """Number of k-slices for a product that streams weights (few tokens): the kernel's persistent blocks, one
-    per SM, walk (feature tile x token tile x k-slice) units round robin, so the slices are chosen to spread
-    the k-blocks evenly over the SMs; each extra slice costs one more partial sum to write and add."""
-    if T > 128:
-        return 1      # enough tokens per weight tile: the product is compute bound and partial sums only cost traffic
-    tiles = -(-M // 128) * -(-T // token_tile(T))
+    """Number of k-slices of a product whose units (feature tile x token tile) do not fill the SMs by themselves.
+    The kernel's persistent blocks, one per SM, walk (feature tile x token tile x k-slice) units round robin, so
+    the slices are chosen to spread the k-blocks evenly over the SMs in whole rounds; each extra slice costs one
+    more 32-bit partial sum to write and to add."""
     total_kb = -(-K // 64)
+    if T > MAX_SPLIT_TOKENS:
+        return 1      # units in plenty: partial sums would only cost traffic
+    if T > 128:
+        # 128 x 256 units (the shape the kernel uses for sliced products of more than 128 tokens).  Times in us,
+        # fitted to measurements at 160 to 1,024 tokens: half a microsecond per k-block of a unit, two per unit,
+        # and the partial sums written and read back at about 5 TB/s.
+        tiles = -(-M // 128) * -(-T // 256)
+        best, best_cost = 1, None
+        for s in range(1, max_splits + 1):
+            kb = -(-total_kb // s)
+            if s > 1 and kb < 8:
+                break
+            s_eff = -(-total_kb // kb)
+            rounds = -(-tiles * s_eff // NUM_SMS)
+            cost = rounds * (0.5 * kb + 2.0) + (s_eff * T * M * 8 / 5e6 if s_eff > 1 else 0.0)
+            if best_cost is None or cost < best_cost - 1e-9:
+                best, best_cost = s, cost
+        return best
+    tiles = -(-M // 128) * -(-T // token_tile(T))
     best, best_cost = 1, None
     for s in range(1, max_splits + 1):
         kb = -(-total_kb // s)
