@@ -69,7 +69,17 @@ def test_swiglu(dtype):
     gu = (3 * torch.randn(T, 2 * I, device=dev())).to(dtype)
     out = torch.empty(T, I, device=dev(), dtype=dtype)
     ops.swiglu(gu, out)
-    g, u = gu[:, :I].double(), gu[:, I:].double()
+    g, u = gu[:, 0::2].double(), gu[:, 1::2].double()     # gate and up alternate along a row
+    torch.testing.assert_close(out.double(), g / (1 + torch.exp(-g)) * u, **tol(dtype))
+    # the 16-byte path (I a multiple of 8), far-out gate values included
+    gu = (30 * torch.randn(T, 2 * I, device=dev())).to(dtype)
+    ops.swiglu(gu, out)
+    g, u = gu[:, 0::2].double(), gu[:, 1::2].double()
+    torch.testing.assert_close(out.double(), g / (1 + torch.exp(-g)) * u, **tol(dtype))
+    gu = gu[:, :2 * 37].contiguous()
+    out = torch.empty(T, 37, device=dev(), dtype=dtype)
+    ops.swiglu(gu, out)
+    g, u = gu[:, 0::2].double(), gu[:, 1::2].double()
     torch.testing.assert_close(out.double(), g / (1 + torch.exp(-g)) * u, **tol(dtype))
 
 
@@ -443,7 +453,7 @@ def test_partial_sum_inputs(out_dtype):
     out = torch.empty(T, I, device=dev(), dtype=out_dtype)
     ops.swiglu(parts, out)
     tot = parts.double().sum(0)
-    g, u = tot[:, :I], tot[:, I:]
+    g, u = tot[:, 0::2], tot[:, 1::2]
     torch.testing.assert_close(out.double(), g / (1 + torch.exp(-g)) * u, **tol(out_dtype))
 
     nh, nkv, hd, ps, num_pages, eps = 4, 2, 32, 4, 6, 1e-6
@@ -487,21 +497,34 @@ def test_sampling_split_over_blocks_matches_plain():
 
 
 @pytest.mark.parametrize("I,T,K", [(128, 256, 64), (200, 300, 96), (12288 // 8, 2048, 512), (72, 130, 264), (264, 160, 128),
-                                   (1024, 385, 64)])
-def test_gemm_bf16_swiglu(I, T, K):
-    """The product with the SiLU-gate in its epilogue against 64-bit."""
+                                   (1024, 385, 64), (100, 7, 64)])
+@pytest.mark.parametrize("shape", [-1, 0, 2, 3, 4, 5, 6])
+def test_gemm_bf16_swiglu(I, T, K, shape):
+    """The product with the SiLU-gate in its epilogue against 64-bit, for the chosen and for forced unit shapes.
+    Gate values reach far below -87, where silu is zero to every precision."""
     from vllm_cpp_b200 import ops
+    if shape >= 0 and T * I > 1 << 20:
+        pytest.skip("the large case runs with the chosen shape only")
     torch.manual_seed(I + T)
     w = (torch.randn(2 * I, K, device=dev()) * 0.2).to(torch.bfloat16)
+    w[0::2][:: 5] *= 40          # some gates far out on both sides
     x = torch.randn(T, K, device=dev()).to(torch.bfloat16)
     out = torch.full((T, I), float("nan"), dtype=torch.bfloat16, device=dev())
     status = torch.zeros(1, dtype=torch.int32, device=dev())
-    ops.gemm_bf16_swiglu(w, x, out, status)
+    ops.gemm_bf16_swiglu(w, x, out, status, shape=shape)
     torch.cuda.synchronize()
     assert status.item() == 0
     gu = x.double() @ w.double().T
-    g, u = gu[:, :I], gu[:, I:]
-    torch.testing.assert_close(out.double(), g / (1 + torch.exp(-g)) * u, rtol=2e-2, atol=2e-2)
+    g, u = gu[:, 0::2], gu[:, 1::2]
+    assert g.min() < -100 and g.max() > 100
+    want = g / (1 + torch.exp(-g)) * u
+    torch.testing.assert_close(out.double(), want, rtol=2e-2, atol=2e-2)
+    # and the same numbers as the product followed by the SiLU-gate kernel, to bfloat16 rounding
+    full = torch.empty(T, 2 * I, dtype=torch.float32, device=dev())
+    ops.gemm_bf16_tn(w, x, full, 1, status)
+    two = torch.empty_like(out)
+    ops.swiglu(full, two)
+    torch.testing.assert_close(out.float(), two.float(), rtol=2 ** -7, atol=1e-30)
 
 
 def test_qknorm_fast_path_matches_general_path():

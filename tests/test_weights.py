@@ -83,6 +83,8 @@ def test_what_is_stored_is_kept():
     f32 = WeightStore(t, torch.float32, "cpu")
     assert f32.vector("g16").dtype == torch.float32 and f32.matrix("m").dtype == torch.float32
     assert torch.equal(bf.matrices(["m", "m"])[4:], t["m"].to(torch.bfloat16))
+    both = bf.matrices(["m", "m"], interleave=True)
+    assert torch.equal(both[0::2], t["m"].to(torch.bfloat16)) and torch.equal(both[1::2], both[0::2])
     with pytest.raises(WeightError, match="integer table"):
         bf.table("m")
     with pytest.raises(WeightError, match="not in the checkpoint"):

@@ -182,7 +182,7 @@ VCB_API int vcb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, in
 }
 
 // ---------------------------------------------------------------------------
-// SiLU-gate product: out[t,i] = silu(gu[t,i]) * gu[t,I+i]
+// SiLU-gate product: out[t,i] = silu(gu[t,2i]) * gu[t,2i+1]   (gate and up alternate along a row)
 // ---------------------------------------------------------------------------
 template <typename TIN, typename T>
 __global__ void swiglu_kernel(const TIN* __restrict__ gu, int S, size_t s_stride, T* __restrict__ out, int I, size_t total) {
@@ -192,8 +192,8 @@ __global__ void swiglu_kernel(const TIN* __restrict__ gu, int S, size_t s_stride
         const size_t t = idx / I, i = idx % I;
         float g = 0.f, u = 0.f;
         for (int s = 0; s < S; ++s) {   // k-slice partials of the product are added in slice order
-            g += to_f32(gu[s * s_stride + t * 2 * I + i]);
-            u += to_f32(gu[s * s_stride + t * 2 * I + I + i]);
+            g += to_f32(gu[s * s_stride + t * 2 * I + 2 * i]);
+            u += to_f32(gu[s * s_stride + t * 2 * I + 2 * i + 1]);
         }
         out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
     }
@@ -203,14 +203,15 @@ __global__ void swiglu_kernel(const TIN* __restrict__ gu, int S, size_t s_stride
 __global__ void swiglu_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I8, size_t total8) {
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I8, i = idx % I8;
-        const uint4 g4 = reinterpret_cast<const uint4*>(gu + t * 16 * I8)[i];
-        const uint4 u4 = reinterpret_cast<const uint4*>(gu + t * 16 * I8 + 8 * (size_t)I8)[i];
-        const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
+        // 16 inputs (8 gate/up pairs) -> 8 outputs
+        const uint4 a4 = reinterpret_cast<const uint4*>(gu + t * 16 * I8)[2 * i];
+        const uint4 b4 = reinterpret_cast<const uint4*>(gu + t * 16 * I8)[2 * i + 1];
+        const uint32_t w[8] = {a4.x, a4.y, a4.z, a4.w, b4.x, b4.y, b4.z, b4.w};   // each word: gate (low half), up (high half)
         uint32_t ow[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            const float g0 = __uint_as_float(gw[k] << 16), g1 = __uint_as_float(gw[k] & 0xffff0000u);
-            const float u0 = __uint_as_float(uw[k] << 16), u1 = __uint_as_float(uw[k] & 0xffff0000u);
+            const float g0 = __uint_as_float(w[2 * k] << 16), u0 = __uint_as_float(w[2 * k] & 0xffff0000u);
+            const float g1 = __uint_as_float(w[2 * k + 1] << 16), u1 = __uint_as_float(w[2 * k + 1] & 0xffff0000u);
             __nv_bfloat162 o = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
             ow[k] = *reinterpret_cast<uint32_t*>(&o);
         }
@@ -218,7 +219,8 @@ __global__ void swiglu_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu, __n
     }
 }
 
-// gate_up: [S, T, 2I] of in_dtype (S partial sums, s_stride elements apart); out: [T, I] of out_dtype
+// gate_up: [S, T, 2I] of in_dtype (S partial sums, s_stride elements apart), gate_i at 2i and up_i at 2i+1;
+// out: [T, I] of out_dtype
 VCB_API int vcb_swiglu(const void* gate_up, int in_dtype, int S, long long s_stride, void* out, int out_dtype, int T,
                        int I, cudaStream_t stream) {
     if (T == 0) return 0;

@@ -126,7 +126,7 @@ struct GemmArgs {
     long long split_stride;   // elements between the partials of consecutive k-slices
     int kb_per_split;         // 64-wide k-blocks per slice
     int splits;               // k-slices
-    int swiglu_rows;          // 0, or I: W is [gate (I rows); up (I rows)] and the output is silu(gate) * up, [tokens, I]
+    int swiglu;               // 1: rows 2i and 2i+1 of W are gate_i and up_i, and the output is silu(gate) * up, [tokens, M/2] bfloat16
     int* status;
 };
 
@@ -144,6 +144,39 @@ struct Smem {
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// silu(z) = z / (1 + exp(-z)) with the fast exponential and division (a few ulp; the result is rounded to
+// bfloat16).  The exponent is capped so that the divisor stays where the fast division is defined; below
+// z = -87 the result is about -1e-36 instead of a smaller denormal.
+__device__ __forceinline__ float silu_fast(float z) { return __fdividef(z, 1.0f + __expf(fminf(-z, 87.0f))); }
+
+// Epilogue of a product whose weight rows alternate gate_i, up_i: lane 2i holds gate_i, lane 2i+1 up_i of the
+// same token, so one shuffle brings them together.  v: CHUNK token columns of this lane's row m; writes
+// out[token][m / 2] for even m.  Every lane of the warp must call it.
+template <int CHUNK>
+__device__ __forceinline__ void swiglu_store(uint32_t (*v)[16], __nv_bfloat16* out, long long ldc, int m, int M, int n_first,
+                                             int N, int lane) {
+#pragma unroll
+    for (int jj = 0; jj < CHUNK; ++jj) {
+        const float mine = __uint_as_float(v[jj / 16][jj % 16]);
+        const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+        if (!(lane & 1) && m + 1 < M && n_first + jj < N)
+            out[(size_t)(n_first + jj) * ldc + (m >> 1)] = __float2bfloat16_rn(silu_fast(mine) * other);
+    }
+}
+
+// Order of the (feature tile, token tile) pairs: token tiles fastest, in groups of up to TOKEN_TILE_GROUP, so
+// that the units in flight at one time (one per SM) share few feature tiles -- every weight tile is then
+// fetched from HBM once and read by its group's blocks from L2 -- while the group's tokens stay in L2 too.
+// (With feature tiles fastest a round touched every weight row, and 2,048 tokens read the weights five times.)
+constexpr int TOKEN_TILE_GROUP = 8;
+__device__ __forceinline__ void tile_of(int idx, int m_tiles, int n_tiles, int& mi, int& ni) {
+    const int per_group = m_tiles * TOKEN_TILE_GROUP;
+    const int grp = idx / per_group, r = idx - grp * per_group;
+    const int gsize = min(TOKEN_TILE_GROUP, n_tiles - grp * TOKEN_TILE_GROUP);
+    mi = r / gsize;
+    ni = grp * TOKEN_TILE_GROUP + (r - mi * gsize);
 }
 
 // Persistent: each block walks the work units blockIdx.x, blockIdx.x + gridDim.x, ...; a unit is
@@ -173,7 +206,7 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_kb = (g.K + BK - 1) / BK;
-    const int unit_rows = g.swiglu_rows ? BM : BM * MT;   // output features per unit
+    const int unit_rows = BM * MT;   // rows of W per unit
     const int m_tiles = (g.M + unit_rows - 1) / unit_rows;
     const int n_tiles = (g.N + BN - 1) / BN;
     const int units = m_tiles * n_tiles * g.splits;
@@ -204,9 +237,10 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
     // unit -> (first feature, first token, first k-block, k-blocks)
     auto unit_at = [&](int u, int& m0, int& n0, int& kb0, int& nkb, int& z) {
         z = u / (m_tiles * n_tiles);
-        const int rem = u % (m_tiles * n_tiles);
-        n0 = (rem / m_tiles) * BN;
-        m0 = (rem % m_tiles) * unit_rows;
+        int mi, ni;
+        tile_of(u % (m_tiles * n_tiles), m_tiles, n_tiles, mi, ni);
+        n0 = ni * BN;
+        m0 = mi * unit_rows;
         kb0 = z * g.kb_per_split;
         nkb = min(total_kb, kb0 + g.kb_per_split) - kb0;
     };
@@ -231,7 +265,7 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
 #pragma unroll
                         for (int mt = 0; mt < MT; ++mt)
                             tma_load_2d(a_dst + mt * L::A_BYTES, &map_w, full_bar(i), (kb0 + i) * BK,
-                                        m0 + mt * (g.swiglu_rows ? g.swiglu_rows : BM));
+                                        m0 + mt * BM);
                     }
                     armed = early;
                 }
@@ -253,7 +287,7 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt)
                         tma_load_2d(a_dst + mt * L::A_BYTES, &map_w, full_bar(s), (kb0 + i) * BK,
-                                    m0 + mt * (g.swiglu_rows ? g.swiglu_rows : BM));
+                                    m0 + mt * BM);
                     tma_load_2d(a_dst + MT * L::A_BYTES, &map_x, full_bar(s), (kb0 + i) * BK, n0);
                     armed = it + 1;
                 }
@@ -312,31 +346,6 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
             tc_fence_after();
             const uint32_t tmem_d = tmem_base + a * (MT * ACC_COLS);
             const size_t zoff = (size_t)z * g.split_stride;
-            if (MT == 2 && g.swiglu_rows) {
-                // accumulator 0 holds the gate rows, accumulator 1 the up rows of the same 128 features
-                const int m = m0 + q * 32 + lane;
-                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out);
-#pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
-                    if (n0 + c0 >= g.N) break;   // uniform over the warp
-                    uint32_t vg[2][16], vu[2][16];
-#pragma unroll
-                    for (int b = 0; b < 2; ++b) {
-                        tc_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(c0 + 16 * b), vg[b]);
-                        tc_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(ACC_COLS + c0 + 16 * b), vu[b]);
-                    }
-                    tc_wait_ld();
-                    if (m < g.M) {
-#pragma unroll
-                        for (int jj = 0; jj < 32; ++jj) {
-                            if (n0 + c0 + jj < g.N) {
-                                const float gv = __uint_as_float(vg[jj / 16][jj % 16]), uv = __uint_as_float(vu[jj / 16][jj % 16]);
-                                o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
-                            }
-                        }
-                    }
-                }
-            } else
 #pragma unroll 1
             for (int cc = 0; cc < MT * BN; cc += CHUNK) {
                 const int mt = cc / BN, c0 = cc % BN;
@@ -348,7 +357,9 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
                 for (int b = 0; b < CHUNK / 16; ++b)
                     tc_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * ACC_COLS + c0 + 16 * b), v[b]);
                 tc_wait_ld();
-                if (m < g.M) {
+                if (g.swiglu) {
+                    swiglu_store<CHUNK>(v, reinterpret_cast<__nv_bfloat16*>(g.out), g.ldc, m, g.M, n0 + c0, g.N, lane);
+                } else if (m < g.M) {
                     if (g.out_dtype == VCB_F32) {
                         float* o = reinterpret_cast<float*>(g.out) + zoff;
 #pragma unroll
@@ -454,13 +465,13 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
     const uint32_t rank = cluster_rank();          // 0 issues the MMAs
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     const int total_kb = (g.K + BK - 1) / BK;
-    const int unit_rows = g.swiglu_rows ? 2 * BM : 4 * BM;   // output features per pair unit
+    const int unit_rows = 4 * BM;   // rows of W per pair unit
     const int m_tiles = (g.M + unit_rows - 1) / unit_rows;
     const int n_tiles = (g.N + BN - 1) / BN;
     const int units = m_tiles * n_tiles;
     // first row in W of this block's feature tile mt
     auto w_row = [&](int m0, int mt) {
-        return g.swiglu_rows ? m0 + (int)rank * BM + mt * g.swiglu_rows : m0 + ((int)rank * 2 + mt) * BM;
+        return m0 + ((int)rank * 2 + mt) * BM;
     };
 
     if (threadIdx.x == 0) {
@@ -492,7 +503,9 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
             int it = 0, armed = 0;
             bool ok = true;
             for (int u = pair; u < units && ok; u += pairs) {
-                const int m0 = (u % m_tiles) * unit_rows, n0 = (u / m_tiles) * BN;
+                int mi, ni;
+                tile_of(u, m_tiles, n_tiles, mi, ni);
+                const int m0 = mi * unit_rows, n0 = ni * BN;
                 for (int i = 0; i < total_kb; ++i, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1u, abort_flag, g.status)) { ok = false; break; }
@@ -547,30 +560,12 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
         const int q = warp & 3;
         int j = 0;
         for (int u = pair; u < units; u += pairs, ++j) {
-            const int m0 = (u % m_tiles) * unit_rows, n0 = (u / m_tiles) * BN;
+            int mi, ni;
+            tile_of(u, m_tiles, n_tiles, mi, ni);
+            const int m0 = mi * unit_rows, n0 = ni * BN;
             if (!mbar_wait(acc_full_bar, j & 1, abort_flag, g.status)) break;
             tc_fence_after();
-            if (g.swiglu_rows) {
-                const int m = m0 + (int)rank * BM + q * 32 + lane;
-                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out);
-#pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    if (n0 + c0 >= g.N) break;   // uniform over the warp
-                    uint32_t vg[16], vu[16];
-                    tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, vg);
-                    tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + c0), vu);
-                    tc_wait_ld();
-                    if (m < g.M) {
-#pragma unroll
-                        for (int jj = 0; jj < 16; ++jj) {
-                            if (n0 + c0 + jj < g.N) {
-                                const float gv = __uint_as_float(vg[jj]), uv = __uint_as_float(vu[jj]);
-                                o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
-                            }
-                        }
-                    }
-                }
-            } else {
+            {
 #pragma unroll 1
                 for (int cc = 0; cc < 2 * BN; cc += 16) {
                     const int mt = cc / BN, c0 = cc % BN;
@@ -579,7 +574,10 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
                     uint32_t v[16];
                     tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * BN + c0), v);
                     tc_wait_ld();
-                    if (m < g.M) {
+                    if (g.swiglu) {
+                        uint32_t (*v1)[16] = reinterpret_cast<uint32_t (*)[16]>(v);
+                        swiglu_store<16>(v1, reinterpret_cast<__nv_bfloat16*>(g.out), g.ldc, m, g.M, n0 + c0, g.N, lane);
+                    } else if (m < g.M) {
                         if (g.out_dtype == VCB_F32) {
                             float* o = reinterpret_cast<float*>(g.out);
 #pragma unroll
@@ -705,7 +703,7 @@ int launch_maps(const void* W, long long w_rows, const void* X, const GemmArgs& 
         }
         opted = true;
     }
-    const int unit_rows = g.swiglu_rows ? BM : BM * MT;
+    const int unit_rows = BM * MT;
     const long long units = (long long)((g.M + unit_rows - 1) / unit_rows) * ((g.N + BN - 1) / BN) * splits;
     const int grid = (int)(units < num_sms() ? units : num_sms());
     launch_pdl(kern, dim3(grid), dim3(NTHREADS), L::TOTAL, stream, mw, mx, g);
@@ -746,7 +744,7 @@ int launch_pair(const void* W, long long w_rows, const void* X, const GemmArgs& 
         }
         opted = true;
     }
-    const int unit_rows = g.swiglu_rows ? 2 * BM : 4 * BM;
+    const int unit_rows = 4 * BM;
     const long long units = (long long)((g.M + unit_rows - 1) / unit_rows) * ((g.N + 255) / 256);
     const long long max_pairs = num_sms() / 2;
     const int pairs = (int)(units < max_pairs ? units : max_pairs);
@@ -782,27 +780,6 @@ VCB_API int vcb_gemm_effective_splits(int K, int splits) {
     if (splits > total_kb) splits = total_kb;
     const int kb_per_split = (total_kb + splits - 1) / splits;
     return (total_kb + kb_per_split - 1) / kb_per_split;
-}
-
-// Fused feed-forward front half: W = [gate (I rows); up (I rows)] x [K]; out[t][i] = silu(gate_i . x_t) * (up_i . x_t),
-// bfloat16 [N, I].  The gate tile and the up tile of the same 128 features are the two accumulators of one unit.
-VCB_API int vcb_gemm_bf16_swiglu(const void* W, const void* X, void* out, int I, int N, int K, long long ldw,
-                                 long long ldx, long long ldc, int* status, cudaStream_t stream) {
-    VCB_CHECK_ARG(I > 0 && N > 0 && K > 0, "gemm_bf16_swiglu: bad sizes I=%d N=%d K=%d", I, N, K);
-    VCB_CHECK_ARG(K % 8 == 0 && ldw % 8 == 0 && ldx % 8 == 0,
-                  "gemm_bf16_swiglu: inner size %d and row strides %lld, %lld must be multiples of 8 (16-byte rows for TMA)", K, ldw, ldx);
-    VCB_CHECK_ARG(((uintptr_t)W % 16 == 0) && ((uintptr_t)X % 16 == 0), "gemm_bf16_swiglu: operands must be 16-byte aligned");
-    const int total_kb = (K + BK - 1) / BK;
-    GemmArgs g{out, VCB_BF16, I, N, K, ldc, 0, total_kb, 1, I, status};
-    // the weight map spans both halves so that the up tile is addressed as row I + m
-    if (pairs_enabled()) return launch_pair(W, 2LL * I, X, g, ldw, ldx, stream);
-    // 192 or 256 tokens a unit: whichever leaves fewer whole rounds of work over the SMs
-    auto cost = [&](int bn) {
-        const long long units = (long long)((I + BM - 1) / BM) * ((N + bn - 1) / bn);
-        return ((units + num_sms() - 1) / num_sms()) * (long long)bn;
-    };
-    if (cost(192) < cost(256)) return launch_maps<192, 3, 2, 1>(W, 2LL * I, X, g, ldw, ldx, 1, stream);
-    return launch_maps<256, 3, 2, 1>(W, 2LL * I, X, g, ldw, ldx, 1, stream);
 }
 
 // The unit shapes that are built: tokens per tile (BN), stages of the ring, 128-feature tiles per unit, accumulators.
@@ -862,6 +839,21 @@ VCB_API int vcb_gemm_bf16_tn_shape(const void* W, const void* X, void* out, int 
     GemmArgs g{out, out_dtype, M, N, K, ldc, split_stride, kb_per_split, splits, 0, status};
     if (shape < 0 && pairs_enabled() && N > 128 && M >= 512) return launch_pair(W, M, X, g, ldw, ldx, stream);
     return launch_shape(shape < 0 ? pick_shape(M, N, splits) : shape, W, X, g, ldw, ldx, splits, stream);
+}
+
+// Fused feed-forward front half.  W [2I, K] holds gate_i in row 2i and up_i in row 2i+1; out[t][i] =
+// silu(gate_i . x_t) * (up_i . x_t), bfloat16 [N, I].  The pairing is done in the epilogue (adjacent TMEM lanes),
+// so every unit shape serves; shape < 0 chooses as for a plain product of 2I features.
+VCB_API int vcb_gemm_bf16_swiglu(const void* W, const void* X, void* out, int I, int N, int K, long long ldw,
+                                 long long ldx, long long ldc, int shape, int* status, cudaStream_t stream) {
+    VCB_CHECK_ARG(I > 0 && N > 0 && K > 0, "gemm_bf16_swiglu: bad sizes I=%d N=%d K=%d", I, N, K);
+    VCB_CHECK_ARG(K % 8 == 0 && ldw % 8 == 0 && ldx % 8 == 0,
+                  "gemm_bf16_swiglu: inner size %d and row strides %lld, %lld must be multiples of 8 (16-byte rows for TMA)", K, ldw, ldx);
+    VCB_CHECK_ARG(((uintptr_t)W % 16 == 0) && ((uintptr_t)X % 16 == 0), "gemm_bf16_swiglu: operands must be 16-byte aligned");
+    const int total_kb = (K + BK - 1) / BK;
+    GemmArgs g{out, VCB_BF16, 2 * I, N, K, ldc, 0, total_kb, 1, 1, status};
+    if (shape < 0 && pairs_enabled() && N > 128 && I >= 256) return launch_pair(W, 2LL * I, X, g, ldw, ldx, stream);
+    return launch_shape(shape < 0 ? pick_shape(2 * I, N, 1) : shape, W, X, g, ldw, ldx, 1, stream);
 }
 
 VCB_API int vcb_gemm_bf16_tn(const void* W, const void* X, void* out, int out_dtype, int M, int N, int K,

@@ -59,7 +59,7 @@ def _declare(L):
         "vcb_gemm_bf16_tn": [P, P, P, I, I, I, I, LL, LL, LL, I, LL, P, P],
         "vcb_gemm_bf16_tn_shape": [P, P, P, I, I, I, I, LL, LL, LL, I, LL, I, P, P],
         "vcb_gemm_effective_splits": [I, I],
-        "vcb_gemm_bf16_swiglu": [P, P, P, I, I, I, LL, LL, LL, P, P],
+        "vcb_gemm_bf16_swiglu": [P, P, P, I, I, I, LL, LL, LL, I, P, P],
         "vcb_sgemm_tn": [P, P, P, I, I, I, LL, LL, LL, P],
         "vcb_gemm_bf16_plain": [P, P, P, I, I, I, I, LL, LL, LL, P],
         "vcb_attn_paged": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, P],
@@ -156,7 +156,8 @@ def _partials(t: torch.Tensor, name: str):
 
 
 def swiglu(gate_up, out):
-    """gate_up [T, 2I] or [S, T, 2I] (32-bit partial sums); out [T, I]."""
+    """out[t, i] = silu(gate_up[t, 2i]) * gate_up[t, 2i+1]: gate and up alternate along a row.
+    gate_up [T, 2I] or [S, T, 2I] (32-bit partial sums); out [T, I]."""
     S, stride = _partials(gate_up, "gate_up"); _need(out, "out")
     T, I2 = gate_up.shape[-2:]
     assert out.shape == (T, I2 // 2)
@@ -231,16 +232,17 @@ def gemm_bf16_tn(w, x, out, splits, status, shape=-1):
           int(shape), _p(status), _stream())
 
 
-def gemm_bf16_swiglu(w_gate_up, x, out, status):
-    """out[t, i] = silu(gate_i . x_t) * (up_i . x_t) with w_gate_up = [gate (I rows); up (I rows)]: the product and
-    the SiLU-gate in one kernel (the two 128-feature tiles are the two accumulators of one unit)."""
+def gemm_bf16_swiglu(w_gate_up, x, out, status, shape=-1):
+    """out[t, i] = silu(gate_i . x_t) * (up_i . x_t) with gate_i in row 2i and up_i in row 2i+1 of w_gate_up: the
+    product and the SiLU-gate in one kernel (adjacent accumulator lanes are paired in the epilogue).
+    ``shape`` as in gemm_bf16_tn."""
     _need(w_gate_up, "w_gate_up", torch.bfloat16); _need(x, "x", torch.bfloat16, contiguous=False)
     _need(out, "out", torch.bfloat16)
     I2, K = w_gate_up.shape
     T = x.shape[0]
     assert I2 % 2 == 0 and x.shape[1] == K and x.stride(1) == 1 and out.shape == (T, I2 // 2)
     _call("vcb_gemm_bf16_swiglu", _p(w_gate_up), _p(x), _p(out), I2 // 2, T, K, w_gate_up.stride(0), x.stride(0),
-          out.stride(0), _p(status), _stream())
+          out.stride(0), int(shape), _p(status), _stream())
 
 
 def sgemm_tn(a, b, out):

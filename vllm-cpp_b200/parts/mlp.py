@@ -1,7 +1,9 @@
 """SwiGLU feed-forward: down(silu(gate(y)) * up(y)), silu(z) = z / (1 + exp(-z))
 (src/model.cpp:964-966, 1237-1244), with separate input and output buffers for the
-down projection.  gate and up are stacked into one [2I, H] matrix at load so one
-product yields both."""
+down projection.  gate and up become one [2I, H] matrix at load, gate_i in row 2i
+and up_i in row 2i+1, so that one product yields both side by side: in the
+tensor-core kernel the two land in adjacent accumulator lanes and the SiLU-gate
+is a shuffle away in its epilogue."""
 from __future__ import annotations
 
 import torch
@@ -32,7 +34,7 @@ class SwiGLUMLP(FeedForward):
 
     def bind(self, store):
         p = self.prefix
-        self.w_gate_up = store.matrices([p + "gate_proj.weight", p + "up_proj.weight"])
+        self.w_gate_up = store.matrices([p + "gate_proj.weight", p + "up_proj.weight"], interleave=True)
         self.w_down = store.matrix(p + "down_proj.weight")
 
     def forward(self, x, ctx):

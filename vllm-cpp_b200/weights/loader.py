@@ -88,11 +88,19 @@ class WeightStore:
             self._cache[key] = self._to_device(self._raw(name), self.compute_dtype)
         return self._cache[key]
 
-    def matrices(self, names: list[str]) -> torch.Tensor:
-        """Several matrices with equal inner size stacked along the output axis (q,k,v -> qkv; gate,up -> gate_up)."""
+    def matrices(self, names: list[str], interleave: bool = False) -> torch.Tensor:
+        """Several matrices with equal inner size stacked along the output axis (q,k,v -> qkv).  With
+        ``interleave`` their rows alternate instead (row n*i + j is row i of matrix j; gate,up -> gate_up)."""
         parts = [self._raw(n) for n in names]
         rows = sum(p.shape[0] for p in parts)
         out = torch.empty((rows, parts[0].shape[1]), dtype=self.compute_dtype, device=self.device)
+        if interleave:
+            if any(p.shape != parts[0].shape for p in parts):
+                raise WeightError(f"tensors {names} must have one shape to be interleaved")
+            view = out.view(parts[0].shape[0], len(parts), parts[0].shape[1])
+            for j, p in enumerate(parts):
+                view[:, j].copy_(p.to(self.device), non_blocking=False)
+            return out
         r = 0
         for p in parts:
             out[r: r + p.shape[0]].copy_(p.to(self.device), non_blocking=False)

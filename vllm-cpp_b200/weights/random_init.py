@@ -81,8 +81,11 @@ class RandomWeightStore(WeightStore):
     def matrix(self, name):
         return self._draw(name).to(self.compute_dtype)
 
-    def matrices(self, names):
-        return torch.cat([self.matrix(n) for n in names], dim=0)
+    def matrices(self, names, interleave=False):
+        parts = [self.matrix(n) for n in names]
+        if interleave:
+            return torch.stack(parts, dim=1).reshape(-1, parts[0].shape[1]).contiguous()
+        return torch.cat(parts, dim=0)
 
     def vector(self, name):
         t = self._draw(name)
