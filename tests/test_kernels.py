@@ -183,6 +183,8 @@ def run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft=None):
     if ops.attn_mma_supported(dtype, hd):
         plan = _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma=True)           # TMA tile loads where the page size allows
         plan = _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma="no_tma")      # cp.async tile loads
+    if ops.attn_tc_supported(dtype, hd, ps):
+        plan = _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma="tc")           # tcgen05 for the prompt portions
     return plan
 
 
@@ -238,8 +240,11 @@ def _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma):
             assert int(plan.slice_counters.abs().sum()) == 0        # left ready for the next launch
         elif S > 1:
             ops.attn_merge(po, pm, plan.dec_rows, out, plan.n_dec, nh, hd, S)
-    if plan.n_span_items:
+    if plan.n_span_items and mma == "tc":
+        ops.attn_tc(q_flat, out, *args, plan.span_items, plan.n_span_items, nh, nkv, hd, window, status)
+    elif plan.n_span_items:
         kernel(q_flat, out, *args, plan.span_items, plan.n_span_items, SPAN_ROWS, None, None, nh, nkv, hd, window, status)
+    torch.cuda.synchronize()
     assert status.item() == 0
     got = out.double().cpu().view(T, nh, hd)
     t = 0
@@ -264,6 +269,14 @@ def test_attention_mixed_batch(dtype, nh, nkv, hd, ps):
 @pytest.mark.parametrize("hd", [32, 64])
 def test_attention_window(dtype, window, hd):
     run_attention(dtype, 6, 2, hd, 8, window, [(0, 40), (57, 1), (23, 3), (130, 1), (300, 70)])
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(8, 2, 128, 16, 0), (3, 3, 128, 64, 0), (10, 2, 64, 8, 0), (4, 1, 128, 32, 0),
+                                                 (8, 2, 128, 16, 100), (2, 1, 64, 16, 7), (130, 1, 64, 16, 0)])
+def test_attention_long_prompt_portions(nh, nkv, hd, ps, window):
+    """Prompt portions over many key tiles (what the tcgen05 kernel pipelines): from an empty cache, behind a long
+    prefix, a prefix that ends inside a page and inside a tile, group sizes that do not divide 128 rows."""
+    run_attention(torch.bfloat16, nh, nkv, hd, ps, window, [(0, 300), (517, 130), (1000, 2), (63, 65), (64, 64), (0, 64)])
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

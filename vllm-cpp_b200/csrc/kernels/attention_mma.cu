@@ -24,6 +24,7 @@
 // on addresses; every wait is bounded and reports through the status word.  Other page sizes use cp.async
 // from all threads with two stages.
 #include "common.cuh"
+#include "kv_tensor_map.h"
 
 #include <cuda.h>
 #include <math_constants.h>
@@ -668,6 +669,10 @@ int launch_rows(const AttnArgs& a, int n_items, int rows_max, cudaStream_t strea
 }
 
 }  // namespace
+
+bool vcb_kv_tensor_map(const void* pages, long long rows, int hd, int page_size, CUtensorMap* out) {
+    return kv_tensor_map(pages, rows, hd, page_size, out);
+}
 
 // rows_max: 16 (single decoded tokens; four warps split each tile's keys) or 128 (prompt portions; eight warps of
 // 16 rows each share the K and V tiles, enough independent MMA chains per SM to keep the tensor pipe fed).

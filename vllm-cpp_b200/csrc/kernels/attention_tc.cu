@@ -1,0 +1,496 @@
+// bfloat16 attention of prompt portions over the paged cache on the fifth-generation tensor cores
+// (tcgen05.mma with accumulators in TMEM), head_dim 64 or 128, pages of 8, 16, 32 or 64 tokens.
+//
+// Same contract, work items and math as attention_mma.cu (one item = an entry and a run of its query tokens;
+// rows = tokens x the query heads that share a KV head, at most 128; scores (q.k)/sqrt(head_dim) in 32-bit, keys
+// in (pos - window, pos], streaming softmax, sum_j w_j v_j: src/model.cpp:1000-1052 of the reference).  What
+// differs is where the products run.  Per block of 128 rows and per tile of 64 keys:
+//
+//   S = Q . K^T     one MMA chain, M = 128 rows (TMEM lanes), N = 64 keys, K = head_dim; Q and the K tile are
+//                   K-major operands in 128-byte-swizzled shared memory, S lands in TMEM (two buffers);
+//   softmax         four warps, one thread per row (= per TMEM lane): tcgen05.ld of the row's 64 scores, mask,
+//                   running maximum and sum in 32-bit, P = exp2(s - m) rounded to bfloat16 into shared memory
+//                   (two buffers), laid out as the A operand of the next product;
+//   O_j = P . V     M = 128, N = head_dim, K = 64 keys; the V tile is used as it lies in the cache (keys x
+//                   head_dim, head_dim contiguous), i.e. as an MN-major B operand; O_j lands in TMEM (two
+//                   buffers) and the row's thread folds it into its 32-bit accumulator, o = o * alpha + O_j,
+//                   one tile behind, so that the fold overlaps the next tile's products.
+//
+// Roles (192 threads): warp 0 issues TMA loads of K and V pages (cp.async.bulk.tensor, 128-byte swizzle; no
+// multicast) into a ring of stages; warp 1 allocates TMEM and issues every MMA; warps 2-5 are the softmax rows.
+// All hand-offs are mbarriers; every wait is bounded by the clock, and a wait that runs out sets a bit in the
+// status word and an abort flag that the other roles see, after which the block frees its TMEM and returns.
+#include "common.cuh"
+#include "kv_tensor_map.h"
+
+#include <cuda.h>
+#include <math_constants.h>
+
+namespace {
+
+constexpr int BNK = 64;       // keys per tile
+constexpr int ROWS = 128;     // rows per block = TMEM lanes
+constexpr int ITEM_INTS = 6;  // entry, q0, nq, slice, nslices, decode index (as in attention_mma.cu)
+constexpr int NTHREADS = 192;
+constexpr long long WAIT_CLOCKS = 2000000000ll;   // about a second
+
+struct TcArgs {
+    const __nv_bfloat16* q;
+    __nv_bfloat16* out;
+    const int* block_table;
+    const int* table_row;
+    int max_blocks;
+    const int* q_start;
+    const int* q_len;
+    const int* ctx_len;
+    const int* items;
+    int nh, nkv, page_size, num_pages, window;
+    float scale;
+    int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the barrier did not flip within WAIT_CLOCKS or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_CLOCKS) {
+            *abort_flag = 1;
+            atomicOr(status, VCB_STATUS_WAIT_TIMEOUT);
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptors (version 1, 128-byte swizzle = layout 2 in bits 61-63; addresses and offsets
+// in units of 16 bytes).  K-major tile (rows of 128 bytes along the inner dimension): 8-row groups 1024 bytes
+// apart (stride offset, bits 32-45); the leading offset is unused.  MN-major tile (rows of 128 bytes = 64
+// elements along M or N, one row per inner index): groups of 8 inner indices 1024 bytes apart (stride offset),
+// groups of 64 outer elements `outer_bytes` apart (leading offset, bits 16-29).
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t outer_bytes) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(outer_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+// kind::f16 instruction descriptor: f32 accumulate (bits 4-5 = 1), A and B bfloat16 (bits 7-9, 10-12 = 1),
+// A K-major (bit 15 = 0), B K-major or MN-major (bit 16), N / 8 in bits 17-22, M / 16 in bits 24-28.
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(ROWS >> 4) << 24);
+}
+
+// Byte offset of 16-byte chunk c of row r in a tile of NROWS rows stored as head_dim/64 blocks of [NROWS][128
+// bytes], each row XOR-swizzled by its index: what a 128-byte-swizzled TMA box of 64 lanes produces and what
+// the descriptors above describe.
+template <int NROWS> __device__ __forceinline__ int swz(int r, int c) {
+    return (c >> 3) * (NROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD, int STAGES>
+struct Layout {
+    static constexpr int Q_BYTES = ROWS * HD * 2;
+    static constexpr int KV_BYTES = BNK * HD * 2;       // one K or V tile
+    static constexpr int P_BYTES = ROWS * BNK * 2;
+    static constexpr int K_OFF = Q_BYTES;
+    static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
+    static constexpr int P_OFF = V_OFF + STAGES * KV_BYTES;
+    static constexpr int BAR_OFF = P_OFF + 2 * P_BYTES;
+    static constexpr int NUM_BARS = 2 * STAGES + 9;
+    static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16 + 1024;   // + TMEM address, abort flag, alignment slack
+    static constexpr uint32_t TMEM_COLS = (2 * BNK + 2 * HD) <= 256 ? 256 : 512;   // S, S, O, O
+};
+
+template <int HD, int STAGES>
+__global__ __launch_bounds__(NTHREADS, 1) void attn_tc_kernel(const __grid_constant__ CUtensorMap kv_map, TcArgs a) {
+    using L = Layout<HD, STAGES>;
+    constexpr int CH = HD / 8;          // 16-byte chunks per row of head_dim
+    constexpr int ROWB = HD * 2;
+    constexpr float LOG2E = 1.4426950408889634f;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzle atoms are 1024-byte aligned
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + L::BAR_OFF;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto s_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+    auto s_empty = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
+    auto p_ready = [&](int b) { return bars + 8u * (2 * STAGES + 4 + b); };
+    auto o_full = [&](int b) { return bars + 8u * (2 * STAGES + 6 + b); };
+    const uint32_t q_ready = bars + 8u * (2 * STAGES + 8);
+    // o_empty is not needed: the fold of tile j-2, which frees O buffer j & 1, precedes the row's arrival on
+    // p_ready for tile j, which the MMA thread awaits before it writes that buffer.
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(gen + L::BAR_OFF + L::NUM_BARS * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::BAR_OFF + L::NUM_BARS * 8 + 8);
+
+    pdl_trigger();
+    pdl_wait();   // the queries and the newest keys come from the kernel before this one
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int* item = a.items + (size_t)blockIdx.x * ITEM_INTS;
+    const int e = item[0], q0 = item[1], nq = item[2];
+
+    const int g = a.nh / a.nkv;
+    const int gq_max = g < ROWS ? g : ROWS;
+    const int hchunks = (g + gq_max - 1) / gq_max;
+    const int kvh = blockIdx.y / hchunks, hc = blockIdx.y % hchunks;
+    const int head0 = kvh * g + hc * gq_max;
+    const int gq = min(gq_max, g - hc * gq_max);
+    const int R = nq * gq;
+
+    const int qlen = a.q_len[e], ctx = a.ctx_len[e];
+    if (qlen <= 0 || ctx <= 0) return;   // uniform over the block, before anything is allocated
+    const int row0 = a.q_start[e] + q0;
+    const int pos0 = ctx - qlen + q0;
+    const int pos_last = pos0 + nq - 1;
+    const int W = a.window;
+    const int ps = a.page_size;
+    const int lo = W > 0 ? max(0, pos0 - W + 1) : 0;
+    const int k_end = pos_last + 1;
+    const int pb_lo = lo / ps, pb_hi = (k_end + ps - 1) / ps;
+    const int t_first = pb_lo * ps;     // tiles start on a page boundary: whole pages are loaded
+    const int n_tiles = (k_end - t_first + BNK - 1) / BNK;   // >= 1: every query sees itself
+    const int* bt = a.block_table + (size_t)(a.table_row ? a.table_row[e] : e) * a.max_blocks;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(s_full(b), 1);
+            mbar_init(s_empty(b), 4);       // one arrival per softmax warp
+            mbar_init(p_ready(b), ROWS);    // one arrival per row
+            mbar_init(o_full(b), 1);
+        }
+        mbar_init(q_ready, ROWS);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32((const void*)tmem_holder)), "r"(L::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * BNK;
+
+    if (warp == 0) {
+        // ---- TMA producer: one box of [page_size keys x 64 lanes] per page, per half of head_dim, for K and V ----
+        if (lane == 0) {
+            const int pages_per_tile = BNK / ps;
+            const int rows_kv = a.nkv * ps;          // rows of the flattened [pages * 2 * nkv * ps, HD] view per K or V
+            int armed = 0;
+            for (int it = 0; it < n_tiles; ++it) {
+                const int st = it % STAGES;
+                if (!mbar_wait(empty_bar(st), ((it / STAGES) & 1) ^ 1u, abort_flag, a.status)) break;
+                const int pb0 = pb_lo + it * pages_per_tile;
+                const int np = min(pages_per_tile, pb_hi - pb0);
+                mbar_expect_tx(full_bar(st), (uint32_t)(np * ps * ROWB * 2));
+                const uint32_t kd = base + L::K_OFF + st * L::KV_BYTES, vd = base + L::V_OFF + st * L::KV_BYTES;
+                for (int pg = 0; pg < np; ++pg) {
+                    int page = bt[pb0 + pg];
+                    if (page < 0 || page >= a.num_pages) {
+                        atomicOr(a.status, VCB_STATUS_BAD_PAGE);
+                        page = 0;   // keep the byte count whole; the status word reports the fault
+                    }
+                    const int krow = (page * 2 * a.nkv + kvh) * ps;
+#pragma unroll
+                    for (int h = 0; h < HD / 64; ++h) {
+                        const uint32_t off = h * (BNK * 128) + pg * ps * 128;
+                        tma_load_2d(kd + off, &kv_map, full_bar(st), h * 64, krow);
+                        tma_load_2d(vd + off, &kv_map, full_bar(st), h * 64, krow + rows_kv);
+                    }
+                }
+                armed = it + 1;
+            }
+            if (*abort_flag) {   // let copies in flight land before the block goes away
+                for (int i = max(0, armed - STAGES); i < armed; ++i) {
+                    const long long t0 = clock64();
+                    while (!mbar_try(full_bar(i % STAGES), (i / STAGES) & 1) && clock64() - t0 < WAIT_CLOCKS) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ----
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = instr_desc(BNK, false);
+            constexpr uint32_t idesc_pv = instr_desc(HD, true);
+            bool ok = mbar_wait(q_ready, 0, abort_flag, a.status);
+            // S[j & 1] = Q . K_j^T once the tile has landed and the rows have read the scores of tile j - 2
+            auto issue_qk = [&](int j) {
+                const int st = j % STAGES, b = j & 1;
+                if (!mbar_wait(full_bar(st), (j / STAGES) & 1, abort_flag, a.status)) return false;
+                if (!mbar_wait(s_empty(b), ((j >> 1) & 1) ^ 1u, abort_flag, a.status)) return false;
+                tc_fence_after();
+                const uint32_t qa = base, ka = base + L::K_OFF + st * L::KV_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    // 16 lanes of head_dim = 32 bytes along the 128-byte rows; the second 64 lanes are the next block
+                    const uint64_t da = desc_k_major(qa + (ks / 4) * (ROWS * 128) + (ks % 4) * 32);
+                    const uint64_t db = desc_k_major(ka + (ks / 4) * (BNK * 128) + (ks % 4) * 32);
+                    tc_mma(tmem_s + b * BNK, da, db, idesc_qk, ks > 0);
+                }
+                tc_commit(s_full(b));
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int st = j % STAGES, b = j & 1;
+                if (j + 1 < n_tiles) {
+                    ok = issue_qk(j + 1);   // runs while the rows work on tile j
+                    if (!ok) break;
+                }
+                ok = mbar_wait(p_ready(b), (j >> 1) & 1, abort_flag, a.status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t pa = base + L::P_OFF + b * L::P_BYTES, va = base + L::V_OFF + st * L::KV_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < BNK / 16; ++ks) {
+                    const uint64_t da = desc_k_major(pa + ks * 32);
+                    // 16 keys = 16 rows of 128 bytes further on; the second 64 lanes of head_dim are the next block
+                    const uint64_t db = desc_mn_major(va + ks * 16 * 128, BNK * 128);
+                    tc_mma(tmem_o + b * HD, da, db, idesc_pv, ks > 0);
+                }
+                tc_commit(o_full(b));
+                tc_commit(empty_bar(st));   // K and V of this stage have been read
+            }
+        }
+    } else {
+        // ---- softmax rows: warp w reads TMEM lanes 32 (w % 4) .. + 31 ----
+        const int qtr = warp & 3;
+        const int r = qtr * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(qtr * 32) << 16;
+        const bool row_ok = r < R;
+        const int iq = r / gq, ih = r % gq;
+        const int pos_r = pos0 + iq;
+        const int lo_r = W > 0 ? max(0, pos_r - W + 1) : 0;
+
+        // the row's query -> shared memory (rows beyond R are zero)
+        {
+            const __nv_bfloat16* src = a.q + ((size_t)(row0 + iq) * a.nh + head0 + ih) * HD;
+#pragma unroll
+            for (int c = 0; c < CH; ++c) {
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (row_ok) v = *reinterpret_cast<const uint4*>(src + c * 8);
+                *reinterpret_cast<uint4*>(gen + swz<ROWS>(r, c)) = v;
+            }
+            fence_async_smem();
+            mbar_arrive(q_ready);
+        }
+
+        float o[HD];
+#pragma unroll
+        for (int d = 0; d < HD; ++d) o[d] = 0.f;
+        float m_run = -CUDART_INF_F, l_run = 0.f, alpha_prev = 1.f;
+        const float scale_log2 = a.scale * LOG2E;
+        bool ok = true;
+
+        // o = o * alpha + O_jj, and the O buffer is the MMA thread's again
+        auto fold = [&](int jj, float alpha) {
+            const int bb = jj & 1;
+            if (!mbar_wait(o_full(bb), (jj >> 1) & 1, abort_flag, a.status)) return false;
+            tc_fence_after();
+#pragma unroll
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t v[2][16];
+                tc_ld16(tmem_o + lane_addr + (uint32_t)(bb * HD + c0), v[0]);
+                tc_ld16(tmem_o + lane_addr + (uint32_t)(bb * HD + c0 + 16), v[1]);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, __uint_as_float(v[i / 16][i % 16]));
+            }
+            tc_fence_before();
+            return true;
+        };
+
+        for (int j = 0; j < n_tiles; ++j) {
+            const int b = j & 1, st = j % STAGES;
+            const int t0 = t_first + j * BNK;
+            ok = mbar_wait(s_full(b), (j >> 1) & 1, abort_flag, a.status);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t sv[4][16];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) tc_ld16(tmem_s + lane_addr + (uint32_t)(b * BNK + 16 * i), sv[i]);
+            tc_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_empty(b));   // this warp has read its quarter of the scores
+
+            float mx = -CUDART_INF_F;
+#pragma unroll
+            for (int c = 0; c < BNK; ++c) {
+                const int kidx = t0 + c;
+                const bool valid = row_ok && kidx >= lo_r && kidx <= pos_r;
+                const float s = valid ? __uint_as_float(sv[c / 16][c % 16]) * scale_log2 : -CUDART_INF_F;
+                sv[c / 16][c % 16] = __float_as_uint(s);
+                mx = fmaxf(mx, s);
+            }
+            const float m_new = fmaxf(m_run, mx);
+            float alpha = 1.f, m_sub = 0.f;
+            if (m_new != -CUDART_INF_F) {       // otherwise the row has seen no key yet: every weight is zero
+                alpha = exp2f(m_run - m_new);   // 0 for the first keys
+                m_sub = m_new;
+            }
+            float sum = 0.f;
+            uint32_t pk[BNK / 2];
+#pragma unroll
+            for (int c = 0; c < BNK; c += 2) {
+                const float p0 = exp2f(__uint_as_float(sv[c / 16][c % 16]) - m_sub);
+                const float p1 = exp2f(__uint_as_float(sv[(c + 1) / 16][(c + 1) % 16]) - m_sub);
+                sum += p0 + p1;
+                pk[c / 2] = pack_bf16(p0, p1);
+            }
+            l_run = l_run * alpha + sum;
+            m_run = m_new;
+
+            if (t0 + BNK > k_end) {
+                // The last page may hold slots beyond the sequence, and rows of pages that were not loaded are
+                // stale: their V must be finite, because a zero weight times NaN is NaN.
+                ok = mbar_wait(full_bar(st), (j / STAGES) & 1, abort_flag, a.status);
+                if (!ok) break;
+                const int first = k_end - t0;
+                for (int idx = r; idx < (BNK - first) * CH; idx += ROWS) {
+                    const int jj = first + idx / CH, c = idx % CH;
+                    *reinterpret_cast<uint4*>(gen + L::V_OFF + st * L::KV_BYTES + swz<BNK>(jj, c)) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            // the row of P as the A operand of P . V: 64 keys = 128 bytes, swizzled like every other row
+            uint8_t* prow = gen + L::P_OFF + b * L::P_BYTES + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            fence_async_smem();
+            mbar_arrive(p_ready(b));
+
+            if (j > 0) {
+                ok = fold(j - 1, alpha_prev);
+                if (!ok) break;
+            }
+            alpha_prev = alpha;
+        }
+        if (ok) ok = fold(n_tiles - 1, alpha_prev);
+
+        if (ok && row_ok) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            __nv_bfloat16* dst = a.out + ((size_t)(row0 + iq) * a.nh + head0 + ih) * HD;
+#pragma unroll
+            for (int c = 0; c < CH; ++c)
+                *reinterpret_cast<uint4*>(dst + c * 8) =
+                    make_uint4(pack_bf16(o[8 * c] * inv, o[8 * c + 1] * inv), pack_bf16(o[8 * c + 2] * inv, o[8 * c + 3] * inv),
+                               pack_bf16(o[8 * c + 4] * inv, o[8 * c + 5] * inv), pack_bf16(o[8 * c + 6] * inv, o[8 * c + 7] * inv));
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS) : "memory");
+    }
+}
+
+template <int HD>
+int launch(const CUtensorMap& map, const TcArgs& a, int n_items, cudaStream_t stream) {
+    constexpr int STAGES = 4;
+    using L = Layout<HD, STAGES>;
+    auto kern = attn_tc_kernel<HD, STAGES>;
+    static bool opted = false;
+    if (!opted) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) {
+            vcb_set_error("attn_tc: %d bytes of shared memory refused: %s", L::TOTAL, cudaGetErrorString(e));
+            return -2;
+        }
+        opted = true;
+    }
+    const int g = a.nh / a.nkv;
+    const int gq_max = g < ROWS ? g : ROWS;
+    const int hchunks = (g + gq_max - 1) / gq_max;
+    launch_pdl(kern, dim3(n_items, a.nkv * hchunks), dim3(NTHREADS), (size_t)L::TOTAL, stream, map, a);
+    VCB_CHECK_LAUNCH("attn_tc");
+    return 0;
+}
+
+}  // namespace
+
+// What the tcgen05 kernel takes; the caller uses vcb_attn_mma (or vcb_attn_paged) for everything else.
+VCB_API int vcb_attn_tc_supported(int dtype, int hd, int page_size) {
+    return dtype == VCB_BF16 && (hd == 64 || hd == 128) &&
+           (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
+}
+
+// Prompt portions only: every item has slice 0 of 1 and at most 128 rows (tokens x query heads per KV head).
+VCB_API int vcb_attn_tc(const void* q, void* out, const void* pages, long long page_stride, const int* block_table,
+                        const int* table_row, int max_blocks, const int* q_start, const int* q_len, const int* ctx_len,
+                        const int* items, int n_items, int nh, int nkv, int hd, int page_size, int num_pages, int window,
+                        float scale, int* status, cudaStream_t stream) {
+    if (n_items == 0) return 0;
+    VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_tc: %d query heads are not a multiple of %d KV heads", nh, nkv);
+    VCB_CHECK_ARG(vcb_attn_tc_supported(VCB_BF16, hd, page_size), "attn_tc: head_dim %d with pages of %d tokens is not supported", hd, page_size);
+    VCB_CHECK_ARG(window >= 0, "attn_tc: bad window %d", window);
+    VCB_CHECK_ARG(((uintptr_t)pages % 16 == 0) && page_stride == (long long)2 * nkv * page_size * hd,
+                  "attn_tc: the pages of a layer must be contiguous and 16-byte aligned for TMA loads");
+    VCB_CHECK_ARG(((uintptr_t)q % 16 == 0) && ((uintptr_t)out % 16 == 0), "attn_tc: q and out must be 16-byte aligned");
+    CUtensorMap map;
+    if (!vcb_kv_tensor_map(pages, (long long)num_pages * 2 * nkv * page_size, hd, page_size, &map)) return -3;
+    TcArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, block_table, table_row, max_blocks, q_start, q_len, ctx_len,
+             items, nh, nkv, page_size, num_pages, window, scale, status};
+    return hd == 64 ? launch<64>(map, a, n_items, stream) : launch<128>(map, a, n_items, stream);
+}

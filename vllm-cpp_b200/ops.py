@@ -66,6 +66,8 @@ def _declare(L):
         "vcb_scatter_i32": [P, P, P, P, I, LL, P],
         "vcb_attn_mma": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, F, P, I, P],
         "vcb_attn_mma_supported": [I, I],
+        "vcb_attn_tc": [P, P, P, LL, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, P, P],
+        "vcb_attn_tc_supported": [I, I, I],
         "vcb_attn_merge": [P, P, P, P, I, I, I, I, I, P],
         "vcb_sample": [P, LL, I, I, P, P, P, P],
         "vcb_sample_split": [P, LL, I, I, P, P, P, P, I, P, P],
@@ -314,6 +316,26 @@ def scatter_i32(dst, idx, val, count, capacity):
 def attn_mma_supported(dtype: torch.dtype, hd: int) -> bool:
     """Whether the tensor-core attention kernel takes this element type and head size."""
     return bool(lib().vcb_attn_mma_supported(BF16 if dtype == torch.bfloat16 else F32, hd))
+
+
+def attn_tc_supported(dtype: torch.dtype, hd: int, page_size: int) -> bool:
+    """Whether the tcgen05 attention kernel for prompt portions takes this element type, head size and page size."""
+    return bool(lib().vcb_attn_tc_supported(BF16 if dtype == torch.bfloat16 else F32, hd, page_size))
+
+
+def attn_tc(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, nh, nkv, hd, window, status,
+            table_row=None):
+    """Attention of prompt portions on tcgen05 tensor cores (bfloat16, head_dim 64 or 128, pages of 8 to 64
+    tokens).  Items as for :func:`attn_paged` with one key slice and at most 128 rows each."""
+    _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(pages, "pages", torch.bfloat16)
+    for name, t in (("block_table", block_table), ("q_start", q_start), ("q_len", q_len), ("ctx_len", ctx_len),
+                    ("items", items)):
+        _need(t, name, torch.int32)
+    num_pages, two, nkv_p, page_size, hd_p = pages.shape
+    assert two == 2 and nkv_p == nkv and hd_p == hd
+    _call("vcb_attn_tc", _p(q), _p(out), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
+          block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, nh, nkv, hd, page_size,
+          num_pages, int(window or 0), 1.0 / math.sqrt(hd), _p(status), _stream())
 
 
 def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, rows_max, part_o, part_ml,

@@ -14,6 +14,8 @@ side is computed, and the part must have been built with ``has_kv`` False.
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import torch
 
@@ -29,6 +31,8 @@ MMA_DECODE_ROWS = 16   # the same for the tensor-core kernel
 MMA_SPAN_ROWS = 128
 MAX_SLICES = 64
 TARGET_BLOCKS = 2 * 148   # blocks of the decode kernel that are resident at once (two per SM)
+# prompt portions run on the tcgen05 kernel where it takes the sizes; 0 keeps them on the mma.sync kernel (comparison runs)
+TCGEN05_SPANS = os.environ.get("VLLM_CPP_B200_ATTN_TCGEN05", "1") != "0"
 
 
 class AttentionPlan:
@@ -158,7 +162,10 @@ class GQAAttention(Mixer):
                                plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml, **common)
                 if S > 1:
                     ops.attn_merge(part_o, part_ml, plan.dec_rows, out, plan.n_dec, nh, hd, S)
-        if plan.n_span_items:
+        if plan.n_span_items and mma and TCGEN05_SPANS and ops.attn_tc_supported(x.dtype, hd, cache.pages.shape[3]):
+            ops.attn_tc(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
+                        plan.span_items, plan.n_span_items, **common)
+        elif plan.n_span_items:
             kernel(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
                    plan.span_items, plan.n_span_items, span_rows, None, None, **common)
         return matmul_tn(out, self.w_o, ctx.status, out_dtype=torch.float32, allow_partials=True)
