@@ -10,12 +10,16 @@
 //                   K-major operands in 128-byte-swizzled shared memory, S lands in TMEM (two buffers);
 //   softmax         four warps, one thread per row (= per TMEM lane): tcgen05.ld of the row's 64 scores, mask,
 //                   running maximum and sum in 32-bit, P = exp2(s - m) rounded to bfloat16 into shared memory
-//                   (two buffers), laid out as the A operand of the next product;
-//   O_j = P . V     M = 128, N = head_dim, K = 64 keys; the V tile is used as it lies in the cache (keys x
-//                   head_dim, head_dim contiguous), i.e. as an MN-major B operand; O_j lands in TMEM (two
-//                   buffers) and the row's thread folds it into its 32-bit accumulator, o = o * alpha + O_j,
-//                   one tile behind, so that the fold overlaps the next tile's products.
+//                   laid out as the A operand of the next product;
+//   O += P . V      M = 128, N = head_dim, K = 64 keys; the V tile is used as it lies in the cache (keys x
+//                   head_dim, head_dim contiguous), i.e. as an MN-major B operand; O stays in TMEM over all
+//                   tiles.  A row's weights are taken against a reference maximum that is only moved, and O
+//                   and the sum rescaled with it (tcgen05.ld, multiply, tcgen05.st), when the row's true maximum
+//                   has outgrown it by more than 2^8 -- the weights then stay below 256, exact in the end because
+//                   numerator and denominator carry the same reference.
 //
+// Two blocks share an SM (112 KB of shared memory and 256 TMEM columns each), so one block's softmax overlaps
+// the other's products.
 // Roles (192 threads): warp 0 issues TMA loads of K and V pages (cp.async.bulk.tensor, 128-byte swizzle; no
 // multicast) into a ring of stages; warp 1 allocates TMEM and issues every MMA; warps 2-5 are the softmax rows.
 // All hand-offs are mbarriers; every wait is bounded by the clock, and a wait that runs out sets a bit in the
@@ -108,6 +112,13 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptors (version 1, 128-byte swizzle = layout 2 in bits 61-63; addresses and offsets
 // in units of 16 bytes).  K-major tile (rows of 128 bytes along the inner dimension): 8-row groups 1024 bytes
@@ -134,6 +145,12 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
 template <int NROWS> __device__ __forceinline__ int swz(int r, int c) {
     return (c >> 3) * (NROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
 }
+// 2^x to 2^-22 relative; -inf gives 0
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -147,32 +164,38 @@ struct Layout {
     static constexpr int K_OFF = Q_BYTES;
     static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
     static constexpr int P_OFF = V_OFF + STAGES * KV_BYTES;
-    static constexpr int BAR_OFF = P_OFF + 2 * P_BYTES;
-    static constexpr int NUM_BARS = 2 * STAGES + 9;
-    static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16 + 1024;   // + TMEM address, abort flag, alignment slack
-    static constexpr uint32_t TMEM_COLS = (2 * BNK + 2 * HD) <= 256 ? 256 : 512;   // S, S, O, O
+    static constexpr int BAR_OFF = P_OFF + P_BYTES;
+    static constexpr int NUM_BARS = 4 * STAGES + 7;
+    static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16;   // + TMEM address, abort flag
+    static constexpr uint32_t TMEM_COLS = 256;                  // S, S (64 each), O (head_dim)
+    static_assert(2 * BNK + HD <= 256, "TMEM columns");
+    static_assert(2 * (TOTAL + 1024) <= 228 * 1024, "two blocks per SM");
 };
 
+constexpr float RESCALE_STEP = 8.0f;   // log2 of how far a row's maximum may outgrow its reference
+
 template <int HD, int STAGES>
-__global__ __launch_bounds__(NTHREADS, 1) void attn_tc_kernel(const __grid_constant__ CUtensorMap kv_map, TcArgs a) {
+__global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_constant__ CUtensorMap kv_map, TcArgs a) {
     using L = Layout<HD, STAGES>;
     constexpr int CH = HD / 8;          // 16-byte chunks per row of head_dim
     constexpr int ROWB = HD * 2;
     constexpr float LOG2E = 1.4426950408889634f;
 
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzle atoms are 1024-byte aligned
-    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    extern __shared__ __align__(1024) uint8_t smem_raw[];   // swizzle atoms are 1024-byte aligned
+    uint8_t* gen = smem_raw;
+    const uint32_t base = smem_u32(smem_raw);
     const uint32_t bars = base + L::BAR_OFF;
-    auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-    auto s_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
-    auto s_empty = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
-    auto p_ready = [&](int b) { return bars + 8u * (2 * STAGES + 4 + b); };
-    auto o_full = [&](int b) { return bars + 8u * (2 * STAGES + 6 + b); };
-    const uint32_t q_ready = bars + 8u * (2 * STAGES + 8);
-    // o_empty is not needed: the fold of tile j-2, which frees O buffer j & 1, precedes the row's arrival on
-    // p_ready for tile j, which the MMA thread awaits before it writes that buffer.
+    // K and V tiles have rings of their own: a K stage is free again once the scores of its tile are computed,
+    // a whole tile's softmax before the V stage is, so the next keys are asked for that much earlier.
+    auto k_full = [&](int s) { return bars + 8u * s; };
+    auto k_empty = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto v_full = [&](int s) { return bars + 8u * (2 * STAGES + s); };
+    auto v_empty = [&](int s) { return bars + 8u * (3 * STAGES + s); };
+    auto s_full = [&](int b) { return bars + 8u * (4 * STAGES + b); };
+    auto s_empty = [&](int b) { return bars + 8u * (4 * STAGES + 2 + b); };
+    const uint32_t p_ready = bars + 8u * (4 * STAGES + 4);   // one phase per tile: every row has written its weights
+    const uint32_t pv_done = bars + 8u * (4 * STAGES + 5);   // one phase per tile: P . V of the tile has been added to O
+    const uint32_t q_ready = bars + 8u * (4 * STAGES + 6);
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(gen + L::BAR_OFF + L::NUM_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::BAR_OFF + L::NUM_BARS * 8 + 8);
 
@@ -192,6 +215,10 @@ __global__ __launch_bounds__(NTHREADS, 1) void attn_tc_kernel(const __grid_const
 
     const int qlen = a.q_len[e], ctx = a.ctx_len[e];
     if (qlen <= 0 || ctx <= 0) return;   // uniform over the block, before anything is allocated
+    if (base & 1023u) {                  // the layout below needs the alignment asked for above
+        if (tid == 0) atomicOr(a.status, VCB_STATUS_BAD_LAYOUT);
+        return;
+    }
     const int row0 = a.q_start[e] + q0;
     const int pos0 = ctx - qlen + q0;
     const int pos_last = pos0 + nq - 1;
@@ -206,15 +233,17 @@ __global__ __launch_bounds__(NTHREADS, 1) void attn_tc_kernel(const __grid_const
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 1);
+            mbar_init(k_full(s), 1);
+            mbar_init(k_empty(s), 1);
+            mbar_init(v_full(s), 1);
+            mbar_init(v_empty(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(s_full(b), 1);
             mbar_init(s_empty(b), 4);       // one arrival per softmax warp
-            mbar_init(p_ready(b), ROWS);    // one arrival per row
-            mbar_init(o_full(b), 1);
         }
+        mbar_init(p_ready, ROWS);           // one arrival per row
+        mbar_init(pv_done, 1);
         mbar_init(q_ready, ROWS);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -229,43 +258,53 @@ __global__ __launch_bounds__(NTHREADS, 1) void attn_tc_kernel(const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * BNK;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * BNK;   // S, S, O
 
     if (warp == 0) {
-        // ---- TMA producer: one box of [page_size keys x 64 lanes] per page, per half of head_dim, for K and V ----
-        if (lane == 0) {
-            const int pages_per_tile = BNK / ps;
-            const int rows_kv = a.nkv * ps;          // rows of the flattened [pages * 2 * nkv * ps, HD] view per K or V
-            int armed = 0;
-            for (int it = 0; it < n_tiles; ++it) {
-                const int st = it % STAGES;
-                if (!mbar_wait(empty_bar(st), ((it / STAGES) & 1) ^ 1u, abort_flag, a.status)) break;
-                const int pb0 = pb_lo + it * pages_per_tile;
-                const int np = min(pages_per_tile, pb_hi - pb0);
-                mbar_expect_tx(full_bar(st), (uint32_t)(np * ps * ROWB * 2));
-                const uint32_t kd = base + L::K_OFF + st * L::KV_BYTES, vd = base + L::V_OFF + st * L::KV_BYTES;
-                for (int pg = 0; pg < np; ++pg) {
-                    int page = bt[pb0 + pg];
-                    if (page < 0 || page >= a.num_pages) {
-                        atomicOr(a.status, VCB_STATUS_BAD_PAGE);
-                        page = 0;   // keep the byte count whole; the status word reports the fault
-                    }
-                    const int krow = (page * 2 * a.nkv + kvh) * ps;
-#pragma unroll
-                    for (int h = 0; h < HD / 64; ++h) {
-                        const uint32_t off = h * (BNK * 128) + pg * ps * 128;
-                        tma_load_2d(kd + off, &kv_map, full_bar(st), h * 64, krow);
-                        tma_load_2d(vd + off, &kv_map, full_bar(st), h * 64, krow + rows_kv);
-                    }
+        // ---- TMA producer: one box of [page_size keys x 64 lanes] per page, per half of head_dim, for K and V.
+        // The boxes of a tile (up to 32) are issued by as many lanes at once: a single thread issuing them one
+        // after the other, each behind its own block-table read, was the slowest role of the block. ----
+        const int pages_per_tile = BNK / ps;
+        const int rows_kv = a.nkv * ps;          // rows of the flattened [pages * 2 * nkv * ps, HD] view per K or V
+        constexpr int HALVES = HD / 64;
+        int armed[2] = {0, 0};
+        // loads the K (is_v 0) or V (1) tile `it` into its ring once the stage is free; false: give up
+        auto load_tile = [&](int it, int is_v) {
+            const int st = it % STAGES;
+            const uint32_t fullb = is_v ? v_full(st) : k_full(st);
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(is_v ? v_empty(st) : k_empty(st), ((it / STAGES) & 1) ^ 1u, abort_flag, a.status);
+            if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
+            const int pb0 = pb_lo + it * pages_per_tile;
+            const int np = min(pages_per_tile, pb_hi - pb0);
+            if (lane == 0) mbar_expect_tx(fullb, (uint32_t)(np * ps * ROWB));
+            __syncwarp();
+            const uint32_t dst = base + (is_v ? L::V_OFF : L::K_OFF) + st * L::KV_BYTES;
+            for (int job = lane; job < np * HALVES; job += 32) {
+                const int pg = job / HALVES, h = job % HALVES;
+                int page = bt[pb0 + pg];
+                if (page < 0 || page >= a.num_pages) {
+                    atomicOr(a.status, VCB_STATUS_BAD_PAGE);
+                    page = 0;   // keep the byte count whole; the status word reports the fault
                 }
-                armed = it + 1;
+                const int row = (page * 2 * a.nkv + kvh) * ps + (is_v ? rows_kv : 0);
+                tma_load_2d(dst + h * (BNK * 128) + pg * ps * 128, &kv_map, fullb, h * 64, row);
             }
-            if (*abort_flag) {   // let copies in flight land before the block goes away
-                for (int i = max(0, armed - STAGES); i < armed; ++i) {
+            armed[is_v] = it + 1;
+            return true;
+        };
+        bool ok = load_tile(0, 0);
+        for (int it = 0; it < n_tiles && ok; ++it) {
+            if (it + 1 < n_tiles) ok = load_tile(it + 1, 0);   // the keys of the next tile before the values of this one
+            if (ok) ok = load_tile(it, 1);
+        }
+        if (lane == 0 && *abort_flag) {   // let copies in flight land before the block goes away
+            for (int is_v = 0; is_v < 2; ++is_v)
+                for (int i = max(0, armed[is_v] - STAGES); i < armed[is_v]; ++i) {
                     const long long t0 = clock64();
-                    while (!mbar_try(full_bar(i % STAGES), (i / STAGES) & 1) && clock64() - t0 < WAIT_CLOCKS) {}
+                    const uint32_t fullb = is_v ? v_full(i % STAGES) : k_full(i % STAGES);
+                    while (!mbar_try(fullb, (i / STAGES) & 1) && clock64() - t0 < WAIT_CLOCKS) {}
                 }
-            }
         }
     } else if (warp == 1) {
         // ---- MMA issuer ----
@@ -276,7 +315,7 @@ __global__ __launch_bounds__(NTHREADS, 1) void attn_tc_kernel(const __grid_const
             // S[j & 1] = Q . K_j^T once the tile has landed and the rows have read the scores of tile j - 2
             auto issue_qk = [&](int j) {
                 const int st = j % STAGES, b = j & 1;
-                if (!mbar_wait(full_bar(st), (j / STAGES) & 1, abort_flag, a.status)) return false;
+                if (!mbar_wait(k_full(st), (j / STAGES) & 1, abort_flag, a.status)) return false;
                 if (!mbar_wait(s_empty(b), ((j >> 1) & 1) ^ 1u, abort_flag, a.status)) return false;
                 tc_fence_after();
                 const uint32_t qa = base, ka = base + L::K_OFF + st * L::KV_BYTES;
@@ -288,28 +327,29 @@ __global__ __launch_bounds__(NTHREADS, 1) void attn_tc_kernel(const __grid_const
                     tc_mma(tmem_s + b * BNK, da, db, idesc_qk, ks > 0);
                 }
                 tc_commit(s_full(b));
+                tc_commit(k_empty(st));   // the keys of this stage have been read
                 return true;
             };
             if (ok) ok = issue_qk(0);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                const int st = j % STAGES, b = j & 1;
+                const int st = j % STAGES;
                 if (j + 1 < n_tiles) {
                     ok = issue_qk(j + 1);   // runs while the rows work on tile j
                     if (!ok) break;
                 }
-                ok = mbar_wait(p_ready(b), (j >> 1) & 1, abort_flag, a.status);
+                ok = mbar_wait(p_ready, j & 1, abort_flag, a.status) && mbar_wait(v_full(st), (j / STAGES) & 1, abort_flag, a.status);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t pa = base + L::P_OFF + b * L::P_BYTES, va = base + L::V_OFF + st * L::KV_BYTES;
+                const uint32_t pa = base + L::P_OFF, va = base + L::V_OFF + st * L::KV_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < BNK / 16; ++ks) {
                     const uint64_t da = desc_k_major(pa + ks * 32);
                     // 16 keys = 16 rows of 128 bytes further on; the second 64 lanes of head_dim are the next block
                     const uint64_t db = desc_mn_major(va + ks * 16 * 128, BNK * 128);
-                    tc_mma(tmem_o + b * HD, da, db, idesc_pv, ks > 0);
+                    tc_mma(tmem_o, da, db, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                 }
-                tc_commit(o_full(b));
-                tc_commit(empty_bar(st));   // K and V of this stage have been read
+                tc_commit(pv_done);
+                tc_commit(v_empty(st));   // the values of this stage have been read
             }
         }
     } else {
@@ -335,30 +375,9 @@ __global__ __launch_bounds__(NTHREADS, 1) void attn_tc_kernel(const __grid_const
             mbar_arrive(q_ready);
         }
 
-        float o[HD];
-#pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.f;
-        float m_run = -CUDART_INF_F, l_run = 0.f, alpha_prev = 1.f;
+        float m_ref = -CUDART_INF_F, l_run = 0.f;   // reference maximum (scaled, log2 domain) and sum against it
         const float scale_log2 = a.scale * LOG2E;
         bool ok = true;
-
-        // o = o * alpha + O_jj, and the O buffer is the MMA thread's again
-        auto fold = [&](int jj, float alpha) {
-            const int bb = jj & 1;
-            if (!mbar_wait(o_full(bb), (jj >> 1) & 1, abort_flag, a.status)) return false;
-            tc_fence_after();
-#pragma unroll
-            for (int c0 = 0; c0 < HD; c0 += 32) {
-                uint32_t v[2][16];
-                tc_ld16(tmem_o + lane_addr + (uint32_t)(bb * HD + c0), v[0]);
-                tc_ld16(tmem_o + lane_addr + (uint32_t)(bb * HD + c0 + 16), v[1]);
-                tc_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, __uint_as_float(v[i / 16][i % 16]));
-            }
-            tc_fence_before();
-            return true;
-        };
 
         for (int j = 0; j < n_tiles; ++j) {
             const int b = j & 1, st = j % STAGES;
@@ -374,37 +393,66 @@ __global__ __launch_bounds__(NTHREADS, 1) void attn_tc_kernel(const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive(s_empty(b));   // this warp has read its quarter of the scores
 
-            float mx = -CUDART_INF_F;
+            // Scores stay unscaled in sv; only tiles that touch a row's own position or the window's edge mask.
+            const bool plain_tile = t0 + BNK - 1 <= pos0 && (W == 0 || t0 >= pos_last - W + 1);   // uniform over the block
+            float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+            if (plain_tile) {
 #pragma unroll
-            for (int c = 0; c < BNK; ++c) {
-                const int kidx = t0 + c;
-                const bool valid = row_ok && kidx >= lo_r && kidx <= pos_r;
-                const float s = valid ? __uint_as_float(sv[c / 16][c % 16]) * scale_log2 : -CUDART_INF_F;
-                sv[c / 16][c % 16] = __float_as_uint(s);
-                mx = fmaxf(mx, s);
+                for (int c = 0; c < BNK; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c / 16][c % 16]));
+            } else {
+#pragma unroll
+                for (int c = 0; c < BNK; ++c) {
+                    const int kidx = t0 + c;
+                    const bool valid = row_ok && kidx >= lo_r && kidx <= pos_r;
+                    const float sc = valid ? __uint_as_float(sv[c / 16][c % 16]) : -CUDART_INF_F;
+                    sv[c / 16][c % 16] = __float_as_uint(sc);
+                    mx4[c & 3] = fmaxf(mx4[c & 3], sc);
+                }
             }
-            const float m_new = fmaxf(m_run, mx);
-            float alpha = 1.f, m_sub = 0.f;
-            if (m_new != -CUDART_INF_F) {       // otherwise the row has seen no key yet: every weight is zero
-                alpha = exp2f(m_run - m_new);   // 0 for the first keys
-                m_sub = m_new;
+            // the scale is positive: the maximum of the scaled scores is the scaled maximum
+            const float m_new = fmaxf(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2, m_ref);
+            // Move the reference when the maximum has outgrown it.  O (in TMEM) holds the sum so far against the
+            // old reference: the warp rescales its 32 rows together, rows that keep theirs by a factor of one.
+            const bool first_keys = m_ref == -CUDART_INF_F && m_new != -CUDART_INF_F;   // nothing summed yet
+            const bool grow = m_ref != -CUDART_INF_F && m_new > m_ref + RESCALE_STEP;
+            if (__any_sync(0xffffffffu, grow)) {
+                ok = mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status);   // grow implies j > 0
+                if (!ok) break;
+                tc_fence_after();
+                const float alpha = grow ? exp2f(m_ref - m_new) : 1.f;
+#pragma unroll
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t v[2][16];
+                    tc_ld16(tmem_o + lane_addr + (uint32_t)c0, v[0]);
+                    tc_ld16(tmem_o + lane_addr + (uint32_t)(c0 + 16), v[1]);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i / 16][i % 16] = __float_as_uint(__uint_as_float(v[i / 16][i % 16]) * alpha);
+                    tc_st16(tmem_o + lane_addr + (uint32_t)c0, v[0]);
+                    tc_st16(tmem_o + lane_addr + (uint32_t)(c0 + 16), v[1]);
+                }
+                tc_wait_st();
+                tc_fence_before();
+                l_run *= alpha;
             }
-            float sum = 0.f;
+            if (grow || first_keys) m_ref = m_new;
+            const float m_sub = m_ref == -CUDART_INF_F ? 0.f : m_ref;   // no key yet: every weight is exp2(-inf) = 0
+
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk[BNK / 2];
 #pragma unroll
             for (int c = 0; c < BNK; c += 2) {
-                const float p0 = exp2f(__uint_as_float(sv[c / 16][c % 16]) - m_sub);
-                const float p1 = exp2f(__uint_as_float(sv[(c + 1) / 16][(c + 1) % 16]) - m_sub);
-                sum += p0 + p1;
+                const float p0 = ex2_fast(fmaf(__uint_as_float(sv[c / 16][c % 16]), scale_log2, -m_sub));
+                const float p1 = ex2_fast(fmaf(__uint_as_float(sv[(c + 1) / 16][(c + 1) % 16]), scale_log2, -m_sub));
+                sum4[(c >> 1) & 3] += p0 + p1;
                 pk[c / 2] = pack_bf16(p0, p1);
             }
-            l_run = l_run * alpha + sum;
-            m_run = m_new;
+            l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
 
             if (t0 + BNK > k_end) {
                 // The last page may hold slots beyond the sequence, and rows of pages that were not loaded are
                 // stale: their V must be finite, because a zero weight times NaN is NaN.
-                ok = mbar_wait(full_bar(st), (j / STAGES) & 1, abort_flag, a.status);
+                ok = mbar_wait(v_full(st), (j / STAGES) & 1, abort_flag, a.status);
                 if (!ok) break;
                 const int first = k_end - t0;
                 for (int idx = r; idx < (BNK - first) * CH; idx += ROWS) {
@@ -412,30 +460,41 @@ __global__ __launch_bounds__(NTHREADS, 1) void attn_tc_kernel(const __grid_const
                     *reinterpret_cast<uint4*>(gen + L::V_OFF + st * L::KV_BYTES + swz<BNK>(jj, c)) = make_uint4(0, 0, 0, 0);
                 }
             }
+            if (j > 0) {   // the product of the tile before has read P
+                ok = mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status);
+                if (!ok) break;
+            }
             // the row of P as the A operand of P . V: 64 keys = 128 bytes, swizzled like every other row
-            uint8_t* prow = gen + L::P_OFF + b * L::P_BYTES + r * 128;
+            uint8_t* prow = gen + L::P_OFF + r * 128;
 #pragma unroll
             for (int c = 0; c < 8; ++c)
                 *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
             fence_async_smem();
-            mbar_arrive(p_ready(b));
-
-            if (j > 0) {
-                ok = fold(j - 1, alpha_prev);
-                if (!ok) break;
-            }
-            alpha_prev = alpha;
+            mbar_arrive(p_ready);
         }
-        if (ok) ok = fold(n_tiles - 1, alpha_prev);
+        if (ok) ok = mbar_wait(pv_done, (n_tiles - 1) & 1, abort_flag, a.status);
 
-        if (ok && row_ok) {
+        if (ok) {
+            tc_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             __nv_bfloat16* dst = a.out + ((size_t)(row0 + iq) * a.nh + head0 + ih) * HD;
 #pragma unroll
-            for (int c = 0; c < CH; ++c)
-                *reinterpret_cast<uint4*>(dst + c * 8) =
-                    make_uint4(pack_bf16(o[8 * c] * inv, o[8 * c + 1] * inv), pack_bf16(o[8 * c + 2] * inv, o[8 * c + 3] * inv),
-                               pack_bf16(o[8 * c + 4] * inv, o[8 * c + 5] * inv), pack_bf16(o[8 * c + 6] * inv, o[8 * c + 7] * inv));
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t v[2][16];
+                tc_ld16(tmem_o + lane_addr + (uint32_t)c0, v[0]);
+                tc_ld16(tmem_o + lane_addr + (uint32_t)(c0 + 16), v[1]);
+                tc_wait_ld();
+                if (row_ok) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float f[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[(8 * c + i) / 16][(8 * c + i) % 16]) * inv;
+                        *reinterpret_cast<uint4*>(dst + c0 + 8 * c) =
+                            make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+                    }
+                }
+            }
         }
         tc_fence_before();
     }
@@ -448,7 +507,7 @@ __global__ __launch_bounds__(NTHREADS, 1) void attn_tc_kernel(const __grid_const
 
 template <int HD>
 int launch(const CUtensorMap& map, const TcArgs& a, int n_items, cudaStream_t stream) {
-    constexpr int STAGES = 4;
+    constexpr int STAGES = 2;
     using L = Layout<HD, STAGES>;
     auto kern = attn_tc_kernel<HD, STAGES>;
     static bool opted = false;

@@ -16,7 +16,8 @@ from .csrc import build as _build
 
 F32, BF16 = 0, 1
 STATUS_BITS = {1: "token id outside the vocabulary", 2: "page id outside the pool",
-               4: "a bounded wait inside a kernel gave up", 8: "position outside the rotary table"}
+               4: "a bounded wait inside a kernel gave up", 8: "position outside the rotary table",
+               16: "shared memory did not start on the boundary a kernel's tiles need"}
 ITEM_INTS = 6
 
 _lib = None
