@@ -279,6 +279,40 @@ def test_attention_long_prompt_portions(nh, nkv, hd, ps, window):
     run_attention(torch.bfloat16, nh, nkv, hd, ps, window, [(0, 300), (517, 130), (1000, 2), (63, 65), (64, 64), (0, 64)])
 
 
+def test_attention_tcgen05_many_blocks_many_launches():
+    """Two thousand tokens on 32 heads: 512 blocks of up to 32 key tiles, launched over and over, against the
+    mma.sync kernel on the same inputs.  (Warps of a block may run a tile apart; a hand-off that counted on their
+    staying together showed only here, once in a few hundred launches.)"""
+    from vllm_cpp_b200 import ops
+    from vllm_cpp_b200.parts import attention as A
+    nh, nkv, hd, ps, T = 32, 8, 128, 16, 2048
+    torch.manual_seed(3)
+    npages = T // ps
+    pages = torch.randn(npages, 2, nkv, ps, hd, device=dev()).to(torch.bfloat16)
+    bt = torch.randperm(npages, device=dev()).to(torch.int32).view(1, -1)
+    q = torch.randn(T, nh * hd, device=dev()).to(torch.bfloat16)
+
+    class Ctx:
+        pass
+    c = Ctx()
+    c.device, c.host_q_len, c.host_ctx_len, c.host_q_start = dev(), [T], [T], [0]
+    plan = A.AttentionPlan(c, nh, nkv, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev())
+    qs, ql, cl = i32([0]), i32([T]), i32([T])
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    want = torch.empty_like(q)
+    ops.attn_mma(q, want, pages, bt, qs, ql, cl, plan.span_items, plan.n_span_items, A.MMA_SPAN_ROWS, None, None,
+                 nh, nkv, hd, 0, status)
+    outs = [torch.full_like(q, float("nan")) for _ in range(4)]
+    for i in range(200):
+        ops.attn_tc(q, outs[i % 4], pages, bt, qs, ql, cl, plan.span_items, plan.n_span_items, nh, nkv, hd, 0, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    for o in outs:
+        torch.testing.assert_close(o.float(), want.float(), rtol=2e-2, atol=2e-2)
+        assert torch.equal(o, outs[0])      # and the same bits every time
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_long_decode_is_sliced(dtype):
     plan = run_attention(dtype, 8, 2, 64, 16, 0, [(3000, 1), (1025, 1)])

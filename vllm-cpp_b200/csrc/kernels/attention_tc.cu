@@ -9,8 +9,9 @@
 //   S = Q . K^T     one MMA chain, M = 128 rows (TMEM lanes), N = 64 keys, K = head_dim; Q and the K tile are
 //                   K-major operands in 128-byte-swizzled shared memory, S lands in TMEM (two buffers);
 //   softmax         four warps, one thread per row (= per TMEM lane): tcgen05.ld of the row's 64 scores, mask,
-//                   running maximum and sum in 32-bit, P = exp2(s - m) rounded to bfloat16 into shared memory
-//                   laid out as the A operand of the next product;
+//                   running maximum and sum in 32-bit, P = exp2(s - m) rounded to bfloat16 and written back over the
+//                   row's scores in TMEM (tcgen05.st, two weights a column), where the next product reads it as
+//                   its A operand;
 //   O += P . V      M = 128, N = head_dim, K = 64 keys; the V tile is used as it lies in the cache (keys x
 //                   head_dim, head_dim contiguous), i.e. as an MN-major B operand; O stays in TMEM over all
 //                   tiles.  A row's weights are taken against a reference maximum that is only moved, and O
@@ -19,7 +20,8 @@
 //                   numerator and denominator carry the same reference.
 //
 // Two blocks share an SM (112 KB of shared memory and 256 TMEM columns each), so one block's softmax overlaps
-// the other's products.
+// the other's products.  K tiles have a ring of three stages and V tiles one of two: a K stage is free again
+// as soon as its scores are computed, and the next keys must be asked for two tiles ahead to arrive in time.
 // Roles (192 threads): warp 0 issues TMA loads of K and V pages (cp.async.bulk.tensor, 128-byte swizzle; no
 // multicast) into a ring of stages; warp 1 allocates TMEM and issues every MMA; warps 2-5 are the softmax rows.
 // All hand-offs are mbarriers; every wait is bounded by the clock, and a wait that runs out sets a bit in the
@@ -104,6 +106,14 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the same with the A operand in TMEM (lane = row, two bfloat16 of consecutive k per 32-bit column)
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -156,27 +166,25 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int HD, int STAGES>
+template <int HD, int KS, int VS>
 struct Layout {
     static constexpr int Q_BYTES = ROWS * HD * 2;
     static constexpr int KV_BYTES = BNK * HD * 2;       // one K or V tile
-    static constexpr int P_BYTES = ROWS * BNK * 2;
     static constexpr int K_OFF = Q_BYTES;
-    static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
-    static constexpr int P_OFF = V_OFF + STAGES * KV_BYTES;
-    static constexpr int BAR_OFF = P_OFF + P_BYTES;
-    static constexpr int NUM_BARS = 4 * STAGES + 7;
+    static constexpr int V_OFF = K_OFF + KS * KV_BYTES;
+    static constexpr int BAR_OFF = V_OFF + VS * KV_BYTES;
+    static constexpr int NUM_BARS = 2 * KS + 2 * VS + 6;
     static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16;   // + TMEM address, abort flag
-    static constexpr uint32_t TMEM_COLS = 256;                  // S, S (64 each), O (head_dim)
+    static constexpr uint32_t TMEM_COLS = 256;                  // S, S (64 each; P over the first half of its S), O (head_dim)
     static_assert(2 * BNK + HD <= 256, "TMEM columns");
     static_assert(2 * (TOTAL + 1024) <= 228 * 1024, "two blocks per SM");
 };
 
 constexpr float RESCALE_STEP = 8.0f;   // log2 of how far a row's maximum may outgrow its reference
 
-template <int HD, int STAGES>
+template <int HD, int KS, int VS>
 __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_constant__ CUtensorMap kv_map, TcArgs a) {
-    using L = Layout<HD, STAGES>;
+    using L = Layout<HD, KS, VS>;
     constexpr int CH = HD / 8;          // 16-byte chunks per row of head_dim
     constexpr int ROWB = HD * 2;
     constexpr float LOG2E = 1.4426950408889634f;
@@ -185,17 +193,17 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
     uint8_t* gen = smem_raw;
     const uint32_t base = smem_u32(smem_raw);
     const uint32_t bars = base + L::BAR_OFF;
-    // K and V tiles have rings of their own: a K stage is free again once the scores of its tile are computed,
-    // a whole tile's softmax before the V stage is, so the next keys are asked for that much earlier.
     auto k_full = [&](int s) { return bars + 8u * s; };
-    auto k_empty = [&](int s) { return bars + 8u * (STAGES + s); };
-    auto v_full = [&](int s) { return bars + 8u * (2 * STAGES + s); };
-    auto v_empty = [&](int s) { return bars + 8u * (3 * STAGES + s); };
-    auto s_full = [&](int b) { return bars + 8u * (4 * STAGES + b); };
-    auto s_empty = [&](int b) { return bars + 8u * (4 * STAGES + 2 + b); };
-    const uint32_t p_ready = bars + 8u * (4 * STAGES + 4);   // one phase per tile: every row has written its weights
-    const uint32_t pv_done = bars + 8u * (4 * STAGES + 5);   // one phase per tile: P . V of the tile has been added to O
-    const uint32_t q_ready = bars + 8u * (4 * STAGES + 6);
+    auto k_empty = [&](int s) { return bars + 8u * (KS + s); };
+    auto v_full = [&](int s) { return bars + 8u * (2 * KS + s); };
+    auto v_empty = [&](int s) { return bars + 8u * (2 * KS + VS + s); };
+    auto s_full = [&](int b) { return bars + 8u * (2 * KS + 2 * VS + b); };
+    // Every row has written its weights of a tile.  One barrier per score buffer: a warp may finish tile j + 1
+    // before another has finished tile j (its scores are ready early), and with a single barrier its second
+    // arrival would be counted into the phase of tile j.  Tile j + 2 cannot begin before that phase is over.
+    auto p_ready = [&](int b) { return bars + 8u * (2 * KS + 2 * VS + 2 + b); };
+    const uint32_t pv_done = bars + 8u * (2 * KS + 2 * VS + 4);   // one phase per tile: P . V of the tile has been added to O
+    const uint32_t q_ready = bars + 8u * (2 * KS + 2 * VS + 5);
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(gen + L::BAR_OFF + L::NUM_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::BAR_OFF + L::NUM_BARS * 8 + 8);
 
@@ -232,17 +240,18 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
     const int* bt = a.block_table + (size_t)(a.table_row ? a.table_row[e] : e) * a.max_blocks;
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < KS; ++s) {
             mbar_init(k_full(s), 1);
             mbar_init(k_empty(s), 1);
+        }
+        for (int s = 0; s < VS; ++s) {
             mbar_init(v_full(s), 1);
             mbar_init(v_empty(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(s_full(b), 1);
-            mbar_init(s_empty(b), 4);       // one arrival per softmax warp
+            mbar_init(p_ready(b), ROWS);    // one arrival per row
         }
-        mbar_init(p_ready, ROWS);           // one arrival per row
         mbar_init(pv_done, 1);
         mbar_init(q_ready, ROWS);
         *abort_flag = 0;
@@ -268,43 +277,55 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
         const int rows_kv = a.nkv * ps;          // rows of the flattened [pages * 2 * nkv * ps, HD] view per K or V
         constexpr int HALVES = HD / 64;
         int armed[2] = {0, 0};
+        // This lane's page id for the next K and the next V tile, read one call ahead: a block-table read that
+        // misses L1 costs about as long as a whole tile's products, and it stood between the stage's release
+        // and the load.  Tiles of one kind are loaded in order, so the next tile is known.
+        const int my_pg = lane / HALVES, my_h = lane % HALVES;
+        auto page_of = [&](int it) {
+            const int pb = pb_lo + it * pages_per_tile + my_pg;
+            return (it < n_tiles && my_pg < pages_per_tile && pb < pb_hi) ? bt[pb] : -1;
+        };
+        int next_page[2] = {page_of(0), page_of(0)};
         // loads the K (is_v 0) or V (1) tile `it` into its ring once the stage is free; false: give up
         auto load_tile = [&](int it, int is_v) {
-            const int st = it % STAGES;
+            const int ns = is_v ? VS : KS, st = it % ns;
             const uint32_t fullb = is_v ? v_full(st) : k_full(st);
             bool ok = true;
-            if (lane == 0) ok = mbar_wait(is_v ? v_empty(st) : k_empty(st), ((it / STAGES) & 1) ^ 1u, abort_flag, a.status);
+            if (lane == 0) ok = mbar_wait(is_v ? v_empty(st) : k_empty(st), ((it / ns) & 1) ^ 1u, abort_flag, a.status);
             if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
             const int pb0 = pb_lo + it * pages_per_tile;
             const int np = min(pages_per_tile, pb_hi - pb0);
             if (lane == 0) mbar_expect_tx(fullb, (uint32_t)(np * ps * ROWB));
             __syncwarp();
             const uint32_t dst = base + (is_v ? L::V_OFF : L::K_OFF) + st * L::KV_BYTES;
-            for (int job = lane; job < np * HALVES; job += 32) {
-                const int pg = job / HALVES, h = job % HALVES;
-                int page = bt[pb0 + pg];
+            if (lane < np * HALVES) {   // at most 8 pages x 2 halves: one box a lane
+                int page = next_page[is_v];
                 if (page < 0 || page >= a.num_pages) {
                     atomicOr(a.status, VCB_STATUS_BAD_PAGE);
                     page = 0;   // keep the byte count whole; the status word reports the fault
                 }
                 const int row = (page * 2 * a.nkv + kvh) * ps + (is_v ? rows_kv : 0);
-                tma_load_2d(dst + h * (BNK * 128) + pg * ps * 128, &kv_map, fullb, h * 64, row);
+                tma_load_2d(dst + my_h * (BNK * 128) + my_pg * ps * 128, &kv_map, fullb, my_h * 64, row);
             }
+            next_page[is_v] = page_of(it + 1);
             armed[is_v] = it + 1;
             return true;
         };
         bool ok = load_tile(0, 0);
+        if (ok && n_tiles > 1) ok = load_tile(1, 0);
         for (int it = 0; it < n_tiles && ok; ++it) {
-            if (it + 1 < n_tiles) ok = load_tile(it + 1, 0);   // the keys of the next tile before the values of this one
+            if (it + 2 < n_tiles) ok = load_tile(it + 2, 0);   // keys two tiles ahead of the values
             if (ok) ok = load_tile(it, 1);
         }
         if (lane == 0 && *abort_flag) {   // let copies in flight land before the block goes away
-            for (int is_v = 0; is_v < 2; ++is_v)
-                for (int i = max(0, armed[is_v] - STAGES); i < armed[is_v]; ++i) {
+            for (int is_v = 0; is_v < 2; ++is_v) {
+                const int ns = is_v ? VS : KS;
+                for (int i = max(0, armed[is_v] - ns); i < armed[is_v]; ++i) {
                     const long long t0 = clock64();
-                    const uint32_t fullb = is_v ? v_full(i % STAGES) : k_full(i % STAGES);
-                    while (!mbar_try(fullb, (i / STAGES) & 1) && clock64() - t0 < WAIT_CLOCKS) {}
+                    const uint32_t fullb = is_v ? v_full(i % ns) : k_full(i % ns);
+                    while (!mbar_try(fullb, (i / ns) & 1) && clock64() - t0 < WAIT_CLOCKS) {}
                 }
+            }
         }
     } else if (warp == 1) {
         // ---- MMA issuer ----
@@ -312,11 +333,11 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
             constexpr uint32_t idesc_qk = instr_desc(BNK, false);
             constexpr uint32_t idesc_pv = instr_desc(HD, true);
             bool ok = mbar_wait(q_ready, 0, abort_flag, a.status);
-            // S[j & 1] = Q . K_j^T once the tile has landed and the rows have read the scores of tile j - 2
+            // S[j & 1] = Q . K_j^T once the tile has landed.  The buffer's last user was P . V of tile j - 2, issued
+            // before this by the same thread, and the tensor cores work through their queue in order.
             auto issue_qk = [&](int j) {
-                const int st = j % STAGES, b = j & 1;
-                if (!mbar_wait(k_full(st), (j / STAGES) & 1, abort_flag, a.status)) return false;
-                if (!mbar_wait(s_empty(b), ((j >> 1) & 1) ^ 1u, abort_flag, a.status)) return false;
+                const int st = j % KS, b = j & 1;
+                if (!mbar_wait(k_full(st), (j / KS) & 1, abort_flag, a.status)) return false;
                 tc_fence_after();
                 const uint32_t qa = base, ka = base + L::K_OFF + st * L::KV_BYTES;
 #pragma unroll
@@ -332,21 +353,21 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
             };
             if (ok) ok = issue_qk(0);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                const int st = j % STAGES;
+                const int st = j % VS, b = j & 1;
                 if (j + 1 < n_tiles) {
                     ok = issue_qk(j + 1);   // runs while the rows work on tile j
                     if (!ok) break;
                 }
-                ok = mbar_wait(p_ready, j & 1, abort_flag, a.status) && mbar_wait(v_full(st), (j / STAGES) & 1, abort_flag, a.status);
+                ok = mbar_wait(p_ready(b), (j >> 1) & 1, abort_flag, a.status) && mbar_wait(v_full(st), (j / VS) & 1, abort_flag, a.status);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t pa = base + L::P_OFF, va = base + L::V_OFF + st * L::KV_BYTES;
+                const uint32_t va = base + L::V_OFF + st * L::KV_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < BNK / 16; ++ks) {
-                    const uint64_t da = desc_k_major(pa + ks * 32);
-                    // 16 keys = 16 rows of 128 bytes further on; the second 64 lanes of head_dim are the next block
+                    // 16 keys = 16 rows of 128 bytes further on; the second 64 lanes of head_dim are the next block.
+                    // P: 16 keys = 8 columns of the scores' buffer.
                     const uint64_t db = desc_mn_major(va + ks * 16 * 128, BNK * 128);
-                    tc_mma(tmem_o, da, db, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    tc_mma_ts(tmem_o, tmem_s + b * BNK + ks * 8, db, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 tc_commit(pv_done);
                 tc_commit(v_empty(st));   // the values of this stage have been read
@@ -380,7 +401,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
         bool ok = true;
 
         for (int j = 0; j < n_tiles; ++j) {
-            const int b = j & 1, st = j % STAGES;
+            const int b = j & 1, st = j % VS;
             const int t0 = t_first + j * BNK;
             ok = mbar_wait(s_full(b), (j >> 1) & 1, abort_flag, a.status);
             if (!ok) break;
@@ -389,9 +410,6 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
 #pragma unroll
             for (int i = 0; i < 4; ++i) tc_ld16(tmem_s + lane_addr + (uint32_t)(b * BNK + 16 * i), sv[i]);
             tc_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty(b));   // this warp has read its quarter of the scores
 
             // Scores stay unscaled in sv; only tiles that touch a row's own position or the window's edge mask.
             const bool plain_tile = t0 + BNK - 1 <= pos0 && (W == 0 || t0 >= pos_last - W + 1);   // uniform over the block
@@ -452,25 +470,33 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
             if (t0 + BNK > k_end) {
                 // The last page may hold slots beyond the sequence, and rows of pages that were not loaded are
                 // stale: their V must be finite, because a zero weight times NaN is NaN.
-                ok = mbar_wait(v_full(st), (j / STAGES) & 1, abort_flag, a.status);
+                ok = mbar_wait(v_full(st), (j / VS) & 1, abort_flag, a.status);
                 if (!ok) break;
                 const int first = k_end - t0;
                 for (int idx = r; idx < (BNK - first) * CH; idx += ROWS) {
                     const int jj = first + idx / CH, c = idx % CH;
                     *reinterpret_cast<uint4*>(gen + L::V_OFF + st * L::KV_BYTES + swz<BNK>(jj, c)) = make_uint4(0, 0, 0, 0);
                 }
+                fence_async_smem();   // before the arrival below, which the product that reads these rows awaits
             }
-            if (j > 0) {   // the product of the tile before has read P
+            // Every row sees the product of the tile before finish before it hands over this one.  Nothing it
+            // writes needs that, but the barrier counts one phase per tile and is asked by parity: a row that ran
+            // two tiles ahead of it would take an old phase for the one it waits for (when it rescales O, and
+            // before it reads O at the end).
+            if (j > 0) {
                 ok = mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status);
                 if (!ok) break;
             }
-            // the row of P as the A operand of P . V: 64 keys = 128 bytes, swizzled like every other row
-            uint8_t* prow = gen + L::P_OFF + r * 128;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-            fence_async_smem();
-            mbar_arrive(p_ready);
+            // The row of P over the first half of its scores: column c holds the weights of keys 2c and 2c + 1.
+            // (P of tile j - 2 lay here; its product was issued before the scores of this tile were computed.)
+            {
+                uint32_t (*pk16)[16] = reinterpret_cast<uint32_t (*)[16]>(pk);
+                tc_st16(tmem_s + lane_addr + (uint32_t)(b * BNK), pk16[0]);
+                tc_st16(tmem_s + lane_addr + (uint32_t)(b * BNK + 16), pk16[1]);
+                tc_wait_st();
+            }
+            tc_fence_before();
+            mbar_arrive(p_ready(b));
         }
         if (ok) ok = mbar_wait(pv_done, (n_tiles - 1) & 1, abort_flag, a.status);
 
@@ -507,9 +533,9 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
 
 template <int HD>
 int launch(const CUtensorMap& map, const TcArgs& a, int n_items, cudaStream_t stream) {
-    constexpr int STAGES = 2;
-    using L = Layout<HD, STAGES>;
-    auto kern = attn_tc_kernel<HD, STAGES>;
+    constexpr int KS = 3, VS = 2;
+    using L = Layout<HD, KS, VS>;
+    auto kern = attn_tc_kernel<HD, KS, VS>;
     static bool opted = false;
     if (!opted) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
