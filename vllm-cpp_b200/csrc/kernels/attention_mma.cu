@@ -246,39 +246,46 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
     __syncthreads();   // Q and the barriers are in shared memory
 
     if (TMA && warp == NW) {
-        // ---- TMA producer: one box of [page_size keys x 64 lanes] per page, per half of head_dim, for K and V ----
-        if (lane == 0) {
-            const int pages_per_tile = BN / ps;
-            const int rows_kv = a.nkv * ps;          // rows of the flattened [pages * 2 * nkv * ps, HD] view per K or V
-            int armed = 0;
-            for (int it = 0; it < n_tiles; ++it) {
-                const int st = it % STAGES;
-                if (!mbar_wait(empty_bar(st), ((it / STAGES) & 1) ^ 1u, abort_flag, a.status)) break;
-                const int pb0 = my_pb_lo + it * pages_per_tile;
-                const int np = min(pages_per_tile, my_pb_hi - pb0);
-                mbar_expect_tx(full_bar(st), (uint32_t)(np * ps * ROWB * 2));
-                const uint32_t kd = smem_u32(k_s + st * TILE_BYTES), vd = smem_u32(v_s + st * TILE_BYTES);
-                for (int pg = 0; pg < np; ++pg) {
-                    int page = bt[pb0 + pg];
-                    if (page < 0 || page >= a.num_pages) {
-                        atomicOr(a.status, VCB_STATUS_BAD_PAGE);
-                        page = 0;   // keep the byte count whole; the status word reports the fault
-                    }
-                    const int krow = (page * 2 * a.nkv + kvh) * ps;
-#pragma unroll
-                    for (int h = 0; h < HD / 64; ++h) {
-                        const uint32_t off = h * (BN * 128) + pg * ps * 128;
-                        tma_load_2d(kd + off, &kv_map, full_bar(st), h * 64, krow);
-                        tma_load_2d(vd + off, &kv_map, full_bar(st), h * 64, krow + rows_kv);
-                    }
+        // ---- TMA producer: one box of [page_size keys x 64 lanes] per page, per half of head_dim, for K and V.
+        // The boxes of a tile (up to 32) are issued by as many lanes at once, each with its page id read one tile
+        // ahead: one thread issuing them in turn, each behind its own block-table read, took about as long as
+        // the tile's share of HBM time. ----
+        const int pages_per_tile = BN / ps;
+        const int rows_kv = a.nkv * ps;          // rows of the flattened [pages * 2 * nkv * ps, HD] view per K or V
+        constexpr int HALVES = HD / 64;
+        const int my_pg = lane / (HALVES * 2), my_h = (lane >> 1) % HALVES, my_v = lane & 1;
+        auto page_of = [&](int it) {
+            const int pb = my_pb_lo + it * pages_per_tile + my_pg;
+            return (it < n_tiles && my_pg < pages_per_tile && pb < my_pb_hi) ? bt[pb] : -1;
+        };
+        int next_page = page_of(0);
+        int armed = 0;
+        for (int it = 0; it < n_tiles; ++it) {
+            const int st = it % STAGES;
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(empty_bar(st), ((it / STAGES) & 1) ^ 1u, abort_flag, a.status);
+            if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+            const int pb0 = my_pb_lo + it * pages_per_tile;
+            const int np = min(pages_per_tile, my_pb_hi - pb0);
+            if (lane == 0) mbar_expect_tx(full_bar(st), (uint32_t)(np * ps * ROWB * 2));
+            __syncwarp();
+            if (my_pg < np) {
+                int page = next_page;
+                if (page < 0 || page >= a.num_pages) {
+                    atomicOr(a.status, VCB_STATUS_BAD_PAGE);
+                    page = 0;   // keep the byte count whole; the status word reports the fault
                 }
-                armed = it + 1;
+                const int row = (page * 2 * a.nkv + kvh) * ps + (my_v ? rows_kv : 0);
+                const uint32_t dst = smem_u32((my_v ? v_s : k_s) + st * TILE_BYTES) + my_h * (BN * 128) + my_pg * ps * 128;
+                tma_load_2d(dst, &kv_map, full_bar(st), my_h * 64, row);
             }
-            if (*abort_flag) {   // let copies in flight land before the block goes away
-                for (int i = max(0, armed - STAGES); i < armed; ++i) {
-                    const long long t0 = clock64();
-                    while (!mbar_try(full_bar(i % STAGES), (i / STAGES) & 1) && clock64() - t0 < WAIT_CLOCKS) {}
-                }
+            next_page = page_of(it + 1);
+            armed = it + 1;
+        }
+        if (lane == 0 && *abort_flag) {   // let copies in flight land before the block goes away
+            for (int i = max(0, armed - STAGES); i < armed; ++i) {
+                const long long t0 = clock64();
+                while (!mbar_try(full_bar(i % STAGES), (i / STAGES) & 1) && clock64() - t0 < WAIT_CLOCKS) {}
             }
         }
     }
