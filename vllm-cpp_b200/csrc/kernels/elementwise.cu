@@ -371,32 +371,45 @@ __global__ __launch_bounds__(256) void qknorm_rope_kvwrite_hd128_kernel(
         }
     }
     const __nv_bfloat16* row = qkv + (size_t)t * heads_total * hd;
-    for (int h = warp; h < heads_total; h += nwarps) {
-        const __nv_bfloat16* src = row + (size_t)h * hd;
-        __nv_bfloat16* dst;
-        if (h < nh) {
-            dst = q_out + ((size_t)t * nh + h) * hd;
-        } else {
-            if (slot < 0) continue;   // padded token: nothing to store
-            const int kv = h >= nh + nkv, kvh = kv ? h - nh - nkv : h - nh;
-            dst = pages + (size_t)(slot / page_size) * page_stride + ((size_t)(kv * nkv + kvh) * page_size + slot % page_size) * hd;
+    // four heads a round: their loads are all issued before the first is used
+    constexpr int U = 4;
+    for (int h0 = warp; h0 < heads_total; h0 += U * nwarps) {
+        __nv_bfloat162 lo[U], hi[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int h = h0 + u * nwarps;
+            if (h < heads_total) {
+                lo[u] = *reinterpret_cast<const __nv_bfloat162*>(row + (size_t)h * hd + 2 * lane);
+                hi[u] = *reinterpret_cast<const __nv_bfloat162*>(row + (size_t)h * hd + half + 2 * lane);
+            }
         }
-        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(src + 2 * lane);
-        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(src + half + 2 * lane);
-        if (h >= nh + nkv) {   // V: stored as it is
-            *reinterpret_cast<__nv_bfloat162*>(dst + 2 * lane) = lo;
-            *reinterpret_cast<__nv_bfloat162*>(dst + half + 2 * lane) = hi;
-            continue;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int h = h0 + u * nwarps;
+            if (h >= heads_total) break;
+            __nv_bfloat16* dst;
+            if (h < nh) {
+                dst = q_out + ((size_t)t * nh + h) * hd;
+            } else {
+                if (slot < 0) continue;   // padded token: nothing to store
+                const int kv = h >= nh + nkv, kvh = kv ? h - nh - nkv : h - nh;
+                dst = pages + (size_t)(slot / page_size) * page_stride + ((size_t)(kv * nkv + kvh) * page_size + slot % page_size) * hd;
+            }
+            if (h >= nh + nkv) {   // V: stored as it is
+                *reinterpret_cast<__nv_bfloat162*>(dst + 2 * lane) = lo[u];
+                *reinterpret_cast<__nv_bfloat162*>(dst + half + 2 * lane) = hi[u];
+                continue;
+            }
+            float a0 = __low2float(lo[u]), a1 = __high2float(lo[u]), b0 = __low2float(hi[u]), b1 = __high2float(hi[u]);
+            if (use_norm) {
+                const float ss = warp_sum(a0 * a0 + a1 * a1 + b0 * b0 + b1 * b1);
+                const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+                const float* gw = h < nh ? gq : gk;
+                a0 = gw[0] * a0 * inv; a1 = gw[1] * a1 * inv; b0 = gw[2] * b0 * inv; b1 = gw[3] * b1 * inv;
+            }
+            *reinterpret_cast<__nv_bfloat162*>(dst + 2 * lane) = __floats2bfloat162_rn(a0 * c.x - b0 * sn.x, a1 * c.y - b1 * sn.y);
+            *reinterpret_cast<__nv_bfloat162*>(dst + half + 2 * lane) = __floats2bfloat162_rn(b0 * c.x + a0 * sn.x, b1 * c.y + a1 * sn.y);
         }
-        float a0 = __low2float(lo), a1 = __high2float(lo), b0 = __low2float(hi), b1 = __high2float(hi);
-        if (use_norm) {
-            const float ss = warp_sum(a0 * a0 + a1 * a1 + b0 * b0 + b1 * b1);
-            const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
-            const float* gw = h < nh ? gq : gk;
-            a0 = gw[0] * a0 * inv; a1 = gw[1] * a1 * inv; b0 = gw[2] * b0 * inv; b1 = gw[3] * b1 * inv;
-        }
-        *reinterpret_cast<__nv_bfloat162*>(dst + 2 * lane) = __floats2bfloat162_rn(a0 * c.x - b0 * sn.x, a1 * c.y - b1 * sn.y);
-        *reinterpret_cast<__nv_bfloat162*>(dst + half + 2 * lane) = __floats2bfloat162_rn(b0 * c.x + a0 * sn.x, b1 * c.y + a1 * sn.y);
     }
 }
 
