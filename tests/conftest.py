@@ -40,9 +40,14 @@ TINY = {
               num_key_value_heads=2, head_dim=32, max_position_embeddings=256, rms_norm_eps=1e-5, rope_theta=1e6,
               tie_word_embeddings=False, sliding_window=24,
               layer_types=("full_attention", "sliding_attention", "sliding_attention")),
+    # head_dim 64 with pages of 16 tokens: in bfloat16 the tensor-core attention kernels (tcgen05 for prompt
+    # portions, mma.sync for decoded tokens); four query heads on one KV head, one windowed layer
+    "C": dict(vocab_size=320, hidden_size=128, intermediate_size=176, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=1, head_dim=64, max_position_embeddings=256, rms_norm_eps=1e-6, rope_theta=5e4,
+              tie_word_embeddings=False, sliding_window=40, layer_types=("sliding_attention", "full_attention")),
 }
-TINY_SEED = {"A": 0, "B": 2}
-TINY_PAGE = {"A": 4, "B": 8}
+TINY_SEED = {"A": 0, "B": 2, "C": 4}
+TINY_PAGE = {"A": 4, "B": 8, "C": 16}
 
 
 def tiny_config(name):

@@ -1,6 +1,6 @@
 """bin/trace_run against the plain implementation: the same requests whole, with the last 32
 tokens one by one, in portions of changing size down to two tokens, and mixed (up to four live
-requests, pages used again) -- in 32-bit and in bfloat16, on both tiny configurations."""
+requests, pages used again) -- in 32-bit and in bfloat16, on the three tiny configurations."""
 import numpy as np
 import pytest
 
@@ -9,7 +9,8 @@ from conftest import TINY, TINY_PAGE, random_tokens
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [40, 75, 128, 33, 90, 64, 17, 2], "B": [1, 7, 33, 64, 150, 256, 97, 130]}
+LENGTHS = {"A": [40, 75, 128, 33, 90, 64, 17, 2], "B": [1, 7, 33, 64, 150, 256, 97, 130],
+           "C": [200, 65, 256, 3, 129, 64, 48, 100]}
 # largest |difference| allowed, as a fraction of the largest |logit| of the reference row set
 REL_TOL = {"float32": 2e-5, "bfloat16": 3e-2}
 
@@ -39,7 +40,7 @@ def compare(name, dtype, trace, out_dir, requests, plain_logits):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 def test_replay(name, dtype, mode, model_dirs, plain_logits, tmp_path):
     requests = make_requests(name)
@@ -68,7 +69,7 @@ def test_replay_modes_agree_with_each_other(dtype, model_dirs, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_replay_mixed_with_poisoned_pages(name, dtype, model_dirs, plain_logits, tmp_path):
     """The mixed trace again with the cache NaN-filled at the start and every returned page NaN-filled again:
     a key read from a page's unwritten tail, from a page a window has passed, or from a previous owner's
