@@ -157,12 +157,20 @@ __device__ __forceinline__ float silu_fast(float z) { return __fdividef(z, 1.0f 
 template <int CHUNK>
 __device__ __forceinline__ void swiglu_store(uint32_t (*v)[16], __nv_bfloat16* out, long long ldc, int m, int M, int n_first,
                                              int N, int lane) {
+    // All values first, without a branch in sight, so that the shuffles' and the exponentials' latencies overlap
+    // across the columns; a branch per column made this epilogue slower than the unit's MMAs.
+    float r[CHUNK];
 #pragma unroll
     for (int jj = 0; jj < CHUNK; ++jj) {
         const float mine = __uint_as_float(v[jj / 16][jj % 16]);
         const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
-        if (!(lane & 1) && m + 1 < M && n_first + jj < N)
-            out[(size_t)(n_first + jj) * ldc + (m >> 1)] = __float2bfloat16_rn(silu_fast(mine) * other);
+        r[jj] = silu_fast(mine) * other;
+    }
+    if (!(lane & 1) && m + 1 < M) {
+        __nv_bfloat16* o = out + (size_t)n_first * ldc + (m >> 1);
+#pragma unroll
+        for (int jj = 0; jj < CHUNK; ++jj)
+            if (n_first + jj < N) o[(size_t)jj * ldc] = __float2bfloat16_rn(r[jj]);
     }
 }
 
