@@ -809,7 +809,7 @@ int launch_shape(int shape, const void* W, const void* X, const GemmArgs& g, lon
     return -1;
 }
 
-int pick_shape(int M, int N, int splits) {
+int pick_shape(int M, int N, int K, int splits) {
     if (N <= 16) return SHAPE_N16;
     if (N <= 32) return SHAPE_N32;
     if (N <= 64) return SHAPE_N64;
@@ -819,13 +819,15 @@ int pick_shape(int M, int N, int splits) {
     if (M <= 128 || splits > 1) return SHAPE_N256;
     // Units of 128 x 256 (two accumulator buffers: the epilogue of one unit overlaps the MMAs of the next),
     // 256 x 256 or 256 x 192 tokens: whichever needs the least time over the SMs, counting whole rounds.
-    // Measured at 2,048 tokens the 128 x 256 units are as fast per flop as the 256-feature ones (the ring of
-    // stages, not the traffic, bounds the main loop), so ties go to them.
+    // Measured at 2,048 tokens the 128 x 256 units are as fast per flop as the 256-feature ones at an inner size
+    // of 4096, so ties go to them; at 12288 the 256 x 256 units, which read the token tile half as often, are
+    // 7 to 9 % faster (down_proj 156 -> 146 us), so there ties go the other way.
     auto cost = [&](int mt, int bn) {
         const long long units = (long long)((M + mt * BM - 1) / (mt * BM)) * ((N + bn - 1) / bn);
         return ((units + num_sms() - 1) / num_sms()) * (long long)(mt * bn);
     };
     const long long c1 = cost(1, 256), c2 = cost(2, 256), c3 = cost(2, 192);
+    if (c1 == c2 && c2 <= c3 && K >= 8192) return SHAPE_M256_N256;
     if (c1 <= c2 && c1 <= c3) return SHAPE_N256;
     return c3 < c2 ? SHAPE_M256_N192 : SHAPE_M256_N256;
 }
@@ -846,7 +848,7 @@ VCB_API int vcb_gemm_bf16_tn_shape(const void* W, const void* X, void* out, int 
     splits = (total_kb + kb_per_split - 1) / kb_per_split;
     GemmArgs g{out, out_dtype, M, N, K, ldc, split_stride, kb_per_split, splits, 0, status};
     if (shape < 0 && pairs_enabled() && N > 128 && M >= 512) return launch_pair(W, M, X, g, ldw, ldx, stream);
-    return launch_shape(shape < 0 ? pick_shape(M, N, splits) : shape, W, X, g, ldw, ldx, splits, stream);
+    return launch_shape(shape < 0 ? pick_shape(M, N, K, splits) : shape, W, X, g, ldw, ldx, splits, stream);
 }
 
 // Fused feed-forward front half.  W [2I, K] holds gate_i in row 2i and up_i in row 2i+1; out[t][i] =
@@ -861,7 +863,7 @@ VCB_API int vcb_gemm_bf16_swiglu(const void* W, const void* X, void* out, int I,
     const int total_kb = (K + BK - 1) / BK;
     GemmArgs g{out, VCB_BF16, 2 * I, N, K, ldc, 0, total_kb, 1, 1, status};
     if (shape < 0 && pairs_enabled() && N > 128 && I >= 256) return launch_pair(W, 2LL * I, X, g, ldw, ldx, stream);
-    return launch_shape(shape < 0 ? pick_shape(2 * I, N, 1) : shape, W, X, g, ldw, ldx, 1, stream);
+    return launch_shape(shape < 0 ? pick_shape(2 * I, N, K, 1) : shape, W, X, g, ldw, ldx, 1, stream);
 }
 
 VCB_API int vcb_gemm_bf16_tn(const void* W, const void* X, void* out, int out_dtype, int M, int N, int K,
