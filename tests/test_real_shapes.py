@@ -49,3 +49,52 @@ def test_bf16_engine_follows_the_32_bit_engine_at_8b_layer_sizes():
     err = ((got - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)).max().item()
     assert err < 3e-2, err
     assert (got.argmax(dim=1) == ref.argmax(dim=1)).float().mean().item() >= 0.8
+
+
+@pytest.mark.parametrize("page_size,window,hd,nh,nkv,hidden,inter", [
+    (8, 0, 128, 32, 8, 4096, 12288),          # eight pages a key tile
+    (64, 256, 128, 32, 8, 4096, 12288),       # one page a key tile, a windowed layer before a full one
+    (16, 100, 64, 14, 2, 896, 4864),          # head_dim 64, seven query heads a KV head, sizes that are no power of two
+    (4, 0, 128, 16, 2, 2048, 6144),           # pages too small for TMA boxes: the cp.async loaders
+])
+def test_bf16_engine_follows_the_32_bit_engine_at_other_serving_sizes(page_size, window, hd, nh, nkv, hidden, inter):
+    """Two requests fed in large and small portions, then decoded, in bfloat16 against the true-32-bit engine: other
+    page sizes, group sizes and head sizes than the benchmark model's, with and without a window."""
+    from vllm_cpp_b200 import LLM, EngineConfig, Qwen3Config
+    from vllm_cpp_b200.engine.step import StepEntry
+    from vllm_cpp_b200.runtime import runtime
+    kw = dict(sliding_window=window, layer_types=("sliding_attention", "full_attention")) if window else {}
+    cfg = Qwen3Config(vocab_size=32000, hidden_size=hidden, intermediate_size=inter, num_hidden_layers=2,
+                      num_attention_heads=nh, num_key_value_heads=nkv, head_dim=hd, max_position_embeddings=4096,
+                      rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False, **kw)
+    rng = np.random.default_rng(0)
+    tokens = {0: rng.integers(0, cfg.vocab_size, 900).tolist(), 1: rng.integers(0, cfg.vocab_size, 200).tolist()}
+    plan = [[(0, 300), (1, 17)], [(0, 500), (1, 100)], [(0, 90), (1, 60)]] + [[(0, 1), (1, 1)]] * 6 + [[(0, 4)]]
+    rows = {}
+    for dtype in ("float32", "bfloat16"):
+        llm = LLM(config=cfg, random_seed=1, engine=EngineConfig(dtype=dtype, page_size=page_size, max_tokens=2048,
+                                                                 max_num_seqs=2, max_step_tokens=1024))
+        runner = llm.runner
+        rt = runtime()
+        cm = rt.CacheManager(runner.layout.runtime_groups(rt, page_size, 2048 // page_size), 2)
+        pos = {0: 0, 1: 0}
+        for r in pos:
+            cm.open(r)
+        got = []
+        for step in plan:
+            entries = []
+            for r, n in step:
+                assert cm.reserve(r, pos[r] + n)
+                tables = [cm.block_table(r, g) for g in range(len(runner.layout.groups))]
+                entries.append(StepEntry(cm.slot(r), pos[r], tokens[r][pos[r]:pos[r] + n], tables, [n - 1]))
+                pos[r] += n
+            got.append(runner.step(entries).float().cpu().clone())
+            for r, _ in step:
+                cm.commit(r, pos[r])
+        rows[dtype] = torch.cat(got)
+        del llm, runner
+        torch.cuda.empty_cache()
+    ref, got = rows["float32"], rows["bfloat16"]
+    err = ((got - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)).max().item()
+    assert err < 3e-2, err
+    assert (got.argmax(dim=1) == ref.argmax(dim=1)).float().mean().item() >= 0.8
