@@ -98,11 +98,23 @@ __global__ __launch_bounds__(1024) void add_rmsnorm_vec_kernel(float* __restrict
                                                                const int* __restrict__ rows, int H) {
     __shared__ float scratch[33];
     pdl_trigger();
-    pdl_wait();
+    // What no kernel of the step writes -- the row index and the gains -- is read before waiting for the kernel
+    // that produces the sums, so that only one round trip to memory follows the wait.
     const int i = blockIdx.x;
     const size_t r = rows ? (size_t)rows[i] : (size_t)i;
     const bool write_back = rows == nullptr && S > 0;
     const int H4 = H >> 2;
+    float4 gain[VPT];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int c = threadIdx.x + v * blockDim.x;
+        if (c < H4) {
+            const int h = c * 4;
+            gain[v] = make_float4(load_as_f32(w, w_dtype, h), load_as_f32(w, w_dtype, h + 1), load_as_f32(w, w_dtype, h + 2),
+                                  load_as_f32(w, w_dtype, h + 3));
+        }
+    }
+    pdl_wait();
     float4 x[VPT];
     float ss = 0.f;
 #pragma unroll
@@ -135,11 +147,8 @@ __global__ __launch_bounds__(1024) void add_rmsnorm_vec_kernel(float* __restrict
     for (int v = 0; v < VPT; ++v) {
         const int c = threadIdx.x + v * blockDim.x;
         if (c < H4) {
-            const int h = c * 4;
-            const float w0 = load_as_f32(w, w_dtype, h), w1 = load_as_f32(w, w_dtype, h + 1);
-            const float w2 = load_as_f32(w, w_dtype, h + 2), w3 = load_as_f32(w, w_dtype, h + 3);
-            __nv_bfloat162 lo = __floats2bfloat162_rn(w0 * x[v].x * inv, w1 * x[v].y * inv);
-            __nv_bfloat162 hi = __floats2bfloat162_rn(w2 * x[v].z * inv, w3 * x[v].w * inv);
+            __nv_bfloat162 lo = __floats2bfloat162_rn(gain[v].x * x[v].x * inv, gain[v].y * x[v].y * inv);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(gain[v].z * x[v].z * inv, gain[v].w * x[v].w * inv);
             uint2 pk;
             pk.x = *reinterpret_cast<uint32_t*>(&lo);
             pk.y = *reinterpret_cast<uint32_t*>(&hi);
@@ -262,20 +271,49 @@ __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, s
                                            int page_size, int num_pages, int nh, int nkv, int hd, int n_tokens,
                                            int has_kv, int* status) {
     pdl_trigger();
-    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int heads_total = nh + (has_kv ? 2 * nkv : 0);
     const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (gw >= (long long)n_tokens * heads_total) return;
-    const int t = (int)(gw / heads_total), h = (int)(gw % heads_total);
+    const bool active = gw < (long long)n_tokens * heads_total;
+    const int t = active ? (int)(gw / heads_total) : 0, h = active ? (int)(gw % heads_total) : 0;
     const TIN* src = qkv + (size_t)t * heads_total * hd + (size_t)h * hd;
     const int half = hd >> 1;
+    constexpr int MAXP = VCB_MAX_HEAD_DIM / 64;  // pairs per lane
 
+    // What no kernel of the step writes -- the token's slot and position, the gains, the angles -- is read before
+    // waiting for the kernel that produces qkv, so that only one round trip to memory follows the wait.
     long long slot = -1;
+    int pos = 0;
+    bool bad_page = false, bad_pos = false;
+    float g1[MAXP], g2[MAXP], cs1[MAXP], sn1[MAXP];
+    if (active) {
+        if (h >= nh) {
+            slot = slot_map[t];
+            bad_page = slot >= 0 && slot / page_size >= num_pages;
+        }
+        if (h < nh + nkv) {
+            pos = positions[t];
+            bad_pos = pos < 0 || pos >= max_pos;
+            if (bad_pos) pos = 0;
+            const void* gain = h < nh ? qw : kw;
+            const float* cs = cos_sin + (size_t)pos * hd;
+#pragma unroll
+            for (int j = 0; j < MAXP; ++j) {
+                const int p = lane + 32 * j;
+                if (p < half) {
+                    g1[j] = use_norm ? load_as_f32(gain, w_dtype, p) : 1.f;
+                    g2[j] = use_norm ? load_as_f32(gain, w_dtype, p + half) : 1.f;
+                    cs1[j] = cs[p];
+                    sn1[j] = cs[half + p];
+                }
+            }
+        }
+    }
+    pdl_wait();
+    if (!active) return;
     if (h >= nh) {
-        slot = slot_map[t];
         if (slot < 0) return;  // padded token: nothing to store
-        if (slot / page_size >= num_pages) {
+        if (bad_page) {
             if (lane == 0) atomicOr(status, VCB_STATUS_BAD_PAGE);
             return;
         }
@@ -292,12 +330,7 @@ __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, s
         return;
     }
 
-    int pos = positions[t];
-    if (pos < 0 || pos >= max_pos) {
-        if (lane == 0) atomicOr(status, VCB_STATUS_BAD_POSITION);
-        pos = 0;
-    }
-    constexpr int MAXP = VCB_MAX_HEAD_DIM / 64;  // pairs per lane
+    if (bad_pos && lane == 0) atomicOr(status, VCB_STATUS_BAD_POSITION);
     float x1[MAXP], x2[MAXP];
     float ss = 0.f;
 #pragma unroll
@@ -312,7 +345,6 @@ __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, s
             ss += x1[j] * x1[j] + x2[j] * x2[j];
         }
     }
-    const void* gain = h < nh ? qw : kw;
     float inv = 1.f;
     if (use_norm) {
         ss = warp_sum(ss);
@@ -321,19 +353,17 @@ __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, s
     T* dst;
     if (h < nh) dst = q_out + (size_t)t * nh * hd + (size_t)h * hd;
     else dst = pages + (slot / page_size) * page_stride + ((size_t)(h - nh) * page_size + slot % page_size) * hd;
-    const float* cs = cos_sin + (size_t)pos * hd;
 #pragma unroll
     for (int j = 0; j < MAXP; ++j) {
         const int p = lane + 32 * j;
         if (p < half) {
             float a = x1[j], b = x2[j];
             if (use_norm) {
-                a = load_as_f32(gain, w_dtype, p) * a * inv;
-                b = load_as_f32(gain, w_dtype, p + half) * b * inv;
+                a = g1[j] * a * inv;
+                b = g2[j] * b * inv;
             }
-            const float c = cs[p], s = cs[half + p];
-            dst[p] = from_f32<T>(a * c - b * s);
-            dst[p + half] = from_f32<T>(b * c + a * s);
+            dst[p] = from_f32<T>(a * cs1[j] - b * sn1[j]);
+            dst[p + half] = from_f32<T>(b * cs1[j] + a * sn1[j]);
         }
     }
 }
