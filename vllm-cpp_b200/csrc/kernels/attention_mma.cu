@@ -159,7 +159,11 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_s + 16 * STAGES);
 
     pdl_trigger();
-    pdl_wait();   // the queries and the newest keys come from the kernel before this one
+    // The queries and the newest keys come from the kernel before this one.  With TMA loads the wait is put off:
+    // what describes the work (items, lengths and block tables are in place before the step's first model kernel
+    // starts: the copy of the step's integers is an ordinary stream operation and the kernel that updates the tables
+    // triggers no early launch) and the keys and values of earlier steps can be read before it.
+    if (!TMA) pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wr = (warp % NW) / WK, wk = (warp % NW) % WK;
     const int* item = a.items + (size_t)blockIdx.x * ITEM_INTS;
@@ -174,7 +178,10 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
     const int R = nq * gq;
 
     const int qlen = a.q_len[e], ctx = a.ctx_len[e];
-    if (qlen <= 0 || ctx <= 0) return;
+    if (qlen <= 0 || ctx <= 0) {
+        if (TMA) pdl_wait();
+        return;
+    }
     const int row0 = a.q_start[e] + q0;
     const int pos0 = ctx - qlen + q0;
     const int pos_last = pos0 + nq - 1;
@@ -200,6 +207,58 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+
+    // ---- TMA producer state: one box of [page_size keys x 64 lanes] per page, per half of head_dim, for K and V.
+    // The boxes of a tile (up to 32) are issued by as many lanes at once, each with its page id read one tile
+    // ahead: one thread issuing them in turn, each behind its own block-table read, took about as long as
+    // the tile's share of HBM time. ----
+    const int pages_per_tile = BN / ps;
+    const int rows_kv = a.nkv * ps;          // rows of the flattened [pages * 2 * nkv * ps, HD] view per K or V
+    constexpr int HALVES = HD / 64;
+    const int my_pg = lane / (HALVES * 2), my_h = (lane >> 1) % HALVES, my_v = lane & 1;
+    auto page_of = [&](int it) {
+        const int pb = my_pb_lo + it * pages_per_tile + my_pg;
+        return (it < n_tiles && my_pg < pages_per_tile && pb < my_pb_hi) ? bt[pb] : -1;
+    };
+    int next_page = -1;
+    // asks for tile `it` once its stage is free (the producer warp, all lanes); false: give up
+    auto issue_tile = [&](int it) {
+        const int st = it % STAGES;
+        bool ok = true;
+        if (lane == 0) ok = mbar_wait(empty_bar(st), ((it / STAGES) & 1) ^ 1u, abort_flag, a.status);
+        if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
+        const int pb0 = my_pb_lo + it * pages_per_tile;
+        const int np = min(pages_per_tile, my_pb_hi - pb0);
+        if (lane == 0) mbar_expect_tx(full_bar(st), (uint32_t)(np * ps * ROWB * 2));
+        __syncwarp();
+        if (my_pg < np) {
+            int page = next_page;
+            if (page < 0 || page >= a.num_pages) {
+                atomicOr(a.status, VCB_STATUS_BAD_PAGE);
+                page = 0;   // keep the byte count whole; the status word reports the fault
+            }
+            const int row = (page * 2 * a.nkv + kvh) * ps + (my_v ? rows_kv : 0);
+            const uint32_t dst = smem_u32((my_v ? v_s : k_s) + st * TILE_BYTES) + my_h * (BN * 128) + my_pg * ps * 128;
+            tma_load_2d(dst, &kv_map, full_bar(st), my_h * 64, row);
+        }
+        next_page = page_of(it + 1);
+        return true;
+    };
+    int pre_tiles = 0;
+    if (TMA) {
+        __syncthreads();   // the barriers are initialised
+        if (warp == NW) {
+            // Tiles whose pages hold only tokens of earlier steps are asked for before the wait: up to a ring's worth.
+            const int first_new = ctx - qlen;
+            next_page = page_of(0);
+            while (pre_tiles < n_tiles && pre_tiles < STAGES &&
+                   min(my_pb_hi, my_pb_lo + (pre_tiles + 1) * pages_per_tile) * ps <= first_new) {
+                if (!issue_tile(pre_tiles)) break;
+                ++pre_tiles;
+            }
+        }
+        pdl_wait();
     }
 
     // ---- Q rows -> shared memory (rows beyond R are zero) ----
@@ -246,40 +305,10 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
     __syncthreads();   // Q and the barriers are in shared memory
 
     if (TMA && warp == NW) {
-        // ---- TMA producer: one box of [page_size keys x 64 lanes] per page, per half of head_dim, for K and V.
-        // The boxes of a tile (up to 32) are issued by as many lanes at once, each with its page id read one tile
-        // ahead: one thread issuing them in turn, each behind its own block-table read, took about as long as
-        // the tile's share of HBM time. ----
-        const int pages_per_tile = BN / ps;
-        const int rows_kv = a.nkv * ps;          // rows of the flattened [pages * 2 * nkv * ps, HD] view per K or V
-        constexpr int HALVES = HD / 64;
-        const int my_pg = lane / (HALVES * 2), my_h = (lane >> 1) % HALVES, my_v = lane & 1;
-        auto page_of = [&](int it) {
-            const int pb = my_pb_lo + it * pages_per_tile + my_pg;
-            return (it < n_tiles && my_pg < pages_per_tile && pb < my_pb_hi) ? bt[pb] : -1;
-        };
-        int next_page = page_of(0);
-        int armed = 0;
-        for (int it = 0; it < n_tiles; ++it) {
-            const int st = it % STAGES;
-            bool ok = true;
-            if (lane == 0) ok = mbar_wait(empty_bar(st), ((it / STAGES) & 1) ^ 1u, abort_flag, a.status);
-            if (!__shfl_sync(0xffffffffu, ok, 0)) break;
-            const int pb0 = my_pb_lo + it * pages_per_tile;
-            const int np = min(pages_per_tile, my_pb_hi - pb0);
-            if (lane == 0) mbar_expect_tx(full_bar(st), (uint32_t)(np * ps * ROWB * 2));
-            __syncwarp();
-            if (my_pg < np) {
-                int page = next_page;
-                if (page < 0 || page >= a.num_pages) {
-                    atomicOr(a.status, VCB_STATUS_BAD_PAGE);
-                    page = 0;   // keep the byte count whole; the status word reports the fault
-                }
-                const int row = (page * 2 * a.nkv + kvh) * ps + (my_v ? rows_kv : 0);
-                const uint32_t dst = smem_u32((my_v ? v_s : k_s) + st * TILE_BYTES) + my_h * (BN * 128) + my_pg * ps * 128;
-                tma_load_2d(dst, &kv_map, full_bar(st), my_h * 64, row);
-            }
-            next_page = page_of(it + 1);
+        // ---- TMA producer: the tiles after the ones asked for before the wait ----
+        int armed = pre_tiles;
+        for (int it = pre_tiles; it < n_tiles; ++it) {
+            if (!issue_tile(it)) break;
             armed = it + 1;
         }
         if (lane == 0 && *abort_flag) {   // let copies in flight land before the block goes away

@@ -484,7 +484,9 @@ VCB_API int vcb_qknorm_rope_kvwrite(const void* qkv, int in_dtype, int S, long l
 // ---------------------------------------------------------------------------
 __global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict__ idx, const int* __restrict__ val,
                                    const int* __restrict__ count, int capacity, long long dst_size) {
-    pdl_trigger();
+    // No early trigger here: the kernel after this one then starts only when this one has ended, and every later
+    // kernel of the step after that, so all of them may read the block tables before their own dependency wait
+    // (the attention kernel asks for old key tiles that early).
     pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const int n = min(*count, capacity);
