@@ -111,6 +111,7 @@ class ModelRunner:
     """Owns the model, its device cache, the device-resident block tables and the status word; runs steps."""
 
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+    GRAPH_CONTEXT_BOUNDS = (8192,)      # captured steps are kept per context class: up to 8192 tokens, and beyond
 
     def __init__(self, model, page_size: int, num_pages: int, num_slots: int, dtype: torch.dtype, device,
                  cuda_graphs: bool = True, max_model_len: int | None = None):
@@ -314,7 +315,11 @@ class ModelRunner:
         return np.asarray(flat, dtype=np.int32), facts
 
     def _step_graph(self, entries, updates, bucket, user=None, post=None, post_key=None):
-        key = (bucket, post_key if post is not None else None)
+        # one captured step per padded batch size and context class: the attention part slices the key ranges of
+        # short contexts differently from long ones, and a captured step cannot ask how long they are
+        longest = max(e.start_pos for e in entries) + 1
+        ctx_bound = next((b for b in self.GRAPH_CONTEXT_BOUNDS if longest <= b), None)
+        key = (bucket, post_key if post is not None else None, ctx_bound)
         if key not in self._graphs:
             self._capture(key, post)
         graph, ctx, result, pinned = self._graphs[key]
@@ -338,6 +343,7 @@ class ModelRunner:
         dev = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
         pinned = torch.zeros(lay.size, dtype=torch.int32).pin_memory()
         ctx = StepContext(self, lay, dev, static=True)
+        ctx.static_max_ctx = key[2]
         host = np.zeros(lay.size, dtype=np.int32)
         o = lay.offsets
         for g in range(len(self.tables)):
