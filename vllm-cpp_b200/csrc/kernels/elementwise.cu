@@ -157,6 +157,76 @@ __global__ __launch_bounds__(1024) void add_rmsnorm_vec_kernel(float* __restrict
     }
 }
 
+// The same for many rows (prompt portions; at most one slice of deltas, every row in place): blocks walk the rows
+// and ask for the next row's values before they reduce the current one, so that loads stay in flight across the
+// block-wide sum.  One row a block left the memory system a third busy (24 us for 2,048 rows of 4096).
+template <int VPT>
+__global__ __launch_bounds__(1024) void add_rmsnorm_stream_kernel(float* __restrict__ resid, const float* __restrict__ delta,
+                                                                  int S, const void* __restrict__ w, int w_dtype, float eps,
+                                                                  __nv_bfloat16* __restrict__ out, int n_rows, int H) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    const int H4 = H >> 2;
+    float4 gain[VPT];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int c = threadIdx.x + v * blockDim.x;
+        if (c < H4) {
+            const int h = c * 4;
+            gain[v] = make_float4(load_as_f32(w, w_dtype, h), load_as_f32(w, w_dtype, h + 1), load_as_f32(w, w_dtype, h + 2),
+                                  load_as_f32(w, w_dtype, h + 3));
+        }
+    }
+    pdl_wait();
+    float4 xr[VPT], xd[VPT], nr[VPT], nd[VPT];
+    auto fetch = [&](int row, float4* r4, float4* d4) {
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            const int c = threadIdx.x + v * blockDim.x;
+            d4[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < H4) {
+                r4[v] = reinterpret_cast<const float4*>(resid + (size_t)row * H)[c];
+                if (S > 0) d4[v] = reinterpret_cast<const float4*>(delta + (size_t)row * H)[c];
+            }
+        }
+    };
+    int row = blockIdx.x;
+    if (row < n_rows) fetch(row, xr, xd);
+    for (; row < n_rows; row += gridDim.x) {
+        const int next = row + gridDim.x;
+        if (next < n_rows) fetch(next, nr, nd);
+        float ss = 0.f;
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            const int c = threadIdx.x + v * blockDim.x;
+            if (c < H4) {
+                xr[v].x += xd[v].x; xr[v].y += xd[v].y; xr[v].z += xd[v].z; xr[v].w += xd[v].w;
+                ss += xr[v].x * xr[v].x + xr[v].y * xr[v].y + xr[v].z * xr[v].z + xr[v].w * xr[v].w;
+                if (S > 0) reinterpret_cast<float4*>(resid + (size_t)row * H)[c] = xr[v];
+            }
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            const int c = threadIdx.x + v * blockDim.x;
+            if (c < H4) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(gain[v].x * xr[v].x * inv, gain[v].y * xr[v].y * inv);
+                __nv_bfloat162 hi = __floats2bfloat162_rn(gain[v].z * xr[v].z * inv, gain[v].w * xr[v].w * inv);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(out + (size_t)row * H)[c] = pk;
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            xr[v] = nr[v];
+            xd[v] = nd[v];
+        }
+    }
+}
+
 VCB_API int vcb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, int S, long long delta_stride,
                             const void* w, int w_dtype, float eps, void* out, int out_dtype, const int* rows,
                             int n_out, int H, cudaStream_t stream) {
@@ -177,6 +247,13 @@ VCB_API int vcb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, in
         const int vpt = (H4 + threads - 1) / threads;
         const float* d = (const float*)delta;
         __nv_bfloat16* o = (__nv_bfloat16*)out;
+        if (rows == nullptr && S <= 1 && n_out > 4 * 148 && vpt <= 2) {
+            const int grid = 2 * 148;   // two blocks of 1024 threads fill an SM
+            if (vpt == 1) launch_pdl(add_rmsnorm_stream_kernel<1>, dim3(grid), dim3(threads), 0, stream, resid, d, S, w, w_dtype, eps, o, n_out, H);
+            else launch_pdl(add_rmsnorm_stream_kernel<2>, dim3(grid), dim3(threads), 0, stream, resid, d, S, w, w_dtype, eps, o, n_out, H);
+            VCB_CHECK_LAUNCH("add_rmsnorm");
+            return 0;
+        }
         if (vpt == 1) launch_pdl(add_rmsnorm_vec_kernel<1>, dim3(n_out), dim3(threads), 0, stream, resid, d, S, (size_t)delta_stride, w, w_dtype, eps, o, rows, H);
         else if (vpt == 2) launch_pdl(add_rmsnorm_vec_kernel<2>, dim3(n_out), dim3(threads), 0, stream, resid, d, S, (size_t)delta_stride, w, w_dtype, eps, o, rows, H);
         else launch_pdl(add_rmsnorm_vec_kernel<4>, dim3(n_out), dim3(threads), 0, stream, resid, d, S, (size_t)delta_stride, w, w_dtype, eps, o, rows, H);
