@@ -123,7 +123,9 @@ def write_model(folder, spec):
 
 
 def main():
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <folder of a laik/vllm-cpp checkout>")
+    ref = Path(sys.argv[1])
     src = ref / "src"
     with tempfile.TemporaryDirectory() as tmp:
         tmp = Path(tmp)
