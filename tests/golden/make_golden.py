@@ -19,7 +19,7 @@ implementation:
   * it sizes the Q projection by hidden_size (:1206)        -> heads * head_dim == hidden_size
   * its down projection runs in place (:1243)               -> plain runs with down_in_place=True
 
-Usage: python tests/golden/make_golden.py [/path/to/laik-vllm-cpp]
+Usage: python tests/golden/make_golden.py /path/to/laik-vllm-cpp
 """
 import json
 import subprocess
