@@ -1,0 +1,179 @@
+"""Per-kernel timings at the benchmark model's layer sizes (Qwen3-8B shape), on one GPU.
+
+    python -m vllm_cpp_b200.microbench gemm [T ...]     the four projections (and lm_head) at T tokens
+    python -m vllm_cpp_b200.microbench attention        decode attention over a paged cache; prompt attention
+    python -m vllm_cpp_b200.microbench small            add+norm, norm-rotate-store, SiLU-gate
+
+How it times: every launch is captured ``reps`` times in a CUDA graph (so that launch overhead does not set the
+floor), the graph is replayed ten times between CUDA events, and the median replay divided by ``reps`` is reported.
+Products rotate over copies of their weights that together exceed L2, so that weights come from HBM as in a step.
+Each line also gives the time the same bytes or flops take at the peaks in ``MEASURED_PEAKS.json`` (when present
+beside the repository's bench.py; otherwise the stated fallbacks) and, for products, the library's time.
+"""
+from __future__ import annotations
+
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+from . import ops
+from .parts import attention as A
+from .parts.linear import choose_splits
+
+SHAPES = {"qkv": (6144, 4096), "o": (4096, 4096), "gate_up": (24576, 4096), "down": (4096, 12288), "lm_head": (151936, 4096)}
+NH, NKV, HD, PAGE = 32, 8, 128, 16
+
+
+def peaks():
+    f = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
+    try:
+        d = json.loads(f.read_text())
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"])
+    except (OSError, KeyError, ValueError):
+        return 6650.0, 1590.0
+
+
+def timeit(fn, reps: int = 20, iters: int = 10) -> float:
+    """fn(k) launches once, using buffer set k.  Microseconds per launch."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for k in range(3):
+            fn(k)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for k in range(reps):
+            fn(k)
+    g.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        e1.synchronize()
+        ts.append(e0.elapsed_time(e1) / reps)
+    ts.sort()
+    return ts[len(ts) // 2] * 1e3
+
+
+def bench_gemm(tokens, dev, status):
+    hbm, tc = peaks()
+    for T in tokens:
+        for name, (M, K) in SHAPES.items():
+            if name == "lm_head" and T > 256:
+                continue
+            ncopy = max(1, min(8, (300 << 20) // (M * K * 2) + 1))
+            ws = [(0.02 * torch.randn(M, K, device=dev)).to(torch.bfloat16) for _ in range(ncopy)]
+            x = torch.randn(T, K, device=dev).to(torch.bfloat16)
+            s = choose_splits(M, T, K)
+            S = ops.gemm_effective_splits(K, s)
+            out = torch.empty((S, T, M) if S > 1 else (T, M), dtype=torch.float32 if S > 1 else torch.bfloat16, device=dev)
+            ours = timeit(lambda k: ops.gemm_bf16_tn(ws[k % ncopy], x, out, s, status))
+            extra = ""
+            if name == "gate_up" and T > 128:
+                act = torch.empty(T, M // 2, dtype=torch.bfloat16, device=dev)
+                extra = f"  with SiLU-gate {timeit(lambda k: ops.gemm_bf16_swiglu(ws[k % ncopy], x, act, status)):.1f}"
+            lib = timeit(lambda k: torch.mm(x, ws[k % ncopy].t()))
+            print(f"product {name:8s} T={T:5d} k-slices {S}: {ours:7.1f} us{extra}   library {lib:7.1f}   "
+                  f"at HBM peak {M * K * 2 / hbm / 1e3:6.1f}   at bf16 peak {2.0 * M * K * T / tc / 1e6:6.1f}", flush=True)
+            del ws, x
+
+
+class _Ctx:
+    pass
+
+
+def bench_attention(dev, status):
+    hbm, tc = peaks()
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    for B, ctx_len in ((1, 4096), (8, 4096), (64, 4096), (64, 512), (256, 128)):
+        npages = B * (ctx_len // PAGE + 1)
+        pages = torch.randn(npages, 2, NKV, PAGE, HD, device=dev).to(torch.bfloat16)
+        bt = torch.arange(npages, dtype=torch.int32, device=dev).view(B, -1)
+        q = torch.randn(B, NH * HD, device=dev).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        c = _Ctx()
+        c.device, c.host_q_len, c.host_ctx_len, c.host_q_start = dev, [1] * B, [ctx_len] * B, list(range(B))
+        plan = A.AttentionPlan(c, NH, NKV, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+        S = plan.nslices
+        po = torch.empty(B * NH * S, HD, device=dev) if S > 1 else None
+        pm = torch.empty(B * NH * S, 2, device=dev) if S > 1 else None
+        qs, ql, cl = i32(c.host_q_start), i32(c.host_q_len), i32(c.host_ctx_len)
+        us = timeit(lambda k: ops.attn_mma(q, out, pages, bt, qs, ql, cl, plan.dec_items, B * S, A.MMA_DECODE_ROWS, po, pm,
+                                           NH, NKV, HD, 0, status, slice_counters=plan.slice_counters if S > 1 else None,
+                                           dec_rows=plan.dec_rows))
+        kv_bytes = B * ctx_len * 2 * NKV * HD * 2
+        print(f"decode attention  batch {B:3d} context {ctx_len:5d} key slices {S:2d}: {us:7.1f} us   at HBM peak {kv_bytes / hbm / 1e3:6.1f}", flush=True)
+        del pages
+    for T in (2048,):
+        npages = T // PAGE
+        pages = torch.randn(npages, 2, NKV, PAGE, HD, device=dev).to(torch.bfloat16)
+        bt = torch.arange(npages, dtype=torch.int32, device=dev).view(1, -1)
+        q = torch.randn(T, NH * HD, device=dev).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        c = _Ctx()
+        c.device, c.host_q_len, c.host_ctx_len, c.host_q_start = dev, [T], [T], [0]
+        plan = A.AttentionPlan(c, NH, NKV, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+        qs, ql, cl = i32([0]), i32([T]), i32([T])
+        flops = 4.0 * NH * HD * T * (T + 1) / 2
+        mma = timeit(lambda k: ops.attn_mma(q, out, pages, bt, qs, ql, cl, plan.span_items, plan.n_span_items, A.MMA_SPAN_ROWS,
+                                            None, None, NH, NKV, HD, 0, status))
+        tcg = timeit(lambda k: ops.attn_tc(q, out, pages, bt, qs, ql, cl, plan.span_items, plan.n_span_items, NH, NKV, HD, 0, status))
+        print(f"prompt attention  {T} tokens: mma.sync {mma:7.1f} us ({flops / mma / 1e6:5.0f} TFLOP/s)   tcgen05 {tcg:7.1f} us "
+              f"({flops / tcg / 1e6:5.0f} TFLOP/s)   at bf16 peak {flops / tc / 1e6:6.1f}", flush=True)
+
+
+def bench_small(dev, status):
+    hbm, _ = peaks()
+    H, I = 4096, 12288
+    for T in (8, 64, 2048):
+        resid = torch.randn(T, H, device=dev)
+        w = torch.ones(H, device=dev).to(torch.bfloat16)
+        out = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+        for S in ((4,) if T <= 128 else (1,)):
+            d = torch.randn(S, T, H, device=dev)
+            us = timeit(lambda k: ops.add_rmsnorm(resid, d, w, 1e-6, out))
+            print(f"add+norm          T={T:5d} slices {S}: {us:7.1f} us   at HBM peak {(T * H * (8 + 4 * S + 2)) / hbm / 1e3:6.1f}", flush=True)
+        S = 3 if T <= 128 else 1
+        gu = torch.randn(S, T, 2 * I, device=dev) if S > 1 else torch.randn(T, 2 * I, device=dev).to(torch.bfloat16)
+        act = torch.empty(T, I, device=dev, dtype=torch.bfloat16)
+        print(f"SiLU-gate         T={T:5d} slices {S}: {timeit(lambda k: ops.swiglu(gu, act)):7.1f} us", flush=True)
+        width = (NH + 2 * NKV) * HD
+        qkv = torch.randn(S, T, width, device=dev) if S > 1 else torch.randn(T, width, device=dev).to(torch.bfloat16)
+        gain = torch.ones(HD, device=dev, dtype=torch.bfloat16)
+        table = torch.randn(8192, HD, device=dev)
+        pos = torch.arange(T, device=dev, dtype=torch.int32)
+        pages = torch.zeros(T // PAGE + 2, 2, NKV, PAGE, HD, device=dev, dtype=torch.bfloat16)
+        qo = torch.empty(T, NH * HD, device=dev, dtype=torch.bfloat16)
+        us = timeit(lambda k: ops.qknorm_rope_kvwrite(qkv, gain, gain, 1e-6, table, pos, pos, qo, pages, NH, NKV, HD, status))
+        print(f"norm-rotate-store T={T:5d} slices {S}: {us:7.1f} us", flush=True)
+
+
+def main(argv):
+    if not torch.cuda.is_available():
+        print("microbench: needs a CUDA device", file=sys.stderr)
+        return 2
+    dev = torch.device("cuda:0")
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    what = argv[0] if argv else "gemm"
+    if what == "gemm":
+        bench_gemm([int(a) for a in argv[1:]] or [8, 64, 256, 2048], dev, status)
+    elif what == "attention":
+        bench_attention(dev, status)
+    elif what == "small":
+        bench_small(dev, status)
+    else:
+        print(__doc__)
+        return 2
+    ops.check_status(status, "microbench")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main(sys.argv[1:]))
