@@ -279,9 +279,10 @@ class ModelRunner:
         ctx = StepContext(self, lay, dev, static=False)
         ctx.__dict__.update(facts)
         self.last_ctx, self.last_h2d_bytes = ctx, host.nbytes
-        self._apply_table_updates(ctx)
-        logits = self.model.forward(ctx, self.cache.views)
-        return post(ctx, logits) if post is not None else logits
+        with ops.hold_stream():   # kernel by kernel, the host's time per launch is what a short portion waits for
+            self._apply_table_updates(ctx)
+            logits = self.model.forward(ctx, self.cache.views)
+            return post(ctx, logits) if post is not None else logits
 
     USER_INTS_PER_ENTRY = 12  # room in a captured step's buffer for the caller's numbers
 

@@ -12,6 +12,7 @@ product in for comparison runs.
 """
 from __future__ import annotations
 
+import functools
 import os
 
 import torch
@@ -30,6 +31,7 @@ def token_tile(T: int) -> int:
     return 256
 
 
+@functools.lru_cache(maxsize=4096)
 def choose_splits(M: int, T: int, K: int, max_splits: int = 8) -> int:
     """Number of k-slices of a product whose units (feature tile x token tile) do not fill the SMs by themselves.
     The kernel's persistent blocks, one per SM, walk (feature tile x token tile x k-slice) units round robin, so
