@@ -58,7 +58,9 @@ def tail_one_by_one(requests, tail=32):
 PORTIONS = [7, 2, 16, 3, 2, 5, 33, 2, 9, 4, 64, 2, 11]
 
 
-def portions(requests, sizes=PORTIONS):
+def portions(requests, sizes=PORTIONS, last_only=False):
+    """Each request alone, cut into portions of the given sizes in turn; logits wanted everywhere, or
+    (last_only) at each portion's last token, which is what a serving step asks for."""
     t = Trace()
     k = 0
     for rid, toks in requests.items():
@@ -66,9 +68,13 @@ def portions(requests, sizes=PORTIONS):
         while p < len(toks):
             n = min(sizes[k % len(sizes)], len(toks) - p)
             k += 1
-            t.add([(rid, toks[p:p + n], p, range(n))], end=[rid] if p + n == len(toks) else [])
+            t.add([(rid, toks[p:p + n], p, [n - 1] if last_only else range(n))], end=[rid] if p + n == len(toks) else [])
             p += n
     return t
+
+
+def portions_last(requests):
+    return portions(requests, sizes=[7, 2, 16, 3, 40, 5, 33, 2, 100, 17, 64, 130], last_only=True)
 
 
 def mixed(requests, seed=0, max_live=4, decode_tail=12):

@@ -1,5 +1,5 @@
 """bin/trace_run against the plain implementation: the same requests whole, with the last 32
-tokens one by one, in portions of changing size down to two tokens, and mixed (up to four live
+tokens one by one, in portions of changing size down to two tokens (all logits wanted, or the last one's), and mixed (up to four live
 requests, pages used again) -- in 32-bit and in bfloat16, on the three tiny configurations."""
 import numpy as np
 import pytest
@@ -41,11 +41,15 @@ def compare(name, dtype, trace, out_dir, requests, plain_logits):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C"])
-@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "portions_last", "mixed"])
 def test_replay(name, dtype, mode, model_dirs, plain_logits, tmp_path):
+    """``portions_last`` asks for the last token's logits only, as serving does: such a portion runs as a
+    captured step padded to the next size, here also over a NaN-filled cache."""
     requests = make_requests(name)
-    trace = {"whole": R.whole, "tail": R.tail_one_by_one, "portions": R.portions, "mixed": R.mixed}[mode](requests)
-    out = R.run_trace(model_dirs[name], dtype, trace, tmp_path / "out", TINY_PAGE[name])
+    trace = {"whole": R.whole, "tail": R.tail_one_by_one, "portions": R.portions, "portions_last": R.portions_last,
+             "mixed": R.mixed}[mode](requests)
+    out = R.run_trace(model_dirs[name], dtype, trace, tmp_path / "out", TINY_PAGE[name],
+                      extra_args=["--poison"] if mode == "portions_last" else [])
     worst = compare(name, dtype, trace, out, requests, plain_logits)
     print(f"{name} {dtype} {mode}: worst relative error {worst:.3e}, pool {trace.max_tokens} tokens, {len(trace.steps)} steps")
 

@@ -72,7 +72,11 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int* item = a.items + (size_t)blockIdx.x * ITEM_INTS;
-    const int e = item[0], q0 = item[1], nq = item[2], slice = item[3], nslices = item[4], dec_index = item[5];
+    const int e = item[0], q0 = item[1], slice = item[3], nslices = item[4], dec_index = item[5];
+    const int qlen = a.q_len[e], ctx = a.ctx_len[e];
+    // an item of a captured step is laid out for the largest portion the step serves: fewer tokens may be there
+    const int nq = min(item[2], qlen - q0);
+    if (qlen <= 0 || ctx <= 0 || nq <= 0) return;
 
     const int g = a.nh / a.nkv;
     const int gq_max = g < RMAX ? g : RMAX;
@@ -82,8 +86,6 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
     const int gq = min(gq_max, g - hc * gq_max);
     const int R = nq * gq;  // rows in use: r = iq * gq + ih
 
-    const int qlen = a.q_len[e], ctx = a.ctx_len[e];
-    if (qlen <= 0 || ctx <= 0) return;
     const int row0 = a.q_start[e] + q0;       // flat token index of the first query
     const int pos0 = ctx - qlen + q0;         // its position
     const int pos_last = pos0 + nq - 1;

@@ -167,7 +167,14 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wr = (warp % NW) / WK, wk = (warp % NW) % WK;
     const int* item = a.items + (size_t)blockIdx.x * ITEM_INTS;
-    const int e = item[0], q0 = item[1], nq = item[2], slice = item[3], nslices = item[4], dec_index = item[5];
+    const int e = item[0], q0 = item[1], slice = item[3], nslices = item[4], dec_index = item[5];
+    const int qlen = a.q_len[e], ctx = a.ctx_len[e];
+    // an item of a captured step is laid out for the largest portion the step serves: fewer tokens may be there
+    const int nq = min(item[2], qlen - q0);
+    if (qlen <= 0 || ctx <= 0 || nq <= 0) {
+        if (TMA) pdl_wait();
+        return;
+    }
 
     const int g = a.nh / a.nkv;
     const int gq_max = g < RMAX ? g : RMAX;
@@ -177,11 +184,6 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
     const int gq = min(gq_max, g - hc * gq_max);
     const int R = nq * gq;
 
-    const int qlen = a.q_len[e], ctx = a.ctx_len[e];
-    if (qlen <= 0 || ctx <= 0) {
-        if (TMA) pdl_wait();
-        return;
-    }
     const int row0 = a.q_start[e] + q0;
     const int pos0 = ctx - qlen + q0;
     const int pos_last = pos0 + nq - 1;

@@ -211,7 +211,11 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
     pdl_wait();   // the queries and the newest keys come from the kernel before this one
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int* item = a.items + (size_t)blockIdx.x * ITEM_INTS;
-    const int e = item[0], q0 = item[1], nq = item[2];
+    const int e = item[0], q0 = item[1];
+    const int qlen = a.q_len[e], ctx = a.ctx_len[e];
+    // an item of a captured step is laid out for the largest portion the step serves: fewer tokens may be there
+    const int nq = min(item[2], qlen - q0);
+    if (qlen <= 0 || ctx <= 0 || nq <= 0) return;   // uniform over the block, before anything is allocated
 
     const int g = a.nh / a.nkv;
     const int gq_max = g < ROWS ? g : ROWS;
@@ -221,8 +225,6 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
     const int gq = min(gq_max, g - hc * gq_max);
     const int R = nq * gq;
 
-    const int qlen = a.q_len[e], ctx = a.ctx_len[e];
-    if (qlen <= 0 || ctx <= 0) return;   // uniform over the block, before anything is allocated
     if (base & 1023u) {                  // the layout below needs the alignment asked for above
         if (tid == 0) atomicOr(a.status, VCB_STATUS_BAD_LAYOUT);
         return;

@@ -112,6 +112,7 @@ class ModelRunner:
 
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
     GRAPH_CONTEXT_BOUNDS = (8192,)      # captured steps are kept per context class: up to 8192 tokens, and beyond
+    PORTION_BUCKETS = (16, 32, 64, 128, 256, 512)   # token counts of captured steps that run one prompt portion
 
     def __init__(self, model, page_size: int, num_pages: int, num_slots: int, dtype: torch.dtype, device,
                  cuda_graphs: bool = True, max_model_len: int | None = None):
@@ -243,6 +244,22 @@ class ModelRunner:
             return None
         return next((b for b in self.GRAPH_BUCKETS if b >= len(entries)), None)
 
+    def portion_size(self, entries) -> int | None:
+        """The padded token count of the captured step that would run these entries: one entry, a prompt portion of
+        up to 512 tokens, logits wanted at most at its last token.  Kernel by kernel the host needs some twenty
+        microseconds a launch, which for a short portion is twice the time the GPU needs."""
+        if not self.cuda_graphs or len(entries) != 1:
+            return None
+        e = entries[0]
+        n = len(e.tokens)
+        if n < 2 or n > self.PORTION_BUCKETS[-1] or e.want not in ([], [n - 1]):
+            return None
+        return next(b for b in self.PORTION_BUCKETS if b >= n)
+
+    def _portion_updates(self, portion: int) -> int:
+        """Block-table entries that a captured portion's buffer has room for: the pages its tokens can touch."""
+        return portion // self.page_size + 2
+
     # ------------------------------------------------------------------ running
     def step(self, entries: list[StepEntry], check: bool = True, user=None, post=None, post_key=None):
         """Runs the entries' tokens as one batch.  Returns logits [wanted rows, vocab] (32-bit, on the
@@ -260,8 +277,12 @@ class ModelRunner:
         updates = self._table_updates(entries)
         n_rows = sum(len(e.want) for e in entries)
         bucket = self.capture_size(entries)
+        portion = None if bucket else self.portion_size(entries)
         if bucket and all(len(u[0]) <= bucket for u in updates) and (post is None or post_key is not None):
             logits = self._step_graph(entries, updates, bucket, user, post, post_key)
+        elif (portion and all(len(u[0]) <= self._portion_updates(portion) for u in updates)
+              and (post is None or post_key is not None)):
+            logits = self._step_portion_graph(entries, updates, portion, n_rows, user, post, post_key)
         else:
             logits = self._step_eager(entries, updates, n_rows, user, post)
         if check:
@@ -335,6 +356,62 @@ class ModelRunner:
         self.graph_replays += 1
         ops.launch_count += self.launches_per_graph[key]
         return result[:len(entries)]
+
+    def _step_portion_graph(self, entries, updates, portion, n_rows, user=None, post=None, post_key=None):
+        """One prompt portion through a captured step of ``portion`` token rows: the tokens beyond the entry's own
+        are padding (token 0 at position 0, stored nowhere, attended by nothing, their rows never read)."""
+        key = ("portion", portion, n_rows, post_key if post is not None else None)
+        if key not in self._graphs:
+            self._capture_portion(key, post)
+        graph, ctx, result, pinned = self._graphs[key]
+        lay = ctx.meta_layout
+        if user is not None and len(user) > lay.X:
+            raise ValueError(f"a captured step carries at most {lay.X} user integers, {len(user)} given")
+        host, facts = self._fill(lay, entries, updates)
+        if user is not None:
+            host[lay.offsets["user"][0]:lay.offsets["user"][0] + len(user)] = user
+        ctx.__dict__.update(facts)
+        pinned.copy_(torch.from_numpy(host))
+        ctx.buffer.copy_(pinned, non_blocking=True)
+        self.last_ctx, self.last_h2d_bytes = ctx, host.nbytes
+        graph.replay()
+        self.graph_replays += 1
+        ops.launch_count += self.launches_per_graph[key]
+        return result
+
+    def _capture_portion(self, key, post=None):
+        """Captures the forward pass of one entry of ``portion`` tokens (and what ``post`` adds), on an entry of
+        length 0.  The attention part lays its work items out for all ``portion`` tokens; at replay the kernels cut
+        them down to the tokens that are there."""
+        _, portion, n_rows, _ = key
+        lay = MetaLayout(portion, 1, n_rows, self._portion_updates(portion), len(self.tables), 8 * max(n_rows, 1) + portion)
+        dev = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
+        pinned = torch.zeros(lay.size, dtype=torch.int32).pin_memory()
+        ctx = StepContext(self, lay, dev, static=True)
+        host = np.zeros(lay.size, dtype=np.int32)
+        o = lay.offsets
+        for g in range(len(self.tables)):
+            host[o[f"slot_map{g}"][0]:o[f"slot_map{g}"][1]] = -1
+        dev.copy_(torch.from_numpy(host))
+        ctx.host_q_len, ctx.host_q_start, ctx.host_ctx_len, ctx.host_slots = [portion], [0], [portion], [0]
+
+        def run():
+            self._apply_table_updates(ctx)
+            logits = self.model.forward(ctx, self.cache.views)
+            return post(ctx, logits) if post is not None else logits
+
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            run()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        before = ops.launch_count
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            result = run()
+        self.launches_per_graph[key] = ops.launch_count - before
+        self._graphs[key] = (graph, ctx, result, pinned)
 
     def _capture(self, key, post=None):
         """Captures the forward pass of ``bucket`` single-token entries (and what ``post`` adds).  The capture
