@@ -210,17 +210,21 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
     pdl_trigger();
     pdl_wait();   // the queries and the newest keys come from the kernel before this one
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int* item = a.items + (size_t)blockIdx.x * ITEM_INTS;
+    // Blocks are numbered item by item, the KV heads of an item side by side: the items come longest first, and
+    // so do the blocks then (with the items of one KV head after those of another, the long items of the last
+    // heads started when the SMs were already half through).
+    const int g = a.nh / a.nkv;
+    const int gq_max = g < ROWS ? g : ROWS;
+    const int hchunks = (g + gq_max - 1) / gq_max;
+    const int per_item = a.nkv * hchunks;
+    const int* item = a.items + (size_t)(blockIdx.x / per_item) * ITEM_INTS;
     const int e = item[0], q0 = item[1];
     const int qlen = a.q_len[e], ctx = a.ctx_len[e];
     // an item of a captured step is laid out for the largest portion the step serves: fewer tokens may be there
     const int nq = min(item[2], qlen - q0);
     if (qlen <= 0 || ctx <= 0 || nq <= 0) return;   // uniform over the block, before anything is allocated
 
-    const int g = a.nh / a.nkv;
-    const int gq_max = g < ROWS ? g : ROWS;
-    const int hchunks = (g + gq_max - 1) / gq_max;
-    const int kvh = blockIdx.y / hchunks, hc = blockIdx.y % hchunks;
+    const int kvh = (blockIdx.x % per_item) / hchunks, hc = (blockIdx.x % per_item) % hchunks;
     const int head0 = kvh * g + hc * gq_max;
     const int gq = min(gq_max, g - hc * gq_max);
     const int R = nq * gq;
@@ -550,7 +554,7 @@ int launch(const CUtensorMap& map, const TcArgs& a, int n_items, cudaStream_t st
     const int g = a.nh / a.nkv;
     const int gq_max = g < ROWS ? g : ROWS;
     const int hchunks = (g + gq_max - 1) / gq_max;
-    launch_pdl(kern, dim3(n_items, a.nkv * hchunks), dim3(NTHREADS), (size_t)L::TOTAL, stream, map, a);
+    launch_pdl(kern, dim3((unsigned)n_items * a.nkv * hchunks), dim3(NTHREADS), (size_t)L::TOTAL, stream, map, a);
     VCB_CHECK_LAUNCH("attn_tc");
     return 0;
 }
@@ -572,6 +576,7 @@ VCB_API int vcb_attn_tc(const void* q, void* out, const void* pages, long long p
     VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_tc: %d query heads are not a multiple of %d KV heads", nh, nkv);
     VCB_CHECK_ARG(vcb_attn_tc_supported(VCB_BF16, hd, page_size), "attn_tc: head_dim %d with pages of %d tokens is not supported", hd, page_size);
     VCB_CHECK_ARG(window >= 0, "attn_tc: bad window %d", window);
+    VCB_CHECK_ARG((long long)n_items * nh < (1ll << 31), "attn_tc: %d items of %d heads are more blocks than a grid holds", n_items, nh);
     VCB_CHECK_ARG(((uintptr_t)pages % 16 == 0) && page_stride == (long long)2 * nkv * page_size * hd,
                   "attn_tc: the pages of a layer must be contiguous and 16-byte aligned for TMA loads");
     VCB_CHECK_ARG(((uintptr_t)q % 16 == 0) && ((uintptr_t)out % 16 == 0), "attn_tc: q and out must be 16-byte aligned");
