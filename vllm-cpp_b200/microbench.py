@@ -111,7 +111,7 @@ def bench_attention(dev, status):
         kv_bytes = B * ctx_len * 2 * NKV * HD * 2
         print(f"decode attention  batch {B:3d} context {ctx_len:5d} key slices {S:2d}: {us:7.1f} us   at HBM peak {kv_bytes / hbm / 1e3:6.1f}", flush=True)
         del pages
-    for T in (2048,):
+    for T in (2048, 8192):
         npages = T // PAGE
         pages = torch.randn(npages, 2, NKV, PAGE, HD, device=dev).to(torch.bfloat16)
         bt = torch.arange(npages, dtype=torch.int32, device=dev).view(1, -1)
