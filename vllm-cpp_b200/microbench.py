@@ -7,12 +7,14 @@
 How it times: every launch is captured ``reps`` times in a CUDA graph (so that launch overhead does not set the
 floor), the graph is replayed ten times between CUDA events, and the median replay divided by ``reps`` is reported.
 Products rotate over copies of their weights that together exceed L2, so that weights come from HBM as in a step.
+``VCB_MICROBENCH_PAGE`` sets the page size of the attention runs (default 16).
 Each line also gives the time the same bytes or flops take at the peaks in ``MEASURED_PEAKS.json`` (when present
 beside the repository's bench.py; otherwise the stated fallbacks) and, for products, the library's time.
 """
 from __future__ import annotations
 
 import json
+import os
 import sys
 from pathlib import Path
 
@@ -23,7 +25,7 @@ from .parts import attention as A
 from .parts.linear import choose_splits
 
 SHAPES = {"qkv": (6144, 4096), "o": (4096, 4096), "gate_up": (24576, 4096), "down": (4096, 12288), "lm_head": (151936, 4096)}
-NH, NKV, HD, PAGE = 32, 8, 128, 16
+NH, NKV, HD, PAGE = 32, 8, 128, int(os.environ.get("VCB_MICROBENCH_PAGE", "16"))
 
 
 def peaks():
