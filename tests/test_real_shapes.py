@@ -58,6 +58,8 @@ def test_bf16_engine_follows_the_32_bit_engine_at_8b_layer_sizes():
     (64, 256, 128, 32, 8, 4096, 12288),       # one page a key tile, a windowed layer before a full one
     (16, 100, 64, 14, 2, 896, 4864),          # head_dim 64, seven query heads a KV head, sizes that are no power of two
     (4, 0, 128, 16, 2, 2048, 6144),           # pages too small for TMA boxes: the cp.async loaders
+    (16, 0, 128, 40, 8, 5120, 17408),         # the 14B shape: five query heads a KV head, 136 feature tiles of 128
+    (16, 0, 128, 32, 8, 2560, 9728),          # the 4B shape: heads x head_dim wider than the hidden size
 ])
 def test_bf16_engine_follows_the_32_bit_engine_at_other_serving_sizes(page_size, window, hd, nh, nkv, hidden, inter):
     """Two requests fed in large and small portions, then decoded, in bfloat16 against the true-32-bit engine: other
