@@ -32,8 +32,9 @@ def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.isfile(p):
         d = json.load(open(p))
-        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], source="measured")
-    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"],
+                    bf16_tflops_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
 
 
 class ClockSampler:
@@ -226,7 +227,10 @@ def main():
     if args.mode == "prefill":
         print(json.dumps({"mode": "prefill", "ms": pf_ms, "tokens_per_s": T * 1000.0 / pf_ms}))
         return 0
-    prefill = {"value": T * 1000.0 / pf_ms, "tokens": T, "ms": pf_ms, "frac": pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
+    # frac: against the library's burst rate (one product timed alone); the eight back-to-back steps timed here run
+    # under the power cap like the library's seconds-long loop, whose rate frac_of_sustained is taken against
+    prefill = {"value": T * 1000.0 / pf_ms, "tokens": T, "ms": pf_ms, "frac": pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12),
+               "frac_of_sustained": pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12)}
 
     # end to end through the Python entry point: host token lists in, host tokens out, every step
     B = args.batch
