@@ -77,10 +77,11 @@ def portions_last(requests):
     return portions(requests, sizes=[7, 2, 16, 3, 40, 5, 33, 2, 100, 17, 64, 130], last_only=True)
 
 
-def mixed(requests, seed=0, max_live=4, decode_tail=12):
+def mixed(requests, seed=0, max_live=4, decode_tail=12, last_only=False):
     """Up to max_live requests at a time: the prompt part of each goes in portions of changing size,
     its last tokens one by one, beside the others'; a request sometimes sits a step out; a new
-    one starts when one ends, in pages the ended one gave back."""
+    one starts when one ends, in pages the ended one gave back.  ``last_only``: logits are wanted at each
+    entry's last token only and single tokens come first in a step, as a serving step has them."""
     rng = np.random.default_rng(seed)
     t = Trace()
     waiting = list(requests.items())
@@ -103,13 +104,19 @@ def mixed(requests, seed=0, max_live=4, decode_tail=12):
                 n = min(PORTIONS[k % len(PORTIONS)], max(len(toks) - decode_tail - pos, 1))
                 k += 1
             n = min(n, len(toks) - pos)
-            entries.append((rid, toks[pos:pos + n], pos, range(n)))
+            entries.append((rid, toks[pos:pos + n], pos, [n - 1] if last_only else range(n)))
             item[2] = pos + n
             if item[2] == len(toks):
                 ended.append(rid)
         live = [it for it in live if it[0] not in ended]
+        if last_only:
+            entries.sort(key=lambda en: len(en[1]) != 1)
         t.add(entries, end=ended)
     return t
+
+
+def mixed_last(requests):
+    return mixed(requests, seed=2, last_only=True)
 
 
 def run_trace(model_dir, dtype, trace, out_dir, page_size, extra_env=None, timeout=900, extra_args=()):

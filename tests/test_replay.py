@@ -41,15 +41,16 @@ def compare(name, dtype, trace, out_dir, requests, plain_logits):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C"])
-@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "portions_last", "mixed"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "portions_last", "mixed", "mixed_last"])
 def test_replay(name, dtype, mode, model_dirs, plain_logits, tmp_path):
-    """``portions_last`` asks for the last token's logits only, as serving does: such a portion runs as a
-    captured step padded to the next size, here also over a NaN-filled cache."""
+    """``portions_last`` and ``mixed_last`` ask for the last token's logits only, as serving does: such steps run
+    as captured steps padded to the next size (a lone portion; single tokens beside portions), here also over a
+    NaN-filled cache."""
     requests = make_requests(name)
     trace = {"whole": R.whole, "tail": R.tail_one_by_one, "portions": R.portions, "portions_last": R.portions_last,
-             "mixed": R.mixed}[mode](requests)
+             "mixed": R.mixed, "mixed_last": R.mixed_last}[mode](requests)
     out = R.run_trace(model_dirs[name], dtype, trace, tmp_path / "out", TINY_PAGE[name],
-                      extra_args=["--poison"] if mode == "portions_last" else [])
+                      extra_args=["--poison"] if mode.endswith("_last") else [])
     worst = compare(name, dtype, trace, out, requests, plain_logits)
     print(f"{name} {dtype} {mode}: worst relative error {worst:.3e}, pool {trace.max_tokens} tokens, {len(trace.steps)} steps")
 

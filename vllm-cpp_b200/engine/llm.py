@@ -129,16 +129,19 @@ class LLM:
         cache = self.scheduler.cache()
         n_groups = cache.num_groups()
         entries, sampled_entries = [], []
-        for e in sched.entries:
+        # single tokens first, then prompt portions (each kind in the scheduler's order): the order in which a
+        # captured step of both takes them; the tokens go back to the scheduler in its own order
+        ordered = sorted(sched.entries, key=lambda e: len(e.tokens) != 1)
+        for e in ordered:
             tables = [cache.block_table(e.request, g) for g in range(n_groups)]
             n = len(e.tokens)
             entries.append(StepEntry(e.slot, e.start_pos, list(e.tokens), tables, [n - 1] if e.sample else []))
             if e.sample:
                 sampled_entries.append(e)
-        penalised = {e.slot for e in sched.entries if self._options[e.request].repeat_penalty not in (0.0, 1.0)}
+        penalised = {e.slot for e in ordered if self._options[e.request].repeat_penalty not in (0.0, 1.0)}
         if penalised:
             self.sampler._need_counts()
-            self.sampler.forget([e.slot for e in sched.entries if e.start_pos == 0 and e.slot in penalised])
+            self.sampler.forget([e.slot for e in ordered if e.start_pos == 0 and e.slot in penalised])
         # Beside the model's own numbers the step carries 8 per sampled row and then, where occurrences are
         # counted, one per token (its request's slot + 1, 0 for none).  A captured step pads rows and tokens to
         # its own size, so the per-token part starts after the padded rows.
@@ -146,7 +149,7 @@ class LLM:
                                                        [e.gen_step for e in sampled_entries],
                                                        [e.slot for e in sampled_entries])
         n_rows = len(sampled_entries)
-        rows_pad = self.runner.capture_size(entries) or n_rows
+        rows_pad = self.runner.rows_capacity(entries)
         user = flat + [0] * (8 * (rows_pad - n_rows))
         if penalised:
             user += Sampler.token_slots(entries, penalised)
@@ -169,10 +172,12 @@ class LLM:
                 ops.check_status(self.runner.status)
             tokens = host[:-1]
         self.h2d_bytes += self.runner.last_h2d_bytes
-        finished = set(self.scheduler.update(tokens))
-        for e, t in zip(sampled_entries, tokens):
+        by_request = {e.request: t for e, t in zip(sampled_entries, tokens)}
+        in_order = [e for e in sched.entries if e.sample]
+        finished = set(self.scheduler.update([by_request[e.request] for e in in_order]))
+        for e in in_order:
             out.request_ids.append(e.request)
-            out.new_token_ids.append(t)
+            out.new_token_ids.append(by_request[e.request])
             out.finished.append(e.request in finished)
         return out
 

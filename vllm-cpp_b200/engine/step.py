@@ -113,6 +113,11 @@ class ModelRunner:
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
     GRAPH_CONTEXT_BOUNDS = (8192,)      # captured steps are kept per context class: up to 8192 tokens, and beyond
     PORTION_BUCKETS = (16, 32, 64, 128, 256, 512)   # token counts of captured steps that run one prompt portion
+    # captured steps of single tokens beside prompt portions: slots for single-token entries, which come first, then
+    # MIXED_PORTIONS slots for portions that together hold up to one of MIXED_PORTION_TOKENS tokens
+    MIXED_SINGLES = (0, 8, 32, 64)
+    MIXED_PORTIONS = 4
+    MIXED_PORTION_TOKENS = (32, 64, 128, 256, 512)
 
     def __init__(self, model, page_size: int, num_pages: int, num_slots: int, dtype: torch.dtype, device,
                  cuda_graphs: bool = True, max_model_len: int | None = None):
@@ -256,6 +261,45 @@ class ModelRunner:
             return None
         return next(b for b in self.PORTION_BUCKETS if b >= n)
 
+    def mixed_size(self, entries) -> tuple[int, int] | None:
+        """(single-token slots, portion tokens) of the captured step that would run these entries: single-token
+        entries first, then one to four prompt portions of two tokens or more with logits wanted at their last
+        token or nowhere, up to 64 single tokens and 512 portion tokens.  None: they run kernel by kernel."""
+        if not self.cuda_graphs or len(entries) < 2:
+            return None
+        n_single = 0
+        while n_single < len(entries) and len(entries[n_single].tokens) == 1:
+            n_single += 1
+        portions = entries[n_single:]
+        if not portions or len(portions) > self.MIXED_PORTIONS or n_single > self.MIXED_SINGLES[-1]:
+            return None
+        tokens = 0
+        for e in portions:
+            n = len(e.tokens)
+            if n < 2 or e.want not in ([], [n - 1]):
+                return None
+            tokens += n
+        if tokens > self.MIXED_PORTION_TOKENS[-1]:
+            return None
+        return (next(b for b in self.MIXED_SINGLES if b >= n_single),
+                next(b for b in self.MIXED_PORTION_TOKENS if b >= tokens))
+
+    def _mixed_updates(self, singles: int, tokens: int) -> int:
+        """Block-table entries that a captured mixed step's buffer has room for."""
+        return singles + tokens // self.page_size + 2 * self.MIXED_PORTIONS
+
+    def rows_capacity(self, entries) -> int:
+        """Rows of logits that the step running these entries computes: the wanted ones, or more where a captured
+        step rounds up (the caller sizes what it sends along per row by this)."""
+        n_rows = sum(len(e.want) for e in entries)
+        bucket = self.capture_size(entries)
+        if bucket:
+            return bucket
+        mixed = self.mixed_size(entries)
+        if mixed:
+            return mixed[0] + self.MIXED_PORTIONS
+        return n_rows
+
     def _portion_updates(self, portion: int) -> int:
         """Block-table entries that a captured portion's buffer has room for: the pages its tokens can touch."""
         return portion // self.page_size + 2
@@ -283,6 +327,9 @@ class ModelRunner:
         elif (portion and all(len(u[0]) <= self._portion_updates(portion) for u in updates)
               and (post is None or post_key is not None)):
             logits = self._step_portion_graph(entries, updates, portion, n_rows, user, post, post_key)
+        elif (not bucket and (mixed := self.mixed_size(entries)) and (post is None or post_key is not None)
+              and all(len(u[0]) <= self._mixed_updates(*mixed) for u in updates)):
+            logits = self._step_mixed_graph(entries, updates, mixed, n_rows, user, post, post_key)
         else:
             logits = self._step_eager(entries, updates, n_rows, user, post)
         if check:
@@ -378,6 +425,75 @@ class ModelRunner:
         self.graph_replays += 1
         ops.launch_count += self.launches_per_graph[key]
         return result
+
+    def _step_mixed_graph(self, entries, updates, mixed, n_rows, user=None, post=None, post_key=None):
+        """Single tokens beside prompt portions through a captured step: the single-token entries fill the first
+        slots (token row = slot, as in a captured decoding step), unused slots stay empty, the portions follow."""
+        singles, tokens = mixed
+        n_single = sum(1 for e in entries if len(e.tokens) == 1)
+        longest = max([e.start_pos + 1 for e in entries[:n_single]] + [1])
+        ctx_bound = next((b for b in self.GRAPH_CONTEXT_BOUNDS if longest <= b), None)
+        key = ("mixed", singles, tokens, post_key if post is not None else None, ctx_bound)
+        if key not in self._graphs:
+            self._capture_mixed(key, post)
+        graph, ctx, result, pinned = self._graphs[key]
+        lay = ctx.meta_layout
+        if user is not None and len(user) > lay.X:
+            raise ValueError(f"a captured step carries at most {lay.X} user integers, {len(user)} given")
+        empty = StepEntry(0, 0, [], [[] for _ in self.tables], [])
+        slotted = entries[:n_single] + [empty] * (singles - n_single) + entries[n_single:]
+        host, facts = self._fill(lay, slotted, updates)
+        if user is not None:
+            host[lay.offsets["user"][0]:lay.offsets["user"][0] + len(user)] = user
+        ctx.__dict__.update(facts)
+        pinned.copy_(torch.from_numpy(host))
+        ctx.buffer.copy_(pinned, non_blocking=True)
+        self.last_ctx, self.last_h2d_bytes = ctx, host.nbytes
+        graph.replay()
+        self.graph_replays += 1
+        ops.launch_count += self.launches_per_graph[key]
+        return None if result is None else result[:n_rows]
+
+    def _capture_mixed(self, key, post=None):
+        """Captures the forward pass of ``singles`` one-token entries and MIXED_PORTIONS portions in ``tokens`` rows
+        (and what ``post`` adds), on empty entries.  The attention part lays out work items for every slot: sliced key
+        ranges for the single tokens, query tiles over all ``tokens`` rows for each portion; at replay the kernels
+        leave out empty slots and cut the portions' items down to the tokens that are there."""
+        _, singles, tokens, _, ctx_bound = key
+        E = R = singles + self.MIXED_PORTIONS
+        T = singles + tokens
+        lay = MetaLayout(T, E, R, self._mixed_updates(singles, tokens), len(self.tables), 8 * R + T)
+        dev = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
+        pinned = torch.zeros(lay.size, dtype=torch.int32).pin_memory()
+        ctx = StepContext(self, lay, dev, static=True)
+        ctx.static_max_ctx = ctx_bound
+        host = np.zeros(lay.size, dtype=np.int32)
+        o = lay.offsets
+        for g in range(len(self.tables)):
+            host[o[f"slot_map{g}"][0]:o[f"slot_map{g}"][1]] = -1
+        dev.copy_(torch.from_numpy(host))
+        ctx.host_q_len = [1] * singles + [tokens] * self.MIXED_PORTIONS
+        ctx.host_q_start = list(range(singles)) + [singles] * self.MIXED_PORTIONS
+        ctx.host_ctx_len = [0] * singles + [tokens] * self.MIXED_PORTIONS
+        ctx.host_slots = [0] * E
+
+        def run():
+            self._apply_table_updates(ctx)
+            logits = self.model.forward(ctx, self.cache.views)
+            return post(ctx, logits) if post is not None else logits
+
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            run()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        before = ops.launch_count
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            result = run()
+        self.launches_per_graph[key] = ops.launch_count - before
+        self._graphs[key] = (graph, ctx, result, pinned)
 
     def _capture_portion(self, key, post=None):
         """Captures the forward pass of one entry of ``portion`` tokens (and what ``post`` adds), on an entry of
