@@ -114,10 +114,11 @@ class ModelRunner:
     GRAPH_CONTEXT_BOUNDS = (8192,)      # captured steps are kept per context class: up to 8192 tokens, and beyond
     PORTION_BUCKETS = (16, 32, 64, 128, 256, 512)   # token counts of captured steps that run one prompt portion
     # captured steps of single tokens beside prompt portions: slots for single-token entries, which come first, then
-    # MIXED_PORTIONS slots for portions that together hold up to one of MIXED_PORTION_TOKENS tokens
+    # MIXED_PORTIONS slots for portions; MIXED_TOKENS are the token rows of the whole step (the products work in
+    # token tiles of up to 256: a step padded to 264 rows would cost two tiles)
     MIXED_SINGLES = (0, 8, 32, 64)
     MIXED_PORTIONS = 4
-    MIXED_PORTION_TOKENS = (32, 64, 128, 256, 512)
+    MIXED_TOKENS = (32, 64, 96, 128, 192, 256, 384, 512)
 
     def __init__(self, model, page_size: int, num_pages: int, num_slots: int, dtype: torch.dtype, device,
                  cuda_graphs: bool = True, max_model_len: int | None = None):
@@ -262,9 +263,9 @@ class ModelRunner:
         return next(b for b in self.PORTION_BUCKETS if b >= n)
 
     def mixed_size(self, entries) -> tuple[int, int] | None:
-        """(single-token slots, portion tokens) of the captured step that would run these entries: single-token
+        """(single-token slots, token rows) of the captured step that would run these entries: single-token
         entries first, then one to four prompt portions of two tokens or more with logits wanted at their last
-        token or nowhere, up to 64 single tokens and 512 portion tokens.  None: they run kernel by kernel."""
+        token or nowhere, up to 64 single tokens and 512 tokens in all.  None: they run kernel by kernel."""
         if not self.cuda_graphs or len(entries) < 2:
             return None
         n_single = 0
@@ -279,14 +280,13 @@ class ModelRunner:
             if n < 2 or e.want not in ([], [n - 1]):
                 return None
             tokens += n
-        if tokens > self.MIXED_PORTION_TOKENS[-1]:
-            return None
-        return (next(b for b in self.MIXED_SINGLES if b >= n_single),
-                next(b for b in self.MIXED_PORTION_TOKENS if b >= tokens))
+        singles = next(b for b in self.MIXED_SINGLES if b >= n_single)
+        rows = next((b for b in self.MIXED_TOKENS if b >= singles + tokens), None)
+        return None if rows is None else (singles, rows)
 
-    def _mixed_updates(self, singles: int, tokens: int) -> int:
+    def _mixed_updates(self, singles: int, rows: int) -> int:
         """Block-table entries that a captured mixed step's buffer has room for."""
-        return singles + tokens // self.page_size + 2 * self.MIXED_PORTIONS
+        return singles + (rows - singles) // self.page_size + 2 * self.MIXED_PORTIONS
 
     def rows_capacity(self, entries) -> int:
         """Rows of logits that the step running these entries computes: the wanted ones, or more where a captured
@@ -429,11 +429,11 @@ class ModelRunner:
     def _step_mixed_graph(self, entries, updates, mixed, n_rows, user=None, post=None, post_key=None):
         """Single tokens beside prompt portions through a captured step: the single-token entries fill the first
         slots (token row = slot, as in a captured decoding step), unused slots stay empty, the portions follow."""
-        singles, tokens = mixed
+        singles, rows = mixed
         n_single = sum(1 for e in entries if len(e.tokens) == 1)
         longest = max([e.start_pos + 1 for e in entries[:n_single]] + [1])
         ctx_bound = next((b for b in self.GRAPH_CONTEXT_BOUNDS if longest <= b), None)
-        key = ("mixed", singles, tokens, post_key if post is not None else None, ctx_bound)
+        key = ("mixed", singles, rows, post_key if post is not None else None, ctx_bound)
         if key not in self._graphs:
             self._capture_mixed(key, post)
         graph, ctx, result, pinned = self._graphs[key]
@@ -455,14 +455,14 @@ class ModelRunner:
         return None if result is None else result[:n_rows]
 
     def _capture_mixed(self, key, post=None):
-        """Captures the forward pass of ``singles`` one-token entries and MIXED_PORTIONS portions in ``tokens`` rows
-        (and what ``post`` adds), on empty entries.  The attention part lays out work items for every slot: sliced key
-        ranges for the single tokens, query tiles over all ``tokens`` rows for each portion; at replay the kernels
-        leave out empty slots and cut the portions' items down to the tokens that are there."""
-        _, singles, tokens, _, ctx_bound = key
+        """Captures the forward pass of ``singles`` one-token entries and MIXED_PORTIONS portions in ``rows`` token
+        rows together (and what ``post`` adds), on empty entries.  The attention part lays out work items for every
+        slot: sliced key ranges for the single tokens, query tiles over all the remaining rows for each portion; at
+        replay the kernels leave out empty slots and cut the portions' items down to the tokens that are there."""
+        _, singles, T, _, ctx_bound = key
         E = R = singles + self.MIXED_PORTIONS
-        T = singles + tokens
-        lay = MetaLayout(T, E, R, self._mixed_updates(singles, tokens), len(self.tables), 8 * R + T)
+        tokens = T - singles
+        lay = MetaLayout(T, E, R, self._mixed_updates(singles, T), len(self.tables), 8 * R + T)
         dev = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
         pinned = torch.zeros(lay.size, dtype=torch.int32).pin_memory()
         ctx = StepContext(self, lay, dev, static=True)
