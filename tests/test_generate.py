@@ -40,6 +40,21 @@ def test_sampled_config_b(model_dirs, plain_models):
     assert got == want
 
 
+def test_captured_steps_are_dropped_and_made_again(model_dirs, plain_models):
+    """With room for two captured steps only, the steps of this run (lone portions, portions beside single tokens,
+    one to four single tokens) push one another out and are captured again: the tokens stay those of the plain
+    implementation."""
+    prompts = [random_tokens(384, n, 3 + i) for i, n in enumerate((1, 7, 33, 64))]
+    llm = make_llm(model_dirs["B"], "B")
+    llm.runner.MAX_GRAPHS = 2
+    got = llm.generate(prompts, 12, 0.8, 1.0, repeat_penalty=1.0, seed=4)
+    got += llm.generate(prompts[:1], 5, 0.0, 1.0, repeat_penalty=1.0)
+    want = [plain_generate(plain_models, "B", p, 12, temperature=0.8, seed=4 + i) for i, p in enumerate(prompts)]
+    want.append(plain_generate(plain_models, "B", prompts[0], 5))
+    assert got == want
+    assert len(llm.runner._graphs) <= 2 and llm.runner.graph_replays > 10
+
+
 def test_reference_defaults_top_p_and_penalty(model_dirs, plain_models):
     """The reference's own defaults: temperature 0.7, top-p 0.8, repetition penalty 1.1 over prompt + output."""
     prompts = [random_tokens(256, n, 20 + i) for i, n in enumerate((9, 30))]

@@ -22,6 +22,8 @@ hundred small kernels would otherwise exceed the time the GPU needs for them.
 """
 from __future__ import annotations
 
+import collections
+
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -112,6 +114,7 @@ class ModelRunner:
 
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
     GRAPH_CONTEXT_BOUNDS = (8192,)      # captured steps are kept per context class: up to 8192 tokens, and beyond
+    MAX_GRAPHS = 48                     # captured steps kept; the least recently used one goes when another is captured
     PORTION_BUCKETS = (16, 32, 64, 128, 256, 512)   # token counts of captured steps that run one prompt portion
     # captured steps of single tokens beside prompt portions: slots for single-token entries, which come first, then
     # MIXED_PORTIONS slots for portions; MIXED_TOKENS are the token rows of the whole step (the products work in
@@ -138,7 +141,7 @@ class ModelRunner:
                        for _ in range(n_paged)]
         self._uploaded = [[0] * num_slots for _ in range(n_paged)]   # table entries of each slot already on the device
         self.cuda_graphs = cuda_graphs and self.device.type == "cuda" and getattr(model, "capturable", True)
-        self._graphs: dict[tuple, tuple] = {}
+        self._graphs: collections.OrderedDict[tuple, tuple] = collections.OrderedDict()   # least recently used first
         self.last_ctx = None
         self.last_h2d_bytes = 0
         self.graph_replays = 0
@@ -383,6 +386,16 @@ class ModelRunner:
                      host_ctx_len=[p + 1 for p in pos], host_slots=[e.slot for e in entries])
         return np.asarray(flat, dtype=np.int32), facts
 
+    def _graph(self, key):
+        self._graphs.move_to_end(key)
+        return self._graphs[key]
+
+    def _keep_graph(self, key, captured) -> None:
+        self._graphs[key] = captured
+        while len(self._graphs) > self.MAX_GRAPHS:
+            old, _ = self._graphs.popitem(last=False)   # its buffers go back to the allocator with the graph
+            self.launches_per_graph.pop(old, None)
+
     def _step_graph(self, entries, updates, bucket, user=None, post=None, post_key=None):
         # one captured step per padded batch size and context class: the attention part slices the key ranges of
         # short contexts differently from long ones, and a captured step cannot ask how long they are
@@ -391,7 +404,7 @@ class ModelRunner:
         key = (bucket, post_key if post is not None else None, ctx_bound)
         if key not in self._graphs:
             self._capture(key, post)
-        graph, ctx, result, pinned = self._graphs[key]
+        graph, ctx, result, pinned = self._graph(key)
         if user is not None and len(user) > ctx.meta_layout.X:
             raise ValueError(f"a captured step carries at most {ctx.meta_layout.X} user integers, {len(user)} given")
         host, facts = self._fill_decode(ctx.meta_layout, entries, updates, user)
@@ -410,7 +423,7 @@ class ModelRunner:
         key = ("portion", portion, n_rows, post_key if post is not None else None)
         if key not in self._graphs:
             self._capture_portion(key, post)
-        graph, ctx, result, pinned = self._graphs[key]
+        graph, ctx, result, pinned = self._graph(key)
         lay = ctx.meta_layout
         if user is not None and len(user) > lay.X:
             raise ValueError(f"a captured step carries at most {lay.X} user integers, {len(user)} given")
@@ -436,7 +449,7 @@ class ModelRunner:
         key = ("mixed", singles, rows, post_key if post is not None else None, ctx_bound)
         if key not in self._graphs:
             self._capture_mixed(key, post)
-        graph, ctx, result, pinned = self._graphs[key]
+        graph, ctx, result, pinned = self._graph(key)
         lay = ctx.meta_layout
         if user is not None and len(user) > lay.X:
             raise ValueError(f"a captured step carries at most {lay.X} user integers, {len(user)} given")
@@ -493,7 +506,7 @@ class ModelRunner:
         with torch.cuda.graph(graph):
             result = run()
         self.launches_per_graph[key] = ops.launch_count - before
-        self._graphs[key] = (graph, ctx, result, pinned)
+        self._keep_graph(key, (graph, ctx, result, pinned))
 
     def _capture_portion(self, key, post=None):
         """Captures the forward pass of one entry of ``portion`` tokens (and what ``post`` adds), on an entry of
@@ -527,7 +540,7 @@ class ModelRunner:
         with torch.cuda.graph(graph):
             result = run()
         self.launches_per_graph[key] = ops.launch_count - before
-        self._graphs[key] = (graph, ctx, result, pinned)
+        self._keep_graph(key, (graph, ctx, result, pinned))
 
     def _capture(self, key, post=None):
         """Captures the forward pass of ``bucket`` single-token entries (and what ``post`` adds).  The capture
@@ -564,4 +577,4 @@ class ModelRunner:
         with torch.cuda.graph(graph):
             result = run()
         self.launches_per_graph[key] = ops.launch_count - before
-        self._graphs[key] = (graph, ctx, result, pinned)
+        self._keep_graph(key, (graph, ctx, result, pinned))
