@@ -121,7 +121,7 @@ class ModelRunner:
     # token tiles of up to 256: a step padded to 264 rows would cost two tiles)
     MIXED_SINGLES = (0, 8, 32, 64)
     MIXED_PORTIONS = 4
-    MIXED_TOKENS = (32, 64, 96, 128, 192, 256, 384, 512)
+    MIXED_TOKENS = (32, 64, 96, 128, 192, 256)
 
     def __init__(self, model, page_size: int, num_pages: int, num_slots: int, dtype: torch.dtype, device,
                  cuda_graphs: bool = True, max_model_len: int | None = None):
@@ -268,7 +268,8 @@ class ModelRunner:
     def mixed_size(self, entries) -> tuple[int, int] | None:
         """(single-token slots, token rows) of the captured step that would run these entries: single-token
         entries first, then one to four prompt portions of two tokens or more with logits wanted at their last
-        token or nowhere, up to 64 single tokens and 512 tokens in all.  None: they run kernel by kernel."""
+        token or nowhere, up to 64 single tokens and 256 tokens in all (beyond that the GPU needs longer for a step
+        than the host needs to launch it kernel by kernel).  None: they run kernel by kernel."""
         if not self.cuda_graphs or len(entries) < 2:
             return None
         n_single = 0
