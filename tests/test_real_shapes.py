@@ -44,7 +44,9 @@ def test_bf16_engine_follows_the_32_bit_engine_at_8b_layer_sizes():
                 cm.commit(r, pos[r])
         rows[dtype] = torch.cat(got)
         if dtype == "bfloat16":
-            assert runner.graph_replays == len(plan)  # every step ran from a captured graph: portions side by side, single tokens, lone portions
+            # all but the first two steps (317 and 400 tokens side by side: too many for a captured mixed step) ran
+            # from captured graphs: portions side by side, single tokens, lone portions
+            assert runner.graph_replays == len(plan) - 2
         del llm, runner
         torch.cuda.empty_cache()
     ref, got = rows["float32"], rows["bfloat16"]
