@@ -472,6 +472,60 @@ def test_gemm_bf16_tn_every_unit_shape(shape, M, T, K, splits):
         ops.gemm_bf16_tn(w, x, out, splits, status, shape=7)
 
 
+@pytest.mark.parametrize("M,T,K", [(256, 129, 64), (512, 300, 256), (1000, 700, 328), (6144, 512, 1024), (4096, 2048, 512),
+                                   (300, 257, 1096), (24576, 160, 128)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_bf16_tn_on_pairs_of_blocks(M, T, K, out_dtype):
+    """The two-block kernel (cta_group::2, 256 x 256 units, each block half of the token tile), forced, against
+    64-bit and against the single-block kernel: ragged feature, token and k edges, one unit and many."""
+    from vllm_cpp_b200 import ops
+    torch.manual_seed(M + T + K)
+    w = torch.randn(M, K, device=dev()).to(torch.bfloat16)
+    x = torch.randn(T, K, device=dev()).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    outs = []
+    try:
+        for mode in (2, 0):
+            ops.gemm_set_pairs(mode)
+            out = torch.full((T, M), float("nan"), dtype=out_dtype, device=dev())
+            ops.gemm_bf16_tn(w, x, out, 1, status)
+            torch.cuda.synchronize()
+            assert status.item() == 0
+            outs.append(out)
+    finally:
+        ops.gemm_set_pairs(1)
+    want = x.double() @ w.double().T
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(outs[0].double(), want, rtol=1e-4, atol=K * 2.0 ** -24 * 64)
+    else:
+        torch.testing.assert_close(outs[0].double(), want, rtol=1e-2, atol=1e-2 * K ** 0.5)
+    assert torch.equal(outs[0], outs[1])      # the same k order, the same bits
+
+
+@pytest.mark.parametrize("I,T,K", [(128, 256, 64), (200, 300, 96), (1536, 2048, 512), (264, 160, 128)])
+def test_gemm_bf16_swiglu_on_pairs_of_blocks(I, T, K):
+    from vllm_cpp_b200 import ops
+    torch.manual_seed(I + T)
+    w = (torch.randn(2 * I, K, device=dev()) * 0.2).to(torch.bfloat16)
+    x = torch.randn(T, K, device=dev()).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    outs = []
+    try:
+        for mode in (2, 0):
+            ops.gemm_set_pairs(mode)
+            out = torch.full((T, I), float("nan"), dtype=torch.bfloat16, device=dev())
+            ops.gemm_bf16_swiglu(w, x, out, status)
+            torch.cuda.synchronize()
+            assert status.item() == 0
+            outs.append(out)
+    finally:
+        ops.gemm_set_pairs(1)
+    gu = x.double() @ w.double().T
+    g, u = gu[:, 0::2], gu[:, 1::2]
+    torch.testing.assert_close(outs[0].double(), g / (1 + torch.exp(-g)) * u, rtol=2e-2, atol=2e-2)
+    assert torch.equal(outs[0], outs[1])
+
+
 def test_choose_splits_fills_the_sms():
     from vllm_cpp_b200.parts.linear import choose_splits
     assert choose_splits(6144, 256, 4096) == 3      # 48 units of 128 x 256 -> 144

@@ -32,6 +32,8 @@
 
 #include <stdlib.h>
 
+#include <algorithm>
+
 #include <mutex>
 #include <unordered_map>
 
@@ -399,9 +401,11 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
 // Two blocks on two SMs working as a pair (cta_group::2) for prompt portions.
 //
 // One MMA of the pair covers 256 features (128 TMEM lanes in each block) x 256 tokens; each block loads only its own
-// 128-token half of the token tile, which the tensor cores of both read.  With two such accumulators per block a
-// pair's unit is 512 features x 256 tokens for 48 KB per block and k-step of 64 -- a quarter less traffic from L2
-// per flop than the single-block kernel's 64 KB, and these products are bound by that traffic.
+// 128 features of the weights and its own 128-token half of the token tile, which the tensor cores of both read:
+// 32 KB per block and k-step of 64 where the single-block kernel draws 48 KB for the same 128 x 256 x 64 products,
+// and what an SM can draw from L2 (about 70 bytes a clock) is what bounds that kernel.  A pair's unit is 256
+// features x 256 tokens; each block holds two accumulators of 256 columns, so the epilogue of one unit overlaps the
+// MMAs of the next.
 //
 // Block 0 of the pair issues every MMA.  Both blocks' TMA loads report to block 0's "full" barrier
 // (cp.async.bulk.tensor with .cta_group::2 lets a load signal the peer's barrier; no multicast load is used);
@@ -444,9 +448,9 @@ struct SmemPair {
     static constexpr int BN = 256;
     static constexpr int A_BYTES = BM * BK * 2;           // one 128-feature tile
     static constexpr int B_BYTES = (BN / 2) * BK * 2;     // this block's half of the token tile
-    static constexpr int STAGE_BYTES = 2 * A_BYTES + B_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int NUM_BARS = 2 * STAGES + 2;
+    static constexpr int NUM_BARS = 2 * STAGES + 4;
     static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;
 };
 
@@ -456,15 +460,16 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
                                                                          GemmArgs g) {
     using L = SmemPair<STAGES>;
     constexpr int BN = 256;
-    constexpr uint32_t TMEM_COLS = 512;   // two accumulators of 256 token columns
+    constexpr uint32_t TMEM_COLS = 512;   // two accumulators of 256 token columns, used in turn
+    constexpr int CHUNK = 64;             // accumulator columns read per wait in the epilogue
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t bars = base + L::BAR_OFFSET;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-    const uint32_t acc_full_bar = bars + 8u * (2 * STAGES);
-    const uint32_t acc_empty_bar = bars + 8u * (2 * STAGES + 1);
+    auto acc_full_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+    auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(gen + L::BAR_OFFSET + L::NUM_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::BAR_OFFSET + L::NUM_BARS * 8 + 8);
 
@@ -473,22 +478,20 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
     const uint32_t rank = cluster_rank();          // 0 issues the MMAs
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     const int total_kb = (g.K + BK - 1) / BK;
-    const int unit_rows = 4 * BM;   // rows of W per pair unit
+    const int unit_rows = 2 * BM;   // rows of W per pair unit: 128 in each block
     const int m_tiles = (g.M + unit_rows - 1) / unit_rows;
     const int n_tiles = (g.N + BN - 1) / BN;
     const int units = m_tiles * n_tiles;
-    // first row in W of this block's feature tile mt
-    auto w_row = [&](int m0, int mt) {
-        return m0 + ((int)rank * 2 + mt) * BM;
-    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
-        mbar_init(acc_full_bar, 1);
-        mbar_init(acc_empty_bar, 8);   // four epilogue warps in each block of the pair
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_full_bar(a), 1);
+            mbar_init(acc_empty_bar(a), 8);   // four epilogue warps in each block of the pair
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -505,7 +508,7 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
     const uint32_t tmem_base = *tmem_holder;
 
     if (warp == 0) {
-        // ---- TMA producer (in both blocks): its two feature tiles and its half of the token tile ----
+        // ---- TMA producer (in both blocks): its feature tile and its half of the token tile ----
         if (lane == 0) {
             pdl_wait();
             int it = 0, armed = 0;
@@ -520,9 +523,8 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
                     if (rank == 0) mbar_expect_tx(full_bar(s), 2 * L::STAGE_BYTES);   // both blocks' bytes land on block 0's barrier
                     const uint32_t dst = base + s * L::STAGE_BYTES;
                     const uint32_t bar0 = full_bar(s) & PEER_BIT_MASK;
-                    tma_load_2d_pair(dst, &map_w, bar0, i * BK, w_row(m0, 0));
-                    tma_load_2d_pair(dst + L::A_BYTES, &map_w, bar0, i * BK, w_row(m0, 1));
-                    tma_load_2d_pair(dst + 2 * L::A_BYTES, &map_x, bar0, i * BK, n0 + (int)rank * (BN / 2));
+                    tma_load_2d_pair(dst, &map_w, bar0, i * BK, m0 + (int)rank * BM);
+                    tma_load_2d_pair(dst + L::A_BYTES, &map_x, bar0, i * BK, n0 + (int)rank * (BN / 2));
                     armed = it + 1;
                 }
             }
@@ -541,7 +543,8 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
             int it = 0, j = 0;
             bool ok = true;
             for (int u = pair; u < units && ok; u += pairs, ++j) {
-                ok = mbar_wait(acc_empty_bar, (j & 1) ^ 1u, abort_flag, g.status);   // both epilogues drained the last unit
+                const int a = j & 1;
+                ok = mbar_wait(acc_empty_bar(a), ((j >> 1) & 1) ^ 1u, abort_flag, g.status);   // both epilogues drained it
                 if (!ok) break;
                 tc_fence_after();
                 for (int i = 0; i < total_kb; ++i, ++it) {
@@ -550,59 +553,55 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t a_addr = base + s * L::STAGE_BYTES;
-                    const uint64_t db = smem_desc(a_addr + 2 * L::A_BYTES);
+                    const uint64_t da = smem_desc(a_addr), db = smem_desc(a_addr + L::A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-#pragma unroll
-                        for (int mt = 0; mt < 2; ++mt)
-                            tc_mma_pair(tmem_base + mt * BN, smem_desc(a_addr + mt * L::A_BYTES) + 2 * k, db + 2 * k, idesc,
-                                        (i > 0 || k > 0) ? 1u : 0u);
-                    }
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tc_mma_pair(tmem_base + a * BN, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
                     tc_commit_pair(empty_bar(s));   // frees the stage in both blocks
                 }
-                if (ok) tc_commit_pair(acc_full_bar);
+                if (ok) tc_commit_pair(acc_full_bar(a));
             }
         }
     } else {
-        // ---- epilogue (both blocks): each owns its 128 lanes of both accumulators ----
+        // ---- epilogue (both blocks): each owns its 128 lanes of the accumulator ----
         const int q = warp & 3;
         int j = 0;
         for (int u = pair; u < units; u += pairs, ++j) {
             int mi, ni;
             tile_of(u, m_tiles, n_tiles, mi, ni);
             const int m0 = mi * unit_rows, n0 = ni * BN;
-            if (!mbar_wait(acc_full_bar, j & 1, abort_flag, g.status)) break;
+            const int a = j & 1;
+            if (!mbar_wait(acc_full_bar(a), (j >> 1) & 1, abort_flag, g.status)) break;
             tc_fence_after();
-            {
+            const int m = m0 + (int)rank * BM + q * 32 + lane;
 #pragma unroll 1
-                for (int cc = 0; cc < 2 * BN; cc += 16) {
-                    const int mt = cc / BN, c0 = cc % BN;
-                    if (n0 + c0 >= g.N) continue;   // uniform over the warp
-                    const int m = m0 + ((int)rank * 2 + mt) * BM + q * 32 + lane;
-                    uint32_t v[16];
-                    tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * BN + c0), v);
-                    tc_wait_ld();
-                    if (g.swiglu) {
-                        uint32_t (*v1)[16] = reinterpret_cast<uint32_t (*)[16]>(v);
-                        swiglu_store<16>(v1, reinterpret_cast<__nv_bfloat16*>(g.out), g.ldc, m, g.M, n0 + c0, g.N, lane);
-                    } else if (m < g.M) {
-                        if (g.out_dtype == VCB_F32) {
-                            float* o = reinterpret_cast<float*>(g.out);
+            for (int c0 = 0; c0 < BN; c0 += CHUNK) {
+                if (n0 + c0 >= g.N) continue;   // uniform over the warp
+                uint32_t v[CHUNK / 16][16];
 #pragma unroll
-                            for (int jj = 0; jj < 16; ++jj)
-                                if (n0 + c0 + jj < g.N) o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __uint_as_float(v[jj]);
-                        } else {
-                            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out);
+                for (int b = 0; b < CHUNK / 16; ++b)
+                    tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + c0 + 16 * b), v[b]);
+                tc_wait_ld();
+                if (g.swiglu) {
+                    swiglu_store<CHUNK>(v, reinterpret_cast<__nv_bfloat16*>(g.out), g.ldc, m, g.M, n0 + c0, g.N, lane);
+                } else if (m < g.M) {
+                    if (g.out_dtype == VCB_F32) {
+                        float* o = reinterpret_cast<float*>(g.out);
 #pragma unroll
-                            for (int jj = 0; jj < 16; ++jj)
-                                if (n0 + c0 + jj < g.N) o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __float2bfloat16_rn(__uint_as_float(v[jj]));
-                        }
+                        for (int jj = 0; jj < CHUNK; ++jj)
+                            if (n0 + c0 + jj < g.N) o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __uint_as_float(v[jj / 16][jj % 16]);
+                    } else {
+                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out);
+#pragma unroll
+                        for (int jj = 0; jj < CHUNK; ++jj)
+                            if (n0 + c0 + jj < g.N)
+                                o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __float2bfloat16_rn(__uint_as_float(v[jj / 16][jj % 16]));
                     }
                 }
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_block0(acc_empty_bar);
+            if (lane == 0) mbar_arrive_block0(acc_empty_bar(a));
         }
         tc_fence_before();
     }
@@ -724,21 +723,23 @@ int launch(const void* W, const void* X, const GemmArgs& g, long long ldw, long 
     return launch_maps<BN, STAGES, MT, ACC>(W, g.M, X, g, ldw, ldx, splits, stream);
 }
 
-// VLLM_CPP_B200_GEMM_PAIRS=1 sends prompt-portion products to the two-block kernel.  Off by default: measured on
-// B200 it is no faster than the single-block kernel at the benchmark's shapes (qkv 118 vs 96 us, o 60 vs 60,
-// gate_up 432 vs 426, down 180 vs 174), so the bytes it saves are not what bounds these products.
-bool pairs_enabled() {
-    static int on = -1;
-    if (on < 0) {
+// Which products of more than 128 tokens without k-slices run on the two-block kernel: 0 none, 1 (the default) those
+// whose 256 x 256 units fill the rounds of the 74 pairs no worse than the single-block kernel's best shape fills
+// those of the 148 SMs -- round for round the pairs measured about 4 % faster (2,048 tokens: qkv 79.4 -> 75.9 us,
+// o 54.4 -> 52.6, gate_up 294 -> 288; 4,096 tokens: 158 -> 147, 106.5 -> 99.9, 600 -> 575, down 330 -> 297) --
+// 2 all of them (tests).  VLLM_CPP_B200_GEMM_PAIRS sets the default.
+int g_pairs = -1;
+int pairs_mode() {
+    if (g_pairs < 0) {
         const char* e = getenv("VLLM_CPP_B200_GEMM_PAIRS");
-        on = (e && e[0] == '1') ? 1 : 0;
+        g_pairs = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1;
     }
-    return on == 1;
+    return g_pairs;
 }
 
 int launch_pair(const void* W, long long w_rows, const void* X, const GemmArgs& g, long long ldw, long long ldx,
                 cudaStream_t stream) {
-    constexpr int STAGES = 4;
+    constexpr int STAGES = 6;
     using L = SmemPair<STAGES>;
     CUtensorMap mw, mx;
     if (!tensor_map(W, w_rows, g.K, ldw, BM, &mw) || !tensor_map(X, g.N, g.K, ldx, 128, &mx)) return -3;
@@ -752,7 +753,7 @@ int launch_pair(const void* W, long long w_rows, const void* X, const GemmArgs& 
         }
         opted = true;
     }
-    const int unit_rows = 4 * BM;
+    const int unit_rows = 2 * BM;
     const long long units = (long long)((g.M + unit_rows - 1) / unit_rows) * ((g.N + 255) / 256);
     const long long max_pairs = num_sms() / 2;
     const int pairs = (int)(units < max_pairs ? units : max_pairs);
@@ -809,7 +810,15 @@ int launch_shape(int shape, const void* W, const void* X, const GemmArgs& g, lon
     return -1;
 }
 
-int pick_shape(int M, int N, int K, int splits) {
+// time of a product on pairs of blocks in the units of pick_shape's costs (token columns a block works through)
+long long pair_cost(int M, int N) {
+    const long long units = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+    const long long pairs = num_sms() / 2;
+    return ((units + pairs - 1) / pairs) * 256;
+}
+
+int pick_shape(int M, int N, int K, int splits, long long* cost_out = nullptr) {
+    if (cost_out) *cost_out = -1;
     if (N <= 16) return SHAPE_N16;
     if (N <= 32) return SHAPE_N32;
     if (N <= 64) return SHAPE_N64;
@@ -831,10 +840,19 @@ int pick_shape(int M, int N, int K, int splits) {
     // four fifths of the time for half the work.  They pay where they fill one round and 256-token units leave a
     // third of the SMs idle (qkv_proj at 384 tokens: 30.5 -> 24.5 us).
     const long long c0 = cost(1, 128) * 8 / 5;
+    if (cost_out) *cost_out = std::min(std::min(c0, c1), std::min(c2, c3));
     if (c0 < c1 && c0 < c2 && c0 < c3) return SHAPE_N128;
     if (c1 == c2 && c2 <= c3 && K >= 8192) return SHAPE_M256_N256;
     if (c1 <= c2 && c1 <= c3) return SHAPE_N256;
     return c3 < c2 ? SHAPE_M256_N192 : SHAPE_M256_N256;
+}
+bool use_pairs(int M, int N, int K, int splits) {
+    const int mode = pairs_mode();
+    if (mode == 0 || splits != 1 || N <= 128 || M < 2 * BM) return false;
+    if (mode == 2) return true;
+    long long single = -1;
+    pick_shape(M, N, K, 1, &single);
+    return single > 0 && pair_cost(M, N) * 24 <= single * 25;
 }
 }  // namespace
 
@@ -852,7 +870,7 @@ VCB_API int vcb_gemm_bf16_tn_shape(const void* W, const void* X, void* out, int 
     const int kb_per_split = (total_kb + splits - 1) / splits;
     splits = (total_kb + kb_per_split - 1) / kb_per_split;
     GemmArgs g{out, out_dtype, M, N, K, ldc, split_stride, kb_per_split, splits, 0, status};
-    if (shape < 0 && pairs_enabled() && N > 128 && M >= 512) return launch_pair(W, M, X, g, ldw, ldx, stream);
+    if (shape < 0 && use_pairs(M, N, K, splits)) return launch_pair(W, M, X, g, ldw, ldx, stream);
     return launch_shape(shape < 0 ? pick_shape(M, N, K, splits) : shape, W, X, g, ldw, ldx, splits, stream);
 }
 
@@ -867,7 +885,7 @@ VCB_API int vcb_gemm_bf16_swiglu(const void* W, const void* X, void* out, int I,
     VCB_CHECK_ARG(((uintptr_t)W % 16 == 0) && ((uintptr_t)X % 16 == 0), "gemm_bf16_swiglu: operands must be 16-byte aligned");
     const int total_kb = (K + BK - 1) / BK;
     GemmArgs g{out, VCB_BF16, 2 * I, N, K, ldc, 0, total_kb, 1, 1, status};
-    if (shape < 0 && pairs_enabled() && N > 128 && I >= 256) return launch_pair(W, 2LL * I, X, g, ldw, ldx, stream);
+    if (shape < 0 && use_pairs(2 * I, N, K, 1)) return launch_pair(W, 2LL * I, X, g, ldw, ldx, stream);
     return launch_shape(shape < 0 ? pick_shape(2 * I, N, K, 1) : shape, W, X, g, ldw, ldx, 1, stream);
 }
 
@@ -876,3 +894,6 @@ VCB_API int vcb_gemm_bf16_tn(const void* W, const void* X, void* out, int out_dt
                              int* status, cudaStream_t stream) {
     return vcb_gemm_bf16_tn_shape(W, X, out, out_dtype, M, N, K, ldw, ldx, ldc, splits, split_stride, -1, status, stream);
 }
+
+// 0: no product runs on pairs of blocks; 1: those that the rule above sends there; 2: all that can.
+VCB_API void vcb_gemm_set_pairs(int mode) { g_pairs = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }

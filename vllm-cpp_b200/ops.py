@@ -60,6 +60,7 @@ def _declare(L):
         "vcb_gemm_bf16_tn": [P, P, P, I, I, I, I, LL, LL, LL, I, LL, P, P],
         "vcb_gemm_bf16_tn_shape": [P, P, P, I, I, I, I, LL, LL, LL, I, LL, I, P, P],
         "vcb_gemm_effective_splits": [I, I],
+        "vcb_gemm_set_pairs": [I],
         "vcb_gemm_bf16_swiglu": [P, P, P, I, I, I, LL, LL, LL, I, P, P],
         "vcb_sgemm_tn": [P, P, P, I, I, I, LL, LL, LL, P],
         "vcb_gemm_bf16_plain": [P, P, P, I, I, I, I, LL, LL, LL, P],
@@ -239,6 +240,14 @@ def gemm_effective_splits(K: int, splits: int) -> int:
 
 
 GEMM_SHAPES = ("n16", "n32", "n64", "n128", "n256", "m256_n192", "m256_n256")   # unit shapes of the kernel, by index
+
+
+def gemm_set_pairs(mode: int) -> None:
+    """Which products of more than 128 tokens without k-slices run on pairs of blocks (``cta_group::2``: one MMA
+    spans 256 features on two SMs, each block loads its half of the token tile): 0 none, 1 those whose units fill
+    the pairs' rounds no worse than the single-block kernel's fill the SMs' (the default, which
+    ``VLLM_CPP_B200_GEMM_PAIRS`` overrides), 2 all that can.  Process-wide."""
+    lib().vcb_gemm_set_pairs(int(mode))
 
 
 def gemm_bf16_tn(w, x, out, splits, status, shape=-1):
