@@ -55,6 +55,37 @@ def test_captured_steps_are_dropped_and_made_again(model_dirs, plain_models):
     assert len(llm.runner._graphs) <= 2 and llm.runner.graph_replays > 10
 
 
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_captured_and_kernel_by_kernel_steps_give_the_same_tokens(name, model_dirs):
+    """Forty requests arriving a few at a time, sampled with the reference's defaults (temperature, nucleus,
+    repetition penalty), in a pool so small that requests are preempted: in 32-bit the tokens do not depend on
+    whether steps replay captured graphs (padded, slots left empty) or run kernel by kernel."""
+    import numpy as np
+    from conftest import TINY
+    vocab = TINY[name]["vocab_size"]
+    streams = []
+    for graphs in (True, False):
+        llm = make_llm(model_dirs[name], name, cuda_graphs=graphs, max_tokens=320, max_num_seqs=6, max_step_tokens=48)
+        rng = np.random.default_rng(11)
+        pending = [random_tokens(vocab, int(n), 500 + i) for i, n in enumerate(rng.integers(1, 90, 40))]
+        ids, out, steps = [], {}, 0
+        while pending or llm.has_requests():
+            if pending and steps % 3 == 0:
+                for _ in range(min(int(rng.integers(1, 4)), len(pending))):
+                    ids.append(llm.submit_tokens(pending.pop(), int(rng.integers(1, 24)), seed=len(ids), ignore_eos=True))
+            o = llm.step()
+            steps += 1
+            for rid, tok in zip(o.request_ids, o.new_token_ids):
+                out.setdefault(rid, []).append(tok)
+        streams.append([out[r] for r in ids])
+        if graphs:
+            assert llm.runner.graph_replays > steps // 2
+            kinds = {k[0] if isinstance(k[0], str) else "single tokens" for k in llm.runner._graphs}
+            assert kinds == {"single tokens", "portion", "mixed"}, kinds
+        assert llm.stats().preemptions > 0
+    assert streams[0] == streams[1]
+
+
 def test_reference_defaults_top_p_and_penalty(model_dirs, plain_models):
     """The reference's own defaults: temperature 0.7, top-p 0.8, repetition penalty 1.1 over prompt + output."""
     prompts = [random_tokens(256, n, 20 + i) for i, n in enumerate((9, 30))]
