@@ -478,8 +478,9 @@ __global__ __launch_bounds__(256) void qknorm_rope_kvwrite_hd128_kernel(
         }
     }
     const __nv_bfloat16* row = qkv + (size_t)t * heads_total * hd;
-    // four heads a round: their loads are all issued before the first is used
-    constexpr int U = 4;
+    // six heads a round (the 48 heads of the 8B shape in one round of eight warps): their loads are all issued
+    // before the first is used
+    constexpr int U = 6;
     for (int h0 = warp; h0 < heads_total; h0 += U * nwarps) {
         __nv_bfloat162 lo[U], hi[U];
 #pragma unroll
