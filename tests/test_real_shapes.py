@@ -104,3 +104,41 @@ def test_bf16_engine_follows_the_32_bit_engine_at_other_serving_sizes(page_size,
     err = ((got - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)).max().item()
     assert err < 3e-2, err
     assert (got.argmax(dim=1) == ref.argmax(dim=1)).float().mean().item() >= 0.8
+
+
+def test_long_context_decoding_at_8b_layer_sizes():
+    """A prompt of 12,000 tokens in portions of 2,048, then single tokens at a context beyond the 8,192 of the first
+    class of captured steps (other key slicing, other graph), in bfloat16 against the true-32-bit engine."""
+    from vllm_cpp_b200 import LLM, EngineConfig, Qwen3Config
+    from vllm_cpp_b200.engine.step import StepEntry
+    from vllm_cpp_b200.runtime import runtime
+    cfg = Qwen3Config(vocab_size=32000, hidden_size=4096, intermediate_size=12288, num_hidden_layers=2,
+                      num_attention_heads=32, num_key_value_heads=8, head_dim=128, max_position_embeddings=16384,
+                      rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+    rng = np.random.default_rng(3)
+    n_prompt, n_decode = 12000, 5
+    tokens = rng.integers(0, cfg.vocab_size, n_prompt + n_decode).tolist()
+    rows = {}
+    for dtype in ("float32", "bfloat16"):
+        llm = LLM(config=cfg, random_seed=2, engine=EngineConfig(dtype=dtype, page_size=16, max_tokens=12288, max_num_seqs=1,
+                                                                 max_step_tokens=2048, max_model_len=16384))
+        runner = llm.runner
+        rt = runtime()
+        cm = rt.CacheManager(runner.layout.runtime_groups(rt, 16, 12288 // 16), 1)
+        cm.open(0)
+        got, pos = [], 0
+        steps = [2048] * (n_prompt // 2048) + [n_prompt % 2048] + [1] * n_decode
+        for n in steps:
+            assert cm.reserve(0, pos + n)
+            out = runner.step([StepEntry(cm.slot(0), pos, tokens[pos:pos + n], [cm.block_table(0, 0)], [n - 1])])
+            got.append(out.float().cpu().clone())
+            pos += n
+            cm.commit(0, pos)
+        rows[dtype] = torch.cat(got)
+        if dtype == "bfloat16":
+            assert runner.graph_replays >= n_decode
+        del llm, runner
+        torch.cuda.empty_cache()
+    ref, got = rows["float32"], rows["bfloat16"]
+    err = ((got - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)).max().item()
+    assert err < 3e-2, err
