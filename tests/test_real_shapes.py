@@ -142,3 +142,55 @@ def test_long_context_decoding_at_8b_layer_sizes():
     ref, got = rows["float32"], rows["bfloat16"]
     err = ((got - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)).max().item()
     assert err < 3e-2, err
+
+
+def test_single_tokens_beside_portions_at_8b_layer_sizes():
+    """Twelve requests decoding beside the prompt portions of newcomers, the kind of step that is captured with slots
+    for single tokens and for portions, in bfloat16 against the true-32-bit engine."""
+    from vllm_cpp_b200 import LLM, EngineConfig, Qwen3Config
+    from vllm_cpp_b200.engine.step import StepEntry
+    from vllm_cpp_b200.runtime import runtime
+    cfg = Qwen3Config(vocab_size=32000, hidden_size=4096, intermediate_size=12288, num_hidden_layers=2,
+                      num_attention_heads=32, num_key_value_heads=8, head_dim=128, max_position_embeddings=4096,
+                      rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+    rng = np.random.default_rng(4)
+    lengths = [int(n) for n in rng.integers(40, 700, 12)] + [190, 130]
+    tokens = [rng.integers(0, cfg.vocab_size, n + 8).tolist() for n in lengths]
+    rows = {}
+    for dtype in ("float32", "bfloat16"):
+        llm = LLM(config=cfg, random_seed=3, engine=EngineConfig(dtype=dtype, page_size=16, max_tokens=8192, max_num_seqs=14,
+                                                                 max_step_tokens=1024))
+        runner = llm.runner
+        rt = runtime()
+        cm = rt.CacheManager(runner.layout.runtime_groups(rt, 16, 512), 14)
+        pos = [0] * 14
+        for r in range(14):
+            cm.open(r)
+
+        def entry(r, n):
+            assert cm.reserve(r, pos[r] + n)
+            e = StepEntry(cm.slot(r), pos[r], tokens[r][pos[r]:pos[r] + n], [cm.block_table(r, 0)], [n - 1])
+            pos[r] += n
+            return e
+
+        def run(entries):
+            out = runner.step(entries).float().cpu().clone()
+            for r in range(14):
+                cm.commit(r, pos[r])
+            return out
+
+        got = [run([entry(r, lengths[r])]) for r in range(12)]                    # the twelve prompts, one at a time
+        got.append(run([entry(r, 1) for r in range(12)] + [entry(12, 100)]))          # single tokens beside one portion
+        got.append(run([entry(r, 1) for r in range(12)] + [entry(12, 90), entry(13, 70)]))   # beside two
+        got.append(run([entry(r, 1) for r in range(5)] + [entry(13, 60)]))            # fewer single tokens: a smaller step
+        got.append(run([entry(r, 1) for r in range(14)]))                             # all fourteen decode
+        rows[dtype] = torch.cat(got)
+        if dtype == "bfloat16":
+            # two captured kinds of mixed step served the three: 32 single-token slots in 192 rows (twice), 8 in 96
+            assert sorted(k[1:3] for k in runner._graphs if k[0] == "mixed") == [(8, 96), (32, 192)]
+        del llm, runner
+        torch.cuda.empty_cache()
+    ref, got = rows["float32"], rows["bfloat16"]
+    err = ((got - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)).max().item()
+    assert err < 3e-2, err
+    assert (got.argmax(dim=1) == ref.argmax(dim=1)).float().mean().item() >= 0.8
