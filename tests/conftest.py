@@ -29,7 +29,7 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
-# Two tiny configurations that differ in every size and option.
+# Tiny configurations that differ in every size and option.
 TINY = {
     # 2 layers, tied head, no window, page 4
     "A": dict(vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
@@ -45,9 +45,14 @@ TINY = {
     "C": dict(vocab_size=320, hidden_size=128, intermediate_size=176, num_hidden_layers=2, num_attention_heads=4,
               num_key_value_heads=1, head_dim=64, max_position_embeddings=256, rms_norm_eps=1e-6, rope_theta=5e4,
               tie_word_embeddings=False, sliding_window=40, layer_types=("sliding_attention", "full_attention")),
+    # head_dim 128, the serving models' head size (its own norm-rotate-store kernel, 128-lane attention tiles),
+    # two query heads a KV head, an intermediate size that is no multiple of 64
+    "D": dict(vocab_size=512, hidden_size=256, intermediate_size=344, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=128, max_position_embeddings=512, rms_norm_eps=1e-6, rope_theta=1e6,
+              tie_word_embeddings=False),
 }
-TINY_SEED = {"A": 0, "B": 2, "C": 4}
-TINY_PAGE = {"A": 4, "B": 8, "C": 16}
+TINY_SEED = {"A": 0, "B": 2, "C": 4, "D": 6}
+TINY_PAGE = {"A": 4, "B": 8, "C": 16, "D": 16}
 
 
 def tiny_config(name):

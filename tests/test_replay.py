@@ -10,7 +10,7 @@ from conftest import TINY, TINY_PAGE, random_tokens
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [40, 75, 128, 33, 90, 64, 17, 2], "B": [1, 7, 33, 64, 150, 256, 97, 130],
-           "C": [200, 65, 256, 3, 129, 64, 48, 100]}
+           "C": [200, 65, 256, 3, 129, 64, 48, 100], "D": [300, 64, 17, 500, 129, 33, 256, 2]}
 # largest |difference| allowed, as a fraction of the largest |logit| of the reference row set
 REL_TOL = {"float32": 2e-5, "bfloat16": 3e-2}
 
@@ -53,6 +53,18 @@ def test_replay(name, dtype, mode, model_dirs, plain_logits, tmp_path):
                       extra_args=["--poison"] if mode.endswith("_last") else [])
     worst = compare(name, dtype, trace, out, requests, plain_logits)
     print(f"{name} {dtype} {mode}: worst relative error {worst:.3e}, pool {trace.max_tokens} tokens, {len(trace.steps)} steps")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "mixed_last"])
+def test_replay_head_dim_128(dtype, mode, model_dirs, plain_logits, tmp_path):
+    """Configuration D (heads of 128 lanes, as the serving models have them) through the same replays."""
+    requests = make_requests("D")
+    trace = {"whole": R.whole, "tail": R.tail_one_by_one, "mixed_last": R.mixed_last}[mode](requests)
+    out = R.run_trace(model_dirs["D"], dtype, trace, tmp_path / "out", TINY_PAGE["D"],
+                      extra_args=["--poison"] if mode.endswith("_last") else [])
+    worst = compare("D", dtype, trace, out, requests, plain_logits)
+    print(f"D {dtype} {mode}: worst relative error {worst:.3e}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
