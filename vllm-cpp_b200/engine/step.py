@@ -397,6 +397,28 @@ class ModelRunner:
             old, _ = self._graphs.popitem(last=False)   # its buffers go back to the allocator with the graph
             self.launches_per_graph.pop(old, None)
 
+    def _replay(self, key, host, facts, nbytes):
+        """Copies a filled step buffer to the device and replays the captured step of ``key``; returns its result."""
+        graph, ctx, result, pinned = self._graph(key)
+        ctx.__dict__.update(facts)
+        pinned.copy_(torch.from_numpy(host))
+        ctx.buffer.copy_(pinned, non_blocking=True)
+        self.last_ctx, self.last_h2d_bytes = ctx, nbytes
+        graph.replay()
+        self.graph_replays += 1
+        ops.launch_count += self.launches_per_graph[key]
+        return result
+
+    def _fill_padded(self, key, entries, updates, user):
+        """_fill into the layout of the captured step of ``key``, with the caller's integers."""
+        lay = self._graphs[key][1].meta_layout
+        if user is not None and len(user) > lay.X:
+            raise ValueError(f"a captured step carries at most {lay.X} user integers, {len(user)} given")
+        host, facts = self._fill(lay, entries, updates)
+        if user is not None:
+            host[lay.offsets["user"][0]:lay.offsets["user"][0] + len(user)] = user
+        return host, facts
+
     def _step_graph(self, entries, updates, bucket, user=None, post=None, post_key=None):
         # one captured step per padded batch size and context class: the attention part slices the key ranges of
         # short contexts differently from long ones, and a captured step cannot ask how long they are
@@ -405,18 +427,11 @@ class ModelRunner:
         key = (bucket, post_key if post is not None else None, ctx_bound)
         if key not in self._graphs:
             self._capture(key, post)
-        graph, ctx, result, pinned = self._graph(key)
-        if user is not None and len(user) > ctx.meta_layout.X:
-            raise ValueError(f"a captured step carries at most {ctx.meta_layout.X} user integers, {len(user)} given")
-        host, facts = self._fill_decode(ctx.meta_layout, entries, updates, user)
-        ctx.__dict__.update(facts)
-        pinned.copy_(torch.from_numpy(host))
-        ctx.buffer.copy_(pinned, non_blocking=True)
-        self.last_ctx, self.last_h2d_bytes = ctx, host.nbytes
-        graph.replay()
-        self.graph_replays += 1
-        ops.launch_count += self.launches_per_graph[key]
-        return result[:len(entries)]
+        lay = self._graphs[key][1].meta_layout
+        if user is not None and len(user) > lay.X:
+            raise ValueError(f"a captured step carries at most {lay.X} user integers, {len(user)} given")
+        host, facts = self._fill_decode(lay, entries, updates, user)
+        return self._replay(key, host, facts, host.nbytes)[:len(entries)]
 
     def _step_portion_graph(self, entries, updates, portion, n_rows, user=None, post=None, post_key=None):
         """One prompt portion through a captured step of ``portion`` token rows: the tokens beyond the entry's own
@@ -424,21 +439,8 @@ class ModelRunner:
         key = ("portion", portion, n_rows, post_key if post is not None else None)
         if key not in self._graphs:
             self._capture_portion(key, post)
-        graph, ctx, result, pinned = self._graph(key)
-        lay = ctx.meta_layout
-        if user is not None and len(user) > lay.X:
-            raise ValueError(f"a captured step carries at most {lay.X} user integers, {len(user)} given")
-        host, facts = self._fill(lay, entries, updates)
-        if user is not None:
-            host[lay.offsets["user"][0]:lay.offsets["user"][0] + len(user)] = user
-        ctx.__dict__.update(facts)
-        pinned.copy_(torch.from_numpy(host))
-        ctx.buffer.copy_(pinned, non_blocking=True)
-        self.last_ctx, self.last_h2d_bytes = ctx, host.nbytes
-        graph.replay()
-        self.graph_replays += 1
-        ops.launch_count += self.launches_per_graph[key]
-        return result
+        host, facts = self._fill_padded(key, entries, updates, user)
+        return self._replay(key, host, facts, host.nbytes)
 
     def _step_mixed_graph(self, entries, updates, mixed, n_rows, user=None, post=None, post_key=None):
         """Single tokens beside prompt portions through a captured step: the single-token entries fill the first
@@ -450,33 +452,16 @@ class ModelRunner:
         key = ("mixed", singles, rows, post_key if post is not None else None, ctx_bound)
         if key not in self._graphs:
             self._capture_mixed(key, post)
-        graph, ctx, result, pinned = self._graph(key)
-        lay = ctx.meta_layout
-        if user is not None and len(user) > lay.X:
-            raise ValueError(f"a captured step carries at most {lay.X} user integers, {len(user)} given")
         empty = StepEntry(0, 0, [], [[] for _ in self.tables], [])
         slotted = entries[:n_single] + [empty] * (singles - n_single) + entries[n_single:]
-        host, facts = self._fill(lay, slotted, updates)
-        if user is not None:
-            host[lay.offsets["user"][0]:lay.offsets["user"][0] + len(user)] = user
-        ctx.__dict__.update(facts)
-        pinned.copy_(torch.from_numpy(host))
-        ctx.buffer.copy_(pinned, non_blocking=True)
-        self.last_ctx, self.last_h2d_bytes = ctx, host.nbytes
-        graph.replay()
-        self.graph_replays += 1
-        ops.launch_count += self.launches_per_graph[key]
+        host, facts = self._fill_padded(key, slotted, updates, user)
+        result = self._replay(key, host, facts, host.nbytes)
         return None if result is None else result[:n_rows]
 
-    def _capture_mixed(self, key, post=None):
-        """Captures the forward pass of ``singles`` one-token entries and MIXED_PORTIONS portions in ``rows`` token
-        rows together (and what ``post`` adds), on empty entries.  The attention part lays out work items for every
-        slot: sliced key ranges for the single tokens, query tiles over all the remaining rows for each portion; at
-        replay the kernels leave out empty slots and cut the portions' items down to the tokens that are there."""
-        _, singles, T, _, ctx_bound = key
-        E = R = singles + self.MIXED_PORTIONS
-        tokens = T - singles
-        lay = MetaLayout(T, E, R, self._mixed_updates(singles, T), len(self.tables), 8 * R + T)
+    def _capture_graph(self, key, lay, host_facts, post, ctx_bound=None, logit_rows=None):
+        """Captures the forward pass (and what ``post`` adds) over a static step buffer of layout ``lay``.  The
+        capture itself runs on empty entries (length 0), which store nothing and attend to nothing; ``host_facts``
+        are the entry lengths that the attention part lays its work items out for."""
         dev = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
         pinned = torch.zeros(lay.size, dtype=torch.int32).pin_memory()
         ctx = StepContext(self, lay, dev, static=True)
@@ -485,81 +470,10 @@ class ModelRunner:
         o = lay.offsets
         for g in range(len(self.tables)):
             host[o[f"slot_map{g}"][0]:o[f"slot_map{g}"][1]] = -1
+        if logit_rows is not None:
+            host[o["logit_rows"][0]:o["logit_rows"][1]] = logit_rows
         dev.copy_(torch.from_numpy(host))
-        ctx.host_q_len = [1] * singles + [tokens] * self.MIXED_PORTIONS
-        ctx.host_q_start = list(range(singles)) + [singles] * self.MIXED_PORTIONS
-        ctx.host_ctx_len = [0] * singles + [tokens] * self.MIXED_PORTIONS
-        ctx.host_slots = [0] * E
-
-        def run():
-            self._apply_table_updates(ctx)
-            logits = self.model.forward(ctx, self.cache.views)
-            return post(ctx, logits) if post is not None else logits
-
-        side = torch.cuda.Stream(device=self.device)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            run()
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        before = ops.launch_count
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            result = run()
-        self.launches_per_graph[key] = ops.launch_count - before
-        self._keep_graph(key, (graph, ctx, result, pinned))
-
-    def _capture_portion(self, key, post=None):
-        """Captures the forward pass of one entry of ``portion`` tokens (and what ``post`` adds), on an entry of
-        length 0.  The attention part lays its work items out for all ``portion`` tokens; at replay the kernels cut
-        them down to the tokens that are there."""
-        _, portion, n_rows, _ = key
-        lay = MetaLayout(portion, 1, n_rows, self._portion_updates(portion), len(self.tables), 8 * max(n_rows, 1) + portion)
-        dev = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
-        pinned = torch.zeros(lay.size, dtype=torch.int32).pin_memory()
-        ctx = StepContext(self, lay, dev, static=True)
-        host = np.zeros(lay.size, dtype=np.int32)
-        o = lay.offsets
-        for g in range(len(self.tables)):
-            host[o[f"slot_map{g}"][0]:o[f"slot_map{g}"][1]] = -1
-        dev.copy_(torch.from_numpy(host))
-        ctx.host_q_len, ctx.host_q_start, ctx.host_ctx_len, ctx.host_slots = [portion], [0], [portion], [0]
-
-        def run():
-            self._apply_table_updates(ctx)
-            logits = self.model.forward(ctx, self.cache.views)
-            return post(ctx, logits) if post is not None else logits
-
-        side = torch.cuda.Stream(device=self.device)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            run()
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        before = ops.launch_count
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            result = run()
-        self.launches_per_graph[key] = ops.launch_count - before
-        self._keep_graph(key, (graph, ctx, result, pinned))
-
-    def _capture(self, key, post=None):
-        """Captures the forward pass of ``bucket`` single-token entries (and what ``post`` adds).  The capture
-        itself runs on empty entries (length 0), which store nothing and attend to nothing."""
-        bucket = key[0]
-        lay = MetaLayout(bucket, bucket, bucket, bucket, len(self.tables), bucket * self.USER_INTS_PER_ENTRY)
-        dev = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
-        pinned = torch.zeros(lay.size, dtype=torch.int32).pin_memory()
-        ctx = StepContext(self, lay, dev, static=True)
-        ctx.static_max_ctx = key[2]
-        host = np.zeros(lay.size, dtype=np.int32)
-        o = lay.offsets
-        for g in range(len(self.tables)):
-            host[o[f"slot_map{g}"][0]:o[f"slot_map{g}"][1]] = -1
-        host[o["logit_rows"][0]:o["logit_rows"][1]] = np.arange(bucket)
-        dev.copy_(torch.from_numpy(host))
-        ctx.host_q_len, ctx.host_q_start = [1] * bucket, list(range(bucket))
-        ctx.host_ctx_len, ctx.host_slots = [0] * bucket, [0] * bucket
+        ctx.host_q_len, ctx.host_q_start, ctx.host_ctx_len, ctx.host_slots = host_facts
 
         def run():
             self._apply_table_updates(ctx)
@@ -579,3 +493,30 @@ class ModelRunner:
             result = run()
         self.launches_per_graph[key] = ops.launch_count - before
         self._keep_graph(key, (graph, ctx, result, pinned))
+
+    def _capture_mixed(self, key, post=None):
+        """``singles`` one-token entries and MIXED_PORTIONS portions in ``rows`` token rows together.  The attention
+        part lays out work items for every slot: sliced key ranges for the single tokens, query tiles over all the
+        remaining rows for each portion; at replay the kernels leave out empty slots and cut the portions' items
+        down to the tokens that are there."""
+        _, singles, T, _, ctx_bound = key
+        P = self.MIXED_PORTIONS
+        E = R = singles + P
+        tokens = T - singles
+        lay = MetaLayout(T, E, R, self._mixed_updates(singles, T), len(self.tables), 8 * R + T)
+        facts = ([1] * singles + [tokens] * P, list(range(singles)) + [singles] * P, [0] * singles + [tokens] * P, [0] * E)
+        self._capture_graph(key, lay, facts, post, ctx_bound)
+
+    def _capture_portion(self, key, post=None):
+        """One entry of ``portion`` tokens.  The attention part lays its work items out for all ``portion`` tokens;
+        at replay the kernels cut them down to the tokens that are there."""
+        _, portion, n_rows, _ = key
+        lay = MetaLayout(portion, 1, n_rows, self._portion_updates(portion), len(self.tables), 8 * max(n_rows, 1) + portion)
+        self._capture_graph(key, lay, ([portion], [0], [portion], [0]), post)
+
+    def _capture(self, key, post=None):
+        """``bucket`` single-token entries, each with logits wanted."""
+        bucket = key[0]
+        lay = MetaLayout(bucket, bucket, bucket, bucket, len(self.tables), bucket * self.USER_INTS_PER_ENTRY)
+        facts = ([1] * bucket, list(range(bucket)), [0] * bucket, [0] * bucket)
+        self._capture_graph(key, lay, facts, post, key[2], logit_rows=np.arange(bucket))
