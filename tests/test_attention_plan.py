@@ -1,0 +1,61 @@
+"""The work items the attention part lays out for a step (host-side decisions; no GPU needed)."""
+import types
+
+import torch
+
+from vllm_cpp_b200.parts import attention as A
+
+
+def ctx(q_lens, ctx_lens, static=False, bound=None):
+    c = types.SimpleNamespace(device=torch.device("cpu"), host_q_len=list(q_lens), host_ctx_len=list(ctx_lens), static=static)
+    starts, s = [], 0
+    for n in q_lens:
+        starts.append(s)
+        s += n
+    c.host_q_start = starts
+    if static:
+        c.static_max_ctx = bound
+    return c
+
+
+def test_single_tokens_get_key_slices_that_fill_the_sms():
+    # one request, 4,096 keys: short contexts are cut into at most SHORT_SLICES slices
+    p = A.AttentionPlan(ctx([1], [4096]), 32, 8, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+    assert p.n_dec == 1 and p.nslices == A.SHORT_SLICES and p.n_span_items == 0
+    assert p.dec_items.shape == (p.nslices, 6)
+    assert p.dec_items[:, 3].tolist() == list(range(p.nslices)) and set(p.dec_items[:, 4].tolist()) == {p.nslices}
+    # a long context: as many slices as keep one wave of blocks resident, 128 keys a slice at least
+    p = A.AttentionPlan(ctx([1], [32768]), 32, 8, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+    assert p.nslices == A.TARGET_BLOCKS // 8
+    # sixty-four requests: one block per request and KV head already fills the SMs
+    p = A.AttentionPlan(ctx([1] * 64, [4096] * 64), 32, 8, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+    assert p.nslices == 1 and p.dec_rows.tolist() == list(range(64))
+    # very short contexts are not cut below 128 keys a slice
+    p = A.AttentionPlan(ctx([1], [200]), 32, 8, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+    assert p.nslices == 1
+
+
+def test_a_captured_step_slices_for_its_context_class():
+    short = A.AttentionPlan(ctx([1] * 8, [0] * 8, static=True, bound=8192), 32, 8, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+    long = A.AttentionPlan(ctx([1] * 8, [0] * 8, static=True, bound=None), 32, 8, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+    assert short.nslices == min(A.SHORT_SLICES, A.TARGET_BLOCKS // 64) and long.nslices == A.TARGET_BLOCKS // 64
+    assert short.slice_counters.numel() == 8 * 8 and int(short.slice_counters.abs().sum()) == 0
+
+
+def test_portions_are_cut_into_query_tiles_longest_first():
+    # 4 query heads a KV head: 32 tokens fill the 128 rows of a tile
+    p = A.AttentionPlan(ctx([100, 1, 40], [1000, 500, 40]), 32, 8, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+    assert p.n_dec == 1 and p.dec_rows.tolist() == [100]
+    items = p.span_items.tolist()
+    assert p.n_span_items == len(items) == 4 + 2
+    covered = {0: [], 2: []}
+    for e, q0, nq, s, ns, _ in items:
+        assert (s, ns) == (0, 1) and nq <= 32
+        covered[e] += list(range(q0, q0 + nq))
+    assert sorted(covered[0]) == list(range(100)) and sorted(covered[2]) == list(range(40))
+    # the item that reads the most keys comes first
+    reach = [({0: 1000, 2: 40}[e] - {0: 100, 2: 40}[e]) + q0 + nq for e, q0, nq, *_ in items]
+    assert reach == sorted(reach, reverse=True)
+    # seven query heads a KV head: 18 tokens a tile (126 rows)
+    p = A.AttentionPlan(ctx([40], [40]), 14, 2, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+    assert sorted(i[2] for i in p.span_items.tolist()) == [4, 18, 18]
