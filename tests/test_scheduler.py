@@ -163,3 +163,61 @@ def test_window_group_lets_long_requests_fit_a_small_pool():
     run(s)
     assert len(s.request(a).generated) == 50
     assert s.cache().free_pages(0) == 40 and s.cache().free_pages(1) == 40
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_workloads_keep_every_promise(seed):
+    """Random arrivals, lengths, pools, budgets and windows: every step stays under the token budget and the slot
+    limit, a request's tokens arrive in order without gaps, a preempted request starts again from position 0 and is
+    fed its prompt and what it had generated, every request ends with exactly the tokens it was promised, and the
+    pool is whole again at the end."""
+    import random
+    rnd = random.Random(seed)
+    page = rnd.choice([2, 4, 8])
+    window = rnd.choice([0, 0, 6, 16])
+    num_pages, seqs, budget = rnd.randint(12, 40), rnd.randint(2, 5), rnd.randint(4, 24)
+    max_len = page * num_pages
+    rt, s = make(num_pages=num_pages, page=page, seqs=seqs, budget=budget, max_len=max_len, window=window)
+    pending = []
+    for _ in range(rnd.randint(8, 20)):
+        n_prompt = rnd.randint(1, max(1, max_len // 3))
+        pending.append((list(rnd.randrange(100) for _ in range(n_prompt)), rnd.randint(1, max(1, max_len // 4))))
+    want, fed, next_pos, preemptions = {}, {}, {}, 0
+    for step in range(5000):
+        if pending and rnd.random() < 0.4:
+            prompt, max_new = pending.pop()
+            try:
+                rid = s.submit(prompt, max_new, greedy(rt), [])
+                want[rid] = (prompt, max_new)
+                fed[rid], next_pos[rid] = [], 0
+            except Exception as e:      # a request that an empty pool could not hold is refused, and says so
+                assert "pool" in str(e) or "length" in str(e) or "positions" in str(e), e
+        if not s.has_unfinished():
+            if not pending:
+                break
+            continue
+        out = s.schedule()
+        preemptions += len(out.preempted)
+        for rid in out.preempted:
+            fed[rid], next_pos[rid] = [], 0                      # recomputed from its first token
+        assert sum(len(e.tokens) for e in out.entries) <= budget
+        assert len({e.request for e in out.entries}) == len(out.entries) <= seqs
+        assert len({e.slot for e in out.entries}) == len(out.entries)
+        for e in out.entries:
+            assert e.start_pos == next_pos[e.request] and len(e.tokens) >= 1
+            fed[e.request] += list(e.tokens)
+            next_pos[e.request] += len(e.tokens)
+            prompt, _ = want[e.request]
+            so_far = prompt + list(s.request(e.request).generated)
+            assert fed[e.request] == so_far[:len(fed[e.request])]          # prompt, then what was generated, in order
+            assert e.sample == (next_pos[e.request] == len(so_far))         # logits are wanted at the sequence's end only
+        s.update([1000 + e.gen_step for e in out.entries if e.sample])
+        s.cache().check_invariants()
+    assert not s.has_unfinished() and not pending
+    for rid, (prompt, max_new) in want.items():
+        r = s.request(rid)
+        room = max_len - len(prompt)
+        assert r.state == rt.RequestState.FINISHED
+        assert list(r.generated) == [1000 + i for i in range(min(max_new, room))], (rid, r.finish_reason)
+    c = s.cache()
+    assert c.free_slots() == seqs and all(c.free_pages(g) == num_pages for g in range(c.num_groups()))
