@@ -29,31 +29,42 @@ import torch
 _ST_DTYPES = {"F32": (np.float32, 4), "F16": (np.float16, 2), "BF16": (np.uint16, 2), "I32": (np.int32, 4)}
 
 
-def read_safetensors(path) -> dict[str, torch.Tensor]:
+def read_safetensors(path, max_rows=None) -> dict[str, torch.Tensor]:
     """File layout as src/model.cpp:169-219 reads it: 8-byte little-endian header
     length, JSON header {name: {dtype, shape, data_offsets}}, then raw data;
-    bf16 widened as src/model.cpp:262-275 does (bits << 16)."""
-    raw = Path(path).read_bytes()
-    (hlen,) = struct.unpack("<Q", raw[:8])
-    header = json.loads(raw[8 : 8 + hlen])
+    bf16 widened as src/model.cpp:262-275 does (bits << 16).
+    ``max_rows`` {tensor name: n} keeps only the first n rows of those tensors (a
+    vocabulary too large to hold in 64-bit; the rest of the file is not read)."""
+    path = Path(path)
+    with open(path, "rb") as f:
+        (hlen,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(hlen))
     base = 8 + hlen
+    raw = np.memmap(path, dtype=np.uint8, mode="r")
     out = {}
     for name, meta in header.items():
         if name == "__metadata__":
             continue
-        npdt, _ = _ST_DTYPES[meta["dtype"]]
+        npdt, size = _ST_DTYPES[meta["dtype"]]
         b, e = meta["data_offsets"]
-        arr = np.frombuffer(raw[base + b : base + e], dtype=npdt).reshape(meta["shape"])
+        shape = list(meta["shape"])
+        if max_rows and name in max_rows and shape and shape[0] > max_rows[name]:
+            shape[0] = max_rows[name]
+            e = b + int(np.prod(shape)) * size
+        arr = np.frombuffer(raw[base + b : base + e], dtype=npdt).reshape(shape)
         if meta["dtype"] == "BF16":
             arr = (arr.astype(np.uint32) << 16).view(np.float32)
         out[name] = torch.from_numpy(np.array(arr, dtype=np.float64 if arr.dtype != np.int32 else np.int32))
     return out
 
 
-def read_model(model_dir):
+def read_model(model_dir, vocab_rows=None):
+    """``vocab_rows``: keep only that many rows of the embedding table and the LM head (token ids and logits
+    below that number are then all the oracle can speak about)."""
     model_dir = Path(model_dir)
     cfg = json.loads((model_dir / "config.json").read_text())
-    weights = read_safetensors(model_dir / "model.safetensors")
+    limit = {"model.embed_tokens.weight": vocab_rows, "lm_head.weight": vocab_rows} if vocab_rows else None
+    weights = read_safetensors(model_dir / "model.safetensors", limit)
     return cfg, weights
 
 

@@ -26,7 +26,7 @@ def test_single_tokens_get_key_slices_that_fill_the_sms():
     assert p.dec_items[:, 3].tolist() == list(range(p.nslices)) and set(p.dec_items[:, 4].tolist()) == {p.nslices}
     # a long context: as many slices as keep one wave of blocks resident, 128 keys a slice at least
     p = A.AttentionPlan(ctx([1], [32768]), 32, 8, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
-    assert p.nslices == A.TARGET_BLOCKS // 8
+    assert p.nslices == (A.BLOCKS_PER_SM * 148) // 8
     # sixty-four requests: one block per request and KV head already fills the SMs
     p = A.AttentionPlan(ctx([1] * 64, [4096] * 64), 32, 8, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
     assert p.nslices == 1 and p.dec_rows.tolist() == list(range(64))
@@ -38,7 +38,7 @@ def test_single_tokens_get_key_slices_that_fill_the_sms():
 def test_a_captured_step_slices_for_its_context_class():
     short = A.AttentionPlan(ctx([1] * 8, [0] * 8, static=True, bound=8192), 32, 8, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
     long = A.AttentionPlan(ctx([1] * 8, [0] * 8, static=True, bound=None), 32, 8, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
-    assert short.nslices == min(A.SHORT_SLICES, A.TARGET_BLOCKS // 64) and long.nslices == A.TARGET_BLOCKS // 64
+    assert short.nslices == min(A.SHORT_SLICES, (A.BLOCKS_PER_SM * 148) // 64) and long.nslices == (A.BLOCKS_PER_SM * 148) // 64
     assert short.slice_counters.numel() == 8 * 8 and int(short.slice_counters.abs().sum()) == 0
 
 

@@ -179,3 +179,80 @@ def test_sizes_that_fit_no_fast_path(tmp_path, plain_models):
     llm = LLM(d, engine=EngineConfig(dtype="bfloat16", page_size=8, max_tokens=512, max_num_seqs=4, max_step_tokens=16))
     got = llm.generate(prompts, 10, 0.0, 1.0, repeat_penalty=1.0)
     assert sum(a == b for g, w in zip(got, want) for a, b in zip(g, w)) >= 24
+
+
+def test_host_running_ahead_of_the_gpu_does_not_mix_up_steps(model_dirs, plain_models):
+    """A prompt cut into many portions samples nothing until its last portion, so nothing makes the host wait for
+    the GPU between those steps: with the GPU held back (a bounded sleep kernel in front of every step) the host
+    fills the buffers of several steps before the first of them has been copied.  Each step must still get its own
+    tokens, positions and cache slots."""
+    import torch
+    prompts = [random_tokens(384, 150, 91), random_tokens(384, 97, 92)]
+    want = [plain_generate(plain_models, "B", p, 4) for p in prompts]
+    for graphs in (True, False):
+        llm = make_llm(model_dirs["B"], "B", cuda_graphs=graphs, max_step_tokens=16, max_num_seqs=1)
+        inner = llm.runner.step
+
+        def lagging_step(*a, **kw):
+            torch.cuda._sleep(30_000_000)      # some 15 ms during which the host goes on to the next steps
+            return inner(*a, **kw)
+
+        llm.runner.step = lagging_step
+        got = llm.generate(prompts, 4, 0.0, 1.0, repeat_penalty=1.0)
+        assert got == want, f"captured steps {graphs}"
+        if graphs:
+            assert llm.runner.graph_replays >= 150 // 16 + 97 // 16
+
+
+def test_many_live_requests_through_the_large_captured_steps(model_dirs, plain_models):
+    """More than 130 requests decoding at once: the captured steps of 128 and 256 single tokens, and the captured
+    mixed step with 64 single-token slots (forty requests decoding beside a newcomer's prompt), against the plain
+    implementation's greedy tokens, in 32-bit."""
+    first = [random_tokens(256, 3 + i % 7, 300 + i) for i in range(40)]
+    late = [random_tokens(256, 2 + i % 9, 700 + i) for i in range(101)]
+    llm = make_llm(model_dirs["A"], "A", max_tokens=8192, max_num_seqs=256, max_step_tokens=256)
+    out = {}
+
+    def step():
+        o = llm.step()
+        for rid, tok in zip(o.request_ids, o.new_token_ids):
+            out.setdefault(rid, []).append(tok)
+
+    ids = [llm.submit_tokens(p, 20, 0.0, 1.0, repeat_penalty=1.0, ignore_eos=True) for p in first]
+    while llm.scheduler.num_waiting() or len(out) < 40:
+        step()                                    # all forty are decoding now
+    ids.append(llm.submit_tokens(late[0], 9, 0.0, 1.0, repeat_penalty=1.0, ignore_eos=True))
+    step()                                        # forty single tokens beside one portion
+    assert any(k[0] == "mixed" and k[1] == 64 for k in llm.runner._graphs), list(llm.runner._graphs)
+    ids += [llm.submit_tokens(p, 5 + i % 5, 0.0, 1.0, repeat_penalty=1.0, ignore_eos=True) for i, p in enumerate(late[1:])]
+    most = 0
+    while llm.has_requests():
+        most = max(most, llm.scheduler.num_running())
+        step()
+    assert most > 130
+    buckets = {k[0] for k in llm.runner._graphs if not isinstance(k[0], str)}
+    assert {128, 256} <= buckets, buckets
+    new = [20] * 40 + [9] + [5 + i % 5 for i in range(100)]
+    for rid, p, n in zip(ids, first + late, new):
+        assert out[rid] == plain_generate(plain_models, "A", p, n), f"request {rid}"
+
+
+def test_steps_take_their_buffers_from_the_workspace(model_dirs):
+    """Kernel by kernel, a step asks the device allocator for nothing once the scratch memory has its size: fifty
+    mixed steps (portions beside single tokens, requests coming and going), the allocator's count of allocations
+    unchanged from the tenth step on."""
+    import numpy as np
+    import torch
+    llm = make_llm(model_dirs["C"], "C", dtype="bfloat16", cuda_graphs=False, max_tokens=2048, max_num_seqs=6, max_step_tokens=48)
+    rng = np.random.default_rng(5)
+    steps, counts = 0, []
+    pending = [random_tokens(320, int(n), 900 + i) for i, n in enumerate(rng.integers(2, 120, 30))]
+    while steps < 50:
+        if pending and steps % 2 == 0:
+            llm.submit_tokens(pending.pop(), int(rng.integers(4, 30)), seed=steps, ignore_eos=True)
+        llm.step()
+        steps += 1
+        counts.append(torch.cuda.memory_stats()["allocation.all.allocated"])
+    assert llm.runner.graph_replays == 0
+    assert counts[49] == counts[9], (counts[9], counts[49], llm.runner.workspace.overflows)
+    assert llm.runner.workspace.overflows == 0

@@ -97,6 +97,25 @@ def test_sgemm_tn(M, N, K):
     assert torch.equal(out1[0], out[M - 1])
 
 
+@pytest.mark.parametrize("M,N,K", [(5, 300, 4096), (3, 136, 12288), (7, 200, 17408), (130, 264, 5120)])
+def test_sgemm_tn_at_serving_inner_sizes(M, N, K):
+    """The inner sizes of the 4B, 8B and 14B layer shapes (the 32-bit engine at those sizes is the oracle of the
+    bfloat16 engine): operands of the scale activations and weights have there, against a 64-bit product."""
+    from vllm_cpp_b200 import ops
+    g = torch.Generator(device=dev()).manual_seed(K)
+    a = torch.randn(M, K, device=dev(), generator=g)
+    b = 0.02 * torch.randn(N, K, device=dev(), generator=g)
+    out = torch.empty(M, N, device=dev())
+    ops.sgemm_tn(a, b, out)
+    want = a.double() @ b.double().T
+    # results of size sqrt(K) * 0.02; 32-bit accumulation in a fixed order errs by about sqrt(K) * 2^-24 of that
+    scale = want.abs().max().item()
+    assert (out.double() - want).abs().max().item() < 2e-6 * scale
+    out1 = torch.empty(1, N, device=dev())
+    ops.sgemm_tn(a[M - 1:M].contiguous(), b, out1)
+    assert torch.equal(out1[0], out[M - 1])
+
+
 def rope_table(hd, theta, n):
     i = torch.arange(hd // 2, dtype=torch.float64)
     ang = torch.arange(n, dtype=torch.float64)[:, None] * theta ** (-2 * i / hd)[None]

@@ -81,3 +81,62 @@ def test_sampling_rules():
     assert np.abs(freq - want).max() < 0.1
     us = [P.uniform(1, 2, i) for i in range(1000)]
     assert 0 < min(us) and max(us) < 1 and abs(np.mean(us) - 0.5) < 0.05
+
+
+def test_half_split_rotation_is_the_interleaved_one_on_permuted_lanes():
+    """The reference's CPU path rotates lanes (2i, 2i+1) (src/model.cpp:983-985) and is what the compiled-reference
+    anchor pins; the model as intended pairs lanes (i, i + head_dim/2) (src/mlx_backend.cpp:411-412).  The two are
+    the same rotation up to the lane permutation 2i -> i, 2i+1 -> i + head_dim/2, so the half-split function
+    inherits the anchored one's angles and signs."""
+    hd = 32
+    cos, sin = P.rope_angles(hd, 1e4, [0, 1, 7, 100])
+    x = torch.randn(4, 3, hd, dtype=torch.float64)
+    perm = torch.cat([torch.arange(0, hd, 2), torch.arange(1, hd, 2)])     # interleaved lane that sits at each half-split lane
+    inter = P.rope_interleaved(x, cos, sin)
+    # put x's half-split lanes where the interleaved function pairs them, rotate, and bring them back
+    y = torch.empty_like(x)
+    y[..., perm] = x
+    back = P.rope_interleaved(y, cos, sin)[..., perm]
+    assert torch.allclose(P.rope_half_split(x, cos, sin), back, atol=1e-15)
+    assert not torch.allclose(P.rope_half_split(x, cos, sin), inter)
+
+
+def test_one_head_by_hand():
+    """A pin that does not come from the same hand as the code: head_dim 4, theta 100, two positions, gains other
+    than one, every number below worked out with pencil and the formulas alone
+    (norm: x * w / sqrt(mean(x^2) + eps), cuda/attention.cu:169-182; angle = pos * theta^(-2i/hd),
+    src/model.cpp:979-982; pairs (i, i + hd/2), src/mlx_backend.cpp:411-412; norm before rotation).
+
+    x = (3, 4, 0, 0), eps = 0: mean(x^2) = 25/4, 1/rms = 2/5, normalised (1.2, 1.6, 0, 0); gains (2, 1, 3, 0.5)
+    give (2.4, 1.6, 0, 0).  At position 1 the angles are 1 * 100^0 = 1 and 1 * 100^(-1/2) = 0.1: lane pair (0, 2)
+    turns by 1 rad, pair (1, 3) by 0.1 rad: (2.4 cos 1, 1.6 cos 0.1, 2.4 sin 1, 1.6 sin 0.1).  At position 0
+    nothing turns."""
+    import math
+    x = torch.tensor([[[3.0, 4.0, 0.0, 0.0]], [[3.0, 4.0, 0.0, 0.0]]], dtype=torch.float64)   # [T=2, heads=1, hd=4]
+    w = torch.tensor([2.0, 1.0, 3.0, 0.5], dtype=torch.float64)
+    n = P.head_rms_norm(x, w, 0.0)
+    assert torch.allclose(n[0, 0], torch.tensor([2.4, 1.6, 0.0, 0.0], dtype=torch.float64), atol=1e-15)
+    cos, sin = P.rope_angles(4, 100.0, [0, 1])
+    assert torch.allclose(cos[1], torch.tensor([math.cos(1.0), math.cos(0.1)], dtype=torch.float64))
+    r = P.rope_half_split(n, cos, sin)
+    assert torch.allclose(r[0, 0], n[0, 0])
+    want = torch.tensor([2.4 * math.cos(1.0), 1.6 * math.cos(0.1), 2.4 * math.sin(1.0), 1.6 * math.sin(0.1)], dtype=torch.float64)
+    assert torch.allclose(r[1, 0], want, atol=1e-15)
+    # a second vector with weight in the upper half, so that the sign of the sine term is pinned as well:
+    # x = (0, 0, 1, 0) at position 1 -> pair (0, 2) = (0, 1) turned by 1 rad = (-sin 1, cos 1)
+    e = torch.tensor([[[0.0, 0.0, 1.0, 0.0]]], dtype=torch.float64)
+    r = P.rope_half_split(e, cos[1:], sin[1:])
+    assert torch.allclose(r[0, 0], torch.tensor([-math.sin(1.0), 0.0, math.cos(1.0), 0.0], dtype=torch.float64), atol=1e-15)
+    # eps enters under the root: x = (1, 1, 1, 1), eps = 3 -> 1 / sqrt(1 + 3) = 1/2
+    one = torch.ones(1, 1, 4, dtype=torch.float64)
+    assert torch.allclose(P.head_rms_norm(one, torch.ones(4, dtype=torch.float64), 3.0), 0.5 * one)
+    # and the whole attention of two positions, scores scaled by 1/sqrt(hd) = 1/2: q = k, |k0| = |k1| = 2 would
+    # need more arithmetic than a pencil likes; take q1 = (2, 0, 0, 0), k0 = (2, 0, 0, 0), k1 = (0, 0, 0, 0):
+    # scores (2, 0), weights e^2/(e^2+1) and 1/(e^2+1); v0 = (1, 0, 0, 0), v1 = (0, 1, 0, 0)
+    q = torch.tensor([[[0.0, 0, 0, 0]], [[2.0, 0, 0, 0]]], dtype=torch.float64)
+    k = torch.tensor([[[2.0, 0, 0, 0]], [[0.0, 0, 0, 0]]], dtype=torch.float64)
+    v = torch.tensor([[[1.0, 0, 0, 0]], [[0.0, 1, 0, 0]]], dtype=torch.float64)
+    a = P.attention(q, k, v)
+    e2 = math.exp(2.0)
+    assert torch.allclose(a[1, 0], torch.tensor([e2 / (e2 + 1), 1 / (e2 + 1), 0, 0], dtype=torch.float64), atol=1e-15)
+    assert torch.allclose(a[0, 0], v[0, 0])     # position 0 sees itself only

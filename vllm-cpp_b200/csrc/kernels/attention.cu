@@ -37,6 +37,9 @@ struct AttnArgs {
     int nh, nkv, hd, page_size, num_pages, window;
     float scale;
     int* status;
+    // bounds of the partial-result buffers, for callers whose buffers have a fixed size (0: not checked): decoded
+    // tokens and key slices that part_o / part_ml were laid out for
+    int part_tokens, part_slices;
 };
 
 template <typename T> struct Vec8;
@@ -76,7 +79,12 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
     const int qlen = a.q_len[e], ctx = a.ctx_len[e];
     // an item of a captured step is laid out for the largest portion the step serves: fewer tokens may be there
     const int nq = min(item[2], qlen - q0);
-    if (qlen <= 0 || ctx <= 0 || nq <= 0) return;
+    if (a.part_tokens > 0 &&
+        (dec_index < 0 || dec_index >= a.part_tokens || slice < 0 || slice >= nslices || nslices != a.part_slices)) {
+        // the item's partial row would lie outside the fixed buffer: report it and touch nothing
+        if (tid == 0) atomicOr(a.status, VCB_STATUS_BAD_ITEM);
+        return;
+    }
 
     const int g = a.nh / a.nkv;
     const int gq_max = g < RMAX ? g : RMAX;
@@ -84,6 +92,16 @@ __global__ __launch_bounds__(TK) void attn_paged_kernel(AttnArgs a) {
     const int kvh = blockIdx.y / hchunks, hc = blockIdx.y % hchunks;
     const int head0 = kvh * g + hc * gq_max;
     const int gq = min(gq_max, g - hc * gq_max);
+    if (qlen <= 0 || ctx <= 0 || nq <= 0) {
+        // an empty entry: its slices still say "nothing here" (max = -inf, sum = 0), so that the merge writes zeros
+        // rather than whatever the partial buffers held before
+        if (nslices > 1 && a.part_ml != nullptr && tid < gq) {
+            const size_t prow = ((size_t)dec_index * a.nh + head0 + tid) * nslices + slice;
+            a.part_ml[prow * 2] = -CUDART_INF_F;
+            a.part_ml[prow * 2 + 1] = 0.f;
+        }
+        return;
+    }
     const int R = nq * gq;  // rows in use: r = iq * gq + ih
 
     const int row0 = a.q_start[e] + q0;       // flat token index of the first query
@@ -312,7 +330,7 @@ VCB_API int vcb_attn_paged(const void* q, void* out, int dtype, const void* page
     VCB_CHECK_ARG(rows_max == 8 || rows_max == 32, "attn_paged: rows_max must be 8 or 32");
     VCB_CHECK_ARG(page_size > 0 && window >= 0, "attn_paged: bad page_size %d or window %d", page_size, window);
     AttnArgs a{q, out, pages, page_stride, block_table, table_row, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml,
-               nh, nkv, hd, page_size, num_pages, window, scale, status};
+               nh, nkv, hd, page_size, num_pages, window, scale, status, 0, 0};
     if (dtype == VCB_F32) return rows_max == 8 ? launch_attn<float, 8>(a, n_items, stream) : launch_attn<float, 32>(a, n_items, stream);
     return rows_max == 8 ? launch_attn<__nv_bfloat16, 8>(a, n_items, stream) : launch_attn<__nv_bfloat16, 32>(a, n_items, stream);
 }
@@ -394,10 +412,15 @@ VCB_API int vcb_attn_decode_no_alloc(const void* q, void* out, int dtype, const 
     if (int rc = partials_address(&scratch)) return rc;
     float* part_o = scratch;               // [rows, hd]
     float* part_ml = scratch + rows * hd;  // [rows, 2]
-    // every slice of every live row writes its partial (an empty slice writes max = -inf, sum = 0), so nothing of
-    // an earlier call's contents is read and nothing has to be cleared
+    // Every (token, head, slice) row is written by the block that owns it before the merge reads it -- an empty
+    // slice and an entry without tokens write max = -inf, sum = 0 -- so nothing of an earlier call's contents is
+    // read and nothing has to be cleared.  The one exception is an item the kernel refuses (see below): its rows
+    // keep what they held, the status word says so, and the output of that token is not to be used.
+    // The kernel checks every item against the layout the array was cut for (n_dec tokens, nslices slices): an item
+    // naming a token or slice beyond it, or another slice count, sets VCB_STATUS_BAD_ITEM and writes nothing.
+    VCB_CHECK_ARG(status != nullptr, "attn_decode_no_alloc: a status word is required (bad items are reported there)");
     AttnArgs a{q, out, pages, page_stride, block_table, table_row, max_blocks, q_start, q_len, ctx_len, items, part_o,
-               part_ml, nh, nkv, hd, page_size, num_pages, window, scale, status};
+               part_ml, nh, nkv, hd, page_size, num_pages, window, scale, status, n_dec, nslices};
     const int rc = dtype == VCB_F32 ? launch_attn<float, 8>(a, n_dec * nslices, stream)
                                     : launch_attn<__nv_bfloat16, 8>(a, n_dec * nslices, stream);
     if (rc) return rc;

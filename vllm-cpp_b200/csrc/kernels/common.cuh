@@ -23,6 +23,7 @@ enum VcbStatus : int {
     VCB_STATUS_WAIT_TIMEOUT = 4,   // a bounded mbarrier wait gave up
     VCB_STATUS_BAD_POSITION = 8,   // position outside the rotary table
     VCB_STATUS_BAD_LAYOUT = 16,    // shared memory did not start on the boundary a kernel's tiles need
+    VCB_STATUS_BAD_ITEM = 32,      // a work item names a partial-result row outside the buffer it was given
 };
 
 void vcb_set_error(const char* fmt, ...);

@@ -22,6 +22,12 @@
 //    overlap on the GPU (different streams without an ordering between them) race on it: order them.
 //  * Arguments as vcb_attn_paged with rows_max 8 (one item per (decoded token, key slice), item[5] = index of
 //    the token among the n_dec), plus dec_rows[n_dec]: the output row of each token, or -1 to skip it.
+//  * An entry without tokens (q_len <= 0 or ctx_len <= 0) gets zeros in its output row; give it dec_rows = -1
+//    if that row must stay as it is.
+//  * Every item must name a token index below n_dec (item[5]), a slice below nslices (item[3]) and the same
+//    slice count as the call (item[4] == nslices).  An item that does not is left out, nothing of the built-in
+//    array is touched for it, bit 32 is set in *status (which must not be null), and the output row of its token
+//    is not valid.
 #pragma once
 #include <cuda_runtime.h>
 

@@ -62,7 +62,8 @@ class LLM:
         store.release()
         self.max_model_len = min(ec.max_model_len or self.model.spec.max_positions, self.model.spec.max_positions)
         self.runner = ModelRunner(self.model, ec.page_size, ec.num_pages, ec.max_num_seqs, dtype, self.device,
-                                  cuda_graphs=ec.cuda_graphs, max_model_len=self.max_model_len)
+                                  cuda_graphs=ec.cuda_graphs, max_model_len=self.max_model_len,
+                                  max_step_tokens=ec.max_step_tokens)
         rt = runtime()
         self.scheduler = rt.Scheduler(self.runner.layout.runtime_groups(rt, ec.page_size, ec.num_pages),
                                       ec.max_num_seqs, ec.max_step_tokens, self.max_model_len)

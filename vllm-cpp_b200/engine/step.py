@@ -29,7 +29,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
-from .. import ops
+from .. import ops, workspace
 from ..cache.device_cache import CacheLayout, DeviceCache
 
 
@@ -53,6 +53,52 @@ class GroupContext:
     upd_idx: torch.Tensor             # int32 [U]  flat indices into block_table
     upd_val: torch.Tensor             # int32 [U]
     upd_capacity: int
+
+
+class StagingRing:
+    """Pinned host buffers for the packed integers of a step, used in turn.
+
+    The copy of a pinned buffer to the device is asynchronous: the host may be several steps ahead of the GPU
+    (a prompt cut into portions samples nothing, so nothing makes the host wait), and a buffer written again
+    before its last copy has run would hand that earlier step the later step's tokens, positions and cache
+    slots.  Each buffer therefore carries an event recorded after its copy, and is written only once that
+    event has passed; with ``DEPTH`` buffers the host waits only when it is that many steps ahead."""
+
+    def __init__(self, size: int, depth: int = 4):
+        self.DEPTH = depth
+        self.size = 0
+        self._buffers: list[torch.Tensor] = []
+        self._events: list = []
+        self._next = 0
+        self.waits = 0          # times the host had to wait for an earlier copy (a measure of how far it runs ahead)
+        self._grow(size)
+
+    def _grow(self, size: int) -> None:
+        for ev in self._events:
+            if ev is not None:
+                ev.synchronize()
+        self.size = size
+        self._buffers = [torch.empty(size, dtype=torch.int32).pin_memory() for _ in range(self.DEPTH)]
+        self._events = [None] * self.DEPTH
+        self._next = 0
+
+    def send(self, host: np.ndarray, dev: torch.Tensor) -> None:
+        """Queues the copy of ``host`` (int32) into the first ``len(host)`` integers of ``dev`` on the current stream."""
+        n = host.shape[0]
+        if n > self.size:
+            self._grow(max(n, 2 * self.size))
+        i = self._next
+        self._next = (i + 1) % self.DEPTH
+        ev = self._events[i]
+        if ev is None:
+            ev = self._events[i] = torch.cuda.Event()
+        elif not ev.query():
+            self.waits += 1
+            ev.synchronize()
+        buf = self._buffers[i][:n]
+        buf.numpy()[:] = host
+        dev[:n].copy_(buf, non_blocking=True)
+        ev.record()
 
 
 class MetaLayout:
@@ -80,6 +126,7 @@ class StepContext:
     def __init__(self, runner, layout: MetaLayout, dev_buffer: torch.Tensor, static: bool):
         self.device = runner.device
         self.status = runner.status
+        self._runner = runner
         self.static = static
         self.meta_layout = layout
         self.T, self.E, self.n_rows = layout.T, layout.E, layout.R
@@ -101,6 +148,16 @@ class StepContext:
         # host-side facts of the current step (refreshed by fill)
         self.entries: list[StepEntry] = []
         self.host_q_len, self.host_q_start, self.host_ctx_len, self.host_slots = [], [], [], []
+
+    def upload(self, host: np.ndarray) -> torch.Tensor:
+        """An int32 array of the host on the device, for this step.  A captured step does this once, at capture;
+        a step that runs kernel by kernel takes the room from the step's workspace and a pinned staging buffer."""
+        host = np.ascontiguousarray(host, dtype=np.int32)
+        if self.static or self._runner is None:
+            return torch.from_numpy(host).to(self.device)
+        dev = workspace.empty(host.shape, torch.int32, self.device)
+        self._runner.staging.send(host.reshape(-1), dev.view(-1))
+        return dev
 
     def plan(self, key, make):
         """Per-step data that several layers share (built by the first one that asks)."""
@@ -124,7 +181,10 @@ class ModelRunner:
     MIXED_TOKENS = (32, 64, 96, 128, 192, 256)
 
     def __init__(self, model, page_size: int, num_pages: int, num_slots: int, dtype: torch.dtype, device,
-                 cuda_graphs: bool = True, max_model_len: int | None = None):
+                 cuda_graphs: bool = True, max_model_len: int | None = None, max_step_tokens: int | None = None):
+        """``max_step_tokens``: the most tokens a step will bring; given, the scratch memory of steps that run
+        kernel by kernel is sized now (by running the model over that many padding rows), so that no later step
+        allocates.  Without it the scratch grows to what the steps need as they come."""
         self.model = model
         self.device = torch.device(device)
         self.dtype = dtype
@@ -144,6 +204,11 @@ class ModelRunner:
         self._graphs: collections.OrderedDict[tuple, tuple] = collections.OrderedDict()   # least recently used first
         self.last_ctx = None
         self.last_h2d_bytes = 0
+        self.workspace = workspace.Workspace(self.device)
+        self.staging = StagingRing(4096, depth=16)     # for steps that run kernel by kernel (a captured step has its own)
+        # (a model with a part that reads host-side facts of a step cannot run over padding: its scratch grows on demand)
+        if max_step_tokens and self.device.type == "cuda" and getattr(model, "capturable", True):
+            self.size_workspace(max_step_tokens)
         self.graph_replays = 0
         self.launches_per_graph: dict[tuple, int] = {}
 
@@ -347,14 +412,36 @@ class ModelRunner:
         host, facts = self._fill(lay, entries, updates)
         if user is not None:
             host[lay.offsets["user"][0]:lay.offsets["user"][0] + len(user)] = user
-        dev = torch.from_numpy(host).pin_memory().to(self.device, non_blocking=True)
-        ctx = StepContext(self, lay, dev, static=False)
-        ctx.__dict__.update(facts)
-        self.last_ctx, self.last_h2d_bytes = ctx, host.nbytes
-        with ops.hold_stream():   # kernel by kernel, the host's time per launch is what a short portion waits for
+        with self.workspace, ops.hold_stream():   # kernel by kernel, the host's time per launch is what a short portion waits for
+            dev = workspace.empty((lay.size,), torch.int32, self.device)
+            self.staging.send(host, dev)
+            ctx = StepContext(self, lay, dev, static=False)
+            ctx.__dict__.update(facts)
+            self.last_ctx, self.last_h2d_bytes = ctx, host.nbytes
             self._apply_table_updates(ctx)
             logits = self.model.forward(ctx, self.cache.views)
             return post(ctx, logits) if post is not None else logits
+
+    def size_workspace(self, max_step_tokens: int) -> None:
+        """Sizes the scratch memory for steps of up to ``max_step_tokens`` tokens: the model runs over padding rows
+        (token 0, stored nowhere, entries of length 0: nothing is read or written in the cache), once per token
+        count at which the parts' buffers are largest -- the budget itself, and the largest counts whose products
+        still write partial sums per k-slice."""
+        sizes = sorted({max_step_tokens, min(max_step_tokens, 1024), min(max_step_tokens, 128)})
+        for T in sizes:
+            lay = MetaLayout(T, 1, 1, 0, len(self.tables), 0)
+            host = np.zeros(lay.size, dtype=np.int32)
+            for g in range(len(self.tables)):
+                host[lay.offsets[f"slot_map{g}"][0]:lay.offsets[f"slot_map{g}"][1]] = -1
+            for _ in range(2):     # the first pass finds the sizes, the second must fit
+                with self.workspace, ops.hold_stream():
+                    dev = workspace.empty((lay.size,), torch.int32, self.device)
+                    self.staging.send(host, dev)
+                    ctx = StepContext(self, lay, dev, static=False)
+                    ctx.entries, ctx.host_q_len, ctx.host_q_start, ctx.host_ctx_len, ctx.host_slots = [], [T], [0], [T], [0]
+                    self.model.forward(ctx, self.cache.views)
+        torch.cuda.current_stream().synchronize()
+        ops.check_status(self.status)
 
     USER_INTS_PER_ENTRY = 12  # room in a captured step's buffer for the caller's numbers
 
@@ -399,10 +486,9 @@ class ModelRunner:
 
     def _replay(self, key, host, facts, nbytes):
         """Copies a filled step buffer to the device and replays the captured step of ``key``; returns its result."""
-        graph, ctx, result, pinned = self._graph(key)
+        graph, ctx, result, staging = self._graph(key)
         ctx.__dict__.update(facts)
-        pinned.copy_(torch.from_numpy(host))
-        ctx.buffer.copy_(pinned, non_blocking=True)
+        staging.send(host, ctx.buffer)
         self.last_ctx, self.last_h2d_bytes = ctx, nbytes
         graph.replay()
         self.graph_replays += 1
@@ -463,7 +549,7 @@ class ModelRunner:
         capture itself runs on empty entries (length 0), which store nothing and attend to nothing; ``host_facts``
         are the entry lengths that the attention part lays its work items out for."""
         dev = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
-        pinned = torch.zeros(lay.size, dtype=torch.int32).pin_memory()
+        staging = StagingRing(lay.size)
         ctx = StepContext(self, lay, dev, static=True)
         ctx.static_max_ctx = ctx_bound
         host = np.zeros(lay.size, dtype=np.int32)
@@ -492,7 +578,7 @@ class ModelRunner:
         with torch.cuda.graph(graph):
             result = run()
         self.launches_per_graph[key] = ops.launch_count - before
-        self._keep_graph(key, (graph, ctx, result, pinned))
+        self._keep_graph(key, (graph, ctx, result, staging))
 
     def _capture_mixed(self, key, post=None):
         """``singles`` one-token entries and MIXED_PORTIONS portions in ``rows`` token rows together.  The attention

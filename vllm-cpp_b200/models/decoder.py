@@ -10,6 +10,7 @@ were asked for (the reference: last position only, src/model.cpp:1255-1263).
 """
 from __future__ import annotations
 
+from .. import workspace
 from ..parts.base import BuildContext, CacheSpec
 from ..parts.embedding import LMHead, TokenEmbedding
 from ..registry import ModelSpec, part_class
@@ -84,9 +85,11 @@ class DecoderModel:
         """ctx: the step's tensors; caches: cache id -> view.  Returns 32-bit logits [rows, vocab]."""
         resid = self.embedding.forward(ctx.token_ids, ctx.T, ctx.status)
         pending = None
-        for run in self.order:
+        for i, run in enumerate(self.order):
             cache = caches[run.cache] if run.cache is not None else None
+            workspace.begin_run(i)      # the run's buffers come from the scratch region that run i - 2 used
             pending = self.layers[run.layer].forward(resid, pending, ctx, cache, run.writes)
+        workspace.end_runs()
         if ctx.n_rows == 0:
             return None
         y = self.final_norm.forward(resid, pending, rows=ctx.logit_rows)

@@ -17,7 +17,8 @@ from .csrc import build as _build
 F32, BF16 = 0, 1
 STATUS_BITS = {1: "token id outside the vocabulary", 2: "page id outside the pool",
                4: "a bounded wait inside a kernel gave up", 8: "position outside the rotary table",
-               16: "shared memory did not start on the boundary a kernel's tiles need"}
+               16: "shared memory did not start on the boundary a kernel's tiles need",
+               32: "a work item names a partial-result row outside the buffer it was given"}
 ITEM_INTS = 6
 
 _lib = None
@@ -79,6 +80,19 @@ def _declare(L):
         fn = getattr(L, name)
         fn.argtypes = args
         fn.restype = c_int
+
+
+_num_sms = None
+
+
+def num_sms() -> int:
+    """Streaming multiprocessors of the current device, asked once (148 on a B200); where there is no device
+    -- the host-side tests of the planning arithmetic -- the B200's count."""
+    global _num_sms
+    if _num_sms is None:
+        _num_sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count \
+            if torch.cuda.is_available() else 148
+    return _num_sms
 
 
 launch_count = 0   # kernels of this library launched so far (every launcher starts exactly one)
@@ -323,11 +337,12 @@ def sample(logits, params, counts, out, no_nucleus=False):
     if counts is not None:
         _need(counts, "counts", torch.int32)
         assert counts.shape[1] == V
-    nb = max(1, min(64, 2 * 148 // max(R, 1), V // 2048))
+    nb = max(1, min(64, 2 * num_sms() // max(R, 1), V // 2048))
     if no_nucleus and nb > 1:
         global launch_count
-        part_v = torch.empty(R * nb, dtype=torch.float32, device=logits.device)
-        part_i = torch.empty(R * nb, dtype=torch.int32, device=logits.device)
+        from . import workspace
+        part_v = workspace.empty((R * nb,), torch.float32, logits.device)
+        part_i = workspace.empty((R * nb,), torch.int32, logits.device)
         _call("vcb_sample_split", _p(logits), logits.stride(0), R, V, _p(params), _p(counts), _p(part_v), _p(part_i),
               nb, _p(out), _stream())
         launch_count += 1   # two kernels

@@ -19,7 +19,7 @@ import os
 import numpy as np
 import torch
 
-from .. import ops
+from .. import ops, workspace
 from ..registry import PartSpec, part_class
 from ..weights.loader import TensorSpec
 from .base import CacheSpec, Mixer
@@ -30,7 +30,7 @@ SPAN_ROWS = 32      # rows of its prompt-portion variant
 MMA_DECODE_ROWS = 16   # the same for the tensor-core kernel
 MMA_SPAN_ROWS = 128
 MAX_SLICES = 64
-TARGET_BLOCKS = 2 * 148   # blocks of the decode kernel that are resident at once (two per SM)
+BLOCKS_PER_SM = 2         # blocks of the decode kernel that are resident at once on one SM
 SHORT_CONTEXT = 8192      # contexts up to here count as short for the slicing of decoded tokens' key ranges
 SHORT_SLICES = 12
 # prompt portions run on the tcgen05 kernel where it takes the sizes; 0 keeps them on the mma.sync kernel (comparison runs)
@@ -43,6 +43,8 @@ class AttentionPlan:
     def __init__(self, ctx, nh: int, nkv: int, decode_rows: int = DECODE_ROWS, span_rows: int = SPAN_ROWS):
         g = nh // nkv
         dev = ctx.device
+        # int32 arrays go to the device with the step's own staging buffers where the step has them
+        upload = getattr(ctx, "upload", None) or (lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev))
         dec = [i for i, n in enumerate(ctx.host_q_len) if n == 1]
         spans = [i for i, n in enumerate(ctx.host_q_len) if n > 1]
         self.n_dec = len(dec)
@@ -62,7 +64,7 @@ class AttentionPlan:
             # as many slices as keep every block resident in one wave; over short contexts no more than
             # SHORT_SLICES, beyond which merging the partial results costs more than the shorter key ranges save
             # (one request at 4,096 keys, 12-layer step: 8 slices 1.437 ms, 12: 1.420, 18: 1.444, 37: 1.495)
-            fit = TARGET_BLOCKS // blocks
+            fit = BLOCKS_PER_SM * ops.num_sms() // blocks
             if longest is not None and longest <= SHORT_CONTEXT:
                 fit = min(fit, SHORT_SLICES)
             self.nslices = int(max(1, min(MAX_SLICES, by_pages, fit)))
@@ -72,10 +74,10 @@ class AttentionPlan:
                 for s in range(self.nslices):
                     items[k] = (e, 0, 1, s, self.nslices, n)
                     k += 1
-            self.dec_items = torch.from_numpy(items).to(dev)
-            self.dec_rows = torch.tensor([ctx.host_q_start[e] for e in dec], dtype=torch.int32).to(dev)
+            self.dec_items = upload(items)
+            self.dec_rows = upload(np.asarray([ctx.host_q_start[e] for e in dec], dtype=np.int32))
             # arrival counters of the key slices (the tensor-core kernel merges in its last-arriving block)
-            self.slice_counters = torch.zeros(len(dec) * nkv * hchunks, dtype=torch.int32, device=dev)
+            self.slice_counters = workspace.zeros((len(dec) * nkv * hchunks,), torch.int32, dev)
         if spans:
             nq_max = max(1, span_rows // min(g, span_rows))
             rows = []
@@ -86,7 +88,7 @@ class AttentionPlan:
             # longest key ranges first: the blocks that run longest start first, the short ones fill the tail
             rows.sort(key=lambda r: -(ctx.host_ctx_len[r[0]] - ctx.host_q_len[r[0]] + r[1] + r[2]))
             self.n_span_items = len(rows)
-            self.span_items = torch.tensor(rows, dtype=torch.int32).to(dev)
+            self.span_items = upload(np.asarray(rows, dtype=np.int32).reshape(-1, ops.ITEM_INTS))
 
 
 class GQAAttention(Mixer):
@@ -147,11 +149,11 @@ class GQAAttention(Mixer):
         nh, nkv, hd = self.nh, self.nkv, self.hd
         group = ctx.groups[cache.group]
         qkv = matmul_tn(x, self.w_qkv, ctx.status, allow_partials=True)
-        q = torch.empty((T, nh * hd), dtype=x.dtype, device=x.device)
+        q = workspace.empty((T, nh * hd), x.dtype, x.device)
         ops.qknorm_rope_kvwrite(qkv, self.q_norm_w, self.k_norm_w, self.eps, self.rope.table, ctx.positions,
                                 group.slot_map, q, cache.pages, nh, nkv, hd, ctx.status,
                                 has_kv=self.has_kv, use_norm=self.qk_norm)
-        out = torch.empty_like(q)
+        out = workspace.empty((T, nh * hd), x.dtype, x.device)
         mma = ops.attn_mma_supported(x.dtype, hd)
         kernel = ops.attn_mma if mma else ops.attn_paged
         dec_rows, span_rows = (MMA_DECODE_ROWS, MMA_SPAN_ROWS) if mma else (DECODE_ROWS, SPAN_ROWS)
@@ -161,8 +163,8 @@ class GQAAttention(Mixer):
             S = plan.nslices
             part_o = part_ml = None
             if S > 1:
-                part_o = torch.empty((plan.n_dec * nh * S, hd), dtype=torch.float32, device=x.device)
-                part_ml = torch.empty((plan.n_dec * nh * S, 2), dtype=torch.float32, device=x.device)
+                part_o = workspace.empty((plan.n_dec * nh * S, hd), torch.float32, x.device)
+                part_ml = workspace.empty((plan.n_dec * nh * S, 2), torch.float32, x.device)
             if mma:
                 ops.attn_mma(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
                              plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml,

@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch
 
-from .. import ops
+from .. import ops, workspace
 from ..weights.loader import TensorSpec
 from .linear import matmul_tn
 
@@ -22,7 +22,7 @@ class TokenEmbedding:
         self.table = store.matrix(self.name)
 
     def forward(self, ids, n_tokens, status):
-        out = torch.empty((n_tokens, self.hidden), dtype=torch.float32, device=ids.device)
+        out = workspace.empty((n_tokens, self.hidden), torch.float32, ids.device)
         ops.embed_gather(self.table, ids, out, status)
         return out
 

@@ -7,21 +7,17 @@ With few tokens the product is a stream of weights from HBM; the inner dimension
 is then cut into slices so that enough blocks are in flight to fill the GPU, each
 slice writes a 32-bit partial sum, and whichever kernel reads the result next adds
 the slices in order.  The reference calls cublasGemmEx for these products
-(cuda/tp_model.cu:259-269); ``VLLM_CPP_B200_LIBRARY_GEMM=1`` swaps a library
-product in for comparison runs.
+(cuda/tp_model.cu:259-269); no library product stands on this path.
 """
 from __future__ import annotations
 
 import functools
-import os
 
 import torch
 
-from .. import ops
+from .. import ops, workspace
 
-NUM_SMS = 148
 MAX_SPLIT_TOKENS = 1024     # above this many tokens a product is never cut into k-slices
-LIBRARY_GEMM = os.environ.get("VLLM_CPP_B200_LIBRARY_GEMM", "0") == "1"
 
 
 def token_tile(T: int) -> int:
@@ -32,11 +28,12 @@ def token_tile(T: int) -> int:
 
 
 @functools.lru_cache(maxsize=4096)
-def choose_splits(M: int, T: int, K: int, max_splits: int = 8) -> int:
+def choose_splits(M: int, T: int, K: int, max_splits: int = 8, num_sms: int | None = None) -> int:
     """Number of k-slices of a product whose units (feature tile x token tile) do not fill the SMs by themselves.
     The kernel's persistent blocks, one per SM, walk (feature tile x token tile x k-slice) units round robin, so
     the slices are chosen to spread the k-blocks evenly over the SMs in whole rounds; each extra slice costs one
     more 32-bit partial sum to write and to add."""
+    NUM_SMS = num_sms or ops.num_sms()
     total_kb = -(-K // 64)
     if T > MAX_SPLIT_TOKENS:
         return 1      # units in plenty: partial sums would only cost traffic
@@ -80,24 +77,22 @@ def matmul_tn(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor | None = No
     if x.dtype == torch.float32:
         if w.dtype != torch.float32:
             raise ops.KernelError("float32 activations need float32 weights")
-        out = torch.empty((T, N), dtype=torch.float32, device=x.device)
+        out = workspace.empty((T, N), torch.float32, x.device)
         ops.sgemm_tn(x, w, out)
         return out
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise ops.KernelError(f"matmul_tn: unsupported operand types {x.dtype} x {w.dtype}")
-    if LIBRARY_GEMM:
-        return torch.mm(x, w.t(), out_dtype=torch.float32) if out_dtype == torch.float32 else torch.mm(x, w.t())
     K = x.shape[1]
     if not ops.gemm_tma_ok(x, w):
         # rows that are not 16-byte multiples (an inner size like 100): the plain kernel takes them
-        out = torch.empty((T, N), dtype=out_dtype, device=x.device)
+        out = workspace.empty((T, N), out_dtype, x.device)
         ops.gemm_bf16_plain(x, w, out)
         return out
     splits = choose_splits(N, T, K) if allow_partials else 1
     splits = ops.gemm_effective_splits(K, splits)
     if splits > 1:
-        out = torch.empty((splits, T, N), dtype=torch.float32, device=x.device)
+        out = workspace.empty((splits, T, N), torch.float32, x.device)
     else:
-        out = torch.empty((T, N), dtype=out_dtype, device=x.device)
+        out = workspace.empty((T, N), out_dtype, x.device)
     ops.gemm_bf16_tn(w, x, out, splits, status)
     return out

@@ -8,10 +8,10 @@ from __future__ import annotations
 
 import torch
 
-from .. import ops
+from .. import ops, workspace
 from ..weights.loader import TensorSpec
 from .base import FeedForward
-from .linear import LIBRARY_GEMM, matmul_tn
+from .linear import matmul_tn
 
 FUSE_ABOVE_TOKENS = 128   # below this the product is cut into k-slices, whose sums must exist before the SiLU
 
@@ -38,8 +38,8 @@ class SwiGLUMLP(FeedForward):
         self.w_down = store.matrix(p + "down_proj.weight")
 
     def forward(self, x, ctx):
-        act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        if x.dtype == torch.bfloat16 and x.shape[0] > FUSE_ABOVE_TOKENS and not LIBRARY_GEMM and ops.gemm_tma_ok(x, self.w_gate_up):
+        act = workspace.empty((x.shape[0], self.inter), x.dtype, x.device)
+        if x.dtype == torch.bfloat16 and x.shape[0] > FUSE_ABOVE_TOKENS and ops.gemm_tma_ok(x, self.w_gate_up):
             # many tokens: no k-slices are needed, so the SiLU-gate runs in the product's epilogue
             ops.gemm_bf16_swiglu(self.w_gate_up, x, act, ctx.status)
         else:

@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch
 
-from .. import ops
+from .. import ops, workspace
 from ..weights.loader import TensorSpec
 from .base import Norm
 
@@ -27,6 +27,6 @@ class RMSNorm(Norm):
 
     def forward(self, resid, delta, rows=None):
         n = resid.shape[0] if rows is None else rows.numel()
-        out = torch.empty((n, self.size), dtype=self.build.compute_dtype, device=resid.device)
+        out = workspace.empty((n, self.size), self.build.compute_dtype, resid.device)
         ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, rows)
         return out

@@ -20,7 +20,7 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
-from .. import ops
+from .. import ops, workspace
 
 
 @dataclass(frozen=True)
@@ -83,7 +83,7 @@ class Sampler:
         """One token per row of ``logits`` from records already on the device (int32 [rows, 8])."""
         if use_counts:
             self._need_counts()
-        out = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
+        out = workspace.empty((logits.shape[0],), torch.int32, self.device)
         ops.sample(logits, params, self.counts if use_counts else None, out, no_nucleus)
         return out
 
