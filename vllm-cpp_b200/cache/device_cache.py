@@ -98,8 +98,8 @@ class DeviceCache:
             return
         for g, t in zip(self.layout.groups, self.tensors):
             if not g.paged:
-                idx = torch.tensor(slots, dtype=torch.long, device=t.device)
-                t.index_fill_(1, idx, 0)
+                for s in slots:     # a fill per slot: no index tensor to allocate
+                    t[:, s].zero_()
 
     def poison(self, value: float = float("nan")) -> None:
         """Fills every page with a value that shows if anything reads what it should not."""

@@ -155,14 +155,17 @@ class StepContext:
         host = np.ascontiguousarray(host, dtype=np.int32)
         if self.static or self._runner is None:
             return torch.from_numpy(host).to(self.device)
-        dev = workspace.empty(host.shape, torch.int32, self.device)
+        with workspace.whole_step():
+            dev = workspace.empty(host.shape, torch.int32, self.device)
         self._runner.staging.send(host.reshape(-1), dev.view(-1))
         return dev
 
     def plan(self, key, make):
-        """Per-step data that several layers share (built by the first one that asks)."""
+        """Per-step data that several layers share (built by the first one that asks; its buffers live as long as
+        the step, not only as long as the layer that happened to build it)."""
         if key not in self._plans:
-            self._plans[key] = make()
+            with workspace.whole_step():
+                self._plans[key] = make()
         return self._plans[key]
 
 
@@ -429,16 +432,24 @@ class ModelRunner:
         still write partial sums per k-slice."""
         sizes = sorted({max_step_tokens, min(max_step_tokens, 1024), min(max_step_tokens, 128)})
         for T in sizes:
-            lay = MetaLayout(T, 1, 1, 0, len(self.tables), 0)
+            # as many single-token entries as there are request slots (their contexts taken as the longest there
+            # can be, which gives their key ranges the most slices), the rest of the rows one portion; logits
+            # wanted of every entry, and room for the integers a sampler sends along
+            S = min(self.num_slots, T)
+            E = S + (1 if T > S else 0)
+            lay = MetaLayout(T, E, E, E + T // self.page_size + 2, len(self.tables), 8 * E + T)
             host = np.zeros(lay.size, dtype=np.int32)
             for g in range(len(self.tables)):
                 host[lay.offsets[f"slot_map{g}"][0]:lay.offsets[f"slot_map{g}"][1]] = -1
+            q_len = [1] * S + ([T - S] if T > S else [])
+            q_start = list(range(S)) + ([S] if T > S else [])
+            ctx_len = [self.max_positions] * S + ([T - S] if T > S else [])
             for _ in range(2):     # the first pass finds the sizes, the second must fit
                 with self.workspace, ops.hold_stream():
                     dev = workspace.empty((lay.size,), torch.int32, self.device)
                     self.staging.send(host, dev)
                     ctx = StepContext(self, lay, dev, static=False)
-                    ctx.entries, ctx.host_q_len, ctx.host_q_start, ctx.host_ctx_len, ctx.host_slots = [], [T], [0], [T], [0]
+                    ctx.entries, ctx.host_q_len, ctx.host_q_start, ctx.host_ctx_len, ctx.host_slots = [], q_len, q_start, ctx_len, [0] * E
                     self.model.forward(ctx, self.cache.views)
         torch.cuda.current_stream().synchronize()
         ops.check_status(self.status)

@@ -18,6 +18,12 @@ Families and what each must offer (beside ``tensor_specs`` and ``bind``):
 ``feed_forward``  ``forward(x, ctx) -> delta``.
 ``block``         the arrangement: ``forward(resid, pending, ctx, cache, writes) ->
                   pending`` where ``pending`` is a delta not yet added to ``resid``.
+
+Buffers: a part takes its outputs from ``workspace.empty`` (plain ``torch.empty``
+works too, at the price of an allocation per step).  Such a buffer is valid until
+the run after the next begins -- long enough for what a layer hands to the next
+one.  What all runs of a step share is made through ``ctx.plan(key, make)`` and
+``ctx.upload(array)``, which live as long as the step.
 """
 from __future__ import annotations
 

@@ -47,7 +47,8 @@ class Sampler:
     def forget(self, slots: list[int]) -> None:
         """Clears the counts of slots whose requests start (again) from their first token."""
         if slots and self.counts is not None:
-            self.counts.index_fill_(0, torch.tensor(slots, dtype=torch.long, device=self.device), 0)
+            for s in slots:     # a fill per row: no index tensor to allocate
+                self.counts[s].zero_()
 
     @staticmethod
     def token_slots(entries, penalised_slots: set) -> list[int]:

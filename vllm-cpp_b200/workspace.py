@@ -16,7 +16,10 @@ A workspace has three regions, each handed out front to back:
 * two ``layer`` regions used in turn by the runs of the execution order: run
   ``i`` takes from region ``i % 2``, which is reset when run ``i`` begins.  What
   a run hands to the next one (its pending delta) therefore outlives the run
-  that made it by exactly one run, which is as long as it is read.
+  that made it by exactly one run, which is as long as it is read.  **Whatever
+  several runs share** (the work items an attention part lays out once per step)
+  must come from the ``step`` region: make it through ``ctx.plan`` or
+  ``ctx.upload``, or inside ``with workspace.whole_step():``.
 
 All work of a step is queued on one stream, so a region may be handed out again
 as soon as the host has moved on: the kernels that read the old contents are
@@ -54,7 +57,7 @@ class _Region:
         self.peak = max(self.peak, self.wanted)
         if self.peak <= self.buffer.numel():
             return False
-        size = -(-int(self.peak * 1.125) // (1 << 20)) * (1 << 20)
+        size = (-(-int(self.peak * 1.125) // (1 << 20)) + 4) * (1 << 20)     # an eighth and 4 MB to spare
         self.buffer = torch.empty(size, dtype=torch.uint8, device=self.device)
         return True
 
@@ -126,6 +129,22 @@ def empty(shape, dtype, device) -> torch.Tensor:
 
 def zeros(shape, dtype, device) -> torch.Tensor:
     return empty(shape, dtype, device).zero_()
+
+
+class whole_step:
+    """Within this context buffers come from the region that lives for the whole step, whichever run is on."""
+
+    def __enter__(self):
+        self._ws = _active
+        if self._ws is not None:
+            self._saved = self._ws._current
+            self._ws._current = self._ws.step_region
+        return self
+
+    def __exit__(self, *exc):
+        if self._ws is not None:
+            self._ws._current = self._saved
+        return False
 
 
 def begin_run(index: int) -> None:
