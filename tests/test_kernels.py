@@ -284,6 +284,87 @@ def test_attention_mixed_batch(dtype, nh, nkv, hd, ps):
     run_attention(dtype, nh, nkv, hd, ps, 0, [(0, 7), (31, 1), (0, 1), (13, 34), (63, 2), (200, 1), (16, 16)])
 
 
+@pytest.mark.parametrize("nh,nkv,hd,ps,window,S,norm", [(8, 2, 128, 16, 0, 3, True), (4, 1, 64, 8, 0, 1, True), (32, 8, 128, 16, 0, 4, True),
+                                                       (6, 2, 64, 32, 40, 2, True), (16, 1, 128, 64, 100, 5, False)])
+def test_attention_of_decoded_tokens_straight_from_the_projection(nh, nkv, hd, ps, window, S, norm):
+    """attn_mma_decode_fused (per-head norm, rotation, cache store and attention of single tokens in one kernel, from
+    the projection's k-slice partial sums) against the two kernels it replaces: the same bits in the output and in
+    the cache, whose contexts end at every place of a page, and against 64-bit attention over the stored keys."""
+    from vllm_cpp_b200 import ops
+    from vllm_cpp_b200.parts import attention as A
+    torch.manual_seed(hd + ps + S)
+    dtype = torch.bfloat16
+    ctxs = [1, ps, ps + 1, 3 * ps - 1, 200, 64, 777, 5 * ps]       # context lengths including the new token
+    B = len(ctxs)
+    seqs = [(torch.randn(c, nkv, hd, dtype=torch.float64).to(dtype).double(),
+             torch.randn(c, nkv, hd, dtype=torch.float64).to(dtype).double()) for c in ctxs]
+    num_pages = sum(-(-c // ps) for c in ctxs) + 3
+    pages, tables = build_paged(seqs, nkv, hd, ps, dtype, num_pages)
+    # the newest position of every request is still to be written: poison it
+    slots = []
+    for c, tab in zip(ctxs, tables):
+        slot = tab[(c - 1) // ps] * ps + (c - 1) % ps
+        slots.append(slot)
+        pages[slot // ps, :, :, slot % ps] = float("nan")
+    W = (nh + 2 * nkv) * hd
+    qkv = torch.randn(S, B, W, device=dev())
+    qw = (1 + 0.1 * torch.randn(hd, device=dev())).to(dtype) if norm else None
+    kw = (1 + 0.1 * torch.randn(hd, device=dev())).to(dtype) if norm else None
+    max_pos = 1024
+    table = rope_table(hd, 1e4, max_pos)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())
+    positions, slot_map = i32([c - 1 for c in ctxs]), i32(slots)
+
+    class Ctx:
+        pass
+    ctx = Ctx()
+    ctx.device, ctx.host_q_len, ctx.host_ctx_len, ctx.host_q_start = dev(), [1] * B, ctxs, list(range(B))
+    plan = A.AttentionPlan(ctx, nh, nkv, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+    assert plan.decode_only
+    NS = plan.nslices
+    mb = max(len(t) for t in tables)
+    bt = torch.full((B, mb), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        bt[i, :len(t)] = torch.tensor(t)
+    bt = bt.to(dev())
+    qs, ql, cl = i32(list(range(B))), i32([1] * B), i32(ctxs)
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    eps = 1e-6
+
+    def partials():
+        if NS == 1:
+            return None, None
+        return torch.empty(B * nh * NS, hd, device=dev()), torch.empty(B * nh * NS, 2, device=dev())
+
+    # the two kernels
+    pages_a = pages.clone()
+    q = torch.empty(B, nh * hd, device=dev(), dtype=dtype)
+    ops.qknorm_rope_kvwrite(qkv, qw, kw, eps, table, positions, slot_map, q, pages_a, nh, nkv, hd, status, use_norm=norm)
+    out_a = torch.full_like(q, float("nan"))
+    po, pm = partials()
+    ops.attn_mma(q, out_a, pages_a, bt, qs, ql, cl, plan.dec_items, B * NS, A.MMA_DECODE_ROWS, po, pm, nh, nkv, hd, window, status,
+                 slice_counters=plan.slice_counters if NS > 1 else None, dec_rows=plan.dec_rows)
+    # the one
+    pages_b = pages.clone()
+    out_b = torch.full_like(q, float("nan"))
+    po, pm = partials()
+    ops.attn_mma_decode_fused(qkv, qw, kw, eps, table, slot_map, out_b, pages_b, bt, qs, ql, cl, plan.dec_items,
+                              B * NS, po, pm, plan.slice_counters if NS > 1 else None, plan.dec_rows, nh, nkv, hd, window,
+                              status, use_norm=norm)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert torch.equal(pages_a.view(torch.int16), pages_b.view(torch.int16)), "the cache differs"
+    assert not torch.isnan(out_b.float()).any()
+    assert torch.equal(out_a.view(torch.int16), out_b.view(torch.int16)), "the attention output differs"
+    # and what came out is attention of the rotated query over the stored keys
+    got = out_b.double().cpu().view(B, nh, hd)
+    for b, (c, tab) in enumerate(zip(ctxs, tables)):
+        k = torch.stack([pages_b[tab[p // ps], 0, :, p % ps] for p in range(c)]).double().cpu()
+        v = torch.stack([pages_b[tab[p // ps], 1, :, p % ps] for p in range(c)]).double().cpu()
+        want = attention_reference(q[b].double().cpu().view(1, nh, hd), k, v, c - 1, window)
+        torch.testing.assert_close(got[b:b + 1], want, **tol(dtype))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 5, 24, 100])
 @pytest.mark.parametrize("hd", [32, 64])

@@ -32,6 +32,10 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
 ]
+# VLLM_CPP_B200_TIMELINE=1 builds the kernels with their timeline marks (see tl_mark in kernels/common.cuh); give such
+# a build a folder of its own (VLLM_CPP_B200_BUILD_DIR) so that it does not replace the regular one
+if os.environ.get("VLLM_CPP_B200_TIMELINE", "0") == "1":
+    NVCC_FLAGS.append("-DVCB_TIMELINE")
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
 
 _lock = threading.Lock()

@@ -37,6 +37,25 @@ namespace {
 constexpr int BN = 64;        // keys per tile
 constexpr int ITEM_INTS = 6;  // entry, q0, nq, slice, nslices, decode index
 
+// Decoding straight from the stacked q, k, v projection (single-token items only): the block makes its own query
+// rows -- k-slice partial sums added in slice order, per-head RMSNorm, rotation by the token's position, exactly
+// the arithmetic of qknorm_rope_kvwrite_kernel -- and the blocks whose key slice holds the token's own position
+// make its key and value likewise and store them in the token's cache slot before they load that page.  One kernel
+// and one kernel boundary less per layer.  qkv == null: queries come from q, keys and values are in the cache.
+struct FusedQkv {
+    const float* qkv;          // [slices][tokens][(nh + 2 nkv) * HD] 32-bit partial sums
+    int slices;
+    long long slice_stride;    // elements between slices
+    const void* q_gain;        // [HD] gains of the per-head norms (null with use_norm 0)
+    const void* k_gain;
+    int gain_dtype, use_norm;
+    float eps;
+    const float* cos_sin;      // [max_pos][HD]: HD/2 cosines, then HD/2 sines
+    int max_pos;
+    const int* slot_map;       // [tokens]: page * page_size + offset of the token's cache entry, -1: none
+    __nv_bfloat16* pages_w;    // the same pages, to write
+};
+
 struct AttnArgs {
     const __nv_bfloat16* q;
     __nv_bfloat16* out;
@@ -56,6 +75,7 @@ struct AttnArgs {
     int nh, nkv, page_size, num_pages, window;
     float scale;
     int* status;
+    FusedQkv f;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -159,6 +179,7 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_s + 16 * STAGES);
 
     pdl_trigger();
+    tl_mark(VCB_TL_ATTN_DEC, 0);
     // The queries and the newest keys come from the kernel before this one.  With TMA loads the wait is put off:
     // what describes the work (items, lengths and block tables are in place before the step's first model kernel
     // starts: the copy of the step's integers is an ordinary stream operation and the kernel that updates the tables
@@ -248,6 +269,9 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
         return true;
     };
     int pre_tiles = 0;
+    constexpr int FPJ = HD / 64;   // lanes of half a head that one thread owns
+    float f_cos[FPJ], f_sin[FPJ], f_g1[FPJ], f_g2[FPJ];
+    long long f_slot = -1;
     if (TMA) {
         __syncthreads();   // the barriers are initialised
         if (warp == NW) {
@@ -260,18 +284,150 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
                 ++pre_tiles;
             }
         }
+        // What the fused form needs beside the projection -- the token's position, its cosines and sines, the gains of
+        // this warp's heads (queries for the multiplying warps, keys for the loading warp), its cache slot -- is written
+        // by no kernel of the step and read before the wait, so that one round trip to memory follows it.
+        if constexpr (WR == 1 && MR == 1) {
+            if (a.f.qkv != nullptr) {
+                int pos = pos0;   // a decoded token's position is its context length less one: no load to wait for
+                if (pos < 0 || pos >= a.f.max_pos) {
+                    if (tid == 0) atomicOr(a.status, VCB_STATUS_BAD_POSITION);
+                    pos = 0;
+                }
+                const float* cs = a.f.cos_sin + (size_t)pos * HD;
+                const void* gain = warp < NW ? a.f.q_gain : a.f.k_gain;
+#pragma unroll
+                for (int j = 0; j < FPJ; ++j) {
+                    const int p = lane + 32 * j;
+                    f_cos[j] = cs[p];
+                    f_sin[j] = cs[HD / 2 + p];
+                    f_g1[j] = a.f.use_norm ? load_as_f32(gain, a.f.gain_dtype, p) : 1.f;
+                    f_g2[j] = a.f.use_norm ? load_as_f32(gain, a.f.gain_dtype, p + HD / 2) : 1.f;
+                }
+                if (warp == NW) f_slot = a.f.slot_map[row0];
+            }
+        }
         pdl_wait();
     }
+    tl_mark(VCB_TL_ATTN_DEC, 1);
 
-    // ---- Q rows -> shared memory (rows beyond R are zero) ----
-    for (int idx = tid; idx < RMAX * CH; idx += blockDim.x) {
-        const int r = idx / CH, c = idx % CH;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < R) {
-            const int iq = r / gq, ih = r % gq;
-            v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(row0 + iq) * a.nh + head0 + ih) * HD + c * 8);
+    bool fused = false;
+    if constexpr (TMA && WR == 1 && MR == 1) fused = a.f.qkv != nullptr;
+    if (fused) {
+        if constexpr (TMA && WR == 1 && MR == 1) {
+            // ---- the token's heads from the stacked projection: warp per head, lane l owns lanes l + 32 j and their
+            // partners half a head further on ----
+            constexpr int HALF = HD / 2, PJ = HALF / 32;
+            const int tok = row0;
+            const size_t row_w = (size_t)(a.nh + 2 * a.nkv) * HD;
+            // sums of the k-slice partials of one head, four slices' loads in flight at a time
+            auto head_sums = [&](int head_col, float (&x1)[PJ], float (&x2)[PJ]) {
+                const float* src = a.f.qkv + (size_t)tok * row_w + (size_t)head_col * HD;
+#pragma unroll
+                for (int j = 0; j < PJ; ++j) x1[j] = x2[j] = 0.f;
+                for (int s0 = 0; s0 < a.f.slices; s0 += 4) {
+                    float t1[4][PJ], t2[4][PJ];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (s0 + k < a.f.slices) {
+#pragma unroll
+                            for (int j = 0; j < PJ; ++j) {
+                                t1[k][j] = src[(size_t)(s0 + k) * a.f.slice_stride + lane + 32 * j];
+                                t2[k][j] = src[(size_t)(s0 + k) * a.f.slice_stride + lane + 32 * j + HALF];
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (s0 + k < a.f.slices) {
+#pragma unroll
+                            for (int j = 0; j < PJ; ++j) { x1[j] += t1[k][j]; x2[j] += t2[k][j]; }
+                        }
+                    }
+                }
+            };
+            // norm and rotation of one head in place (the order of operations of qknorm_rope_kvwrite_kernel)
+            auto norm_rotate = [&](float (&x1)[PJ], float (&x2)[PJ]) {
+                float inv = 1.f;
+                if (a.f.use_norm) {
+                    float ss = 0.f;
+#pragma unroll
+                    for (int j = 0; j < PJ; ++j) ss += x1[j] * x1[j] + x2[j] * x2[j];
+                    ss = warp_sum(ss);
+                    inv = 1.0f / sqrtf(ss / (float)HD + a.f.eps);
+                }
+#pragma unroll
+                for (int j = 0; j < PJ; ++j) {
+                    float u = x1[j], w = x2[j];
+                    if (a.f.use_norm) {
+                        u = f_g1[j] * u * inv;
+                        w = f_g2[j] * w * inv;
+                    }
+                    x1[j] = u * f_cos[j] - w * f_sin[j];
+                    x2[j] = w * f_cos[j] + u * f_sin[j];
+                }
+            };
+            // rows beyond the token's heads are zero
+            for (int idx = tid; idx < (RMAX - R) * CH; idx += blockDim.x)
+                *reinterpret_cast<uint4*>(q_s + swz<RMAX>(R + idx / CH, idx % CH)) = make_uint4(0, 0, 0, 0);
+            if (warp < NW) {
+                for (int r = warp; r < R; r += NW) {
+                    float x1[PJ], x2[PJ];
+                    head_sums(head0 + r, x1, x2);
+                    norm_rotate(x1, x2);
+#pragma unroll
+                    for (int j = 0; j < PJ; ++j) {
+                        const int p = lane + 32 * j, p2 = p + HALF;
+                        *reinterpret_cast<__nv_bfloat16*>(q_s + swz<RMAX>(r, p >> 3) + (p & 7) * 2) = __float2bfloat16_rn(x1[j]);
+                        *reinterpret_cast<__nv_bfloat16*>(q_s + swz<RMAX>(r, p2 >> 3) + (p2 & 7) * 2) = __float2bfloat16_rn(x2[j]);
+                    }
+                }
+            } else if (k_end == hi && k_end > k_begin) {
+                // The loading warp of a block whose slice ends with the token's own position: key and value of the
+                // token go into its cache slot, and only then does this warp ask for the page that holds them.
+                // (Blocks of several head chunks of one KV head each write the same values.)
+                const long long slot = f_slot;
+                if (slot >= 0) {
+                    if (slot / ps >= a.num_pages) {
+                        if (lane == 0) atomicOr(a.status, VCB_STATUS_BAD_PAGE);
+                    } else {
+                        __nv_bfloat16* page = a.f.pages_w + (slot / ps) * a.page_stride;
+                        float x1[PJ], x2[PJ], v1[PJ], v2[PJ];
+                        head_sums(a.nh + a.nkv + kvh, v1, v2);     // (the compiler issues these loads with the key's)
+                        head_sums(a.nh + kvh, x1, x2);
+                        norm_rotate(x1, x2);
+                        __nv_bfloat16* kd = page + ((size_t)kvh * ps + slot % ps) * HD;
+#pragma unroll
+                        for (int j = 0; j < PJ; ++j) {
+                            kd[lane + 32 * j] = __float2bfloat16_rn(x1[j]);
+                            kd[lane + 32 * j + HALF] = __float2bfloat16_rn(x2[j]);
+                        }
+#pragma unroll
+                        for (int j = 0; j < PJ; ++j) { x1[j] = v1[j]; x2[j] = v2[j]; }
+                        __nv_bfloat16* vd = page + ((size_t)(a.nkv + kvh) * ps + slot % ps) * HD;
+#pragma unroll
+                        for (int j = 0; j < PJ; ++j) {
+                            vd[lane + 32 * j] = __float2bfloat16_rn(x1[j]);
+                            vd[lane + 32 * j + HALF] = __float2bfloat16_rn(x2[j]);
+                        }
+                        // the stores above are ordinary ones, the page loads that follow go through the async proxy
+                        asm volatile("fence.proxy.async;" ::: "memory");
+                        __syncwarp();
+                    }
+                }
+            }
         }
-        *reinterpret_cast<uint4*>(q_s + swz<RMAX>(r, c)) = v;
+    } else {
+        // ---- Q rows -> shared memory (rows beyond R are zero) ----
+        for (int idx = tid; idx < RMAX * CH; idx += blockDim.x) {
+            const int r = idx / CH, c = idx % CH;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < R) {
+                const int iq = r / gq, ih = r % gq;
+                v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(row0 + iq) * a.nh + head0 + ih) * HD + c * 8);
+            }
+            *reinterpret_cast<uint4*>(q_s + swz<RMAX>(r, c)) = v;
+        }
     }
 
     // ---- cp.async loader (all threads): 64 keys x HD of K and of V, gathered page by page ----
@@ -601,6 +757,7 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
             }
         }
     }
+    tl_mark(VCB_TL_ATTN_DEC, 2);
 }
 
 // ---------------------------------------------------------------------------
@@ -708,6 +865,8 @@ int launch_rows(const AttnArgs& a, int n_items, int rows_max, cudaStream_t strea
 
 }  // namespace
 
+VCB_TIMELINE_UNIT(attn_mma)
+
 bool vcb_kv_tensor_map(const void* pages, long long rows, int hd, int page_size, CUtensorMap* out) {
     return kv_tensor_map(pages, rows, hd, page_size, out);
 }
@@ -730,9 +889,41 @@ VCB_API int vcb_attn_mma(const void* q, void* out, const void* pages, long long 
     VCB_CHECK_ARG(page_size > 0 && window >= 0, "attn_mma: bad page_size %d or window %d", page_size, window);
     AttnArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_stride, block_table,
                table_row, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml, slice_counters, dec_rows, nh, nkv,
-               page_size, num_pages, window, scale, status};
+               page_size, num_pages, window, scale, status, FusedQkv{}};
     const bool tma = allow_tma && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64) &&
                      ((uintptr_t)pages % 16 == 0) && page_stride == (long long)2 * nkv * page_size * hd;
     if (hd == 64) return tma ? launch_rows<64, true>(a, n_items, rows_max, stream) : launch_rows<64, false>(a, n_items, rows_max, stream);
     return tma ? launch_rows<128, true>(a, n_items, rows_max, stream) : launch_rows<128, false>(a, n_items, rows_max, stream);
+}
+
+// Whether vcb_attn_mma_decode_fused takes these sizes: the page sizes whose pages the TMA loader brings in whole.
+VCB_API int vcb_attn_mma_fused_supported(int dtype, int hd, int page_size) {
+    return dtype == VCB_BF16 && (hd == 64 || hd == 128) && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
+}
+
+// Decoded tokens straight from the stacked q, k, v projection (see FusedQkv): items of one token each (rows_max 16).
+// qkv: [slices][tokens][(nh + 2 nkv) * hd] float; gains bfloat16 or float (gain_dtype), may be null with use_norm 0.
+VCB_API int vcb_attn_mma_decode_fused(const float* qkv, int slices, long long slice_stride, const void* q_gain,
+                                      const void* k_gain, int gain_dtype, int use_norm, float eps, const float* cos_sin,
+                                      int max_pos, const int* slot_map, void* out, void* pages,
+                                      long long page_stride, const int* block_table, const int* table_row, int max_blocks,
+                                      const int* q_start, const int* q_len, const int* ctx_len, const int* items, int n_items,
+                                      float* part_o, float* part_ml, int* slice_counters, const int* dec_rows, int nh, int nkv,
+                                      int hd, int page_size, int num_pages, int window, float scale, int* status,
+                                      cudaStream_t stream) {
+    if (n_items == 0) return 0;
+    VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_mma_decode_fused: %d query heads are not a multiple of %d KV heads", nh, nkv);
+    VCB_CHECK_ARG(vcb_attn_mma_fused_supported(VCB_BF16, hd, page_size), "attn_mma_decode_fused: head_dim %d with pages of %d tokens is not supported", hd, page_size);
+    VCB_CHECK_ARG(((uintptr_t)pages % 16 == 0) && page_stride == (long long)2 * nkv * page_size * hd,
+                  "attn_mma_decode_fused: the pages of a layer must be contiguous and 16-byte aligned");
+    VCB_CHECK_ARG(qkv != nullptr && slices >= 1 && cos_sin != nullptr && slot_map != nullptr && status != nullptr,
+                  "attn_mma_decode_fused: missing operand");
+    VCB_CHECK_ARG(!use_norm || (q_gain != nullptr && k_gain != nullptr), "attn_mma_decode_fused: the per-head norms need their gains");
+    VCB_CHECK_ARG(window >= 0, "attn_mma_decode_fused: bad window %d", window);
+    AttnArgs a{nullptr, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_stride, block_table, table_row, max_blocks,
+               q_start, q_len, ctx_len, items, part_o, part_ml, slice_counters, dec_rows, nh, nkv, page_size, num_pages, window,
+               scale, status,
+               FusedQkv{qkv, slices, slice_stride, q_gain, k_gain, gain_dtype, use_norm, eps, cos_sin, max_pos,
+                        slot_map, (__nv_bfloat16*)pages}};
+    return hd == 64 ? launch<64, 1, 4, 1, true>(a, n_items, stream) : launch<128, 1, 4, 1, true>(a, n_items, stream);
 }

@@ -70,6 +70,41 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// A look at a step from inside (built only with -DVCB_TIMELINE; otherwise tl_mark is nothing).  Thread 0 of every
+// block appends (time, kernel, phase, block, SM) records to a buffer that the host hands to each translation unit:
+// word 0 counts the records, word 1 is the capacity, then four words a record.  Phases: 0 the block starts,
+// 1 its wait for the kernel before it is over, 2 it ends.  This is how one sees, in a captured step with
+// programmatic dependent launch, when blocks of the next kernel are really resident and how long they wait.
+enum VcbTlKernel : int { VCB_TL_GEMM = 1, VCB_TL_ATTN_DEC = 2, VCB_TL_NORM = 3, VCB_TL_ROPE = 4, VCB_TL_SWIGLU = 5,
+                         VCB_TL_ATTN_TC = 6, VCB_TL_OTHER = 7 };
+#ifdef VCB_TIMELINE
+static __device__ unsigned long long* vcb_tl;
+__device__ __forceinline__ void tl_mark(int kernel, int phase) {
+    if (threadIdx.x == 0 && vcb_tl != nullptr) {
+        unsigned long long t, c;
+        unsigned int sm;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        asm volatile("mov.u64 %0, %%clock64;" : "=l"(c));
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+        const unsigned long long i = atomicAdd(vcb_tl, 1ull);
+        if (i < vcb_tl[1]) {
+            unsigned long long* r = vcb_tl + 2 + 4 * i;
+            r[0] = t;
+            r[1] = c;
+            r[2] = ((unsigned long long)kernel << 32) | ((unsigned long long)phase << 24) | sm;
+            r[3] = ((unsigned long long)gridDim.x << 32) | (blockIdx.x + gridDim.x * blockIdx.y);
+        }
+    }
+}
+#define VCB_TIMELINE_UNIT(name)                                                             \
+    VCB_API int vcb_timeline_set_##name(unsigned long long* p) {                            \
+        return cudaMemcpyToSymbol(vcb_tl, &p, sizeof(p)) == cudaSuccess ? 0 : -1;           \
+    }
+#else
+__device__ __forceinline__ void tl_mark(int, int) {}
+#define VCB_TIMELINE_UNIT(name)
+#endif
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

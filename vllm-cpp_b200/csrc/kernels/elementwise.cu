@@ -52,6 +52,8 @@ __global__ void embed_gather_kernel(const void* __restrict__ table, int table_dt
         dst[h] = ok ? load_as_f32(table, table_dtype, (size_t)id * H + h) : 0.f;
 }
 
+VCB_TIMELINE_UNIT(elementwise)
+
 VCB_API int vcb_embed_gather(const void* table, int table_dtype, const int* ids, float* out, int T, int H, int V,
                              int* status, cudaStream_t stream) {
     if (T == 0) return 0;
@@ -98,6 +100,7 @@ __global__ __launch_bounds__(1024) void add_rmsnorm_vec_kernel(float* __restrict
                                                                const int* __restrict__ rows, int H) {
     __shared__ float scratch[33];
     pdl_trigger();
+    tl_mark(VCB_TL_NORM, 0);
     // What no kernel of the step writes -- the row index and the gains -- is read before waiting for the kernel
     // that produces the sums, so that only one round trip to memory follows the wait.
     const int i = blockIdx.x;
@@ -115,6 +118,7 @@ __global__ __launch_bounds__(1024) void add_rmsnorm_vec_kernel(float* __restrict
         }
     }
     pdl_wait();
+    tl_mark(VCB_TL_NORM, 1);
     float4 x[VPT];
     float ss = 0.f;
 #pragma unroll
@@ -122,14 +126,31 @@ __global__ __launch_bounds__(1024) void add_rmsnorm_vec_kernel(float* __restrict
         const int c = threadIdx.x + v * blockDim.x;
         if (c < H4) x[v] = reinterpret_cast<const float4*>(resid + r * H)[c];
     }
-    for (int s = 0; s < S; ++s) {
-        const float4* d4 = reinterpret_cast<const float4*>(delta + (size_t)s * delta_stride + r * H);
+    // the slices' loads are issued several at a time before any is added: one round trip to memory for up to four
+    // slices instead of one each (they are added in slice order all the same); wide rows, which hold more of a row
+    // per thread, take fewer at a time to stay within the registers of a 1024-thread block
+    constexpr int G = VPT == 1 ? 4 : (VPT == 2 ? 2 : 1);
+    for (int s0 = 0; s0 < S; s0 += G) {
+        float4 d[G][VPT];
 #pragma unroll
-        for (int v = 0; v < VPT; ++v) {
-            const int c = threadIdx.x + v * blockDim.x;
-            if (c < H4) {
-                const float4 d = d4[c];
-                x[v].x += d.x; x[v].y += d.y; x[v].z += d.z; x[v].w += d.w;
+        for (int j = 0; j < G; ++j) {
+            if (s0 + j < S) {
+                const float4* d4 = reinterpret_cast<const float4*>(delta + (size_t)(s0 + j) * delta_stride + r * H);
+#pragma unroll
+                for (int v = 0; v < VPT; ++v) {
+                    const int c = threadIdx.x + v * blockDim.x;
+                    if (c < H4) d[j][v] = d4[c];
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+            if (s0 + j < S) {
+#pragma unroll
+                for (int v = 0; v < VPT; ++v) {
+                    const int c = threadIdx.x + v * blockDim.x;
+                    if (c < H4) { x[v].x += d[j][v].x; x[v].y += d[j][v].y; x[v].z += d[j][v].z; x[v].w += d[j][v].w; }
+                }
             }
         }
     }
@@ -155,6 +176,7 @@ __global__ __launch_bounds__(1024) void add_rmsnorm_vec_kernel(float* __restrict
             reinterpret_cast<uint2*>(out + (size_t)i * H)[c] = pk;
         }
     }
+    tl_mark(VCB_TL_NORM, 2);
 }
 
 // The same for many rows (prompt portions; at most one slice of deltas, every row in place): blocks walk the rows
@@ -273,16 +295,30 @@ VCB_API int vcb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, in
 template <typename TIN, typename T>
 __global__ void swiglu_kernel(const TIN* __restrict__ gu, int S, size_t s_stride, T* __restrict__ out, int I, size_t total) {
     pdl_trigger();
+    tl_mark(VCB_TL_SWIGLU, 0);
     pdl_wait();
+    tl_mark(VCB_TL_SWIGLU, 1);
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I, i = idx % I;
         float g = 0.f, u = 0.f;
-        for (int s = 0; s < S; ++s) {   // k-slice partials of the product are added in slice order
-            g += to_f32(gu[s * s_stride + t * 2 * I + 2 * i]);
-            u += to_f32(gu[s * s_stride + t * 2 * I + 2 * i + 1]);
+        // k-slice partials of the product are added in slice order; their loads go out four slices at a time
+        for (int s0 = 0; s0 < S; s0 += 4) {
+            float gs[4], us[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (s0 + j < S) {
+                    gs[j] = to_f32(gu[(s0 + j) * s_stride + t * 2 * I + 2 * i]);
+                    us[j] = to_f32(gu[(s0 + j) * s_stride + t * 2 * I + 2 * i + 1]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (s0 + j < S) { g += gs[j]; u += us[j]; }
+            }
         }
         out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
     }
+    tl_mark(VCB_TL_SWIGLU, 2);
 }
 
 // bfloat16 in and out, one slice, I a multiple of 8: 16-byte loads and stores
@@ -348,6 +384,7 @@ __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, s
                                            int page_size, int num_pages, int nh, int nkv, int hd, int n_tokens,
                                            int has_kv, int* status) {
     pdl_trigger();
+    tl_mark(VCB_TL_ROPE, 0);
     const int lane = threadIdx.x & 31;
     const int heads_total = nh + (has_kv ? 2 * nkv : 0);
     const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -387,6 +424,7 @@ __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, s
         }
     }
     pdl_wait();
+    tl_mark(VCB_TL_ROPE, 1);
     if (!active) return;
     if (h >= nh) {
         if (slot < 0) return;  // padded token: nothing to store
@@ -401,7 +439,15 @@ __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, s
         T* dst = pages + (slot / page_size) * page_stride + ((size_t)(nkv + kvh) * page_size + slot % page_size) * hd;
         for (int i = lane; i < hd; i += 32) {
             float v = 0.f;
-            for (int s = 0; s < S; ++s) v += to_f32(src[s * s_stride + i]);
+            for (int s0 = 0; s0 < S; s0 += 4) {   // loads of four slices at a time, added in slice order
+                float vs[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (s0 + j < S) vs[j] = to_f32(src[(s0 + j) * s_stride + i]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (s0 + j < S) v += vs[j];
+            }
             dst[i] = from_f32<T>(v);
         }
         return;
@@ -413,14 +459,37 @@ __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, s
 #pragma unroll
     for (int j = 0; j < MAXP; ++j) {
         const int p = lane + 32 * j;
-        if (p < half) {
-            x1[j] = x2[j] = 0.f;
-            for (int s = 0; s < S; ++s) {   // k-slice partials of the projection are added in slice order
-                x1[j] += to_f32(src[s * s_stride + p]);
-                x2[j] += to_f32(src[s * s_stride + p + half]);
+        if (p < half) x1[j] = x2[j] = 0.f;
+    }
+    // k-slice partials of the projection are added in slice order; the loads of four slices go out together
+    for (int s0 = 0; s0 < S; s0 += 4) {
+        float a1[4][MAXP], a2[4][MAXP];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (s0 + k < S) {
+#pragma unroll
+                for (int j = 0; j < MAXP; ++j) {
+                    const int p = lane + 32 * j;
+                    if (p < half) {
+                        a1[k][j] = to_f32(src[(s0 + k) * s_stride + p]);
+                        a2[k][j] = to_f32(src[(s0 + k) * s_stride + p + half]);
+                    }
+                }
             }
-            ss += x1[j] * x1[j] + x2[j] * x2[j];
         }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (s0 + k < S) {
+#pragma unroll
+                for (int j = 0; j < MAXP; ++j) {
+                    if (lane + 32 * j < half) { x1[j] += a1[k][j]; x2[j] += a2[k][j]; }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < MAXP; ++j) {
+        if (lane + 32 * j < half) ss += x1[j] * x1[j] + x2[j] * x2[j];
     }
     float inv = 1.f;
     if (use_norm) {

@@ -214,6 +214,7 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::BAR_OFFSET + L::NUM_BARS * 8 + 8);
 
     pdl_trigger();
+    tl_mark(VCB_TL_GEMM, 0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_kb = (g.K + BK - 1) / BK;
     const int unit_rows = BM * MT;   // rows of W per unit
@@ -281,6 +282,7 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
                 }
             }
             pdl_wait();
+            tl_mark(VCB_TL_GEMM, 1);
             for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
                 int m0, n0, kb0, nkb, z;
                 unit_at(u, m0, n0, kb0, nkb, z);
@@ -391,6 +393,7 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
         tc_fence_before();
     }
     __syncthreads();
+    tl_mark(VCB_TL_GEMM, 2);
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -780,6 +783,8 @@ int launch_pair(const void* W, long long w_rows, const void* X, const GemmArgs& 
 }
 
 }  // namespace
+
+VCB_TIMELINE_UNIT(gemm)
 
 // out[z][t][m] (z < splits) = sum over k-slice z of W[m][k] X[t][k];  W [M,K], X [N,K] bfloat16, K contiguous.
 // out_dtype bfloat16 needs splits == 1.  The number of slices actually used is vcb_gemm_effective_splits(K, splits).

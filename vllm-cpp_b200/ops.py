@@ -69,6 +69,9 @@ def _declare(L):
         "vcb_scatter_i32": [P, P, P, P, I, LL, P],
         "vcb_attn_mma": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, F, P, I, P],
         "vcb_attn_mma_supported": [I, I],
+        "vcb_attn_mma_fused_supported": [I, I, I],
+        "vcb_attn_mma_decode_fused": [P, I, LL, P, P, I, I, F, P, I, P, P, P, LL, P, P, I, P, P, P, P, I, P, P, P, P, I, I,
+                                      I, I, I, I, F, P, P],
         "vcb_attn_tc": [P, P, P, LL, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, P, P],
         "vcb_attn_tc_supported": [I, I, I],
         "vcb_attn_merge": [P, P, P, P, I, I, I, I, I, P],
@@ -368,6 +371,37 @@ def attn_mma_supported(dtype: torch.dtype, hd: int) -> bool:
     return bool(lib().vcb_attn_mma_supported(BF16 if dtype == torch.bfloat16 else F32, hd))
 
 
+def attn_mma_fused_supported(dtype: torch.dtype, hd: int, page_size: int) -> bool:
+    """Whether decoded tokens can be attended straight from the stacked q, k, v projection (attn_mma_decode_fused)."""
+    return bool(lib().vcb_attn_mma_fused_supported(BF16 if dtype == torch.bfloat16 else F32, hd, page_size))
+
+
+def attn_mma_decode_fused(qkv, q_weight, k_weight, eps, cos_sin, slot_map, out, pages, block_table, q_start,
+                          q_len, ctx_len, items, n_items, part_o, part_ml, slice_counters, dec_rows, nh, nkv, hd, window,
+                          status, table_row=None, use_norm=True):
+    """Attention of single decoded tokens straight from the stacked projection ``qkv`` [S, T, (nh + 2 nkv) hd]
+    (32-bit k-slice partial sums): each block norms and rotates its own query heads, and the blocks that read the
+    token's own position store its key and value in the cache first -- what qknorm_rope_kvwrite and attn_mma do
+    in two kernels.  Items: one token each, as for :func:`attn_mma` with rows_max 16; a token's position is its
+    entry's context length less one."""
+    _need(qkv, "qkv", torch.float32); _need(out, "out", torch.bfloat16); _need(pages, "pages", torch.bfloat16)
+    _need(cos_sin, "cos_sin", torch.float32); _need(slot_map, "slot_map", torch.int32)
+    for name, t in (("block_table", block_table), ("q_start", q_start), ("q_len", q_len), ("ctx_len", ctx_len), ("items", items)):
+        _need(t, name, torch.int32)
+    assert qkv.dim() == 3 and qkv.shape[2] == (nh + 2 * nkv) * hd and cos_sin.shape[1] == hd
+    num_pages, two, nkv_p, page_size, hd_p = pages.shape
+    assert two == 2 and nkv_p == nkv and hd_p == hd
+    wdt = F32
+    if use_norm:
+        _need(q_weight, "q_norm weight"); _need(k_weight, "k_norm weight", q_weight.dtype)
+        wdt = _dt(q_weight)
+    _call("vcb_attn_mma_decode_fused", _p(qkv), qkv.shape[0], qkv.stride(0), _p(q_weight), _p(k_weight), wdt, int(use_norm),
+          float(eps), _p(cos_sin), cos_sin.shape[0], _p(slot_map), _p(out), _p(pages), pages.stride(0),
+          _p(block_table), _p(table_row), block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items,
+          _p(part_o), _p(part_ml), _p(slice_counters), _p(dec_rows), nh, nkv, hd, page_size, num_pages, int(window or 0),
+          1.0 / math.sqrt(hd), _p(status), _stream())
+
+
 def attn_tc_supported(dtype: torch.dtype, hd: int, page_size: int) -> bool:
     """Whether the tcgen05 attention kernel for prompt portions takes this element type, head size and page size."""
     return bool(lib().vcb_attn_tc_supported(BF16 if dtype == torch.bfloat16 else F32, hd, page_size))
@@ -403,3 +437,42 @@ def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items
           block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, rows_max, _p(part_o),
           _p(part_ml), _p(slice_counters), _p(dec_rows), nh, nkv, hd, page_size, num_pages, int(window or 0),
           1.0 / math.sqrt(hd), _p(status), int(allow_tma), _stream())
+
+
+# --------------------------------------------------------------------------  a look at a step from inside
+_timeline = None
+TIMELINE_KERNELS = {1: "gemm", 2: "attn_decode", 3: "add_rmsnorm", 4: "qknorm_rope", 5: "swiglu", 6: "attn_tc", 7: "other"}
+
+
+def timeline_begin(capacity: int = 1 << 18) -> None:
+    """Starts recording the kernels' timeline marks (a library built with VLLM_CPP_B200_TIMELINE=1 only): thread 0 of
+    every block notes when the block starts, when its wait for the kernel before it ends, and when it ends."""
+    global _timeline
+    L = lib()
+    if not hasattr(L, "vcb_timeline_set_gemm"):
+        raise KernelError("this kernel library was built without timeline marks (build with VLLM_CPP_B200_TIMELINE=1)")
+    _timeline = torch.zeros(2 + 4 * capacity, dtype=torch.int64, device="cuda")
+    _timeline[1] = capacity
+    torch.cuda.synchronize()
+    for unit in ("gemm", "attn_mma", "elementwise"):
+        fn = getattr(L, f"vcb_timeline_set_{unit}")
+        fn.argtypes, fn.restype = [c_void_p], c_int
+        if fn(_timeline.data_ptr()) != 0:
+            raise KernelError("could not hand the timeline buffer to the kernels")
+
+
+def timeline_end():
+    """Stops recording; returns the records as a list of dicts (t_ns, clock, kernel, phase, sm, block, grid), by time."""
+    global _timeline
+    L = lib()
+    torch.cuda.synchronize()
+    for unit in ("gemm", "attn_mma", "elementwise"):
+        getattr(L, f"vcb_timeline_set_{unit}")(None)
+    buf = _timeline.cpu().numpy()
+    _timeline = None
+    n = int(min(buf[0], buf[1]))
+    rec = buf[2:2 + 4 * n].reshape(n, 4)
+    out = [dict(t_ns=int(r[0]), clock=int(r[1]), kernel=TIMELINE_KERNELS.get(int(r[2]) >> 32, "?"), phase=(int(r[2]) >> 24) & 0xFF,
+                sm=int(r[2]) & 0xFFFFFF, block=int(r[3]) & 0xFFFFFFFF, grid=int(r[3]) >> 32) for r in rec]
+    out.sort(key=lambda d: d["t_ns"])
+    return out
