@@ -162,6 +162,74 @@ def test_qknorm_rope_kvwrite(dtype, nh, nkv, hd):
             assert pages[s // ps, :, :, s % ps].abs().max().item() == 0
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd,rot,interleaved", [(16, 8, True), (32, 32, True), (64, 16, False), (128, 64, False), (48, 2, True), (128, 128, True)])
+def test_qknorm_rope_kvwrite_partial_and_interleaved(dtype, hd, rot, interleaved):
+    """Only the first ``rot`` lanes of a head turn (the norm still covers the whole head), paired (i, i + rot/2) or
+    (2i, 2i+1); three k-slices of partial sums in 32-bit where the input is."""
+    from vllm_cpp_b200 import ops
+    nh, nkv, T, ps, num_pages, eps, max_pos = 3, 1, 9, 4, 5, 1e-6, 40
+    S = 3 if dtype == torch.float32 else 1
+    parts = torch.randn(S, T, (nh + 2 * nkv) * hd, device=dev()).to(dtype)
+    qkv = parts if S > 1 else parts[0]
+    qw = (1 + 0.1 * torch.randn(hd, device=dev())).to(dtype)
+    kw = (1 + 0.1 * torch.randn(hd, device=dev())).to(dtype)
+    table = rope_table(rot, 300.0, max_pos)
+    pos = torch.randint(0, max_pos, (T,), device=dev(), dtype=torch.int32)
+    slots = torch.randperm(num_pages * ps, device=dev())[:T].to(torch.int32)
+    pages = torch.zeros(num_pages, 2, nkv, ps, hd, device=dev(), dtype=dtype)
+    q_out = torch.empty(T, nh * hd, device=dev(), dtype=dtype)
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    ops.qknorm_rope_kvwrite(qkv, qw, kw, eps, table, pos, slots, q_out, pages, nh, nkv, hd, status,
+                            rotary_dim=rot, interleaved=interleaved)
+    assert status.item() == 0
+    x = parts.double().sum(0).view(T, nh + 2 * nkv, hd)
+    c, sn = table[pos.long(), :rot // 2].double()[:, None], table[pos.long(), rot // 2:].double()[:, None]
+
+    def norm_rope(h, w):
+        h = w.double() * h / torch.sqrt((h * h).mean(-1, keepdim=True) + eps)
+        out = h.clone()
+        if interleaved:
+            a, b = h[..., 0:rot:2], h[..., 1:rot:2]
+            out[..., 0:rot:2], out[..., 1:rot:2] = a * c - b * sn, b * c + a * sn
+        else:
+            a, b = h[..., :rot // 2], h[..., rot // 2:rot]
+            out[..., :rot // 2], out[..., rot // 2:rot] = a * c - b * sn, b * c + a * sn
+        return out
+
+    torch.testing.assert_close(q_out.double().view(T, nh, hd), norm_rope(x[:, :nh], qw), **tol(dtype))
+    k_want = norm_rope(x[:, nh:nh + nkv], kw)
+    for t in range(T):
+        s = int(slots[t])
+        torch.testing.assert_close(pages[s // ps, 0, :, s % ps].double(), k_want[t], **tol(dtype))
+        torch.testing.assert_close(pages[s // ps, 1, :, s % ps].double(), x[t, nh + nkv:], **tol(dtype))
+    with pytest.raises(ops.KernelError):       # a table of another width than the lanes to turn
+        ops.qknorm_rope_kvwrite(qkv, qw, kw, eps, rope_table(hd + 2, 300.0, max_pos), pos, slots, q_out, pages, nh, nkv, hd,
+                                status, rotary_dim=rot, interleaved=interleaved)
+
+
+@pytest.mark.parametrize("sdtype,value", [(torch.float32, 0.25), (torch.bfloat16, -1.5), (torch.int32, 7)])
+def test_state_reset(sdtype, value):
+    """The state rows of requests whose entries start at position 0 take the initial value, in every cache of the
+    group; entries further on, empty entries and other slots keep what they hold; a slot outside the table is
+    reported and nothing is written for it."""
+    from vllm_cpp_b200 import ops
+    caches, slots_n, shape = 3, 6, (5, 7)
+    state = torch.full((caches, slots_n) + shape, 9, dtype=sdtype, device=dev())
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev())
+    # entry: (slot, q_len, ctx_len): starts, is further on, starts, is empty
+    slots, q_len, ctx_len = i32([4, 1, 0, 2]), i32([3, 1, 1, 0]), i32([3, 10, 1, 0])
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    ops.state_reset(state, slots, q_len, ctx_len, 4, value, status)
+    assert status.item() == 0
+    for s in range(slots_n):
+        want = value if s in (4, 0) else 9
+        assert (state[:, s] == torch.tensor(want, dtype=sdtype)).all(), s
+    ops.state_reset(state, i32([77]), i32([2]), i32([2]), 1, value, status)
+    assert status.item() == 32
+    assert (state[:, 1] == 9).all()
+
+
 def build_paged(seqs_kv, nkv, hd, ps, dtype, num_pages, shuffle_seed=0):
     """Scatters per-request K/V [len, nkv, hd] into shuffled pages; returns pages and block tables."""
     g = torch.Generator().manual_seed(shuffle_seed)

@@ -162,17 +162,21 @@ class ToyConfig:
         return d
 
 
+PRIOR = 0.25      # what the running-mean mixer's state holds before a request's first token
+
+
 def register_toy():
     from vllm_cpp_b200.parts import CacheSpec, Mixer
     from vllm_cpp_b200.registry import LayerRun, LayerSpec, ModelSpec, PartSpec, register_architecture, register_part
     from vllm_cpp_b200.weights import TensorSpec
 
     class RunningMeanMixer(Mixer):
-        """delta_t = W . mean(x_0..x_t): needs the running sum of a request's inputs, a state of fixed size."""
+        """delta_t = W . mean(PRIOR, x_0..x_t): needs the running sum of a request's inputs, a state of fixed size
+        that starts at PRIOR in every lane (the cache sets it when a request's first tokens arrive)."""
         capturable = False
 
         def cache_spec(self):
-            return CacheSpec("state", shape=(int(self.params["size"]),), dtype="float32")
+            return CacheSpec("state", shape=(int(self.params["size"]),), dtype="float32", initial_value=PRIOR)
 
         def tensor_specs(self):
             n = int(self.params["size"])
@@ -187,7 +191,7 @@ def register_toy():
                 s, n = ctx.host_q_start[i], len(e.tokens)
                 run = cache.state[e.slot] + torch.cumsum(x[s:s + n].float(), 0)
                 cache.state[e.slot] = run[-1]
-                count = torch.arange(e.start_pos + 1, e.start_pos + n + 1, device=x.device, dtype=torch.float32)
+                count = torch.arange(e.start_pos + 2, e.start_pos + n + 2, device=x.device, dtype=torch.float32)
                 out[s:s + n] = run / count[:, None]
             return out @ self.w.float().T
 
@@ -237,7 +241,7 @@ def plain_toy(cfg: ToyConfig, W, ids):
     def mean_layer(x):
         p = "toy.1."
         y = P.rms_norm(x, W[p + "n1.weight"], cfg.eps)
-        mean = torch.cumsum(y, 0) / torch.arange(1, T + 1, dtype=torch.float64)[:, None]
+        mean = (PRIOR + torch.cumsum(y, 0)) / torch.arange(2, T + 2, dtype=torch.float64)[:, None]
         x = x + P.linear(mean, W[p + "mix.mix.weight"])
         y = P.rms_norm(x, W[p + "n2.weight"], cfg.eps)
         return x + P.swiglu_mlp(y, W[p + "ff.gate_proj.weight"], W[p + "ff.up_proj.weight"], W[p + "ff.down_proj.weight"])
@@ -327,6 +331,10 @@ class RoutedToyConfig:
     eps: float = 1e-6
     theta: float = 500.0
     position_scale: float = 4.0
+    rotary_dim: int = 8            # of the 16 lanes of a head, paired (2i, 2i+1)
+    embedding_scale: float = 3.0
+    logit_cap: float = 2.0
+    second_layer_page_size: int = 16
     max_positions: int = 96
     num_layers: int = 2
     architecture: str = "RoutedToyForCausalLM"
@@ -342,6 +350,7 @@ class RoutedToyConfig:
 
 
 def register_routed_toy():
+    from vllm_cpp_b200.parts import GQAAttention, LMHead, TokenEmbedding
     from vllm_cpp_b200.parts.base import FeedForward, PositionEncoding
     from vllm_cpp_b200.registry import LayerRun, LayerSpec, ModelSpec, PartSpec, register_architecture, register_part
     from vllm_cpp_b200.weights import TensorSpec
@@ -375,47 +384,84 @@ def register_routed_toy():
             return out
 
     class ScaledRotary(PositionEncoding):
-        """Rotary angles of position / scale: what the attention part asks of its position part is ``table``."""
+        """Rotary angles of position / scale on the first ``rotary_dim`` lanes of a head, paired (2i, 2i+1): what the
+        attention part asks of its position part is ``table``, ``rotary_dim`` and ``pairing``."""
 
         def __init__(self, params, prefix, build):
             super().__init__(params, prefix, build)
-            hd, theta, scale, n = int(params["head_dim"]), float(params["theta"]), float(params["scale"]), int(params["max_positions"])
-            inv = theta ** (-2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)
+            rd, theta, scale, n = int(params["rotary_dim"]), float(params["theta"]), float(params["scale"]), int(params["max_positions"])
+            inv = theta ** (-2.0 * torch.arange(rd // 2, dtype=torch.float64) / rd)
             ang = (torch.arange(n, dtype=torch.float64) / scale)[:, None] * inv[None, :]
             self.table = torch.cat([torch.cos(ang), torch.sin(ang)], 1).float().contiguous().to(build.device)
+            self.rotary_dim, self.pairing = rd, "interleaved"
+
+    class ScaledEmbedding(TokenEmbedding):
+        """x = scale * E[id]: an embedding of another kind, registered from here."""
+
+        def forward(self, ids, n_tokens, status):
+            return super().forward(ids, n_tokens, status) * float(self.params["scale"])
+
+    class CappedHead(LMHead):
+        """logits = cap * tanh(logits / cap): a head of another kind."""
+
+        def forward(self, y, status=None):
+            cap = float(self.params["cap"])
+            return cap * torch.tanh(super().forward(y, status) / cap)
+
+    class PagedAttention(GQAAttention):
+        """The package's attention with pages of a size of its own: its caches get a pool of their own."""
+
+        def cache_spec(self):
+            import dataclasses
+            return dataclasses.replace(super().cache_spec(), page_size=int(self.params["page_size"]))
 
     def describe(cfg: RoutedToyConfig):
         H = cfg.hidden_size
         norm = PartSpec("rmsnorm", {"size": H, "eps": cfg.eps})
         ffn = PartSpec("top_one_experts", {"hidden_size": H, "expert_size": cfg.expert_size, "num_experts": cfg.num_experts})
-        pos = PartSpec("scaled_rotary", {"head_dim": cfg.head_dim, "theta": cfg.theta, "scale": cfg.position_scale,
+        pos = PartSpec("scaled_rotary", {"rotary_dim": cfg.rotary_dim, "theta": cfg.theta, "scale": cfg.position_scale,
                                          "max_positions": cfg.max_positions})
-        attn = PartSpec("gqa_attention", dict(hidden_size=H, num_heads=cfg.num_heads, num_kv_heads=cfg.num_kv_heads,
-                                              head_dim=cfg.head_dim, eps=cfg.eps, qk_norm=False, window=0, position=pos))
+        attn = dict(hidden_size=H, num_heads=cfg.num_heads, num_kv_heads=cfg.num_kv_heads, head_dim=cfg.head_dim,
+                    eps=cfg.eps, qk_norm=True, window=0, position=pos)
+        # the first layer's keys lie in pages of the engine's size, the second layer's in pages of its own
+        mixers = [PartSpec("gqa_attention", attn)] + [PartSpec("paged_attention", dict(attn, page_size=cfg.second_layer_page_size))] * (cfg.num_layers - 1)
+        # the roles of a layer may name their families themselves (here as the defaults would)
         layers = tuple(LayerSpec(prefix=f"rt.{i}.", block=PartSpec("prenorm"),
-                                 parts={"norm1": (norm, "n1."), "mixer": (attn, "att."), "norm2": (norm, "n2."),
+                                 parts={"norm1": (norm, "n1.", "norm"), "mixer": (mixers[i], "att.", "mixer"), "norm2": (norm, "n2."),
                                         "feed_forward": (ffn, "moe.")}) for i in range(cfg.num_layers))
         return ModelSpec(hidden_size=H, vocab_size=cfg.vocab_size, max_positions=cfg.max_positions,
-                         embed_tensor="rt.embed.weight", layers=layers,
+                         embed_tensor=None, layers=layers,
                          order=tuple(LayerRun(i, i) for i in range(cfg.num_layers)), final_norm=norm,
-                         final_norm_prefix="rt.norm.", lm_head_tensor="rt.head.weight")
+                         final_norm_prefix="rt.norm.", lm_head_tensor=None,
+                         embedding=PartSpec("scaled_embedding", {"tensor": "rt.embed.weight", "vocab_size": cfg.vocab_size,
+                                                                 "hidden_size": H, "scale": cfg.embedding_scale}),
+                         head=PartSpec("capped_head", {"tensor": "rt.head.weight", "vocab_size": cfg.vocab_size,
+                                                       "hidden_size": H, "cap": cfg.logit_cap}))
 
     register_part("feed_forward", "top_one_experts", TopOneExperts)
     register_part("position", "scaled_rotary", ScaledRotary)
+    register_part("embedding", "scaled_embedding", ScaledEmbedding)
+    register_part("head", "capped_head", CappedHead)
+    register_part("mixer", "paged_attention", PagedAttention)
     register_architecture("RoutedToyForCausalLM", RoutedToyConfig, describe)
 
 
 def plain_routed_toy(cfg: RoutedToyConfig, W, ids, act_dtype):
     T, nh, nkv, hd = len(ids), cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
-    inv = cfg.theta ** (-2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)
+    rd = cfg.rotary_dim
+    inv = cfg.theta ** (-2.0 * torch.arange(rd // 2, dtype=torch.float64) / rd)
     ang = (torch.arange(T, dtype=torch.float64) / cfg.position_scale)[:, None] * inv[None, :]
     cos, sin = torch.cos(ang).float().double(), torch.sin(ang).float().double()
-    x = P.embed(ids, W["rt.embed.weight"])
+
+    def rotate(h):      # the first rd lanes of every head turn, paired (2i, 2i+1); the rest pass
+        return torch.cat([P.rope_interleaved(h[..., :rd], cos, sin), h[..., rd:]], -1)
+
+    x = cfg.embedding_scale * P.embed(ids, W["rt.embed.weight"])
     for i in range(cfg.num_layers):
         p = f"rt.{i}."
         y = P.rms_norm(x, W[p + "n1.weight"], cfg.eps)
-        q = P.rope_half_split(P.linear(y, W[p + "att.q_proj.weight"]).view(T, nh, hd), cos, sin)
-        k = P.rope_half_split(P.linear(y, W[p + "att.k_proj.weight"]).view(T, nkv, hd), cos, sin)
+        q = rotate(P.head_rms_norm(P.linear(y, W[p + "att.q_proj.weight"]).view(T, nh, hd), W[p + "att.q_norm.weight"], cfg.eps))
+        k = rotate(P.head_rms_norm(P.linear(y, W[p + "att.k_proj.weight"]).view(T, nkv, hd), W[p + "att.k_norm.weight"], cfg.eps))
         v = P.linear(y, W[p + "att.v_proj.weight"]).view(T, nkv, hd)
         x = x + P.linear(P.attention(q, k, v).reshape(T, nh * hd), W[p + "att.o_proj.weight"])
         y = P.rms_norm(x, W[p + "n2.weight"], cfg.eps)
@@ -428,14 +474,17 @@ def plain_routed_toy(cfg: RoutedToyConfig, W, ids, act_dtype):
             h = h / (1 + torch.exp(-h)) * P.linear(y[t:t + 1], W[f"{p}moe.experts.{e}.up.weight"])
             d[t] = prob[t, e] * P.linear(h, W[f"{p}moe.experts.{e}.down.weight"])[0]
         x = x + d
-    return P.linear(P.rms_norm(x, W["rt.norm.weight"], cfg.eps), W["rt.head.weight"]), best
+    logits = P.linear(P.rms_norm(x, W["rt.norm.weight"], cfg.eps), W["rt.head.weight"])
+    return cfg.logit_cap * torch.tanh(logits / cfg.logit_cap), best
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_toy_routed_feed_forward_and_other_positions(dtype, tmp_path):
-    """A feed-forward with routing and a position encoding of another kind, registered from here, run through the
-    unchanged loader, cache, step function and scheduler: portions and batching give the plain model's logits, and
-    greedy generation through the entry point gives its tokens."""
+    """A feed-forward with routing, a position encoding of another kind (scaled positions, half of each head's lanes
+    rotated, in interleaved pairs), a scaled embedding, a head that caps its logits, and a second layer whose keys
+    lie in pages of another size than the first layer's (two pools, two block tables a request) -- all registered
+    from here and run through the unchanged loader, cache, step function and scheduler: portions and batching give
+    the plain model's logits, and greedy generation through the entry point gives its tokens."""
     from vllm_cpp_b200 import LLM, EngineConfig, load_config, write_random_model, unregister_architecture, unregister_part
     from vllm_cpp_b200.engine.llm import TORCH_DTYPES
     from vllm_cpp_b200.engine.step import ModelRunner, StepEntry
@@ -454,8 +503,10 @@ def test_toy_routed_feed_forward_and_other_positions(dtype, tmp_path):
         model.load(open_model_weights(folder, td, DEV))
         ps = 8
         runner = ModelRunner(model, ps, 16, 2, td, DEV)
+        assert runner.page_sizes == [ps, cfg.second_layer_page_size] and [t.shape[1] for t in runner.tables] == [12, 6]
         rt = runtime()
         cm = rt.CacheManager(runner.layout.runtime_groups(rt, ps, 16), 2)
+        assert cm.num_groups() == 2
         rng = np.random.default_rng(5)
         seqs = {0: rng.integers(0, cfg.vocab_size, 37).tolist(), 1: rng.integers(0, cfg.vocab_size, 12).tolist()}
         want = {r: plain_routed_toy(cfg, W, t, td)[0] for r, t in seqs.items()}
@@ -469,7 +520,8 @@ def test_toy_routed_feed_forward_and_other_positions(dtype, tmp_path):
                 if step < len(cuts[r]):
                     n = cuts[r][step]
                     assert cm.reserve(r, pos[r] + n)
-                    entries.append(StepEntry(cm.slot(r), pos[r], seqs[r][pos[r]:pos[r] + n], [cm.block_table(r, 0)], list(range(n))))
+                    entries.append(StepEntry(cm.slot(r), pos[r], seqs[r][pos[r]:pos[r] + n],
+                                             [cm.block_table(r, g) for g in range(2)], list(range(n))))
                     rows += [(r, pos[r] + i) for i in range(n)]
                     pos[r] += n
             out = runner.step(entries).double().cpu()
@@ -490,3 +542,6 @@ def test_toy_routed_feed_forward_and_other_positions(dtype, tmp_path):
         unregister_architecture("RoutedToyForCausalLM")
         unregister_part("feed_forward", "top_one_experts")
         unregister_part("position", "scaled_rotary")
+        unregister_part("embedding", "scaled_embedding")
+        unregister_part("head", "capped_head")
+        unregister_part("mixer", "paged_attention")

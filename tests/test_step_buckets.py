@@ -5,7 +5,7 @@ from vllm_cpp_b200.engine.step import ModelRunner, StepEntry
 
 
 def fake_runner(graphs=True, page_size=16):
-    r = types.SimpleNamespace(cuda_graphs=graphs, page_size=page_size)
+    r = types.SimpleNamespace(cuda_graphs=graphs, page_size=page_size, page_sizes=[page_size])
     for name in ("GRAPH_BUCKETS", "PORTION_BUCKETS", "MIXED_SINGLES", "MIXED_PORTIONS", "MIXED_TOKENS"):
         setattr(r, name, getattr(ModelRunner, name))
     for name in ("capture_size", "portion_size", "mixed_size", "rows_capacity", "_mixed_updates", "_portion_updates"):

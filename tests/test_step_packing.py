@@ -9,7 +9,8 @@ from vllm_cpp_b200.engine.step import MetaLayout, ModelRunner, StepEntry
 
 
 def fake_runner(groups=1, page_size=16, num_slots=8, max_blocks=64):
-    r = types.SimpleNamespace(page_size=page_size, num_slots=num_slots, max_blocks=max_blocks, tables=[None] * groups,
+    r = types.SimpleNamespace(page_size=page_size, page_sizes=[page_size] * groups, num_slots=num_slots,
+                              max_blocks=[max_blocks] * groups, tables=[None] * groups,
                               _uploaded=[[0] * num_slots for _ in range(groups)], vocab_size=1000, max_positions=page_size * max_blocks)
     for name in ("_fill", "_fill_decode", "_table_updates", "_validate"):
         setattr(r, name, types.MethodType(getattr(ModelRunner, name), r))

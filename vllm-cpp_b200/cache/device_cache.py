@@ -66,9 +66,18 @@ class CacheLayout:
             g.runtime_index = i
         self.where = {cid: (gi, g.cache_ids.index(cid)) for gi, g in enumerate(self.groups) for cid in g.cache_ids}
 
+    def page_size_of(self, group: CacheGroup, page_size: int) -> int:
+        """Tokens per page of a paged group: what its caches asked for, else the engine's ``page_size``."""
+        return group.spec.page_size or page_size
+
+    def num_pages_of(self, group: CacheGroup, page_size: int, num_pages: int) -> int:
+        """Every paged group gets a pool for as many tokens as ``num_pages`` pages of the engine's size hold."""
+        return num_pages * page_size // self.page_size_of(group, page_size)
+
     def runtime_groups(self, runtime, page_size: int, num_pages: int):
-        """GroupSpec list for the host CacheManager: every paged group gets a pool of ``num_pages``."""
-        return [runtime.GroupSpec(page_size, num_pages, g.spec.window) for g in self.paged]
+        """GroupSpec list for the host CacheManager, one pool per paged group."""
+        return [runtime.GroupSpec(self.page_size_of(g, page_size), self.num_pages_of(g, page_size, num_pages), g.spec.window)
+                for g in self.paged]
 
     def bytes_per_token(self, elem_size: int) -> int:
         return sum(len(g.cache_ids) * 2 * g.spec.num_kv_heads * g.spec.head_dim * elem_size for g in self.paged)
@@ -82,24 +91,24 @@ class DeviceCache:
         for g in layout.groups:
             n = len(g.cache_ids)
             if g.paged:
-                shape = (n, num_pages, 2, g.spec.num_kv_heads, page_size, g.spec.head_dim)
+                shape = (n, layout.num_pages_of(g, page_size, num_pages), 2, g.spec.num_kv_heads,
+                         layout.page_size_of(g, page_size), g.spec.head_dim)
                 self.tensors.append(torch.zeros(shape, dtype=dtype, device=device))
             else:
                 sdt = _TORCH_DTYPES[g.spec.dtype]
-                self.tensors.append(torch.zeros((n, num_slots) + tuple(g.spec.shape), dtype=sdt, device=device))
+                self.tensors.append(torch.full((n, num_slots) + tuple(g.spec.shape), g.spec.initial_value, dtype=sdt, device=device))
         self.views = {}
         for cid, (gi, li) in layout.where.items():
             t = self.tensors[gi][li]
             self.views[cid] = KVCacheView(gi, t) if layout.groups[gi].paged else StateCacheView(gi, t)
 
-    def reset_state(self, slots: list[int]) -> None:
-        """Zeroes the fixed-size state of requests that start from position 0."""
-        if not slots:
-            return
+    def reset_state(self, ctx) -> None:
+        """Sets the fixed-size state of the requests whose entries start at position 0 to its initial value: a
+        kernel that reads the step's own integers, so that a captured step does it as well."""
+        from .. import ops
         for g, t in zip(self.layout.groups, self.tensors):
             if not g.paged:
-                for s in slots:     # a fill per slot: no index tensor to allocate
-                    t[:, s].zero_()
+                ops.state_reset(t, ctx.slots, ctx.q_len, ctx.ctx_len, ctx.E, g.spec.initial_value, ctx.status)
 
     def poison(self, value: float = float("nan")) -> None:
         """Fills every page with a value that shows if anything reads what it should not."""

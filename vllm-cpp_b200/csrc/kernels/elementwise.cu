@@ -372,8 +372,12 @@ VCB_API int vcb_swiglu(const void* gate_up, int in_dtype, int S, long long s_str
 // per-head RMSNorm of Q and K, rotary rotation by the token's position, Q store,
 // and K/V scatter into the token's cache page.  One warp per (token, head).
 //   qkv:     [T, (nh + 2 nkv) * hd]   (only [T, nh * hd] when has_kv == 0)
-//   cos_sin: [max_pos, hd]  (hd/2 cosines then hd/2 sines, 32-bit)
+//   cos_sin: [max_pos, rot_dim]  (rot_dim/2 cosines then rot_dim/2 sines, 32-bit)
 //   pages:   [num_pages, 2, nkv, page_size, hd] of one layer
+// rot_dim <= hd lanes of a head are rotated, the rest pass (normed) as they are; the rotated lanes are paired
+// (i, i + rot_dim/2), or (2i, 2i+1) with `interleaved` (the two pairings of the reference's back ends,
+// src/mlx_backend.cpp:411-412 and src/model.cpp:983-985).  A thread owns pair i = lane + 32 j of a head: lanes
+// (i, i + rot_dim/2) or (2i, 2i+1) while i < rot_dim/2, and the unrotated lanes (2i, 2i+1) beyond.
 // ---------------------------------------------------------------------------
 template <typename TIN, typename T>
 __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, size_t s_stride, const void* __restrict__ qw,
@@ -382,9 +386,12 @@ __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, s
                                            const int* __restrict__ positions, const int* __restrict__ slot_map,
                                            T* __restrict__ q_out, T* __restrict__ pages, long long page_stride,
                                            int page_size, int num_pages, int nh, int nkv, int hd, int n_tokens,
-                                           int has_kv, int* status) {
+                                           int has_kv, int rot_dim, int interleaved, int* status) {
     pdl_trigger();
     tl_mark(VCB_TL_ROPE, 0);
+    const int rot_half = rot_dim >> 1;
+    auto e1_of = [&](int i) { return (interleaved || i >= rot_half) ? 2 * i : i; };
+    auto e2_of = [&](int i) { return (interleaved || i >= rot_half) ? 2 * i + 1 : i + rot_half; };
     const int lane = threadIdx.x & 31;
     const int heads_total = nh + (has_kv ? 2 * nkv : 0);
     const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -410,15 +417,15 @@ __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, s
             bad_pos = pos < 0 || pos >= max_pos;
             if (bad_pos) pos = 0;
             const void* gain = h < nh ? qw : kw;
-            const float* cs = cos_sin + (size_t)pos * hd;
+            const float* cs = cos_sin + (size_t)pos * rot_dim;
 #pragma unroll
             for (int j = 0; j < MAXP; ++j) {
                 const int p = lane + 32 * j;
                 if (p < half) {
-                    g1[j] = use_norm ? load_as_f32(gain, w_dtype, p) : 1.f;
-                    g2[j] = use_norm ? load_as_f32(gain, w_dtype, p + half) : 1.f;
-                    cs1[j] = cs[p];
-                    sn1[j] = cs[half + p];
+                    g1[j] = use_norm ? load_as_f32(gain, w_dtype, e1_of(p)) : 1.f;
+                    g2[j] = use_norm ? load_as_f32(gain, w_dtype, e2_of(p)) : 1.f;
+                    cs1[j] = p < rot_half ? cs[p] : 1.f;
+                    sn1[j] = p < rot_half ? cs[rot_half + p] : 0.f;
                 }
             }
         }
@@ -471,8 +478,8 @@ __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, s
                 for (int j = 0; j < MAXP; ++j) {
                     const int p = lane + 32 * j;
                     if (p < half) {
-                        a1[k][j] = to_f32(src[(s0 + k) * s_stride + p]);
-                        a2[k][j] = to_f32(src[(s0 + k) * s_stride + p + half]);
+                        a1[k][j] = to_f32(src[(s0 + k) * s_stride + e1_of(p)]);
+                        a2[k][j] = to_f32(src[(s0 + k) * s_stride + e2_of(p)]);
                     }
                 }
             }
@@ -508,8 +515,8 @@ __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, s
                 a = g1[j] * a * inv;
                 b = g2[j] * b * inv;
             }
-            dst[p] = from_f32<T>(a * cs1[j] - b * sn1[j]);
-            dst[p + half] = from_f32<T>(b * cs1[j] + a * sn1[j]);
+            dst[e1_of(p)] = from_f32<T>(a * cs1[j] - b * sn1[j]);
+            dst[e2_of(p)] = from_f32<T>(b * cs1[j] + a * sn1[j]);
         }
     }
 }
@@ -595,13 +602,16 @@ VCB_API int vcb_qknorm_rope_kvwrite(const void* qkv, int in_dtype, int S, long l
                                     const void* qw, const void* kw, int w_dtype, int use_norm, float eps,
                                     const float* cos_sin, int max_pos, const int* positions, const int* slot_map,
                                     void* q_out, void* pages, long long page_stride, int page_size, int num_pages,
-                                    int nh, int nkv, int hd, int T, int has_kv, int* status, cudaStream_t stream) {
+                                    int nh, int nkv, int hd, int T, int has_kv, int rot_dim, int interleaved, int* status,
+                                    cudaStream_t stream) {
     if (T == 0) return 0;
+    VCB_CHECK_ARG(rot_dim >= 0 && rot_dim <= hd && rot_dim % 2 == 0,
+                  "qknorm_rope_kvwrite: %d rotated lanes of a head of %d (an even number up to head_dim)", rot_dim, hd);
     VCB_CHECK_ARG(hd > 0 && hd % 2 == 0 && hd <= VCB_MAX_HEAD_DIM,
                   "qknorm_rope_kvwrite: head_dim %d must be even and <= %d", hd, VCB_MAX_HEAD_DIM);
     VCB_CHECK_ARG(nh > 0 && nkv > 0 && page_size > 0 && S >= 1, "qknorm_rope_kvwrite: bad sizes nh=%d nkv=%d page=%d S=%d",
                   nh, nkv, page_size, S);
-    if (hd == 128 && in_dtype == VCB_BF16 && out_dtype == VCB_BF16 && S == 1 && ((uintptr_t)qkv % 4 == 0) &&
+    if (hd == 128 && rot_dim == hd && !interleaved && in_dtype == VCB_BF16 && out_dtype == VCB_BF16 && S == 1 && ((uintptr_t)qkv % 4 == 0) &&
         ((uintptr_t)q_out % 4 == 0) && ((uintptr_t)pages % 4 == 0)) {
         qknorm_rope_kvwrite_hd128_kernel<<<T, 256, 0, stream>>>(
             (const __nv_bfloat16*)qkv, qw, kw, w_dtype, use_norm, eps, cos_sin, max_pos, positions, slot_map,
@@ -616,7 +626,7 @@ VCB_API int vcb_qknorm_rope_kvwrite(const void* qkv, int in_dtype, int S, long l
 #define VCB_QK_LAUNCH(TIN, TOUT)                                                                                      \
     launch_pdl(qknorm_rope_kvwrite_kernel<TIN, TOUT>, dim3((unsigned)blocks), dim3(wpb * 32), 0, stream,                 \
         (const TIN*)qkv, S, (size_t)s_stride, qw, kw, w_dtype, use_norm, eps, cos_sin, max_pos, positions, slot_map,   \
-        (TOUT*)q_out, (TOUT*)pages, page_stride, page_size, num_pages, nh, nkv, hd, T, has_kv, status)
+        (TOUT*)q_out, (TOUT*)pages, page_stride, page_size, num_pages, nh, nkv, hd, T, has_kv, rot_dim, interleaved, status)
     if (in_dtype == VCB_F32 && out_dtype == VCB_F32) VCB_QK_LAUNCH(float, float);
     else if (in_dtype == VCB_F32) VCB_QK_LAUNCH(float, __nv_bfloat16);
     else if (out_dtype == VCB_BF16) VCB_QK_LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -646,5 +656,44 @@ VCB_API int vcb_scatter_i32(int* dst, const int* idx, const int* val, const int*
     if (capacity == 0) return 0;
     launch_pdl(scatter_i32_kernel, dim3((capacity + 255) / 256), dim3(256), 0, stream, dst, idx, val, count, capacity, dst_size);
     VCB_CHECK_LAUNCH("scatter_i32");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Fixed-size per-request state: the state of every request whose first tokens arrive in this step (its entry
+// starts at position 0) is set to the state's initial value, in every cache of the group.  On the device, so that
+// a captured step does it too.  state: [caches][slots][row] of 2- or 4-byte elements; grid (entries, caches).
+// ---------------------------------------------------------------------------
+template <typename E>
+__global__ void state_reset_kernel(E* __restrict__ state, long long cache_stride, long long slot_stride, long long row,
+                                   int num_slots, const int* __restrict__ slots, const int* __restrict__ q_len,
+                                   const int* __restrict__ ctx_len, E value, int* status) {
+    pdl_trigger();
+    pdl_wait();
+    const int e = blockIdx.x;
+    if (q_len[e] <= 0 || ctx_len[e] != q_len[e]) return;     // empty, or a request that is further on than its start
+    const int slot = slots[e];
+    if (slot < 0 || slot >= num_slots) {
+        if (threadIdx.x == 0) atomicOr(status, VCB_STATUS_BAD_ITEM);
+        return;
+    }
+    E* dst = state + (size_t)blockIdx.y * cache_stride + (size_t)slot * slot_stride;
+    for (long long i = threadIdx.x; i < row; i += blockDim.x) dst[i] = value;
+}
+
+VCB_API int vcb_state_reset(void* state, int elem_bytes, long long cache_stride, long long slot_stride, long long row,
+                            int n_caches, int num_slots, const int* slots, const int* q_len, const int* ctx_len,
+                            int n_entries, unsigned int value_bits, int* status, cudaStream_t stream) {
+    if (n_entries == 0 || n_caches == 0 || row == 0) return 0;
+    VCB_CHECK_ARG(elem_bytes == 2 || elem_bytes == 4, "state_reset: elements of %d bytes (2 or 4)", elem_bytes);
+    VCB_CHECK_ARG(status != nullptr, "state_reset: a status word is required");
+    const int threads = row >= 256 ? 256 : 64;
+    if (elem_bytes == 4)
+        launch_pdl(state_reset_kernel<unsigned int>, dim3(n_entries, n_caches), dim3(threads), 0, stream, (unsigned int*)state,
+                   cache_stride, slot_stride, row, num_slots, slots, q_len, ctx_len, value_bits, status);
+    else
+        launch_pdl(state_reset_kernel<unsigned short>, dim3(n_entries, n_caches), dim3(threads), 0, stream, (unsigned short*)state,
+                   cache_stride, slot_stride, row, num_slots, slots, q_len, ctx_len, (unsigned short)value_bits, status);
+    VCB_CHECK_LAUNCH("state_reset");
     return 0;
 }

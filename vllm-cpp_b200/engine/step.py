@@ -140,7 +140,7 @@ class StepContext:
         for g in runner.layout.groups:
             if g.paged:
                 k = g.runtime_index
-                self.groups.append(GroupContext(runner.page_size, g.spec.window, runner.tables[k], v(f"slot_map{k}"),
+                self.groups.append(GroupContext(runner.page_sizes[k], g.spec.window, runner.tables[k], v(f"slot_map{k}"),
                                                 v(f"upd_count{k}"), v(f"upd_idx{k}"), v(f"upd_val{k}"), layout.U))
             else:
                 self.groups.append(None)
@@ -198,10 +198,11 @@ class ModelRunner:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.vocab_size = model.spec.vocab_size
         self.max_positions = min(max_model_len or model.spec.max_positions, model.spec.max_positions)
-        self.max_blocks = -(-self.max_positions // page_size)
         n_paged = len(self.layout.paged)
-        self.tables = [torch.full((num_slots, self.max_blocks), -1, dtype=torch.int32, device=self.device)
-                       for _ in range(n_paged)]
+        # each paged group has pages of its own size (the engine's unless its caches asked for another)
+        self.page_sizes = [self.layout.page_size_of(g, page_size) for g in self.layout.paged]
+        self.max_blocks = [-(-self.max_positions // ps) for ps in self.page_sizes]
+        self.tables = [torch.full((num_slots, mb), -1, dtype=torch.int32, device=self.device) for mb in self.max_blocks]
         self._uploaded = [[0] * num_slots for _ in range(n_paged)]   # table entries of each slot already on the device
         self.cuda_graphs = cuda_graphs and self.device.type == "cuda" and getattr(model, "capturable", True)
         self._graphs: collections.OrderedDict[tuple, tuple] = collections.OrderedDict()   # least recently used first
@@ -245,12 +246,12 @@ class ModelRunner:
                     self._uploaded[g][e.slot] = 0     # a request that starts (again) from nothing
                 tab = e.tables[g]
                 have = self._uploaded[g][e.slot]
-                need = -(-(e.start_pos + len(e.tokens)) // self.page_size)
+                need = -(-(e.start_pos + len(e.tokens)) // self.page_sizes[g])
                 if need > len(tab):
                     raise ValueError(f"the block table of group {g} does not reach position "
                                      f"{e.start_pos + len(e.tokens) - 1}")
                 for b in range(have, need):
-                    idx.append(e.slot * self.max_blocks + b)
+                    idx.append(e.slot * self.max_blocks[g] + b)
                     val.append(tab[b])
                 self._uploaded[g][e.slot] = max(have, need)
             ups.append((idx, val))
@@ -278,8 +279,8 @@ class ModelRunner:
         packed[o["ctx_len"][0]:o["ctx_len"][0] + E] = [e.start_pos + n for e, n in zip(entries, lens)]
         packed[o["slots"][0]:o["slots"][0] + E] = [e.slot for e in entries]
         packed[o["logit_rows"][0]:o["logit_rows"][0] + len(rows)] = rows
-        ps = self.page_size
         for g in range(len(self.tables)):
+            ps = self.page_sizes[g]
             sm = packed[o[f"slot_map{g}"][0]:o[f"slot_map{g}"][1]]
             sm[:] = -1
             for i, e in enumerate(entries):
@@ -302,6 +303,9 @@ class ModelRunner:
         return packed, facts
 
     def _apply_table_updates(self, ctx: StepContext):
+        """What a step does on the device before the model runs: new block-table entries, and the initial state of
+        requests that start in this step."""
+        self.cache.reset_state(ctx)
         for k, table in enumerate(self.tables):
             g = next(gc for gc, grp in zip(ctx.groups, self.layout.groups) if grp.paged and grp.runtime_index == k)
             if g.upd_capacity:
@@ -358,7 +362,7 @@ class ModelRunner:
 
     def _mixed_updates(self, singles: int, rows: int) -> int:
         """Block-table entries that a captured mixed step's buffer has room for."""
-        return singles + (rows - singles) // self.page_size + 2 * self.MIXED_PORTIONS
+        return singles + (rows - singles) // min(self.page_sizes + [self.page_size]) + 2 * self.MIXED_PORTIONS
 
     def rows_capacity(self, entries) -> int:
         """Rows of logits that the step running these entries computes: the wanted ones, or more where a captured
@@ -374,7 +378,7 @@ class ModelRunner:
 
     def _portion_updates(self, portion: int) -> int:
         """Block-table entries that a captured portion's buffer has room for: the pages its tokens can touch."""
-        return portion // self.page_size + 2
+        return portion // min(self.page_sizes + [self.page_size]) + 2
 
     # ------------------------------------------------------------------ running
     def step(self, entries: list[StepEntry], check: bool = True, user=None, post=None, post_key=None):
@@ -389,7 +393,6 @@ class ModelRunner:
         if not entries:
             return None
         self._validate(entries)
-        self.cache.reset_state([e.slot for e in entries if e.start_pos == 0])
         updates = self._table_updates(entries)
         n_rows = sum(len(e.want) for e in entries)
         bucket = self.capture_size(entries)
@@ -437,7 +440,7 @@ class ModelRunner:
             # wanted of every entry, and room for the integers a sampler sends along
             S = min(self.num_slots, T)
             E = S + (1 if T > S else 0)
-            lay = MetaLayout(T, E, E, E + T // self.page_size + 2, len(self.tables), 8 * E + T)
+            lay = MetaLayout(T, E, E, E + T // min(self.page_sizes + [self.page_size]) + 2, len(self.tables), 8 * E + T)
             host = np.zeros(lay.size, dtype=np.int32)
             for g in range(len(self.tables)):
                 host[lay.offsets[f"slot_map{g}"][0]:lay.offsets[f"slot_map{g}"][1]] = -1
@@ -458,7 +461,7 @@ class ModelRunner:
 
     def _fill_decode(self, lay: MetaLayout, entries, updates, user):
         """_fill for single-token entries, without per-entry array work."""
-        E, B, ps = len(entries), lay.E, self.page_size
+        E, B = len(entries), lay.E
         pad = B - E
         toks = [e.tokens[0] for e in entries]
         pos = [e.start_pos for e in entries]
@@ -470,7 +473,7 @@ class ModelRunner:
             ux[:len(user)] = [int(v) for v in user]
         parts.append(ux)
         for g in range(len(self.tables)):
-            sm = []
+            sm, ps = [], self.page_sizes[g]
             for e, p in zip(entries, pos):
                 page = e.tables[g][p // ps]
                 if page < 0:

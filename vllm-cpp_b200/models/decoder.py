@@ -12,16 +12,15 @@ from __future__ import annotations
 
 from .. import workspace
 from ..parts.base import BuildContext, CacheSpec
-from ..parts.embedding import LMHead, TokenEmbedding
 from ..registry import ModelSpec, part_class
 from ..weights.loader import TensorSpec, WeightStore
 
 
 def _build_layer(lspec, build: BuildContext):
     parts = {}
-    for role, (pspec, sub) in lspec.parts.items():
-        family = {"norm1": "norm", "norm2": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}.get(role, role)
-        parts[role] = part_class(family, pspec.kind)(pspec.params, lspec.prefix + sub, build)
+    for role, entry in lspec.parts.items():
+        pspec, sub = entry[0], entry[1]
+        parts[role] = part_class(lspec.family_of(role), pspec.kind)(pspec.params, lspec.prefix + sub, build)
     return part_class("block", lspec.block.kind)(lspec.block.params, lspec.prefix, build, parts)
 
 
@@ -29,10 +28,14 @@ class DecoderModel:
     def __init__(self, spec: ModelSpec, build: BuildContext):
         self.spec = spec
         self.build = build
-        self.embedding = TokenEmbedding(spec.embed_tensor, spec.vocab_size, spec.hidden_size)
+        emb, head = spec.embedding_spec(), spec.head_spec()
+        self.embedding = part_class("embedding", emb.kind)(emb.params, "", build)
         self.layers = [_build_layer(l, build) for l in spec.layers]
-        self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm.params, spec.final_norm_prefix, build)
-        self.lm_head = LMHead(spec.lm_head_tensor, spec.vocab_size, spec.hidden_size, self.embedding)
+        self.final_norm = None
+        if spec.final_norm is not None:
+            self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm.params, spec.final_norm_prefix, build)
+        self.lm_head = part_class("head", head.kind)(head.params, "", build)
+        self.lm_head.attach(self.embedding)
         self.order = list(spec.order)
         for run in self.order:
             if not 0 <= run.layer < len(self.layers):
@@ -41,22 +44,25 @@ class DecoderModel:
     @property
     def capturable(self) -> bool:
         """Whether a decoding step of this model can be captured as a CUDA graph."""
-        return all(getattr(p, "capturable", True) for layer in self.layers for p in layer.parts.values())
+        parts = [p for layer in self.layers for p in layer.parts.values()] + [self.embedding, self.lm_head]
+        return all(getattr(p, "capturable", True) for p in parts)
 
     # ---- weights ----
     def tensor_specs(self) -> list[TensorSpec]:
         specs = list(self.embedding.tensor_specs())
         for layer in self.layers:
             specs += layer.tensor_specs()
-        specs += self.final_norm.tensor_specs() + self.lm_head.tensor_specs()
-        return specs
+        if self.final_norm is not None:
+            specs += self.final_norm.tensor_specs()
+        return specs + self.lm_head.tensor_specs()
 
     def load(self, store: WeightStore) -> None:
         store.check(self.tensor_specs())
         self.embedding.bind(store)
         for layer in self.layers:
             layer.bind(store)
-        self.final_norm.bind(store)
+        if self.final_norm is not None:
+            self.final_norm.bind(store)
         self.lm_head.bind(store)
 
     # ---- caches ----
@@ -92,5 +98,10 @@ class DecoderModel:
         workspace.end_runs()
         if ctx.n_rows == 0:
             return None
-        y = self.final_norm.forward(resid, pending, rows=ctx.logit_rows)
+        if self.final_norm is None:
+            # an architecture without a final norm: the head reads the wanted rows of the stream as they are
+            x = resid if pending is None else resid + (pending.sum(0) if pending.dim() == 3 else pending).float()
+            y = x[ctx.logit_rows.long()].to(self.build.compute_dtype)
+        else:
+            y = self.final_norm.forward(resid, pending, rows=ctx.logit_rows)
         return self.lm_head.forward(y, ctx.status)

@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import struct
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -57,7 +58,7 @@ def _declare(L):
         "vcb_embed_gather": [P, I, P, P, I, I, I, P, P],
         "vcb_add_rmsnorm": [P, P, I, I, LL, P, I, F, P, I, P, I, I, P],
         "vcb_swiglu": [P, I, I, LL, P, I, I, I, P],
-        "vcb_qknorm_rope_kvwrite": [P, I, I, LL, I, P, P, I, I, F, P, I, P, P, P, P, LL, I, I, I, I, I, I, I, P, P],
+        "vcb_qknorm_rope_kvwrite": [P, I, I, LL, I, P, P, I, I, F, P, I, P, P, P, P, LL, I, I, I, I, I, I, I, I, I, P, P],
         "vcb_gemm_bf16_tn": [P, P, P, I, I, I, I, LL, LL, LL, I, LL, P, P],
         "vcb_gemm_bf16_tn_shape": [P, P, P, I, I, I, I, LL, LL, LL, I, LL, I, P, P],
         "vcb_gemm_effective_splits": [I, I],
@@ -67,6 +68,7 @@ def _declare(L):
         "vcb_gemm_bf16_plain": [P, P, P, I, I, I, I, LL, LL, LL, P],
         "vcb_attn_paged": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, P],
         "vcb_scatter_i32": [P, P, P, P, I, LL, P],
+        "vcb_state_reset": [P, I, LL, LL, LL, I, I, P, P, P, I, ctypes.c_uint, P, P],
         "vcb_attn_mma": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, F, P, I, P],
         "vcb_attn_mma_supported": [I, I],
         "vcb_attn_mma_fused_supported": [I, I, I],
@@ -206,15 +208,18 @@ def swiglu(gate_up, out):
 
 
 def qknorm_rope_kvwrite(qkv, q_weight, k_weight, eps, cos_sin, positions, slot_map, q_out, pages, nh, nkv, hd,
-                        status, has_kv=True, use_norm=True):
+                        status, has_kv=True, use_norm=True, rotary_dim=None, interleaved=False):
     """qkv [T, W] or [S, T, W] (32-bit partial sums); pages: one layer's [num_pages, 2, nkv, page_size, hd];
-    slot_map int32 [T] = page * page_size + offset or -1."""
+    slot_map int32 [T] = page * page_size + offset or -1.  ``rotary_dim`` (default: hd) lanes of a head are
+    rotated, paired (i, i + rotary_dim/2) or, with ``interleaved``, (2i, 2i+1); cos_sin is [positions, rotary_dim]."""
+    rotary_dim = hd if rotary_dim is None else int(rotary_dim)
     S, stride = _partials(qkv, "qkv")
     _need(cos_sin, "cos_sin", torch.float32); _need(positions, "positions", torch.int32); _need(q_out, "q_out")
     T = qkv.shape[-2]
     width = (nh + (2 * nkv if has_kv else 0)) * hd
     assert qkv.shape[-1] == width, (qkv.shape, width)
-    assert cos_sin.shape[1] == hd
+    if cos_sin.shape[1] != rotary_dim:
+        raise KernelError(f"the table of angles has {cos_sin.shape[1]} columns, {rotary_dim} lanes are to be rotated")
     wdt = F32
     if use_norm:
         _need(q_weight, "q_norm weight"); wdt = _dt(q_weight)
@@ -228,7 +233,8 @@ def qknorm_rope_kvwrite(qkv, q_weight, k_weight, eps, cos_sin, positions, slot_m
         page_stride = pages.stride(0)
     _call("vcb_qknorm_rope_kvwrite", _p(qkv), _dt(qkv), S, stride, _dt(q_out), _p(q_weight), _p(k_weight), wdt,
           int(use_norm), float(eps), _p(cos_sin), cos_sin.shape[0], _p(positions), _p(slot_map), _p(q_out), _p(pages),
-          page_stride, max(page_size, 1), num_pages, nh, nkv, hd, T, int(has_kv), _p(status), _stream())
+          page_stride, max(page_size, 1), num_pages, nh, nkv, hd, T, int(has_kv), rotary_dim, int(bool(interleaved)),
+          _p(status), _stream())
 
 
 def gemm_bf16_plain(x, w, out):
@@ -364,6 +370,26 @@ def scatter_i32(dst, idx, val, count, capacity):
     _need(dst, "dst", torch.int32); _need(idx, "idx", torch.int32); _need(val, "val", torch.int32)
     _need(count, "count", torch.int32)
     _call("vcb_scatter_i32", _p(dst), _p(idx), _p(val), _p(count), capacity, dst.numel(), _stream())
+
+
+def state_reset(state, slots, q_len, ctx_len, n_entries, value, status):
+    """state [caches, slots, ...]: the rows of the requests whose entries start at position 0 (ctx_len == q_len > 0)
+    are filled with ``value``; all on the device (a captured step includes it)."""
+    _need(state, "state"); _need(slots, "slots", torch.int32); _need(q_len, "q_len", torch.int32); _need(ctx_len, "ctx_len", torch.int32)
+    if state.dim() < 2:
+        raise KernelError("a state tensor is [caches, slots, ...]")
+    n_caches, num_slots = state.shape[0], state.shape[1]
+    row = state[0, 0].numel()
+    if state.dtype == torch.float32:
+        bits = struct.unpack("<I", struct.pack("<f", float(value)))[0]
+    elif state.dtype == torch.bfloat16:
+        bits = struct.unpack("<I", struct.pack("<f", float(torch.tensor(float(value)).to(torch.bfloat16).float())))[0] >> 16
+    elif state.dtype == torch.int32:
+        bits = int(value) & 0xFFFFFFFF
+    else:
+        raise KernelError(f"state of type {state.dtype} (float32, bfloat16 or int32)")
+    _call("vcb_state_reset", _p(state), state.element_size(), state.stride(0), state.stride(1), row, n_caches, num_slots,
+          _p(slots), _p(q_len), _p(ctx_len), n_entries, bits, _p(status), _stream())
 
 
 def attn_mma_supported(dtype: torch.dtype, hd: int) -> bool:

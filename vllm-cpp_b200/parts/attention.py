@@ -120,6 +120,9 @@ class GQAAttention(Mixer):
             raise ValueError(f"head_dim {self.hd} is not supported: the kernels take multiples of 16 from 16 to 256")
         pos: PartSpec = p["position"]
         self.rope = part_class("position", pos.kind)(pos.params, prefix, build)
+        # what the position part asks of the norm-rotate-store kernel (a part without these wants all lanes, in halves)
+        self.rotary_dim = int(getattr(self.rope, "rotary_dim", self.hd))
+        self.interleaved = getattr(self.rope, "pairing", "half") == "interleaved"
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
 
     def cache_spec(self):
@@ -165,6 +168,7 @@ class GQAAttention(Mixer):
         # A step of single tokens only, run kernel by kernel: the attention kernel norms, rotates and stores for itself,
         # straight from the projection's k-slice partial sums (one launch less in every layer).
         if ((FUSED_DECODE == 2 or (FUSED_DECODE == 1 and not getattr(ctx, "static", False))) and mma and plan.decode_only and self.has_kv and qkv.dim() == 3 and nh // nkv <= MMA_DECODE_ROWS
+                and self.rotary_dim == hd and not self.interleaved
                 and ops.attn_mma_fused_supported(x.dtype, hd, cache.pages.shape[3])):
             S = plan.nslices
             part_o = part_ml = None
@@ -179,7 +183,8 @@ class GQAAttention(Mixer):
         q = workspace.empty((T, nh * hd), x.dtype, x.device)
         ops.qknorm_rope_kvwrite(qkv, self.q_norm_w, self.k_norm_w, self.eps, self.rope.table, ctx.positions,
                                 group.slot_map, q, cache.pages, nh, nkv, hd, ctx.status,
-                                has_kv=self.has_kv, use_norm=self.qk_norm)
+                                has_kv=self.has_kv, use_norm=self.qk_norm, rotary_dim=self.rotary_dim,
+                                interleaved=self.interleaved)
         if plan.n_dec:
             S = plan.nslices
             part_o = part_ml = None

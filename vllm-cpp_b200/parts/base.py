@@ -47,7 +47,9 @@ class CacheSpec:
 
     kind "kv":    keys and values per token, ``[2, num_kv_heads, head_dim]`` each
                   token, in pages; ``window`` > 0 means only the last ``window``
-                  keys are ever read, so older pages may be given back.
+                  keys are ever read, so older pages may be given back;
+                  ``page_size`` > 0 asks for pages of that many tokens instead of
+                  the engine's (caches that differ in it get pools of their own).
     kind "state": a block of fixed size per request, ``shape`` of ``dtype``,
                   addressed by the request's slot."""
     kind: str
@@ -56,6 +58,8 @@ class CacheSpec:
     window: int = 0
     shape: tuple = ()
     dtype: str = "float32"
+    page_size: int = 0
+    initial_value: float = 0.0    # kind "state": what a request's state holds before its first token
 
 
 class Part:

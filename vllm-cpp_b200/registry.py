@@ -16,7 +16,9 @@ from typing import Any, Callable
 
 from .config.base import ConfigError, ModelConfig
 
-PART_FAMILIES = ("mixer", "feed_forward", "norm", "position", "block")
+PART_FAMILIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
+# the family of a layer's part when its LayerSpec names none: by the role it plays in the block
+ROLE_FAMILIES = {"norm1": "norm", "norm2": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
 
 
 @dataclass(frozen=True)
@@ -44,7 +46,14 @@ class LayerSpec:
     """One layer: the arrangement (block) and the parts it arranges; ``prefix`` starts its tensor names."""
     prefix: str
     block: PartSpec
-    parts: dict  # role -> (PartSpec, sub-prefix), e.g. {"norm1": (…, "input_layernorm."), "mixer": (…, "self_attn."), …}
+    # role -> (PartSpec, sub-prefix) or (PartSpec, sub-prefix, family), e.g. {"norm1": (…, "input_layernorm."),
+    # "mixer": (…, "self_attn."), …}.  Without a family the role's usual one is taken (ROLE_FAMILIES), else the role's
+    # own name: a block of another arrangement names its roles and their families as it likes.
+    parts: dict
+
+    def family_of(self, role: str) -> str:
+        entry = self.parts[role]
+        return entry[2] if len(entry) > 2 else ROLE_FAMILIES.get(role, role)
 
 
 @dataclass(frozen=True)
@@ -61,16 +70,30 @@ class LayerRun:
 
 @dataclass(frozen=True)
 class ModelSpec:
+    """What a model is made of.  The embedding and the head are parts like the rest: ``embedding`` and ``head`` name
+    them (families "embedding" and "head"); left out, they are the plain token embedding over ``embed_tensor`` and
+    the plain LM head over ``lm_head_tensor`` (None: tied to the embedding table).  ``final_norm`` None: the head
+    reads the residual stream as it is."""
     hidden_size: int
     vocab_size: int
     max_positions: int
-    embed_tensor: str
+    embed_tensor: str | None
     layers: tuple            # of LayerSpec
     order: tuple             # of LayerRun
-    final_norm: PartSpec
+    final_norm: PartSpec | None
     final_norm_prefix: str
     lm_head_tensor: str | None   # None: the embedding table is the LM head
     stop_ids: tuple = ()
+    embedding: PartSpec | None = None
+    head: PartSpec | None = None
+
+    def embedding_spec(self) -> PartSpec:
+        return self.embedding or PartSpec("token_embedding", {"tensor": self.embed_tensor, "vocab_size": self.vocab_size,
+                                                              "hidden_size": self.hidden_size})
+
+    def head_spec(self) -> PartSpec:
+        return self.head or PartSpec("lm_head", {"tensor": self.lm_head_tensor, "vocab_size": self.vocab_size,
+                                                 "hidden_size": self.hidden_size})
 
 
 @dataclass(frozen=True)

@@ -31,6 +31,7 @@ class TensorSpec:
     shape: tuple
     role: str = "matrix"     # "matrix" (operand of a matrix product), "vector" (gains), "table" (integers)
     optional: bool = False
+    high: int = 0            # role "table": entries lie in [0, high) (what the random-weights mode draws from)
 
 
 class WeightStore:

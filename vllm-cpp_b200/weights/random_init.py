@@ -32,7 +32,9 @@ def _generate(spec: TensorSpec, seed: int, device="cpu") -> torch.Tensor:
     if spec.role == "vector":
         return 1.0 + GAIN_STD * torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
     if spec.role == "table":
-        raise ValueError(f"no random rule for integer table '{spec.name}'")
+        if spec.high < 1:
+            raise ValueError(f"integer table '{spec.name}' does not say what range its entries have (TensorSpec.high)")
+        return torch.randint(0, spec.high, tuple(spec.shape), generator=g, dtype=torch.int32, device=device)
     return MATRIX_STD * torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
 
 
@@ -49,7 +51,8 @@ def write_random_model(config, seed: int, out_dir, dtype: str = "bfloat16") -> P
     cfg = config.to_dict()
     cfg["torch_dtype"] = dtype
     (out_dir / "config.json").write_text(json.dumps(cfg, indent=2))
-    tensors = {s.name: _generate(s, seed).to(store_dtype) for s in expected_tensors(config)}
+    tensors = {s.name: (_generate(s, seed) if s.role == "table" else _generate(s, seed).to(store_dtype))
+               for s in expected_tensors(config)}
     write_safetensors(out_dir / "model.safetensors", tensors, {"format": "pt", "seed": str(seed)})
     return out_dir
 
@@ -90,3 +93,6 @@ class RandomWeightStore(WeightStore):
     def vector(self, name):
         t = self._draw(name)
         return t.float() if self.compute_dtype == torch.float32 else t
+
+    def table(self, name):
+        return _generate(self._specs[name], self._seed, self.device)
