@@ -1,40 +1,59 @@
-"""Per-kernel timings at the benchmark model's layer sizes (Qwen3-8B shape), on one GPU.
+#!/usr/bin/env python3
+"""Per-kernel timings at a model's layer sizes, on one GPU.
 
-    python -m vllm_cpp_b200.microbench gemm [T ...]     the four projections (and lm_head) at T tokens
-    python -m vllm_cpp_b200.microbench attention        decode attention over a paged cache; prompt attention
-    python -m vllm_cpp_b200.microbench small            add+norm, norm-rotate-store, SiLU-gate
+    python microbench.py [--model 8b|4b|14b|CONFIG.json] [--peaks FILE] gemm [T ...]   the four projections (and lm_head) at T tokens
+    python microbench.py [...] attention        decode attention over a paged cache; prompt attention
+    python microbench.py [...] small            add+norm, norm-rotate-store, SiLU-gate
+    python microbench.py [...] gemm --library   the products beside the library's (torch.mm), for comparison
+
+The sizes come from a Qwen3 configuration: one of the three serving shapes by name (default 8b) or a config.json.
 
 How it times: every launch is captured ``reps`` times in a CUDA graph (so that launch overhead does not set the
 floor), the graph is replayed ten times between CUDA events, and the median replay divided by ``reps`` is reported.
 Products rotate over copies of their weights that together exceed L2, so that weights come from HBM as in a step.
 ``VCB_MICROBENCH_PAGE`` sets the page size of the attention runs (default 16).
-Each line also gives the time the same bytes or flops take at the peaks in ``MEASURED_PEAKS.json`` (when present
-beside the repository's bench.py; otherwise the stated fallbacks) and, for products, the library's time.
+Each line also gives the time the same bytes or flops take at the peaks of ``--peaks FILE`` (JSON with ``hbm_gbs``
+and ``bf16_tflops``; default: MEASURED_PEAKS.json in the current folder if there is one, else 6650 GB/s and
+1590 TFLOP/s) and, with ``--library``, the library's time for the same product.
 """
 from __future__ import annotations
 
+import argparse
 import json
 import os
 import sys
 from pathlib import Path
 
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
 import torch
 
-from . import ops
-from .parts import attention as A
-from .parts.linear import choose_splits
+from vllm_cpp_b200 import Qwen3Config, ops
+from vllm_cpp_b200.parts import attention as A
+from vllm_cpp_b200.parts.linear import choose_splits
 
-SHAPES = {"qkv": (6144, 4096), "o": (4096, 4096), "gate_up": (24576, 4096), "down": (4096, 12288), "lm_head": (151936, 4096)}
-NH, NKV, HD, PAGE = 32, 8, 128, int(os.environ.get("VCB_MICROBENCH_PAGE", "16"))
+NAMED = {
+    "8b": dict(hidden_size=4096, intermediate_size=12288, num_attention_heads=32, num_key_value_heads=8, head_dim=128),
+    "14b": dict(hidden_size=5120, intermediate_size=17408, num_attention_heads=40, num_key_value_heads=8, head_dim=128),
+    "4b": dict(hidden_size=2560, intermediate_size=9728, num_attention_heads=32, num_key_value_heads=8, head_dim=128),
+}
+PAGE = int(os.environ.get("VCB_MICROBENCH_PAGE", "16"))
+# set from the command line in main()
+SHAPES: dict = {}
+NH = NKV = HD = 0
+PEAKS = (6650.0, 1590.0)
+LIBRARY = False
+
+
+def set_model(cfg: Qwen3Config) -> None:
+    global SHAPES, NH, NKV, HD
+    NH, NKV, HD = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    H, I = cfg.hidden_size, cfg.intermediate_size
+    SHAPES = {"qkv": ((NH + 2 * NKV) * HD, H), "o": (H, NH * HD), "gate_up": (2 * I, H), "down": (H, I), "lm_head": (cfg.vocab_size, H)}
 
 
 def peaks():
-    f = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
-    try:
-        d = json.loads(f.read_text())
-        return float(d["hbm_gbs"]), float(d["bf16_tflops"])
-    except (OSError, KeyError, ValueError):
-        return 6650.0, 1590.0
+    return PEAKS
 
 
 def timeit(fn, reps: int = 20, iters: int = 10) -> float:
@@ -81,7 +100,7 @@ def bench_gemm(tokens, dev, status):
             if name == "gate_up" and T > 128:
                 act = torch.empty(T, M // 2, dtype=torch.bfloat16, device=dev)
                 extra = f"  with SiLU-gate {timeit(lambda k: ops.gemm_bf16_swiglu(ws[k % ncopy], x, act, status)):.1f}"
-            lib = timeit(lambda k: torch.mm(x, ws[k % ncopy].t()))
+            lib = timeit(lambda k: torch.mm(x, ws[k % ncopy].t())) if LIBRARY else float("nan")
             print(f"product {name:8s} T={T:5d} k-slices {S}: {ours:7.1f} us{extra}   library {lib:7.1f}   "
                   f"at HBM peak {M * K * 2 / hbm / 1e3:6.1f}   at bf16 peak {2.0 * M * K * T / tc / 1e6:6.1f}", flush=True)
             del ws, x
@@ -133,7 +152,7 @@ def bench_attention(dev, status):
 
 def bench_small(dev, status):
     hbm, _ = peaks()
-    H, I = 4096, 12288
+    H, I = SHAPES["o"][0], SHAPES["down"][1]
     for T in (8, 64, 2048):
         resid = torch.randn(T, H, device=dev)
         w = torch.ones(H, device=dev).to(torch.bfloat16)
@@ -158,14 +177,35 @@ def bench_small(dev, status):
 
 
 def main(argv):
+    global PEAKS, LIBRARY
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--model", default="8b", help="8b, 4b, 14b, or a config.json of the Qwen3 architecture")
+    ap.add_argument("--peaks", default=None, help="JSON file with hbm_gbs and bf16_tflops")
+    ap.add_argument("--library", action="store_true", help="time the library's product (torch.mm) beside each of ours")
+    ap.add_argument("what", nargs="?", default="gemm", choices=["gemm", "attention", "small"])
+    ap.add_argument("tokens", nargs="*", type=int)
+    args = ap.parse_args(argv)
+    if args.model in NAMED:
+        cfg = Qwen3Config(vocab_size=151936, num_hidden_layers=1, max_position_embeddings=40960, **NAMED[args.model])
+    else:
+        cfg = Qwen3Config.from_dict(json.loads(Path(args.model).read_text()))
+    set_model(cfg)
+    pfile = Path(args.peaks) if args.peaks else Path("MEASURED_PEAKS.json")
+    if pfile.is_file():
+        d = json.loads(pfile.read_text())
+        PEAKS = (float(d["hbm_gbs"]), float(d["bf16_tflops"]))
+    elif args.peaks:
+        print(f"microbench: {pfile} not found", file=sys.stderr)
+        return 2
+    LIBRARY = args.library
     if not torch.cuda.is_available():
         print("microbench: needs a CUDA device", file=sys.stderr)
         return 2
     dev = torch.device("cuda:0")
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    what = argv[0] if argv else "gemm"
+    what = args.what
     if what == "gemm":
-        bench_gemm([int(a) for a in argv[1:]] or [8, 64, 256, 2048], dev, status)
+        bench_gemm(args.tokens or [8, 64, 256, 2048], dev, status)
     elif what == "attention":
         bench_attention(dev, status)
     elif what == "small":

@@ -257,3 +257,18 @@ def test_steps_take_their_buffers_from_the_workspace(model_dirs):
     assert llm.runner.graph_replays == 0
     assert counts[49] == counts[9], (counts[9], counts[49], overflows[9], overflows[49])
     assert overflows[49] == overflows[9]
+
+
+def test_profile_of_kernel_groups(model_dirs, plain_models):
+    """EngineConfig(profile=True): the same tokens, every step kernel by kernel, and the time of each group of
+    kernels (embedding, each layer's mixer and feed-forward, head, sampling) summed in the engine's statistics."""
+    prompts = [random_tokens(384, n, 40 + i) for i, n in enumerate((12, 50))]
+    llm = make_llm(model_dirs["B"], "B", profile=True)
+    got = llm.generate(prompts, 6, 0.0, 1.0, repeat_penalty=1.0)
+    assert got == [plain_generate(plain_models, "B", p, 6) for p in prompts]
+    st = llm.stats()
+    assert llm.runner.graph_replays == 0 and 0 < st.profiled_steps <= st.steps
+    assert {"embedding", "mixer", "feed_forward", "head", "sampling", "tables"} <= set(st.kernel_ms)
+    assert all(v > 0 for v in st.kernel_ms.values())
+    assert st.preemptions == 0                       # the scheduler's own counters are still there
+    assert make_llm(model_dirs["B"], "B").stats().kernel_ms == {}

@@ -830,3 +830,28 @@ def test_bf16_product_of_unaligned_inner_size(out_dtype):
     y = matmul_tn(x, w, torch.zeros(1, dtype=torch.int32, device=dev()), out_dtype=out_dtype, allow_partials=True)
     assert y.shape == (T, N) and y.dtype == out_dtype
     torch.testing.assert_close(y.double(), x.double() @ w.double().T, rtol=1e-2, atol=1e-1)
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_harmless():
+    """Every TMA and tcgen05 kernel of the library waits on mbarriers through one helper whose waits are bounded by
+    the clock.  Here that helper waits, for a millisecond at most, on a barrier that nothing arrives at: the wait
+    answers false, the status word gets the wait-timeout bit, the block's abort flag is up (a later wait in the block
+    gives up at once), check_status raises with the bit's text and clears it, and the next ordinary kernels run."""
+    from vllm_cpp_b200 import ops
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    got = ops.selftest_wait_timeout(2_000_000, status)
+    assert got == [0, 1, 0, 1], got
+    assert status.item() == 4
+    with pytest.raises(ops.KernelError, match="bounded wait"):
+        ops.check_status(status)
+    assert status.item() == 0
+    # the context is as usable as before: a TMA / tcgen05 product right after
+    x = torch.randn(8, 256, device=dev()).to(torch.bfloat16)
+    w = torch.randn(128, 256, device=dev()).to(torch.bfloat16)
+    out = torch.empty(8, 128, device=dev(), dtype=torch.float32)
+    ops.gemm_bf16_tn(w, x, out, 1, status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    torch.testing.assert_close(out.double(), x.double() @ w.double().T, rtol=1e-3, atol=1e-3)
+    with pytest.raises(ops.KernelError):
+        ops.selftest_wait_timeout(10 ** 12, status)       # no long waits on request

@@ -43,6 +43,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-step-tokens", type=int, default=2048)
     ap.add_argument("--stop-id", type=int, action="append", default=None)
     ap.add_argument("--ignore-eos", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="time the groups of kernels of every step (steps then run kernel by kernel); printed at the end, and per step with --debug")
     ap.add_argument("--random", metavar="CONFIG.json", default=None,
                     help="write random weights for this configuration into <model_path> first")
     ap.add_argument("--random-seed", type=int, default=0)
@@ -71,7 +73,8 @@ def main(argv=None) -> int:
     t0 = time.time()
     max_tokens = -(-args.max_tokens // args.page_size) * args.page_size
     llm = LLM(args.model_path, engine=EngineConfig(dtype=args.dtype, page_size=args.page_size, max_tokens=max_tokens,
-                                                   max_num_seqs=args.max_batch, max_step_tokens=args.max_step_tokens))
+                                                   max_num_seqs=args.max_batch, max_step_tokens=args.max_step_tokens,
+                                                   profile=args.profile))
     llm.debug = args.debug
     print(f"Model loaded in {int((time.time() - t0) * 1000)} ms", file=sys.stderr)
     for i, p in enumerate(prompts):
@@ -97,6 +100,12 @@ def main(argv=None) -> int:
     print(f"\n--- Generation complete ---\nTokens generated: {n}\nTotal time: {int(dt * 1000)} ms", file=sys.stderr)
     if n:
         print(f"Speed: {dt * 1000 / n:.2f} ms/token", file=sys.stderr)
+    st = llm.stats()
+    if st.kernel_ms:
+        total = sum(st.kernel_ms.values())
+        print(f"Kernel groups over {st.profiled_steps} steps ({total:.1f} ms on the device):", file=sys.stderr)
+        for k, v in sorted(st.kernel_ms.items(), key=lambda kv: -kv[1]):
+            print(f"  {k:14s} {v:10.2f} ms  {100 * v / total:5.1f} %", file=sys.stderr)
     return 0
 
 

@@ -23,6 +23,8 @@ class EngineConfig:
     max_model_len: int | None = None   # longest request; default: the model's max positions
     device: str = "cuda:0"
     cuda_graphs: bool = True           # replay decode-only steps from captured graphs
+    profile: bool = False              # time the groups of kernels of every step (embedding, each layer's mixer and
+                                       # feed-forward, head, sampling) with CUDA events; steps then run kernel by kernel
 
     def __post_init__(self):
         if self.dtype not in DTYPES:

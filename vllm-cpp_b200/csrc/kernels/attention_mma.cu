@@ -24,6 +24,7 @@
 // on addresses; every wait is bounded and reports through the status word.  Other page sizes use cp.async
 // from all threads with two stages.
 #include "common.cuh"
+#include "mbarrier.cuh"
 #include "kv_tensor_map.h"
 
 #include <cuda.h>
@@ -78,8 +79,6 @@ struct AttnArgs {
     FusedQkv f;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
 }
@@ -111,38 +110,6 @@ template <int ROWS> __device__ __forceinline__ int swz(int r, int c) {
     return (c >> 3) * (ROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
 }
 
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-constexpr long long WAIT_CLOCKS = 2000000000ll;   // about a second
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (!mbar_try(bar, parity)) {
-        if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_CLOCKS) {
-            *abort_flag = 1;
-            atomicOr(status, VCB_STATUS_WAIT_TIMEOUT);
-            return false;
-        }
-    }
-    return true;
-}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -472,7 +439,7 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
         if (lane == 0 && *abort_flag) {   // let copies in flight land before the block goes away
             for (int i = max(0, armed - STAGES); i < armed; ++i) {
                 const long long t0 = clock64();
-                while (!mbar_try(full_bar(i % STAGES), (i / STAGES) & 1) && clock64() - t0 < WAIT_CLOCKS) {}
+                while (!mbar_try(full_bar(i % STAGES), (i / STAGES) & 1) && clock64() - t0 < VCB_WAIT_CLOCKS) {}
             }
         }
     }

@@ -27,6 +27,7 @@
 // All hand-offs are mbarriers; every wait is bounded by the clock, and a wait that runs out sets a bit in the
 // status word and an abort flag that the other roles see, after which the block frees its TMEM and returns.
 #include "common.cuh"
+#include "mbarrier.cuh"
 #include "kv_tensor_map.h"
 
 #include <cuda.h>
@@ -38,7 +39,6 @@ constexpr int BNK = 64;       // keys per tile
 constexpr int ROWS = 128;     // rows per block = TMEM lanes
 constexpr int ITEM_INTS = 6;  // entry, q0, nq, slice, nslices, decode index (as in attention_mma.cu)
 constexpr int NTHREADS = 192;
-constexpr long long WAIT_CLOCKS = 2000000000ll;   // about a second
 
 struct TcArgs {
     const __nv_bfloat16* q;
@@ -55,39 +55,6 @@ struct TcArgs {
     int* status;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the barrier did not flip within WAIT_CLOCKS or another role gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (!mbar_try(bar, parity)) {
-        if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_CLOCKS) {
-            *abort_flag = 1;
-            atomicOr(status, VCB_STATUS_WAIT_TIMEOUT);
-            return false;
-        }
-    }
-    return true;
-}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -329,7 +296,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                 for (int i = max(0, armed[is_v] - ns); i < armed[is_v]; ++i) {
                     const long long t0 = clock64();
                     const uint32_t fullb = is_v ? v_full(i % ns) : k_full(i % ns);
-                    while (!mbar_try(fullb, (i / ns) & 1) && clock64() - t0 < WAIT_CLOCKS) {}
+                    while (!mbar_try(fullb, (i / ns) & 1) && clock64() - t0 < VCB_WAIT_CLOCKS) {}
                 }
             }
         }

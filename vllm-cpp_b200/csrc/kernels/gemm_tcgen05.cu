@@ -27,6 +27,7 @@
 // the status word, raises an abort flag that the other roles see, and the block
 // still frees its TMEM and returns.  No cluster multicast anywhere.
 #include "common.cuh"
+#include "mbarrier.cuh"
 
 #include <cuda.h>
 
@@ -43,39 +44,7 @@ constexpr int BM = 128;   // output features per tile (TMEM lanes)
 constexpr int BK = 64;    // k per stage: 64 bf16 = 128 bytes = one swizzle span
 constexpr int UMMA_K = 16;
 constexpr int NTHREADS = 192;
-constexpr long long WAIT_CLOCKS = 2000000000ll;   // about a second
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the barrier did not flip within WAIT_CLOCKS or another role gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (!mbar_try(bar, parity)) {
-        if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_CLOCKS) {
-            *abort_flag = 1;
-            atomicOr(status, VCB_STATUS_WAIT_TIMEOUT);
-            return false;
-        }
-    }
-    return true;
-}
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
     asm volatile(
@@ -144,9 +113,6 @@ struct Smem {
     static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;   // + alignment slack
 };
 
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 
 // silu(z) = z / (1 + exp(-z)) with the fast exponential and division (a few ulp; the result is rounded to
 // bfloat16).  The exponent is capped so that the divisor stays where the fast division is defined; below
@@ -308,7 +274,7 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
                 // let the copies already in flight land before the block goes away
                 for (int i = max(0, armed - STAGES); i < armed; ++i) {
                     const long long t0 = clock64();
-                    while (!mbar_try(full_bar(i % STAGES), (i / STAGES) & 1) && clock64() - t0 < WAIT_CLOCKS) {}
+                    while (!mbar_try(full_bar(i % STAGES), (i / STAGES) & 1) && clock64() - t0 < VCB_WAIT_CLOCKS) {}
                 }
             }
         }
@@ -534,7 +500,7 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
             if (*abort_flag && rank == 0) {
                 for (int i = max(0, armed - STAGES); i < armed; ++i) {
                     const long long t0 = clock64();
-                    while (!mbar_try(full_bar(i % STAGES), (i / STAGES) & 1) && clock64() - t0 < WAIT_CLOCKS) {}
+                    while (!mbar_try(full_bar(i % STAGES), (i / STAGES) & 1) && clock64() - t0 < VCB_WAIT_CLOCKS) {}
                 }
             }
         }

@@ -35,6 +35,18 @@ class EngineOutput:
     preempted: list = field(default_factory=list)
 
 
+class EngineStats:
+    """The scheduler's counters by attribute, plus the profile of the kernel groups when it is switched on."""
+
+    def __init__(self, scheduler_stats, kernel_ms: dict, profiled_steps: int):
+        self._scheduler = scheduler_stats
+        self.kernel_ms = kernel_ms
+        self.profiled_steps = profiled_steps
+
+    def __getattr__(self, name):
+        return getattr(self._scheduler, name)
+
+
 class LLM:
     """One model on one GPU with its cache, scheduler and sampler."""
 
@@ -63,7 +75,7 @@ class LLM:
         self.max_model_len = min(ec.max_model_len or self.model.spec.max_positions, self.model.spec.max_positions)
         self.runner = ModelRunner(self.model, ec.page_size, ec.num_pages, ec.max_num_seqs, dtype, self.device,
                                   cuda_graphs=ec.cuda_graphs, max_model_len=self.max_model_len,
-                                  max_step_tokens=ec.max_step_tokens)
+                                  max_step_tokens=ec.max_step_tokens, profile=ec.profile)
         rt = runtime()
         self.scheduler = rt.Scheduler(self.runner.layout.runtime_groups(rt, ec.page_size, ec.num_pages),
                                       ec.max_num_seqs, ec.max_step_tokens, self.max_model_len)
@@ -116,7 +128,9 @@ class LLM:
             print(f"[step {self._step_index}] prompt_tokens={out.num_prompt_tokens} generation_tokens={out.num_generation_tokens} "
                   f"sampled={len(out.new_token_ids)} finished={sum(out.finished)} preempted={len(out.preempted)} "
                   f"waiting={self.scheduler.num_waiting()} running={self.scheduler.num_running()} free_pages={free} "
-                  f"ms={(time.perf_counter() - t0) * 1e3:.2f}", file=sys.stderr, flush=True)
+                  f"ms={(time.perf_counter() - t0) * 1e3:.2f}"
+                  + ("".join(f" {k}_ms={v:.3f}" for k, v in sorted(self.runner.profile.items())) if self.runner.profile else ""),
+                  file=sys.stderr, flush=True)
         self._step_index += 1
         return out
 
@@ -215,4 +229,7 @@ class LLM:
         return [results[r] for r in rids]
 
     def stats(self):
-        return self.scheduler.stats()
+        """The scheduler's counters (requests, tokens, steps, preemptions, ...) and, with ``EngineConfig(profile=True)``,
+        ``kernel_ms``: milliseconds per group of kernels (embedding, mixer, feed_forward, head, sampling, tables),
+        summed over ``profiled_steps`` steps."""
+        return EngineStats(self.scheduler.stats(), dict(self.runner.profile or {}), self.runner.profile_steps)

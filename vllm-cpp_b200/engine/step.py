@@ -145,6 +145,7 @@ class StepContext:
             else:
                 self.groups.append(None)
         self._plans: dict = {}
+        self._marks: list = []
         # host-side facts of the current step (refreshed by fill)
         self.entries: list[StepEntry] = []
         self.host_q_len, self.host_q_start, self.host_ctx_len, self.host_slots = [], [], [], []
@@ -159,6 +160,14 @@ class StepContext:
             dev = workspace.empty(host.shape, torch.int32, self.device)
         self._runner.staging.send(host.reshape(-1), dev.view(-1))
         return dev
+
+    def mark(self, label: str) -> None:
+        """With profiling on: the kernels launched since the last mark belong to the group ``label`` (an event is
+        recorded here; the runner adds up the times between events after the step).  Otherwise nothing."""
+        if self._runner is not None and self._runner.profile is not None and not self.static:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._marks.append((label, ev))
 
     def plan(self, key, make):
         """Per-step data that several layers share (built by the first one that asks; its buffers live as long as
@@ -184,7 +193,8 @@ class ModelRunner:
     MIXED_TOKENS = (32, 64, 96, 128, 192, 256)
 
     def __init__(self, model, page_size: int, num_pages: int, num_slots: int, dtype: torch.dtype, device,
-                 cuda_graphs: bool = True, max_model_len: int | None = None, max_step_tokens: int | None = None):
+                 cuda_graphs: bool = True, max_model_len: int | None = None, max_step_tokens: int | None = None,
+                 profile: bool = False):
         """``max_step_tokens``: the most tokens a step will bring; given, the scratch memory of steps that run
         kernel by kernel is sized now (by running the model over that many padding rows), so that no later step
         allocates.  Without it the scratch grows to what the steps need as they come."""
@@ -204,7 +214,11 @@ class ModelRunner:
         self.max_blocks = [-(-self.max_positions // ps) for ps in self.page_sizes]
         self.tables = [torch.full((num_slots, mb), -1, dtype=torch.int32, device=self.device) for mb in self.max_blocks]
         self._uploaded = [[0] * num_slots for _ in range(n_paged)]   # table entries of each slot already on the device
-        self.cuda_graphs = cuda_graphs and self.device.type == "cuda" and getattr(model, "capturable", True)
+        # profiling: milliseconds per group of kernels, summed over the steps so far (None: off); a profiled runner
+        # runs every step kernel by kernel, since the events sit between the kernels
+        self.profile: dict | None = {} if profile else None
+        self.profile_steps = 0
+        self.cuda_graphs = (cuda_graphs and not profile and self.device.type == "cuda" and getattr(model, "capturable", True))
         self._graphs: collections.OrderedDict[tuple, tuple] = collections.OrderedDict()   # least recently used first
         self.last_ctx = None
         self.last_h2d_bytes = 0
@@ -424,9 +438,23 @@ class ModelRunner:
             ctx = StepContext(self, lay, dev, static=False)
             ctx.__dict__.update(facts)
             self.last_ctx, self.last_h2d_bytes = ctx, host.nbytes
+            ctx.mark("start")
             self._apply_table_updates(ctx)
+            ctx.mark("tables")
             logits = self.model.forward(ctx, self.cache.views)
-            return post(ctx, logits) if post is not None else logits
+            result = post(ctx, logits) if post is not None else logits
+            if post is not None:
+                ctx.mark("sampling")
+            if self.profile is not None:
+                self._add_up(ctx)
+            return result
+
+    def _add_up(self, ctx) -> None:
+        """Adds the times between the step's marks to the totals of their groups (waits for the step to end)."""
+        torch.cuda.current_stream().synchronize()
+        for (_, a), (label, b) in zip(ctx._marks, ctx._marks[1:]):
+            self.profile[label] = self.profile.get(label, 0.0) + a.elapsed_time(b)
+        self.profile_steps += 1
 
     def size_workspace(self, max_step_tokens: int) -> None:
         """Sizes the scratch memory for steps of up to ``max_step_tokens`` tokens: the model runs over padding rows

@@ -89,7 +89,9 @@ class DecoderModel:
     # ---- one step ----
     def forward(self, ctx, caches):
         """ctx: the step's tensors; caches: cache id -> view.  Returns 32-bit logits [rows, vocab]."""
+        mark = getattr(ctx, "mark", lambda label: None)     # kernel groups for the profile, where the step keeps one
         resid = self.embedding.forward(ctx.token_ids, ctx.T, ctx.status)
+        mark("embedding")
         pending = None
         for i, run in enumerate(self.order):
             cache = caches[run.cache] if run.cache is not None else None
@@ -104,4 +106,6 @@ class DecoderModel:
             y = x[ctx.logit_rows.long()].to(self.build.compute_dtype)
         else:
             y = self.final_norm.forward(resid, pending, rows=ctx.logit_rows)
-        return self.lm_head.forward(y, ctx.status)
+        logits = self.lm_head.forward(y, ctx.status)
+        mark("head")
+        return logits

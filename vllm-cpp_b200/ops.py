@@ -68,6 +68,7 @@ def _declare(L):
         "vcb_gemm_bf16_plain": [P, P, P, I, I, I, I, LL, LL, LL, P],
         "vcb_attn_paged": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, P],
         "vcb_scatter_i32": [P, P, P, P, I, LL, P],
+        "vcb_selftest_wait_timeout": [LL, P, P, P],
         "vcb_state_reset": [P, I, LL, LL, LL, I, I, P, P, P, I, ctypes.c_uint, P, P],
         "vcb_attn_mma": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, F, P, I, P],
         "vcb_attn_mma_supported": [I, I],
@@ -390,6 +391,16 @@ def state_reset(state, slots, q_len, ctx_len, n_entries, value, status):
         raise KernelError(f"state of type {state.dtype} (float32, bfloat16 or int32)")
     _call("vcb_state_reset", _p(state), state.element_size(), state.stride(0), state.stride(1), row, n_caches, num_slots,
           _p(slots), _p(q_len), _p(ctx_len), n_entries, bits, _p(status), _stream())
+
+
+def selftest_wait_timeout(limit_clocks: int, status: torch.Tensor) -> list[int]:
+    """Lets the kernels' bounded mbarrier wait run out on a barrier nothing arrives at (see csrc/kernels/selftest.cu)
+    and returns [the wait's answer, the abort flag seen by another warp, a later wait's answer, whether that one
+    returned at once]; the status word gets the wait-timeout bit."""
+    _need(status, "status", torch.int32)
+    out = torch.full((4,), -1, dtype=torch.int32, device=status.device)
+    _call("vcb_selftest_wait_timeout", int(limit_clocks), _p(status), _p(out), _stream())
+    return out.tolist()
 
 
 def attn_mma_supported(dtype: torch.dtype, hd: int) -> bool:

@@ -13,7 +13,11 @@ class PreNormBlock(Block):
     """parts: ``norm1``, ``mixer``, ``norm2``, ``feed_forward``."""
 
     def forward(self, resid, pending, ctx, cache, writes=True):
+        mark = getattr(ctx, "mark", lambda label: None)     # kernel groups for the profile, where the step keeps one
         y = self.parts["norm1"].forward(resid, pending)
         d = self.parts["mixer"].forward(y, ctx, cache, writes)
+        mark("mixer")
         y = self.parts["norm2"].forward(resid, d)
-        return self.parts["feed_forward"].forward(y, ctx)
+        out = self.parts["feed_forward"].forward(y, ctx)
+        mark("feed_forward")
+        return out
