@@ -5,6 +5,9 @@
     python microbench.py [...] attention        decode attention over a paged cache; prompt attention
     python microbench.py [...] small            add+norm, norm-rotate-store, SiLU-gate
     python microbench.py [...] gemm --library   the products beside the library's (torch.mm), for comparison
+    VLLM_CPP_B200_TIMELINE=1 VLLM_CPP_B200_BUILD_DIR=/tmp/vcb_timeline python microbench.py [--layers L] [--batch B]
+        [--context C] timeline              one captured decode step seen from inside: when the blocks of each kernel
+                                            start, when their wait for the kernel before ends, when they end
 
 The sizes come from a Qwen3 configuration: one of the three serving shapes by name (default 8b) or a config.json.
 
@@ -176,13 +179,87 @@ def bench_small(dev, status):
         print(f"norm-rotate-store T={T:5d} slices {S}: {us:7.1f} us", flush=True)
 
 
+def bench_timeline(cfg, batch: int, context: int, layers: int, first: int, count: int):
+    """One captured decode step of ``layers`` layers, recorded by the kernels' own timeline marks (a library built with
+    VLLM_CPP_B200_TIMELINE=1), printed launch by launch: the times (us from the step's first mark) at which the first
+    and the last block of a launch started, left their wait for the kernel before, and ended."""
+    import numpy as np
+    from vllm_cpp_b200 import EngineConfig, LLM
+    from vllm_cpp_b200.engine.step import StepEntry
+    from vllm_cpp_b200.runtime import runtime
+    from vllm_cpp_b200.sampling import Sampler, SamplingOptions
+    import dataclasses
+    cfg = dataclasses.replace(cfg, num_hidden_layers=layers, layer_types=())     # (the kinds of the layers follow from the window)
+    max_tokens = batch * (-(-(context + 128) // 64) * 64)
+    llm = LLM(config=cfg, random_seed=0, engine=EngineConfig(dtype="bfloat16", page_size=PAGE, max_tokens=max_tokens,
+                                                            max_num_seqs=batch, max_step_tokens=256, max_model_len=context + 128))
+    runner, rt = llm.runner, runtime()
+    cm = rt.CacheManager(runner.layout.runtime_groups(rt, PAGE, max_tokens // PAGE), batch)
+    for t in runner.cache.tensors:
+        t.normal_(0, 1)
+    for r in range(batch):
+        cm.open(r)
+        assert cm.reserve(r, context + 100)
+        cm.commit(r, context)
+    greedy = SamplingOptions(0.0, 1.0, 1.0, 0)
+    rng = np.random.default_rng(0)
+
+    def post(ctx, logits):
+        return llm.sampler.sample_records(logits, ctx.user[:8 * logits.shape[0]].view(-1, 8), False, True)
+
+    def step():
+        entries = [StepEntry(cm.slot(r), cm.num_tokens(r), [int(rng.integers(0, 1000))], [cm.block_table(r, 0)], [0]) for r in range(batch)]
+        flat, _, _ = Sampler.records([greedy] * batch, [0] * batch, [e.slot for e in entries])
+        runner.step(entries, check=False, user=flat, post=post, post_key=("sample", False, True))
+        for r in range(batch):
+            cm.commit(r, cm.num_tokens(r) + 1)
+
+    for _ in range(10):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(); step(); e1.record(); e1.synchronize()
+    plain_ms = e0.elapsed_time(e1)
+    ops.timeline_begin()
+    e0.record(); step(); e1.record(); e1.synchronize()
+    rec = ops.timeline_end()
+    print(f"decode step, batch {batch}, context {context}, {layers} layers: {plain_ms:.3f} ms; with the marks recorded {e0.elapsed_time(e1):.3f} ms; "
+          f"{len(rec)} marks")
+    # marks -> launches: a launch of a kernel takes every (block, phase) once
+    t0 = rec[0]["t_ns"]
+    launches, open_by = [], {}
+    for r in rec:
+        lst = open_by.setdefault((r["kernel"], r["grid"]), [])
+        tag = (r["block"], r["phase"])
+        target = next((c for c in lst[-3:] if tag not in c["tags"] and (r["phase"] == 0 or (r["block"], 0) in c["tags"])), None)
+        if target is None:
+            target = dict(kernel=r["kernel"], tags=set(), recs=[])
+            lst.append(target)
+            launches.append(target)
+        target["tags"].add(tag)
+        target["recs"].append(r)
+    launches.sort(key=lambda c: min(x["t_ns"] for x in c["recs"]))
+
+    def span(rs, ph):
+        ts = [(x["t_ns"] - t0) / 1e3 for x in rs if x["phase"] == ph]
+        return (f"{min(ts):9.2f} {max(ts):9.2f}" if ts else "        -         -")
+    print(f"{'kernel':12s} {'blocks':>6s}   {'start: first':>9s} {'last':>9s}   {'wait over: first':>9s} {'last':>6s}   {'end: first':>9s} {'last':>9s}")
+    for c in launches[first:first + count]:
+        print(f"{c['kernel']:12s} {len({t[0] for t in c['tags']}):6d}   {span(c['recs'], 0)}   {span(c['recs'], 1)}   {span(c['recs'], 2)}")
+
+
 def main(argv):
     global PEAKS, LIBRARY
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--model", default="8b", help="8b, 4b, 14b, or a config.json of the Qwen3 architecture")
     ap.add_argument("--peaks", default=None, help="JSON file with hbm_gbs and bf16_tflops")
     ap.add_argument("--library", action="store_true", help="time the library's product (torch.mm) beside each of ours")
-    ap.add_argument("what", nargs="?", default="gemm", choices=["gemm", "attention", "small"])
+    ap.add_argument("--layers", type=int, default=12, help="timeline: layers of the model")
+    ap.add_argument("--batch", type=int, default=8, help="timeline: requests decoding")
+    ap.add_argument("--context", type=int, default=4096, help="timeline: tokens each request holds")
+    ap.add_argument("--first", type=int, default=18, help="timeline: first launch to print")
+    ap.add_argument("--count", type=int, default=30, help="timeline: launches to print")
+    ap.add_argument("what", nargs="?", default="gemm", choices=["gemm", "attention", "small", "timeline"])
     ap.add_argument("tokens", nargs="*", type=int)
     args = ap.parse_args(argv)
     if args.model in NAMED:
@@ -210,6 +287,8 @@ def main(argv):
         bench_attention(dev, status)
     elif what == "small":
         bench_small(dev, status)
+    elif what == "timeline":
+        bench_timeline(cfg, args.batch, args.context, args.layers, args.first, args.count)
     else:
         print(__doc__)
         return 2

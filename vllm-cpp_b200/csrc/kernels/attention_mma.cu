@@ -702,22 +702,57 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
             __threadfence();        // the other slices' partials are visible to this block
             const int out_row = a.dec_rows[dec_index];
             if (out_row >= 0) {
+                // First every slice's (maximum, sum) of this block's heads comes into shared memory in one round trip
+                // and becomes a weight per slice; then the slices' outputs are added, four loads in flight at a time.
+                // One load behind the other, the merge of twelve slices took the block as long as its keys had.
+                float* w_s = reinterpret_cast<float*>(k_s);            // [gq][nslices] weights, then [gq] 1 / sum
+                float* inv_s = w_s + gq * nslices;
+                for (int idx = tid; idx < gq * nslices; idx += blockDim.x) {
+                    const int ih = idx / nslices, sl = idx % nslices;
+                    w_s[idx] = __ldcg(a.part_ml + (((size_t)dec_index * a.nh + head0 + ih) * nslices + sl) * 2);
+                }
+                __syncthreads();
+                if (tid < gq) {
+                    const size_t prow0 = ((size_t)dec_index * a.nh + head0 + tid) * nslices;
+                    float m = -CUDART_INF_F;
+                    for (int sl = 0; sl < nslices; ++sl) m = fmaxf(m, w_s[tid * nslices + sl]);
+                    float l = 0.f;
+                    for (int sl0 = 0; sl0 < nslices; sl0 += 4) {       // slice order, as the separate merge kernel does
+                        float ls[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (sl0 + j < nslices) ls[j] = __ldcg(a.part_ml + (prow0 + sl0 + j) * 2 + 1);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (sl0 + j < nslices) {
+                                const float ms = w_s[tid * nslices + sl0 + j];
+                                const float w = ms == -CUDART_INF_F ? 0.f : expf(ms - m);
+                                if (ms != -CUDART_INF_F) l += ls[j] * w;
+                                w_s[tid * nslices + sl0 + j] = w;
+                            }
+                        }
+                    }
+                    inv_s[tid] = l > 0.f ? 1.f / l : 0.f;
+                }
+                __syncthreads();
                 for (int idx = tid; idx < gq * (HD / 2); idx += blockDim.x) {
                     const int ih = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
                     const size_t prow0 = ((size_t)dec_index * a.nh + head0 + ih) * nslices;
-                    float m = -CUDART_INF_F;
-                    for (int sl = 0; sl < nslices; ++sl) m = fmaxf(m, __ldcg(a.part_ml + (prow0 + sl) * 2));
-                    float l = 0.f, o0 = 0.f, o1 = 0.f;
-                    for (int sl = 0; sl < nslices; ++sl) {     // slice order, as the separate merge kernel does
-                        const float ms = __ldcg(a.part_ml + (prow0 + sl) * 2);
-                        if (ms == -CUDART_INF_F) continue;
-                        const float w = expf(ms - m);
-                        l += __ldcg(a.part_ml + (prow0 + sl) * 2 + 1) * w;
-                        const float2 ov = __ldcg(reinterpret_cast<const float2*>(a.part_o + (prow0 + sl) * HD + d));
-                        o0 += ov.x * w;
-                        o1 += ov.y * w;
+                    float o0 = 0.f, o1 = 0.f;
+                    for (int sl0 = 0; sl0 < nslices; sl0 += 4) {
+                        float2 ov[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (sl0 + j < nslices) ov[j] = __ldcg(reinterpret_cast<const float2*>(a.part_o + (prow0 + sl0 + j) * HD + d));
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (sl0 + j < nslices) {
+                                const float w = w_s[ih * nslices + sl0 + j];
+                                if (w != 0.f) { o0 += ov[j].x * w; o1 += ov[j].y * w; }
+                            }
+                        }
                     }
-                    const float inv = l > 0.f ? 1.f / l : 0.f;
+                    const float inv = inv_s[ih];
                     *reinterpret_cast<__nv_bfloat162*>(a.out + ((size_t)out_row * a.nh + head0 + ih) * HD + d) =
                         __floats2bfloat162_rn(o0 * inv, o1 * inv);
                 }
