@@ -620,7 +620,7 @@ def test_gemm_bf16_tn(M, T, K, splits, out_dtype):
         assert torch.equal(one[0], out[T - 1])
 
 
-@pytest.mark.parametrize("shape", range(7))
+@pytest.mark.parametrize("shape", range(8))
 @pytest.mark.parametrize("M,T,K,splits", [(300, 5, 200, 1), (520, 300, 1096, 1), (520, 300, 1096, 3), (128, 700, 64, 1)])
 def test_gemm_bf16_tn_every_unit_shape(shape, M, T, K, splits):
     """Each unit shape of the kernel, forced, at sizes that are not the ones it is chosen for: many token tiles
@@ -632,13 +632,17 @@ def test_gemm_bf16_tn_every_unit_shape(shape, M, T, K, splits):
     status = torch.zeros(1, dtype=torch.int32, device=dev())
     S = ops.gemm_effective_splits(K, splits)
     out = torch.full((S, T, M) if S > 1 else (T, M), float("nan"), dtype=torch.float32, device=dev())
+    if ops.GEMM_SHAPES[shape] == "pair" and M < 256:
+        with pytest.raises(ops.KernelError, match="at least 256 features"):
+            ops.gemm_bf16_tn(w, x, out, splits, status, shape=shape)
+        return
     ops.gemm_bf16_tn(w, x, out, splits, status, shape=shape)
     torch.cuda.synchronize()
     assert status.item() == 0
     got = out.double().sum(0) if S > 1 else out.double()
     torch.testing.assert_close(got, x.double() @ w.double().T, rtol=1e-4, atol=K * 2.0 ** -24 * 64)
     with pytest.raises(ops.KernelError, match="no unit shape"):
-        ops.gemm_bf16_tn(w, x, out, splits, status, shape=7)
+        ops.gemm_bf16_tn(w, x, out, splits, status, shape=8)
 
 
 @pytest.mark.parametrize("M,T,K", [(256, 129, 64), (512, 300, 256), (1000, 700, 328), (6144, 512, 1024), (4096, 2048, 512),
@@ -693,6 +697,27 @@ def test_gemm_bf16_swiglu_on_pairs_of_blocks(I, T, K):
     g, u = gu[:, 0::2], gu[:, 1::2]
     torch.testing.assert_close(outs[0].double(), g / (1 + torch.exp(-g)) * u, rtol=2e-2, atol=2e-2)
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("M,T,K,splits", [(6144, 256, 4096, 3), (4096, 512, 12288, 4), (1000, 300, 1096, 5), (512, 130, 640, 2)])
+def test_gemm_k_slices_on_pairs_of_blocks(M, T, K, splits):
+    """k-slices on the two-block kernel: every slice's 32-bit partial equals the single-block kernel's to the bit
+    (the same k-blocks in the same order), and their sum is the product."""
+    from vllm_cpp_b200 import ops
+    torch.manual_seed(M + T + K)
+    w = torch.randn(M, K, device=dev()).to(torch.bfloat16)
+    x = torch.randn(T, K, device=dev()).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    S = ops.gemm_effective_splits(K, splits)
+    assert S > 1
+    pair = torch.full((S, T, M), float("nan"), dtype=torch.float32, device=dev())
+    single = torch.full((S, T, M), float("nan"), dtype=torch.float32, device=dev())
+    ops.gemm_bf16_tn(w, x, pair, splits, status, shape=ops.GEMM_SHAPES.index("pair"))
+    ops.gemm_bf16_tn(w, x, single, splits, status, shape=ops.GEMM_SHAPES.index("n256"))
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert torch.equal(pair, single)
+    torch.testing.assert_close(pair.double().sum(0), x.double() @ w.double().T, rtol=1e-4, atol=K * 2.0 ** -24 * 64)
 
 
 def test_choose_splits_fills_the_sms():

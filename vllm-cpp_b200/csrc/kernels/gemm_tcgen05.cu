@@ -450,7 +450,18 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
     const int unit_rows = 2 * BM;   // rows of W per pair unit: 128 in each block
     const int m_tiles = (g.M + unit_rows - 1) / unit_rows;
     const int n_tiles = (g.N + BN - 1) / BN;
-    const int units = m_tiles * n_tiles;
+    const int units = m_tiles * n_tiles * g.splits;
+    // unit -> (feature tile, token tile, k-slice): the k-slices of a tile are units of their own, each with a
+    // 32-bit partial output, as in the single-block kernel
+    auto unit_at = [&](int u, int& m0, int& n0, int& kb0, int& nkb, int& z) {
+        z = u / (m_tiles * n_tiles);
+        int mi, ni;
+        tile_of(u % (m_tiles * n_tiles), m_tiles, n_tiles, mi, ni);
+        m0 = mi * unit_rows;
+        n0 = ni * BN;
+        kb0 = z * g.kb_per_split;
+        nkb = min(total_kb, kb0 + g.kb_per_split) - kb0;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -483,17 +494,16 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
             int it = 0, armed = 0;
             bool ok = true;
             for (int u = pair; u < units && ok; u += pairs) {
-                int mi, ni;
-                tile_of(u, m_tiles, n_tiles, mi, ni);
-                const int m0 = mi * unit_rows, n0 = ni * BN;
-                for (int i = 0; i < total_kb; ++i, ++it) {
+                int m0, n0, kb0, nkb, z;
+                unit_at(u, m0, n0, kb0, nkb, z);
+                for (int i = 0; i < nkb; ++i, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1u, abort_flag, g.status)) { ok = false; break; }
                     if (rank == 0) mbar_expect_tx(full_bar(s), 2 * L::STAGE_BYTES);   // both blocks' bytes land on block 0's barrier
                     const uint32_t dst = base + s * L::STAGE_BYTES;
                     const uint32_t bar0 = full_bar(s) & PEER_BIT_MASK;
-                    tma_load_2d_pair(dst, &map_w, bar0, i * BK, m0 + (int)rank * BM);
-                    tma_load_2d_pair(dst + L::A_BYTES, &map_x, bar0, i * BK, n0 + (int)rank * (BN / 2));
+                    tma_load_2d_pair(dst, &map_w, bar0, (kb0 + i) * BK, m0 + (int)rank * BM);
+                    tma_load_2d_pair(dst + L::A_BYTES, &map_x, bar0, (kb0 + i) * BK, n0 + (int)rank * (BN / 2));
                     armed = it + 1;
                 }
             }
@@ -512,11 +522,13 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
             int it = 0, j = 0;
             bool ok = true;
             for (int u = pair; u < units && ok; u += pairs, ++j) {
+                int m0, n0, kb0, nkb, z;
+                unit_at(u, m0, n0, kb0, nkb, z);
                 const int a = j & 1;
                 ok = mbar_wait(acc_empty_bar(a), ((j >> 1) & 1) ^ 1u, abort_flag, g.status);   // both epilogues drained it
                 if (!ok) break;
                 tc_fence_after();
-                for (int i = 0; i < total_kb; ++i, ++it) {
+                for (int i = 0; i < nkb; ++i, ++it) {
                     const int s = it % STAGES;
                     ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag, g.status);
                     if (!ok) break;
@@ -536,9 +548,9 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
         const int q = warp & 3;
         int j = 0;
         for (int u = pair; u < units; u += pairs, ++j) {
-            int mi, ni;
-            tile_of(u, m_tiles, n_tiles, mi, ni);
-            const int m0 = mi * unit_rows, n0 = ni * BN;
+            int m0, n0, kb0, nkb, z;
+            unit_at(u, m0, n0, kb0, nkb, z);
+            const size_t zoff = (size_t)z * g.split_stride;
             const int a = j & 1;
             if (!mbar_wait(acc_full_bar(a), (j >> 1) & 1, abort_flag, g.status)) break;
             tc_fence_after();
@@ -555,12 +567,12 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
                     swiglu_store<CHUNK>(v, reinterpret_cast<__nv_bfloat16*>(g.out), g.ldc, m, g.M, n0 + c0, g.N, lane);
                 } else if (m < g.M) {
                     if (g.out_dtype == VCB_F32) {
-                        float* o = reinterpret_cast<float*>(g.out);
+                        float* o = reinterpret_cast<float*>(g.out) + zoff;
 #pragma unroll
                         for (int jj = 0; jj < CHUNK; ++jj)
                             if (n0 + c0 + jj < g.N) o[(size_t)(n0 + c0 + jj) * g.ldc + m] = __uint_as_float(v[jj / 16][jj % 16]);
                     } else {
-                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out);
+                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(g.out) + zoff;
 #pragma unroll
                         for (int jj = 0; jj < CHUNK; ++jj)
                             if (n0 + c0 + jj < g.N)
@@ -723,7 +735,7 @@ int launch_pair(const void* W, long long w_rows, const void* X, const GemmArgs& 
         opted = true;
     }
     const int unit_rows = 2 * BM;
-    const long long units = (long long)((g.M + unit_rows - 1) / unit_rows) * ((g.N + 255) / 256);
+    const long long units = (long long)((g.M + unit_rows - 1) / unit_rows) * ((g.N + 255) / 256) * g.splits;
     const long long max_pairs = num_sms() / 2;
     const int pairs = (int)(units < max_pairs ? units : max_pairs);
     cudaLaunchConfig_t cfg = {};
@@ -763,7 +775,7 @@ VCB_API int vcb_gemm_effective_splits(int K, int splits) {
 }
 
 // The unit shapes that are built: tokens per tile (BN), stages of the ring, 128-feature tiles per unit, accumulators.
-enum GemmShape { SHAPE_N16 = 0, SHAPE_N32, SHAPE_N64, SHAPE_N128, SHAPE_N256, SHAPE_M256_N192, SHAPE_M256_N256, SHAPE_COUNT };
+enum GemmShape { SHAPE_N16 = 0, SHAPE_N32, SHAPE_N64, SHAPE_N128, SHAPE_N256, SHAPE_M256_N192, SHAPE_M256_N256, SHAPE_PAIR, SHAPE_COUNT };
 
 namespace {
 int launch_shape(int shape, const void* W, const void* X, const GemmArgs& g, long long ldw, long long ldx, int splits,
@@ -776,6 +788,9 @@ int launch_shape(int shape, const void* W, const void* X, const GemmArgs& g, lon
         case SHAPE_N256: return launch<256, 4, 1, 2>(W, X, g, ldw, ldx, splits, stream);
         case SHAPE_M256_N192: return launch<192, 3, 2, 1>(W, X, g, ldw, ldx, splits, stream);
         case SHAPE_M256_N256: return launch<256, 3, 2, 1>(W, X, g, ldw, ldx, splits, stream);
+        case SHAPE_PAIR:
+            if (g.M < 2 * BM) { vcb_set_error("gemm_bf16_tn: pairs of blocks need at least 256 features"); return -1; }
+            return launch_pair(W, g.M, X, g, ldw, ldx, stream);
     }
     vcb_set_error("gemm_bf16_tn: no unit shape %d (0..%d)", shape, SHAPE_COUNT - 1);
     return -1;
@@ -819,8 +834,19 @@ int pick_shape(int M, int N, int K, int splits, long long* cost_out = nullptr) {
 }
 bool use_pairs(int M, int N, int K, int splits) {
     const int mode = pairs_mode();
-    if (mode == 0 || splits != 1 || N <= 128 || M < 2 * BM) return false;
+    if (mode == 0 || N <= 128 || M < 2 * BM) return false;
     if (mode == 2) return true;
+    if (splits != 1) {
+        // k-slices on pairs: a pair's unit is 256 x 256 where a single block's is 128 x 256, so there are half as many
+        // units for half as many takers; the pairs draw a third less from L2 per k-block.  That pays for the long inner
+        // sizes (down_proj, 12288: 5 to 7 % at 384 to 768 tokens) where the rounds come out no worse, and not for 4096
+        // (qkv_proj at 256 tokens: 18.1 -> 19.7 us).
+        if (K < 8192) return false;
+        const long long pair_units = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256) * splits;
+        const long long single_units = (long long)((M + BM - 1) / BM) * ((N + 255) / 256) * splits;
+        const long long pairs = num_sms() / 2;
+        return (pair_units + pairs - 1) / pairs <= (single_units + num_sms() - 1) / num_sms();
+    }
     long long single = -1;
     pick_shape(M, N, K, 1, &single);
     return single > 0 && pair_cost(M, N) * 24 <= single * 25;
