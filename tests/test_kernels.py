@@ -720,66 +720,6 @@ def test_gemm_k_slices_on_pairs_of_blocks(M, T, K, splits):
     torch.testing.assert_close(pair.double().sum(0), x.double() @ w.double().T, rtol=1e-4, atol=K * 2.0 ** -24 * 64)
 
 
-@pytest.mark.parametrize("M,T,K,splits,n_delta,gdt", [(6144, 8, 4096, 3, 4, torch.bfloat16), (300, 1, 200, 1, 0, torch.float32),
-                                                     (24576, 8, 4096, 3, 4, torch.bfloat16), (520, 16, 1096, 5, 2, torch.bfloat16),
-                                                     (128, 3, 64, 1, 1, torch.float32), (4096, 13, 2560, 4, 9, torch.bfloat16)])
-def test_gemm_with_the_norm_as_the_maker_of_its_operand(M, T, K, splits, n_delta, gdt):
-    """The product whose token operand the kernel makes itself from the residual stream, the pending deltas and the
-    norm's gains: product, rows written back and sums of squares against 64-bit, over feature, token and k edges."""
-    from vllm_cpp_b200 import ops
-    torch.manual_seed(M + T + K)
-    w = (0.05 * torch.randn(M, K, device=dev())).to(torch.bfloat16)
-    resid = 3 * torch.randn(T, K, device=dev())
-    delta = torch.randn(n_delta, T, K, device=dev()) if n_delta else None
-    gain = (1 + 0.1 * torch.randn(K, device=dev())).to(gdt)
-    resid_out = torch.full_like(resid, float("nan"))
-    status = torch.zeros(1, dtype=torch.int32, device=dev())
-    S = ops.gemm_effective_splits(K, splits)
-    out = torch.full((S, T, M) if S > 1 else (T, M), float("nan"), device=dev())
-    ssq = ops.gemm_bf16_made_norm(w, resid, delta, gain, resid_out, out, splits, status)
-    torch.cuda.synchronize()
-    assert status.item() == 0
-    x = resid.double() + (delta.double().sum(0) if n_delta else 0)
-    torch.testing.assert_close(resid_out.double(), x, rtol=1e-6, atol=1e-6)
-    torch.testing.assert_close(ssq.double().sum(0), (x * x).sum(1), rtol=1e-5, atol=1e-5)
-    operand = (gain.double() * x).to(torch.bfloat16).double()         # what the tensor cores are given
-    got = out.double().sum(0) if S > 1 else out.double()
-    torch.testing.assert_close(got, operand @ w.double().T, rtol=1e-4, atol=K * 2.0 ** -24 * 64)
-    # against the kernels it replaces: norm, then product, with the norm's factor applied afterwards
-    eps = 1e-6
-    normed = torch.empty(T, K, device=dev(), dtype=torch.bfloat16)
-    r2 = resid.clone()
-    ops.add_rmsnorm(r2, delta, gain, eps, normed)
-    inv = 1.0 / torch.sqrt(ssq.double().sum(0) / K + eps)
-    torch.testing.assert_close(got * inv[:, None], normed.double() @ w.double().T, rtol=3e-2, atol=3e-2 * (normed.double() @ w.double().T).abs().max().item())
-
-
-@pytest.mark.parametrize("M,T,K,splits,n_gu,scaled", [(4096, 8, 12288, 4, 3, True), (300, 1, 200, 1, 1, False), (520, 16, 1096, 5, 2, True),
-                                                      (128, 5, 64, 1, 4, True), (2560, 12, 9728, 6, 3, False)])
-def test_gemm_with_the_silu_gate_as_the_maker_of_its_operand(M, T, K, splits, n_gu, scaled):
-    from vllm_cpp_b200 import ops
-    torch.manual_seed(M + T + K)
-    w = (0.05 * torch.randn(M, K, device=dev())).to(torch.bfloat16)
-    gate_up = 2 * torch.randn(n_gu, T, 2 * K, device=dev())
-    ssq = (torch.rand(3, T, device=dev()) * 500 + 50) if scaled else None
-    width, eps = 77.0, 1e-5
-    status = torch.zeros(1, dtype=torch.int32, device=dev())
-    S = ops.gemm_effective_splits(K, splits)
-    out = torch.full((S, T, M) if S > 1 else (T, M), float("nan"), device=dev())
-    ops.gemm_bf16_made_swiglu(w, gate_up, ssq, width, eps, out, splits, status)
-    torch.cuda.synchronize()
-    assert status.item() == 0
-    gu = gate_up.double().sum(0)
-    if scaled:
-        gu = gu / torch.sqrt(ssq.double().sum(0) / width + eps)[:, None]
-    g, u = gu[:, 0::2], gu[:, 1::2]
-    operand = (g / (1 + torch.exp(-g)) * u).to(torch.bfloat16).double()
-    got = out.double().sum(0) if S > 1 else out.double()
-    want = operand @ w.double().T
-    # (an operand that rounds the other way in its last bfloat16 bit moves the result by 2^-8 of one product)
-    torch.testing.assert_close(got, want, rtol=2e-3, atol=2e-3 * want.abs().max().item())
-
-
 def test_choose_splits_fills_the_sms():
     from vllm_cpp_b200.parts.linear import choose_splits
     assert choose_splits(6144, 256, 4096) == 3      # 48 units of 128 x 256 -> 144

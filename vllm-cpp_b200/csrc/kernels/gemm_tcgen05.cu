@@ -367,343 +367,6 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
 }
 
 // ---------------------------------------------------------------------------
-// Products whose token operand the block makes for itself (few tokens: decoding).
-//
-// A decode step is a chain: product, small kernel, product, ...; every link costs a kernel boundary, and the small
-// kernels between the products (residual add and norm; SiLU-gate) are one round trip to memory each during which the
-// weight stream stands still.  Here the small step is the producer of the product's token operand: two extra warps
-// read what the kernel before left (32-bit partial sums, from L2), compute the operand of one k-block at a time and
-// write it into the stage's B tile in the 128-byte-swizzled layout a TMA load would have produced, behind the same
-// full/empty barriers (a stage is full once the weight tile has landed and the operand warp has arrived), so the
-// operand of k-block i is made while k-blocks before it are multiplied and the weights after it are in flight.
-//
-//  kind 1  x[t][k] = resid[t][k] + sum_s delta[s][t][k];  operand = bfloat16(gain[k] * x[t][k]).
-//          The norm's statistic needs the whole row, which no block sees: the product is taken of the un-normalised
-//          gain * x, and whoever reads the product's result multiplies row t by 1 / sqrt(mean(x_t^2) + eps).  The
-//          blocks of the first feature tile also write x back (resid_out, another buffer than resid: other blocks
-//          are still reading that) and the sums of squares of their part of the row (ssq_out[(slice * 2 + warp)][t],
-//          added up by the reader in that order).
-//  kind 2  g, u = sums over the slices of a stacked gate/up product (gate_i at 2i, up_i at 2i+1), each row scaled
-//          by its 1 / sqrt(sum(ssq_in[.][t]) / width + eps) (ssq_in null: 1);  operand = bfloat16(silu(g) * u).
-// ---------------------------------------------------------------------------
-struct OperandArgs {
-    int kind;
-    const float* resid;        // kind 1: [N][K]
-    const float* delta;        //         [n_delta][N][K], n_delta >= 0
-    int n_delta;
-    long long delta_stride;
-    const void* gain;          //         [K]
-    int gain_dtype;
-    float* resid_out;          //         [N][K]
-    float* ssq_out;            //         [splits * 2][N]
-    const float* gate_up;      // kind 2: [n_gu][N][2K]
-    int n_gu;
-    long long gu_stride;
-    const float* ssq_in;       //         [n_ssq][N] or null
-    int n_ssq;
-    float ssq_width, ssq_eps;
-};
-
-constexpr int MADE_THREADS = 256;   // the roles of gemm_bf16_tn_kernel and two operand warps
-
-template <int BN, int STAGES>
-__global__ __launch_bounds__(MADE_THREADS, 1) void gemm_bf16_tn_made_kernel(const __grid_constant__ CUtensorMap map_w,
-                                                                            GemmArgs g, OperandArgs op) {
-    static_assert(BN == 16 && STAGES % 2 == 0, "one operand warp per stage parity; rows of at most 16 tokens");
-    using L = Smem<BN, STAGES, 1, 2>;
-    constexpr int ACC = 2;
-    constexpr uint32_t ACC_COLS = 32;
-    constexpr uint32_t TMEM_COLS = 64;
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t bars = base + L::BAR_OFFSET;
-    auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-    auto acc_full_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
-    auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * STAGES + ACC + a); };
-    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(gen + L::BAR_OFFSET + L::NUM_BARS * 8);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::BAR_OFFSET + L::NUM_BARS * 8 + 8);
-
-    pdl_trigger();
-    tl_mark(VCB_TL_GEMM, 0);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int total_kb = (g.K + BK - 1) / BK;
-    const int m_tiles = (g.M + BM - 1) / BM;
-    const int units = m_tiles * g.splits;     // one token tile
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full_bar(s), 2);    // the weight tile's bytes (with the loading thread's arrival) and the operand warp
-            mbar_init(empty_bar(s), 1);
-        }
-        for (int a = 0; a < ACC; ++a) {
-            mbar_init(acc_full_bar(a), 1);
-            mbar_init(acc_empty_bar(a), 4);
-        }
-        *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32((const void*)tmem_holder)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_holder;
-
-    auto unit_at = [&](int u, int& m0, int& kb0, int& nkb, int& z) {
-        z = u / m_tiles;
-        m0 = (u % m_tiles) * BM;
-        kb0 = z * g.kb_per_split;
-        nkb = min(total_kb, kb0 + g.kb_per_split) - kb0;
-    };
-
-    if (warp == 0) {
-        // ---- weight tiles by TMA; nothing of the step writes them, so the ring is filled before the wait ----
-        if (lane == 0) {
-            int it = 0, armed = 0;
-            bool ok = true;
-            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-                int m0, kb0, nkb, z;
-                unit_at(u, m0, kb0, nkb, z);
-                for (int i = 0; i < nkb; ++i, ++it) {
-                    const int s = it % STAGES;
-                    if (it >= STAGES && !mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1u, abort_flag, g.status)) { ok = false; break; }
-                    mbar_expect_tx(full_bar(s), L::A_BYTES);
-                    tma_load_2d(base + s * L::STAGE_BYTES, &map_w, full_bar(s), (kb0 + i) * BK, m0);
-                    armed = it + 1;
-                }
-            }
-            if (*abort_flag) {
-                for (int i = max(0, armed - STAGES); i < armed; ++i) {
-                    const long long t0 = clock64();
-                    while (!mbar_try(full_bar(i % STAGES), (i / STAGES) & 1) && clock64() - t0 < VCB_WAIT_CLOCKS) {}
-                }
-            }
-        }
-    } else if (warp == 1) {
-        // ---- MMA issuer ----
-        if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc(BN);
-            int it = 0, j = 0;
-            bool ok = true;
-            for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++j) {
-                int m0, kb0, nkb, z;
-                unit_at(u, m0, kb0, nkb, z);
-                const int a = j % ACC;
-                ok = mbar_wait(acc_empty_bar(a), ((j / ACC) & 1) ^ 1u, abort_flag, g.status);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t tmem_d = tmem_base + a * ACC_COLS;
-                for (int i = 0; i < nkb; ++i, ++it) {
-                    const int s = it % STAGES;
-                    ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag, g.status);
-                    if (!ok) break;
-                    tc_fence_after();
-                    const uint32_t a_addr = base + s * L::STAGE_BYTES;
-                    const uint64_t da = smem_desc(a_addr), db = smem_desc(a_addr + L::A_BYTES);
-#pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) tc_mma(tmem_d, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-                    tc_commit(empty_bar(s));
-                }
-                if (ok) tc_commit(acc_full_bar(a));
-            }
-        }
-    } else if (warp < 6) {
-        // ---- epilogue: 32-bit partial sums, out[z][t][m] ----
-        const int q = warp & 3;
-        int j = 0;
-        for (int u = blockIdx.x; u < units; u += gridDim.x, ++j) {
-            int m0, kb0, nkb, z;
-            unit_at(u, m0, kb0, nkb, z);
-            const int a = j % ACC;
-            if (!mbar_wait(acc_full_bar(a), (j / ACC) & 1, abort_flag, g.status)) break;
-            tc_fence_after();
-            const int m = m0 + q * 32 + lane;
-            uint32_t v[16];
-            tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * ACC_COLS), v);
-            tc_wait_ld();
-            if (m < g.M) {
-                float* o = reinterpret_cast<float*>(g.out) + (size_t)z * g.split_stride;
-#pragma unroll
-                for (int jj = 0; jj < 16; ++jj)
-                    if (jj < g.N) o[(size_t)jj * g.ldc + m] = __uint_as_float(v[jj]);
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty_bar(a));
-        }
-        tc_fence_before();
-    } else {
-        // ---- operand warps: warp 6 makes the B tiles of the even stages, warp 7 those of the odd ones ----
-        const int pw = warp - 6;
-        // rows beyond the tokens stay zero for good; the rest of a tile is rewritten every time round
-        for (int s = pw; s < STAGES; s += 2) {
-            uint4* b = reinterpret_cast<uint4*>(gen + s * L::STAGE_BYTES + L::A_BYTES);
-            for (int i = lane; i < L::B_BYTES / 16; i += 32) b[i] = make_uint4(0, 0, 0, 0);
-        }
-        pdl_wait();
-        tl_mark(VCB_TL_GEMM, 1);
-        // a lane owns the four columns 4 * (lane & 15) .. + 3 of a k-block in the rows (lane >> 4) + 2 * jj (+ 8 in the
-        // second batch of a tile of more than 8 tokens)
-        const int c4 = lane & 15;
-        constexpr int BATCHES = BN / 8;
-        float row_inv[BATCHES][4];
-#pragma unroll
-        for (int b = 0; b < BATCHES; ++b)
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-                const int row = 8 * b + (lane >> 4) + 2 * jj;
-                float inv = 1.f;
-                if (op.kind == 2 && op.ssq_in != nullptr && row < g.N) {
-                    float ss = 0.f;
-                    for (int n = 0; n < op.n_ssq; ++n) ss += op.ssq_in[(size_t)n * g.N + row];
-                    inv = 1.0f / sqrtf(ss / op.ssq_width + op.ssq_eps);
-                }
-                row_inv[b][jj] = inv;
-            }
-        int it = 0;
-        bool ok = true;
-        for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-            int m0, kb0, nkb, z;
-            unit_at(u, m0, kb0, nkb, z);
-            const bool owner = op.kind == 1 && m0 == 0;     // this unit writes the rows back and their sums of squares
-            float ssq[BATCHES][4];
-#pragma unroll
-            for (int b = 0; b < BATCHES; ++b)
-#pragma unroll
-                for (int jj = 0; jj < 4; ++jj) ssq[b][jj] = 0.f;
-            for (int i = 0; i < nkb; ++i, ++it) {
-                if ((it & 1) != pw) continue;
-                const int s = it % STAGES;
-                const int k = (kb0 + i) * BK + 4 * c4;       // this lane's first column
-                const bool k_in = k < g.K;                   // (K is a multiple of 8: four columns are in or out together)
-                float gn[4] = {0.f, 0.f, 0.f, 0.f};
-                if (op.kind == 1 && k_in) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) gn[e] = load_as_f32(op.gain, op.gain_dtype, (size_t)k + e);
-                }
-                if (it >= STAGES && !mbar_wait(empty_bar(s), ((it / STAGES) & 1) ^ 1u, abort_flag, g.status)) { ok = false; break; }
-                uint8_t* btile = gen + s * L::STAGE_BYTES + L::A_BYTES;
-#pragma unroll
-                for (int b = 0; b < BATCHES; ++b) {
-                    if (8 * b >= g.N) break;
-                    float4 x[4];
-                    if (op.kind == 1) {
-#pragma unroll
-                        for (int jj = 0; jj < 4; ++jj) {
-                            const int row = 8 * b + (lane >> 4) + 2 * jj;
-                            x[jj] = (row < g.N && k_in) ? *reinterpret_cast<const float4*>(op.resid + (size_t)row * g.K + k)
-                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
-                        for (int s0 = 0; s0 < op.n_delta; s0 += 4) {      // four slices' loads in flight, added in slice order
-                            float4 d[4][4];
-#pragma unroll
-                            for (int sl = 0; sl < 4; ++sl)
-#pragma unroll
-                                for (int jj = 0; jj < 4; ++jj) {
-                                    const int row = 8 * b + (lane >> 4) + 2 * jj;
-                                    if (s0 + sl < op.n_delta && row < g.N && k_in)
-                                        d[sl][jj] = *reinterpret_cast<const float4*>(op.delta + (size_t)(s0 + sl) * op.delta_stride + (size_t)row * g.K + k);
-                                }
-#pragma unroll
-                            for (int sl = 0; sl < 4; ++sl)
-#pragma unroll
-                                for (int jj = 0; jj < 4; ++jj) {
-                                    const int row = 8 * b + (lane >> 4) + 2 * jj;
-                                    if (s0 + sl < op.n_delta && row < g.N && k_in) {
-                                        x[jj].x += d[sl][jj].x; x[jj].y += d[sl][jj].y; x[jj].z += d[sl][jj].z; x[jj].w += d[sl][jj].w;
-                                    }
-                                }
-                        }
-#pragma unroll
-                        for (int jj = 0; jj < 4; ++jj) {
-                            const int row = 8 * b + (lane >> 4) + 2 * jj;
-                            if (owner && row < g.N && k_in) {
-                                *reinterpret_cast<float4*>(op.resid_out + (size_t)row * g.K + k) = x[jj];
-                                ssq[b][jj] += x[jj].x * x[jj].x + x[jj].y * x[jj].y + x[jj].z * x[jj].z + x[jj].w * x[jj].w;
-                            }
-                            x[jj].x *= gn[0]; x[jj].y *= gn[1]; x[jj].z *= gn[2]; x[jj].w *= gn[3];
-                        }
-                    } else {
-                        float4 ga[4], gb[4];     // (g0 u0 g1 u1), (g2 u2 g3 u3) of this lane's four columns
-#pragma unroll
-                        for (int jj = 0; jj < 4; ++jj) ga[jj] = gb[jj] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        for (int s0 = 0; s0 < op.n_gu; s0 += 2) {
-                            float4 ta[2][4], tb[2][4];
-#pragma unroll
-                            for (int sl = 0; sl < 2; ++sl)
-#pragma unroll
-                                for (int jj = 0; jj < 4; ++jj) {
-                                    const int row = 8 * b + (lane >> 4) + 2 * jj;
-                                    if (s0 + sl < op.n_gu && row < g.N && k_in) {
-                                        const float* src = op.gate_up + (size_t)(s0 + sl) * op.gu_stride + ((size_t)row * g.K + k) * 2;
-                                        ta[sl][jj] = *reinterpret_cast<const float4*>(src);
-                                        tb[sl][jj] = *reinterpret_cast<const float4*>(src + 4);
-                                    }
-                                }
-#pragma unroll
-                            for (int sl = 0; sl < 2; ++sl)
-#pragma unroll
-                                for (int jj = 0; jj < 4; ++jj) {
-                                    const int row = 8 * b + (lane >> 4) + 2 * jj;
-                                    if (s0 + sl < op.n_gu && row < g.N && k_in) {
-                                        ga[jj].x += ta[sl][jj].x; ga[jj].y += ta[sl][jj].y; ga[jj].z += ta[sl][jj].z; ga[jj].w += ta[sl][jj].w;
-                                        gb[jj].x += tb[sl][jj].x; gb[jj].y += tb[sl][jj].y; gb[jj].z += tb[sl][jj].z; gb[jj].w += tb[sl][jj].w;
-                                    }
-                                }
-                        }
-#pragma unroll
-                        for (int jj = 0; jj < 4; ++jj) {
-                            const float inv = row_inv[b][jj];
-                            auto act = [&](float gate, float up) { gate *= inv; up *= inv; return gate / (1.0f + expf(-gate)) * up; };
-                            x[jj] = make_float4(act(ga[jj].x, ga[jj].y), act(ga[jj].z, ga[jj].w), act(gb[jj].x, gb[jj].y), act(gb[jj].z, gb[jj].w));
-                        }
-                    }
-#pragma unroll
-                    for (int jj = 0; jj < 4; ++jj) {
-                        const int row = 8 * b + (lane >> 4) + 2 * jj;
-                        if (row < g.N) {
-                            __nv_bfloat162 lo = __floats2bfloat162_rn(x[jj].x, x[jj].y), hi = __floats2bfloat162_rn(x[jj].z, x[jj].w);
-                            uint2 pk;
-                            pk.x = *reinterpret_cast<uint32_t*>(&lo);
-                            pk.y = *reinterpret_cast<uint32_t*>(&hi);
-                            // 128-byte rows, 16-byte chunks XOR-swizzled by the row within its group of eight
-                            *reinterpret_cast<uint2*>(btile + row * 128 + ((((c4 >> 1) ^ (row & 7))) << 4) + (c4 & 1) * 8) = pk;
-                        }
-                    }
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // ordinary stores, read by the tensor cores
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full_bar(s));
-            }
-            if (owner && ok) {
-#pragma unroll
-                for (int b = 0; b < BATCHES; ++b)
-#pragma unroll
-                    for (int jj = 0; jj < 4; ++jj) {
-                        float v = ssq[b][jj];
-#pragma unroll
-                        for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);     // the 16 lanes of a row
-                        const int row = 8 * b + (lane >> 4) + 2 * jj;
-                        if ((lane & 15) == 0 && row < g.N) op.ssq_out[(size_t)(z * 2 + pw) * g.N + row] = v;
-                    }
-            }
-        }
-    }
-    __syncthreads();
-    tl_mark(VCB_TL_GEMM, 2);
-    if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
-    }
-}
-
-// ---------------------------------------------------------------------------
 // Two blocks on two SMs working as a pair (cta_group::2) for prompt portions.
 //
 // One MMA of the pair covers 256 features (128 TMEM lanes in each block) x 256 tokens; each block loads only its own
@@ -1227,58 +890,6 @@ VCB_API int vcb_gemm_bf16_tn(const void* W, const void* X, void* out, int out_dt
                              long long ldw, long long ldx, long long ldc, int splits, long long split_stride,
                              int* status, cudaStream_t stream) {
     return vcb_gemm_bf16_tn_shape(W, X, out, out_dtype, M, N, K, ldw, ldx, ldc, splits, split_stride, -1, status, stream);
-}
-
-// A product of at most 16 tokens whose token operand the kernel makes for itself (see OperandArgs): out[z][t][m],
-// 32-bit partial sums of the k-slices, as vcb_gemm_bf16_tn writes them.  kind 1: the operand is
-// bfloat16(gain * (resid + the deltas)), resid_out and ssq_out [slices * 2][N] are written as well (the reader of
-// `out` owes row t the factor 1 / sqrt(sum(ssq_out[.][t]) / K + eps)); kind 2: the operand is the SiLU-gate of a
-// stacked gate/up product, each row scaled first by the factor that ssq_in (null: none) gives it.
-VCB_API int vcb_gemm_bf16_made(const void* W, void* out, int M, int N, int K, long long ldw, long long ldc, int splits,
-                               long long split_stride, int kind, const float* resid, const float* delta, int n_delta,
-                               long long delta_stride, const void* gain, int gain_dtype, float* resid_out, float* ssq_out,
-                               const float* gate_up, int n_gu, long long gu_stride, const float* ssq_in, int n_ssq,
-                               float ssq_width, float ssq_eps, int* status, cudaStream_t stream) {
-    VCB_CHECK_ARG(M > 0 && K > 0 && N >= 1 && N <= 16, "gemm_bf16_made: %d tokens (1 to 16), M=%d K=%d", N, M, K);
-    VCB_CHECK_ARG(K % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)W % 16 == 0), "gemm_bf16_made: inner size %d and weight rows must be multiples of 8 elements, 16-byte aligned", K);
-    VCB_CHECK_ARG(kind == 1 || kind == 2, "gemm_bf16_made: operand kind %d (1 or 2)", kind);
-    VCB_CHECK_ARG(status != nullptr && out != nullptr, "gemm_bf16_made: out and status are required");
-    if (kind == 1) {
-        VCB_CHECK_ARG(resid != nullptr && resid_out != nullptr && resid_out != resid && ssq_out != nullptr && gain != nullptr && n_delta >= 0,
-                      "gemm_bf16_made: kind 1 needs resid, gain, ssq_out and a resid_out that is another buffer than resid");
-        VCB_CHECK_ARG(n_delta == 0 || (delta != nullptr && delta_stride % 4 == 0 && (uintptr_t)delta % 16 == 0), "gemm_bf16_made: deltas must be 16-byte aligned");
-        VCB_CHECK_ARG((uintptr_t)resid % 16 == 0 && (uintptr_t)resid_out % 16 == 0, "gemm_bf16_made: resid and resid_out must be 16-byte aligned");
-    } else {
-        VCB_CHECK_ARG(gate_up != nullptr && n_gu >= 1 && gu_stride % 4 == 0 && (uintptr_t)gate_up % 16 == 0,
-                      "gemm_bf16_made: kind 2 needs the stacked gate/up product, 16-byte aligned");
-        VCB_CHECK_ARG(ssq_in == nullptr || (n_ssq >= 1 && ssq_width > 0.f), "gemm_bf16_made: a row scale needs its slices and width");
-    }
-    const int total_kb = (K + BK - 1) / BK;
-    if (splits < 1) splits = 1;
-    if (splits > total_kb) splits = total_kb;
-    const int kb_per_split = (total_kb + splits - 1) / splits;
-    splits = (total_kb + kb_per_split - 1) / kb_per_split;
-    GemmArgs g{out, VCB_F32, M, N, K, ldc, split_stride, kb_per_split, splits, 0, status};
-    OperandArgs op{kind, resid, delta, n_delta, delta_stride, gain, gain_dtype, resid_out, ssq_out,
-                   gate_up, n_gu, gu_stride, ssq_in, n_ssq, ssq_width, ssq_eps};
-    using L = Smem<16, 8, 1, 2>;
-    CUtensorMap mw;
-    if (!tensor_map(W, M, K, ldw, BM, &mw)) return -3;
-    auto kern = gemm_bf16_tn_made_kernel<16, 8>;
-    static bool opted = false;
-    if (!opted) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
-        if (e != cudaSuccess) {
-            vcb_set_error("gemm_bf16_made: %d bytes of shared memory refused: %s", L::TOTAL, cudaGetErrorString(e));
-            return -2;
-        }
-        opted = true;
-    }
-    const long long units = (long long)((M + BM - 1) / BM) * splits;
-    const int grid = (int)(units < num_sms() ? units : num_sms());
-    launch_pdl(kern, dim3(grid), dim3(MADE_THREADS), L::TOTAL, stream, mw, g, op);
-    VCB_CHECK_LAUNCH("gemm_bf16_made");
-    return 0;
 }
 
 // 0: no product runs on pairs of blocks; 1: those that the rule above sends there; 2: all that can.

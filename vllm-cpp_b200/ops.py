@@ -62,7 +62,6 @@ def _declare(L):
         "vcb_gemm_bf16_tn": [P, P, P, I, I, I, I, LL, LL, LL, I, LL, P, P],
         "vcb_gemm_bf16_tn_shape": [P, P, P, I, I, I, I, LL, LL, LL, I, LL, I, P, P],
         "vcb_gemm_effective_splits": [I, I],
-        "vcb_gemm_bf16_made": [P, P, I, I, I, LL, LL, I, LL, I, P, P, I, LL, P, I, P, P, P, I, LL, P, I, F, F, P, P],
         "vcb_gemm_set_pairs": [I],
         "vcb_gemm_bf16_swiglu": [P, P, P, I, I, I, LL, LL, LL, I, P, P],
         "vcb_sgemm_tn": [P, P, P, I, I, I, LL, LL, LL, P],
@@ -292,62 +291,6 @@ def gemm_bf16_tn(w, x, out, splits, status, shape=-1):
         ldc, sstride = out.stride(1), out.stride(0)
     _call("vcb_gemm_bf16_tn_shape", _p(w), _p(x), _p(out), _dt(out), M, T, K, w.stride(0), x.stride(0), ldc, S, sstride,
           int(shape), _p(status), _stream())
-
-
-def _split_out(out, T, M, K, splits):
-    S = gemm_effective_splits(K, splits)
-    _need(out, "out", torch.float32)
-    if out.dim() == 2:
-        assert S == 1 and out.shape == (T, M)
-        return S, out.stride(0), 0
-    assert out.shape == (S, T, M)
-    return S, out.stride(1), out.stride(0)
-
-
-def gemm_bf16_made_norm(w, resid, delta, gain, resid_out, out, splits, status):
-    """out[z, t, m] = k-slice z of  w[m, :] . bfloat16(gain * (resid[t] + sum of delta[s, t]))  for at most 16 tokens:
-    the residual add and the norm's gain folded into the product's token operand, which the kernel makes for itself
-    (no kernel of their own).  The norm's factor is NOT applied: whoever reads ``out`` multiplies row t by
-    1 / sqrt(sum(ssq[:, t]) / K + eps), with ``ssq`` [2 * slices, T] as returned.  ``resid_out`` (another buffer than
-    ``resid``) receives resid + the deltas.  delta: None, [T, K] or [S', T, K] 32-bit."""
-    _need(w, "w", torch.bfloat16, contiguous=False); _need(resid, "resid", torch.float32); _need(resid_out, "resid_out", torch.float32)
-    _need(gain, "gain")
-    M, K = w.shape
-    T = resid.shape[0]
-    assert resid.shape == (T, K) and resid_out.shape == (T, K) and gain.numel() == K and w.stride(1) == 1
-    n_delta, dstride, dptr = 0, 0, None
-    if delta is not None:
-        _need(delta, "delta", torch.float32)
-        if delta.dim() == 2:
-            delta = delta.unsqueeze(0)
-        assert delta.shape[1:] == (T, K)
-        n_delta, dstride, dptr = delta.shape[0], delta.stride(0), delta.data_ptr()
-    S, ldc, sstride = _split_out(out, T, M, K, splits)
-    from . import workspace
-    ssq = workspace.empty((2 * S, T), torch.float32, resid.device)
-    _call("vcb_gemm_bf16_made", _p(w), _p(out), M, T, K, w.stride(0), ldc, S, sstride, 1, _p(resid), dptr, n_delta, dstride,
-          _p(gain), _dt(gain), _p(resid_out), _p(ssq), None, 0, 0, None, 0, 0.0, 0.0, _p(status), _stream())
-    return ssq
-
-
-def gemm_bf16_made_swiglu(w, gate_up, ssq, width, eps, out, splits, status):
-    """out[z, t, m] = k-slice z of  w[m, :] . bfloat16(silu(g_t) * u_t)  for at most 16 tokens, where g, u are the sums
-    of the slices of a stacked gate/up product ``gate_up`` [S', T, 2K] (gate_i at 2i, up_i at 2i+1), row t scaled first
-    by 1 / sqrt(sum(ssq[:, t]) / width + eps) (``ssq`` None: unscaled): the SiLU-gate as the maker of the down
-    projection's token operand."""
-    _need(w, "w", torch.bfloat16, contiguous=False); _need(gate_up, "gate_up", torch.float32)
-    M, K = w.shape
-    if gate_up.dim() == 2:
-        gate_up = gate_up.unsqueeze(0)
-    T = gate_up.shape[1]
-    assert gate_up.shape[2] == 2 * K and w.stride(1) == 1
-    if ssq is not None:
-        _need(ssq, "ssq", torch.float32)
-        assert ssq.shape[1] == T
-    S, ldc, sstride = _split_out(out, T, M, K, splits)
-    _call("vcb_gemm_bf16_made", _p(w), _p(out), M, T, K, w.stride(0), ldc, S, sstride, 2, None, None, 0, 0, None, 0, None, None,
-          _p(gate_up), gate_up.shape[0], gate_up.stride(0), _p(ssq), 0 if ssq is None else ssq.shape[0], float(width), float(eps),
-          _p(status), _stream())
 
 
 def gemm_bf16_swiglu(w_gate_up, x, out, status, shape=-1):
