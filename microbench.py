@@ -243,6 +243,8 @@ def bench_timeline(cfg, batch: int, context: int, layers: int, first: int, count
     def span(rs, ph):
         ts = [(x["t_ns"] - t0) / 1e3 for x in rs if x["phase"] == ph]
         return (f"{min(ts):9.2f} {max(ts):9.2f}" if ts else "        -         -")
+    if os.environ.get("VCB_TIMELINE_DUMP"):
+        json.dump(rec, open(os.environ["VCB_TIMELINE_DUMP"], "w"))
     print(f"{'kernel':12s} {'blocks':>6s}   {'start: first':>9s} {'last':>9s}   {'wait over: first':>9s} {'last':>6s}   {'end: first':>9s} {'last':>9s}")
     for c in launches[first:first + count]:
         print(f"{c['kernel']:12s} {len({t[0] for t in c['tags']}):6d}   {span(c['recs'], 0)}   {span(c['recs'], 1)}   {span(c['recs'], 2)}")

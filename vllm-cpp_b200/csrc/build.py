@@ -36,6 +36,8 @@ NVCC_FLAGS = [
 # a build a folder of its own (VLLM_CPP_B200_BUILD_DIR) so that it does not replace the regular one
 if os.environ.get("VLLM_CPP_B200_TIMELINE", "0") == "1":
     NVCC_FLAGS.append("-DVCB_TIMELINE")
+# further nvcc flags for experiments (-D switches of single kernels); a build with them wants a folder of its own too
+NVCC_FLAGS += os.environ.get("VLLM_CPP_B200_NVCC_EXTRA", "").split()
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
 
 _lock = threading.Lock()

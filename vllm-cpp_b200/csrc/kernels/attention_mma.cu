@@ -211,7 +211,16 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
         const int pb = my_pb_lo + it * pages_per_tile + my_pg;
         return (it < n_tiles && my_pg < pages_per_tile && pb < my_pb_hi) ? bt[pb] : -1;
     };
-    int next_page = -1;
+    // page ids of the next AHEAD tiles, read that far ahead: each is a load from the block table, and read only one
+    // tile ahead they made the tiles of a short key range (a few tiles, nothing else to wait for) follow each other
+    // at one round trip to memory apiece
+#ifndef VCB_AHEAD
+#define VCB_AHEAD 4
+#endif
+    constexpr int AHEAD = VCB_AHEAD;
+    int ahead_page[AHEAD];
+#pragma unroll
+    for (int k = 0; k < AHEAD; ++k) ahead_page[k] = -1;
     // asks for tile `it` once its stage is free (the producer warp, all lanes); false: give up
     auto issue_tile = [&](int it) {
         const int st = it % STAGES;
@@ -223,7 +232,7 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
         if (lane == 0) mbar_expect_tx(full_bar(st), (uint32_t)(np * ps * ROWB * 2));
         __syncwarp();
         if (my_pg < np) {
-            int page = next_page;
+            int page = ahead_page[0];
             if (page < 0 || page >= a.num_pages) {
                 atomicOr(a.status, VCB_STATUS_BAD_PAGE);
                 page = 0;   // keep the byte count whole; the status word reports the fault
@@ -232,7 +241,9 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
             const uint32_t dst = smem_u32((my_v ? v_s : k_s) + st * TILE_BYTES) + my_h * (BN * 128) + my_pg * ps * 128;
             tma_load_2d(dst, &kv_map, full_bar(st), my_h * 64, row);
         }
-        next_page = page_of(it + 1);
+#pragma unroll
+        for (int k = 0; k + 1 < AHEAD; ++k) ahead_page[k] = ahead_page[k + 1];
+        ahead_page[AHEAD - 1] = page_of(it + AHEAD);
         return true;
     };
     int pre_tiles = 0;
@@ -244,7 +255,8 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
         if (warp == NW) {
             // Tiles whose pages hold only tokens of earlier steps are asked for before the wait: up to a ring's worth.
             const int first_new = ctx - qlen;
-            next_page = page_of(0);
+#pragma unroll
+            for (int k = 0; k < AHEAD; ++k) ahead_page[k] = page_of(k);
             while (pre_tiles < n_tiles && pre_tiles < STAGES &&
                    min(my_pb_hi, my_pb_lo + (pre_tiles + 1) * pages_per_tile) * ps <= first_new) {
                 if (!issue_tile(pre_tiles)) break;
@@ -628,6 +640,7 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
         }
     }
     __syncthreads();   // every tile has been multiplied; the stages and the Q rows are free
+    tl_mark(VCB_TL_ATTN_DEC, 3);
 
     // ---- partial states -> shared memory: o_s[wk][row][HD], ml_s[wk][row][2] ----
     float* o_s = reinterpret_cast<float*>(k_s);             // WK * RMAX x HD floats, over the K and V stages
@@ -698,61 +711,66 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
             if (is_last) *counter = 0;   // ready for the next launch
         }
         __syncthreads();
+        tl_mark(VCB_TL_ATTN_DEC, 4);
         if (is_last) {
             __threadfence();        // the other slices' partials are visible to this block
             const int out_row = a.dec_rows[dec_index];
             if (out_row >= 0) {
-                // First every slice's (maximum, sum) of this block's heads comes into shared memory in one round trip
-                // and becomes a weight per slice; then the slices' outputs are added, four loads in flight at a time.
-                // One load behind the other, the merge of twelve slices took the block as long as its keys had.
-                float* w_s = reinterpret_cast<float*>(k_s);            // [gq][nslices] weights, then [gq] 1 / sum
-                float* inv_s = w_s + gq * nslices;
-                for (int idx = tid; idx < gq * nslices; idx += blockDim.x) {
-                    const int ih = idx / nslices, sl = idx % nslices;
-                    w_s[idx] = __ldcg(a.part_ml + (((size_t)dec_index * a.nh + head0 + ih) * nslices + sl) * 2);
-                }
-                __syncthreads();
-                if (tid < gq) {
-                    const size_t prow0 = ((size_t)dec_index * a.nh + head0 + tid) * nslices;
-                    float m = -CUDART_INF_F;
-                    for (int sl = 0; sl < nslices; ++sl) m = fmaxf(m, w_s[tid * nslices + sl]);
-                    float l = 0.f;
-                    for (int sl0 = 0; sl0 < nslices; sl0 += 4) {       // slice order, as the separate merge kernel does
-                        float ls[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (sl0 + j < nslices) ls[j] = __ldcg(a.part_ml + (prow0 + sl0 + j) * 2 + 1);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (sl0 + j < nslices) {
-                                const float ms = w_s[tid * nslices + sl0 + j];
-                                const float w = ms == -CUDART_INF_F ? 0.f : expf(ms - m);
-                                if (ms != -CUDART_INF_F) l += ls[j] * w;
-                                w_s[tid * nslices + sl0 + j] = w;
-                            }
-                        }
-                    }
-                    inv_s[tid] = l > 0.f ? 1.f / l : 0.f;
-                }
-                __syncthreads();
+                // Everything the merge reads -- every slice's (maximum, sum) and output of this thread's head and pair of
+                // lanes -- is asked for at once and then combined in slice order: one round trip to memory.  One load
+                // behind the other, the merge of twelve slices took the block as long as its keys had.
+#ifndef VCB_MS
+#define VCB_MS 12
+#endif
+                constexpr int MS = VCB_MS;     // slices merged per batch (more run through the loop again)
                 for (int idx = tid; idx < gq * (HD / 2); idx += blockDim.x) {
                     const int ih = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
                     const size_t prow0 = ((size_t)dec_index * a.nh + head0 + ih) * nslices;
-                    float o0 = 0.f, o1 = 0.f;
-                    for (int sl0 = 0; sl0 < nslices; sl0 += 4) {
-                        float2 ov[4];
+                    float m = -CUDART_INF_F, l = 0.f, o0 = 0.f, o1 = 0.f;
+                    if (nslices <= MS) {
+                        float2 mlv[MS], ov[MS];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (sl0 + j < nslices) ov[j] = __ldcg(reinterpret_cast<const float2*>(a.part_o + (prow0 + sl0 + j) * HD + d));
+                        for (int j = 0; j < MS; ++j) {
+                            if (j < nslices) {
+                                mlv[j] = __ldcg(reinterpret_cast<const float2*>(a.part_ml + (prow0 + j) * 2));
+                                ov[j] = __ldcg(reinterpret_cast<const float2*>(a.part_o + (prow0 + j) * HD + d));
+                            }
+                        }
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (sl0 + j < nslices) {
-                                const float w = w_s[ih * nslices + sl0 + j];
-                                if (w != 0.f) { o0 += ov[j].x * w; o1 += ov[j].y * w; }
+                        for (int j = 0; j < MS; ++j)
+                            if (j < nslices) m = fmaxf(m, mlv[j].x);
+#pragma unroll
+                        for (int j = 0; j < MS; ++j) {     // slice order, as the separate merge kernel does
+                            if (j < nslices && mlv[j].x != -CUDART_INF_F) {
+                                const float w = expf(mlv[j].x - m);
+                                l += mlv[j].y * w;
+                                o0 += ov[j].x * w;
+                                o1 += ov[j].y * w;
+                            }
+                        }
+                    } else {
+                        for (int sl = 0; sl < nslices; ++sl) m = fmaxf(m, __ldcg(a.part_ml + (prow0 + sl) * 2));
+                        for (int sl0 = 0; sl0 < nslices; sl0 += MS) {
+                            float2 mlv[MS], ov[MS];
+#pragma unroll
+                            for (int j = 0; j < MS; ++j) {
+                                if (sl0 + j < nslices) {
+                                    mlv[j] = __ldcg(reinterpret_cast<const float2*>(a.part_ml + (prow0 + sl0 + j) * 2));
+                                    ov[j] = __ldcg(reinterpret_cast<const float2*>(a.part_o + (prow0 + sl0 + j) * HD + d));
+                                }
+                            }
+#pragma unroll
+                            for (int j = 0; j < MS; ++j) {
+                                if (sl0 + j < nslices && mlv[j].x != -CUDART_INF_F) {
+                                    const float w = expf(mlv[j].x - m);
+                                    l += mlv[j].y * w;
+                                    o0 += ov[j].x * w;
+                                    o1 += ov[j].y * w;
+                                }
                             }
                         }
                     }
-                    const float inv = inv_s[ih];
+                    const float inv = l > 0.f ? 1.f / l : 0.f;
                     *reinterpret_cast<__nv_bfloat162*>(a.out + ((size_t)out_row * a.nh + head0 + ih) * HD + d) =
                         __floats2bfloat162_rn(o0 * inv, o1 * inv);
                 }
