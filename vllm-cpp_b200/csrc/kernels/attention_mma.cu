@@ -118,7 +118,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 
 // WR row groups x WK key groups multiplying warps, MR tiles of 16 rows each; TMA adds one warp that only issues
 // tile loads.
-template <int HD, int WR, int WK, int MR, bool TMA>
+// DEEP: a ring of six stages instead of three, for launches whose blocks have an SM each anyway (one or two requests
+// decoding): a short key slice is then all on its way before the block's wait is over, where a ring of three brought
+// the second half one memory latency after the first.
+template <int HD, int WR, int WK, int MR, bool TMA, bool DEEP = false>
 __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel(const __grid_constant__ CUtensorMap kv_map,
                                                                         AttnArgs a) {
     static_assert(HD % 64 == 0 && BN % (16 * WK) == 0, "layout");
@@ -130,7 +133,7 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
     constexpr int KW = BN / WK;     // keys of a tile that one warp multiplies
     constexpr int NS = KW / 8;      // score n-tiles per warp
     constexpr int ND = HD / 8;      // output n-tiles
-    constexpr int STAGES = (TMA && WK == 4) ? 3 : 2;   // decoding streams keys: a deeper ring; prompt portions multiply more
+    constexpr int STAGES = (TMA && WK == 4) ? (DEEP ? 6 : 3) : 2;   // decoding streams keys: a deeper ring; prompt portions multiply more
     constexpr int TILE_BYTES = BN * ROWB;   // one K or V tile
     constexpr float LOG2E = 1.4426950408889634f;
 
@@ -843,10 +846,25 @@ bool kv_tensor_map(const void* pages, long long rows, int hd, int page_size, CUt
     return true;
 }
 
-template <int HD, int WR, int WK, int MR, bool TMA>
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int HD, int WR, int WK, int MR, bool TMA, bool DEEP = false>
 int launch(const AttnArgs& a, int n_items, cudaStream_t stream) {
     constexpr int RMAX = 16 * WR * MR;
-    constexpr int STAGES = (TMA && WK == 4) ? 3 : 2;
+    constexpr int STAGES = (TMA && WK == 4) ? (DEEP ? 6 : 3) : 2;
+    if constexpr (TMA && WK == 4 && !DEEP) {
+        // blocks that have an SM to themselves anyway take the deep ring
+        const int g0 = a.nh / a.nkv, gq0 = g0 < RMAX ? g0 : RMAX;
+        if ((long long)n_items * a.nkv * ((g0 + gq0 - 1) / gq0) <= sm_count()) return launch<HD, WR, WK, MR, TMA, true>(a, n_items, stream);
+    }
     const int g = a.nh / a.nkv;
     const int gq_max = g < RMAX ? g : RMAX;
     const int hchunks = (g + gq_max - 1) / gq_max;
@@ -863,7 +881,7 @@ int launch(const AttnArgs& a, int n_items, cudaStream_t stream) {
         }
         if (!kv_tensor_map(a.pages, rows, HD, a.page_size, &map)) return -3;
     }
-    auto kern = attn_mma_kernel<HD, WR, WK, MR, TMA>;
+    auto kern = attn_mma_kernel<HD, WR, WK, MR, TMA, DEEP>;
     static bool opted = false;
     if (!opted) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
