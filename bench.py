@@ -221,7 +221,9 @@ def run_headline(args, pk, clocks, windows):
             results[("ctx", WORKLOAD_CONTEXT)] = decode_point(args.batch, WORKLOAD_CONTEXT, args.steps, args.warmup)
             results[("eager", args.batch)] = decode_point(args.batch, args.context, args.steps, args.warmup, graphs=False)
     if args.mode == "decode":
-        print(json.dumps({"mode": "decode", "ms_per_step": {f"{k[0]}{k[1]}": v["ms"] for k, v in results.items()}}))
+        print(json.dumps({"mode": "decode", "batch": args.batch, "context": args.context, "layers": args.layers,
+                          "ms_per_step": {f"{k[0]}{k[1]}": v["ms"] for k, v in results.items()},
+                          "roofline_frac": {f"{k[0]}{k[1]}": round(v["frac"], 4) for k, v in results.items()}}))
         return None
     head = results.get(("b", args.batch))
 

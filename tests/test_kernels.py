@@ -83,6 +83,20 @@ def test_swiglu(dtype):
     torch.testing.assert_close(out.double(), g / (1 + torch.exp(-g)) * u, **tol(dtype))
 
 
+@pytest.mark.parametrize("T,I,S", [(8, 12288, 3), (64, 200, 1), (257, 1004, 5), (3, 36, 9)])
+def test_swiglu_of_k_slice_partial_sums(T, I, S):
+    """32-bit partial sums of a stacked gate/up product in, bfloat16 out (what follows a sliced product in the
+    bfloat16 engine): the slices are added in order, then the SiLU-gate."""
+    from vllm_cpp_b200 import ops
+    torch.manual_seed(T + I + S)
+    gu = 2 * torch.randn(S, T, 2 * I, device=dev())
+    out = torch.empty(T, I, device=dev(), dtype=torch.bfloat16)
+    ops.swiglu(gu, out)
+    x = gu.double().sum(0)
+    g, u = x[:, 0::2], x[:, 1::2]
+    torch.testing.assert_close(out.double(), g / (1 + torch.exp(-g)) * u, **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 64, 64), (3, 200, 96), (17, 384, 200), (130, 67, 33), (64, 64, 1)])
 def test_sgemm_tn(M, N, K):
     from vllm_cpp_b200 import ops

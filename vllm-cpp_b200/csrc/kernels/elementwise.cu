@@ -321,6 +321,46 @@ __global__ void swiglu_kernel(const TIN* __restrict__ gu, int S, size_t s_stride
     tl_mark(VCB_TL_SWIGLU, 2);
 }
 
+// 32-bit k-slice partial sums in, bfloat16 out, I a multiple of 4: a thread makes four outputs from two 16-byte loads a
+// slice (g0 u0 g1 u1, g2 u2 g3 u3), all slices' loads of up to four slices in flight together, added in slice order.
+__global__ void swiglu_partials_vec_kernel(const float* __restrict__ gu, int S, size_t s_stride, __nv_bfloat16* __restrict__ out,
+                                           int I4, size_t total4) {
+    pdl_trigger();
+    tl_mark(VCB_TL_SWIGLU, 0);
+    pdl_wait();
+    tl_mark(VCB_TL_SWIGLU, 1);
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I4, i = idx % I4;
+        const float4* src = reinterpret_cast<const float4*>(gu + t * 8 * (size_t)I4) + 2 * i;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        for (int s0 = 0; s0 < S; s0 += 4) {
+            float4 ta[4], tb[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (s0 + j < S) {
+                    const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) + (size_t)(s0 + j) * s_stride);
+                    ta[j] = p[0];
+                    tb[j] = p[1];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (s0 + j < S) {
+                    a.x += ta[j].x; a.y += ta[j].y; a.z += ta[j].z; a.w += ta[j].w;
+                    b.x += tb[j].x; b.y += tb[j].y; b.z += tb[j].z; b.w += tb[j].w;
+                }
+            }
+        }
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a.x / (1.0f + expf(-a.x)) * a.y, a.z / (1.0f + expf(-a.z)) * a.w);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(b.x / (1.0f + expf(-b.x)) * b.y, b.z / (1.0f + expf(-b.z)) * b.w);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&lo);
+        pk.y = *reinterpret_cast<uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(out)[idx] = pk;
+    }
+    tl_mark(VCB_TL_SWIGLU, 2);
+}
+
 // bfloat16 in and out, one slice, I a multiple of 8: 16-byte loads and stores
 __global__ void swiglu_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I8, size_t total8) {
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
@@ -356,6 +396,15 @@ VCB_API int vcb_swiglu(const void* gate_up, int in_dtype, int S, long long s_str
         VCB_CHECK_LAUNCH("swiglu");
         return 0;
     }
+    if (in_dtype == VCB_F32 && out_dtype == VCB_BF16 && I % 4 == 0 && s_stride % 4 == 0 && ((uintptr_t)gate_up % 16 == 0) &&
+        ((uintptr_t)out % 8 == 0)) {
+        const size_t total4 = total / 4;
+        const int nb = (int)((total4 + 255) / 256 < 148 * 8 ? (total4 + 255) / 256 : 148 * 8);   // all blocks resident at once
+        launch_pdl(swiglu_partials_vec_kernel, dim3(nb), dim3(256), 0, stream, (const float*)gate_up, S, (size_t)s_stride,
+                   (__nv_bfloat16*)out, I / 4, total4);
+        VCB_CHECK_LAUNCH("swiglu");
+        return 0;
+    }
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     if (in_dtype == VCB_F32 && out_dtype == VCB_F32)
         launch_pdl(swiglu_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, S, (size_t)s_stride, (float*)out, I, total);
@@ -379,7 +428,9 @@ VCB_API int vcb_swiglu(const void* gate_up, int in_dtype, int S, long long s_str
 // src/mlx_backend.cpp:411-412 and src/model.cpp:983-985).  A thread owns pair i = lane + 32 j of a head: lanes
 // (i, i + rot_dim/2) or (2i, 2i+1) while i < rot_dim/2, and the unrotated lanes (2i, 2i+1) beyond.
 // ---------------------------------------------------------------------------
-template <typename TIN, typename T>
+// MAXP: lane pairs a thread owns (2 serves heads of up to 128 lanes, 4 of up to 256): the serving models' heads
+// keep the kernel at a register count that lets an SM hold enough warps when there are thousands of (token, head)s.
+template <typename TIN, typename T, int MAXP>
 __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, size_t s_stride, const void* __restrict__ qw,
                                            const void* __restrict__ kw, int w_dtype, int use_norm, float eps,
                                            const float* __restrict__ cos_sin, int max_pos,
@@ -399,7 +450,6 @@ __global__ void qknorm_rope_kvwrite_kernel(const TIN* __restrict__ qkv, int S, s
     const int t = active ? (int)(gw / heads_total) : 0, h = active ? (int)(gw % heads_total) : 0;
     const TIN* src = qkv + (size_t)t * heads_total * hd + (size_t)h * hd;
     const int half = hd >> 1;
-    constexpr int MAXP = VCB_MAX_HEAD_DIM / 64;  // pairs per lane
 
     // What no kernel of the step writes -- the token's slot and position, the gains, the angles -- is read before
     // waiting for the kernel that produces qkv, so that only one round trip to memory follows the wait.
@@ -624,7 +674,12 @@ VCB_API int vcb_qknorm_rope_kvwrite(const void* qkv, int in_dtype, int S, long l
     const long long blocks = (warps + wpb - 1) / wpb;
     VCB_CHECK_ARG(blocks < (1ll << 31), "qknorm_rope_kvwrite: too many blocks");
 #define VCB_QK_LAUNCH(TIN, TOUT)                                                                                      \
-    launch_pdl(qknorm_rope_kvwrite_kernel<TIN, TOUT>, dim3((unsigned)blocks), dim3(wpb * 32), 0, stream,                 \
+    if (hd <= 128)                                                                                                    \
+    launch_pdl(qknorm_rope_kvwrite_kernel<TIN, TOUT, 2>, dim3((unsigned)blocks), dim3(wpb * 32), 0, stream,              \
+        (const TIN*)qkv, S, (size_t)s_stride, qw, kw, w_dtype, use_norm, eps, cos_sin, max_pos, positions, slot_map,   \
+        (TOUT*)q_out, (TOUT*)pages, page_stride, page_size, num_pages, nh, nkv, hd, T, has_kv, rot_dim, interleaved, status); \
+    else                                                                                                              \
+    launch_pdl(qknorm_rope_kvwrite_kernel<TIN, TOUT, VCB_MAX_HEAD_DIM / 64>, dim3((unsigned)blocks), dim3(wpb * 32), 0, stream, \
         (const TIN*)qkv, S, (size_t)s_stride, qw, kw, w_dtype, use_norm, eps, cos_sin, max_pos, positions, slot_map,   \
         (TOUT*)q_out, (TOUT*)pages, page_stride, page_size, num_pages, nh, nkv, hd, T, has_kv, rot_dim, interleaved, status)
     if (in_dtype == VCB_F32 && out_dtype == VCB_F32) VCB_QK_LAUNCH(float, float);
