@@ -272,3 +272,38 @@ def test_profile_of_kernel_groups(model_dirs, plain_models):
     assert all(v > 0 for v in st.kernel_ms.values())
     assert st.preemptions == 0                       # the scheduler's own counters are still there
     assert make_llm(model_dirs["B"], "B").stats().kernel_ms == {}
+
+
+def test_nothing_is_finalised_while_a_step_is_captured(model_dirs, plain_models):
+    """An engine that is dropped leaves captured graphs behind, in reference cycles that only the collector frees;
+    destroying one while another capture is open makes that capture invalid.  So the runner collects before it
+    captures and keeps the collector off until the capture is closed: seen here from inside the model's forward
+    pass, with the dropped engine's graphs as the garbage."""
+    import gc
+    import weakref
+
+    import torch
+    prompts = [random_tokens(256, n, 1 + i) for i, n in enumerate((5, 11, 17))]
+    old = make_llm(model_dirs["A"], "A")
+    old.generate(prompts, 4, 0.0, 1.0, repeat_penalty=1.0)
+    assert len(old.runner._graphs) > 0
+    ring = [old]
+    ring.append(ring)                      # garbage that reference counting alone does not free
+    gone = weakref.ref(old.runner)
+    del old, ring
+
+    llm = make_llm(model_dirs["A"], "A")
+    seen = []
+    forward = llm.runner.model.forward
+
+    def watched(ctx, views):
+        if torch.cuda.is_current_stream_capturing():
+            seen.append((gc.isenabled(), gone() is None))
+        return forward(ctx, views)
+
+    llm.runner.model.forward = watched
+    assert gc.isenabled()
+    got = llm.generate(prompts, 8, 0.0, 1.0, repeat_penalty=1.0)
+    assert seen and all(not enabled and freed for enabled, freed in seen)
+    assert gc.isenabled()
+    assert got == [plain_generate(plain_models, "A", p, 8) for p in prompts]

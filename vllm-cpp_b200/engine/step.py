@@ -23,6 +23,7 @@ hundred small kernels would otherwise exceed the time the GPU needs for them.
 from __future__ import annotations
 
 import collections
+import gc
 
 from dataclasses import dataclass, field
 
@@ -617,8 +618,18 @@ class ModelRunner:
         torch.cuda.synchronize()
         before = ops.launch_count
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            result = run()
+        # Nothing may be destroyed on the device while a capture is open: a captured graph of an engine that is no
+        # longer referenced, finalised by the collector in the middle of this capture, makes the capture invalid.
+        # So what is garbage goes now, and the collector rests until the capture is closed.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                result = run()
+        finally:
+            if collecting:
+                gc.enable()
         self.launches_per_graph[key] = ops.launch_count - before
         self._keep_graph(key, (graph, ctx, result, staging))
 
