@@ -804,7 +804,7 @@ EncodeTiledFn encode_fn() {
 }
 
 // The pages of one layer seen as a matrix [num_pages * 2 * nkv * page_size, HD]; boxes of [page_size rows, 64 lanes].
-bool kv_tensor_map(const void* pages, long long rows, int hd, int page_size, CUtensorMap* out) {
+bool kv_tensor_map(const void* pages, long long rows, int hd, int page_size, CUtensorMap* out, bool grouped = false) {
     struct Key {
         const void* p; long long rows; int hd, ps;
         bool operator==(const Key& o) const { return p == o.p && rows == o.rows && hd == o.hd && ps == o.ps; }
@@ -816,7 +816,7 @@ bool kv_tensor_map(const void* pages, long long rows, int hd, int page_size, CUt
     };
     static std::mutex mu;
     static std::unordered_map<Key, CUtensorMap, Hash> cache;
-    const Key key{pages, rows, hd, page_size};
+    const Key key{pages, rows, hd, grouped ? -page_size : page_size};
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
     if (it != cache.end()) {
@@ -833,9 +833,21 @@ bool kv_tensor_map(const void* pages, long long rows, int hd, int page_size, CUt
     const cuuint32_t box[2] = {64u, (cuuint32_t)page_size};
     const cuuint32_t elem[2] = {1, 1};
     CUtensorMap m;
-    const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, elem,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r;
+    if (!grouped) {
+        r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        // [groups of 8 rows][halves of head_dim][8 rows][64 lanes], innermost first
+        const cuuint64_t dims4[4] = {64, 8, (cuuint64_t)(hd / 64), (cuuint64_t)(rows / 8)};
+        const cuuint64_t strides4[3] = {(cuuint64_t)hd * 2, 128, (cuuint64_t)hd * 2 * 8};
+        const cuuint32_t box4[4] = {64u, 8u, (cuuint32_t)(hd / 64), (cuuint32_t)(page_size / 8)};
+        const cuuint32_t elem4[4] = {1, 1, 1, 1};
+        r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(pages), dims4, strides4, box4, elem4,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     if (r != CUDA_SUCCESS) {
         vcb_set_error("attn_mma: cuTensorMapEncodeTiled failed with %d (rows %lld, head_dim %d, page %d)", (int)r, rows, hd, page_size);
         return false;
@@ -905,8 +917,8 @@ int launch_rows(const AttnArgs& a, int n_items, int rows_max, cudaStream_t strea
 
 VCB_TIMELINE_UNIT(attn_mma)
 
-bool vcb_kv_tensor_map(const void* pages, long long rows, int hd, int page_size, CUtensorMap* out) {
-    return kv_tensor_map(pages, rows, hd, page_size, out);
+bool vcb_kv_tensor_map(const void* pages, long long rows, int hd, int page_size, CUtensorMap* out, bool grouped) {
+    return kv_tensor_map(pages, rows, hd, page_size, out, grouped);
 }
 
 // rows_max: 16 (single decoded tokens; four warps split each tile's keys) or 128 (prompt portions; eight warps of

@@ -24,6 +24,13 @@
 // as soon as its scores are computed, and the next keys must be asked for two tiles ahead to arrive in time.
 // Roles (192 threads): warp 0 issues TMA loads of K and V pages (cp.async.bulk.tensor, 128-byte swizzle; no
 // multicast) into a ring of stages; warp 1 allocates TMEM and issues every MMA; warps 2-5 are the softmax rows.
+//
+// A page comes in with ONE copy, whatever head_dim: the cache is described to the TMA unit as a four-dimensional
+// tensor [groups of 8 tokens][halves of head_dim][8 tokens][64 lanes], and a box of a page's groups lands as
+// [group][half][8 rows of 128 bytes] -- every 1 KB piece a swizzle atom of 8 rows.  The descriptors of both products
+// step from one group of 8 keys to the next by the same stride (halves x 1 KB) and from one half of head_dim to the
+// other by 1 KB, so the keys keep their order in a tile whatever the page size.  (One copy per page and half, the
+// obvious way, made the copying warp the slowest role of the block: about 100 clocks a copy, 16 copies a tile.)
 // All hand-offs are mbarriers; every wait is bounded by the clock, and a wait that runs out sets a bit in the
 // status word and an abort flag that the other roles see, after which the block frees its TMEM and returns.
 #include "common.cuh"
@@ -55,10 +62,11 @@ struct TcArgs {
     int* status;
 };
 
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+// a box of whole groups of 8 tokens, all lanes: coordinates (lane 0, token 0, half 0, group)
+__device__ __forceinline__ void tma_load_groups(uint32_t dst, const CUtensorMap* map, uint32_t bar, int group) {
     asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %3, %3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(group) : "memory");
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -98,15 +106,15 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16])
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptors (version 1, 128-byte swizzle = layout 2 in bits 61-63; addresses and offsets
-// in units of 16 bytes).  K-major tile (rows of 128 bytes along the inner dimension): 8-row groups 1024 bytes
+// in units of 16 bytes).  K-major tile (rows of 128 bytes along the inner dimension): 8-row groups `group_bytes`
 // apart (stride offset, bits 32-45); the leading offset is unused.  MN-major tile (rows of 128 bytes = 64
-// elements along M or N, one row per inner index): groups of 8 inner indices 1024 bytes apart (stride offset),
+// elements along M or N, one row per inner index): groups of 8 inner indices `group_bytes` apart (stride offset),
 // groups of 64 outer elements `outer_bytes` apart (leading offset, bits 16-29).
-__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr, uint32_t group_bytes) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(group_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
-__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t outer_bytes) {
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(outer_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t outer_bytes, uint32_t group_bytes) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(outer_bytes >> 4) << 16) | ((uint64_t)(group_bytes >> 4) << 32) |
            (1ull << 46) | (2ull << 61);
 }
 // kind::f16 instruction descriptor: f32 accumulate (bits 4-5 = 1), A and B bfloat16 (bits 7-9, 10-12 = 1),
@@ -121,6 +129,10 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
 // the descriptors above describe.
 template <int NROWS> __device__ __forceinline__ int swz(int r, int c) {
     return (c >> 3) * (NROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+}
+// The same for a K or V tile as the page copies lay it out: [groups of 8 keys][halves of head_dim][8 rows][128 bytes].
+template <int HALVES> __device__ __forceinline__ int swz_groups(int key, int c) {
+    return (key >> 3) * (HALVES * 1024) + (c >> 3) * 1024 + (key & 7) * 128 + (((c & 7) ^ (key & 7)) << 4);
 }
 // 2^x to 2^-22 relative; -inf gives 0
 __device__ __forceinline__ float ex2_fast(float x) {
@@ -140,7 +152,8 @@ struct Layout {
     static constexpr int K_OFF = Q_BYTES;
     static constexpr int V_OFF = K_OFF + KS * KV_BYTES;
     static constexpr int BAR_OFF = V_OFF + VS * KV_BYTES;
-    static constexpr int NUM_BARS = 2 * KS + 2 * VS + 6;
+    static constexpr int NUM_BARS = 2 * KS + VS + 7;
+    static_assert(VS == 2, "a V stage is given back by the barrier of the score buffer its tile used");
     static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 16;   // + TMEM address, abort flag
     static constexpr uint32_t TMEM_COLS = 256;                  // S, S (64 each; P over the first half of its S), O (head_dim)
     static_assert(2 * BNK + HD <= 256, "TMEM columns");
@@ -154,6 +167,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
     using L = Layout<HD, KS, VS>;
     constexpr int CH = HD / 8;          // 16-byte chunks per row of head_dim
     constexpr int ROWB = HD * 2;
+    constexpr int HALVES = HD / 64;
     constexpr float LOG2E = 1.4426950408889634f;
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];   // swizzle atoms are 1024-byte aligned
@@ -163,14 +177,16 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
     auto k_full = [&](int s) { return bars + 8u * s; };
     auto k_empty = [&](int s) { return bars + 8u * (KS + s); };
     auto v_full = [&](int s) { return bars + 8u * (2 * KS + s); };
-    auto v_empty = [&](int s) { return bars + 8u * (2 * KS + VS + s); };
-    auto s_full = [&](int b) { return bars + 8u * (2 * KS + 2 * VS + b); };
+    auto s_full = [&](int b) { return bars + 8u * (2 * KS + VS + b); };
     // Every row has written its weights of a tile.  One barrier per score buffer: a warp may finish tile j + 1
     // before another has finished tile j (its scores are ready early), and with a single barrier its second
     // arrival would be counted into the phase of tile j.  Tile j + 2 cannot begin before that phase is over.
-    auto p_ready = [&](int b) { return bars + 8u * (2 * KS + 2 * VS + 2 + b); };
-    const uint32_t pv_done = bars + 8u * (2 * KS + 2 * VS + 4);   // one phase per tile: P . V of the tile has been added to O
-    const uint32_t q_ready = bars + 8u * (2 * KS + 2 * VS + 5);
+    auto p_ready = [&](int b) { return bars + 8u * (2 * KS + VS + 2 + b); };
+    // P . V of a tile has been added to O: tile j completes phase j / 2 of barrier j % 2.  Two barriers, because those
+    // who ask (a row that must rescale O, the loader that wants the tile's V stage back) ask by parity and may be a
+    // tile behind the products; with one phase per tile on a single barrier an old phase would pass for the new one.
+    auto pv_done = [&](int b) { return bars + 8u * (2 * KS + VS + 4 + b); };
+    const uint32_t q_ready = bars + 8u * (2 * KS + VS + 6);
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(gen + L::BAR_OFF + L::NUM_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::BAR_OFF + L::NUM_BARS * 8 + 8);
 
@@ -217,15 +233,12 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
             mbar_init(k_full(s), 1);
             mbar_init(k_empty(s), 1);
         }
-        for (int s = 0; s < VS; ++s) {
-            mbar_init(v_full(s), 1);
-            mbar_init(v_empty(s), 1);
-        }
+        for (int s = 0; s < VS; ++s) mbar_init(v_full(s), 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(s_full(b), 1);
             mbar_init(p_ready(b), ROWS);    // one arrival per row
+            mbar_init(pv_done(b), 1);
         }
-        mbar_init(pv_done, 1);
         mbar_init(q_ready, ROWS);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -243,20 +256,19 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * BNK;   // S, S, O
 
     if (warp == 0) {
-        // ---- TMA producer: one box of [page_size keys x 64 lanes] per page, per half of head_dim, for K and V.
-        // The boxes of a tile (up to 32) are issued by as many lanes at once: a single thread issuing them one
-        // after the other, each behind its own block-table read, was the slowest role of the block. ----
+        // ---- TMA producer: one box per page, for K and for V.  The boxes of a tile (up to 8) are issued by as
+        // many lanes at once: a single thread issuing them one after the other, each behind its own block-table
+        // read, was the slowest role of the block. ----
         const int pages_per_tile = BNK / ps;
-        const int rows_kv = a.nkv * ps;          // rows of the flattened [pages * 2 * nkv * ps, HD] view per K or V
-        constexpr int HALVES = HD / 64;
+        const int groups_page = ps / 8;
+        const int groups_kv = a.nkv * groups_page;   // groups of 8 rows from a page's K to its V
         int armed[2] = {0, 0};
         // This lane's page id for the next K and the next V tile, read one call ahead: a block-table read that
         // misses L1 costs about as long as a whole tile's products, and it stood between the stage's release
         // and the load.  Tiles of one kind are loaded in order, so the next tile is known.
-        const int my_pg = lane / HALVES, my_h = lane % HALVES;
         auto page_of = [&](int it) {
-            const int pb = pb_lo + it * pages_per_tile + my_pg;
-            return (it < n_tiles && my_pg < pages_per_tile && pb < pb_hi) ? bt[pb] : -1;
+            const int pb = pb_lo + it * pages_per_tile + lane;
+            return (it < n_tiles && lane < pages_per_tile && pb < pb_hi) ? bt[pb] : -1;
         };
         int next_page[2] = {page_of(0), page_of(0)};
         // loads the K (is_v 0) or V (1) tile `it` into its ring once the stage is free; false: give up
@@ -264,21 +276,26 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
             const int ns = is_v ? VS : KS, st = it % ns;
             const uint32_t fullb = is_v ? v_full(st) : k_full(st);
             bool ok = true;
-            if (lane == 0) ok = mbar_wait(is_v ? v_empty(st) : k_empty(st), ((it / ns) & 1) ^ 1u, abort_flag, a.status);
+            if (lane == 0) {
+                // a K stage is free when its scores are there; a V stage when the product of the tile that used it
+                // (VS = 2 tiles ago, so on the same score buffer) has been added
+                if (!is_v) ok = mbar_wait(k_empty(st), ((it / ns) & 1) ^ 1u, abort_flag, a.status);
+                else if (it >= VS) ok = mbar_wait(pv_done(it & 1), (((it - VS) >> 1) & 1), abort_flag, a.status);
+            }
             if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
             const int pb0 = pb_lo + it * pages_per_tile;
             const int np = min(pages_per_tile, pb_hi - pb0);
             if (lane == 0) mbar_expect_tx(fullb, (uint32_t)(np * ps * ROWB));
             __syncwarp();
             const uint32_t dst = base + (is_v ? L::V_OFF : L::K_OFF) + st * L::KV_BYTES;
-            if (lane < np * HALVES) {   // at most 8 pages x 2 halves: one box a lane
+            if (lane < np) {   // at most 8 pages: one box a lane
                 int page = next_page[is_v];
                 if (page < 0 || page >= a.num_pages) {
                     atomicOr(a.status, VCB_STATUS_BAD_PAGE);
                     page = 0;   // keep the byte count whole; the status word reports the fault
                 }
-                const int row = (page * 2 * a.nkv + kvh) * ps + (is_v ? rows_kv : 0);
-                tma_load_2d(dst + my_h * (BNK * 128) + my_pg * ps * 128, &kv_map, fullb, my_h * 64, row);
+                const int group = (page * 2 * a.nkv + kvh) * groups_page + (is_v ? groups_kv : 0);
+                tma_load_groups(dst + lane * ps * ROWB, &kv_map, fullb, group);
             }
             next_page[is_v] = page_of(it + 1);
             armed[is_v] = it + 1;
@@ -316,12 +333,11 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks) {
                     // 16 lanes of head_dim = 32 bytes along the 128-byte rows; the second 64 lanes are the next block
-                    const uint64_t da = desc_k_major(qa + (ks / 4) * (ROWS * 128) + (ks % 4) * 32);
-                    const uint64_t db = desc_k_major(ka + (ks / 4) * (BNK * 128) + (ks % 4) * 32);
+                    const uint64_t da = desc_k_major(qa + (ks / 4) * (ROWS * 128) + (ks % 4) * 32, 1024);
+                    const uint64_t db = desc_k_major(ka + (ks / 4) * 1024 + (ks % 4) * 32, HALVES * 1024);
                     tc_mma(tmem_s + b * BNK, da, db, idesc_qk, ks > 0);
                 }
-                tc_commit(s_full(b));
-                tc_commit(k_empty(st));   // the keys of this stage have been read
+                tc_commit(s_full(b));   // the row that sees it first gives the K stage back (a commit less for this thread)
                 return true;
             };
             if (ok) ok = issue_qk(0);
@@ -337,13 +353,12 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                 const uint32_t va = base + L::V_OFF + st * L::KV_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < BNK / 16; ++ks) {
-                    // 16 keys = 16 rows of 128 bytes further on; the second 64 lanes of head_dim are the next block.
+                    // 16 keys = two groups of 8 rows; the second 64 lanes of head_dim lie 1 KB after the first.
                     // P: 16 keys = 8 columns of the scores' buffer.
-                    const uint64_t db = desc_mn_major(va + ks * 16 * 128, BNK * 128);
+                    const uint64_t db = desc_mn_major(va + ks * 2 * (HALVES * 1024), 1024, HALVES * 1024);
                     tc_mma_ts(tmem_o, tmem_s + b * BNK + ks * 8, db, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                 }
-                tc_commit(pv_done);
-                tc_commit(v_empty(st));   // the values of this stage have been read
+                tc_commit(pv_done(b));   // also gives the V stage back
             }
         }
     } else {
@@ -378,6 +393,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
             const int t0 = t_first + j * BNK;
             ok = mbar_wait(s_full(b), (j >> 1) & 1, abort_flag, a.status);
             if (!ok) break;
+            if (tid == 64) mbar_arrive(k_empty(j % KS));   // the scores are there: the keys of this stage have been read
             tc_fence_after();
             uint32_t sv[4][16];
 #pragma unroll
@@ -407,7 +423,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
             const bool first_keys = m_ref == -CUDART_INF_F && m_new != -CUDART_INF_F;   // nothing summed yet
             const bool grow = m_ref != -CUDART_INF_F && m_new > m_ref + RESCALE_STEP;
             if (__any_sync(0xffffffffu, grow)) {
-                ok = mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status);   // grow implies j > 0
+                ok = mbar_wait(pv_done((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag, a.status);   // grow implies j > 0
                 if (!ok) break;
                 tc_fence_after();
                 const float alpha = grow ? exp2f(m_ref - m_new) : 1.f;
@@ -448,17 +464,9 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                 const int first = k_end - t0;
                 for (int idx = r; idx < (BNK - first) * CH; idx += ROWS) {
                     const int jj = first + idx / CH, c = idx % CH;
-                    *reinterpret_cast<uint4*>(gen + L::V_OFF + st * L::KV_BYTES + swz<BNK>(jj, c)) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(gen + L::V_OFF + st * L::KV_BYTES + swz_groups<HALVES>(jj, c)) = make_uint4(0, 0, 0, 0);
                 }
                 fence_async_smem();   // before the arrival below, which the product that reads these rows awaits
-            }
-            // Every row sees the product of the tile before finish before it hands over this one.  Nothing it
-            // writes needs that, but the barrier counts one phase per tile and is asked by parity: a row that ran
-            // two tiles ahead of it would take an old phase for the one it waits for (when it rescales O, and
-            // before it reads O at the end).
-            if (j > 0) {
-                ok = mbar_wait(pv_done, (j - 1) & 1, abort_flag, a.status);
-                if (!ok) break;
             }
             // The row of P over the first half of its scores: column c holds the weights of keys 2c and 2c + 1.
             // (P of tile j - 2 lay here; its product was issued before the scores of this tile were computed.)
@@ -471,7 +479,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
             tc_fence_before();
             mbar_arrive(p_ready(b));
         }
-        if (ok) ok = mbar_wait(pv_done, (n_tiles - 1) & 1, abort_flag, a.status);
+        if (ok) ok = mbar_wait(pv_done((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag, a.status);
 
         if (ok) {
             tc_fence_after();
@@ -548,7 +556,7 @@ VCB_API int vcb_attn_tc(const void* q, void* out, const void* pages, long long p
                   "attn_tc: the pages of a layer must be contiguous and 16-byte aligned for TMA loads");
     VCB_CHECK_ARG(((uintptr_t)q % 16 == 0) && ((uintptr_t)out % 16 == 0), "attn_tc: q and out must be 16-byte aligned");
     CUtensorMap map;
-    if (!vcb_kv_tensor_map(pages, (long long)num_pages * 2 * nkv * page_size, hd, page_size, &map)) return -3;
+    if (!vcb_kv_tensor_map(pages, (long long)num_pages * 2 * nkv * page_size, hd, page_size, &map, true)) return -3;
     TcArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, block_table, table_row, max_blocks, q_start, q_len, ctx_len,
              items, nh, nkv, page_size, num_pages, window, scale, status};
     return hd == 64 ? launch<64>(map, a, n_items, stream) : launch<128>(map, a, n_items, stream);
