@@ -140,6 +140,31 @@ __device__ __forceinline__ float ex2_fast(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// What halves the instructions of a row's softmax: the maximum of three numbers in one instruction, and the
+// scaling and the summation on pairs of 32-bit numbers (two results an instruction, each rounded as alone).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t pair_f32(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpair_f32(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_pair(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add_pair(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -190,8 +215,10 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(gen + L::BAR_OFF + L::NUM_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::BAR_OFF + L::NUM_BARS * 8 + 8);
 
+    tl_mark(VCB_TL_ATTN_TC, 0);
     pdl_trigger();
     pdl_wait();   // the queries and the newest keys come from the kernel before this one
+    tl_mark(VCB_TL_ATTN_TC, 1);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // Blocks are numbered item by item, the KV heads of an item side by side: the items come longest first, and
     // so do the blocks then (with the items of one KV head after those of another, the long items of the last
@@ -256,57 +283,59 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * BNK;   // S, S, O
 
     if (warp == 0) {
-        // ---- TMA producer: one box per page, for K and for V.  The boxes of a tile (up to 8) are issued by as
-        // many lanes at once: a single thread issuing them one after the other, each behind its own block-table
-        // read, was the slowest role of the block. ----
+        // ---- TMA producer: one box per page.  Lanes 0-7 copy the pages of a K tile, lanes 8-15 those of a V tile, in
+        // one go: the K tile two ahead of the V tile, so that one wait, one round of byte counts and one divergent
+        // copy instruction serve both (a call of its own per tile cost this warp 1,000 clocks, of which the copies
+        // themselves were a third, and made it the slowest role of the block). ----
         const int pages_per_tile = BNK / ps;
         const int groups_page = ps / 8;
         const int groups_kv = a.nkv * groups_page;   // groups of 8 rows from a page's K to its V
+        const bool copies_v = lane >= 8;
+        const int pl = lane & 7;
         int armed[2] = {0, 0};
-        // This lane's page id for the next K and the next V tile, read one call ahead: a block-table read that
-        // misses L1 costs about as long as a whole tile's products, and it stood between the stage's release
-        // and the load.  Tiles of one kind are loaded in order, so the next tile is known.
+        // This lane's page id for its next tile, read one call ahead: a block-table read that misses L1 costs about
+        // as long as a whole tile's products, and it stood between the stage's release and the load.  Tiles of one
+        // kind are loaded in order, so the next tile is known.
         auto page_of = [&](int it) {
-            const int pb = pb_lo + it * pages_per_tile + lane;
-            return (it < n_tiles && lane < pages_per_tile && pb < pb_hi) ? bt[pb] : -1;
+            const int pb = pb_lo + it * pages_per_tile + pl;
+            return (lane < 16 && it < n_tiles && pl < pages_per_tile && pb < pb_hi) ? bt[pb] : -1;
         };
-        int next_page[2] = {page_of(0), page_of(0)};
-        // loads the K (is_v 0) or V (1) tile `it` into its ring once the stage is free; false: give up
-        auto load_tile = [&](int it, int is_v) {
-            const int ns = is_v ? VS : KS, st = it % ns;
-            const uint32_t fullb = is_v ? v_full(st) : k_full(st);
+        int next_page = page_of(0);
+        // loads K tile itk and V tile itv (either may be -1: none) once their stages are free; false: give up
+        auto load_tiles = [&](int itk, int itv) {
             bool ok = true;
             if (lane == 0) {
                 // a K stage is free when its scores are there; a V stage when the product of the tile that used it
                 // (VS = 2 tiles ago, so on the same score buffer) has been added
-                if (!is_v) ok = mbar_wait(k_empty(st), ((it / ns) & 1) ^ 1u, abort_flag, a.status);
-                else if (it >= VS) ok = mbar_wait(pv_done(it & 1), (((it - VS) >> 1) & 1), abort_flag, a.status);
+                if (itk >= 0) ok = mbar_wait(k_empty(itk % KS), ((itk / KS) & 1) ^ 1u, abort_flag, a.status);
+                if (ok && itv >= VS) ok = mbar_wait(pv_done(itv & 1), (((itv - VS) >> 1) & 1), abort_flag, a.status);
             }
             if (!__shfl_sync(0xffffffffu, ok, 0)) return false;
-            const int pb0 = pb_lo + it * pages_per_tile;
-            const int np = min(pages_per_tile, pb_hi - pb0);
-            if (lane == 0) mbar_expect_tx(fullb, (uint32_t)(np * ps * ROWB));
+            const int it = copies_v ? itv : itk;
+            const bool mine = lane < 16 && it >= 0;
+            const int st = mine ? it % (copies_v ? VS : KS) : 0;
+            const uint32_t fullb = copies_v ? v_full(st) : k_full(st);
+            const int np = mine ? min(pages_per_tile, pb_hi - (pb_lo + it * pages_per_tile)) : 0;
+            if (mine && pl == 0) mbar_expect_tx(fullb, (uint32_t)(np * ps * ROWB));
             __syncwarp();
-            const uint32_t dst = base + (is_v ? L::V_OFF : L::K_OFF) + st * L::KV_BYTES;
-            if (lane < np) {   // at most 8 pages: one box a lane
-                int page = next_page[is_v];
+            if (pl < np) {   // at most 8 pages a tile: one box a lane
+                int page = next_page;
                 if (page < 0 || page >= a.num_pages) {
                     atomicOr(a.status, VCB_STATUS_BAD_PAGE);
                     page = 0;   // keep the byte count whole; the status word reports the fault
                 }
-                const int group = (page * 2 * a.nkv + kvh) * groups_page + (is_v ? groups_kv : 0);
-                tma_load_groups(dst + lane * ps * ROWB, &kv_map, fullb, group);
+                const int group = (page * 2 * a.nkv + kvh) * groups_page + (copies_v ? groups_kv : 0);
+                const uint32_t dst = base + (copies_v ? L::V_OFF : L::K_OFF) + st * L::KV_BYTES;
+                tma_load_groups(dst + pl * ps * ROWB, &kv_map, fullb, group);
             }
-            next_page[is_v] = page_of(it + 1);
-            armed[is_v] = it + 1;
+            if (mine) next_page = page_of(it + 1);
+            if (itk >= 0) armed[0] = itk + 1;
+            if (itv >= 0) armed[1] = itv + 1;
             return true;
         };
-        bool ok = load_tile(0, 0);
-        if (ok && n_tiles > 1) ok = load_tile(1, 0);
-        for (int it = 0; it < n_tiles && ok; ++it) {
-            if (it + 2 < n_tiles) ok = load_tile(it + 2, 0);   // keys two tiles ahead of the values
-            if (ok) ok = load_tile(it, 1);
-        }
+        bool ok = load_tiles(0, -1);
+        if (ok && n_tiles > 1) ok = load_tiles(1, -1);
+        for (int it = 0; it < n_tiles && ok; ++it) ok = load_tiles(it + 2 < n_tiles ? it + 2 : -1, it);   // keys two tiles ahead of the values
         if (lane == 0 && *abort_flag) {   // let copies in flight land before the block goes away
             for (int is_v = 0; is_v < 2; ++is_v) {
                 const int ns = is_v ? VS : KS;
@@ -405,7 +434,8 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
             float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
             if (plain_tile) {
 #pragma unroll
-                for (int c = 0; c < BNK; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c / 16][c % 16]));
+                for (int c = 0; c < BNK; c += 2)
+                    mx4[(c >> 1) & 3] = max3(mx4[(c >> 1) & 3], __uint_as_float(sv[c / 16][c % 16]), __uint_as_float(sv[c / 16][c % 16 + 1]));
             } else {
 #pragma unroll
                 for (int c = 0; c < BNK; ++c) {
@@ -413,8 +443,10 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                     const bool valid = row_ok && kidx >= lo_r && kidx <= pos_r;
                     const float sc = valid ? __uint_as_float(sv[c / 16][c % 16]) : -CUDART_INF_F;
                     sv[c / 16][c % 16] = __float_as_uint(sc);
-                    mx4[c & 3] = fmaxf(mx4[c & 3], sc);
                 }
+#pragma unroll
+                for (int c = 0; c < BNK; c += 2)
+                    mx4[(c >> 1) & 3] = max3(mx4[(c >> 1) & 3], __uint_as_float(sv[c / 16][c % 16]), __uint_as_float(sv[c / 16][c % 16 + 1]));
             }
             // the scale is positive: the maximum of the scaled scores is the scaled maximum
             const float m_new = fmaxf(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2, m_ref);
@@ -445,16 +477,22 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
             if (grow || first_keys) m_ref = m_new;
             const float m_sub = m_ref == -CUDART_INF_F ? 0.f : m_ref;   // no key yet: every weight is exp2(-inf) = 0
 
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint64_t sum4[4] = {0ull, 0ull, 0ull, 0ull};   // four pairs of partial sums, all +0
             uint32_t pk[BNK / 2];
+            const uint64_t scale2 = pair_f32(scale_log2, scale_log2), shift2 = pair_f32(-m_sub, -m_sub);
 #pragma unroll
             for (int c = 0; c < BNK; c += 2) {
-                const float p0 = ex2_fast(fmaf(__uint_as_float(sv[c / 16][c % 16]), scale_log2, -m_sub));
-                const float p1 = ex2_fast(fmaf(__uint_as_float(sv[(c + 1) / 16][(c + 1) % 16]), scale_log2, -m_sub));
-                sum4[(c >> 1) & 3] += p0 + p1;
+                float x0, x1;
+                unpair_f32(fma_pair(pair_f32(__uint_as_float(sv[c / 16][c % 16]), __uint_as_float(sv[c / 16][c % 16 + 1])), scale2, shift2), x0, x1);
+                const float p0 = ex2_fast(x0), p1 = ex2_fast(x1);
+                sum4[(c >> 1) & 3] = add_pair(sum4[(c >> 1) & 3], pair_f32(p0, p1));
                 pk[c / 2] = pack_bf16(p0, p1);
             }
-            l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            {
+                float lo4, hi4;
+                unpair_f32(add_pair(add_pair(sum4[0], sum4[1]), add_pair(sum4[2], sum4[3])), lo4, hi4);
+                l_run += lo4 + hi4;
+            }
 
             if (t0 + BNK > k_end) {
                 // The last page may hold slots beyond the sequence, and rows of pages that were not loaded are
@@ -506,6 +544,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
         tc_fence_before();
     }
     __syncthreads();
+    tl_mark(VCB_TL_ATTN_TC, 2);
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS) : "memory");
@@ -535,6 +574,8 @@ int launch(const CUtensorMap& map, const TcArgs& a, int n_items, cudaStream_t st
 }
 
 }  // namespace
+
+VCB_TIMELINE_UNIT(attn_tc)
 
 // What the tcgen05 kernel takes; the caller uses vcb_attn_mma (or vcb_attn_paged) for everything else.
 VCB_API int vcb_attn_tc_supported(int dtype, int hd, int page_size) {

@@ -491,7 +491,7 @@ def timeline_begin(capacity: int = 1 << 18) -> None:
     _timeline = torch.zeros(2 + 4 * capacity, dtype=torch.int64, device="cuda")
     _timeline[1] = capacity
     torch.cuda.synchronize()
-    for unit in ("gemm", "attn_mma", "elementwise"):
+    for unit in ("gemm", "attn_mma", "attn_tc", "elementwise"):
         fn = getattr(L, f"vcb_timeline_set_{unit}")
         fn.argtypes, fn.restype = [c_void_p], c_int
         if fn(_timeline.data_ptr()) != 0:
@@ -503,7 +503,7 @@ def timeline_end():
     global _timeline
     L = lib()
     torch.cuda.synchronize()
-    for unit in ("gemm", "attn_mma", "elementwise"):
+    for unit in ("gemm", "attn_mma", "attn_tc", "elementwise"):
         getattr(L, f"vcb_timeline_set_{unit}")(None)
     buf = _timeline.cpu().numpy()
     _timeline = None
