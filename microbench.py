@@ -148,7 +148,7 @@ def bench_attention(dev, status):
         flops = 4.0 * NH * HD * T * (T + 1) / 2
         mma = timeit(lambda k: ops.attn_mma(q, out, pages, bt, qs, ql, cl, plan.span_items, plan.n_span_items, A.MMA_SPAN_ROWS,
                                             None, None, NH, NKV, HD, 0, status))
-        tcg = timeit(lambda k: ops.attn_tc(q, out, pages, bt, qs, ql, cl, plan.span_items, plan.n_span_items, NH, NKV, HD, 0, status))
+        tcg = timeit(lambda k: ops.attn_tc(q, out, pages, bt, qs, ql, cl, plan.span_items, plan.n_span_items, NH, NKV, HD, 0, status, work=plan.span_work))
         print(f"prompt attention  {T} tokens: mma.sync {mma:7.1f} us ({flops / mma / 1e6:5.0f} TFLOP/s)   tcgen05 {tcg:7.1f} us "
               f"({flops / tcg / 1e6:5.0f} TFLOP/s)   at bf16 peak {flops / tc / 1e6:6.1f}", flush=True)
 

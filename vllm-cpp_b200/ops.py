@@ -75,7 +75,7 @@ def _declare(L):
         "vcb_attn_mma_fused_supported": [I, I, I],
         "vcb_attn_mma_decode_fused": [P, I, LL, P, P, I, I, F, P, I, P, P, P, LL, P, P, I, P, P, P, P, I, P, P, P, P, I, I,
                                       I, I, I, I, F, P, P],
-        "vcb_attn_tc": [P, P, P, LL, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, P, P],
+        "vcb_attn_tc": [P, P, P, LL, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, P, P, P],
         "vcb_attn_tc_supported": [I, I, I],
         "vcb_attn_merge": [P, P, P, P, I, I, I, I, I, P],
         "vcb_sample": [P, LL, I, I, P, P, P, P],
@@ -108,7 +108,12 @@ def _call(name: str, *args):
     global launch_count
     L = lib()
     launch_count += 1
-    rc = getattr(L, name)(*args)
+    fn = getattr(L, name)
+    # ctypes takes arguments beyond the declared ones without a word and passes them as 32-bit integers: a pointer or
+    # a stream handle would lose its upper half
+    if fn.argtypes is None or len(fn.argtypes) != len(args):
+        raise KernelError(f"{name}: {len(args)} arguments for a declaration of {0 if fn.argtypes is None else len(fn.argtypes)}")
+    rc = fn(*args)
     if rc != 0:
         raise KernelError(L.vcb_last_error().decode() or f"{name} failed with code {rc}")
 
@@ -445,9 +450,14 @@ def attn_tc_supported(dtype: torch.dtype, hd: int, page_size: int) -> bool:
 
 
 def attn_tc(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, nh, nkv, hd, window, status,
-            table_row=None):
+            table_row=None, work=None):
     """Attention of prompt portions on tcgen05 tensor cores (bfloat16, head_dim 64 or 128, pages of 8 to 64
-    tokens).  Items as for :func:`attn_paged` with one key slice and at most 128 rows each."""
+    tokens).  Items as for :func:`attn_paged` with one key slice and at most 128 rows each.  ``work``: two int32
+    zeros, zero again when the kernel is through (the queue its blocks take their units from); launches that share
+    them must follow one another on a stream.  Made on the spot when not given."""
+    if work is None:
+        work = torch.zeros(2, dtype=torch.int32, device=q.device)
+    _need(work, "work", torch.int32)
     _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(pages, "pages", torch.bfloat16)
     for name, t in (("block_table", block_table), ("q_start", q_start), ("q_len", q_len), ("ctx_len", ctx_len),
                     ("items", items)):
@@ -456,7 +466,7 @@ def attn_tc(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items,
     assert two == 2 and nkv_p == nkv and hd_p == hd
     _call("vcb_attn_tc", _p(q), _p(out), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
           block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, nh, nkv, hd, page_size,
-          num_pages, int(window or 0), 1.0 / math.sqrt(hd), _p(status), _stream())
+          num_pages, int(window or 0), 1.0 / math.sqrt(hd), _p(status), _p(work), _stream())
 
 
 def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, rows_max, part_o, part_ml,

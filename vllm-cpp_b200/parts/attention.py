@@ -96,6 +96,8 @@ class AttentionPlan:
             rows.sort(key=lambda r: -(ctx.host_ctx_len[r[0]] - ctx.host_q_len[r[0]] + r[1] + r[2]))
             self.n_span_items = len(rows)
             self.span_items = upload(np.asarray(rows, dtype=np.int32).reshape(-1, ops.ITEM_INTS))
+            # the queue that the tensor-core kernel's blocks take their work from (left at zero by every launch)
+            self.span_work = workspace.zeros((2,), torch.int32, dev)
 
 
 class GQAAttention(Mixer):
@@ -202,7 +204,7 @@ class GQAAttention(Mixer):
                     ops.attn_merge(part_o, part_ml, plan.dec_rows, out, plan.n_dec, nh, hd, S)
         if plan.n_span_items and mma and TCGEN05_SPANS and ops.attn_tc_supported(x.dtype, hd, cache.pages.shape[3]):
             ops.attn_tc(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
-                        plan.span_items, plan.n_span_items, **common)
+                        plan.span_items, plan.n_span_items, work=plan.span_work, **common)
         elif plan.n_span_items:
             kernel(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
                    plan.span_items, plan.n_span_items, span_rows, None, None, **common)
