@@ -496,6 +496,66 @@ def test_attention_tcgen05_many_blocks_many_launches():
         assert torch.equal(o, outs[0])      # and the same bits every time
 
 
+@pytest.mark.parametrize("hd,ps,nh,nkv", [(128, 16, 32, 8), (64, 8, 24, 8)])
+def test_attention_tcgen05_units_from_the_queue(hd, ps, nh, nkv):
+    """The tcgen05 kernel's blocks take their work units from a queue.  Here there are more units than blocks that
+    run at once (so most come through the queue), the items are laid out for longer portions than are there (units
+    with nothing to do, at the front and in the middle of the queue), and launch follows launch on the same two
+    counters, eagerly and in a captured graph: every output equals 64-bit attention, and the counters are back at
+    zero."""
+    from vllm_cpp_b200 import ops
+    from vllm_cpp_b200.parts import attention as A
+    torch.manual_seed(hd + ps)
+    planned = [(0, 1400), (300, 40), (16, 900), (1000, 700)]        # (keys before the portion, tokens the items are for)
+    actual = [(0, 1400), (300, 11), (16, 0), (1000, 333)]           # what is there: whole, cut, nothing, cut
+    seqs, qs = [], []
+    for start, n in actual:
+        k = torch.randn(start + n, nkv, hd, dtype=torch.float64).to(torch.bfloat16).double()
+        v = torch.randn(start + n, nkv, hd, dtype=torch.float64).to(torch.bfloat16).double()
+        seqs.append((k, v))
+        qs.append(torch.randn(n, nh, hd, dtype=torch.float64).to(torch.bfloat16).double())
+    num_pages = sum(-(-(s + n) // ps) for s, n in planned) + 3
+    pages, tables = build_paged(seqs, nkv, hd, ps, torch.bfloat16, num_pages)
+
+    class Ctx:
+        pass
+    c = Ctx()
+    c.device = dev()
+    c.host_q_len = [n for _, n in planned]
+    c.host_ctx_len = [s + n for s, n in planned]
+    q_start = [int(x) for x in np.cumsum([0] + [n for _, n in actual[:-1]])]
+    c.host_q_start = q_start
+    plan = A.AttentionPlan(c, nh, nkv, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+    assert plan.n_span_items * nkv > 2 * ops.num_sms()
+    mb = max(-(-(s + n) // ps) for s, n in planned)
+    bt = torch.full((len(planned), mb), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        bt[i, :len(t)] = torch.tensor(t)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())
+    T = sum(n for _, n in actual)
+    q = torch.cat(qs).to(torch.bfloat16).to(dev()).view(T, nh * hd)
+    args = (pages, bt.to(dev()), i32(q_start), i32([n for _, n in actual]), i32([s + n for s, n in actual]))
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    work = torch.zeros(2, dtype=torch.int32, device=dev())
+    outs = [torch.full_like(q, float("nan")) for _ in range(6)]
+    launch = lambda o: ops.attn_tc(q, o, *args, plan.span_items, plan.n_span_items, nh, nkv, hd, 0, status, work=work)
+    for o in outs[:3]:
+        launch(o)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for o in outs[3:]:
+            launch(o)
+    graph.replay()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert status.item() == 0 and work.tolist() == [0, 0]
+    want = torch.cat([attention_reference(qq, k, v, start, 0) for (start, n), qq, (k, v) in zip(actual, qs, seqs) if n])
+    for o in outs:
+        torch.testing.assert_close(o.double().cpu().view(T, nh, hd), want, **tol(torch.bfloat16))
+        assert torch.equal(o, outs[0])
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_long_decode_is_sliced(dtype):
     plan = run_attention(dtype, 8, 2, 64, 16, 0, [(3000, 1), (1025, 1)])
