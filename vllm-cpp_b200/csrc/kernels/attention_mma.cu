@@ -110,10 +110,19 @@ template <int ROWS> __device__ __forceinline__ int swz(int r, int c) {
     return (c >> 3) * (ROWS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
 }
 
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+// The same for a K or V tile: [groups of 8 keys][head_dim/64 halves][8 rows][128 bytes], every 1 KB piece of 8 rows
+// swizzled like the above.  It is what ONE TMA box per page produces, whatever head_dim, from the cache seen as
+// [groups of 8 tokens][halves][8 tokens][64 lanes] (kv_tensor_map, grouped): a copy per page and half of head_dim
+// cost the loading warp about 100 clocks each, 1,600 a tile -- more than the tile's share of the HBM time.
+template <int HALVES> __device__ __forceinline__ int swz_kv(int key, int c) {
+    return (key >> 3) * (HALVES * 1024) + (c >> 3) * 1024 + (key & 7) * 128 + (((c & 7) ^ (key & 7)) << 4);
+}
+
+// a box of whole groups of 8 tokens, all lanes: coordinates (lane 0, token 0, half 0, group)
+__device__ __forceinline__ void tma_load_groups(uint32_t dst, const CUtensorMap* map, uint32_t bar, int group) {
     asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %3, %3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(group) : "memory");
 }
 
 // WR row groups x WK key groups multiplying warps, MR tiles of 16 rows each; TMA adds one warp that only issues
@@ -202,14 +211,13 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
 
-    // ---- TMA producer state: one box of [page_size keys x 64 lanes] per page, per half of head_dim, for K and V.
-    // The boxes of a tile (up to 32) are issued by as many lanes at once, each with its page id read one tile
-    // ahead: one thread issuing them in turn, each behind its own block-table read, took about as long as
-    // the tile's share of HBM time. ----
+    // ---- TMA producer state: one box per page for K and one for V.  The boxes of a tile (up to 16) are issued by
+    // as many lanes at once, each with its page id read ahead: one thread issuing them in turn, each behind its own
+    // block-table read, took about as long as the tile's share of HBM time. ----
     const int pages_per_tile = BN / ps;
-    const int rows_kv = a.nkv * ps;          // rows of the flattened [pages * 2 * nkv * ps, HD] view per K or V
-    constexpr int HALVES = HD / 64;
-    const int my_pg = lane / (HALVES * 2), my_h = (lane >> 1) % HALVES, my_v = lane & 1;
+    const int groups_page = ps / 8;
+    const int groups_kv = a.nkv * groups_page;   // groups of 8 rows from a page's K to its V
+    const int my_pg = lane >> 1, my_v = lane & 1;
     auto page_of = [&](int it) {
         const int pb = my_pb_lo + it * pages_per_tile + my_pg;
         return (it < n_tiles && my_pg < pages_per_tile && pb < my_pb_hi) ? bt[pb] : -1;
@@ -240,9 +248,9 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
                 atomicOr(a.status, VCB_STATUS_BAD_PAGE);
                 page = 0;   // keep the byte count whole; the status word reports the fault
             }
-            const int row = (page * 2 * a.nkv + kvh) * ps + (my_v ? rows_kv : 0);
-            const uint32_t dst = smem_u32((my_v ? v_s : k_s) + st * TILE_BYTES) + my_h * (BN * 128) + my_pg * ps * 128;
-            tma_load_2d(dst, &kv_map, full_bar(st), my_h * 64, row);
+            const int group = (page * 2 * a.nkv + kvh) * groups_page + (my_v ? groups_kv : 0);
+            const uint32_t dst = smem_u32((my_v ? v_s : k_s) + st * TILE_BYTES) + my_pg * ps * ROWB;
+            tma_load_groups(dst, &kv_map, full_bar(st), group);
         }
 #pragma unroll
         for (int k = 0; k + 1 < AHEAD; ++k) ahead_page[k] = ahead_page[k + 1];
@@ -432,7 +440,7 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
                     bytes = 16;
                 }
             }
-            const int off = swz<BN>(j, c);
+            const int off = swz_kv<HD / 64>(j, c);
             cp_async16(smem_u32(kd + off), src, bytes);
             cp_async16(smem_u32(vd + off), bytes ? src + (size_t)a.nkv * ps * HD : src, bytes);
         }
@@ -495,7 +503,7 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
                     // their V must be finite, because a zero weight times NaN is NaN.  Each warp clears what it reads.
                     for (int idx = lane; idx < KW * CH; idx += 32) {
                         const int j = wk * KW + idx / CH, c = idx % CH;
-                        if (t0 + j >= k_end) *reinterpret_cast<uint4*>(v_s + st * TILE_BYTES + swz<BN>(j, c)) = make_uint4(0, 0, 0, 0);
+                        if (t0 + j >= k_end) *reinterpret_cast<uint4*>(v_s + st * TILE_BYTES + swz_kv<HD / 64>(j, c)) = make_uint4(0, 0, 0, 0);
                     }
                     __syncwarp();
                 }
@@ -536,7 +544,7 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
                     uint32_t b[4];
                     const int mi = lane >> 3;
                     const int krow = wk * KW + np * 16 + (mi >> 1) * 8 + (lane & 7);
-                    ldmatrix_x4(b, smem_u32(kt + swz<BN>(krow, ks * 2 + (mi & 1))));
+                    ldmatrix_x4(b, smem_u32(kt + swz_kv<HD / 64>(krow, ks * 2 + (mi & 1))));
 #pragma unroll
                     for (int mr = 0; mr < MR; ++mr) {
                         mma_16816(s[mr][2 * np], qk[mr], b[0], b[1]);
@@ -625,7 +633,7 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
                     uint32_t b[4];
                     const int mi = lane >> 3;
                     const int vrow = wk * KW + kk * 16 + (mi & 1) * 8 + (lane & 7);
-                    ldmatrix_x4_trans(b, smem_u32(vt + swz<BN>(vrow, dp * 2 + (mi >> 1))));
+                    ldmatrix_x4_trans(b, smem_u32(vt + swz_kv<HD / 64>(vrow, dp * 2 + (mi >> 1))));
 #pragma unroll
                     for (int mr = 0; mr < MR; ++mr) {
                         mma_16816(o[mr][2 * dp], pa[mr][kk], b[0], b[1]);
@@ -891,7 +899,7 @@ int launch(const AttnArgs& a, int n_items, cudaStream_t stream) {
             vcb_set_error("attn_mma: the pages of a layer must be contiguous for TMA loads");
             return -1;
         }
-        if (!kv_tensor_map(a.pages, rows, HD, a.page_size, &map)) return -3;
+        if (!kv_tensor_map(a.pages, rows, HD, a.page_size, &map, true)) return -3;
     }
     auto kern = attn_mma_kernel<HD, WR, WK, MR, TMA, DEEP>;
     static bool opted = false;
