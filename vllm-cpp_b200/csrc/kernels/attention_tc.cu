@@ -500,7 +500,8 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                         ok = issue_qk(j + 1);   // runs while the rows work on tile j
                         if (!ok) break;
                     }
-                    ok = mbar_wait(p_ready(b), (gj >> 1) & 1, abort_flag, a.status) && mbar_wait(v_full(st), (gj / VS) & 1, abort_flag, a.status);
+                    // the values first: they have long landed when the rows hand over their weights
+                    ok = mbar_wait(v_full(st), (gj / VS) & 1, abort_flag, a.status) && mbar_wait(p_ready(b), (gj >> 1) & 1, abort_flag, a.status);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t va = base + L::V_OFF + st * L::KV_BYTES;
