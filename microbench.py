@@ -124,16 +124,16 @@ def bench_attention(dev, status):
         out = torch.empty_like(q)
         c = _Ctx()
         c.device, c.host_q_len, c.host_ctx_len, c.host_q_start = dev, [1] * B, [ctx_len] * B, list(range(B))
-        plan = A.AttentionPlan(c, NH, NKV, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+        plan = A.AttentionPlan(c, NH, NKV, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS, HD if A.CLUSTER_MERGE else None)
         S = plan.nslices
         po = torch.empty(B * NH * S, HD, device=dev) if S > 1 else None
         pm = torch.empty(B * NH * S, 2, device=dev) if S > 1 else None
         qs, ql, cl = i32(c.host_q_start), i32(c.host_q_len), i32(c.host_ctx_len)
         us = timeit(lambda k: ops.attn_mma(q, out, pages, bt, qs, ql, cl, plan.dec_items, B * S, A.MMA_DECODE_ROWS, po, pm,
                                            NH, NKV, HD, 0, status, slice_counters=plan.slice_counters if S > 1 else None,
-                                           dec_rows=plan.dec_rows))
+                                           dec_rows=plan.dec_rows, cluster=plan.cluster))
         kv_bytes = B * ctx_len * 2 * NKV * HD * 2
-        print(f"decode attention  batch {B:3d} context {ctx_len:5d} key slices {S:2d}: {us:7.1f} us   at HBM peak {kv_bytes / hbm / 1e3:6.1f}", flush=True)
+        print(f"decode attention  batch {B:3d} context {ctx_len:5d} key slices {S:2d}{' in clusters' if plan.cluster else ''}: {us:7.1f} us   at HBM peak {kv_bytes / hbm / 1e3:6.1f}", flush=True)
         del pages
     for T in (2048, 8192):
         npages = T // PAGE

@@ -77,6 +77,7 @@ struct AttnArgs {
     float scale;
     int* status;
     FusedQkv f;
+    int cluster;   // > 1: the blocks of a token's key slices form a cluster of that many and merge through shared memory
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
@@ -123,6 +124,24 @@ __device__ __forceinline__ void tma_load_groups(uint32_t dst, const CUtensorMap*
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %3, %3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(group) : "memory");
+}
+
+// Blocks of a cluster: rank, the common barrier (arrive with release, wait with acquire), and reads of another
+// block's shared memory.
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float2 ld_cluster_f2(const void* local, uint32_t rank) {
+    uint32_t remote;
+    float2 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(remote) : "memory");
+    return v;
 }
 
 // WR row groups x WK key groups multiplying warps, MR tiles of 16 rows each; TMA adds one warp that only issues
@@ -656,6 +675,9 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
     // ---- partial states -> shared memory: o_s[wk][row][HD], ml_s[wk][row][2] ----
     float* o_s = reinterpret_cast<float*>(k_s);             // WK * RMAX x HD floats, over the K and V stages
     float* ml_s = o_s + WK * RMAX * HD;                     // WK * RMAX x 2 floats
+    float* cl_o = ml_s + WK * RMAX * 2;                     // RMAX x HD floats: the block's own result, for its cluster
+    float* cl_ml = cl_o + RMAX * HD;                        // RMAX x 2 floats
+    const bool in_cluster = a.cluster > 1 && nslices > 1;   // the same for all blocks of a cluster
     if (warp < NW) {
 #pragma unroll
         for (int mr = 0; mr < MR; ++mr) {
@@ -700,6 +722,9 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
             const float inv = l > 0.f ? 1.f / l : 0.f;
             *reinterpret_cast<__nv_bfloat162*>(a.out + ((size_t)(row0 + iq) * a.nh + head0 + ih) * HD + d) =
                 __floats2bfloat162_rn(o0 * inv, o1 * inv);
+        } else if (in_cluster) {
+            *reinterpret_cast<float2*>(cl_o + (size_t)r * HD + d) = make_float2(o0, o1);
+            if (d == 0) *reinterpret_cast<float2*>(cl_ml + r * 2) = make_float2(m, l);
         } else {
             const size_t prow = ((size_t)dec_index * a.nh + head0 + r) * nslices + slice;
             *reinterpret_cast<float2*>(a.part_o + prow * HD + d) = make_float2(o0, o1);
@@ -710,8 +735,47 @@ __global__ __launch_bounds__(WR * WK * 32 + (TMA ? 32 : 0)) void attn_mma_kernel
         }
     }
 
-    // ---- the block that finishes the last slice of a (token, head group) merges the slices ----
-    if (nslices > 1 && a.slice_counters != nullptr) {
+    // ---- the blocks of a token's key slices, a cluster: each merges its share of the lanes from all the blocks' results
+    // in shared memory (two barriers of the cluster and one round of reads between SMs, where the way through global
+    // memory below is a fence, a counter and a round trip of the last block, three to six microseconds a launch) ----
+    if (in_cluster) {
+        cluster_barrier();          // every block's result is in its shared memory (the barrier orders the block's threads too)
+        const int out_row = a.dec_rows[dec_index];
+        const uint32_t me = cluster_rank();
+        if (out_row >= 0) {
+            for (int idx = (int)me * (int)blockDim.x + tid; idx < gq * (HD / 2); idx += nslices * (int)blockDim.x) {
+                const int ih = idx / (HD / 2), d = (idx % (HD / 2)) * 2;
+                constexpr int MC = 8;     // a cluster has at most eight blocks
+                float2 mlv[MC], ov[MC];
+#pragma unroll
+                for (int j = 0; j < MC; ++j) {
+                    if (j < nslices) {
+                        mlv[j] = ld_cluster_f2(cl_ml + ih * 2, (uint32_t)j);
+                        ov[j] = ld_cluster_f2(cl_o + (size_t)ih * HD + d, (uint32_t)j);
+                    }
+                }
+                float m = -CUDART_INF_F, l = 0.f, o0 = 0.f, o1 = 0.f;
+#pragma unroll
+                for (int j = 0; j < MC; ++j)
+                    if (j < nslices) m = fmaxf(m, mlv[j].x);
+#pragma unroll
+                for (int j = 0; j < MC; ++j) {     // slice order (a block's rank in its cluster is its slice)
+                    if (j < nslices && mlv[j].x != -CUDART_INF_F) {
+                        const float w = expf(mlv[j].x - m);
+                        l += mlv[j].y * w;
+                        o0 += ov[j].x * w;
+                        o1 += ov[j].y * w;
+                    }
+                }
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                *reinterpret_cast<__nv_bfloat162*>(a.out + ((size_t)out_row * a.nh + head0 + ih) * HD + d) =
+                    __floats2bfloat162_rn(o0 * inv, o1 * inv);
+            }
+        }
+        cluster_barrier();          // nobody leaves while its result may still be read
+    }
+    // ---- else the block that finishes the last slice of a (token, head group) merges the slices ----
+    if (!in_cluster && nslices > 1 && a.slice_counters != nullptr) {
         __shared__ int is_last;
         __threadfence();            // this block's partials are visible before its arrival is counted
         __syncthreads();
@@ -889,7 +953,7 @@ int launch(const AttnArgs& a, int n_items, cudaStream_t stream) {
     const int gq_max = g < RMAX ? g : RMAX;
     const int hchunks = (g + gq_max - 1) / gq_max;
     const size_t stages = 2 * (size_t)STAGES * BN * HD * 2 + (size_t)RMAX * HD * 2 + 16 * STAGES + 16;
-    const size_t merge = ((size_t)WK * RMAX * HD + (size_t)WK * RMAX * 2) * sizeof(float);
+    const size_t merge = ((size_t)WK * RMAX * HD + (size_t)WK * RMAX * 2 + (size_t)RMAX * HD + (size_t)RMAX * 2) * sizeof(float);
     const size_t smem = (stages > merge ? stages : merge) + 1024;   // + alignment slack
     CUtensorMap map;
     memset(&map, 0, sizeof(map));
@@ -911,7 +975,15 @@ int launch(const AttnArgs& a, int n_items, cudaStream_t stream) {
         }
         opted = true;
     }
-    launch_pdl(kern, dim3(n_items, a.nkv * hchunks), dim3(WR * WK * 32 + (TMA ? 32 : 0)), smem, stream, map, a);
+    if (a.cluster > 1) {
+        if (a.cluster > 8 || n_items % a.cluster != 0 || a.slice_counters == nullptr || a.dec_rows == nullptr) {
+            vcb_set_error("attn_mma: clusters of %d blocks for %d items (at most 8, a divisor of the items, with the merge's arrays)", a.cluster, n_items);
+            return -1;
+        }
+        launch_pdl_clusters(kern, dim3(n_items, a.nkv * hchunks), dim3(WR * WK * 32 + (TMA ? 32 : 0)), smem, stream, (unsigned)a.cluster, map, a);
+    } else {
+        launch_pdl(kern, dim3(n_items, a.nkv * hchunks), dim3(WR * WK * 32 + (TMA ? 32 : 0)), smem, stream, map, a);
+    }
     VCB_CHECK_LAUNCH("attn_mma");
     return 0;
 }
@@ -929,6 +1001,8 @@ bool vcb_kv_tensor_map(const void* pages, long long rows, int hd, int page_size,
     return kv_tensor_map(pages, rows, hd, page_size, out, grouped);
 }
 
+// cluster: 0, or the number of key slices per decoded token (2 to 8) when their blocks are to run as a cluster and
+// merge through shared memory (with slice_counters and dec_rows given, as for the merge by the last block).
 // rows_max: 16 (single decoded tokens; four warps split each tile's keys) or 128 (prompt portions; eight warps of
 // 16 rows each share the K and V tiles, enough independent MMA chains per SM to keep the tensor pipe fed).
 // Only bfloat16 and head_dim 64 or 128; the caller falls back to vcb_attn_paged otherwise.
@@ -939,7 +1013,7 @@ VCB_API int vcb_attn_mma(const void* q, void* out, const void* pages, long long 
                          const int* ctx_len, const int* items, int n_items, int rows_max, float* part_o,
                          float* part_ml, int* slice_counters, const int* dec_rows, int nh, int nkv, int hd,
                          int page_size, int num_pages, int window, float scale, int* status, int allow_tma,
-                         cudaStream_t stream) {
+                         int cluster, cudaStream_t stream) {
     if (n_items == 0) return 0;
     VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_mma: %d query heads are not a multiple of %d KV heads", nh, nkv);
     VCB_CHECK_ARG(hd == 64 || hd == 128, "attn_mma: head_dim %d is not 64 or 128", hd);
@@ -947,11 +1021,45 @@ VCB_API int vcb_attn_mma(const void* q, void* out, const void* pages, long long 
     VCB_CHECK_ARG(page_size > 0 && window >= 0, "attn_mma: bad page_size %d or window %d", page_size, window);
     AttnArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_stride, block_table,
                table_row, max_blocks, q_start, q_len, ctx_len, items, part_o, part_ml, slice_counters, dec_rows, nh, nkv,
-               page_size, num_pages, window, scale, status, FusedQkv{}};
+               page_size, num_pages, window, scale, status, FusedQkv{}, cluster};
     const bool tma = allow_tma && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64) &&
                      ((uintptr_t)pages % 16 == 0) && page_stride == (long long)2 * nkv * page_size * hd;
     if (hd == 64) return tma ? launch_rows<64, true>(a, n_items, rows_max, stream) : launch_rows<64, false>(a, n_items, rows_max, stream);
     return tma ? launch_rows<128, true>(a, n_items, rows_max, stream) : launch_rows<128, false>(a, n_items, rows_max, stream);
+}
+
+// How many clusters of `cluster` blocks of the decode kernel (TMA loads, head_dim hd; the ring of six stages if `deep`)
+// the device runs at once: what a caller needs to choose a number of key slices whose clusters all fit.  -1: unknown.
+template <int HD, bool DEEP> int max_clusters_of(int cluster) {
+    constexpr int WR = 1, WK = 4, MR = 1, RMAX = 16;
+    constexpr int STAGES = DEEP ? 6 : 3;
+    const size_t stages = 2 * (size_t)STAGES * BN * HD * 2 + (size_t)RMAX * HD * 2 + 16 * STAGES + 16;
+    const size_t merge = ((size_t)WK * RMAX * HD + (size_t)WK * RMAX * 2 + (size_t)RMAX * HD + (size_t)RMAX * 2) * sizeof(float);
+    const size_t smem = (stages > merge ? stages : merge) + 1024;
+    auto kern = attn_mma_kernel<HD, WR, WK, MR, true, DEEP>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)cluster * 64, 1);
+    cfg.blockDim = dim3(WR * WK * 32 + 32);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return n;
+}
+VCB_API int vcb_attn_mma_max_clusters(int hd, int cluster, int deep) {
+    if (cluster < 1 || cluster > 8 || (hd != 64 && hd != 128)) return -1;
+    if (hd == 64) return deep ? max_clusters_of<64, true>(cluster) : max_clusters_of<64, false>(cluster);
+    return deep ? max_clusters_of<128, true>(cluster) : max_clusters_of<128, false>(cluster);
 }
 
 // Whether vcb_attn_mma_decode_fused takes these sizes: the page sizes whose pages the TMA loader brings in whole.
@@ -968,7 +1076,7 @@ VCB_API int vcb_attn_mma_decode_fused(const float* qkv, int slices, long long sl
                                       const int* q_start, const int* q_len, const int* ctx_len, const int* items, int n_items,
                                       float* part_o, float* part_ml, int* slice_counters, const int* dec_rows, int nh, int nkv,
                                       int hd, int page_size, int num_pages, int window, float scale, int* status,
-                                      cudaStream_t stream) {
+                                      int cluster, cudaStream_t stream) {
     if (n_items == 0) return 0;
     VCB_CHECK_ARG(nh > 0 && nkv > 0 && nh % nkv == 0, "attn_mma_decode_fused: %d query heads are not a multiple of %d KV heads", nh, nkv);
     VCB_CHECK_ARG(vcb_attn_mma_fused_supported(VCB_BF16, hd, page_size), "attn_mma_decode_fused: head_dim %d with pages of %d tokens is not supported", hd, page_size);
@@ -982,6 +1090,7 @@ VCB_API int vcb_attn_mma_decode_fused(const float* qkv, int slices, long long sl
                q_start, q_len, ctx_len, items, part_o, part_ml, slice_counters, dec_rows, nh, nkv, page_size, num_pages, window,
                scale, status,
                FusedQkv{qkv, slices, slice_stride, q_gain, k_gain, gain_dtype, use_norm, eps, cos_sin, max_pos,
-                        slot_map, (__nv_bfloat16*)pages}};
+                        slot_map, (__nv_bfloat16*)pages},
+               cluster};
     return hd == 64 ? launch<64, 1, 4, 1, true>(a, n_items, stream) : launch<128, 1, 4, 1, true>(a, n_items, stream);
 }

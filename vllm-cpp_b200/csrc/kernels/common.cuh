@@ -70,6 +70,28 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// The same with the grid's blocks in clusters of `cluster_x` along x (blocks of a cluster run at the same time on
+// SMs of one GPC and can read one another's shared memory).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl_clusters(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                       unsigned cluster_x, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster_x;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = vcb_pdl_enabled() ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // A look at a step from inside (built only with -DVCB_TIMELINE; otherwise tl_mark is nothing).  Thread 0 of every
 // block appends (time, kernel, phase, block, SM) records to a buffer that the host hands to each translation unit:
 // word 0 counts the records, word 1 is the capacity, then four words a record.  Phases: 0 the block starts,

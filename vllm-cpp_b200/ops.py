@@ -7,6 +7,7 @@ if the kernel library cannot be built or loaded, importing a kernel raises.
 from __future__ import annotations
 
 import ctypes
+import functools
 import math
 import struct
 from ctypes import c_float, c_int, c_longlong, c_void_p
@@ -70,11 +71,12 @@ def _declare(L):
         "vcb_scatter_i32": [P, P, P, P, I, LL, P],
         "vcb_selftest_wait_timeout": [LL, P, P, P],
         "vcb_state_reset": [P, I, LL, LL, LL, I, I, P, P, P, I, ctypes.c_uint, P, P],
-        "vcb_attn_mma": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, F, P, I, P],
+        "vcb_attn_mma": [P, P, P, LL, P, P, I, P, P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, F, P, I, I, P],
         "vcb_attn_mma_supported": [I, I],
+        "vcb_attn_mma_max_clusters": [I, I, I],
         "vcb_attn_mma_fused_supported": [I, I, I],
         "vcb_attn_mma_decode_fused": [P, I, LL, P, P, I, I, F, P, I, P, P, P, LL, P, P, I, P, P, P, P, I, P, P, P, P, I, I,
-                                      I, I, I, I, F, P, P],
+                                      I, I, I, I, F, P, I, P],
         "vcb_attn_tc": [P, P, P, LL, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, P, P, P],
         "vcb_attn_tc_supported": [I, I, I],
         "vcb_attn_merge": [P, P, P, P, I, I, I, I, I, P],
@@ -420,7 +422,7 @@ def attn_mma_fused_supported(dtype: torch.dtype, hd: int, page_size: int) -> boo
 
 def attn_mma_decode_fused(qkv, q_weight, k_weight, eps, cos_sin, slot_map, out, pages, block_table, q_start,
                           q_len, ctx_len, items, n_items, part_o, part_ml, slice_counters, dec_rows, nh, nkv, hd, window,
-                          status, table_row=None, use_norm=True):
+                          status, table_row=None, use_norm=True, cluster=0):
     """Attention of single decoded tokens straight from the stacked projection ``qkv`` [S, T, (nh + 2 nkv) hd]
     (32-bit k-slice partial sums): each block norms and rotates its own query heads, and the blocks that read the
     token's own position store its key and value in the cache first -- what qknorm_rope_kvwrite and attn_mma do
@@ -441,7 +443,14 @@ def attn_mma_decode_fused(qkv, q_weight, k_weight, eps, cos_sin, slot_map, out, 
           float(eps), _p(cos_sin), cos_sin.shape[0], _p(slot_map), _p(out), _p(pages), pages.stride(0),
           _p(block_table), _p(table_row), block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items,
           _p(part_o), _p(part_ml), _p(slice_counters), _p(dec_rows), nh, nkv, hd, page_size, num_pages, int(window or 0),
-          1.0 / math.sqrt(hd), _p(status), _stream())
+          1.0 / math.sqrt(hd), _p(status), int(cluster), _stream())
+
+
+@functools.lru_cache(maxsize=None)
+def attn_mma_max_clusters(hd: int, cluster: int, deep: bool) -> int:
+    """How many clusters of ``cluster`` blocks of the decode attention kernel run at once on this device (``deep``: the
+    variant with the ring of six stages, which has an SM to itself).  -1 when the driver does not say."""
+    return int(lib().vcb_attn_mma_max_clusters(hd, cluster, int(deep)))
 
 
 def attn_tc_supported(dtype: torch.dtype, hd: int, page_size: int) -> bool:
@@ -470,10 +479,12 @@ def attn_tc(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items,
 
 
 def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items, rows_max, part_o, part_ml,
-             nh, nkv, hd, window, status, table_row=None, allow_tma=True, slice_counters=None, dec_rows=None):
+             nh, nkv, hd, window, status, table_row=None, allow_tma=True, slice_counters=None, dec_rows=None,
+             cluster=0):
     """Tensor-core variant of :func:`attn_paged` (bfloat16, head_dim 64 or 128; rows_max 16 or 128).
     With ``slice_counters`` (int32 zeros, one per decoded token and KV head group, left at zero again) and
-    ``dec_rows``, the block that finishes a token's last key slice merges the slices itself."""
+    ``dec_rows``, the block that finishes a token's last key slice merges the slices itself; with ``cluster`` = the
+    number of slices per token (2 to 8) as well, the slices' blocks run as a cluster and merge through shared memory."""
     _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(pages, "pages", torch.bfloat16)
     for name, t in (("block_table", block_table), ("q_start", q_start), ("q_len", q_len), ("ctx_len", ctx_len),
                     ("items", items)):
@@ -483,7 +494,7 @@ def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items
     _call("vcb_attn_mma", _p(q), _p(out), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
           block_table.shape[1], _p(q_start), _p(q_len), _p(ctx_len), _p(items), n_items, rows_max, _p(part_o),
           _p(part_ml), _p(slice_counters), _p(dec_rows), nh, nkv, hd, page_size, num_pages, int(window or 0),
-          1.0 / math.sqrt(hd), _p(status), int(allow_tma), _stream())
+          1.0 / math.sqrt(hd), _p(status), int(allow_tma), int(cluster), _stream())
 
 
 # --------------------------------------------------------------------------  a look at a step from inside

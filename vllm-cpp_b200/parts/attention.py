@@ -32,7 +32,7 @@ MMA_SPAN_ROWS = 128
 MAX_SLICES = 64
 BLOCKS_PER_SM = 2         # blocks of the decode kernel that are resident at once on one SM
 SHORT_CONTEXT = 8192      # contexts up to here count as short for the slicing of decoded tokens' key ranges
-SHORT_SLICES = 12
+SHORT_SLICES = int(os.environ.get("VLLM_CPP_B200_ATTN_SHORT_SLICES", "12"))
 # prompt portions run on the tcgen05 kernel where it takes the sizes; 0 keeps them on the mma.sync kernel (comparison runs)
 TCGEN05_SPANS = os.environ.get("VLLM_CPP_B200_ATTN_TCGEN05", "1") != "0"
 # Steps of single tokens only that run kernel by kernel: norm, rotation and cache store inside the attention kernel
@@ -41,12 +41,20 @@ TCGEN05_SPANS = os.environ.get("VLLM_CPP_B200_ATTN_TCGEN05", "1") != "0"
 # (1.625 against 1.624 ms; context 2,176: 1.515 against 1.508): the blocks of the attention kernel become resident
 # only as the projection's blocks leave, and what the separate kernel did meanwhile they now do after their wait.
 FUSED_DECODE = int(os.environ.get("VLLM_CPP_B200_ATTN_FUSED_DECODE", "1"))
+# The blocks of a decoded token's key slices run as a thread-block cluster and merge their results through shared
+# memory (up to MAX_CLUSTER slices; more are merged by the last block through global memory).  0 switches it off.
+CLUSTER_MERGE = os.environ.get("VLLM_CPP_B200_ATTN_CLUSTER", "1") != "0"
+MAX_CLUSTER = 8
+MAX_CLUSTER_SHARED = 6
 
 
 class AttentionPlan:
     """Work items of the attention kernel for one step and one head layout, on the device."""
 
-    def __init__(self, ctx, nh: int, nkv: int, decode_rows: int = DECODE_ROWS, span_rows: int = SPAN_ROWS):
+    def __init__(self, ctx, nh: int, nkv: int, decode_rows: int = DECODE_ROWS, span_rows: int = SPAN_ROWS,
+                 cluster_hd: int | None = None):
+        """``cluster_hd``: the head size, when the kernel that takes the decoded tokens can merge a token's key slices
+        within a cluster of its blocks (then the slices are chosen so that all clusters run at once); else None."""
         g = nh // nkv
         dev = ctx.device
         # int32 arrays go to the device with the step's own staging buffers where the step has them
@@ -56,6 +64,7 @@ class AttentionPlan:
         self.n_dec = len(dec)
         self.decode_only = bool(dec) and not spans     # every entry of the step is one decoded token (or empty)
         self.nslices = 1
+        self.cluster = 0      # > 1: a token's key slices are a cluster of that many blocks
         self.dec_items = self.dec_rows = self.span_items = None
         self.n_span_items = 0
         if dec:
@@ -75,6 +84,19 @@ class AttentionPlan:
             if longest is not None and longest <= SHORT_CONTEXT:
                 fit = min(fit, SHORT_SLICES)
             self.nslices = int(max(1, min(MAX_SLICES, by_pages, fit)))
+            if cluster_hd is not None and longest is not None and longest <= SHORT_CONTEXT and self.nslices > 1:
+                # Over short contexts the slices of a token are a cluster that merges through shared memory, which
+                # saves the merge's trip through global memory (3 to 6 us a layer) -- if all the clusters run at
+                # once: the largest number of slices, eight at most, of which the device takes that many clusters
+                # (a cluster stays within one GPC, so sizes that do not divide a GPC's SMs leave some idle).
+                # Clusters of more than six blocks only where every block has an SM to itself: two to an SM, clusters of
+                # eight start late (four requests, 12-layer step: six slices 1.433 ms, eight 1.558, none clustered 1.487).
+                sms = ops.num_sms()
+                for s in range(min(self.nslices, MAX_CLUSTER), 1, -1):
+                    alone = blocks * s <= sms
+                    if (alone or s <= MAX_CLUSTER_SHARED) and blocks <= ops.attn_mma_max_clusters(cluster_hd, s, alone):
+                        self.nslices = self.cluster = s
+                        break
             items = np.zeros((len(dec) * self.nslices, ops.ITEM_INTS), dtype=np.int32)
             k = 0
             for n, e in enumerate(dec):
@@ -165,7 +187,8 @@ class GQAAttention(Mixer):
         mma = ops.attn_mma_supported(x.dtype, hd)
         kernel = ops.attn_mma if mma else ops.attn_paged
         dec_rows, span_rows = (MMA_DECODE_ROWS, MMA_SPAN_ROWS) if mma else (DECODE_ROWS, SPAN_ROWS)
-        plan = ctx.plan(("attention", nh, nkv, mma), lambda: AttentionPlan(ctx, nh, nkv, dec_rows, span_rows))
+        clustered = hd if mma and CLUSTER_MERGE and torch.cuda.is_available() else None
+        plan = ctx.plan(("attention", nh, nkv, mma, clustered), lambda: AttentionPlan(ctx, nh, nkv, dec_rows, span_rows, clustered))
         common = dict(nh=nh, nkv=nkv, hd=hd, window=self.window, status=ctx.status, table_row=ctx.slots)
         # A step of single tokens only, run kernel by kernel: the attention kernel norms, rotates and stores for itself,
         # straight from the projection's k-slice partial sums (one launch less in every layer).
@@ -173,14 +196,16 @@ class GQAAttention(Mixer):
                 and self.rotary_dim == hd and not self.interleaved
                 and ops.attn_mma_fused_supported(x.dtype, hd, cache.pages.shape[3])):
             S = plan.nslices
+            cluster = plan.cluster
             part_o = part_ml = None
-            if S > 1:
+            if S > 1 and not cluster:
                 part_o = workspace.empty((plan.n_dec * nh * S, hd), torch.float32, x.device)
                 part_ml = workspace.empty((plan.n_dec * nh * S, 2), torch.float32, x.device)
             ops.attn_mma_decode_fused(qkv, self.q_norm_w, self.k_norm_w, self.eps, self.rope.table,
                                       group.slot_map, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len,
                                       ctx.ctx_len, plan.dec_items, plan.n_dec * S, part_o, part_ml,
-                                      plan.slice_counters if S > 1 else None, plan.dec_rows, use_norm=self.qk_norm, **common)
+                                      plan.slice_counters if S > 1 else None, plan.dec_rows, use_norm=self.qk_norm,
+                                      cluster=cluster, **common)
             return matmul_tn(out, self.w_o, ctx.status, out_dtype=torch.float32, allow_partials=True)
         q = workspace.empty((T, nh * hd), x.dtype, x.device)
         ops.qknorm_rope_kvwrite(qkv, self.q_norm_w, self.k_norm_w, self.eps, self.rope.table, ctx.positions,
@@ -189,14 +214,16 @@ class GQAAttention(Mixer):
                                 interleaved=self.interleaved)
         if plan.n_dec:
             S = plan.nslices
+            cluster = plan.cluster if mma else 0
             part_o = part_ml = None
-            if S > 1:
+            if S > 1 and not cluster:
                 part_o = workspace.empty((plan.n_dec * nh * S, hd), torch.float32, x.device)
                 part_ml = workspace.empty((plan.n_dec * nh * S, 2), torch.float32, x.device)
             if mma:
                 ops.attn_mma(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
                              plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml,
-                             slice_counters=plan.slice_counters if S > 1 else None, dec_rows=plan.dec_rows, **common)
+                             slice_counters=plan.slice_counters if S > 1 else None, dec_rows=plan.dec_rows,
+                             cluster=cluster, **common)
             else:
                 ops.attn_paged(q, out, cache.pages, group.block_table, ctx.q_start, ctx.q_len, ctx.ctx_len,
                                plan.dec_items, plan.n_dec * S, dec_rows, part_o, part_ml, **common)
