@@ -285,6 +285,7 @@ def run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft=None):
     if ops.attn_mma_supported(dtype, hd):
         plan = _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma=True)           # TMA tile loads where the page size allows
         plan = _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma="no_tma")      # cp.async tile loads
+        plan = _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma="cluster")     # a token's key slices merged within a cluster of blocks
     if ops.attn_tc_supported(dtype, hd, ps):
         plan = _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma="tc")           # tcgen05 for the prompt portions
     return plan
@@ -295,9 +296,9 @@ def _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma):
     from vllm_cpp_b200 import ops
     from vllm_cpp_b200.parts import attention as A
     DECODE_ROWS, SPAN_ROWS = (A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS) if mma else (A.DECODE_ROWS, A.SPAN_ROWS)
-    AttentionPlan = lambda c, h, k: A.AttentionPlan(c, h, k, DECODE_ROWS, SPAN_ROWS)
+    AttentionPlan = lambda c, h, k: A.AttentionPlan(c, h, k, DECODE_ROWS, SPAN_ROWS, hd if mma == "cluster" else None)
     import functools
-    kernel = (functools.partial(ops.attn_mma, allow_tma=(mma is True)) if mma else ops.attn_paged)
+    kernel = (functools.partial(ops.attn_mma, allow_tma=(mma in (True, "cluster"))) if mma else ops.attn_paged)
     torch.manual_seed(1)
     seqs, qs = [], []
     for start, n in shapes:
@@ -335,8 +336,11 @@ def _run_attention(dtype, nh, nkv, hd, ps, window, shapes, craft, mma):
         S = plan.nslices
         po = torch.empty(plan.n_dec * nh * S, hd, device=dev()) if S > 1 else None
         pm = torch.empty(plan.n_dec * nh * S, 2, device=dev()) if S > 1 else None
-        fused = mma is True and S > 1      # the last-arriving block merges the key slices itself
-        extra = dict(slice_counters=plan.slice_counters, dec_rows=plan.dec_rows) if fused else {}
+        fused = mma in (True, "cluster") and S > 1      # the last-arriving block, or the slices' cluster, merges the key slices
+        extra = dict(slice_counters=plan.slice_counters, dec_rows=plan.dec_rows, cluster=plan.cluster) if fused else {}
+        if mma == "cluster" and S > 1:
+            assert plan.cluster == S                    # short contexts: the slices were chosen to fit clusters
+            po = pm = None                              # nothing goes through global memory
         kernel(q_flat, out, *args, plan.dec_items, plan.n_dec * S, DECODE_ROWS, po, pm, nh, nkv, hd, window, status, **extra)
         if fused:
             assert int(plan.slice_counters.abs().sum()) == 0        # left ready for the next launch
@@ -433,11 +437,25 @@ def test_attention_of_decoded_tokens_straight_from_the_projection(nh, nkv, hd, p
     ops.attn_mma_decode_fused(qkv, qw, kw, eps, table, slot_map, out_b, pages_b, bt, qs, ql, cl, plan.dec_items,
                               B * NS, po, pm, plan.slice_counters if NS > 1 else None, plan.dec_rows, nh, nkv, hd, window,
                               status, use_norm=norm)
+    # and the one with a token's key slices as a cluster of blocks that merge through shared memory
+    plan_c = A.AttentionPlan(ctx, nh, nkv, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS, hd)
+    pages_c = pages.clone()
+    out_c = torch.full_like(q, float("nan"))
+    if plan_c.cluster:
+        ops.attn_mma_decode_fused(qkv, qw, kw, eps, table, slot_map, out_c, pages_c, bt, qs, ql, cl, plan_c.dec_items,
+                                  B * plan_c.nslices, None, None, plan_c.slice_counters, plan_c.dec_rows, nh, nkv, hd,
+                                  window, status, use_norm=norm, cluster=plan_c.cluster)
     torch.cuda.synchronize()
     assert status.item() == 0
     assert torch.equal(pages_a.view(torch.int16), pages_b.view(torch.int16)), "the cache differs"
     assert not torch.isnan(out_b.float()).any()
     assert torch.equal(out_a.view(torch.int16), out_b.view(torch.int16)), "the attention output differs"
+    if plan_c.cluster:
+        assert torch.equal(pages_a.view(torch.int16), pages_c.view(torch.int16)), "the cache differs (clusters)"
+        if plan_c.nslices == NS:     # the same slices, merged in the same order: the same bits
+            assert torch.equal(out_b.view(torch.int16), out_c.view(torch.int16)), "the attention output differs (clusters)"
+        else:
+            torch.testing.assert_close(out_c.float(), out_b.float(), **tol(dtype))
     # and what came out is attention of the rotated query over the stored keys
     got = out_b.double().cpu().view(B, nh, hd)
     for b, (c, tab) in enumerate(zip(ctxs, tables)):
