@@ -8,6 +8,9 @@
     VLLM_CPP_B200_TIMELINE=1 VLLM_CPP_B200_BUILD_DIR=/tmp/vcb_timeline python microbench.py [--layers L] [--batch B]
         [--context C] timeline              one captured decode step seen from inside: when the blocks of each kernel
                                             start, when their wait for the kernel before ends, when they end
+    VLLM_CPP_B200_TIMELINE=1 VLLM_CPP_B200_BUILD_DIR=/tmp/vcb_timeline python microbench.py attention-roles [T]
+                                            the roles inside a block of the tcgen05 prompt attention kernel over a
+                                            prompt of T tokens (default 8192): clocks from mark to mark, per tile
 
 The sizes come from a Qwen3 configuration: one of the three serving shapes by name (default 8b) or a config.json.
 
@@ -179,6 +182,45 @@ def bench_small(dev, status):
         print(f"norm-rotate-store T={T:5d} slices {S}: {us:7.1f} us", flush=True)
 
 
+def bench_attention_roles(dev, status, tokens: int):
+    """The roles inside one block of the tcgen05 prompt attention kernel (a library built with VLLM_CPP_B200_TIMELINE=1):
+    a prompt of ``tokens`` tokens, one launch; for the block that works on the longest unit, the median clocks from one
+    mark of a role to its next, tile by tile, and the clocks a tile takes each role."""
+    import statistics
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    T = tokens
+    npages = T // PAGE
+    pages = torch.randn(npages, 2, NKV, PAGE, HD, device=dev).to(torch.bfloat16)
+    bt = torch.arange(npages, dtype=torch.int32, device=dev).view(1, -1)
+    q = torch.randn(T, NH * HD, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    c = _Ctx()
+    c.device, c.host_q_len, c.host_ctx_len, c.host_q_start = dev, [T], [T], [0]
+    plan = A.AttentionPlan(c, NH, NKV, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+    qs, ql, cl = i32([0]), i32([T]), i32([T])
+    run = lambda: ops.attn_tc(q, out, pages, bt, qs, ql, cl, plan.span_items, plan.n_span_items, NH, NKV, HD, 0, status,
+                              work=plan.span_work)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    ops.timeline_begin()
+    run()
+    rec = [r for r in ops.timeline_end() if r["kernel"] == "attn_tc" and r["phase"] >= 10 and r["block"] == 0]
+    names = {10: "load: asks", 11: "load: stages free", 12: "load: copies sent", 20: "products: asks for K", 21: "products: K there",
+             22: "products: Q.K^T issued", 23: "products: weights and V there", 24: "products: P.V issued", 30: "row: asks for scores",
+             31: "row: scores there", 32: "row: scores loaded", 33: "row: weights computed", 34: "row: handed over"}
+    print(f"prompt attention, {T} tokens, block 0: {len(rec)} marks of its roles")
+    for role, phases in (("loading warp", (10, 11, 12)), ("product thread", (20, 21, 22, 23, 24)), ("softmax row", (30, 31, 32, 33, 34))):
+        by = {ph: {r["tile"]: r["clock"] for r in rec if r["phase"] == ph} for ph in phases}
+        last = sorted(by[phases[-1]].items())
+        period = [b[1] - a[1] for a, b in zip(last, last[1:]) if b[0] == a[0] + 1]
+        print(f"  {role}: a tile every {statistics.median(period):.0f} clocks (median of {len(period)})" if period else f"  {role}: too few tiles")
+        for a, b in zip(phases, phases[1:]):
+            d = [by[b][t] - by[a][t] for t in by[a] if t in by[b]]
+            if d:
+                print(f"    {names[a]:30s} -> {names[b]:30s} {statistics.median(d):7.0f}")
+
+
 def bench_timeline(cfg, batch: int, context: int, layers: int, first: int, count: int):
     """One captured decode step of ``layers`` layers, recorded by the kernels' own timeline marks (a library built with
     VLLM_CPP_B200_TIMELINE=1), printed launch by launch: the times (us from the step's first mark) at which the first
@@ -261,7 +303,7 @@ def main(argv):
     ap.add_argument("--context", type=int, default=4096, help="timeline: tokens each request holds")
     ap.add_argument("--first", type=int, default=18, help="timeline: first launch to print")
     ap.add_argument("--count", type=int, default=30, help="timeline: launches to print")
-    ap.add_argument("what", nargs="?", default="gemm", choices=["gemm", "attention", "small", "timeline"])
+    ap.add_argument("what", nargs="?", default="gemm", choices=["gemm", "attention", "attention-roles", "small", "timeline"])
     ap.add_argument("tokens", nargs="*", type=int)
     args = ap.parse_args(argv)
     if args.model in NAMED:
@@ -287,6 +329,8 @@ def main(argv):
         bench_gemm(args.tokens or [8, 64, 256, 2048], dev, status)
     elif what == "attention":
         bench_attention(dev, status)
+    elif what == "attention-roles":
+        bench_attention_roles(dev, status, (args.tokens or [8192])[0])
     elif what == "small":
         bench_small(dev, status)
     elif what == "timeline":

@@ -113,7 +113,26 @@ __device__ __forceinline__ void tl_mark(int kernel, int phase) {
             unsigned long long* r = vcb_tl + 2 + 4 * i;
             r[0] = t;
             r[1] = c;
-            r[2] = ((unsigned long long)kernel << 32) | ((unsigned long long)phase << 24) | sm;
+            r[2] = ((unsigned long long)kernel << 32) | ((unsigned long long)phase << 24) | (sm & 0xFFu);
+            r[3] = ((unsigned long long)gridDim.x << 32) | (blockIdx.x + gridDim.x * blockIdx.y);
+        }
+    }
+}
+// The same from any ONE thread of a block and with a tile number, for a look at the roles inside a block (a loading
+// warp, a thread that issues products, rows of a softmax): every 37th block records, the others pay a comparison.
+__device__ __forceinline__ void tl_mark_role(int kernel, int phase, int tile) {
+    if (vcb_tl != nullptr && blockIdx.x % 37 == 0) {
+        unsigned long long t, c;
+        unsigned int sm;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t) :: "memory");
+        asm volatile("mov.u64 %0, %%clock64;" : "=l"(c) :: "memory");
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+        const unsigned long long i = atomicAdd(vcb_tl, 1ull);
+        if (i < vcb_tl[1]) {
+            unsigned long long* r = vcb_tl + 2 + 4 * i;
+            r[0] = t;
+            r[1] = c;
+            r[2] = ((unsigned long long)kernel << 32) | ((unsigned long long)phase << 24) | ((unsigned long long)(tile & 0xFFFF) << 8) | (sm & 0xFFu);
             r[3] = ((unsigned long long)gridDim.x << 32) | (blockIdx.x + gridDim.x * blockIdx.y);
         }
     }
@@ -124,6 +143,7 @@ __device__ __forceinline__ void tl_mark(int kernel, int phase) {
     }
 #else
 __device__ __forceinline__ void tl_mark(int, int) {}
+__device__ __forceinline__ void tl_mark_role(int, int, int) {}
 #define VCB_TIMELINE_UNIT(name)
 #endif
 

@@ -520,7 +520,8 @@ def timeline_begin(capacity: int = 1 << 18) -> None:
 
 
 def timeline_end():
-    """Stops recording; returns the records as a list of dicts (t_ns, clock, kernel, phase, sm, block, grid), by time."""
+    """Stops recording; returns the records as a list of dicts (t_ns, clock, kernel, phase, sm, tile, block, grid), by
+    time.  ``tile`` is 0 but for the marks of the roles inside a block (phases from 10 on), which carry a tile number."""
     global _timeline
     L = lib()
     torch.cuda.synchronize()
@@ -531,6 +532,6 @@ def timeline_end():
     n = int(min(buf[0], buf[1]))
     rec = buf[2:2 + 4 * n].reshape(n, 4)
     out = [dict(t_ns=int(r[0]), clock=int(r[1]), kernel=TIMELINE_KERNELS.get(int(r[2]) >> 32, "?"), phase=(int(r[2]) >> 24) & 0xFF,
-                sm=int(r[2]) & 0xFFFFFF, block=int(r[3]) & 0xFFFFFFFF, grid=int(r[3]) >> 32) for r in rec]
+                sm=int(r[2]) & 0xFF, tile=(int(r[2]) >> 8) & 0xFFFF, block=int(r[3]) & 0xFFFFFFFF, grid=int(r[3]) >> 32) for r in rec]
     out.sort(key=lambda d: d["t_ns"])
     return out
