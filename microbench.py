@@ -205,7 +205,7 @@ def bench_attention_roles(dev, status, tokens: int):
     torch.cuda.synchronize()
     ops.timeline_begin()
     run()
-    rec = [r for r in ops.timeline_end() if r["kernel"] == "attn_tc" and r["phase"] >= 10 and r["block"] == 0]
+    rec = [r for r in ops.timeline_end() if r["kernel"] == "attn_tc" and "role" in r and r["block"] == 0]
     names = {10: "load: asks", 11: "load: stages free", 12: "load: copies sent", 20: "products: asks for K", 21: "products: K there",
              22: "products: Q.K^T issued", 23: "products: weights and V there", 24: "products: P.V issued", 30: "row: asks for scores",
              31: "row: scores there", 32: "row: scores loaded", 33: "row: weights computed", 34: "row: handed over"}
@@ -264,7 +264,7 @@ def bench_timeline(cfg, batch: int, context: int, layers: int, first: int, count
     plain_ms = e0.elapsed_time(e1)
     ops.timeline_begin()
     e0.record(); step(); e1.record(); e1.synchronize()
-    rec = ops.timeline_end()
+    rec = [r for r in ops.timeline_end() if "role" not in r]     # the block-wide marks; roles inside blocks are another view
     print(f"decode step, batch {batch}, context {context}, {layers} layers: {plain_ms:.3f} ms; with the marks recorded {e0.elapsed_time(e1):.3f} ms; "
           f"{len(rec)} marks")
     # marks -> launches: a launch of a kernel takes every (block, phase) once

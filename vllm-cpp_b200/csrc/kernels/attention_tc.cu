@@ -46,7 +46,7 @@ constexpr int BNK = 64;       // keys per tile
 constexpr int ROWS = 128;     // rows per block = TMEM lanes
 constexpr int ITEM_INTS = 6;  // entry, q0, nq, slice, nslices, decode index (as in attention_mma.cu)
 constexpr int NTHREADS = 192;
-// Marks of the roles inside a block in a timeline build (tl_mark_role; the block-wide marks are phases 0 to 2): the
+// Marks of the roles inside a block in a timeline build (TlRole; the block-wide marks are phases 0 to 2): the
 // loading warp asks for a stage, has it, has sent the copies; the thread that issues the products asks for a K tile,
 // has it, has issued Q.K^T, has the tile's weights (and values), has issued P.V; the first softmax row asks for a
 // tile's scores, has them, has loaded them, has computed its weights, has handed them over.
@@ -350,6 +350,8 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
         int armed[2] = {0, 0};
         bool ok = true;
         int t0 = 0;
+        TlRole tl;
+        tl.begin(VCB_TL_ATTN_TC, 0, lane == 0);
         Unit u;
         int unit = (int)blockIdx.x;
         bool has = read_unit(a, unit, u);
@@ -414,14 +416,14 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                 auto load_tiles = [&](int itk, int itv) {
                     const int gk = t0 + itk, gv = t0 + itv;
                     bool free = true;
-                    if (lane == 0) tl_mark_role(VCB_TL_ATTN_TC, TL_LOAD_ASKS, gv);
+                    tl.mark(TL_LOAD_ASKS, gv);
                     if (lane == 0) {
                         // a K stage is free when its scores are there; a V stage when the product of the tile that
                         // used it (VS = 2 tiles ago, so on the same score buffer) has been added
                         if (itk >= 0) free = mbar_wait(k_empty(gk % KS), ((gk / KS) & 1) ^ 1u, abort_flag, a.status);
                         if (free && itv >= 0 && gv >= VS) free = mbar_wait(pv_done(gv & 1), (((gv - VS) >> 1) & 1), abort_flag, a.status);
                     }
-                    if (lane == 0) tl_mark_role(VCB_TL_ATTN_TC, TL_LOAD_FREE, gv);
+                    tl.mark(TL_LOAD_FREE, gv);
                     if (!__shfl_sync(0xffffffffu, free, 0)) return false;
                     const int it = copies_v ? itv : itk;
                     const bool mine = lane < 16 && it >= 0;
@@ -440,7 +442,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                         const uint32_t dst = base + (copies_v ? L::V_OFF : L::K_OFF) + st * L::KV_BYTES;
                         tma_load_groups(dst + pl * ps * ROWB, &kv_map, fullb, group);
                     }
-                    if (lane == 0) tl_mark_role(VCB_TL_ATTN_TC, TL_LOAD_SENT, gv);
+                    tl.mark(TL_LOAD_SENT, gv);
                     if (mine) next_page = page_of(it + 1);
                     if (itk >= 0) armed[0] = gk + 1;
                     if (itv >= 0) armed[1] = gv + 1;
@@ -478,6 +480,8 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
             constexpr uint32_t idesc_pv = instr_desc(HD, true);
             bool ok = true;
             int t0 = 0, done = 0;
+            TlRole tl;
+            tl.begin(VCB_TL_ATTN_TC, 1, true);
             Unit u;
             int unit = (int)blockIdx.x;
             bool has = read_unit(a, unit, u);
@@ -489,9 +493,9 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                 // before this by the same thread, and the tensor cores work through their queue in order.
                 auto issue_qk = [&](int j) {
                     const int gj = t0 + j, st = gj % KS, b = gj & 1;
-                    tl_mark_role(VCB_TL_ATTN_TC, TL_QK_ASKS, gj);
+                    tl.mark(TL_QK_ASKS, gj);
                     if (!mbar_wait(k_full(st), (gj / KS) & 1, abort_flag, a.status)) return false;
-                    tl_mark_role(VCB_TL_ATTN_TC, TL_QK_KEYS, gj);
+                    tl.mark(TL_QK_KEYS, gj);
                     tc_fence_after();
                     const uint32_t qa = base, ka = base + L::K_OFF + st * L::KV_BYTES;
 #pragma unroll
@@ -502,7 +506,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                         tc_mma(tmem_s + b * BNK, da, db, idesc_qk, ks > 0);
                     }
                     tc_commit(s_full(b));   // the row that sees it first gives the K stage back (a commit less for this thread)
-                    tl_mark_role(VCB_TL_ATTN_TC, TL_QK_ISSUED, gj);
+                    tl.mark(TL_QK_ISSUED, gj);
                     return true;
                 };
                 if (ok) ok = issue_qk(0);
@@ -515,7 +519,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                     // the values first: they have long landed when the rows hand over their weights
                     ok = mbar_wait(v_full(st), (gj / VS) & 1, abort_flag, a.status) && mbar_wait(p_ready(b), (gj >> 1) & 1, abort_flag, a.status);
                     if (!ok) break;
-                    tl_mark_role(VCB_TL_ATTN_TC, TL_PV_WEIGHTS, gj);
+                    tl.mark(TL_PV_WEIGHTS, gj);
                     tc_fence_after();
                     const uint32_t va = base + L::V_OFF + st * L::KV_BYTES;
 #pragma unroll
@@ -526,7 +530,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                         tc_mma_ts(tmem_o, tmem_s + b * BNK + ks * 8, db, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                     }
                     tc_commit(pv_done(b));   // also gives the V stage back
-                    tl_mark_role(VCB_TL_ATTN_TC, TL_PV_ISSUED, gj);
+                    tl.mark(TL_PV_ISSUED, gj);
                 }
                 t0 += u.n_tiles;
                 ++done;
@@ -540,6 +544,8 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
         const float scale_log2 = a.scale * LOG2E;
         bool ok = true;
         int t0 = 0;
+        TlRole tl;
+        tl.begin(VCB_TL_ATTN_TC, 2, tid == 64);
         // This row's query of the unit to come is asked for before the row finishes the unit it is on (the loader
         // names the next unit two or three tiles early), so that the load's latency passes behind the last product
         // and the output of the old unit; it goes to shared memory when that is done.
@@ -582,17 +588,17 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
             for (int j = 0; j < u.n_tiles; ++j) {
                 const int gj = t0 + j, b = gj & 1, st = gj % VS;
                 const int k0 = u.t_first + j * BNK;
-                if (tid == 64) tl_mark_role(VCB_TL_ATTN_TC, TL_ROW_ASKS, gj);
+                tl.mark(TL_ROW_ASKS, gj);
                 ok = mbar_wait(s_full(b), (gj >> 1) & 1, abort_flag, a.status);
                 if (!ok) break;
-                if (tid == 64) tl_mark_role(VCB_TL_ATTN_TC, TL_ROW_SCORES, gj);
+                tl.mark(TL_ROW_SCORES, gj);
                 if (tid == 64) mbar_arrive(k_empty(gj % KS));   // the scores are there: the keys of this stage have been read
                 tc_fence_after();
                 uint32_t sv[4][16];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) tc_ld16(tmem_s + lane_addr + (uint32_t)(b * BNK + 16 * i), sv[i]);
                 tc_wait_ld();
-                if (tid == 64) tl_mark_role(VCB_TL_ATTN_TC, TL_ROW_LOADED, gj);
+                tl.mark(TL_ROW_LOADED, gj);
 
                 // Scores stay unscaled in sv; only tiles that touch a row's own position or the window's edge mask.
                 const bool plain_tile = k0 + BNK - 1 <= u.pos0 && (W == 0 || k0 >= u.pos_last - W + 1);   // uniform over the block
@@ -666,7 +672,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                     }
                     fence_async_smem();   // before the arrival below, which the product that reads these rows awaits
                 }
-                if (tid == 64) tl_mark_role(VCB_TL_ATTN_TC, TL_ROW_COMPUTED, gj);
+                tl.mark(TL_ROW_COMPUTED, gj);
                 // The row of P over the first half of its scores: column c holds the weights of keys 2c and 2c + 1.
                 // (P of tile j - 2 lay here; its product was issued before the scores of this tile were computed.)
                 {
@@ -677,7 +683,7 @@ __global__ __launch_bounds__(NTHREADS, 2) void attn_tc_kernel(const __grid_const
                 }
                 tc_fence_before();
                 mbar_arrive(p_ready(b));
-                if (tid == 64) tl_mark_role(VCB_TL_ATTN_TC, TL_ROW_HANDED, gj);
+                tl.mark(TL_ROW_HANDED, gj);
             }
             const int g_last = t0 + u.n_tiles - 1;
             t0 += u.n_tiles;

@@ -118,32 +118,42 @@ __device__ __forceinline__ void tl_mark(int kernel, int phase) {
         }
     }
 }
-// The same from any ONE thread of a block and with a tile number, for a look at the roles inside a block (a loading
-// warp, a thread that issues products, rows of a softmax): every 37th block records, the others pay a comparison.
-__device__ __forceinline__ void tl_mark_role(int kernel, int phase, int tile) {
-    if (vcb_tl != nullptr && blockIdx.x % 37 == 0) {
-        unsigned long long t, c;
-        unsigned int sm;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t) :: "memory");
-        asm volatile("mov.u64 %0, %%clock64;" : "=l"(c) :: "memory");
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
-        const unsigned long long i = atomicAdd(vcb_tl, 1ull);
-        if (i < vcb_tl[1]) {
-            unsigned long long* r = vcb_tl + 2 + 4 * i;
-            r[0] = t;
-            r[1] = c;
-            r[2] = ((unsigned long long)kernel << 32) | ((unsigned long long)phase << 24) | ((unsigned long long)(tile & 0xFFFF) << 8) | (sm & 0xFFu);
-            r[3] = ((unsigned long long)gridDim.x << 32) | (blockIdx.x + gridDim.x * blockIdx.y);
+// The roles inside a block (a loading warp, a thread that issues products, rows of a softmax) mark their steps in
+// logs of their own behind the records above: no counter to wait for, a clock read and two stores a mark.  Blocks
+// 0, 37, 74, ... (eight at most) record, up to three roles each, each role through one thread.
+constexpr int VCB_TL_ROLE_EVERY = 37, VCB_TL_ROLE_BLOCKS = 8, VCB_TL_ROLES = 3, VCB_TL_ROLE_MARKS = 2048;
+struct TlRole {
+    unsigned long long* log = nullptr;
+    int n = 0;
+    int kernel = 0;
+    __device__ __forceinline__ void begin(int kernel_id, int role, bool this_thread) {
+        log = nullptr;
+        n = 0;
+        kernel = kernel_id;
+        if (this_thread && vcb_tl != nullptr && blockIdx.y == 0 && blockIdx.x % VCB_TL_ROLE_EVERY == 0 &&
+            blockIdx.x / VCB_TL_ROLE_EVERY < VCB_TL_ROLE_BLOCKS)
+            log = vcb_tl + 2 + 4 * vcb_tl[1] + (size_t)((blockIdx.x / VCB_TL_ROLE_EVERY) * VCB_TL_ROLES + role) * VCB_TL_ROLE_MARKS * 2;
+    }
+    __device__ __forceinline__ void mark(int phase, int tile) {
+        if (log != nullptr && n < VCB_TL_ROLE_MARKS) {
+            unsigned long long c;
+            asm volatile("mov.u64 %0, %%clock64;" : "=l"(c) :: "memory");
+            log[2 * n] = c;
+            log[2 * n + 1] = (1ull << 63) | ((unsigned long long)kernel << 48) | ((unsigned long long)phase << 32) | (unsigned int)tile;
+            ++n;
         }
     }
-}
+};
 #define VCB_TIMELINE_UNIT(name)                                                             \
     VCB_API int vcb_timeline_set_##name(unsigned long long* p) {                            \
         return cudaMemcpyToSymbol(vcb_tl, &p, sizeof(p)) == cudaSuccess ? 0 : -1;           \
     }
 #else
 __device__ __forceinline__ void tl_mark(int, int) {}
-__device__ __forceinline__ void tl_mark_role(int, int, int) {}
+struct TlRole {
+    __device__ __forceinline__ void begin(int, int, bool) {}
+    __device__ __forceinline__ void mark(int, int) {}
+};
 #define VCB_TIMELINE_UNIT(name)
 #endif
 

@@ -499,6 +499,8 @@ def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items
 
 # --------------------------------------------------------------------------  a look at a step from inside
 _timeline = None
+_TL_ROLE_EVERY, _TL_ROLE_BLOCKS, _TL_ROLES, _TL_ROLE_MARKS = 37, 8, 3, 2048     # as in kernels/common.cuh
+_TL_ROLE_WORDS = _TL_ROLE_BLOCKS * _TL_ROLES * _TL_ROLE_MARKS * 2
 TIMELINE_KERNELS = {1: "gemm", 2: "attn_decode", 3: "add_rmsnorm", 4: "qknorm_rope", 5: "swiglu", 6: "attn_tc", 7: "other"}
 
 
@@ -509,7 +511,7 @@ def timeline_begin(capacity: int = 1 << 18) -> None:
     L = lib()
     if not hasattr(L, "vcb_timeline_set_gemm"):
         raise KernelError("this kernel library was built without timeline marks (build with VLLM_CPP_B200_TIMELINE=1)")
-    _timeline = torch.zeros(2 + 4 * capacity, dtype=torch.int64, device="cuda")
+    _timeline = torch.zeros(2 + 4 * capacity + _TL_ROLE_WORDS, dtype=torch.int64, device="cuda")
     _timeline[1] = capacity
     torch.cuda.synchronize()
     for unit in ("gemm", "attn_mma", "attn_tc", "elementwise"):
@@ -521,7 +523,8 @@ def timeline_begin(capacity: int = 1 << 18) -> None:
 
 def timeline_end():
     """Stops recording; returns the records as a list of dicts (t_ns, clock, kernel, phase, sm, tile, block, grid), by
-    time.  ``tile`` is 0 but for the marks of the roles inside a block (phases from 10 on), which carry a tile number."""
+    time.  The marks of the roles inside a block (phases from 10 on; they have a ``role``, a tile number and the SM's
+    clock, but no time: t_ns 0) come first."""
     global _timeline
     L = lib()
     torch.cuda.synchronize()
@@ -532,6 +535,15 @@ def timeline_end():
     n = int(min(buf[0], buf[1]))
     rec = buf[2:2 + 4 * n].reshape(n, 4)
     out = [dict(t_ns=int(r[0]), clock=int(r[1]), kernel=TIMELINE_KERNELS.get(int(r[2]) >> 32, "?"), phase=(int(r[2]) >> 24) & 0xFF,
-                sm=int(r[2]) & 0xFF, tile=(int(r[2]) >> 8) & 0xFFFF, block=int(r[3]) & 0xFFFFFFFF, grid=int(r[3]) >> 32) for r in rec]
+                sm=int(r[2]) & 0xFF, tile=0, block=int(r[3]) & 0xFFFFFFFF, grid=int(r[3]) >> 32) for r in rec]
+    # the logs of the roles inside a block: (clock, tag) pairs per (recording block, role)
+    logs = buf[2 + 4 * int(buf[1]):].reshape(_TL_ROLE_BLOCKS, _TL_ROLES, _TL_ROLE_MARKS, 2)
+    for b in range(_TL_ROLE_BLOCKS):
+        for role in range(_TL_ROLES):
+            for clock, tag in logs[b, role]:
+                tag = int(tag) & 0xFFFFFFFFFFFFFFFF
+                if tag >> 63:
+                    out.append(dict(t_ns=0, clock=int(clock), kernel=TIMELINE_KERNELS.get((tag >> 48) & 0xFF, "?"), phase=(tag >> 32) & 0xFFFF,
+                                    sm=-1, tile=tag & 0xFFFFFFFF, block=b * _TL_ROLE_EVERY, grid=0, role=role))
     out.sort(key=lambda d: d["t_ns"])
     return out
