@@ -59,3 +59,48 @@ def test_portions_are_cut_into_query_tiles_longest_first():
     # seven query heads a KV head: 18 tokens a tile (126 rows)
     p = A.AttentionPlan(ctx([40], [40]), 14, 2, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
     assert sorted(i[2] for i in p.span_items.tolist()) == [4, 18, 18]
+
+
+def test_key_slices_that_merge_in_clusters_are_chosen_so_that_all_clusters_run_at_once(monkeypatch):
+    """Where the decode kernel can merge a token's slices within a cluster of blocks, the number of slices is the
+    largest (eight at most; six where two blocks share an SM) of which the device runs as many clusters at once as
+    there are (request, KV head) pairs.  The device's answers here are a B200's."""
+    alone = {1: 148, 2: 74, 3: 45, 4: 33, 5: 26, 6: 22, 7: 15, 8: 15}        # clusters of blocks with an SM each
+    shared = {1: 296, 2: 148, 3: 93, 4: 71, 5: 56, 6: 45, 7: 37, 8: 33}     # two blocks an SM
+    asked = []
+
+    def fits(hd, size, deep):
+        asked.append((hd, size, deep))
+        return (alone if deep else shared)[size]
+
+    monkeypatch.setattr(A.ops, "attn_mma_max_clusters", fits)
+    monkeypatch.setattr(A.ops, "num_sms", lambda: 148)
+
+    def plan(batch, context=4096, **kw):
+        return A.AttentionPlan(ctx([1] * batch, [context] * batch, **kw), 32, 8, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS, 128)
+
+    want = {1: 8,      # 8 pairs: fifteen clusters of eight fit
+            2: 6,      # 16 pairs: not fifteen clusters of eight or seven, but twenty-two of six
+            3: 5,      # 24 pairs: twenty-six clusters of five
+            4: 6,      # 32 pairs, 192 blocks, two to an SM: forty-five clusters of six (eight would start late)
+            8: 4,      # 64 pairs: no more than four slices fill the SMs; seventy-one clusters of four fit
+            16: 2}
+    for batch, slices in want.items():
+        p = plan(batch)
+        assert (p.nslices, p.cluster) == (slices, slices), (batch, p.nslices, p.cluster)
+    assert all(hd == 128 for hd, _, _ in asked)
+    # one slice needs no cluster; long contexts keep their many slices and the merge through global memory
+    p = plan(64)
+    assert (p.nslices, p.cluster) == (1, 0)
+    p = plan(1, 32768)
+    assert p.nslices == (A.BLOCKS_PER_SM * 148) // 8 and p.cluster == 0
+    # a captured step of the short context class chooses the same way; of the long class, no clusters
+    assert plan(8, 0, static=True, bound=8192).cluster == 4
+    assert plan(8, 0, static=True, bound=None).cluster == 0
+    # without a kernel that merges in clusters (no head size given) nothing changes
+    p = A.AttentionPlan(ctx([1], [4096]), 32, 8, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+    assert (p.nslices, p.cluster) == (A.SHORT_SLICES, 0)
+    # a device that takes no clusters of any size: the slices stay, merged through global memory
+    monkeypatch.setattr(A.ops, "attn_mma_max_clusters", lambda hd, size, deep: -1)
+    p = plan(1)
+    assert (p.nslices, p.cluster) == (A.SHORT_SLICES, 0)
