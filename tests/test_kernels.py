@@ -473,7 +473,8 @@ def test_attention_window(dtype, window, hd):
 
 
 @pytest.mark.parametrize("nh,nkv,hd,ps,window", [(8, 2, 128, 16, 0), (3, 3, 128, 64, 0), (10, 2, 64, 8, 0), (4, 1, 128, 32, 0),
-                                                 (8, 2, 128, 16, 100), (2, 1, 64, 16, 7), (130, 1, 64, 16, 0)])
+                                                 (8, 2, 128, 16, 100), (2, 1, 64, 16, 7), (130, 1, 64, 16, 0),
+                                                 (4, 2, 128, 8, 0), (6, 2, 64, 64, 33), (5, 1, 64, 32, 0)])
 def test_attention_long_prompt_portions(nh, nkv, hd, ps, window):
     """Prompt portions over many key tiles (what the tcgen05 kernel pipelines): from an empty cache, behind a long
     prefix, a prefix that ends inside a page and inside a tile, group sizes that do not divide 128 rows."""
