@@ -176,6 +176,63 @@ def test_qknorm_rope_kvwrite(dtype, nh, nkv, hd):
             assert pages[s // ps, :, :, s % ps].abs().max().item() == 0
 
 
+@pytest.mark.parametrize("nh,nkv,T,K,norm,kv", [(4, 2, 300, 192, True, True), (5, 1, 129, 64, True, True), (3, 3, 521, 320, False, True),
+                                                (32, 8, 1024, 256, True, True), (6, 2, 200, 128, True, False)])
+def test_qkv_projection_with_norm_rotation_and_store_in_its_epilogue(nh, nkv, T, K, norm, kv):
+    """gemm_qkv_rope (prompt portions, head_dim 128): the stacked projection whose epilogue norms each query and key
+    head, rotates it and stores queries, keys and values -- against 64-bit arithmetic on the same bfloat16 operands,
+    and against the two kernels it replaces.  Token counts that end inside a unit and inside a chunk of 32, a token
+    that stores nowhere, positions all over the table, pages in any order; with and without the norms; a layer that
+    stores no keys (query rows only)."""
+    from vllm_cpp_b200 import ops
+    hd, ps, eps, max_pos = 128, 16, 1e-6, 700
+    torch.manual_seed(nh * 7 + T)
+    heads = nh + (2 * nkv if kv else 0)
+    w = (0.05 * torch.randn(heads * hd, K, device=dev())).to(torch.bfloat16)
+    x = torch.randn(T, K, device=dev()).to(torch.bfloat16)
+    qw = (1 + 0.1 * torch.randn(hd, device=dev())).to(torch.bfloat16) if norm else None
+    kw = (1 + 0.1 * torch.randn(hd, device=dev())).to(torch.bfloat16) if norm and kv else None
+    table = rope_table(hd, 1e4, max_pos)
+    pos = torch.randint(0, max_pos, (T,), device=dev(), dtype=torch.int32)
+    num_pages = T // ps + 3
+    slots = torch.randperm(num_pages * ps, device=dev())[:T].to(torch.int32)
+    slots[T // 2] = -1
+    pages = torch.zeros(num_pages, 2, nkv, ps, hd, device=dev(), dtype=torch.bfloat16) if kv else None
+    q_out = torch.full((T, nh * hd), float("nan"), device=dev(), dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    ops.gemm_qkv_rope(w, x, q_out, pages, slots if kv else None, pos, table, qw, kw, eps, nh, nkv, status, use_norm=norm)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    h = (x.double() @ w.double().t()).view(T, heads, hd)
+    c, s = table[pos.long(), :hd // 2].double()[:, None], table[pos.long(), hd // 2:].double()[:, None]
+
+    def norm_rope(v, g):
+        if norm:
+            v = g.double() * v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
+        a, b = v[..., :hd // 2], v[..., hd // 2:]
+        return torch.cat([a * c - b * s, b * c + a * s], -1)
+
+    close = dict(rtol=1e-2, atol=2e-2)      # bfloat16 results of sums of up to 320 products
+    torch.testing.assert_close(q_out.double().view(T, nh, hd), norm_rope(h[:, :nh], qw), **close)
+    if kv:
+        k_want, v_want = norm_rope(h[:, nh:nh + nkv], kw), h[:, nh + nkv:]
+        idx = torch.nonzero(slots >= 0).flatten()
+        sl = slots[idx].long()
+        torch.testing.assert_close(pages[sl // ps, 0, :, sl % ps].double(), k_want[idx], **close)
+        torch.testing.assert_close(pages[sl // ps, 1, :, sl % ps].double(), v_want[idx], **close)
+        untouched = torch.ones(num_pages * ps, dtype=torch.bool, device=dev())
+        untouched[sl] = False
+        rest = torch.nonzero(untouched).flatten()
+        assert pages[rest // ps, :, :, rest % ps].abs().max().item() == 0
+        # the two kernels it replaces give the same up to the rounding of the projection to bfloat16 in between
+        qkv = torch.empty(T, heads * hd, device=dev(), dtype=torch.bfloat16)
+        ops.gemm_bf16_tn(w, x, qkv, 1, status)
+        pages2, q2 = torch.zeros_like(pages), torch.empty_like(q_out)
+        ops.qknorm_rope_kvwrite(qkv, qw, kw, eps, table, pos, slots, q2, pages2, nh, nkv, hd, status, use_norm=norm)
+        torch.testing.assert_close(q_out.float(), q2.float(), rtol=2e-2, atol=4e-2)
+        torch.testing.assert_close(pages.float(), pages2.float(), rtol=2e-2, atol=4e-2)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("hd,rot,interleaved", [(16, 8, True), (32, 32, True), (64, 16, False), (128, 64, False), (48, 2, True), (128, 128, True)])
 def test_qknorm_rope_kvwrite_partial_and_interleaved(dtype, hd, rot, interleaved):

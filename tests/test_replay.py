@@ -56,6 +56,20 @@ def test_replay(name, dtype, mode, model_dirs, plain_logits, tmp_path):
     print(f"{name} {dtype} {mode}: worst relative error {worst:.3e}, pool {trace.max_tokens} tokens, {len(trace.steps)} steps")
 
 
+@pytest.mark.parametrize("mode", ["whole", "portions"])
+def test_replay_with_norm_rotation_and_store_in_the_projection(mode, model_dirs, plain_logits, tmp_path):
+    """Configuration D (head_dim 128) in bfloat16 with the q, k, v projection doing the per-head norm, the rotation and
+    the cache store in its epilogue for every portion of more than 32 tokens (serving does from about 1,300 on): the
+    prompts whole -- 500, 300, 256, 129 tokens end in the middle of a unit and of a chunk -- and in portions, over a
+    NaN-filled cache, against the plain implementation."""
+    requests = make_requests("D")
+    trace = {"whole": R.whole, "portions": R.portions}[mode](requests)
+    out = R.run_trace(model_dirs["D"], "bfloat16", trace, tmp_path / "out", TINY_PAGE["D"], extra_args=["--poison"],
+                      extra_env={"VLLM_CPP_B200_QKV_EPILOGUE_ABOVE": "32"})
+    worst = compare("D", "bfloat16", trace, out, requests, plain_logits)
+    print(f"D bfloat16 {mode}, projection epilogue: worst relative error {worst:.3e}")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_replay_modes_agree_with_each_other(dtype, model_dirs, tmp_path):
     """Cutting and batching change the logits by rounding only (far below the distance to the reference)."""

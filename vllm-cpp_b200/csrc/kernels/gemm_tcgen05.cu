@@ -89,6 +89,21 @@ __host__ __device__ constexpr uint32_t instr_desc(int bn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
+// What the epilogue of the stacked q, k, v projection needs to do the work of the norm-rotate-store kernel itself (prompt
+// portions, head_dim 128: a 128-feature unit is one head).  q_out null: an ordinary product.
+struct QkvEpilogue {
+    __nv_bfloat16* q_out;        // [tokens][nh * 128]
+    __nv_bfloat16* pages;        // the layer's pages [page][2][nkv][page_size][128]; null: no keys and values to store
+    long long page_stride;
+    const int* slot_map;         // per token: slot in the cache, -1: store nowhere
+    const int* positions;        // per token
+    const float* cos_sin;        // [max_pos][128]: 64 cosines, 64 sines
+    const void* q_gain;          // per-head norm gains [128] (gain_dtype), unused without use_norm
+    const void* k_gain;
+    int max_pos, gain_dtype, use_norm, nh, nkv, page_size, num_pages;
+    float eps;
+};
+
 struct GemmArgs {
     void* out;
     int out_dtype;            // VCB_F32 or VCB_BF16
@@ -99,6 +114,7 @@ struct GemmArgs {
     int splits;               // k-slices
     int swiglu;               // 1: rows 2i and 2i+1 of W are gate_i and up_i, and the output is silu(gate) * up, [tokens, M/2] bfloat16
     int* status;
+    QkvEpilogue qe;
 };
 
 // MT = 128-feature tiles per work unit that share one token tile (2 halves the bytes that cross L2 per flop);
@@ -110,7 +126,11 @@ struct Smem {
     static constexpr int STAGE_BYTES = MT * A_BYTES + B_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
     static constexpr int NUM_BARS = 2 * STAGES + 2 * ACC;
-    static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;   // + alignment slack
+    // where the q, k, v epilogue passes a head's values between its four warps: 128 features x 32 tokens (rows padded
+    // to 33 words), the warps' partial sums of squares, the tokens' factors, positions and slots
+    static constexpr int EPI_OFFSET = (BAR_OFFSET + NUM_BARS * 8 + 16 + 15) / 16 * 16;
+    static constexpr int EPI_BYTES = (MT == 1 && BN >= 128) ? (128 * 33 + 4 * 32 + 4 * 32) * 4 : 0;
+    static constexpr int TOTAL = EPI_OFFSET + EPI_BYTES + 1024;   // + alignment slack
 };
 
 
@@ -140,6 +160,101 @@ __device__ __forceinline__ void swiglu_store(uint32_t (*v)[16], __nv_bfloat16* o
         for (int jj = 0; jj < CHUNK; ++jj)
             if (n_first + jj < N) o[(size_t)jj * ldc] = __float2bfloat16_rn(r[jj]);
     }
+}
+
+// Epilogue of the stacked q, k, v projection for prompt portions with head_dim 128: the unit's 128 features are one
+// head.  Called by the four epilogue warps together for 32 token columns at a time (thread = feature f = 32 q + lane,
+// x = its 32 values): a query or key head is normed over its 128 features (sum of squares through shared memory),
+// scaled by its gains, rotated with the partner feature 64 away (half-split pairs: out_i = a_i cos_i - a_{i+64} sin_i,
+// out_{i+64} = a_{i+64} cos_i + a_i sin_i), rounded to bfloat16 and stored -- queries to q_out, keys to the token's
+// slot of the cache; a value head is stored as it is.  All in 32-bit, from the product's 32-bit sums (the separate
+// kernel reads them rounded to bfloat16).  Named barrier 1 is the four warps'.
+__device__ __forceinline__ void epilogue_warps_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void qkv_head_store(const float (&x)[32], const QkvEpilogue& e, int head, int f, int q, int lane,
+                                               int tok0, int N, float* stage, int* status) {
+    float* part = stage + 128 * 33;                       // [4][32] partial sums of squares
+    float* factor = part + 4 * 32;                        // [32]
+    int* pos_s = reinterpret_cast<int*>(factor + 32);     // [32]
+    long long* where_s = reinterpret_cast<long long*>(pos_s + 32);   // [32]: where in the pages the token's row of K head 0 begins; -1: nowhere
+    const bool is_q = head < e.nh, is_v = head >= e.nh + e.nkv;
+    const int kvh = is_q ? 0 : (is_v ? head - e.nh - e.nkv : head - e.nh);
+    // this chunk's positions and places in the cache, looked up and checked once
+    if (q == 0) {
+        int pos = tok0 + lane < N ? e.positions[tok0 + lane] : 0;
+        if (pos < 0 || pos >= e.max_pos) {
+            atomicOr(status, VCB_STATUS_BAD_POSITION);
+            pos = 0;
+        }
+        pos_s[lane] = pos;
+    } else if (q == 1) {
+        int slot = (!is_q && e.pages != nullptr && tok0 + lane < N) ? e.slot_map[tok0 + lane] : -1;
+        if (slot >= 0 && slot / e.page_size >= e.num_pages) {
+            atomicOr(status, VCB_STATUS_BAD_PAGE);
+            slot = -1;
+        }
+        where_s[lane] = slot < 0 ? -1ll : (long long)(slot / e.page_size) * e.page_stride + (long long)(slot % e.page_size) * 128;
+    }
+    // this thread's feature of this head within a token's row of the pages
+    const long long head_at = ((long long)((is_v ? e.nkv : 0) + kvh) * e.page_size) * 128 + f;
+    if (!is_v) {
+#pragma unroll
+        for (int t = 0; t < 32; ++t) stage[f * 33 + t] = x[t];
+    }
+    epilogue_warps_sync();
+    if (is_v) {
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+            const long long at = where_s[t];
+            if (at >= 0) e.pages[at + head_at] = __float2bfloat16_rn(x[t]);
+        }
+        epilogue_warps_sync();      // the places are read; the next chunk may write its own
+        return;
+    }
+    float n[32];
+    if (e.use_norm) {
+        // token = lane: the squares of this warp's 32 features, then the four warps' sums
+        float ss = 0.f;
+#pragma unroll
+        for (int ff = 0; ff < 32; ++ff) {
+            const float y = stage[(q * 32 + ff) * 33 + lane];
+            ss += y * y;
+        }
+        part[q * 32 + lane] = ss;
+        epilogue_warps_sync();
+        if (q == 0) factor[lane] = 1.0f / sqrtf((part[lane] + part[32 + lane] + part[64 + lane] + part[96 + lane]) / 128.f + e.eps);
+        epilogue_warps_sync();
+        const float gain = load_as_f32(is_q ? e.q_gain : e.k_gain, e.gain_dtype, f);
+#pragma unroll
+        for (int t = 0; t < 32; ++t) n[t] = gain * x[t] * factor[t];
+#pragma unroll
+        for (int t = 0; t < 32; ++t) stage[f * 33 + t] = n[t];      // every read of the raw values is behind the barriers above
+        epilogue_warps_sync();
+    } else {
+#pragma unroll
+        for (int t = 0; t < 32; ++t) n[t] = x[t];
+    }
+    const int fi = f & 63;
+    const float sign = f < 64 ? -1.f : 1.f;
+    // all the cosines and sines first (read-only loads: none waits behind a store), then all the stores
+#pragma unroll
+    for (int t = 0; t < 32; ++t) {
+        const float partner = stage[(f ^ 64) * 33 + t];
+        const float* cs = e.cos_sin + (size_t)pos_s[t] * 128;
+        n[t] = n[t] * __ldg(cs + fi) + sign * partner * __ldg(cs + 64 + fi);
+    }
+    if (is_q) {
+        __nv_bfloat16* dst = e.q_out + ((size_t)tok0 * e.nh + head) * 128 + f;
+#pragma unroll
+        for (int t = 0; t < 32; ++t)
+            if (tok0 + t < N) dst[(size_t)t * e.nh * 128] = __float2bfloat16_rn(n[t]);
+    } else {
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+            const long long at = where_s[t];
+            if (at >= 0) e.pages[at + head_at] = __float2bfloat16_rn(n[t]);
+        }
+    }
+    epilogue_warps_sync();          // the partners, positions and places are read; the next chunk may write its own
 }
 
 // Order of the (feature tile, token tile) pairs: token tiles fastest, in groups of up to TOKEN_TILE_GROUP, so
@@ -335,6 +450,19 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_kernel(const __grid_
                 for (int b = 0; b < CHUNK / 16; ++b)
                     tc_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * ACC_COLS + c0 + 16 * b), v[b]);
                 tc_wait_ld();
+                if constexpr (L::EPI_BYTES > 0) {
+                    if (g.qe.q_out != nullptr) {     // uniform over the block: every warp takes part in the barriers
+                        float* stage = reinterpret_cast<float*>(gen + L::EPI_OFFSET);
+#pragma unroll
+                        for (int hh = 0; hh < CHUNK / 32; ++hh) {
+                            float x[32];
+#pragma unroll
+                            for (int t = 0; t < 32; ++t) x[t] = __uint_as_float(v[(32 * hh + t) / 16][(32 * hh + t) % 16]);
+                            qkv_head_store(x, g.qe, m0 / BM, q * 32 + lane, q, lane, n0 + c0 + 32 * hh, g.N, stage, g.status);
+                        }
+                        continue;
+                    }
+                }
                 if (g.swiglu) {
                     swiglu_store<CHUNK>(v, reinterpret_cast<__nv_bfloat16*>(g.out), g.ldc, m, g.M, n0 + c0, g.N, lane);
                 } else if (m < g.M) {
@@ -884,6 +1012,34 @@ VCB_API int vcb_gemm_bf16_swiglu(const void* W, const void* X, void* out, int I,
     GemmArgs g{out, VCB_BF16, 2 * I, N, K, ldc, 0, total_kb, 1, 1, status};
     if (shape < 0 && use_pairs(2 * I, N, K, 1)) return launch_pair(W, 2LL * I, X, g, ldw, ldx, stream);
     return launch_shape(shape < 0 ? pick_shape(2 * I, N, K, 1) : shape, W, X, g, ldw, ldx, 1, stream);
+}
+
+// The stacked q, k, v projection of prompt portions with the per-head norm, the rotation and the cache store in its
+// epilogue (head_dim 128, half-split pairs rotated over the whole head; see qkv_head_store).  W [(nh + 2 nkv) * 128, K]
+// (or [nh * 128, K] with pages null: a layer that stores no keys), X [N, K] bfloat16; q_out [N, nh * 128] bfloat16;
+// pages: the layer's pages, bfloat16, `page_stride` elements apart.  No k-slices: for more than 128 tokens.
+VCB_API int vcb_gemm_bf16_qkv(const void* W, const void* X, int N, int K, long long ldw, long long ldx, void* q_out,
+                              void* pages, long long page_stride, int page_size, int num_pages, const int* slot_map,
+                              const int* positions, const float* cos_sin, int max_pos, const void* q_gain,
+                              const void* k_gain, int gain_dtype, int use_norm, float eps, int nh, int nkv, int* status,
+                              cudaStream_t stream) {
+    VCB_CHECK_ARG(N > 0 && K > 0 && nh > 0 && nkv > 0, "gemm_bf16_qkv: bad sizes N=%d K=%d nh=%d nkv=%d", N, K, nh, nkv);
+    VCB_CHECK_ARG(K % 8 == 0 && ldw % 8 == 0 && ldx % 8 == 0,
+                  "gemm_bf16_qkv: inner size %d and row strides %lld, %lld must be multiples of 8 (16-byte rows for TMA)", K, ldw, ldx);
+    VCB_CHECK_ARG(((uintptr_t)W % 16 == 0) && ((uintptr_t)X % 16 == 0), "gemm_bf16_qkv: operands must be 16-byte aligned");
+    VCB_CHECK_ARG(q_out != nullptr && positions != nullptr && cos_sin != nullptr && status != nullptr && max_pos > 0,
+                  "gemm_bf16_qkv: missing operand");
+    VCB_CHECK_ARG(pages == nullptr || (slot_map != nullptr && page_size > 0 && num_pages > 0), "gemm_bf16_qkv: pages without slots or sizes");
+    VCB_CHECK_ARG(!use_norm || (q_gain != nullptr && (pages == nullptr || k_gain != nullptr)), "gemm_bf16_qkv: the per-head norms need their gains");
+    const int M = (nh + (pages != nullptr ? 2 * nkv : 0)) * BM;
+    const int total_kb = (K + BK - 1) / BK;
+    GemmArgs g{nullptr, VCB_BF16, M, N, K, 0, 0, total_kb, 1, 0, status,
+               QkvEpilogue{(__nv_bfloat16*)q_out, (__nv_bfloat16*)pages, page_stride, slot_map, positions, cos_sin, q_gain, k_gain,
+                           max_pos, gain_dtype, use_norm, nh, nkv, page_size, num_pages, eps}};
+    // units of one head: 128 features x 256 tokens, or x 128 where those fill the SMs' rounds better (as pick_shape counts)
+    auto rounds = [&](int bn) { return (((long long)(M / BM) * ((N + bn - 1) / bn) + num_sms() - 1) / num_sms()) * bn; };
+    const bool narrow = N <= 128 || rounds(128) * 8 / 5 < rounds(256);
+    return narrow ? launch<128, 6, 1, 2>(W, X, g, ldw, ldx, 1, stream) : launch<256, 4, 1, 2>(W, X, g, ldw, ldx, 1, stream);
 }
 
 VCB_API int vcb_gemm_bf16_tn(const void* W, const void* X, void* out, int out_dtype, int M, int N, int K,

@@ -65,6 +65,7 @@ def _declare(L):
         "vcb_gemm_effective_splits": [I, I],
         "vcb_gemm_set_pairs": [I],
         "vcb_gemm_bf16_swiglu": [P, P, P, I, I, I, LL, LL, LL, I, P, P],
+        "vcb_gemm_bf16_qkv": [P, P, I, I, LL, LL, P, P, LL, I, I, P, P, P, I, P, P, I, I, F, I, I, P, P],
         "vcb_sgemm_tn": [P, P, P, I, I, I, LL, LL, LL, P],
         "vcb_gemm_bf16_plain": [P, P, P, I, I, I, I, LL, LL, LL, P],
         "vcb_attn_paged": [P, P, I, P, LL, P, P, I, P, P, P, P, I, I, P, P, I, I, I, I, I, I, F, P, P],
@@ -311,6 +312,36 @@ def gemm_bf16_swiglu(w_gate_up, x, out, status, shape=-1):
     assert I2 % 2 == 0 and x.shape[1] == K and x.stride(1) == 1 and out.shape == (T, I2 // 2)
     _call("vcb_gemm_bf16_swiglu", _p(w_gate_up), _p(x), _p(out), I2 // 2, T, K, w_gate_up.stride(0), x.stride(0),
           out.stride(0), int(shape), _p(status), _stream())
+
+
+def gemm_qkv_rope(w_qkv, x, q_out, pages, slot_map, positions, cos_sin, q_weight, k_weight, eps, nh, nkv, status,
+                  use_norm=True):
+    """The stacked q, k, v projection of a prompt portion with what :func:`qknorm_rope_kvwrite` does in its epilogue
+    (head_dim 128, the whole head rotated in half-split pairs): per-head norm of queries and keys, rotation, queries to
+    ``q_out`` [T, nh * 128], keys and values to the tokens' slots of ``pages`` (None: a layer that stores none; then
+    ``w_qkv`` holds the query rows only).  No k-slices, so for more than 128 tokens; 32-bit from the product's sums on."""
+    _need(w_qkv, "w_qkv", torch.bfloat16); _need(x, "x", torch.bfloat16, contiguous=False); _need(q_out, "q_out", torch.bfloat16)
+    _need(cos_sin, "cos_sin", torch.float32); _need(positions, "positions", torch.int32)
+    M, K = w_qkv.shape
+    T = x.shape[0]
+    assert x.shape[1] == K and x.stride(1) == 1 and q_out.shape == (T, nh * 128) and cos_sin.shape[1] == 128
+    page_stride = page_size = num_pages = 0
+    if pages is not None:
+        _need(pages, "pages", torch.bfloat16); _need(slot_map, "slot_map", torch.int32)
+        num_pages, two, nkv_p, page_size, hd_p = pages.shape
+        assert two == 2 and nkv_p == nkv and hd_p == 128 and M == (nh + 2 * nkv) * 128
+        page_stride = pages.stride(0)
+    else:
+        assert M == nh * 128
+    wdt = F32
+    if use_norm:
+        _need(q_weight, "q_norm weight")
+        wdt = _dt(q_weight)
+        if pages is not None:
+            _need(k_weight, "k_norm weight", q_weight.dtype)
+    _call("vcb_gemm_bf16_qkv", _p(w_qkv), _p(x), T, K, w_qkv.stride(0), x.stride(0), _p(q_out), _p(pages), page_stride,
+          page_size, num_pages, _p(slot_map), _p(positions), _p(cos_sin), cos_sin.shape[0], _p(q_weight), _p(k_weight), wdt,
+          int(use_norm), float(eps), nh, nkv, _p(status), _stream())
 
 
 def sgemm_tn(a, b, out):

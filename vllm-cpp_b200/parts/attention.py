@@ -23,7 +23,7 @@ from .. import ops, workspace
 from ..registry import PartSpec, part_class
 from ..weights.loader import TensorSpec
 from .base import CacheSpec, Mixer
-from .linear import matmul_tn
+from .linear import choose_splits, matmul_tn
 
 DECODE_ROWS = 8     # rows a block of the decode variant of the plain attention kernel holds
 SPAN_ROWS = 32      # rows of its prompt-portion variant
@@ -44,6 +44,13 @@ FUSED_DECODE = int(os.environ.get("VLLM_CPP_B200_ATTN_FUSED_DECODE", "1"))
 # The blocks of a decoded token's key slices run as a thread-block cluster and merge their results through shared
 # memory (up to MAX_CLUSTER slices; more are merged by the last block through global memory).  0 switches it off.
 CLUSTER_MERGE = os.environ.get("VLLM_CPP_B200_ATTN_CLUSTER", "1") != "0"
+# Prompt portions of more than QKV_EPILOGUE_ABOVE tokens with head_dim 128 and whole-head half-split rotation: norm,
+# rotation and cache store in the q, k, v projection's epilogue (VLLM_CPP_B200_QKV_EPILOGUE=0 keeps the separate
+# kernel).  The epilogue of a block's last unit is not hidden behind a next one, so it pays from about 1,500 tokens on
+# (8B sizes, product and norm-rotate-store against the one kernel: 1,024 tokens 59.0 against 62.8 us, 1,536 70.0
+# against 66.5, 2,048 99.1 against 95.6, 3,072 144 against 125, 8,192 448 against 336).
+QKV_EPILOGUE = os.environ.get("VLLM_CPP_B200_QKV_EPILOGUE", "1") != "0"
+QKV_EPILOGUE_ABOVE = int(os.environ.get("VLLM_CPP_B200_QKV_EPILOGUE_ABOVE", "1280"))
 MAX_CLUSTER = 8
 MAX_CLUSTER_SHARED = 6
 
@@ -182,7 +189,13 @@ class GQAAttention(Mixer):
         T = x.shape[0]
         nh, nkv, hd = self.nh, self.nkv, self.hd
         group = ctx.groups[cache.group]
-        qkv = matmul_tn(x, self.w_qkv, ctx.status, allow_partials=True)
+        # Prompt portions whose projection needs no k-slices: the per-head norm, the rotation and the cache store run in
+        # the projection's epilogue (a unit of 128 features is one head), from its 32-bit sums.
+        in_epilogue = (QKV_EPILOGUE and x.dtype == torch.bfloat16 and hd == 128 and self.rotary_dim == hd and not self.interleaved
+                       and T > QKV_EPILOGUE_ABOVE and ops.gemm_tma_ok(x, self.w_qkv)
+                       and ops.gemm_effective_splits(x.shape[1], choose_splits(self.w_qkv.shape[0], T, x.shape[1])) == 1
+                       and (not self.has_kv or (cache.pages.dtype == torch.bfloat16 and cache.pages.is_contiguous())))
+        qkv = None if in_epilogue else matmul_tn(x, self.w_qkv, ctx.status, allow_partials=True)
         out = workspace.empty((T, nh * hd), x.dtype, x.device)
         mma = ops.attn_mma_supported(x.dtype, hd)
         kernel = ops.attn_mma if mma else ops.attn_paged
@@ -192,7 +205,7 @@ class GQAAttention(Mixer):
         common = dict(nh=nh, nkv=nkv, hd=hd, window=self.window, status=ctx.status, table_row=ctx.slots)
         # A step of single tokens only, run kernel by kernel: the attention kernel norms, rotates and stores for itself,
         # straight from the projection's k-slice partial sums (one launch less in every layer).
-        if ((FUSED_DECODE == 2 or (FUSED_DECODE == 1 and not getattr(ctx, "static", False))) and mma and plan.decode_only and self.has_kv and qkv.dim() == 3 and nh // nkv <= MMA_DECODE_ROWS
+        if (qkv is not None and (FUSED_DECODE == 2 or (FUSED_DECODE == 1 and not getattr(ctx, "static", False))) and mma and plan.decode_only and self.has_kv and qkv.dim() == 3 and nh // nkv <= MMA_DECODE_ROWS
                 and self.rotary_dim == hd and not self.interleaved
                 and ops.attn_mma_fused_supported(x.dtype, hd, cache.pages.shape[3])):
             S = plan.nslices
@@ -208,10 +221,14 @@ class GQAAttention(Mixer):
                                       cluster=cluster, **common)
             return matmul_tn(out, self.w_o, ctx.status, out_dtype=torch.float32, allow_partials=True)
         q = workspace.empty((T, nh * hd), x.dtype, x.device)
-        ops.qknorm_rope_kvwrite(qkv, self.q_norm_w, self.k_norm_w, self.eps, self.rope.table, ctx.positions,
-                                group.slot_map, q, cache.pages, nh, nkv, hd, ctx.status,
-                                has_kv=self.has_kv, use_norm=self.qk_norm, rotary_dim=self.rotary_dim,
-                                interleaved=self.interleaved)
+        if in_epilogue:
+            ops.gemm_qkv_rope(self.w_qkv, x, q, cache.pages if self.has_kv else None, group.slot_map, ctx.positions,
+                              self.rope.table, self.q_norm_w, self.k_norm_w, self.eps, nh, nkv, ctx.status, use_norm=self.qk_norm)
+        else:
+            ops.qknorm_rope_kvwrite(qkv, self.q_norm_w, self.k_norm_w, self.eps, self.rope.table, ctx.positions,
+                                    group.slot_map, q, cache.pages, nh, nkv, hd, ctx.status,
+                                    has_kv=self.has_kv, use_norm=self.qk_norm, rotary_dim=self.rotary_dim,
+                                    interleaved=self.interleaved)
         if plan.n_dec:
             S = plan.nslices
             cluster = plan.cluster if mma else 0
