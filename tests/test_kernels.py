@@ -176,14 +176,25 @@ def test_qknorm_rope_kvwrite(dtype, nh, nkv, hd):
             assert pages[s // ps, :, :, s % ps].abs().max().item() == 0
 
 
+@pytest.mark.parametrize("pairs", [1, 2])
 @pytest.mark.parametrize("nh,nkv,T,K,norm,kv", [(4, 2, 300, 192, True, True), (5, 1, 129, 64, True, True), (3, 3, 521, 320, False, True),
                                                 (32, 8, 1024, 256, True, True), (6, 2, 200, 128, True, False)])
-def test_qkv_projection_with_norm_rotation_and_store_in_its_epilogue(nh, nkv, T, K, norm, kv):
+def test_qkv_projection_with_norm_rotation_and_store_in_its_epilogue(nh, nkv, T, K, norm, kv, pairs):
     """gemm_qkv_rope (prompt portions, head_dim 128): the stacked projection whose epilogue norms each query and key
     head, rotates it and stores queries, keys and values -- against 64-bit arithmetic on the same bfloat16 operands,
     and against the two kernels it replaces.  Token counts that end inside a unit and inside a chunk of 32, a token
     that stores nowhere, positions all over the table, pages in any order; with and without the norms; a layer that
-    stores no keys (query rows only)."""
+    stores no keys (query rows only).  pairs 2: on pairs of blocks wherever they take the sizes (an odd number of heads
+    leaves the second block of the last pair without one)."""
+    from vllm_cpp_b200 import ops
+    ops.gemm_set_pairs(pairs)
+    try:
+        _qkv_projection_case(nh, nkv, T, K, norm, kv)
+    finally:
+        ops.gemm_set_pairs(1)
+
+
+def _qkv_projection_case(nh, nkv, T, K, norm, kv):
     from vllm_cpp_b200 import ops
     hd, ps, eps, max_pos = 128, 16, 1e-6, 700
     torch.manual_seed(nh * 7 + T)

@@ -548,7 +548,9 @@ struct SmemPair {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
     static constexpr int NUM_BARS = 2 * STAGES + 4;
-    static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;
+    static constexpr int EPI_OFFSET = (BAR_OFFSET + NUM_BARS * 8 + 16 + 15) / 16 * 16;    // as in Smem: the q, k, v epilogue's exchange
+    static constexpr int EPI_BYTES = (128 * 33 + 4 * 32 + 4 * 32) * 4;
+    static constexpr int TOTAL = EPI_OFFSET + EPI_BYTES + 1024;
 };
 
 template <int STAGES>
@@ -691,6 +693,20 @@ __global__ __launch_bounds__(NTHREADS, 1) void gemm_bf16_tn_pair_kernel(const __
                 for (int b = 0; b < CHUNK / 16; ++b)
                     tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + c0 + 16 * b), v[b]);
                 tc_wait_ld();
+                if (g.qe.q_out != nullptr) {     // uniform over the block: every warp takes part in the barriers
+                    float* stage = reinterpret_cast<float*>(gen + L::EPI_OFFSET);
+                    const int head = m0 / BM + (int)rank;
+                    if (head * BM < g.M) {
+#pragma unroll
+                        for (int hh = 0; hh < CHUNK / 32; ++hh) {
+                            float x[32];
+#pragma unroll
+                            for (int t = 0; t < 32; ++t) x[t] = __uint_as_float(v[(32 * hh + t) / 16][(32 * hh + t) % 16]);
+                            qkv_head_store(x, g.qe, head, q * 32 + lane, q, lane, n0 + c0 + 32 * hh, g.N, stage, g.status);
+                        }
+                    }
+                    continue;
+                }
                 if (g.swiglu) {
                     swiglu_store<CHUNK>(v, reinterpret_cast<__nv_bfloat16*>(g.out), g.ldc, m, g.M, n0 + c0, g.N, lane);
                 } else if (m < g.M) {
@@ -1039,6 +1055,8 @@ VCB_API int vcb_gemm_bf16_qkv(const void* W, const void* X, int N, int K, long l
     // units of one head: 128 features x 256 tokens, or x 128 where those fill the SMs' rounds better (as pick_shape counts)
     auto rounds = [&](int bn) { return (((long long)(M / BM) * ((N + bn - 1) / bn) + num_sms() - 1) / num_sms()) * bn; };
     const bool narrow = N <= 128 || rounds(128) * 8 / 5 < rounds(256);
+    // pairs of blocks as for a plain product of these sizes (mode 2, tests: wherever they can run)
+    if ((!narrow || pairs_mode() == 2) && use_pairs(M, N, K, 1)) return launch_pair(W, M, X, g, ldw, ldx, stream);
     return narrow ? launch<128, 6, 1, 2>(W, X, g, ldw, ldx, 1, stream) : launch<256, 4, 1, 2>(W, X, g, ldw, ldx, 1, stream);
 }
 

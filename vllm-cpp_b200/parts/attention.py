@@ -47,8 +47,8 @@ CLUSTER_MERGE = os.environ.get("VLLM_CPP_B200_ATTN_CLUSTER", "1") != "0"
 # Prompt portions of more than QKV_EPILOGUE_ABOVE tokens with head_dim 128 and whole-head half-split rotation: norm,
 # rotation and cache store in the q, k, v projection's epilogue (VLLM_CPP_B200_QKV_EPILOGUE=0 keeps the separate
 # kernel).  The epilogue of a block's last unit is not hidden behind a next one, so it pays from about 1,500 tokens on
-# (8B sizes, product and norm-rotate-store against the one kernel: 1,024 tokens 59.0 against 62.8 us, 1,536 70.0
-# against 66.5, 2,048 99.1 against 95.6, 3,072 144 against 125, 8,192 448 against 336).
+# (8B sizes, product and norm-rotate-store against the one kernel: 1,024 tokens 60.2 against 62.9 us, 1,536 71.8
+# against 63.6, 2,048 100.4 against 94.4, 3,072 142 against 118, 8,192 437 against 326).
 QKV_EPILOGUE = os.environ.get("VLLM_CPP_B200_QKV_EPILOGUE", "1") != "0"
 QKV_EPILOGUE_ABOVE = int(os.environ.get("VLLM_CPP_B200_QKV_EPILOGUE_ABOVE", "1280"))
 MAX_CLUSTER = 8
