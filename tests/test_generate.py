@@ -315,3 +315,19 @@ def test_nothing_is_finalised_while_a_step_is_captured(model_dirs, plain_models)
     gc.collect()
     assert gone() is None
     assert got == [plain_generate(plain_models, "A", p, 8) for p in prompts]
+
+
+def test_warm_up_captures_the_decoding_steps_beforehand(model_dirs, plain_models):
+    """LLM.warm_up captures the decoding steps of every padded batch size up to max_num_seqs for the given sampling
+    options; the run after it captures none of them again and gives the plain implementation's tokens."""
+    prompts = [random_tokens(256, n, 1 + i) for i, n in enumerate((5, 11, 17))]
+    llm = make_llm(model_dirs["A"], "A")
+    made = llm.warm_up(0.0, 1.0, 1.0)
+    assert made == 3 and llm.warm_up(0.0, 1.0, 1.0) == 0            # batch sizes 1, 2, 4 for max_num_seqs 4
+    decoding = {k for k in llm.runner._graphs if isinstance(k[0], int)}
+    assert {k[0] for k in decoding} == {1, 2, 4}
+    got = llm.generate(prompts, 8, 0.0, 1.0, repeat_penalty=1.0)
+    assert {k for k in llm.runner._graphs if isinstance(k[0], int)} == decoding     # replayed, none made anew
+    assert got == [plain_generate(plain_models, "A", p, 8) for p in prompts]
+    # other sampling options are other steps; batch sizes can be named
+    assert llm.warm_up(0.8, 0.9, 1.1, batch_sizes=[3]) == 1

@@ -169,15 +169,7 @@ class LLM:
         if penalised:
             user += Sampler.token_slots(entries, penalised)
         counting = bool(penalised)
-
-        def post(ctx, logits):
-            if counting:
-                self.sampler.observe(ctx.token_ids, ctx.user[8 * rows_pad:8 * rows_pad + ctx.T], ctx.T)
-            if logits is None:
-                return None
-            return self.sampler.sample_records(logits, ctx.user[:8 * logits.shape[0]].view(-1, 8), use_counts, no_nucleus)
-
-        toks = self.runner.step(entries, check=False, user=user, post=post,
+        toks = self.runner.step(entries, check=False, user=user, post=self._sampling_after(rows_pad, counting, use_counts, no_nucleus),
                                 post_key=("sample", counting, use_counts, no_nucleus))
         tokens: list[int] = []
         if sampled_entries:
@@ -195,6 +187,45 @@ class LLM:
             out.new_token_ids.append(by_request[e.request])
             out.finished.append(e.request in finished)
         return out
+
+    def _sampling_after(self, rows_pad: int, counting: bool, use_counts: bool, no_nucleus: bool):
+        """What a step runs on its own stream right after the model: the occurrence counts of the step's tokens where a
+        request has a repetition penalty, then one sampled token per row of logits.  (A captured step includes it.)"""
+        def post(ctx, logits):
+            if counting:
+                self.sampler.observe(ctx.token_ids, ctx.user[8 * rows_pad:8 * rows_pad + ctx.T], ctx.T)
+            if logits is None:
+                return None
+            return self.sampler.sample_records(logits, ctx.user[:8 * logits.shape[0]].view(-1, 8), use_counts, no_nucleus)
+        return post
+
+    def warm_up(self, temperature: float = TEMPERATURE, top_p: float = TOP_P, repeat_penalty: float = REPEAT_PENALTY,
+                batch_sizes=None) -> int:
+        """Captures the decoding steps that requests with these sampling options will replay, before any request is
+        there: one per padded batch size up to ``max_num_seqs`` (or those that ``batch_sizes`` round up to), for
+        contexts of the short class.  Without it a run captures each such step when it first meets the size, 0.1 to
+        0.2 s each at serving sizes, in the middle of serving.  Returns the number of steps captured now."""
+        runner = self.runner
+        if not runner.cuda_graphs:
+            return 0
+        options = SamplingOptions(temperature, top_p, repeat_penalty, 0)
+        _, use_counts, no_nucleus = Sampler.records([options], [0], [0])
+        counting = repeat_penalty not in (0.0, 1.0)
+        if counting:
+            self.sampler._need_counts()
+        post_key = ("sample", counting, use_counts, no_nucleus)
+        limit = next((b for b in runner.GRAPH_BUCKETS if b >= self.engine_config.max_num_seqs), runner.GRAPH_BUCKETS[-1])
+        if batch_sizes is None:
+            buckets = [b for b in runner.GRAPH_BUCKETS if b <= limit]
+        else:
+            buckets = sorted({next((b for b in runner.GRAPH_BUCKETS if b >= n), None) for n in batch_sizes} - {None})
+        made = 0
+        for bucket in buckets:
+            key = (bucket, post_key, runner.GRAPH_CONTEXT_BOUNDS[0])
+            if key not in runner._graphs and len(runner._graphs) < runner.MAX_GRAPHS:
+                runner._capture(key, self._sampling_after(bucket, counting, use_counts, no_nucleus))
+                made += 1
+        return made
 
     def _readback(self, toks: torch.Tensor) -> list[int]:
         """The sampled tokens and the status word in one pinned buffer, one synchronisation."""
