@@ -106,6 +106,35 @@ def test_bfloat16_greedy_mostly_agrees(model_dirs, plain_models):
     assert first == 3 and agree >= 36, (got, want)
 
 
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_bfloat16_generation_on_the_tensor_core_kernels(name, model_dirs, plain_models):
+    """Six requests on the configurations with head sizes 64 and 128 in bfloat16: prompt portions of 64 tokens
+    through the tcgen05 attention kernel beside decoded tokens through the mma.sync one, captured steps.  Greedy
+    tokens of a bfloat16 engine may leave the plain implementation's at a near tie, so each chosen token is judged
+    where it was chosen: the plain implementation's logits over the engine's own sequence must hold that token
+    within the bfloat16 tolerance of their largest, and most tokens must be the plain implementation's choice."""
+    import plain_qwen3
+    cfg, w = plain_models[name]
+    vocab, top = cfg["vocab_size"], cfg["max_position_embeddings"]
+    lengths = (3, 40, 64, 97, 130, 150)
+    prompts = [random_tokens(vocab, n, 500 + i) for i, n in enumerate(lengths)]
+    llm = make_llm(model_dirs[name], name, dtype="bfloat16", max_tokens=2048, max_num_seqs=6, max_step_tokens=64)
+    got = llm.generate(prompts, 24, 0.0, 1.0, repeat_penalty=1.0, ignore_eos=True)
+    assert llm.runner.graph_replays > 20
+    same = total = 0
+    for p, g in zip(prompts, got):
+        assert len(g) == 24 and len(p) + 24 <= top
+        logits = plain_qwen3.forward(cfg, w, p + g[:-1])[len(p) - 1:]
+        assert logits.shape[0] == 24
+        scale = float(logits.abs().max())
+        for t, tok in enumerate(g):
+            best = float(logits[t].max())
+            assert float(logits[t, tok]) >= best - 3e-2 * scale, (len(p), t, tok, int(logits[t].argmax()))
+            same += int(logits[t].argmax()) == tok
+            total += 1
+    assert same >= 0.9 * total, (same, total)
+
+
 def test_preemption_recomputes_to_the_same_tokens(model_dirs, plain_models):
     """A pool too small for all requests at their full length: the youngest is preempted, recomputed
     later, and every request still produces the tokens it produces alone."""
