@@ -119,7 +119,7 @@ class _Ctx:
 def bench_attention(dev, status):
     hbm, tc = peaks()
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
-    for B, ctx_len in ((1, 4096), (8, 4096), (64, 4096), (64, 512), (256, 128)):
+    for B, ctx_len in ((1, 4096), (8, 4096), (64, 4096), (32, 2048), (64, 512), (128, 256), (256, 128), (256, 1024)):
         npages = B * (ctx_len // PAGE + 1)
         pages = torch.randn(npages, 2, NKV, PAGE, HD, device=dev).to(torch.bfloat16)
         bt = torch.arange(npages, dtype=torch.int32, device=dev).view(B, -1)
@@ -136,7 +136,13 @@ def bench_attention(dev, status):
                                            NH, NKV, HD, 0, status, slice_counters=plan.slice_counters if S > 1 else None,
                                            dec_rows=plan.dec_rows, cluster=plan.cluster))
         kv_bytes = B * ctx_len * 2 * NKV * HD * 2
-        print(f"decode attention  batch {B:3d} context {ctx_len:5d} key slices {S:2d}{' in clusters' if plan.cluster else ''}: {us:7.1f} us   at HBM peak {kv_bytes / hbm / 1e3:6.1f}", flush=True)
+        walk = ""
+        if B * NKV > ops.num_sms() and ops.attn_stream_supported(torch.bfloat16, HD, PAGE, NH, NKV):
+            one = A.AttentionPlan(c, NH, NKV, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+            items = one.dec_items if one.nslices == 1 else i32([[e, 0, 1, 0, 1, e] for e in range(B)])
+            us_w = timeit(lambda k: ops.attn_stream(q, out, pages, bt, ql, cl, items, B, one.dec_rows, NH, NKV, HD, 0, status))
+            walk = f"   on blocks that walk the pairs {us_w:7.1f} us"
+        print(f"decode attention  batch {B:3d} context {ctx_len:5d} key slices {S:2d}{' in clusters' if plan.cluster else ''}: {us:7.1f} us{walk}   at HBM peak {kv_bytes / hbm / 1e3:6.1f}", flush=True)
         del pages
     for T in (2048, 8192):
         npages = T // PAGE

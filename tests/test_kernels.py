@@ -438,6 +438,52 @@ def test_attention_mixed_batch(dtype, nh, nkv, hd, ps):
     run_attention(dtype, nh, nkv, hd, ps, 0, [(0, 7), (31, 1), (0, 1), (13, 34), (63, 2), (200, 1), (16, 16)])
 
 
+@pytest.mark.parametrize("nh,nkv,hd,ps,window,blocks", [(32, 8, 128, 16, 0, 0), (8, 2, 128, 16, 0, 3), (4, 1, 64, 8, 0, 2),
+                                                        (6, 2, 64, 32, 40, 3), (16, 1, 128, 64, 100, 1), (10, 2, 64, 16, 0, 5)])
+def test_attention_of_many_decoded_tokens_on_persistent_blocks(nh, nkv, hd, ps, window, blocks):
+    """attn_stream (blocks that walk the (token, KV head) pairs, the loading warp running ahead from pair to pair)
+    against 64-bit attention: 75 single tokens whose contexts end at every place of a page and reach from one key to
+    forty pages, empty entries in between (their rows stay untouched), so few blocks that each takes more than one
+    batch of 32 pairs, every pair's first keys from its description and the later ones from page ids read ahead."""
+    from vllm_cpp_b200 import ops
+    assert ops.attn_stream_supported(torch.bfloat16, hd, ps, nh, nkv)
+    torch.manual_seed(nh + hd + ps)
+    dtype = torch.bfloat16
+    rng = np.random.default_rng(hd + ps)
+    ctxs = [1, 2, ps - 1, ps, ps + 1, 63, 64, 65, 127, 128, 129, 8 * ps, 8 * ps + 1, 40 * ps - 3, 700] + rng.integers(1, 400, 60).tolist()
+    empty = {4, 17, 40}                                   # entries without a token this step
+    B = len(ctxs)
+    seqs = [(torch.randn(c, nkv, hd, dtype=torch.float64).to(dtype).double(),
+             torch.randn(c, nkv, hd, dtype=torch.float64).to(dtype).double()) for c in ctxs]
+    num_pages = sum(-(-c // ps) for c in ctxs) + 3
+    pages, tables = build_paged(seqs, nkv, hd, ps, dtype, num_pages)
+    mb = max(len(t) for t in tables)
+    bt = torch.full((B, mb), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        bt[i, :len(t)] = torch.tensor(t)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())
+    q = torch.randn(B, nh, hd, dtype=torch.float64).to(dtype)
+    q_flat = q.to(dev()).view(B, nh * hd)
+    out = torch.full_like(q_flat, float("nan"))
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    items = np.zeros((B, ops.ITEM_INTS), dtype=np.int32)
+    for n in range(B):
+        items[n] = (n, 0, 1, 0, 1, n)
+    q_len = [0 if e in empty else 1 for e in range(B)]
+    for _ in range(2):      # twice: nothing is left behind by a launch
+        ops.attn_stream(q_flat, out, pages, bt.to(dev()), i32(q_len), i32(ctxs), i32(items), B, i32(list(range(B))),
+                        nh, nkv, hd, window, status, blocks=blocks)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    got = out.double().cpu().view(B, nh, hd)
+    for e, (c, (k, v)) in enumerate(zip(ctxs, seqs)):
+        if e in empty:
+            assert torch.isnan(got[e]).all()
+            continue
+        want = attention_reference(q[e:e + 1].double(), k, v, c - 1, window)
+        torch.testing.assert_close(got[e:e + 1], want, **tol(dtype))
+
+
 @pytest.mark.parametrize("nh,nkv,hd,ps,window,S,norm", [(8, 2, 128, 16, 0, 3, True), (4, 1, 64, 8, 0, 1, True), (32, 8, 128, 16, 0, 4, True),
                                                        (6, 2, 64, 32, 40, 2, True), (16, 1, 128, 64, 100, 5, False)])
 def test_attention_of_decoded_tokens_straight_from_the_projection(nh, nkv, hd, ps, window, S, norm):

@@ -70,6 +70,21 @@ def test_replay_with_norm_rotation_and_store_in_the_projection(mode, model_dirs,
     print(f"D bfloat16 {mode}, projection epilogue: worst relative error {worst:.3e}")
 
 
+@pytest.mark.parametrize("name", ["C", "D"])
+@pytest.mark.parametrize("mode", ["tail", "mixed"])
+def test_replay_with_decoded_tokens_on_persistent_attention_blocks(name, mode, model_dirs, plain_logits, tmp_path):
+    """Head sizes 64 (one layer with a window) and 128 in bfloat16 with every step's single tokens on the attention
+    kernel whose blocks walk the (token, KV head) pairs (serving takes it for more pairs than resident blocks): the
+    last 32 tokens decoded one by one, and the mixed trace in which pages are used again, over a NaN-filled cache,
+    against the plain implementation."""
+    requests = make_requests(name)
+    trace = {"tail": R.tail_one_by_one, "mixed": R.mixed}[mode](requests)
+    out = R.run_trace(model_dirs[name], "bfloat16", trace, tmp_path / "out", TINY_PAGE[name], extra_args=["--poison"],
+                      extra_env={"VLLM_CPP_B200_ATTN_STREAM": "2"})
+    worst = compare(name, "bfloat16", trace, out, requests, plain_logits)
+    print(f"{name} bfloat16 {mode}, single tokens on persistent attention blocks: worst relative error {worst:.3e}")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_replay_modes_agree_with_each_other(dtype, model_dirs, tmp_path):
     """Cutting and batching change the logits by rounding only (far below the distance to the reference)."""

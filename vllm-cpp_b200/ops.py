@@ -80,6 +80,8 @@ def _declare(L):
                                       I, I, I, I, F, P, I, P],
         "vcb_attn_tc": [P, P, P, LL, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, P, P, P],
         "vcb_attn_tc_supported": [I, I, I],
+        "vcb_attn_stream": [P, P, P, LL, P, P, I, P, P, P, I, P, I, I, I, I, I, I, F, P, I, P],
+        "vcb_attn_stream_supported": [I, I, I, I, I],
         "vcb_attn_merge": [P, P, P, P, I, I, I, I, I, P],
         "vcb_sample": [P, LL, I, I, P, P, P, P],
         "vcb_sample_split": [P, LL, I, I, P, P, P, P, I, P, P],
@@ -528,6 +530,29 @@ def attn_mma(q, out, pages, block_table, q_start, q_len, ctx_len, items, n_items
           1.0 / math.sqrt(hd), _p(status), int(allow_tma), int(cluster), _stream())
 
 
+def attn_stream_supported(dtype: torch.dtype, hd: int, page_size: int, nh: int, nkv: int) -> bool:
+    """Whether :func:`attn_stream` takes these sizes (bfloat16, head_dim 64 or 128, pages of 8 to 64 tokens, at
+    most 16 query heads a KV head)."""
+    return bool(lib().vcb_attn_stream_supported(BF16 if dtype == torch.bfloat16 else F32, hd, page_size, nh, nkv))
+
+
+def attn_stream(q, out, pages, block_table, q_len, ctx_len, items, n_dec, dec_rows, nh, nkv, hd, window, status,
+                table_row=None, blocks=0):
+    """Single decoded tokens, many of them: persistent blocks walk the (token, KV head) pairs, all keys of a pair in
+    one block, the loading warp running ahead from pair to pair.  ``items`` [n_dec, 6] as for :func:`attn_mma` with
+    one slice; ``dec_rows`` [n_dec] the tokens' rows of ``q`` and ``out``; entries with q_len 0 are skipped.
+    ``blocks``: how many blocks to run on (0: two an SM, or one where the head group is large)."""
+    _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(pages, "pages", torch.bfloat16)
+    for name, t in (("block_table", block_table), ("q_len", q_len), ("ctx_len", ctx_len), ("items", items),
+                    ("dec_rows", dec_rows)):
+        _need(t, name, torch.int32)
+    num_pages, two, nkv_p, page_size, hd_p = pages.shape
+    assert two == 2 and nkv_p == nkv and hd_p == hd
+    _call("vcb_attn_stream", _p(q), _p(out), _p(pages), pages.stride(0), _p(block_table), _p(table_row),
+          block_table.shape[1], _p(q_len), _p(ctx_len), _p(items), n_dec, _p(dec_rows), nh, nkv, hd, page_size,
+          num_pages, int(window or 0), 1.0 / math.sqrt(hd), _p(status), int(blocks), _stream())
+
+
 # --------------------------------------------------------------------------  a look at a step from inside
 _timeline = None
 _TL_ROLE_EVERY, _TL_ROLE_BLOCKS, _TL_ROLES, _TL_ROLE_MARKS = 37, 8, 3, 2048     # as in kernels/common.cuh
@@ -545,7 +570,7 @@ def timeline_begin(capacity: int = 1 << 18) -> None:
     _timeline = torch.zeros(2 + 4 * capacity + _TL_ROLE_WORDS, dtype=torch.int64, device="cuda")
     _timeline[1] = capacity
     torch.cuda.synchronize()
-    for unit in ("gemm", "attn_mma", "attn_tc", "elementwise"):
+    for unit in ("gemm", "attn_mma", "attn_tc", "attn_stream", "elementwise"):
         fn = getattr(L, f"vcb_timeline_set_{unit}")
         fn.argtypes, fn.restype = [c_void_p], c_int
         if fn(_timeline.data_ptr()) != 0:
@@ -559,7 +584,7 @@ def timeline_end():
     global _timeline
     L = lib()
     torch.cuda.synchronize()
-    for unit in ("gemm", "attn_mma", "attn_tc", "elementwise"):
+    for unit in ("gemm", "attn_mma", "attn_tc", "attn_stream", "elementwise"):
         getattr(L, f"vcb_timeline_set_{unit}")(None)
     buf = _timeline.cpu().numpy()
     _timeline = None

@@ -53,15 +53,23 @@ QKV_EPILOGUE = os.environ.get("VLLM_CPP_B200_QKV_EPILOGUE", "1") != "0"
 QKV_EPILOGUE_ABOVE = int(os.environ.get("VLLM_CPP_B200_QKV_EPILOGUE_ABOVE", "1280"))
 MAX_CLUSTER = 8
 MAX_CLUSTER_SHARED = 6
+# Steps with more (decoded token, KV head) pairs than the decode kernel has resident blocks: persistent blocks walk the
+# pairs, their loading warp running ahead from one pair into the next (ops.attn_stream), instead of a block a pair
+# that lives for one round trip to memory.  Kernel alone, 8B sizes: 256 tokens over 128 keys 47.3 -> 27.4 us (their
+# keys take 20.5 at the copy bandwidth), 128 over 256 36.3 -> 26.2, 64 over 512 28.6 -> 25.6, 256 over 1,024
+# 171 -> 156; with a pair a block or fewer it gains nothing (32 tokens over 2,048 keys: 42.2 against 43.2).
+# VLLM_CPP_B200_ATTN_STREAM=0 keeps a block a pair; 2 sends every step's single tokens this way, one slice each (tests).
+STREAM_DECODE = int(os.environ.get("VLLM_CPP_B200_ATTN_STREAM", "1"))
 
 
 class AttentionPlan:
     """Work items of the attention kernel for one step and one head layout, on the device."""
 
     def __init__(self, ctx, nh: int, nkv: int, decode_rows: int = DECODE_ROWS, span_rows: int = SPAN_ROWS,
-                 cluster_hd: int | None = None):
+                 cluster_hd: int | None = None, one_slice: bool = False):
         """``cluster_hd``: the head size, when the kernel that takes the decoded tokens can merge a token's key slices
-        within a cluster of its blocks (then the slices are chosen so that all clusters run at once); else None."""
+        within a cluster of its blocks (then the slices are chosen so that all clusters run at once); else None.
+        ``one_slice``: no key slices, whatever the contexts."""
         g = nh // nkv
         dev = ctx.device
         # int32 arrays go to the device with the step's own staging buffers where the step has them
@@ -90,7 +98,7 @@ class AttentionPlan:
             fit = BLOCKS_PER_SM * ops.num_sms() // blocks
             if longest is not None and longest <= SHORT_CONTEXT:
                 fit = min(fit, SHORT_SLICES)
-            self.nslices = int(max(1, min(MAX_SLICES, by_pages, fit)))
+            self.nslices = 1 if one_slice else int(max(1, min(MAX_SLICES, by_pages, fit)))
             if cluster_hd is not None and longest is not None and longest <= SHORT_CONTEXT and self.nslices > 1:
                 # Over short contexts the slices of a token are a cluster that merges through shared memory, which
                 # saves the merge's trip through global memory (3 to 6 us a layer) -- if all the clusters run at
@@ -201,11 +209,17 @@ class GQAAttention(Mixer):
         kernel = ops.attn_mma if mma else ops.attn_paged
         dec_rows, span_rows = (MMA_DECODE_ROWS, MMA_SPAN_ROWS) if mma else (DECODE_ROWS, SPAN_ROWS)
         clustered = hd if mma and CLUSTER_MERGE and torch.cuda.is_available() else None
-        plan = ctx.plan(("attention", nh, nkv, mma, clustered), lambda: AttentionPlan(ctx, nh, nkv, dec_rows, span_rows, clustered))
+        always_stream = STREAM_DECODE == 2 and mma and ops.attn_stream_supported(x.dtype, hd, cache.pages.shape[3], nh, nkv)
+        plan = ctx.plan(("attention", nh, nkv, mma, clustered, always_stream),
+                        lambda: AttentionPlan(ctx, nh, nkv, dec_rows, span_rows, clustered, one_slice=always_stream))
         common = dict(nh=nh, nkv=nkv, hd=hd, window=self.window, status=ctx.status, table_row=ctx.slots)
+        # many single tokens: more (token, KV head) pairs than blocks that are resident at once
+        stream = bool(plan.n_dec) and (always_stream or (
+            STREAM_DECODE and mma and plan.nslices == 1 and plan.n_dec * nkv > BLOCKS_PER_SM * ops.num_sms()
+            and ops.attn_stream_supported(x.dtype, hd, cache.pages.shape[3], nh, nkv)))
         # A step of single tokens only, run kernel by kernel: the attention kernel norms, rotates and stores for itself,
         # straight from the projection's k-slice partial sums (one launch less in every layer).
-        if (qkv is not None and (FUSED_DECODE == 2 or (FUSED_DECODE == 1 and not getattr(ctx, "static", False))) and mma and plan.decode_only and self.has_kv and qkv.dim() == 3 and nh // nkv <= MMA_DECODE_ROWS
+        if (not stream and qkv is not None and (FUSED_DECODE == 2 or (FUSED_DECODE == 1 and not getattr(ctx, "static", False))) and mma and plan.decode_only and self.has_kv and qkv.dim() == 3 and nh // nkv <= MMA_DECODE_ROWS
                 and self.rotary_dim == hd and not self.interleaved
                 and ops.attn_mma_fused_supported(x.dtype, hd, cache.pages.shape[3])):
             S = plan.nslices
@@ -229,7 +243,10 @@ class GQAAttention(Mixer):
                                     group.slot_map, q, cache.pages, nh, nkv, hd, ctx.status,
                                     has_kv=self.has_kv, use_norm=self.qk_norm, rotary_dim=self.rotary_dim,
                                     interleaved=self.interleaved)
-        if plan.n_dec:
+        if stream:
+            ops.attn_stream(q, out, cache.pages, group.block_table, ctx.q_len, ctx.ctx_len, plan.dec_items, plan.n_dec,
+                            plan.dec_rows, **common)
+        elif plan.n_dec:
             S = plan.nslices
             cluster = plan.cluster if mma else 0
             part_o = part_ml = None
