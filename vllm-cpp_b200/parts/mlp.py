@@ -11,9 +11,16 @@ import torch
 from .. import ops, workspace
 from ..weights.loader import TensorSpec
 from .base import FeedForward
-from .linear import matmul_tn
+import os
 
-FUSE_ABOVE_TOKENS = 128   # below this the product is cut into k-slices, whose sums must exist before the SiLU
+from .linear import choose_splits, matmul_tn
+
+# The SiLU-gate runs in the gate-and-up product's epilogue when that product is not cut into k-slices (whose sums must
+# exist before the SiLU): always where its units fill the SMs anyway (the 14B sizes, 272 feature tiles: 8 tokens
+# 58.6 -> 56.5 us, 64 tokens 67.6 -> 60.1 against product and SiLU-gate kernel), and above this many tokens, from where
+# the one kernel without slices is as fast as the two with them (8B sizes, 64 tokens: 45.8 against 45.7 us; 128: 51.1
+# against 52.8; 32: 44.0 against 40.8) and the step has a kernel boundary less.
+FUSE_ABOVE_TOKENS = int(os.environ.get("VLLM_CPP_B200_SWIGLU_FUSE_ABOVE", "63"))
 
 
 class SwiGLUMLP(FeedForward):
@@ -39,8 +46,10 @@ class SwiGLUMLP(FeedForward):
 
     def forward(self, x, ctx):
         act = workspace.empty((x.shape[0], self.inter), x.dtype, x.device)
-        if x.dtype == torch.bfloat16 and x.shape[0] > FUSE_ABOVE_TOKENS and ops.gemm_tma_ok(x, self.w_gate_up):
-            # many tokens: no k-slices are needed, so the SiLU-gate runs in the product's epilogue
+        T, K = x.shape
+        if x.dtype == torch.bfloat16 and ops.gemm_tma_ok(x, self.w_gate_up) and (
+                T > FUSE_ABOVE_TOKENS or ops.gemm_effective_splits(K, choose_splits(self.w_gate_up.shape[0], T, K)) == 1):
+            # no k-slices are needed, or they no longer pay: the SiLU-gate runs in the product's epilogue
             ops.gemm_bf16_swiglu(self.w_gate_up, x, act, ctx.status)
         else:
             gate_up = matmul_tn(x, self.w_gate_up, ctx.status, allow_partials=True)
