@@ -104,3 +104,19 @@ def test_key_slices_that_merge_in_clusters_are_chosen_so_that_all_clusters_run_a
     monkeypatch.setattr(A.ops, "attn_mma_max_clusters", lambda hd, size, deep: -1)
     p = plan(1)
     assert (p.nslices, p.cluster) == (A.SHORT_SLICES, 0)
+
+
+def test_many_single_tokens_go_to_the_blocks_that_walk_the_pairs(monkeypatch):
+    """More (token, KV head) pairs than resident blocks, no key slices, and short contexts: known in a step that runs
+    kernel by kernel, implied by the number of pairs in a captured one."""
+    monkeypatch.setattr(A.ops, "num_sms", lambda: 148)
+    plan = lambda n, c, **kw: A.AttentionPlan(ctx([1] * n, [c] * n, **kw), 32, 8, A.MMA_DECODE_ROWS, A.MMA_SPAN_ROWS)
+    assert A.stream_pays(plan(64, 512), 8) and A.stream_pays(plan(256, 128), 8) and A.stream_pays(plan(40, 2048), 8)
+    assert not A.stream_pays(plan(64, 4096), 8)          # long contexts: a block a pair is as fast and ends raggedly
+    assert not A.stream_pays(plan(32, 512), 8)           # 256 pairs: a block each is resident at once
+    assert not A.stream_pays(plan(64, 512), 2)           # 128 pairs
+    assert plan(64, 512).longest == 512 and plan(64, 0, static=True, bound=8192).longest is None
+    assert A.stream_pays(plan(256, 0, static=True, bound=8192), 8)
+    assert not A.stream_pays(plan(64, 0, static=True, bound=8192), 8) and not A.stream_pays(plan(128, 0, static=True, bound=8192), 8)
+    monkeypatch.setattr(A, "STREAM_DECODE", 0)
+    assert not A.stream_pays(plan(256, 128), 8)

@@ -8,8 +8,8 @@
 // for 256 requests of 128 keys.  Here a block walks (token, KV head) pairs, blockIdx.x, + gridDim.x, ..., and its
 // loading warp runs ahead of the four multiplying warps across the pairs: it reads what describes the next 32 pairs
 // (one lane a pair: lengths, the block-table row, the first page ids) while the present ones are streamed, and keeps
-// the ring of K and V tiles full from one pair into the next, the pair's query rows riding on its first tile's
-// barrier.  The multiplying warps split each tile's 64 keys four ways, as in attention_mma.cu, and merge their
+// the ring of K and V tiles full from one pair into the next, the pair's query rows in a ring of their own.  Tiles
+// that hold only keys of earlier steps are asked for before the wait for the kernel that writes this step's.  The multiplying warps split each tile's 64 keys four ways, as in attention_mma.cu, and merge their
 // partial results through shared memory once per pair.  No key slices: this form is for launches with more pairs
 // than blocks.
 //
@@ -99,7 +99,7 @@ __global__ __launch_bounds__(NW * 32 + 32) void attn_stream_kernel(const __grid_
     uint8_t* smem = smem_raw + (base_u32 - smem_u32(smem_raw));
     uint8_t* k_s = smem;                                   // STAGES tiles
     uint8_t* v_s = k_s + STAGES * TILE_BYTES;              // STAGES tiles
-    uint8_t* q_s = v_s + STAGES * TILE_BYTES;              // STAGES x g query rows, then one row of zeros
+    uint8_t* q_s = v_s + STAGES * TILE_BYTES;              // STAGES x g query rows (slot: the pair's number modulo STAGES), then one row of zeros
     uint8_t* zero_s = q_s + STAGES * g * QROWB;
     float* o_s = reinterpret_cast<float*>(zero_s + QROWB);  // [NW][g][HD]: the warps' partial results of a pair
     float* ml_s = o_s + NW * g * HD;                       // [NW][g][2]
@@ -111,7 +111,8 @@ __global__ __launch_bounds__(NW * 32 + 32) void attn_stream_kernel(const __grid_
     auto meta_empty = [&](int p) { return smem_u32(bar_s) + 8u * (2 * STAGES + 2 + p); };
     const uint32_t merge_full = smem_u32(bar_s) + 8u * (2 * STAGES + 4);    // the four warps' partial results are written
     const uint32_t merge_empty = smem_u32(bar_s) + 8u * (2 * STAGES + 5);   // and read
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_s + 8 * (2 * STAGES + 6));
+    auto q_bar = [&](int slot) { return smem_u32(bar_s) + 8u * (2 * STAGES + 6 + slot); };   // a pair's query rows are there
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_s + 8 * (3 * STAGES + 6));
 
     pdl_trigger();
     tl_mark(VCB_TL_ATTN_DEC, 0);
@@ -127,6 +128,7 @@ __global__ __launch_bounds__(NW * 32 + 32) void attn_stream_kernel(const __grid_
         for (int st = 0; st < STAGES; ++st) {
             mbar_init(full_bar(st), 1);
             mbar_init(empty_bar(st), NW);      // one arrival per multiplying warp
+            mbar_init(q_bar(st), 1);
         }
         for (int p = 0; p < 2; ++p) {
             mbar_init(meta_full(p), 1);
@@ -183,10 +185,42 @@ __global__ __launch_bounds__(NW * 32 + 32) void attn_stream_kernel(const __grid_
             __syncwarp();
             if (lane == 0) mbar_arrive(meta_full(0));
         }
+        const int my_pg = lane >> 1, my_v = lane & 1;
+        // asks for the K and V pages of tile t of the pair described by m into stage st; `page`: this lane's page id
+        auto issue_kv = [&](const int* m, int t, int st, int page) {
+            const int pb0 = m[M_PB_LO] + t * pages_per_tile;
+            const int np = min(pages_per_tile, m[M_PB_HI] - pb0);
+            if (lane == 0) mbar_expect_tx(full_bar(st), (uint32_t)(np * ps * ROWB * 2));
+            __syncwarp();
+            if (my_pg < np) {
+                if (page < 0 || page >= a.num_pages) {
+                    atomicOr(a.status, VCB_STATUS_BAD_PAGE);
+                    page = 0;   // keep the byte count whole; the status word reports the fault
+                }
+                const int groups_page = ps / 8;
+                const int group = (page * 2 * a.nkv + m[M_KVH]) * groups_page + (my_v ? a.nkv * groups_page : 0);
+                const uint32_t dst = smem_u32((my_v ? v_s : k_s) + st * TILE_BYTES) + my_pg * ps * ROWB;
+                tma_load_groups(dst, &kv_map, full_bar(st), group);
+            }
+        };
+        // Before the wait: the first tiles of the first batch as far as they hold keys of earlier steps only (their
+        // page ids are in the descriptions), a ring's worth at most.
+        int early = 0;
+        for (int i = 0; i < min(BATCH, mine) && early < STAGES; ++i) {
+            const int* m = meta_s + i * META_INTS;
+            const int n_tiles = m[M_TILES];
+            bool stop = false;
+            for (int t = 0; t < n_tiles && early < STAGES; ++t) {
+                const int end = min(m[M_PB_HI], m[M_PB_LO] + (t + 1) * pages_per_tile) * ps;
+                if (t >= pre_tiles || end > m[M_K_END] - 1) { stop = true; break; }
+                issue_kv(m, t, early, my_pg < pages_per_tile ? m[M_HEAD + t * pages_per_tile + my_pg] : -1);
+                ++early;
+            }
+            if (stop) break;
+        }
         pdl_wait();          // the queries and the newest keys come from the kernel before this one
         tl_mark(VCB_TL_ATTN_DEC, 1);
-        int it = 0, armed = 0;      // tiles of this block so far
-        const int my_pg = lane >> 1, my_v = lane & 1;
+        int it = 0, armed = early, pseq = 0;      // tiles and pairs (with keys) of this block so far
         for (int j = 0; j < batches && ok; ++j) {
             const int in_batch = min(BATCH, mine - j * BATCH);
             for (int i = 0; i < in_batch && ok; ++i) {
@@ -214,38 +248,35 @@ __global__ __launch_bounds__(NW * 32 + 32) void attn_stream_kernel(const __grid_
                 for (int k = 0; k < AHEAD; ++k) ahead_page[k] = n_tiles > pre_tiles ? page_of(pre_tiles + k) : -1;
                 for (int t = 0; t < n_tiles; ++t, ++it) {
                     const int st = it % STAGES;
-                    if (lane == 0) ok = mbar_wait(empty_bar(st), ((it / STAGES) & 1) ^ 1u, abort_flag, a.status);
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
-                    if (!ok) break;
-                    const int pb0 = pb_lo + t * pages_per_tile;
-                    const int np = min(pages_per_tile, pb_hi - pb0);
-                    if (lane == 0) mbar_expect_tx(full_bar(st), (uint32_t)(np * ps * ROWB * 2 + (t == 0 ? g * ROWB : 0)));
-                    __syncwarp();
-                    int page;
-                    if (t < pre_tiles) {
-                        page = my_pg < pages_per_tile ? m[M_HEAD + t * pages_per_tile + my_pg] : -1;
-                    } else {
-                        page = ahead_page[0];
+                    if (it >= early) {      // (the tiles asked for before the wait are on their way)
+                        if (lane == 0) ok = mbar_wait(empty_bar(st), ((it / STAGES) & 1) ^ 1u, abort_flag, a.status);
+                        ok = __shfl_sync(0xffffffffu, ok, 0);
+                        if (!ok) break;
+                        int page;
+                        if (t < pre_tiles) {
+                            page = my_pg < pages_per_tile ? m[M_HEAD + t * pages_per_tile + my_pg] : -1;
+                        } else {
+                            page = ahead_page[0];
 #pragma unroll
-                        for (int k = 0; k + 1 < AHEAD; ++k) ahead_page[k] = ahead_page[k + 1];
-                        ahead_page[AHEAD - 1] = page_of(t + AHEAD);
-                    }
-                    if (my_pg < np) {
-                        if (page < 0 || page >= a.num_pages) {
-                            atomicOr(a.status, VCB_STATUS_BAD_PAGE);
-                            page = 0;   // keep the byte count whole; the status word reports the fault
+                            for (int k = 0; k + 1 < AHEAD; ++k) ahead_page[k] = ahead_page[k + 1];
+                            ahead_page[AHEAD - 1] = page_of(t + AHEAD);
                         }
-                        const int groups_page = ps / 8;
-                        const int group = (page * 2 * a.nkv + kvh) * groups_page + (my_v ? a.nkv * groups_page : 0);
-                        const uint32_t dst = smem_u32((my_v ? v_s : k_s) + st * TILE_BYTES) + my_pg * ps * ROWB;
-                        tma_load_groups(dst, &kv_map, full_bar(st), group);
+                        issue_kv(m, t, st, page);
+                        armed = it + 1;
                     }
-                    if (t == 0 && lane < g) {
-                        // the pair's query rows arrive with its first tile
-                        const __nv_bfloat16* src = a.q + ((size_t)m[M_ROW] * a.nh + (size_t)kvh * g + lane) * HD;
-                        bulk_load(smem_u32(q_s + (st * g + lane) * QROWB), src, ROWB, full_bar(st));
+                    if (t == 0) {
+                        // The pair's query rows, into the slot of the pair's number: the pair that had it before is
+                        // STAGES pairs back, so its first tile, before whose release its rows were read, is at least
+                        // STAGES tiles back and released, or this tile's stage would not be free.
+                        const int slot = pseq % STAGES;
+                        if (lane == 0) mbar_expect_tx(q_bar(slot), (uint32_t)(g * ROWB));
+                        __syncwarp();
+                        if (lane < g) {
+                            const __nv_bfloat16* src = a.q + ((size_t)m[M_ROW] * a.nh + (size_t)kvh * g + lane) * HD;
+                            bulk_load(smem_u32(q_s + (slot * g + lane) * QROWB), src, ROWB, q_bar(slot));
+                        }
+                        ++pseq;
                     }
-                    armed = it + 1;
                 }
             }
         }
@@ -253,6 +284,10 @@ __global__ __launch_bounds__(NW * 32 + 32) void attn_stream_kernel(const __grid_
             for (int i = max(0, armed - STAGES); i < armed; ++i) {
                 const long long t0 = clock64();
                 while (!mbar_try(full_bar(i % STAGES), (i / STAGES) & 1) && clock64() - t0 < VCB_WAIT_CLOCKS) {}
+            }
+            for (int i = max(0, pseq - STAGES); i < pseq; ++i) {
+                const long long t0 = clock64();
+                while (!mbar_try(q_bar(i % STAGES), (i / STAGES) & 1) && clock64() - t0 < VCB_WAIT_CLOCKS) {}
             }
         }
     } else {
@@ -284,8 +319,11 @@ __global__ __launch_bounds__(NW * 32 + 32) void attn_stream_kernel(const __grid_
                     const int t0 = t_first + t * BN;
                     if (t == 0) {
                         // query fragments stay in registers for the pair; rows beyond its heads read the row of zeros
+                        const int slot = done % STAGES;
+                        ok = mbar_wait(q_bar(slot), (done / STAGES) & 1, abort_flag, a.status);
+                        if (!ok) break;
                         const int r = lane & 15;
-                        const uint32_t row = r < g ? smem_u32(q_s + (st * g + r) * QROWB) : smem_u32(zero_s);
+                        const uint32_t row = r < g ? smem_u32(q_s + (slot * g + r) * QROWB) : smem_u32(zero_s);
 #pragma unroll
                         for (int ks = 0; ks < HD / 16; ++ks) ldmatrix_x4(qf[ks], row + (r < g ? (ks * 2 + (lane >> 4)) * 16 : 0));
                     }
@@ -441,7 +479,7 @@ __global__ __launch_bounds__(NW * 32 + 32) void attn_stream_kernel(const __grid_
 size_t stream_smem(int hd, int g, int stages) {
     const size_t tile = (size_t)BN * hd * 2, qrow = (size_t)hd * 2 + 16;
     return 2 * stages * tile + (size_t)stages * g * qrow + qrow + (size_t)NW * g * (hd + 2) * 4 +
-           2 * (size_t)BATCH * META_INTS * 4 + 8 * (2 * (size_t)stages + 6) + 16 + 1024;
+           2 * (size_t)BATCH * META_INTS * 4 + 8 * (3 * (size_t)stages + 6) + 16 + 1024;
 }
 
 int sm_count() {

@@ -58,8 +58,15 @@ MAX_CLUSTER_SHARED = 6
 # that lives for one round trip to memory.  Kernel alone, 8B sizes: 256 tokens over 128 keys 47.3 -> 27.4 us (their
 # keys take 20.5 at the copy bandwidth), 128 over 256 36.3 -> 26.2, 64 over 512 28.6 -> 25.6, 256 over 1,024
 # 171 -> 156; with a pair a block or fewer it gains nothing (32 tokens over 2,048 keys: 42.2 against 43.2).
+# Over long contexts the two forms take the same time alone (64 tokens over 4,096 keys: 157 us), but in the step the
+# persistent one is 2 % behind (10.03 -> 10.25 ms): its blocks all end together, so the output projection's blocks are
+# not resident, with their first weights on the way, before the attention is over.  So it is taken where the longest
+# context is known to be at most STREAM_MAX_CONTEXT, and in captured steps, which serve any context of their class,
+# from STREAM_STATIC_PAIRS pairs on, which no pool holds at long contexts.
 # VLLM_CPP_B200_ATTN_STREAM=0 keeps a block a pair; 2 sends every step's single tokens this way, one slice each (tests).
 STREAM_DECODE = int(os.environ.get("VLLM_CPP_B200_ATTN_STREAM", "1"))
+STREAM_MAX_CONTEXT = 2048
+STREAM_STATIC_PAIRS = 1184
 
 
 class AttentionPlan:
@@ -79,6 +86,7 @@ class AttentionPlan:
         self.n_dec = len(dec)
         self.decode_only = bool(dec) and not spans     # every entry of the step is one decoded token (or empty)
         self.nslices = 1
+        self.longest = None   # the longest context among the single tokens, where the step knows it
         self.cluster = 0      # > 1: a token's key slices are a cluster of that many blocks
         self.dec_items = self.dec_rows = self.span_items = None
         self.n_span_items = 0
@@ -90,7 +98,7 @@ class AttentionPlan:
                 longest = getattr(ctx, "static_max_ctx", None)
                 by_pages = MAX_SLICES if longest is None else max(1, longest // 128)
             else:
-                longest = max(ctx.host_ctx_len[i] for i in dec)
+                longest = self.longest = max(ctx.host_ctx_len[i] for i in dec)
                 by_pages = max(1, longest // 128)   # at least 128 keys a slice
             # as many slices as keep every block resident in one wave; over short contexts no more than
             # SHORT_SLICES, beyond which merging the partial results costs more than the shorter key ranges save
@@ -135,6 +143,15 @@ class AttentionPlan:
             self.span_items = upload(np.asarray(rows, dtype=np.int32).reshape(-1, ops.ITEM_INTS))
             # the queue that the tensor-core kernel's blocks take their work from (left at zero by every launch)
             self.span_work = workspace.zeros((2,), torch.int32, dev)
+
+
+def stream_pays(plan: AttentionPlan, nkv: int) -> bool:
+    """Whether a step's single tokens go to the kernel whose persistent blocks walk the (token, KV head) pairs: more
+    pairs than resident blocks, no key slices, and short contexts (known, or implied by the number of pairs)."""
+    pairs = plan.n_dec * nkv
+    if not STREAM_DECODE or plan.nslices != 1 or pairs <= BLOCKS_PER_SM * ops.num_sms():
+        return False
+    return plan.longest <= STREAM_MAX_CONTEXT if plan.longest is not None else pairs >= STREAM_STATIC_PAIRS
 
 
 class GQAAttention(Mixer):
@@ -215,8 +232,7 @@ class GQAAttention(Mixer):
         common = dict(nh=nh, nkv=nkv, hd=hd, window=self.window, status=ctx.status, table_row=ctx.slots)
         # many single tokens: more (token, KV head) pairs than blocks that are resident at once
         stream = bool(plan.n_dec) and (always_stream or (
-            STREAM_DECODE and mma and plan.nslices == 1 and plan.n_dec * nkv > BLOCKS_PER_SM * ops.num_sms()
-            and ops.attn_stream_supported(x.dtype, hd, cache.pages.shape[3], nh, nkv)))
+            mma and stream_pays(plan, nkv) and ops.attn_stream_supported(x.dtype, hd, cache.pages.shape[3], nh, nkv)))
         # A step of single tokens only, run kernel by kernel: the attention kernel norms, rotates and stores for itself,
         # straight from the projection's k-slice partial sums (one launch less in every layer).
         if (not stream and qkv is not None and (FUSED_DECODE == 2 or (FUSED_DECODE == 1 and not getattr(ctx, "static", False))) and mma and plan.decode_only and self.has_kv and qkv.dim() == 3 and nh // nkv <= MMA_DECODE_ROWS
