@@ -61,7 +61,7 @@ def _declare(L):
         "vcb_swiglu": [P, I, I, LL, P, I, I, I, P],
         "vcb_qknorm_rope_kvwrite": [P, I, I, LL, I, P, P, I, I, F, P, I, P, P, P, P, LL, I, I, I, I, I, I, I, I, I, P, P],
         "vcb_gemm_bf16_tn": [P, P, P, I, I, I, I, LL, LL, LL, I, LL, P, P],
-        "vcb_gemm_bf16_tn_shape": [P, P, P, I, I, I, I, LL, LL, LL, I, LL, I, P, P],
+        "vcb_gemm_bf16_tn_shape": [P, P, P, I, I, I, I, LL, LL, LL, I, LL, I, I, P, P],
         "vcb_gemm_effective_splits": [I, I],
         "vcb_gemm_set_pairs": [I],
         "vcb_gemm_bf16_swiglu": [P, P, P, I, I, I, LL, LL, LL, I, P, P],
@@ -284,10 +284,12 @@ def gemm_set_pairs(mode: int) -> None:
     lib().vcb_gemm_set_pairs(int(mode))
 
 
-def gemm_bf16_tn(w, x, out, splits, status, shape=-1):
+def gemm_bf16_tn(w, x, out, splits, status, shape=-1, after_small_kernel=False):
     """out[z, t, m] = sum over k-slice z of w[m, k] x[t, k]   (tcgen05 + TMA; w [M,K], x [T,K] bfloat16).
     out: [T, M] (bfloat16 or float32, one slice) or [S, T, M] float32 with S = gemm_effective_splits(K, splits).
-    ``shape`` forces one of GEMM_SHAPES (an index) whatever the sizes; -1 lets the kernel choose."""
+    ``shape`` forces one of GEMM_SHAPES (an index) whatever the sizes; -1 lets the kernel choose.
+    ``after_small_kernel``: the kernel before this one in the stream is a short one (a norm, the SiLU-gate): a decode
+    product then asks further weight tiles into L2 while it waits for it (VLLM_CPP_B200_GEMM_PREFETCH)."""
     _need(w, "w", torch.bfloat16, contiguous=False); _need(x, "x", torch.bfloat16, contiguous=False); _need(out, "out")
     M, K = w.shape
     T = x.shape[0]
@@ -300,7 +302,7 @@ def gemm_bf16_tn(w, x, out, splits, status, shape=-1):
         assert out.shape == (S, T, M) and out.dtype == torch.float32
         ldc, sstride = out.stride(1), out.stride(0)
     _call("vcb_gemm_bf16_tn_shape", _p(w), _p(x), _p(out), _dt(out), M, T, K, w.stride(0), x.stride(0), ldc, S, sstride,
-          int(shape), _p(status), _stream())
+          int(shape), int(bool(after_small_kernel)), _p(status), _stream())
 
 
 def gemm_bf16_swiglu(w_gate_up, x, out, status, shape=-1):

@@ -220,7 +220,8 @@ class GQAAttention(Mixer):
                        and T > QKV_EPILOGUE_ABOVE and ops.gemm_tma_ok(x, self.w_qkv)
                        and ops.gemm_effective_splits(x.shape[1], choose_splits(self.w_qkv.shape[0], T, x.shape[1])) == 1
                        and (not self.has_kv or (cache.pages.dtype == torch.bfloat16 and cache.pages.is_contiguous())))
-        qkv = None if in_epilogue else matmul_tn(x, self.w_qkv, ctx.status, allow_partials=True)
+        # (the mixer's input comes from a norm: a short kernel)
+        qkv = None if in_epilogue else matmul_tn(x, self.w_qkv, ctx.status, allow_partials=True, after_small_kernel=True)
         out = workspace.empty((T, nh * hd), x.dtype, x.device)
         mma = ops.attn_mma_supported(x.dtype, hd)
         kernel = ops.attn_mma if mma else ops.attn_paged

@@ -69,9 +69,10 @@ def choose_splits(M: int, T: int, K: int, max_splits: int = 8, num_sms: int | No
 
 
 def matmul_tn(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor | None = None, *, out_dtype=None,
-              allow_partials: bool = False) -> torch.Tensor:
+              allow_partials: bool = False, after_small_kernel: bool = False) -> torch.Tensor:
     """x [T,K], w [N,K] -> [T,N] in ``out_dtype`` (default: x's dtype).  With ``allow_partials`` the result may
-    come back as [S,T,N] 32-bit partial sums, which the caller's next kernel adds."""
+    come back as [S,T,N] 32-bit partial sums, which the caller's next kernel adds.  ``after_small_kernel``: what made
+    ``x`` was a short kernel (see ops.gemm_bf16_tn)."""
     out_dtype = out_dtype or x.dtype
     T, N = x.shape[0], w.shape[0]
     if x.dtype == torch.float32:
@@ -94,5 +95,5 @@ def matmul_tn(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor | None = No
         out = workspace.empty((splits, T, N), torch.float32, x.device)
     else:
         out = workspace.empty((T, N), out_dtype, x.device)
-    ops.gemm_bf16_tn(w, x, out, splits, status)
+    ops.gemm_bf16_tn(w, x, out, splits, status, after_small_kernel=after_small_kernel)
     return out

@@ -52,6 +52,7 @@ class SwiGLUMLP(FeedForward):
             # no k-slices are needed, or they no longer pay: the SiLU-gate runs in the product's epilogue
             ops.gemm_bf16_swiglu(self.w_gate_up, x, act, ctx.status)
         else:
-            gate_up = matmul_tn(x, self.w_gate_up, ctx.status, allow_partials=True)
+            gate_up = matmul_tn(x, self.w_gate_up, ctx.status, allow_partials=True, after_small_kernel=True)   # (after a norm)
             ops.swiglu(gate_up, act)
+            return matmul_tn(act, self.w_down, ctx.status, out_dtype=torch.float32, allow_partials=True, after_small_kernel=True)
         return matmul_tn(act, self.w_down, ctx.status, out_dtype=torch.float32, allow_partials=True)
