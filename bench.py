@@ -315,6 +315,28 @@ def run_headline(args, pk, clocks, windows):
 
 
 # ------------------------------------------------------------------------------------------------ 14B: long prompts, then decode
+class GcPauses:
+    """Seconds the Python collector ran inside a timed region (its pauses are the host's, so they belong to the
+    end-to-end numbers; reported so that a slow run can be told from a slow engine)."""
+
+    def __enter__(self):
+        import gc
+        self.total, self.count, self._t = 0.0, 0, 0.0
+        gc.callbacks.append(self._cb)
+        return self
+
+    def _cb(self, phase, info):
+        if phase == "start":
+            self._t = time.perf_counter()
+        else:
+            self.total += time.perf_counter() - self._t
+            self.count += 1
+
+    def __exit__(self, *exc):
+        import gc
+        gc.callbacks.remove(self._cb)
+
+
 def run_14b(args, pk, clocks, windows):
     """8 prompts of 8,192 tokens in portions of 2,048, then 256 greedy tokens each, through LLM.step()."""
     import numpy as np
@@ -336,18 +358,19 @@ def run_14b(args, pk, clocks, windows):
     t0 = time.perf_counter()
     prefill_steps, decode_s, first_decode = 0, [], None
     flops = 0.0
-    while llm.has_requests():
-        t1 = time.perf_counter()
-        o = llm.step()
-        dt = time.perf_counter() - t1
-        if o.num_prompt_tokens:
-            prefill_steps += 1
-        else:
-            if first_decode is None:
-                torch.cuda.synchronize()
-                first_decode = t1
-            decode_s.append(dt)
-    torch.cuda.synchronize()
+    with GcPauses() as pauses:
+        while llm.has_requests():
+            t1 = time.perf_counter()
+            o = llm.step()
+            dt = time.perf_counter() - t1
+            if o.num_prompt_tokens:
+                prefill_steps += 1
+            else:
+                if first_decode is None:
+                    torch.cuda.synchronize()
+                    first_decode = t1
+                decode_s.append(dt)
+        torch.cuda.synchronize()
     windows[-1][1] = clocks.mark()
     prefill_s = first_decode - t0
     for _ in range(B):     # each prompt: four portions of 2,048 over what came before
@@ -360,7 +383,8 @@ def run_14b(args, pk, clocks, windows):
            "prefill_frac_of_sustained": flops / prefill_s / (pk["bf16_tflops_sustained"] * 1e12),
            "decode_tokens_per_s": B * 1000.0 / ms, "decode_ms_per_step": ms, "decode_steps": len(decode_s),
            "decode_roofline_frac": nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"],
-           "preemptions": llm.stats().preemptions, "through": "LLM.step() and the scheduler, host tokens in and out"}
+           "preemptions": llm.stats().preemptions, "python_gc_s": round(pauses.total, 4), "python_gc_runs": pauses.count,
+           "through": "LLM.step() and the scheduler, host tokens in and out"}
     del llm
     release()
     return out

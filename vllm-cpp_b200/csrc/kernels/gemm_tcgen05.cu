@@ -1072,15 +1072,17 @@ VCB_API int vcb_gemm_bf16_tn_shape(const void* W, const void* X, void* out, int 
 
 // Fused feed-forward front half.  W [2I, K] holds gate_i in row 2i and up_i in row 2i+1; out[t][i] =
 // silu(gate_i . x_t) * (up_i . x_t), bfloat16 [N, I].  The pairing is done in the epilogue (adjacent TMEM lanes),
-// so every unit shape serves; shape < 0 chooses as for a plain product of 2I features.
+// so every unit shape serves; shape < 0 chooses as for a plain product of 2I features; flags as for
+// vcb_gemm_bf16_tn_shape.
 VCB_API int vcb_gemm_bf16_swiglu(const void* W, const void* X, void* out, int I, int N, int K, long long ldw,
-                                 long long ldx, long long ldc, int shape, int* status, cudaStream_t stream) {
+                                 long long ldx, long long ldc, int shape, int flags, int* status, cudaStream_t stream) {
     VCB_CHECK_ARG(I > 0 && N > 0 && K > 0, "gemm_bf16_swiglu: bad sizes I=%d N=%d K=%d", I, N, K);
     VCB_CHECK_ARG(K % 8 == 0 && ldw % 8 == 0 && ldx % 8 == 0,
                   "gemm_bf16_swiglu: inner size %d and row strides %lld, %lld must be multiples of 8 (16-byte rows for TMA)", K, ldw, ldx);
     VCB_CHECK_ARG(((uintptr_t)W % 16 == 0) && ((uintptr_t)X % 16 == 0), "gemm_bf16_swiglu: operands must be 16-byte aligned");
     const int total_kb = (K + BK - 1) / BK;
     GemmArgs g{out, VCB_BF16, 2 * I, N, K, ldc, 0, total_kb, 1, 1, status};
+    if ((flags & VCB_GEMM_AFTER_SMALL_KERNEL) && N <= 16 && vcb_pdl_enabled()) pf_settings(&g.pf_tiles, &g.pf_delay_ns);
     if (shape < 0 && use_pairs(2 * I, N, K, 1)) return launch_pair(W, 2LL * I, X, g, ldw, ldx, stream);
     return launch_shape(shape < 0 ? pick_shape(2 * I, N, K, 1) : shape, W, X, g, ldw, ldx, 1, stream);
 }

@@ -64,7 +64,7 @@ def _declare(L):
         "vcb_gemm_bf16_tn_shape": [P, P, P, I, I, I, I, LL, LL, LL, I, LL, I, I, P, P],
         "vcb_gemm_effective_splits": [I, I],
         "vcb_gemm_set_pairs": [I],
-        "vcb_gemm_bf16_swiglu": [P, P, P, I, I, I, LL, LL, LL, I, P, P],
+        "vcb_gemm_bf16_swiglu": [P, P, P, I, I, I, LL, LL, LL, I, I, P, P],
         "vcb_gemm_bf16_qkv": [P, P, I, I, LL, LL, P, P, LL, I, I, P, P, P, I, P, P, I, I, F, I, I, P, P],
         "vcb_sgemm_tn": [P, P, P, I, I, I, LL, LL, LL, P],
         "vcb_gemm_bf16_plain": [P, P, P, I, I, I, I, LL, LL, LL, P],
@@ -305,17 +305,17 @@ def gemm_bf16_tn(w, x, out, splits, status, shape=-1, after_small_kernel=False):
           int(shape), int(bool(after_small_kernel)), _p(status), _stream())
 
 
-def gemm_bf16_swiglu(w_gate_up, x, out, status, shape=-1):
+def gemm_bf16_swiglu(w_gate_up, x, out, status, shape=-1, after_small_kernel=False):
     """out[t, i] = silu(gate_i . x_t) * (up_i . x_t) with gate_i in row 2i and up_i in row 2i+1 of w_gate_up: the
     product and the SiLU-gate in one kernel (adjacent accumulator lanes are paired in the epilogue).
-    ``shape`` as in gemm_bf16_tn."""
+    ``shape`` and ``after_small_kernel`` as in gemm_bf16_tn."""
     _need(w_gate_up, "w_gate_up", torch.bfloat16); _need(x, "x", torch.bfloat16, contiguous=False)
     _need(out, "out", torch.bfloat16)
     I2, K = w_gate_up.shape
     T = x.shape[0]
     assert I2 % 2 == 0 and x.shape[1] == K and x.stride(1) == 1 and out.shape == (T, I2 // 2)
     _call("vcb_gemm_bf16_swiglu", _p(w_gate_up), _p(x), _p(out), I2 // 2, T, K, w_gate_up.stride(0), x.stride(0),
-          out.stride(0), int(shape), _p(status), _stream())
+          out.stride(0), int(shape), int(bool(after_small_kernel)), _p(status), _stream())
 
 
 def gemm_qkv_rope(w_qkv, x, q_out, pages, slot_map, positions, cos_sin, q_weight, k_weight, eps, nh, nkv, status,

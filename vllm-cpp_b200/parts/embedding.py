@@ -85,4 +85,4 @@ class LMHead(Head):
             self.weight = store.matrix(self.name)
 
     def forward(self, y, status=None):
-        return matmul_tn(y, self.weight, status, out_dtype=torch.float32)
+        return matmul_tn(y, self.weight, status, out_dtype=torch.float32, after_small_kernel=True)   # (after the last norm)

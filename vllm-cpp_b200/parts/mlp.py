@@ -50,7 +50,7 @@ class SwiGLUMLP(FeedForward):
         if x.dtype == torch.bfloat16 and ops.gemm_tma_ok(x, self.w_gate_up) and (
                 T > FUSE_ABOVE_TOKENS or ops.gemm_effective_splits(K, choose_splits(self.w_gate_up.shape[0], T, K)) == 1):
             # no k-slices are needed, or they no longer pay: the SiLU-gate runs in the product's epilogue
-            ops.gemm_bf16_swiglu(self.w_gate_up, x, act, ctx.status)
+            ops.gemm_bf16_swiglu(self.w_gate_up, x, act, ctx.status, after_small_kernel=True)   # (after a norm)
         else:
             gate_up = matmul_tn(x, self.w_gate_up, ctx.status, allow_partials=True, after_small_kernel=True)   # (after a norm)
             ops.swiglu(gate_up, act)
