@@ -116,10 +116,12 @@ class _Ctx:
     pass
 
 
-def bench_attention(dev, status):
+def bench_attention(dev, status, only=None):
+    """``only``: one (requests, context) pair of decode attention instead of the list (and no prompt attention)."""
     hbm, tc = peaks()
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
-    for B, ctx_len in ((1, 4096), (8, 4096), (64, 4096), (32, 2048), (64, 512), (128, 256), (256, 128), (256, 1024)):
+    cases = ((1, 4096), (8, 4096), (64, 4096), (32, 2048), (64, 512), (128, 256), (256, 128), (256, 1024))
+    for B, ctx_len in ((only,) if only else cases):
         npages = B * (ctx_len // PAGE + 1)
         pages = torch.randn(npages, 2, NKV, PAGE, HD, device=dev).to(torch.bfloat16)
         bt = torch.arange(npages, dtype=torch.int32, device=dev).view(B, -1)
@@ -144,7 +146,7 @@ def bench_attention(dev, status):
             walk = f"   on blocks that walk the pairs {us_w:7.1f} us"
         print(f"decode attention  batch {B:3d} context {ctx_len:5d} key slices {S:2d}{' in clusters' if plan.cluster else ''}: {us:7.1f} us{walk}   at HBM peak {kv_bytes / hbm / 1e3:6.1f}", flush=True)
         del pages
-    for T in (2048, 8192):
+    for T in (() if only else (2048, 8192)):
         npages = T // PAGE
         pages = torch.randn(npages, 2, NKV, PAGE, HD, device=dev).to(torch.bfloat16)
         bt = torch.arange(npages, dtype=torch.int32, device=dev).view(1, -1)
@@ -305,8 +307,8 @@ def main(argv):
     ap.add_argument("--peaks", default=None, help="JSON file with hbm_gbs and bf16_tflops")
     ap.add_argument("--library", action="store_true", help="time the library's product (torch.mm) beside each of ours")
     ap.add_argument("--layers", type=int, default=12, help="timeline: layers of the model")
-    ap.add_argument("--batch", type=int, default=8, help="timeline: requests decoding")
-    ap.add_argument("--context", type=int, default=4096, help="timeline: tokens each request holds")
+    ap.add_argument("--batch", type=int, default=None, help="timeline: requests decoding (default 8); attention: with --context, that one case only")
+    ap.add_argument("--context", type=int, default=None, help="timeline: tokens each request holds (default 4096)")
     ap.add_argument("--first", type=int, default=18, help="timeline: first launch to print")
     ap.add_argument("--count", type=int, default=30, help="timeline: launches to print")
     ap.add_argument("what", nargs="?", default="gemm", choices=["gemm", "attention", "attention-roles", "small", "timeline"])
@@ -334,13 +336,13 @@ def main(argv):
     if what == "gemm":
         bench_gemm(args.tokens or [8, 64, 256, 2048], dev, status)
     elif what == "attention":
-        bench_attention(dev, status)
+        bench_attention(dev, status, (args.batch, args.context) if args.batch and args.context else None)
     elif what == "attention-roles":
         bench_attention_roles(dev, status, (args.tokens or [8192])[0])
     elif what == "small":
         bench_small(dev, status)
     elif what == "timeline":
-        bench_timeline(cfg, args.batch, args.context, args.layers, args.first, args.count)
+        bench_timeline(cfg, args.batch or 8, args.context or 4096, args.layers, args.first, args.count)
     else:
         print(__doc__)
         return 2
