@@ -265,7 +265,12 @@ VCB_API int vcb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, in
                      ((uintptr_t)resid % 16 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)out % 8 == 0) && H <= 16384;
     if (vec) {
         const int H4 = H / 4;
-        const int threads = H4 >= 1024 ? 1024 : ((H4 + 31) / 32) * 32;
+        int threads = H4 >= 1024 ? 1024 : ((H4 + 31) / 32) * 32;
+        // More rows than SMs: blocks of 1024 threads are resident one an SM (registers), so 256 rows of 4096 ran as
+        // two rounds of blocks (9 us in the step); with 512 threads and two float4s each, two are, and one round does.
+        static int sms = 0;
+        if (sms == 0 && (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0) != cudaSuccess || sms <= 0)) sms = 148;
+        if (n_out > sms && threads == 1024 && H4 <= 2048) threads = 512;
         const int vpt = (H4 + threads - 1) / threads;
         const float* d = (const float*)delta;
         __nv_bfloat16* o = (__nv_bfloat16*)out;

@@ -51,6 +51,11 @@ CLUSTER_MERGE = os.environ.get("VLLM_CPP_B200_ATTN_CLUSTER", "1") != "0"
 # against 63.6, 2,048 100.4 against 94.4, 3,072 142 against 118, 8,192 437 against 326).
 QKV_EPILOGUE = os.environ.get("VLLM_CPP_B200_QKV_EPILOGUE", "1") != "0"
 QKV_EPILOGUE_ABOVE = int(os.environ.get("VLLM_CPP_B200_QKV_EPILOGUE_ABOVE", "1280"))
+# From this many tokens on the epilogue also replaces a projection that would be cut into k-slices: the one kernel
+# without slices against the sliced product and the kernel that adds and norms its partial sums, 8B sizes at 256
+# tokens 28.8 against 29.4 us, 4B 23.7 against 26.6, 14B 33.0 against 37.9 (768 tokens: 64.8 against 93.3); below,
+# the slices win (144 tokens: 27.9 against 22.6).  A step of 256 single tokens: 8.27 -> 8.15 ms.
+QKV_EPILOGUE_FOR_SLICES_FROM = 256
 MAX_CLUSTER = 8
 MAX_CLUSTER_SHARED = 6
 # Steps with more (decoded token, KV head) pairs than the decode kernel has resident blocks: persistent blocks walk the
@@ -217,9 +222,11 @@ class GQAAttention(Mixer):
         # Prompt portions whose projection needs no k-slices: the per-head norm, the rotation and the cache store run in
         # the projection's epilogue (a unit of 128 features is one head), from its 32-bit sums.
         in_epilogue = (QKV_EPILOGUE and x.dtype == torch.bfloat16 and hd == 128 and self.rotary_dim == hd and not self.interleaved
-                       and T > QKV_EPILOGUE_ABOVE and ops.gemm_tma_ok(x, self.w_qkv)
-                       and ops.gemm_effective_splits(x.shape[1], choose_splits(self.w_qkv.shape[0], T, x.shape[1])) == 1
+                       and T > min(QKV_EPILOGUE_ABOVE, QKV_EPILOGUE_FOR_SLICES_FROM - 1) and ops.gemm_tma_ok(x, self.w_qkv)
                        and (not self.has_kv or (cache.pages.dtype == torch.bfloat16 and cache.pages.is_contiguous())))
+        if in_epilogue:
+            sliced = ops.gemm_effective_splits(x.shape[1], choose_splits(self.w_qkv.shape[0], T, x.shape[1])) > 1
+            in_epilogue = (T >= QKV_EPILOGUE_FOR_SLICES_FROM) if sliced else (T > QKV_EPILOGUE_ABOVE)
         # (the mixer's input comes from a norm: a short kernel)
         qkv = None if in_epilogue else matmul_tn(x, self.w_qkv, ctx.status, allow_partials=True, after_small_kernel=True)
         out = workspace.empty((T, nh * hd), x.dtype, x.device)
