@@ -827,7 +827,7 @@ def test_gemm_bf16_tn(M, T, K, splits, out_dtype):
         assert torch.equal(one[0], out[T - 1])
 
 
-@pytest.mark.parametrize("shape", range(8))
+@pytest.mark.parametrize("shape", range(9))
 @pytest.mark.parametrize("M,T,K,splits", [(300, 5, 200, 1), (520, 300, 1096, 1), (520, 300, 1096, 3), (128, 700, 64, 1)])
 def test_gemm_bf16_tn_every_unit_shape(shape, M, T, K, splits):
     """Each unit shape of the kernel, forced, at sizes that are not the ones it is chosen for: many token tiles
@@ -849,7 +849,7 @@ def test_gemm_bf16_tn_every_unit_shape(shape, M, T, K, splits):
     got = out.double().sum(0) if S > 1 else out.double()
     torch.testing.assert_close(got, x.double() @ w.double().T, rtol=1e-4, atol=K * 2.0 ** -24 * 64)
     with pytest.raises(ops.KernelError, match="no unit shape"):
-        ops.gemm_bf16_tn(w, x, out, splits, status, shape=8)
+        ops.gemm_bf16_tn(w, x, out, splits, status, shape=9)
 
 
 @pytest.mark.parametrize("M,T,K", [(256, 129, 64), (512, 300, 256), (1000, 700, 328), (6144, 512, 1024), (4096, 2048, 512),
@@ -1000,7 +1000,7 @@ def test_sampling_split_over_blocks_matches_plain():
 
 @pytest.mark.parametrize("I,T,K", [(128, 256, 64), (200, 300, 96), (12288 // 8, 2048, 512), (72, 130, 264), (264, 160, 128),
                                    (1024, 385, 64), (100, 7, 64)])
-@pytest.mark.parametrize("shape", [-1, 0, 2, 3, 4, 5, 6])
+@pytest.mark.parametrize("shape", [-1, 0, 2, 3, 4, 5, 6, 8])
 def test_gemm_bf16_swiglu(I, T, K, shape):
     """The product with the SiLU-gate in its epilogue against 64-bit, for the chosen and for forced unit shapes.
     Gate values reach far below -87, where silu is zero to every precision."""

@@ -972,7 +972,8 @@ VCB_API int vcb_gemm_effective_splits(int K, int splits) {
 }
 
 // The unit shapes that are built: tokens per tile (BN), stages of the ring, 128-feature tiles per unit, accumulators.
-enum GemmShape { SHAPE_N16 = 0, SHAPE_N32, SHAPE_N64, SHAPE_N128, SHAPE_N256, SHAPE_M256_N192, SHAPE_M256_N256, SHAPE_PAIR, SHAPE_COUNT };
+enum GemmShape { SHAPE_N16 = 0, SHAPE_N32, SHAPE_N64, SHAPE_N128, SHAPE_N256, SHAPE_M256_N192, SHAPE_M256_N256, SHAPE_PAIR, SHAPE_M256_N160,
+                 SHAPE_COUNT };
 
 namespace {
 int launch_shape(int shape, const void* W, const void* X, const GemmArgs& g, long long ldw, long long ldx, int splits,
@@ -984,6 +985,7 @@ int launch_shape(int shape, const void* W, const void* X, const GemmArgs& g, lon
         case SHAPE_N128: return launch<128, 6, 1, 2>(W, X, g, ldw, ldx, splits, stream);
         case SHAPE_N256: return launch<256, 4, 1, 2>(W, X, g, ldw, ldx, splits, stream);
         case SHAPE_M256_N192: return launch<192, 3, 2, 1>(W, X, g, ldw, ldx, splits, stream);
+        case SHAPE_M256_N160: return launch<160, 3, 2, 1>(W, X, g, ldw, ldx, splits, stream);
         case SHAPE_M256_N256: return launch<256, 3, 2, 1>(W, X, g, ldw, ldx, splits, stream);
         case SHAPE_PAIR:
             if (g.M < 2 * BM) { vcb_set_error("gemm_bf16_tn: pairs of blocks need at least 256 features"); return -1; }
@@ -1019,11 +1021,15 @@ int pick_shape(int M, int N, int K, int splits, long long* cost_out = nullptr) {
         return ((units + num_sms() - 1) / num_sms()) * (long long)(mt * bn);
     };
     const long long c1 = cost(1, 256), c2 = cost(2, 256), c3 = cost(2, 192);
+    // 256 x 160 units where they alone fill one round (2,560 features at 2,048 tokens: 130 units for 148 SMs, where
+    // 192-token units make 110 and 256-token units of 128 features make 160, two rounds)
+    const long long c4 = cost(2, 160);
     // 128 x 128 units draw more from L2 per flop: a k-block of theirs takes 0.29 us where one of 128 x 256 takes 0.36,
     // four fifths of the time for half the work.  They pay where they fill one round and 256-token units leave a
     // third of the SMs idle (qkv_proj at 384 tokens: 30.5 -> 24.5 us).
     const long long c0 = cost(1, 128) * 8 / 5;
-    if (cost_out) *cost_out = std::min(std::min(c0, c1), std::min(c2, c3));
+    if (cost_out) *cost_out = std::min(std::min(std::min(c0, c1), std::min(c2, c3)), c4);
+    if (c4 < c0 && c4 < c1 && c4 < c2 && c4 < c3) return SHAPE_M256_N160;
     if (c0 < c1 && c0 < c2 && c0 < c3) return SHAPE_N128;
     if (c1 == c2 && c2 <= c3 && K >= 8192) return SHAPE_M256_N256;
     if (c1 <= c2 && c1 <= c3) return SHAPE_N256;

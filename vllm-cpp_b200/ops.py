@@ -273,7 +273,7 @@ def gemm_effective_splits(K: int, splits: int) -> int:
     return -(-total_kb // per)
 
 
-GEMM_SHAPES = ("n16", "n32", "n64", "n128", "n256", "m256_n192", "m256_n256", "pair")   # unit shapes of the kernel, by index
+GEMM_SHAPES = ("n16", "n32", "n64", "n128", "n256", "m256_n192", "m256_n256", "pair", "m256_n160")   # unit shapes of the kernel, by index
 
 
 def gemm_set_pairs(mode: int) -> None:
