@@ -304,7 +304,6 @@ __global__ __launch_bounds__(NW * 32 + 32) void attn_stream_kernel(const __grid_
                 const int n_tiles = m[M_TILES];
                 if (n_tiles == 0) continue;
                 const int k_begin = m[M_K_BEGIN], k_end = m[M_K_END], t_first = m[M_PB_LO] * ps;
-                const int pos = k_end - 1;
                 float o[ND][4];
 #pragma unroll
                 for (int d = 0; d < ND; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
@@ -418,7 +417,7 @@ __global__ __launch_bounds__(NW * 32 + 32) void attn_stream_kernel(const __grid_
                 }
                 if (!ok) break;
                 // ---- the four warps' partial results -> shared memory, merged, written ----
-                float* po = o_s;
+                float* po = o_s;      // [warp][row][HD] partial outputs, [warp][row][2] their maxima and sums
                 float* pml = ml_s;
                 // every warp has read the pair before (a wait that is over long since: that pair's tiles lie between)
                 ok = mbar_wait(merge_empty, ((uint32_t)done & 1u) ^ 1u, abort_flag, a.status);
@@ -466,7 +465,6 @@ __global__ __launch_bounds__(NW * 32 + 32) void attn_stream_kernel(const __grid_
                 __syncwarp();
                 if (lane == 0) mbar_arrive(merge_empty);
                 ++done;
-                (void)pos;
             }
             if (!ok) break;
             __syncwarp();
